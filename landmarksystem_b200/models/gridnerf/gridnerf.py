@@ -1,0 +1,482 @@
+"""GridNeRF: VM feature grids + tiny MLP heads, rendered by volume compositing.
+
+Model-zoo counterpart of the reference's ``benchmarks/nerf/gridnerf/gridnerf.py`` (config :33-134,
+decoder heads :137-197, model :200-928).  Same configuration fields, parameter names and checkpoint
+keys; the forward pass is organised around flat ``[R*S]`` sample tensors that feed the channels-last
+lookup kernel, the fused MLP and the warp-scan compositor instead of masked gathers over a packed
+sample struct.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import List, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+from torch import nn
+from typing_extensions import Literal
+
+from ...components.data.rays import Rays
+from ...components.fields.alpha_mask import AlphaGridMask
+from ...components.fields.embedding import AppearanceEmbedding
+from ...components.fields.encodings.base_encoding import VolumeEncoding
+from ...components.fields.encodings.tensor_vm_encoding import TensorVMEncoding
+from ...components.fields.mlp_decoder import MLPDecoder, positional_encoding
+from ...components.fields.nerf_branch import NeRF, raw2outputs
+from ...components.model.base_model import BaseNeRF
+from ...components.ray_samplers import PDFSampler, UniformSampler
+from ...components.renderers import VolumeRenderer
+from ...components.utils.loss_utils import eff_distloss
+from ...configs import ConfigClass
+
+
+class GridNeRFConfig(ConfigClass):
+    """Model hyper-parameters (field names follow the reference config, gridnerf.py:33-134)."""
+
+    resMode: List[int] = [1]
+    encode_app: bool = False
+    run_nerf: bool = False
+    nerf_D: int = 6
+    nerf_D_a: int = 2
+    nerf_W: int = 128
+    nerf_freq: int = 16
+    n_importance: int = 128
+    nerf_n_importance: int = 16
+    nonlinear_density: bool = False
+    fea2denseAct: str = "relu"
+    n_lamb_sigma: List[int] = [16, 16, 16]
+    n_lamb_sh: List[int] = [48, 48, 48]
+    data_dim_color: int = 27
+    pos_pe: int = 6
+    view_pe: int = 6
+    fea_pe: int = 6
+    featureC: int = 128
+    density_shift: float = -10
+    ndims: int = 1
+    appearance_embedding_size: int = 1
+    add_upsample: int = -1
+    add_lpips: int = -1
+    add_nerf: int = -1
+    add_distort: int = -1
+    patch_size: int = 128
+    residnerf: bool = False
+    train_near_far: list = [0.1, 10.0]
+    lr_init: float = 0.02
+    lr_basis: float = 1e-3
+    lr_decay_iters: int = -1
+    lr_decay_target_ratio: float = 0.1
+    lr_upsample_reset: bool = True
+    L1_weight_inital: float = 0.0
+    L1_weight_rest: float = 0.0
+    Ortho_weight: float = 0.0
+    TV_weight_density: float = 0.0
+    TV_weight_app: float = 0.0
+    alpha_mask_thre: float = 0.0001
+    nSamples: int = int(1e6)
+    step_ratio: float = 0.5
+    N_voxel_init: int = 100 ** 3
+    N_voxel_final: int = 300 ** 3
+    upsamp_list: list = []
+    update_AlphaMask_list: list = []
+    progressive_alpha: int = 0
+    alpha_grid_reso: int = 256 ** 3
+    rayMarch_weight_thres: float = 0.001
+    render_px: int = 720
+    render_fov: float = 65.0
+    render_nframes: int = 100
+    render_skip: int = 1
+    render_fps: int = 30
+    render_spherical: bool = False
+    render_spherical_zdiff: float = 1.0
+    render_spherical_radius: float = 4.0
+    render_downward: float = -45.0
+    render_ncircle: float = 1
+    render_path: bool = False
+    render_pathid: int = 0
+    render_near_far: Optional[list] = None
+    render_lb: Optional[list] = None
+    render_ub: Optional[list] = None
+    render_batch_size: int = 8192
+    distance_scale: float = 25
+    sampling_opt: bool = False
+    alpha_mask_filter_thre: float = 0
+    white_bkgd: bool = False
+    dynamic_fetching: bool = False
+    neighbour_size: int = 9
+    camera: str = "normal"
+    rm_weight_mask_thre: float = 0.0
+    runtime: Literal["Torch", "Kernel"] = "Torch"
+    # additions of this framework (defaults keep the reference behaviour)
+    grid_dtype: Literal["fp32", "bf16"] = "fp32"  # bf16: kernels read bf16 shadows of fp32 master grids
+    fused_optimizer: bool = True
+
+    def check_args(self) -> None:
+        super().check_args()
+        assert self.ndims in (1, 2, 3)
+        assert self.fea2denseAct in ("relu", "softplus")
+
+
+class RGBDecoder(nn.Module):
+    """``basis_mat`` projection of the appearance feature, sin/cos encodings of it and of the view
+    direction, then a 3-layer MLP with a sigmoid (reference: gridnerf.py:137-174)."""
+
+    def __init__(self, n_component, resMode, app_dim, view_pe=6, fea_pe=6, featureC=128, encode_app=False) -> None:
+        super().__init__()
+        self.basis_mat = nn.Linear(sum(n_component) * len(resMode), app_dim, bias=False)
+        self.encode_app, self.viewpe, self.feape, self.app_dim = encode_app, view_pe, fea_pe, app_dim
+        in_mlp = 2 * max(view_pe, 0) * 3 + 2 * fea_pe * app_dim + 3 * (view_pe > -1) + app_dim + (48 if encode_app else 0)
+        self.decoder = MLPDecoder(inChanel=in_mlp, layer_width=featureC, num_layers=3, out_dim=3,
+                                  out_activation=nn.Sigmoid())
+
+    def forward(self, samples_dir, app_features, app_latent=None):
+        if app_features.is_cuda and app_latent is None and getattr(self, "use_fused", False):
+            from ...ops.fused_mlp import rgb_decoder_forward, rgb_decoder_supported
+
+            if rgb_decoder_supported(self):
+                return rgb_decoder_forward(self, samples_dir, app_features)
+        f = self.basis_mat(app_features.to(self.basis_mat.weight.dtype))
+        parts = [f]
+        if self.encode_app and app_latent is not None:
+            parts.append(app_latent)
+        if self.viewpe > -1:
+            parts.append(samples_dir)
+        if self.feape > 0:
+            parts.append(positional_encoding(f, self.feape))
+        if self.viewpe > 0:
+            parts.append(positional_encoding(samples_dir, self.viewpe))
+        return self.decoder(torch.cat(parts, dim=-1))
+
+
+class _ShiftedSoftplus(nn.Module):
+    def __init__(self, shift: float):
+        super().__init__()
+        self.shift = shift
+
+    def forward(self, x):
+        return F.softplus(x + self.shift)
+
+
+class Feature2Density(nn.Module):
+    """Density head (reference: gridnerf.py:177-197).  The reference's softplus branch appends a
+    lambda to ``nn.Sequential``, which cannot run; a proper shifted-softplus module is used here."""
+
+    def __init__(self, sum_n_component, resModeLen, nonlinear_density, density_shift, fea2denseAct):
+        super().__init__()
+        layers = []
+        if nonlinear_density:
+            layers += [nn.Linear(sum_n_component * resModeLen, 1, bias=False), nn.ReLU()]
+        self.nonlinear = nonlinear_density
+        layers.append(nn.ReLU() if fea2denseAct == "relu" else _ShiftedSoftplus(density_shift))
+        self.feature2density = nn.Sequential(*layers)
+
+    def forward(self, sigma_feature):
+        if not self.nonlinear:
+            sigma_feature = sigma_feature.sum(dim=-1, keepdim=True)
+        return self.feature2density(sigma_feature)
+
+
+def n_to_reso(n_voxels, bbox):
+    xyz_min, xyz_max = bbox
+    voxel = ((xyz_max - xyz_min).prod() / n_voxels).pow(1 / len(xyz_min))
+    return ((xyz_max - xyz_min) / voxel).long().tolist()
+
+
+def cal_n_samples(reso, step_ratio=0.5):
+    return int(np.linalg.norm(reso) / step_ratio)
+
+
+class GridNeRF(BaseNeRF):
+    def __init__(self, aabb, gridSize, device, alphaMask=None, near_far=(2.0, 6.0), scene_manager=None,
+                 grid_shape=None, config=None):
+        super().__init__(config, scene_manager, aabb=aabb, gridSize=gridSize, device=device, alphaMask=alphaMask,
+                         grid_shape=grid_shape, near_far=list(near_far))
+        self.aabb = torch.as_tensor(aabb, dtype=torch.float32, device=device)
+        self.run_nerf = config.run_nerf
+        self.density_n_comp = config.n_lamb_sigma[: config.ndims]
+        self.app_n_comp = config.n_lamb_sh[: config.ndims]
+        self.app_dim = config.data_dim_color
+        self.plane_division = getattr(config, "plane_division", [1, 1])
+        self.sigma_batch = self.app_batch = self.nerf_batch = None
+        self.update_stepSize(gridSize)
+        self.init_field_components()
+        self.init_sampler()
+        self.init_renderer()
+
+    # -- construction -------------------------------------------------------------------
+    def init_sampler(self):
+        self.sampler = UniformSampler(num_samples=self.nSamples, step_size=self.stepSize, aabb=self.aabb,
+                                      near_far=self.near_far)
+        self.pdf_sampler = PDFSampler(num_samples=self.config.nerf_n_importance)
+
+    def _local_blocks(self) -> int:
+        sm = self.scene_manager
+        if getattr(self.config, "branch_parallel", False) and getattr(self.config, "is_train", False):
+            return 1  # each model-parallel rank owns exactly one spatial block
+        return sm.n_local_blocks if sm is not None else 1
+
+    def init_field_components(self):
+        cfg = self.config
+        part = self.scene_manager.block_partition.tolist() if self.scene_manager is not None else [1, 1]
+        grid = [int(v) for v in self.gridSize]
+        grid[0], grid[1] = grid[0] // part[0], grid[1] // part[1]
+        n_blocks = self._local_blocks()
+        shapes = self.grid_shape or {}
+        self.density_encoding = TensorVMEncoding(cfg.ndims, cfg.resMode, cfg.n_lamb_sigma, grid, self.device,
+                                                 param_shape=shapes.get("density_encoding"), n_blocks=n_blocks)
+        self.rgb_encoding = TensorVMEncoding(cfg.ndims, cfg.resMode, cfg.n_lamb_sh, grid, self.device,
+                                             param_shape=shapes.get("rgb_encoding"), n_blocks=n_blocks)
+        self.feature2density = Feature2Density(sum(self.density_encoding.n_component), len(cfg.resMode),
+                                               cfg.nonlinear_density, cfg.density_shift, cfg.fea2denseAct).to(self.device)
+        self.rgb_decoder = RGBDecoder(self.rgb_encoding.n_component, cfg.resMode, self.app_dim, cfg.view_pe,
+                                      cfg.fea_pe, cfg.featureC, cfg.encode_app).to(self.device)
+        if cfg.encode_app:
+            self.embedding_app = AppearanceEmbedding(cfg.appearance_embedding_size, self.app_n_comp[0], self.device)
+        if cfg.add_nerf > 0 or self.run_nerf:
+            self.init_nerf()
+        if cfg.grid_dtype == "bf16" and torch.device(self.device).type == "cuda":
+            self.enable_shadow()
+
+    def enable_shadow(self):
+        self.density_encoding.enable_shadow(self.config.fused_optimizer)
+        self.rgb_encoding.enable_shadow(self.config.fused_optimizer)
+
+    def init_renderer(self):
+        self.renderer = VolumeRenderer(white_bg=self.config.white_bkgd)
+
+    def init_nerf(self):
+        cfg = self.config
+        self.nerf = NeRF(cfg, sum(self.density_n_comp) * len(cfg.resMode),
+                         sum(self.app_n_comp) * len(cfg.resMode)).to(self.device)
+        self.residnerf = cfg.residnerf
+        self.nerf_n_importance = cfg.nerf_n_importance
+
+    def channel_last(self):
+        self.density_encoding.channel_last()
+        self.rgb_encoding.channel_last()
+
+    def update_stepSize(self, gridSize):
+        cfg = self.config
+        self.aabbSize = self.aabb[1] - self.aabb[0]
+        self.invaabbSize = 2.0 / self.aabbSize
+        self.gridSize = torch.as_tensor([int(v) for v in gridSize], device=self.aabb.device)
+        self.units = self.aabbSize / (self.gridSize - 1)
+        self.stepSize = float(torch.mean(self.units) * cfg.step_ratio)
+        self.aabbDiag = float(torch.sqrt(torch.sum(torch.square(self.aabbSize))))
+        self.nSamples = int(self.aabbDiag / self.stepSize) + 1
+
+    # -- field queries ------------------------------------------------------------------
+    def _xyzb(self, xyz: torch.Tensor, valid: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """World xyz ``[N, 3]`` -> kernel coordinates ``[N, 4]`` (block-local xyz, block id or -1)."""
+        local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
+        if valid is not None:
+            block = torch.where(valid, block, torch.full_like(block, -1.0))
+        if getattr(self.config, "branch_parallel", False) and getattr(self.config, "is_train", False):
+            # this rank stores only its own block (index 0 locally); others are looked up remotely
+            mine = block == float(self.config.mp_rank)
+            self._owner = block
+            block = torch.where(mine, torch.zeros_like(block), torch.full_like(block, -1.0))
+        return torch.cat((local, block[:, None]), dim=-1)
+
+    def _density(self, xyzb: torch.Tensor) -> torch.Tensor:
+        feat = self.density_encoding(xyzb)
+        return self.feature2density(feat).squeeze(-1).float()
+
+    def _rgb(self, xyzb, dirs, app_latent=None) -> torch.Tensor:
+        feat = self.rgb_encoding(xyzb)
+        return self.rgb_decoder(dirs, feat, app_latent).float()
+
+    def compute_alpha(self, xyz_locs: torch.Tensor, length: float = 1.0) -> torch.Tensor:
+        valid = None
+        if self.alphaMask is not None:
+            valid = self.alphaMask.sample_alpha(xyz_locs) > 0
+        sigma = self._density(self._xyzb(xyz_locs, valid))
+        sigma = self._mp_sum(sigma)
+        return 1.0 - torch.exp(-sigma * length)
+
+    def _mp_sum(self, t: torch.Tensor) -> torch.Tensor:
+        """Branch parallel: every sample is evaluated by exactly one rank (zeros elsewhere), so the
+        exchange of the reference's ``sync_sigma``/``sync_rgb`` is a sum over the MP group whose
+        backward is the identity on the local contribution."""
+        if getattr(self.config, "branch_parallel", False) and getattr(self.config, "is_train", False):
+            from ...comm.autograd import all_reduce_sum_local_grad
+
+            return all_reduce_sum_local_grad(t, self.config.mp_group)
+        return t
+
+    @torch.no_grad()
+    def getDenseAlpha(self, gridSize=None):
+        gridSize = [int(v) for v in (self.gridSize if gridSize is None else gridSize)]
+        lin = [torch.linspace(0, 1, g, device=self.aabb.device) for g in gridSize]
+        samples = torch.stack(torch.meshgrid(*lin, indexing="ij"), -1)
+        dense_xyz = self.aabb[0] * (1 - samples) + self.aabb[1] * samples
+        alpha = torch.zeros_like(dense_xyz[..., 0])
+        for i in range(gridSize[0]):
+            alpha[i] = self.compute_alpha(dense_xyz[i].reshape(-1, 3), self.stepSize).view(gridSize[1], gridSize[2])
+        return alpha, dense_xyz
+
+    @torch.no_grad()
+    def updateAlphaMask(self, gridSize=(200, 200, 200), increase_alpha_thresh=0):
+        cfg = self.config
+        gridSize = [int(v) for v in gridSize]
+        alpha, dense_xyz = self.getDenseAlpha(gridSize)
+        dense_xyz = dense_xyz.transpose(0, 2).contiguous()
+        alpha = alpha.clamp(0, 1).transpose(0, 2).contiguous()[None, None]
+        alpha = F.max_pool3d(alpha, kernel_size=3, padding=1, stride=1).view(gridSize[::-1])
+        thre = cfg.alpha_mask_thre * (10 ** increase_alpha_thresh)
+        alpha = (alpha >= thre).float()
+        self.alphaMask = AlphaGridMask(self.device, self.aabb, alpha)
+        valid_xyz = dense_xyz[alpha > 0.5]
+        if valid_xyz.numel() == 0:
+            return self.aabb.clone()
+        return torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
+
+    def distortion_loss(self, weight, z_vals, dists):
+        mids = 0.5 * (z_vals[:, 1:] + z_vals[:, :-1])
+        m = torch.cat((mids, mids[:, -1:]), dim=-1)
+        return 0.01 * eff_distloss(weight, m, dists).unsqueeze(0)
+
+    # -- forward --------------------------------------------------------------------------
+    def _grid_pass(self, rays: torch.Tensor, n_samples: int, hull: bool, app_code=None):
+        """One sampling + density + weights + colour + composite pass over ``rays [R, 7]``."""
+        cfg = self.config
+        train = bool(cfg.is_train)
+        z = self.sampler.compute_z_vals(rays, n_samples if n_samples > 0 else self.sampler.num_samples, train, hull)
+        R, S = z.shape
+        origin, dirs = rays[:, :3], rays[:, 3:6]
+        xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
+        valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
+        if self.alphaMask is not None:
+            valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
+        xyzb = self._xyzb(xyz, valid)
+        self.sigma_batch = (xyzb[:, 3] >= 0).sum()
+        sigma = self._mp_sum(self._density(xyzb)).view(R, S)
+        dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
+        weight = self.renderer.get_weights(sigma, dists * cfg.distance_scale)
+        app_mask = (weight > cfg.rayMarch_weight_thres).reshape(-1)
+        rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)
+        idx = app_mask.nonzero(as_tuple=True)[0]
+        self.app_batch = (xyzb[idx, 3] >= 0).sum()
+        if idx.numel() > 0 or (train and getattr(cfg, "branch_parallel", False)):
+            if idx.numel() == 0:
+                idx = torch.zeros(1, dtype=torch.long, device=rays.device)  # keep every rank's graph alive
+            ray_of = idx // S
+            latent = None
+            if cfg.encode_app:
+                cam = rays[ray_of, 6].long() if app_code is None else None
+                latent = self.embedding_app(cam, xyz[idx], app_code)
+            vals = self._rgb(xyzb[idx], dirs[ray_of], latent)
+            vals = vals * (xyzb[idx, 3:4] >= 0).to(vals.dtype)
+            rgb = rgb.index_put((idx,), vals)
+        rgb = self._mp_sum(rgb)
+        rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
+        return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists
+
+    def forward(self, rays_chunk, app_code=None, N_samples=-1):
+        cfg = self.config
+        rays = rays_chunk.data if isinstance(rays_chunk, Rays) else rays_chunk
+        outputs = {}
+        dense = cfg.is_train or not cfg.sampling_opt
+        if dense:
+            rgb_map, depth_map, weight, app_mask, z, dists = self._grid_pass(rays, N_samples, False, app_code)
+            if not cfg.is_train:
+                outputs = (rgb_map, depth_map)
+            else:
+                outputs = {"rgb_map": rgb_map, "depth_map": depth_map,
+                           "distort_loss": self.distortion_loss(weight * app_mask, z, dists)}
+        if (not cfg.is_train and cfg.sampling_opt) or (cfg.is_train and self.run_nerf):
+            rgb_map, depth_map, weight, app_mask, z, dists = self._grid_pass(rays, cfg.n_importance, True, app_code)
+            if not cfg.is_train:
+                return rgb_map, depth_map
+            outputs.update({"rgb_map1": rgb_map, "depth_map1": depth_map,
+                            "distort_loss1": self.distortion_loss(weight * app_mask, z, dists)})
+            outputs.update(self._nerf_pass(rays, z, weight, rgb_map, app_code))
+        return outputs
+
+    def _nerf_pass(self, rays, z, weight, rgb_map, app_code):
+        cfg = self.config
+        samples = self.pdf_sampler(rays, z, weight[..., 1:-1].detach(), self.nerf_n_importance)
+        R, S = samples.shape
+        xyz = samples.xyz.reshape(-1, 3)
+        xyzb = self._xyzb(xyz)
+        self.nerf_batch = (xyzb[:, 3] >= 0).sum()
+        latent = self.embedding_app(samples.camera_idx.reshape(-1), xyz, app_code) if cfg.encode_app else None
+        den_feat = self.density_encoding(xyzb)
+        app_feat = self.rgb_encoding(xyzb)
+        raw = self.nerf(xyz, samples.dirs.reshape(-1, 3), den_feat, app_feat, latent).float()
+        raw = self._mp_sum(raw * (xyzb[:, 3:4] >= 0).to(raw.dtype)).view(R, S, 4)
+        extras = raw2outputs(raw, samples.dists)
+        depth = (extras["weights"] * samples.z_vals).sum(-1)
+        rgb = (extras["rgb_map"] + rgb_map).clamp(0.0, 1.0) if self.residnerf else extras["rgb_map"]
+        return {"rgb_map_nerf": rgb, "depth_map_nerf": depth}
+
+    def render_all_rays(self, rays, chunk_size: Optional[int] = None, N_samples=-1, idxs=None, app_code=0):
+        n_total = rays.shape[0]
+        chunk_size = chunk_size or n_total
+        if idxs is None:
+            idxs = torch.zeros(n_total, device=rays.device)
+        collected = {}
+        for start in range(0, n_total, chunk_size):
+            chunk = rays[start:start + chunk_size]
+            if chunk.shape[-1] == 6:
+                chunk = torch.cat((chunk, idxs[start:start + chunk_size, None].to(chunk.dtype)), dim=-1)
+            ret = self.forward(chunk, N_samples=N_samples)
+            if not isinstance(ret, dict):
+                ret = {"rgb_map": ret[0], "depth_map": ret[1]}
+            for key, value in ret.items():
+                collected.setdefault(key, []).append(value)
+        return {k: torch.cat(v, 0) for k, v in collected.items()}
+
+    # -- optimisation ----------------------------------------------------------------------
+    def get_optparam_groups(self, lr_init_spatial=0.02, lr_init_network=0.001):
+        groups = [
+            {"params": list(self.density_encoding.parameters()), "lr": lr_init_spatial},
+            {"params": list(self.rgb_encoding.parameters()), "lr": lr_init_spatial},
+            {"params": list(self.feature2density.parameters()), "lr": lr_init_network},
+            {"params": list(self.rgb_decoder.parameters()), "lr": lr_init_network},
+        ]
+        if self.config.encode_app:
+            groups.append({"params": list(self.embedding_app.parameters()), "lr": lr_init_network})
+        if self.run_nerf or hasattr(self, "nerf"):
+            groups.append({"params": list(self.nerf.parameters()), "lr": 5e-4})
+        return [g for g in groups if len(g["params"]) > 0]
+
+    @torch.no_grad()
+    def upsample_volume_grid(self, res_target):
+        part = self.scene_manager.block_partition.tolist()
+        grid = [int(v) for v in res_target]
+        grid[0], grid[1] = grid[0] // part[0], grid[1] // part[1]
+        self.density_encoding.upsample_volume_grid(grid)
+        self.rgb_encoding.upsample_volume_grid(grid)
+        self.update_stepSize(res_target)
+        self.sampler.step_size = self.stepSize
+        self.sampler.num_samples = self.nSamples
+
+    # -- checkpoints ---------------------------------------------------------------------------
+    def kwargs(self):
+        kw = super().kwargs()
+        kw["aabb"] = self.aabb
+        kw["gridSize"] = self.gridSize.tolist()
+        kw["alphaMask"] = self.alphaMask
+        return kw
+
+    def merge_ckpts(self, ckpt_fp_list, kwargs_fp_list, map_location="cpu"):
+        """Merge per-rank ``state_dict-sub{r}.th`` files into one block-stacked state dict and the
+        matching kwargs (with ``grid_shape``), as written by branch-parallel training."""
+        states = [torch.load(fp, map_location=map_location, weights_only=False) for fp in ckpt_fp_list]
+        kwargs = torch.load(kwargs_fp_list[0], map_location=map_location, weights_only=False)
+        merged, grid_shape = OrderedDict(), OrderedDict()
+        for name, module in self.named_children():
+            keys = [k for k in states[0].keys() if k.split(".")[0] == name]
+            if isinstance(module, VolumeEncoding):
+                part = module.merge_state_dicts([{k: sd[k] for k in keys} for sd in states], device=map_location)
+                merged.update(part)
+                grid_shape[name] = {k[len(name) + 1:]: list(v.shape) for k, v in part.items()}
+            else:
+                for k in keys:
+                    merged[k] = states[0][k]
+        kwargs["grid_shape"] = grid_shape
+        return merged, kwargs
+
+    def edit_model(self, edit_mode: dict):
+        return None

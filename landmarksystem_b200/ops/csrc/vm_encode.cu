@@ -1,0 +1,179 @@
+// VM (vector-matrix) feature-grid lookup for GridNeRF-style fields, forward and backward.
+//
+// A sample carries block-local coordinates (x, y, z) in [-1, 1] and the index b of the spatial
+// block that owns it.  For every resolution level l the feature is
+//     bilinear(plane_l[b], x, y)  *  linear(line_l[b], z)          (element-wise over C channels)
+// with align_corners=True / zero-padding semantics, and levels are concatenated: out[n, l*C + c].
+// This is the math of the reference's 5-D/4-D F.grid_sample pair followed by the product
+// (landmark/nerf_components/model_components/fields/encodings/tensor_vm_encoding.py:129-197) and of
+// its channels-last kernel (landmark/ops/kernel/densityappfeature/grid_sampler_3d_ndhwc_kernel.cu:206-369),
+// re-designed around the memory system: planes are stored channels-last [B, H, W, C] so one texel
+// is one or three 32-byte sectors, each thread moves 8 channels with a single 16-byte load, and the
+// plane * line product and the level concat are fused so no intermediate ever reaches HBM.
+#include "common.cuh"
+
+namespace lmb {
+
+struct VMLevels {
+  const void* plane[kMaxLevels];  // [B, H, W, C]
+  const void* line[kMaxLevels];   // [B, Z, C]
+  float* gplane[kMaxLevels];      // fp32 gradient accumulators, same shapes (backward only)
+  float* gline[kMaxLevels];
+  int H[kMaxLevels], W[kMaxLevels], Z[kMaxLevels];
+  int L, C, B;
+};
+
+struct Corner2 {
+  int i0, i1;
+  float w0, w1;  // weights already zeroed for out-of-range taps
+};
+
+__device__ __forceinline__ Corner2 taps(float u, int size) {
+  // u in [-1, 1] -> continuous index in [0, size-1] (align_corners=True); zero padding outside.
+  float f = (u + 1.f) * 0.5f * (float)(size - 1);
+  float fl = floorf(f);
+  int i0 = (int)fl;
+  float t = f - fl;
+  Corner2 c;
+  c.i0 = i0; c.i1 = i0 + 1;
+  c.w0 = (i0 >= 0 && i0 < size) ? 1.f - t : 0.f;
+  c.w1 = (c.i1 >= 0 && c.i1 < size) ? t : 0.f;
+  c.i0 = min(max(c.i0, 0), size - 1);
+  c.i1 = min(max(c.i1, 0), size - 1);
+  return c;
+}
+
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(256)
+vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n,
+                     VMLevels lv, OutT* __restrict__ out) {
+  const int CH = lv.C >> 3;
+  const long long n_valid = resolve_count(count_ptr, max_n);
+  long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long n = tid / CH;
+  int ch = (int)(tid - n * CH);
+  if (n >= n_valid) return;
+  float4 q = __ldg(coords + n);
+  int b = (int)q.w;
+  const int out_stride = lv.L * lv.C;
+  if (b < 0 || b >= lv.B) {
+    F8 z;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) z.v[i] = 0.f;
+    for (int l = 0; l < lv.L; ++l) store8(out + n * out_stride + l * lv.C + ch * 8, z);
+    return;
+  }
+  for (int l = 0; l < lv.L; ++l) {
+    const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+    Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
+    const T* pl = reinterpret_cast<const T*>(lv.plane[l]) + ((long long)b * H * W) * lv.C + ch * 8;
+    const T* ln = reinterpret_cast<const T*>(lv.line[l]) + ((long long)b * Z) * lv.C + ch * 8;
+    F8 p00 = load8(pl + ((long long)cy.i0 * W + cx.i0) * lv.C);
+    F8 p01 = load8(pl + ((long long)cy.i0 * W + cx.i1) * lv.C);
+    F8 p10 = load8(pl + ((long long)cy.i1 * W + cx.i0) * lv.C);
+    F8 p11 = load8(pl + ((long long)cy.i1 * W + cx.i1) * lv.C);
+    F8 l0 = load8(ln + (long long)cz.i0 * lv.C);
+    F8 l1 = load8(ln + (long long)cz.i1 * lv.C);
+    const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+    F8 f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float pv = w00 * p00.v[i] + w01 * p01.v[i] + w10 * p10.v[i] + w11 * p11.v[i];
+      float lvv = cz.w0 * l0.v[i] + cz.w1 * l1.v[i];
+      f.v[i] = pv * lvv;
+    }
+    store8(out + n * out_stride + l * lv.C + ch * 8, f);
+  }
+}
+
+// Backward: recompute the taps and both interpolants, then push d(plane) and d(line) with
+// 16-byte vector reductions into the fp32 accumulators.
+template <typename T, typename GT>
+__global__ void __launch_bounds__(256)
+vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n,
+                     VMLevels lv, const GT* __restrict__ dout) {
+  const int CH = lv.C >> 3;
+  const long long n_valid = resolve_count(count_ptr, max_n);
+  long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long n = tid / CH;
+  int ch = (int)(tid - n * CH);
+  if (n >= n_valid) return;
+  float4 q = __ldg(coords + n);
+  int b = (int)q.w;
+  if (b < 0 || b >= lv.B) return;
+  const int out_stride = lv.L * lv.C;
+  for (int l = 0; l < lv.L; ++l) {
+    const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+    Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
+    const long long pbase = ((long long)b * H * W) * lv.C + ch * 8;
+    const long long lbase = ((long long)b * Z) * lv.C + ch * 8;
+    const T* pl = reinterpret_cast<const T*>(lv.plane[l]) + pbase;
+    const T* ln = reinterpret_cast<const T*>(lv.line[l]) + lbase;
+    const long long o00 = ((long long)cy.i0 * W + cx.i0) * lv.C, o01 = ((long long)cy.i0 * W + cx.i1) * lv.C;
+    const long long o10 = ((long long)cy.i1 * W + cx.i0) * lv.C, o11 = ((long long)cy.i1 * W + cx.i1) * lv.C;
+    F8 p00 = load8(pl + o00), p01 = load8(pl + o01), p10 = load8(pl + o10), p11 = load8(pl + o11);
+    F8 l0 = load8(ln + (long long)cz.i0 * lv.C), l1 = load8(ln + (long long)cz.i1 * lv.C);
+    F8 g = load8(dout + n * out_stride + l * lv.C + ch * 8);
+    const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+    F8 dp, dl;
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float pv = w00 * p00.v[i] + w01 * p01.v[i] + w10 * p10.v[i] + w11 * p11.v[i];
+      float lvv = cz.w0 * l0.v[i] + cz.w1 * l1.v[i];
+      dp.v[i] = g.v[i] * lvv;
+      dl.v[i] = g.v[i] * pv;
+      any |= (g.v[i] != 0.f);
+    }
+    if (!any) continue;
+    float* gp = lv.gplane[l] + pbase;
+    float* gl = lv.gline[l] + lbase;
+    if (w00 != 0.f) red_add8(gp + o00, dp, w00);
+    if (w01 != 0.f) red_add8(gp + o01, dp, w01);
+    if (w10 != 0.f) red_add8(gp + o10, dp, w10);
+    if (w11 != 0.f) red_add8(gp + o11, dp, w11);
+    if (cz.w0 != 0.f) red_add8(gl + (long long)cz.i0 * lv.C, dl, cz.w0);
+    if (cz.w1 != 0.f) red_add8(gl + (long long)cz.i1 * lv.C, dl, cz.w1);
+  }
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+// param_dtype / io_dtype: 0 = fp32, 1 = bf16.
+LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
+                              int param_dtype, void* out, int out_dtype, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
+  const int CH = levels->C / 8;
+  const int threads = 256;
+  const int blocks = ceil_div(max_n * CH, threads);
+  const float4* c4 = reinterpret_cast<const float4*>(coords);
+#define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out)
+  if (param_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
+  else if (param_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  else if (param_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_vm_encode_bwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
+                              int param_dtype, const void* dout, int dout_dtype, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
+  const int CH = levels->C / 8;
+  const int threads = 256;
+  const int blocks = ceil_div(max_n * CH, threads);
+  const float4* c4 = reinterpret_cast<const float4*>(coords);
+#define LAUNCH(T, G) vm_encode_bwd_kernel<T, G><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (const G*)dout)
+  if (param_dtype == 0 && dout_dtype == 0) LAUNCH(float, float);
+  else if (param_dtype == 0 && dout_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  else if (param_dtype == 1 && dout_dtype == 0) LAUNCH(__nv_bfloat16, float);
+  else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  LMB_LAUNCH_CHECK();
+  return 0;
+}

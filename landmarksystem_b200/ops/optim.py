@@ -1,0 +1,79 @@
+"""Fused Adam with fp32 master weights, optional bf16 shadow copies and in-kernel gradient reset.
+
+Replaces ``torch.optim.Adam`` + ``zero_grad`` of the reference trainers
+(benchmarks/nerf/gridnerf/gridnerf_trainer.py:127-154, 296-322) with one HBM pass per tensor.
+On CPU tensors the same update is written with torch ops so that tests can compare the two.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional
+
+import torch
+
+from . import native
+
+
+class FusedAdam(torch.optim.Optimizer):
+    """Adam (no amsgrad).  Per-group options: ``lr, betas, eps, weight_decay``.
+
+    A parameter may carry two optional attributes that the fused path honours:
+
+    * ``_lmb_grad_sink`` - persistent fp32 gradient accumulator written directly by backward kernels
+      (then ``.grad`` is unused and never allocated);
+    * ``_lmb_shadow`` - bf16 copy of the parameter, refreshed in the same kernel that updates it.
+    """
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+
+    @staticmethod
+    def attach_sink(param: torch.Tensor, shadow: bool = False) -> None:
+        """Give ``param`` a persistent zeroed fp32 accumulator (and a bf16 shadow if asked)."""
+        param._lmb_grad_sink = torch.zeros_like(param, dtype=torch.float32)
+        if shadow:
+            param._lmb_shadow = param.detach().to(torch.bfloat16)
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: float = 1.0):
+        loss = closure() if closure is not None else None
+        for group in self.param_groups:
+            beta1, beta2 = group["betas"]
+            for p in group["params"]:
+                sink = getattr(p, "_lmb_grad_sink", None)
+                grad = sink if sink is not None else p.grad
+                if grad is None:
+                    continue
+                state = self.state[p]
+                if not state:
+                    state["step"] = 0
+                    state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                state["step"] += 1
+                shadow = getattr(p, "_lmb_shadow", None)
+                if p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
+                        and grad.dtype == torch.float32:
+                    native.check(native.lib().lmb_adam_step(
+                        p.data_ptr(), grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
+                        native.ptr(shadow), p.numel(), group["lr"], beta1, beta2, group["eps"], state["step"],
+                        grad_scale, group["weight_decay"], native.stream_ptr()), "adam_step")
+                else:
+                    g = grad.float() * grad_scale + group["weight_decay"] * p
+                    state["exp_avg"].mul_(beta1).add_(g, alpha=1 - beta1)
+                    state["exp_avg_sq"].mul_(beta2).addcmul_(g, g, value=1 - beta2)
+                    b1 = 1 - beta1 ** state["step"]
+                    b2 = 1 - beta2 ** state["step"]
+                    denom = (state["exp_avg_sq"] / b2).sqrt_().add_(group["eps"])
+                    p.addcdiv_(state["exp_avg"], denom, value=-group["lr"] / b1)
+                    grad.zero_()
+                    if shadow is not None:
+                        shadow.copy_(p)
+        return loss
+
+    def zero_grad(self, set_to_none: bool = True):  # gradients are cleared inside step()
+        for group in self.param_groups:
+            for p in group["params"]:
+                if getattr(p, "_lmb_grad_sink", None) is None and p.grad is not None:
+                    if set_to_none:
+                        p.grad = None
+                    else:
+                        p.grad.zero_()

@@ -1,0 +1,133 @@
+"""VM feature-grid lookup op: CUDA kernel on GPU tensors, PyTorch math on CPU tensors.
+
+Layout contract (channels-last): ``planes[l]`` is ``[B, H_l, W_l, C]``, ``lines[l]`` is
+``[B, Z_l, C]``; ``coords`` is ``[N, 4]`` fp32 = block-local ``(x, y, z)`` in ``[-1, 1]`` plus the
+block index (negative = sample is outside every block → zero features, zero gradient).
+Output is ``[N, L*C]`` with level-major channel order, i.e. the concat-over-levels of
+``plane ⊙ line`` that the reference builds from two ``F.grid_sample`` calls per level
+(landmark/nerf_components/model_components/fields/encodings/tensor_vm_encoding.py:129-197).
+"""
+from __future__ import annotations
+
+from ctypes import byref
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import native
+
+
+def _taps(u: torch.Tensor, size: int):
+    f = (u + 1.0) * 0.5 * (size - 1)
+    i0 = torch.floor(f)
+    t = f - i0
+    i0 = i0.long()
+    i1 = i0 + 1
+    w0 = torch.where((i0 >= 0) & (i0 < size), 1.0 - t, torch.zeros_like(t))
+    w1 = torch.where((i1 >= 0) & (i1 < size), t, torch.zeros_like(t))
+    return i0.clamp(0, size - 1), i1.clamp(0, size - 1), w0, w1
+
+
+def vm_encode_reference(coords: torch.Tensor, planes: Sequence[torch.Tensor], lines: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Differentiable plain-PyTorch statement of the op (fp32 math); the numerics oracle."""
+    x, y, z, bf = coords.unbind(-1)
+    n_blocks = planes[0].shape[0]
+    b = bf.long()
+    ok = (b >= 0) & (b < n_blocks)
+    bc = b.clamp(0, n_blocks - 1)
+    feats = []
+    for plane, line in zip(planes, lines):
+        _, H, W, C = plane.shape
+        Z = line.shape[1]
+        x0, x1, wx0, wx1 = _taps(x, W)
+        y0, y1, wy0, wy1 = _taps(y, H)
+        z0, z1, wz0, wz1 = _taps(z, Z)
+        pf = plane.float()
+        lf = line.float()
+        pv = (pf[bc, y0, x0] * (wy0 * wx0)[:, None] + pf[bc, y0, x1] * (wy0 * wx1)[:, None]
+              + pf[bc, y1, x0] * (wy1 * wx0)[:, None] + pf[bc, y1, x1] * (wy1 * wx1)[:, None])
+        lv = lf[bc, z0] * wz0[:, None] + lf[bc, z1] * wz1[:, None]
+        feats.append(pv * lv * ok[:, None].to(pv.dtype))
+    return torch.cat(feats, dim=-1)
+
+
+def _levels_struct(planes, lines, gplanes=None, glines=None) -> native.VMLevels:
+    lv = native.VMLevels()
+    lv.L = len(planes)
+    lv.B, _, _, lv.C = planes[0].shape
+    for i, (p, l) in enumerate(zip(planes, lines)):
+        assert p.is_contiguous() and l.is_contiguous(), "VM grids must be contiguous channels-last tensors"
+        lv.plane[i] = p.data_ptr()
+        lv.line[i] = l.data_ptr()
+        lv.H[i], lv.W[i], lv.Z[i] = p.shape[1], p.shape[2], l.shape[1]
+        if gplanes is not None:
+            lv.gplane[i] = gplanes[i].data_ptr()
+            lv.gline[i] = glines[i].data_ptr()
+    return lv
+
+
+class _VMEncode(torch.autograd.Function):
+    """Inputs: coords, count (or None), out_dtype, n_levels, shadow flag, then 2*L master tensors
+    (planes..., lines...) and optionally 2*L bf16 shadow tensors that the kernels read instead."""
+
+    @staticmethod
+    def forward(ctx, coords, count, out_dtype, n_levels, *grids):
+        masters = grids[: 2 * n_levels]
+        shadows = grids[2 * n_levels:]
+        read = shadows if shadows else masters
+        planes, lines = list(read[:n_levels]), list(read[n_levels:])
+        N = coords.shape[0]
+        C = planes[0].shape[-1]
+        out = torch.empty((N, n_levels * C), device=coords.device, dtype=out_dtype)
+        if count is not None:
+            out.zero_()
+        lv = _levels_struct(planes, lines)
+        native.check(
+            native.lib().lmb_vm_encode_fwd(coords.data_ptr(), native.ptr(count), N, byref(lv),
+                                           native.DTYPE_CODE[planes[0].dtype], out.data_ptr(),
+                                           native.DTYPE_CODE[out_dtype], native.stream_ptr()),
+            "vm_encode_fwd")
+        ctx.save_for_backward(coords, count, *read)
+        ctx.n_levels = n_levels
+        ctx.masters = masters
+        ctx.n_shadow = len(shadows)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        coords, count, *read = ctx.saved_tensors
+        L = ctx.n_levels
+        planes, lines = read[:L], read[L:]
+        masters = ctx.masters
+        grads = []
+        sunk = []
+        for m in masters:
+            # A fused optimiser may attach a persistent, pre-zeroed fp32 accumulator (`_lmb_grad_sink`)
+            # to a parameter; the kernel then adds into it directly and autograd gets no tensor, which
+            # saves allocating and re-reading a multi-GB dense gradient every step.
+            sink = getattr(m, "_lmb_grad_sink", None)
+            sunk.append(sink is not None)
+            grads.append(sink if sink is not None else torch.zeros(m.shape, device=m.device, dtype=torch.float32))
+        lv = _levels_struct(planes, lines, grads[:L], grads[L:])
+        dout = dout.contiguous()
+        native.check(
+            native.lib().lmb_vm_encode_bwd(coords.data_ptr(), native.ptr(count), coords.shape[0], byref(lv),
+                                           native.DTYPE_CODE[planes[0].dtype], dout.data_ptr(),
+                                           native.DTYPE_CODE[dout.dtype], native.stream_ptr()),
+            "vm_encode_bwd")
+        out_grads = [None if s else g for s, g in zip(sunk, grads)]
+        return (None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+
+
+def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torch.Tensor],
+              shadow_planes: Optional[List[torch.Tensor]] = None, shadow_lines: Optional[List[torch.Tensor]] = None,
+              count: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Look up ``[N, L*C]`` features.  ``shadow_*`` (bf16 copies of the fp32 masters) are what the
+    CUDA kernels read when given; gradients always flow to the fp32 masters."""
+    if not coords.is_cuda:
+        return vm_encode_reference(coords, planes, lines).to(out_dtype)
+    coords = coords.contiguous().float()
+    grids = list(planes) + list(lines)
+    if shadow_planes is not None:
+        grids += list(shadow_planes) + list(shadow_lines)
+    return _VMEncode.apply(coords, count, out_dtype, len(planes), *grids)
