@@ -1,0 +1,207 @@
+"""Headline benchmark: GridNeRF large-scene training throughput (rays/s), weak scaling.
+
+``python bench.py --gpus N --steps K --warmup W`` (launched under ``torch.distributed.run`` for
+N > 1) trains the benchmark configuration (one 4096^2-plane block per GPU, 8192 rays per GPU, 128
+samples per ray, synthetic aerial rays, random-init weights) for W untimed + K timed steps and
+prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with batches already
+resident; ``e2e`` repeats the run through ``GridNeRFTrainer.train_step`` with a pinned-host ->
+device copy of every batch and a device -> host read of every loss inside the timed region.
+``--impl reference`` runs the unmodified reference trainer from ``baseline/_ref`` on the same
+configuration (see ``baseline/reference_arm.py``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DIVISIONS = {1: [1, 1], 2: [2, 1], 4: [2, 2], 8: [2, 4]}
+RAYS_PER_GPU = 8192
+SAMPLES = 128
+BLOCK_M = (1000.0, 1000.0, 300.0)
+PLANE, LINE = 4096, 512
+BASELINE_VALUE = None  # the reference publishes no throughput number
+
+
+def make_ray_pool(n_rays: int, lb, ub, seed: int):
+    """Synthetic aerial capture: random pixels of random nadir-ish 1920x1080 pinhole cameras 400 m
+    above the ground (tilt <= 30 deg); colours from a smooth procedural ground texture."""
+    import torch
+
+    from landmarksystem_b200.synthetic import aerial_cameras
+
+    g = torch.Generator().manual_seed(seed)
+    n_cam = 256
+    poses = aerial_cameras(n_cam, lb, ub, 400.0, 30.0, seed=seed)
+    cam = torch.randint(0, n_cam, (n_rays,), generator=g)
+    W, H, focal = 1920, 1080, 1662.8
+    i = torch.rand(n_rays, generator=g) * W
+    j = torch.rand(n_rays, generator=g) * H
+    dirs = torch.stack(((i - W / 2) / focal, -(j - H / 2) / focal, -torch.ones(n_rays)), -1)
+    R = poses[cam, :3, :3]
+    rays_d = torch.einsum("nij,nj->ni", R, dirs)
+    rays_d = rays_d / rays_d.norm(dim=-1, keepdim=True)
+    rays_o = poses[cam, :3, 3]
+    t = (lb[2] - rays_o[:, 2]) / rays_d[:, 2].clamp(max=-1e-3)
+    hit = rays_o + rays_d * t[:, None]
+    rgb = 0.5 + 0.5 * torch.stack((torch.sin(hit[:, 0] * 0.01), torch.sin(hit[:, 1] * 0.013),
+                                   torch.sin((hit[:, 0] + hit[:, 1]) * 0.007)), -1)
+    return torch.cat((rays_o, rays_d), -1).float(), rgb.float(), cam.float()
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        self.idx = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        self.tmp.flush()
+        rows = [r.split(", ") for r in open(self.tmp.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.tmp.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.gridnerf.gridnerf_trainer import GridNeRFTrainer
+    from landmarksystem_b200.ops import native
+
+    n = args.gpus
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    assert world == n, f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}"
+    nx, ny = DIVISIONS[n]
+    conf = os.path.join(ROOT, "landmarksystem_b200", "models", "gridnerf", "confs", "bench_branch_parallel.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": os.path.join(tempfile.gettempdir(), "lmb_bench")})
+    cfg.plane_division = [nx, ny]
+    cfg.ub = [BLOCK_M[0] * nx, BLOCK_M[1] * ny, BLOCK_M[2]]
+    cfg.init_grid_size = [PLANE * nx, PLANE * ny, LINE]
+    cfg.branch_parallel = n > 1
+    cfg.batch_size = RAYS_PER_GPU * n
+    trainer = GridNeRFTrainer(cfg)
+    trainer.model.train()
+    dev = trainer.config.device
+    steps, warmup = args.steps, args.warmup
+    global_batch = RAYS_PER_GPU * n
+    pool_steps = min(steps + warmup, 16)
+    # every rank sees the same global batch (seeded pool); model-parallel ranks evaluate their own block
+    rays, rgbs, idxs = make_ray_pool(global_batch * pool_steps, cfg.lb, cfg.ub, seed=1234)
+    host = torch.cat((rays, rgbs, idxs[:, None]), -1).view(pool_steps, global_batch, 10).pin_memory()
+    resident = host.to(dev)
+
+    def step_resident(k):
+        b = resident[k % pool_steps]
+        return trainer.train_step(b[:, :6], b[:, 6:9], b[:, 9])
+
+    def step_e2e(k):
+        b = host[k % pool_steps].to(dev, non_blocking=True)
+        return float(trainer.train_step(b[:, :6], b[:, 6:9], b[:, 9]))
+
+    def timed(fn, count):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for k in range(count):
+            fn(k)
+        end.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    for k in range(warmup):
+        step_resident(k)
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    launches0 = native.LAUNCH_CALLS
+    ms = timed(step_resident, steps)
+    launches = native.LAUNCH_CALLS - launches0
+    for k in range(min(warmup, 3)):
+        step_e2e(k)
+    ms_e2e = timed(step_e2e, steps)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        value = global_batch * steps / (ms / 1e3)
+        e2e = global_batch * steps / (ms_e2e / 1e3)
+        print(json.dumps({
+            "metric": "train rays/s", "value": value, "unit": "rays/s", "n_gpus": n, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "GridNeRF branch-parallel large scene", "global_batch": global_batch,
+                       "seq_len": SAMPLES, "parallelism": f"branch{nx}x{ny}" if n > 1 else "single",
+                       "planes": f"{PLANE}^2 x (16+48)ch bf16 + fp32 master per GPU", "lines": LINE,
+                       "l2_policy": "inputs larger than L2: 6.4 GB of plane parameters touched per step"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "rays/s", "ms_per_step": ms_e2e / steps,
+                    "h2d_bytes_per_step": global_batch * 10 * 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    assert args.gpus in DIVISIONS, "supported GPU counts: 1, 2, 4, 8"
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        run_reference(args, DIVISIONS, RAYS_PER_GPU, SAMPLES, BLOCK_M, PLANE, LINE, make_ray_pool, ClockSampler)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -214,3 +214,136 @@ class TensorVMEncoding(VolumeEncoding):
             else:
                 merged[key] = parts[0]
         return merged
+
+
+class ChannelParallelTensorVMEncoding(TensorVMEncoding):
+    """Feature channels split across the ranks of a group: each rank stores ``C / P`` channels of every
+    plane and line, looks all samples up on its slice and the per-level ``plane * line`` products are
+    all-gathered (reference: tensor_vm_encoding.py:335-551 gathers plane and line features separately,
+    i.e. twice the bytes).  ``init_state_dict`` (reference layout, full channels) seeds the slices."""
+
+    def __init__(self, ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
+                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None):
+        comps = list(n_component) if isinstance(n_component, (list, tuple)) else [n_component] * 3
+        assert all(c % parallel_degree == 0 and (c // parallel_degree) % 8 == 0 for c in comps[:ndims]), \
+            "channel-parallel slices must keep a multiple of 8 channels per rank"
+        self.parallel_degree, self.parallel_part, self.group = parallel_degree, parallel_part, group
+        self.full_component = comps[:ndims]
+        local = [c // parallel_degree for c in comps]
+        super().__init__(ndims, resolution_mode, local, grid_size, device, param_shape=None, n_blocks=n_blocks,
+                         scale=scale)
+        if init_state_dict is not None:
+            self.load_full_state(init_state_dict)
+        self.merge_config = {}  # channel slices are not spatial blocks
+
+    def load_full_state(self, state):
+        """Take this rank's channel slice from a full (reference-layout) state dict."""
+        lo = self.parallel_part
+        for k in range(len(self.plane_coef)):
+            p, l = state[f"plane_coef.{k}"], state[f"line_coef.{k}"]
+            c = p.shape[1] // self.parallel_degree
+            self.plane_coef[k].data = _plane_from_ref(p[:, lo * c:(lo + 1) * c]).to(self.plane_coef[k].device)
+            self.line_coef[k].data = _line_from_ref(l[:, lo * c:(lo + 1) * c]).to(self.line_coef[k].device)
+        if self.use_shadow:
+            self.enable_shadow()
+
+    def forward(self, xyzb, count=None, out_dtype=torch.float32):
+        from ....comm.autograd import AllGather
+
+        local = super().forward(xyzb, count, torch.float32)               # [N, L * C/P]
+        if self.parallel_degree == 1:
+            return local.to(out_dtype)
+        N = local.shape[0]
+        P = self.parallel_degree
+        gathered = AllGather.apply(local, self.group)                     # [P*N, L * C/P]
+        n_pairs, L = self.ndims, len(self.reso_mode)
+        cl = local.shape[1] // (n_pairs * L)
+        full = gathered.view(P, N, n_pairs * L, cl).permute(1, 2, 0, 3).reshape(N, n_pairs * L * P * cl)
+        return full.to(out_dtype)
+
+    def _gather_scalar(self, value: torch.Tensor) -> torch.Tensor:
+        from ....comm.autograd import AllReduce
+
+        return AllReduce.apply(value, self.group) / self.parallel_degree
+
+    def L1_loss(self):
+        return self._gather_scalar(super().L1_loss())
+
+    def TV_loss(self):
+        return self._gather_scalar(super().TV_loss())
+
+    def vector_diffs(self):
+        """Off-diagonal correlations need every channel: gather the (small) line tensors."""
+        from ....comm.autograd import AllGather
+
+        total = 0
+        for line in self.line_coef:
+            B, Z, C = line.shape
+            v = line.permute(2, 1, 0).reshape(C, Z * B)
+            full = AllGather.apply(v, self.group) if self.parallel_degree > 1 else v
+            dotp = full @ full.t()
+            n = full.shape[0]
+            total = total + dotp.flatten()[1:].view(n - 1, n + 1)[:, :-1].abs().mean()
+        return total
+
+    def merge_state_dicts(self, state_dicts, device="cpu"):
+        """Concatenate per-rank channel slices back on the channel dim (reference layout dim 1)."""
+        return {k: torch.cat([sd[k].to(device) for sd in state_dicts], dim=1) if "_coef" in k else state_dicts[0][k]
+                for k in sorted(state_dicts[0].keys())}
+
+
+class BranchParallelTensorVMEncoding(TensorVMEncoding):
+    """One spatial block per rank.  The initial values are drawn once for the whole scene (rank 0),
+    broadcast, and each rank keeps its own block, so a branch-parallel run starts from the same field
+    as a single-process run with the same seed (reference: tensor_vm_encoding.py:554-636)."""
+
+    def __init__(self, ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
+                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None):
+        self.parallel_degree, self.parallel_part, self.group = parallel_degree, parallel_part, group
+        super().__init__(ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
+                         scale=scale)
+        if init_state_dict is not None:
+            self.load_full_state(init_state_dict)
+        elif parallel_degree > 1 and torch.distributed.is_initialized():
+            self._broadcast_init(scale)
+
+    @torch.no_grad()
+    def _broadcast_init(self, scale):
+        import torch.distributed as dist
+
+        src = dist.get_global_rank(self.group, 0) if self.group is not None else 0
+        for params in (self.plane_coef, self.line_coef):
+            for p in params:
+                full = scale * torch.randn(self.parallel_degree, *p.shape[1:], device=p.device)
+                dist.broadcast(full, src=src, group=self.group)
+                p.data.copy_(full[self.parallel_part:self.parallel_part + 1])
+
+    def load_full_state(self, state):
+        """Keep this rank's block of a merged (block-stacked, reference-layout) state dict."""
+        b = self.parallel_part
+        for k in range(len(self.plane_coef)):
+            p, l = state[f"plane_coef.{k}"], state[f"line_coef.{k}"]
+            pb = p[:, :, b:b + 1] if p.shape[2] > 1 else p
+            lb = l[..., b:b + 1] if l.shape[3] > 1 else l
+            self.plane_coef[k].data = _plane_from_ref(pb).to(self.plane_coef[k].device)
+            self.line_coef[k].data = _line_from_ref(lb).to(self.line_coef[k].device)
+        if self.use_shadow:
+            self.enable_shadow()
+
+
+class FusedTensorVMEncoding(TensorVMEncoding):
+    """Kernel-runtime name.  The reference's class raises ``NotImplementedError``
+    (fields/encodings/fused_tensor_vm_encoding.py:6-53); here the base class already runs the fused
+    channels-last lookup kernel, so the subclass only pins bf16 shadows on."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        if torch.device(self.device).type == "cuda":
+            self.enable_shadow(fused_optimizer=False)
+
+
+class FusedChannelParallelTensorVMEncoding(ChannelParallelTensorVMEncoding):
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        if torch.device(self.device).type == "cuda":
+            self.enable_shadow(fused_optimizer=False)

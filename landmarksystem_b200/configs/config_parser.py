@@ -94,6 +94,11 @@ class BaseConfig(Config):
         for key, raw in (console_args or {}).items():
             assert key in cfg, f"Unknown argument {key}."
             target = type(cfg[key])
+            if target.__name__ == "device":  # torch.device given as a string on the console
+                import torch
+
+                cfg[key] = torch.device(str(raw))
+                continue
             assert target in _SCALARS, \
                 f"Unsupported type {target} for argument {key}, please set this argument in config file."
             cfg[key] = _coerce(key, raw, target)

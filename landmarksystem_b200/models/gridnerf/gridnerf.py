@@ -109,6 +109,7 @@ class GridNeRFConfig(ConfigClass):
     runtime: Literal["Torch", "Kernel"] = "Torch"
     # additions of this framework (defaults keep the reference behaviour)
     grid_dtype: Literal["fp32", "bf16"] = "fp32"  # bf16: kernels read bf16 shadows of fp32 master grids
+    init_grid_size: Optional[list] = None         # explicit [nx, ny, nz] voxel grid instead of N_voxel_init
     fused_optimizer: bool = True
 
     def check_args(self) -> None:
@@ -240,6 +241,13 @@ class GridNeRF(BaseNeRF):
     def enable_shadow(self):
         self.density_encoding.enable_shadow(self.config.fused_optimizer)
         self.rgb_encoding.enable_shadow(self.config.fused_optimizer)
+
+    def use_shadow(self) -> bool:
+        return bool(self.density_encoding.use_shadow)
+
+    def refresh_shadow(self):
+        self.density_encoding.refresh_shadow()
+        self.rgb_encoding.refresh_shadow()
 
     def init_renderer(self):
         self.renderer = VolumeRenderer(white_bg=self.config.white_bkgd)

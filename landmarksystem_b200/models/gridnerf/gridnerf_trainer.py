@@ -1,0 +1,312 @@
+"""GridNeRF trainer: schedule, losses, checkpointing and evaluation.
+
+Counterpart of the reference's ``benchmarks/nerf/gridnerf/gridnerf_trainer.py`` (create_model
+:65-125, optimiser :127-164, train loop :166-527, evaluation :529-718).  Launch:
+``torchrun --nproc-per-node N -m landmarksystem_b200.models.gridnerf.gridnerf_trainer --config conf.py [--key value]``.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ...components.data.data_manager import DatasetManager
+from ...components.scene import SceneManager
+from ...components.utils.image_utils import mse2psnr_npy, visualize_depth_numpy
+from ...components.utils.loss_utils import rgb_ssim
+from ...configs import BaseConfig, get_default_parser, parse_console_args
+from ...convertor import ComponentConvertorFactory
+from ...ops import FusedAdam
+from ...parallel.grad_sync import GradSynchronizer
+from ...train.nerf_trainer import NeRFTrainer
+from ...train.utils import is_main_rank
+from .gridnerf import GridNeRF, cal_n_samples, n_to_reso
+
+
+def save_image(path: str, array: np.ndarray) -> None:
+    from PIL import Image
+
+    Image.fromarray(array).save(path)
+
+
+class GridNeRFTrainer(NeRFTrainer):
+    def __init__(self, config):
+        super().__init__(config)
+        self.init_train_env()
+        self.check_args()
+        self.scene_mgr = SceneManager(self.config)
+        self.data_mgr = DatasetManager(self.config)
+        self.iteration = config.start_iters
+        self.create_model()
+        self.create_optimizer()
+        self._init_schedule()
+
+    def check_args(self):
+        super().check_args()
+        cfg = self.config
+        if cfg.branch_parallel:
+            assert cfg.plane_division[0] * cfg.plane_division[1] == cfg.model_parallel_degree
+
+    # -- model / optimiser ---------------------------------------------------------------------
+    def create_model(self):
+        cfg = self.config
+        aabb = self.scene_mgr.aabb.to(cfg.device)
+        self.scene_mgr.to(cfg.device)
+        ckpt, kwargs_fp = self._resume_paths()
+        if kwargs_fp is not None and os.path.exists(kwargs_fp):
+            kwargs = GridNeRF.get_kwargs_from_ckpt(kwargs_fp, cfg.device)
+            kwargs.update(device=cfg.device, scene_manager=self.scene_mgr, config=cfg)
+            model = GridNeRF(**kwargs)
+            model.load_from_state_dict(model.get_state_dict_from_ckpt(ckpt, cfg.device), strict=False)
+            if model.use_shadow():
+                model.refresh_shadow()
+        else:
+            reso = list(cfg.init_grid_size) if cfg.get("init_grid_size") else n_to_reso(cfg.N_voxel_init, aabb)
+            near_far = list(self.data_mgr.dataset_info.near_far)
+            model = GridNeRF(aabb, reso, cfg.device, near_far=near_far, scene_manager=self.scene_mgr, config=cfg)
+        self.module = model
+        if cfg.model_parallel:
+            model = ComponentConvertorFactory.get_convertor("parallelize").convert(model, cfg)
+        if cfg.get("runtime", "Torch") == "Kernel":
+            model = ComponentConvertorFactory.get_convertor("runtime").convert(model, cfg)
+        self.model = self.module = model
+        # replicated parameters are synchronised explicitly between backward and the optimiser step
+        self.mp_sync = GradSynchronizer(cfg.mp_group, average=False) if cfg.branch_parallel else None
+        self.dp_sync = GradSynchronizer(cfg.dp_group if cfg.model_parallel else None, average=True) if cfg.DDP else None
+        return model
+
+    def _resume_paths(self):
+        cfg = self.config
+        ckpt = cfg.get("ckpt")
+        if ckpt == "auto":
+            suffix = f"-sub{cfg.rank}" if cfg.model_parallel else ""
+            ckpt = f"{self.logfolder}/state_dict{suffix}.th"
+            if not os.path.exists(ckpt):
+                return None, None
+        if not ckpt:
+            return None, None
+        kwargs_fp = cfg.get("kwargs") or ckpt.replace("state_dict", "kwargs")
+        return ckpt, kwargs_fp
+
+    def _replicated_params(self):
+        m = self.module
+        mods = [m.feature2density, m.rgb_decoder]
+        if self.config.encode_app:
+            mods.append(m.embedding_app)
+        if hasattr(m, "nerf"):
+            mods.append(m.nerf)
+        return [p for mod in mods for p in mod.parameters()]
+
+    def create_optimizer(self):
+        cfg = self.config
+        groups = self.module.get_optparam_groups(cfg.lr_init, cfg.lr_basis)
+        use_fused = bool(cfg.get("fused_optimizer", True)) and torch.device(cfg.device).type == "cuda"
+        cls = FusedAdam if use_fused else torch.optim.Adam
+        self.optimizer = cls(groups, betas=(0.9, 0.99))
+        optim_file = self._optim_path()
+        if cfg.get("ckpt") and os.path.exists(optim_file):
+            self.optimizer.load_state_dict(torch.load(optim_file, map_location=cfg.device, weights_only=False)["optimizer"])
+        return self.optimizer
+
+    def _optim_path(self):
+        cfg = self.config
+        suffix = f"-sub{cfg.rank}" if cfg.model_parallel else ""
+        return os.path.join(self.optim_dir, f"{cfg.expname}_opt{suffix}.th")
+
+    def save_optimizer(self):
+        os.makedirs(self.optim_dir, exist_ok=True)
+        torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+
+    # -- schedule ---------------------------------------------------------------------------
+    def _init_schedule(self):
+        cfg = self.config
+        decay_iters = cfg.lr_decay_iters if cfg.lr_decay_iters > 0 else cfg.n_iters
+        self.lr_factor = cfg.lr_decay_target_ratio ** (1.0 / decay_iters)
+        n_up = len(cfg.upsamp_list)
+        self.n_voxel_list = torch.round(torch.exp(torch.linspace(
+            np.log(cfg.N_voxel_init), np.log(cfg.N_voxel_final), n_up + 1))).long().tolist()[1:]
+        self.tv_weight_density, self.tv_weight_app = cfg.TV_weight_density, cfg.TV_weight_app
+        self.l1_weight = cfg.L1_weight_inital
+        self.enable_distort = False
+        self.nsamples = min(int(cfg.nSamples), cal_n_samples(self.module.gridSize.tolist(), cfg.step_ratio))
+        # replay the upsampling schedule when resuming
+        for it, n_vox in zip(cfg.upsamp_list, self.n_voxel_list):
+            if cfg.start_iters > it and not cfg.get("ckpt"):
+                self._upsample(n_vox)
+
+    def _upsample(self, n_voxels):
+        cfg = self.config
+        reso = n_to_reso(n_voxels, self.module.aabb)
+        self.nsamples = min(int(cfg.nSamples), cal_n_samples(reso, cfg.step_ratio))
+        self.module.upsample_volume_grid(reso)
+        lr_scale = 1.0 if cfg.lr_upsample_reset else cfg.lr_decay_target_ratio ** (self.iteration / cfg.n_iters)
+        groups = self.module.get_optparam_groups(cfg.lr_init * lr_scale, cfg.lr_basis * lr_scale)
+        self.optimizer = type(self.optimizer)(groups, betas=(0.9, 0.99))  # parameters were replaced: new state
+
+    # -- one optimisation step -------------------------------------------------------------------
+    def compute_loss(self, all_ret, rgb_train):
+        cfg, m = self.config, self.module
+        loss = torch.mean((all_ret["rgb_map"] - rgb_train) ** 2)
+        total = loss
+        if "rgb_map1" in all_ret:
+            total = total + torch.mean((all_ret["rgb_map1"] - rgb_train) ** 2)
+        if m.run_nerf and "rgb_map_nerf" in all_ret:
+            total = total + torch.mean((all_ret["rgb_map_nerf"] - rgb_train) ** 2)
+        if cfg.Ortho_weight > 0:
+            total = total + cfg.Ortho_weight * m.density_encoding.vector_diffs() + m.rgb_encoding.vector_diffs()
+        if self.l1_weight > 0:
+            total = total + self.l1_weight * m.density_encoding.L1_loss()
+        if self.tv_weight_density > 0:
+            self.tv_weight_density *= self.lr_factor
+            total = total + self.tv_weight_density * m.density_encoding.TV_loss()
+        if self.tv_weight_app > 0:
+            self.tv_weight_app *= self.lr_factor
+            total = total + self.tv_weight_app * m.rgb_encoding.TV_loss()
+        if self.enable_distort:
+            for key in ("distort_loss", "distort_loss1", "distort_loss_nerf"):
+                if key in all_ret:
+                    total = total + torch.mean(all_ret[key])
+        return total, loss
+
+    def train_step(self, rays_train, rgb_train, idxs_train):
+        """Forward, backward, gradient sync and optimiser step on one device-resident batch.
+        Returns the (detached, device) photometric MSE."""
+        cfg = self.config
+        with self.timer.stage("forward"):
+            rays_chunk = torch.cat((rays_train, idxs_train[:, None]), dim=-1)
+            all_ret = self.model(rays_chunk, N_samples=self.nsamples)
+            total, loss = self.compute_loss(all_ret, rgb_train)
+        with self.timer.stage("backward"):
+            total.backward()
+        with self.timer.stage("grad_sync"):
+            if self.mp_sync is not None:
+                self.mp_sync.sync(self._replicated_params())
+            if self.dp_sync is not None:
+                self.dp_sync.sync([p for g in self.optimizer.param_groups for p in g["params"]])
+        with self.timer.stage("optimizer"):
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
+            for group in self.optimizer.param_groups:
+                group["lr"] *= self.lr_factor
+        return loss.detach()
+
+    def train(self):
+        cfg = self.config
+        self.model.train()
+        psnrs, t0 = [], time.time()
+        for self.iteration in range(cfg.start_iters, cfg.n_iters):
+            it = self.iteration
+            rays_train, rgb_train, idxs_train = self.data_mgr.get_rays(it)
+            if cfg.add_distort > 0 and it == cfg.add_distort:
+                self.enable_distort = True
+            if cfg.add_nerf > 0 and it == cfg.add_nerf:
+                self.module.run_nerf = True
+                self.optimizer = type(self.optimizer)(self.module.get_optparam_groups(
+                    self.optimizer.param_groups[0]["lr"], self.optimizer.param_groups[2]["lr"]), betas=(0.9, 0.99))
+            loss = self.train_step(rays_train, rgb_train, idxs_train)
+            if it % cfg.progress_refresh_rate == 0:
+                mse = float(loss)
+                psnrs.append(mse2psnr_npy(max(mse, 1e-10)))
+                if is_main_rank():
+                    print(f"[{cfg.expname}] iter {it:06d} mse {mse:.6f} psnr {psnrs[-1]:.2f} "
+                          f"({(time.time() - t0) / max(it - cfg.start_iters + 1, 1) * 1e3:.1f} ms/it)", flush=True)
+                    self.logger.log(it, {"Train/Loss": mse, "Train/PSNR": psnrs[-1],
+                                         "Train/tf_new_lrate": self.optimizer.param_groups[0]["lr"]})
+            if (it + 1) % cfg.vis_every == 0 and cfg.N_vis != 0:
+                psnr_test = self.evaluation(prefix=f"{it:06d}_", n_vis=cfg.N_vis)
+                self.save_ckpt()
+                if is_main_rank():
+                    self.logger.log(it, {"Test/PSNR": psnr_test})
+                self.model.train()
+            if it in cfg.update_AlphaMask_list:
+                reso = self.module.gridSize.tolist()
+                mask_reso = n_to_reso(min(int(np.prod(reso)), cfg.alpha_grid_reso), self.module.aabb)
+                self.module.updateAlphaMask(tuple(mask_reso))
+                if cfg.progressive_alpha > 0:
+                    cfg.alpha_mask_filter_thre = min(cfg.alpha_mask_filter_thre + 0.1 / cfg.progressive_alpha, 0.1)
+            if it in cfg.upsamp_list:
+                self._upsample(self.n_voxel_list[cfg.upsamp_list.index(it)])
+                self.l1_weight = cfg.L1_weight_rest
+        self.save_ckpt(final=True)
+        return psnrs
+
+    # -- checkpoints -------------------------------------------------------------------------------
+    def save_ckpt(self, final: bool = False):
+        cfg = self.config
+        if cfg.model_parallel:
+            self.module.save_model(self.logfolder, rank=cfg.mp_rank) if cfg.dp_rank == 0 else None
+            self.save_optimizer()
+            self.barrier()
+            if final and cfg.rank == 0 and cfg.branch_parallel:
+                n = cfg.model_parallel_degree
+                merged, kwargs = self.module.merge_ckpts(
+                    [f"{self.logfolder}/state_dict-sub{r}.th" for r in range(n)],
+                    [f"{self.logfolder}/kwargs-sub{r}.th" for r in range(n)])
+                torch.save(merged, f"{self.logfolder}/state_dict-merged.th")
+                torch.save(kwargs, f"{self.logfolder}/kwargs-merged.th")
+            self.barrier()
+        elif is_main_rank():
+            self.module.save_model(self.logfolder)
+            self.save_optimizer()
+
+    # -- evaluation ----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def evaluation(self, prefix: str = "", n_vis: int = 5, save: bool = True):
+        cfg = self.config
+        was_train = cfg.is_train
+        self.model.eval()
+        test = self.data_mgr.test_dataset
+        n_img = test.all_rays.shape[0]
+        step = 1 if n_vis < 0 else max(n_img // n_vis, 1)
+        W, H = test.img_wh
+        psnrs, ssims = [], []
+        dp = cfg.world_size if (cfg.DDP and not cfg.model_parallel) else 1
+        for k in range(0, n_img, step):
+            rays = test.all_rays[k].to(cfg.device)
+            if dp > 1:  # data-parallel evaluation: each rank renders a slice of the pixels
+                rays = torch.chunk(rays, dp, dim=0)[cfg.rank]
+            ret = self.module.render_all_rays(rays, chunk_size=cfg.batch_size, N_samples=self.nsamples)
+            rgb, depth = ret["rgb_map"].clamp(0, 1), ret["depth_map"]
+            if dp > 1:
+                from ...comm.varlen import all_gather_varlen
+
+                rgb = torch.cat(all_gather_varlen(rgb), 0)
+                depth = torch.cat(all_gather_varlen(depth[:, None]), 0)[:, 0]
+            rgb, depth = rgb.view(H, W, 3).cpu(), depth.view(H, W).cpu()
+            if test.all_rgbs is not None:
+                gt = test.all_rgbs[k].view(H, W, 3)
+                mse = float(torch.mean((rgb - gt) ** 2))
+                psnrs.append(mse2psnr_npy(max(mse, 1e-10)))
+                if cfg.get("compute_extra_metrics", False):
+                    ssims.append(rgb_ssim(rgb.numpy(), gt.numpy(), 1))
+            if save and is_main_rank() and not cfg.skip_save_imgs:
+                depth_img, _ = visualize_depth_numpy(depth.numpy(), test.near_far)
+                panel = np.concatenate(((rgb.numpy() * 255).astype(np.uint8), depth_img), axis=1)
+                save_image(f"{self.logfolder}/imgs_vis/{prefix}{k:03d}.png", panel)
+        cfg.is_train = was_train
+        mean_psnr = float(np.mean(psnrs)) if psnrs else float("nan")
+        if is_main_rank() and psnrs:
+            with open(f"{self.logfolder}/imgs_vis/{prefix}mean.txt", "w", encoding="utf-8") as fh:
+                fh.write(f"psnr {mean_psnr}\n" + (f"ssim {np.mean(ssims)}\n" if ssims else ""))
+        return mean_psnr
+
+
+def main(argv=None):
+    args, unknown = get_default_parser().parse_known_args(argv)
+    config = BaseConfig.from_file(args.config, parse_console_args(unknown))
+    trainer = GridNeRFTrainer(config)
+    trainer.train()
+    psnr = trainer.evaluation(prefix="final_", n_vis=config.N_vis)
+    if is_main_rank():
+        print(f"final test PSNR {psnr:.3f}", flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -90,7 +90,13 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+LAUNCH_CALLS = 0
+
+
 def check(code: int, what: str) -> None:
+    """Every kernel launcher call is funnelled through here: count it and raise on a CUDA error."""
+    global LAUNCH_CALLS
+    LAUNCH_CALLS += 1
     if code != 0:
         raise RuntimeError(f"{what} failed with CUDA error {code}")
 

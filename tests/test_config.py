@@ -1,0 +1,95 @@
+"""L0: attribute dict, typed config blocks, conf-file loading and console overrides."""
+import textwrap
+
+import pytest
+
+from landmarksystem_b200.configs import BaseConfig, DatasetConfig, RenderConfig, TrainConfig, parse_console_args
+from landmarksystem_b200.utils import Config, SingletonMeta
+
+
+def test_config_attr_access_and_nesting():
+    c = Config({"a": 1, "b": {"c": 2}})
+    assert c.a == 1 and c.b.c == 2 and isinstance(c.b, Config)
+    c.d = {"e": 3}
+    assert c["d"].e == 3
+    assert not hasattr(c, "missing")
+    assert c.to_dict() == {"a": 1, "b": {"c": 2}, "d": {"e": 3}}
+
+
+def test_config_from_file_skips_modules_and_classes(tmp_path):
+    f = tmp_path / "x.py"
+    f.write_text("import os\nclass K: pass\nvalue = 5\nnested = dict(k=1)\n")
+    c = Config.from_file(f)
+    assert c.value == 5 and c.nested.k == 1 and "os" not in c and "K" not in c
+
+
+def test_singleton_meta():
+    class S(metaclass=SingletonMeta):
+        pass
+
+    assert S() is S()
+
+
+def test_parse_console_args():
+    assert parse_console_args(["--a", "1", "--flag", "--b", "x"]) == {"a": "1", "flag": True, "b": "x"}
+    assert parse_console_args(None) is None
+
+
+def _write_conf(tmp_path, extra=""):
+    conf = tmp_path / "conf.py"
+    conf.write_text(textwrap.dedent(f"""
+        from landmarksystem_b200.configs import DatasetConfig, TrainConfig
+        t = TrainConfig(model_name="m", expname="e", n_iters=10, batch_size=128)
+        d = DatasetConfig(datadir="ring", lb=[0, 0, 0], ub=[1, 1, 1])
+        config = [t, d]
+        {extra}
+    """))
+    return conf
+
+
+def test_from_file_flattens_and_overrides(tmp_path):
+    cfg = BaseConfig.from_file(_write_conf(tmp_path), {"n_iters": "25", "DDP": "true", "basedir": "/tmp/x"})
+    assert cfg.n_iters == 25 and cfg.DDP is True and cfg.basedir == "/tmp/x"
+    assert cfg.batch_size == 128 and cfg.datadir == "ring" and cfg.plane_division == [1, 1]
+
+
+def test_from_file_rejects_unknown_and_non_scalar(tmp_path):
+    conf = _write_conf(tmp_path)
+    with pytest.raises(AssertionError):
+        BaseConfig.from_file(conf, {"nope": "1"})
+    with pytest.raises(AssertionError):
+        BaseConfig.from_file(conf, {"plane_division": "[2,2]"})
+    with pytest.raises(ValueError):
+        BaseConfig.from_file(conf, {"DDP": "maybe"})
+
+
+def test_duplicate_fields_rejected(tmp_path):
+    conf = _write_conf(tmp_path, extra='config.append(TrainConfig(model_name="m", expname="e", n_iters=1))')
+    with pytest.raises(AssertionError):
+        BaseConfig.from_file(conf)
+
+
+def test_save_config_roundtrip(tmp_path):
+    cfg = BaseConfig.from_file(_write_conf(tmp_path))
+    out = tmp_path / "dump.txt"
+    cfg.save_config(out)
+    lines = out.read_text().splitlines()
+    assert lines == sorted(lines) and any(l.startswith("batch_size = 128") for l in lines)
+
+
+def test_render_config_inherits_and_checks():
+    t = TrainConfig(model_name="m", expname="e", n_iters=1, plane_division=[2, 2])
+    r = RenderConfig().from_train_config(t)
+    assert r.model_name == "m" and r.plane_division == [2, 2]
+    r.check_args()
+    with pytest.raises(AssertionError):
+        RenderConfig(is_train=True).check_args()
+
+
+def test_dataset_config_checks():
+    with pytest.raises(AssertionError):
+        DatasetConfig(datadir="x", lb=[0, 0], ub=[1, 1, 1]).check_args()
+    with pytest.raises(AssertionError):
+        DatasetConfig(datadir="x", dynamic_load=True, dataset_type="nerf").check_args()
+    with pytest.raises(AssertionError):
+        TrainConfig(model_name="m", expname="e", n_iters=1, channel_parallel=True, branch_parallel=True).check_args()

@@ -1,0 +1,70 @@
+"""PyTorch reference implementations of the ops, checked against independent formulations."""
+import torch
+import torch.nn.functional as F
+
+from landmarksystem_b200.ops import FusedAdam, composite_render, composite_weights, vm_encode_reference
+from landmarksystem_b200.ops.hashgrid import hashgrid_reference, make_meta
+
+
+def test_vm_reference_matches_grid_sample():
+    """The channels-last lookup equals the two F.grid_sample calls + product of the stacked-plane layout."""
+    torch.manual_seed(0)
+    B, H, W, Z, C, N = 3, 9, 7, 5, 8, 200
+    plane = torch.randn(B, H, W, C)
+    line = torch.randn(B, Z, C)
+    coords = torch.rand(N, 4) * 2 - 1
+    block = torch.randint(0, B, (N,)).float()
+    coords[:, 3] = block
+    got = vm_encode_reference(coords, [plane], [line])
+    plane_ref = plane.permute(3, 0, 1, 2)[None]                      # [1,C,B,H,W]
+    line_ref = line.permute(2, 1, 0)[None]                           # [1,C,Z,B]
+    bnorm = -1 + 2 * block / (B - 1)
+    g3 = torch.stack((coords[:, 0], coords[:, 1], bnorm), -1).view(1, N, 1, 1, 3)
+    pf = F.grid_sample(plane_ref, g3, align_corners=True).view(C, N).t()
+    g2 = torch.stack((bnorm, coords[:, 2]), -1).view(1, N, 1, 2)
+    lf = F.grid_sample(line_ref, g2, align_corners=True).view(C, N).t()
+    assert torch.allclose(got, pf * lf, atol=1e-5)
+
+
+def test_vm_reference_invalid_block_is_zero():
+    plane, line = torch.randn(2, 4, 4, 8), torch.randn(2, 4, 8)
+    coords = torch.tensor([[0.0, 0.0, 0.0, -1.0], [0.1, 0.2, 0.3, 5.0]])
+    assert vm_encode_reference(coords, [plane], [line]).abs().sum() == 0
+
+
+def test_weights_and_render_reference():
+    torch.manual_seed(0)
+    sigma, dists = torch.rand(4, 16) * 3, torch.rand(4, 16) * 0.2
+    w, bg = composite_weights(sigma, dists)
+    alpha = 1 - torch.exp(-sigma * dists)
+    T = torch.ones(4)
+    for s in range(16):
+        assert torch.allclose(w[:, s], alpha[:, s] * T, atol=1e-6)
+        T = T * (1 - alpha[:, s] + 1e-10)
+    assert torch.allclose(bg, T, atol=1e-6)
+    rgb, depth, acc = composite_render(w, torch.rand(4, 16, 3), torch.rand(4, 16), 1.0)
+    assert rgb.shape == (4, 3) and depth.shape == (4,) and torch.allclose(acc, w.sum(-1))
+
+
+def test_fused_adam_cpu_matches_torch_adam():
+    torch.manual_seed(0)
+    a = torch.nn.Parameter(torch.randn(37))
+    b = torch.nn.Parameter(a.detach().clone())
+    o1 = FusedAdam([a], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    o2 = torch.optim.Adam([b], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    for _ in range(5):
+        g = torch.randn(37)
+        a.grad, b.grad = g.clone(), g.clone()
+        o1.step(); o2.step()
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_hashgrid_reference_dense_level_interpolates():
+    meta = make_meta(2, 2, 10, 4, 2.0)
+    assert meta.resolutions[0] == 4 and meta.offsets[1] == 64   # 4^3 dense entries
+    table = torch.zeros(meta.offsets[-1], 2)
+    table[: meta.offsets[1], 0] = 1.0
+    x = torch.rand(50, 3)
+    out = hashgrid_reference(x, table, meta)
+    assert out.shape == (50, 4) and torch.allclose(out[:, 0], torch.ones(50), atol=1e-5)
+    assert out[:, 1].abs().max() == 0

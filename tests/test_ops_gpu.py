@@ -1,0 +1,117 @@
+"""CUDA kernels vs their plain-PyTorch fp32 references (run on a B200)."""
+import pytest
+import torch
+
+from landmarksystem_b200.ops import (FusedAdam, composite_render, composite_weights, vm_encode, vm_encode_reference)
+from landmarksystem_b200.ops.composite import render_reference, weights_reference
+from landmarksystem_b200.ops.hashgrid import hashgrid_encode, hashgrid_reference, make_meta
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _vm_case(B=3, C=16, L=2, N=5000, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    planes = [torch.randn(B, 33 * (l + 1), 29 * (l + 1), C, generator=g) for l in range(L)]
+    lines = [torch.randn(B, 17 * (l + 1), C, generator=g) for l in range(L)]
+    coords = torch.rand(N, 4, generator=g) * 2.2 - 1.1          # some taps fall outside -> zero padding
+    coords[:, 3] = torch.randint(-1, B + 1, (N,), generator=g).float()
+    return planes, lines, coords
+
+
+@pytest.mark.parametrize("C", [16, 48])
+def test_vm_encode_fwd_bwd_fp32(C):
+    planes, lines, coords = _vm_case(C=C)
+    ref_p = [p.clone().requires_grad_() for p in planes]
+    ref_l = [l.clone().requires_grad_() for l in lines]
+    ref = vm_encode_reference(coords, ref_p, ref_l)
+    gout = torch.randn(ref.shape, generator=torch.Generator().manual_seed(1))
+    ref.backward(gout)
+    cp = [p.to(DEV).requires_grad_() for p in planes]
+    cl = [l.to(DEV).requires_grad_() for l in lines]
+    out = vm_encode(coords.to(DEV), cp, cl)
+    assert torch.allclose(out.cpu(), ref.detach(), atol=1e-5, rtol=1e-5)
+    out.backward(gout.to(DEV))
+    for a, b in zip(cp + cl, ref_p + ref_l):
+        assert torch.allclose(a.grad.cpu(), b.grad, atol=2e-4, rtol=1e-4)
+
+
+def test_vm_encode_bf16_shadow_and_sink():
+    planes, lines, coords = _vm_case(C=16, L=1)
+    cp = [torch.nn.Parameter(p.to(DEV)) for p in planes]
+    cl = [torch.nn.Parameter(l.to(DEV)) for l in lines]
+    for p in cp + cl:
+        FusedAdam.attach_sink(p, shadow=True)
+    out = vm_encode(coords.to(DEV), cp, cl, [p._lmb_shadow for p in cp], [l._lmb_shadow for l in cl])
+    ref = vm_encode_reference(coords, [p.bfloat16().float() for p in planes], [l.bfloat16().float() for l in lines])
+    assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)
+    out.sum().backward()
+    assert cp[0].grad is None and cp[0]._lmb_grad_sink.abs().sum() > 0
+
+
+def test_vm_encode_device_count():
+    planes, lines, coords = _vm_case(C=16, L=1, N=1000)
+    cp, cl = [p.to(DEV) for p in planes], [l.to(DEV) for l in lines]
+    count = torch.tensor([300], device=DEV, dtype=torch.int32)
+    out = vm_encode(coords.to(DEV), cp, cl, count=count)
+    ref = vm_encode_reference(coords, planes, lines)
+    assert torch.allclose(out[:300].cpu(), ref[:300], atol=1e-5) and out[300:].abs().sum() == 0
+
+
+@pytest.mark.parametrize("S", [16, 64, 200])
+def test_composite_fwd_bwd(S):
+    torch.manual_seed(0)
+    R = 257
+    sigma = (torch.rand(R, S) * 4).requires_grad_()
+    dists = torch.rand(R, S) * 0.3
+    rgbs = torch.rand(R, S, 3).requires_grad_()
+    z = torch.sort(torch.rand(R, S), -1)[0]
+    w_ref, bg_ref = weights_reference(sigma, dists)
+    rgb_ref, depth_ref, acc_ref = render_reference(w_ref, rgbs, z, 1.0)
+    loss_ref = (rgb_ref * torch.arange(1, 4)).sum() + 0.3 * bg_ref.sum()
+    loss_ref.backward()
+    s2 = sigma.detach().to(DEV).requires_grad_()
+    c2 = rgbs.detach().to(DEV).requires_grad_()
+    w, bg = composite_weights(s2, dists.to(DEV))
+    rgb, depth, acc = composite_render(w, c2, z.to(DEV), 1.0)
+    assert torch.allclose(w.cpu(), w_ref, atol=1e-5) and torch.allclose(bg.cpu(), bg_ref, atol=1e-5)
+    assert torch.allclose(rgb.cpu(), rgb_ref, atol=1e-4) and torch.allclose(depth.cpu(), depth_ref, atol=1e-4)
+    loss = (rgb * torch.arange(1, 4, device=DEV)).sum() + 0.3 * bg.sum()
+    loss.backward()
+    assert torch.allclose(s2.grad.cpu(), sigma.grad, atol=2e-4, rtol=1e-3)
+    assert torch.allclose(c2.grad.cpu(), rgbs.grad, atol=1e-5)
+
+
+def test_fused_adam_matches_torch():
+    torch.manual_seed(0)
+    n = 4 * 1000 + 3
+    a = torch.nn.Parameter(torch.randn(n, device=DEV))
+    b = torch.nn.Parameter(a.detach().clone())
+    FusedAdam.attach_sink(a, shadow=True)
+    o1 = FusedAdam([a], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    o2 = torch.optim.Adam([b], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    for _ in range(5):
+        g = torch.randn(n, device=DEV)
+        a._lmb_grad_sink.copy_(g)
+        b.grad = g.clone()
+        o1.step(); o2.step()
+        assert a._lmb_grad_sink.abs().sum() == 0          # cleared inside the kernel
+    assert torch.allclose(a, b, atol=1e-5)
+    assert torch.allclose(a._lmb_shadow.float(), a.detach().bfloat16().float())
+
+
+@pytest.mark.parametrize("log2", [10, 19])
+def test_hashgrid_fwd_bwd(log2):
+    torch.manual_seed(0)
+    meta = make_meta(8, 2, log2, 16, 1.6)
+    table = torch.randn(meta.offsets[-1], 2) * 0.1
+    x = torch.rand(3000, 3)
+    t_ref = table.clone().requires_grad_()
+    ref = hashgrid_reference(x, t_ref, meta)
+    gout = torch.randn_like(ref)
+    ref.backward(gout)
+    t_gpu = table.to(DEV).requires_grad_()
+    out = hashgrid_encode(x.to(DEV), t_gpu, meta)
+    assert torch.allclose(out.cpu(), ref.detach(), atol=1e-5)
+    out.backward(gout.to(DEV))
+    assert torch.allclose(t_gpu.grad.cpu(), t_ref.grad, atol=1e-4, rtol=1e-4)
