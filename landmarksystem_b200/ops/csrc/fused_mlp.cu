@@ -1,0 +1,255 @@
+// Fused small-MLP inference/forward kernel on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// One persistent CTA per SM runs kSlots independent 128-thread "slots"; each slot walks tiles of 128
+// input rows.  Per tile and layer one elected thread issues K/16 tcgen05.mma instructions
+// (A = activations in shared memory, B = the layer's weights in shared memory, D = fp32 accumulator in
+// tensor memory), commits them to an mbarrier, and the slot's four warps then pull their 32 TMEM lanes
+// with tcgen05.ld, apply bias + activation in registers and write the bf16 result back into the SAME
+// shared-memory buffer as the next layer's A operand (the MMA that read it has completed).  While
+// one slot runs its epilogue the tensor core works on another slot's tile.  All weights of the network
+// arrive once per CTA with a single TMA bulk copy; input tiles arrive by tiled TMA loads.
+//
+// This replaces the per-layer cuBLAS GEMMs + elementwise kernels of the reference's nn.Sequential MLPs
+// (landmark/nerf_components/model_components/fields/mlp_decoder.py:70-109) and the tiny-cuda-nn
+// networks of its fused decoder (fused_mlp_decoder.py:69-90).  The optional "GridNeRF colour" stage
+// reproduces benchmarks/nerf/gridnerf/gridnerf.py:137-174: layer 0 is the bias-free basis projection
+// (features -> 27), whose output f together with the view direction d is expanded in registers to
+// [f, d, sin(f 2^k), cos(f 2^k), sin(d 2^k), cos(d 2^k)] (k = 0, 1) = 150 inputs of the 3-layer decoder.
+#include <cuda.h>
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace lmb {
+
+constexpr int kSlots = 3;
+constexpr int kSlotThreads = 128;
+constexpr int kTileRows = 128;
+constexpr int kMaxLayers = 5;
+constexpr int kMaxK = 160;            // widest activation row kept in shared memory
+constexpr int kSlotCols = 160;        // TMEM columns per slot (>= widest layer output)
+constexpr int kActBytes = kTileRows * kMaxK * 2;
+
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_TANH = 3, ACT_EXP = 4 };
+
+struct MLPSpec {
+  int n_layers;
+  int K[kMaxLayers];        // padded input width of each layer (multiple of 16, <= kMaxK)
+  int N[kMaxLayers];        // padded output width (multiple of 16, <= kSlotCols)
+  int act[kMaxLayers];
+  int w_off[kMaxLayers];    // byte offset of the packed [K/8][N][8] bf16 weights inside the blob
+  int b_off[kMaxLayers];    // byte offset of N fp32 biases inside the blob (-1: no bias)
+  int blob_bytes;           // multiple of 16
+  int in_width;             // row width of the input tensor (multiple of 8)
+  int out_dim;              // number of valid output columns of the last layer
+  int pe_stage;             // 1: GridNeRF colour expansion between layer 0 and layer 1
+  int dir_col;              // column of the input row that holds the view direction (pe_stage)
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+    case ACT_TANH: return tanhf(x);
+    case ACT_EXP: return __expf(x);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ void store_chunk(unsigned char* buf, int chunk, int row, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(buf + ((size_t)chunk * kTileRows + row) * 16) = u;
+}
+
+__device__ __forceinline__ float load_elem(const unsigned char* buf, int col, int row) {
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(buf + ((size_t)(col >> 3) * kTileRows + row) * 16);
+  return __bfloat162float(p[col & 7]);
+}
+
+// status words: 0 ok, 1 weight load timed out, 2 input tile load timed out, 3 MMA completion timed out
+__global__ void __launch_bounds__(kSlots * kSlotThreads, 1)
+fused_mlp_kernel(const __grid_constant__ CUtensorMap in_map, const unsigned char* __restrict__ blob, MLPSpec spec,
+                 const int* __restrict__ count_ptr, long long max_rows, float* __restrict__ out, int out_stride,
+                 int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // round the dynamic window up to 1 KB so TMA destinations and operand chunks are well aligned
+  unsigned char* smem = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* wsm = smem;                                        // weights + biases
+  unsigned char* act_base = smem + ((spec.blob_bytes + 1023) & ~1023);
+  __shared__ __align__(8) uint64_t bar_w, bar_in[kSlots], bar_mma[kSlots];
+  __shared__ uint32_t tmem_base_sh;
+
+  const int tid = threadIdx.x;
+  const int slot = tid / kSlotThreads;
+  const int row = tid % kSlotThreads;          // row of the tile == TMEM lane owned by this thread
+  const int warp_in_slot = row >> 5;
+  unsigned char* act = act_base + (size_t)slot * kActBytes;
+
+  if (tid == 0) {
+    tc05::mbar_init(&bar_w, 1);
+    for (int s = 0; s < kSlots; ++s) { tc05::mbar_init(&bar_in[s], 1); tc05::mbar_init(&bar_mma[s], 1); }
+    tc05::fence_barrier_init();
+  }
+  if (tid < 32) tc05::tmem_alloc(&tmem_base_sh, 512);
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem_slot = tmem_base_sh + (uint32_t)(slot * kSlotCols);
+  const uint32_t tmem_lane = tmem_slot + ((uint32_t)(warp_in_slot * 32) << 16);
+
+  if (tid == 0) {
+    tc05::mbar_expect_tx(&bar_w, (uint32_t)spec.blob_bytes);
+    tc05::tma_bulk_g2s(wsm, blob, (uint32_t)spec.blob_bytes, &bar_w);
+  }
+  bool ok = tc05::mbar_wait(&bar_w, 0);
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) atomicExch(status, 1);
+
+  const long long n_rows = resolve_count(count_ptr, max_rows);
+  const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+  const int in_chunks = spec.in_width >> 3;
+  const uint32_t in_bytes = (uint32_t)(in_chunks * kTileRows * 16);
+  const int bar_id = 1 + slot;
+  uint32_t ph_in = 0, ph_mma = 0;
+
+  for (long long tile = (long long)blockIdx.x * kSlots + slot; ok && tile < n_tiles; tile += (long long)gridDim.x * kSlots) {
+    const long long row0 = tile * kTileRows;
+    // ---- input tile: one TMA box [8 elems, 1 chunk, 128 rows] per 16-byte column chunk -------------
+    if (row == 0) {
+      tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
+      for (int c = 0; c < in_chunks; ++c)
+        tc05::tma_load_3d(act + (size_t)c * kTileRows * 16, &in_map, 0, c, (int)row0, &bar_in[slot]);
+    }
+    bool got = tc05::mbar_wait(&bar_in[slot], ph_in);
+    ph_in ^= 1;
+    if (!tc05::bar_and(bar_id, kSlotThreads, got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
+
+    float dir[3] = {0.f, 0.f, 0.f};
+    if (spec.pe_stage) {
+#pragma unroll
+      for (int i = 0; i < 3; ++i) dir[i] = load_elem(act, spec.dir_col + i, row);
+    }
+
+    for (int l = 0; l < spec.n_layers; ++l) {
+      const int K = spec.K[l], N = spec.N[l];
+      // ---- MMA: D[128 x N] = A[128 x K] * W_l^T ----------------------------------------------------
+      if (row == 0) {
+        tc05::fence_after_sync();
+        const uint32_t a_addr = tc05::smem_u32(act);
+        const uint32_t b_addr = tc05::smem_u32(wsm + spec.w_off[l]);
+        const uint32_t idesc = tc05::idesc_bf16(N, false, false);
+        for (int k = 0; k < K; k += 16) {
+          const uint64_t da = tc05::smem_desc(a_addr + (uint32_t)(k >> 3) * (kTileRows * 16), kTileRows * 16, 128);
+          const uint64_t db = tc05::smem_desc(b_addr + (uint32_t)(k >> 3) * (uint32_t)(N * 16), (uint32_t)(N * 16), 128);
+          tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
+        }
+        tc05::mma_commit(&bar_mma[slot]);
+      }
+      bool done = tc05::mbar_wait(&bar_mma[slot], ph_mma);
+      ph_mma ^= 1;
+      if (!tc05::bar_and(bar_id, kSlotThreads, done)) { if (row == 0) atomicExch(status, 3); ok = false; break; }
+      tc05::fence_after_sync();
+
+      // ---- epilogue -------------------------------------------------------------------------------
+      const float* bias = spec.b_off[l] >= 0 ? reinterpret_cast<const float*>(wsm + spec.b_off[l]) : nullptr;
+      const bool last = (l == spec.n_layers - 1);
+      if (spec.pe_stage && l == 0) {
+        // f = first 27 accumulator columns; expand to the 150-wide decoder input, in place
+        float f[32];
+        tc05::tmem_ld16(tmem_lane, f);
+        tc05::tmem_ld16(tmem_lane + 16, f + 16);
+        float x[160];
+#pragma unroll
+        for (int i = 0; i < 27; ++i) {
+          x[i] = f[i];
+          float s1, c1, s2, c2;
+          __sincosf(f[i], &s1, &c1);
+          __sincosf(2.f * f[i], &s2, &c2);
+          x[30 + 2 * i] = s1; x[31 + 2 * i] = s2;
+          x[84 + 2 * i] = c1; x[85 + 2 * i] = c2;
+        }
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          x[27 + i] = dir[i];
+          float s1, c1, s2, c2;
+          __sincosf(dir[i], &s1, &c1);
+          __sincosf(2.f * dir[i], &s2, &c2);
+          x[138 + 2 * i] = s1; x[139 + 2 * i] = s2;
+          x[144 + 2 * i] = c1; x[145 + 2 * i] = c2;
+        }
+#pragma unroll
+        for (int i = 150; i < 160; ++i) x[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 20; ++c) store_chunk(act, c, row, x + 8 * c);
+      } else {
+        for (int n0 = 0; n0 < N; n0 += 16) {
+          float v[16];
+          tc05::tmem_ld16(tmem_lane + n0, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i] + (bias ? bias[n0 + i] : 0.f), spec.act[l]);
+          if (!last) {
+            store_chunk(act, (n0 >> 3), row, v);
+            store_chunk(act, (n0 >> 3) + 1, row, v + 8);
+          } else if (row0 + row < n_rows) {
+            float* o = out + (row0 + row) * (long long)out_stride;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (n0 + i < spec.out_dim) o[n0 + i] = v[i];
+          }
+        }
+      }
+      // TMEM reads and shared-memory writes of this slot are complete before the next MMA / TMA
+      tc05::fence_before_sync();
+      tc05::fence_async_shared();
+      tc05::bar_sync(bar_id, kSlotThreads);
+    }
+  }
+
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (tid < 32) tc05::tmem_dealloc(tmem_base_sh, 512);
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+// x: [max_rows, spec.in_width] bf16 row-major (16-byte aligned rows).  out: fp32 [max_rows, out_stride].
+// status: one int in device memory, written non-zero if a bounded wait expired.
+LMB_API int lmb_fused_mlp_fwd(const void* x, const int* count_ptr, long long max_rows, const void* blob,
+                              const MLPSpec* spec, float* out, int out_stride, int* status, cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  if (spec->n_layers < 1 || spec->n_layers > kMaxLayers || spec->in_width % 8 || spec->in_width > kMaxK ||
+      spec->blob_bytes % 16)
+    return (int)cudaErrorInvalidValue;
+  for (int l = 0; l < spec->n_layers; ++l)
+    if (spec->K[l] % 16 || spec->K[l] > kMaxK || spec->N[l] % 16 || spec->N[l] > kSlotCols || spec->N[l] < 16)
+      return (int)cudaErrorInvalidValue;
+  CUtensorMap map;
+  const cuuint64_t gdim[3] = {8, (cuuint64_t)(spec->in_width / 8), (cuuint64_t)max_rows};
+  const cuuint64_t gstride[2] = {16, (cuuint64_t)spec->in_width * 2};
+  const cuuint32_t box[3] = {8, 1, (cuuint32_t)kTileRows};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride,
+                                      box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 10000 + (int)r;
+  const size_t smem = ((spec->blob_bytes + 1023) & ~1023) + (size_t)kSlots * kActBytes + 1024;
+  static bool configured = false;
+  if (!configured) {
+    LMB_CUDA_TRY(cudaFuncSetAttribute(fused_mlp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured = true;
+  }
+  if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = (max_rows + kTileRows - 1) / kTileRows;
+  const int grid = (int)((tiles + kSlots - 1) / kSlots < sms ? (tiles + kSlots - 1) / kSlots : sms);
+  fused_mlp_kernel<<<grid, kSlots * kSlotThreads, smem, stream>>>(map, (const unsigned char*)blob, *spec, count_ptr,
+                                                                max_rows, out, out_stride, status);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}

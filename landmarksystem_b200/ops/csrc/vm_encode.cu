@@ -46,7 +46,7 @@ __device__ __forceinline__ Corner2 taps(float u, int size) {
 template <typename T, typename OutT>
 __global__ void __launch_bounds__(256)
 vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n,
-                     VMLevels lv, OutT* __restrict__ out) {
+                     VMLevels lv, OutT* __restrict__ out, int out_stride) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
   long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -55,7 +55,6 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
   if (n >= n_valid) return;
   float4 q = __ldg(coords + n);
   int b = (int)q.w;
-  const int out_stride = lv.L * lv.C;
   if (b < 0 || b >= lv.B) {
     F8 z;
 #pragma unroll
@@ -91,7 +90,7 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
 template <typename T, typename GT>
 __global__ void __launch_bounds__(256)
 vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n,
-                     VMLevels lv, const GT* __restrict__ dout) {
+                     VMLevels lv, const GT* __restrict__ dout, int out_stride) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
   long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,7 +100,6 @@ vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
   float4 q = __ldg(coords + n);
   int b = (int)q.w;
   if (b < 0 || b >= lv.B) return;
-  const int out_stride = lv.L * lv.C;
   for (int l = 0; l < lv.L; ++l) {
     const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
     Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
@@ -143,14 +141,14 @@ using namespace lmb;
 
 // param_dtype / io_dtype: 0 = fp32, 1 = bf16.
 LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
-                              int param_dtype, void* out, int out_dtype, cudaStream_t stream) {
+                              int param_dtype, void* out, int out_dtype, int out_stride, cudaStream_t stream) {
   if (max_n <= 0) return 0;
   if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
   const int CH = levels->C / 8;
   const int threads = 256;
   const int blocks = ceil_div(max_n * CH, threads);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
-#define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out)
+#define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out, out_stride > 0 ? out_stride : levels->L * levels->C)
   if (param_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
   else if (param_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
   else if (param_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
@@ -161,14 +159,14 @@ LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long lo
 }
 
 LMB_API int lmb_vm_encode_bwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
-                              int param_dtype, const void* dout, int dout_dtype, cudaStream_t stream) {
+                              int param_dtype, const void* dout, int dout_dtype, int dout_stride, cudaStream_t stream) {
   if (max_n <= 0) return 0;
   if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
   const int CH = levels->C / 8;
   const int threads = 256;
   const int blocks = ceil_div(max_n * CH, threads);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
-#define LAUNCH(T, G) vm_encode_bwd_kernel<T, G><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (const G*)dout)
+#define LAUNCH(T, G) vm_encode_bwd_kernel<T, G><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (const G*)dout, dout_stride > 0 ? dout_stride : levels->L * levels->C)
   if (param_dtype == 0 && dout_dtype == 0) LAUNCH(float, float);
   else if (param_dtype == 0 && dout_dtype == 1) LAUNCH(float, __nv_bfloat16);
   else if (param_dtype == 1 && dout_dtype == 0) LAUNCH(__nv_bfloat16, float);

@@ -1,28 +1,296 @@
-"""Python side of the tcgen05 fused-MLP kernels (see ``csrc/fused_mlp.cu``)."""
+"""Python side of the tcgen05 fused-MLP kernel (``csrc/fused_mlp.cu``).
+
+Weights of a whole network are packed once (and re-packed when their version counters change) into
+one device blob in the shared-memory operand layout ``[K/8][N][8]`` bf16 + fp32 biases, which the
+kernel pulls in with a single TMA bulk copy.  Supported: up to 5 layers, every padded layer width
+<= 160, activations none/relu/sigmoid/tanh/exp.  ``rgb_decoder_*`` drives the GridNeRF colour head
+(basis projection + sin/cos expansion + 3-layer decoder) as one kernel.
+
+Backward currently recomputes the network with PyTorch ops under bf16 autocast (cuBLAS); the forward
+of training and all of rendering run the fused kernel.
+"""
 from __future__ import annotations
+
+from ctypes import POINTER, Structure, byref, c_int, c_longlong
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
+from . import native
+
+MAX_LAYERS, MAX_K, MAX_N = 5, 160, 160
+ACT = {"none": 0, "relu": 1, "sigmoid": 2, "tanh": 3, "exp": 4}
+
+
+class MLPSpec(Structure):
+    _fields_ = [("n_layers", c_int), ("K", c_int * MAX_LAYERS), ("N", c_int * MAX_LAYERS), ("act", c_int * MAX_LAYERS),
+                ("w_off", c_int * MAX_LAYERS), ("b_off", c_int * MAX_LAYERS), ("blob_bytes", c_int),
+                ("in_width", c_int), ("out_dim", c_int), ("pe_stage", c_int), ("dir_col", c_int)]
+
+
+native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P,
+                                                 c_int, native.P, native.P])
+
+
+def _pad16(v: int) -> int:
+    return (v + 15) // 16 * 16
+
+
+def _act_name(module) -> str:
+    if module is None:
+        return "none"
+    name = type(module).__name__.lower()
+    return {"relu": "relu", "sigmoid": "sigmoid", "tanh": "tanh"}.get(name, "unsupported")
+
+
+def pack_weight(w: torch.Tensor, n_pad: int, k_pad: int) -> torch.Tensor:
+    """``[N, K]`` -> bf16 ``[k_pad/8, n_pad, 8]`` flattened (zero padded)."""
+    full = torch.zeros(n_pad, k_pad, device=w.device, dtype=torch.float32)
+    full[: w.shape[0], : w.shape[1]] = w.detach().float()
+    return full.view(n_pad, k_pad // 8, 8).permute(1, 0, 2).contiguous().to(torch.bfloat16).view(-1)
+
+
+class PackedMLP:
+    """Device blob + spec for a list of ``(weight [N,K], bias or None, activation)`` layers."""
+
+    def __init__(self, layers: Sequence[Tuple[torch.Tensor, Optional[torch.Tensor], str]], in_width: int,
+                 out_dim: int, pe_stage: bool = False, dir_col: int = 0, k_override: Optional[List[int]] = None):
+        self.layers = layers
+        self.in_width, self.out_dim, self.pe_stage, self.dir_col, self.k_override = in_width, out_dim, pe_stage, dir_col, k_override
+        self.versions = None
+        self.blob = None
+        self.spec = None
+        self.status = None
+
+    def _versions(self):
+        return tuple((w._version, None if b is None else b._version) for w, b, _ in self.layers)
+
+    def refresh(self):
+        if self.versions == self._versions() and self.blob is not None:
+            return
+        dev = self.layers[0][0].device
+        spec = MLPSpec()
+        spec.n_layers = len(self.layers)
+        parts, off = [], 0
+        for l, (w, b, act) in enumerate(self.layers):
+            k_pad = self.k_override[l] if self.k_override else _pad16(w.shape[1])
+            n_pad = _pad16(w.shape[0])
+            assert k_pad <= MAX_K and n_pad <= MAX_N, "layer too wide for the fused kernel"
+            spec.K[l], spec.N[l], spec.act[l] = k_pad, n_pad, ACT[act]
+            packed = pack_weight(w, n_pad, k_pad).view(torch.uint8)
+            spec.w_off[l] = off
+            parts.append(packed)
+            off += packed.numel()
+            if b is not None:
+                bias = torch.zeros(n_pad, device=dev, dtype=torch.float32)
+                bias[: b.shape[0]] = b.detach().float()
+                spec.b_off[l] = off
+                parts.append(bias.view(torch.uint8))
+                off += n_pad * 4
+            else:
+                spec.b_off[l] = -1
+        pad = (-off) % 16
+        if pad:
+            parts.append(torch.zeros(pad, device=dev, dtype=torch.uint8))
+            off += pad
+        spec.blob_bytes, spec.in_width, spec.out_dim = off, self.in_width, self.out_dim
+        spec.pe_stage, spec.dir_col = int(self.pe_stage), self.dir_col
+        self.blob = torch.cat(parts).contiguous()
+        self.spec = spec
+        self.versions = self._versions()
+        if self.status is None:
+            self.status = torch.zeros(1, device=dev, dtype=torch.int32)
+
+    def run(self, x: torch.Tensor, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x [N, in_width]`` bf16 contiguous -> fp32 ``[N, out_dim]``."""
+        self.refresh()
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.in_width
+        out = torch.empty((x.shape[0], self.out_dim), device=x.device, dtype=torch.float32)
+        if count is not None:
+            out.zero_()
+        native.check(native.lib().lmb_fused_mlp_fwd(x.data_ptr(), native.ptr(count), x.shape[0], self.blob.data_ptr(),
+                                                    byref(self.spec), out.data_ptr(), self.out_dim,
+                                                    self.status.data_ptr(), native.stream_ptr()), "fused_mlp_fwd")
+        return out
+
+    def check_status(self) -> None:
+        """Host-side read of the kernel's error word (a bounded wait that expired); call off the hot path."""
+        code = int(self.status.item()) if self.status is not None else 0
+        if code:
+            raise RuntimeError(f"fused MLP kernel reported status {code} (1: weights, 2: input tile, 3: MMA wait)")
+
+
+# -- generic MLPDecoder -----------------------------------------------------------------------
+def _decoder_layers(decoder):
+    linears = decoder.linears()
+    out_act = _act_name(decoder.out_activation)
+    layers = []
+    for i, lin in enumerate(linears):
+        act = "relu" if i < len(linears) - 1 else out_act
+        layers.append((lin.weight, lin.bias, act))
+    return layers
+
 
 def fused_mlp_supported(decoder) -> bool:
-    return False
+    if not native.available():
+        return False
+    layers = _decoder_layers(decoder)
+    if len(layers) > MAX_LAYERS or any(a == "unsupported" for _, _, a in layers):
+        return False
+    return all(_pad16(w.shape[0]) <= MAX_N and _pad16(w.shape[1]) <= MAX_K for w, _, _ in layers)
+
+
+def _torch_mlp(x, layers, acts):
+    h = x
+    for (w, b), act in zip(layers, acts):
+        h = torch.nn.functional.linear(h, w, b)
+        if act == "relu":
+            h = torch.relu(h)
+        elif act == "sigmoid":
+            h = torch.sigmoid(h)
+        elif act == "tanh":
+            h = torch.tanh(h)
+        elif act == "exp":
+            h = torch.exp(h)
+    return h
+
+
+class _FusedMLPFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, packed, n_params, *params):
+        ctx.packed, ctx.n_params = packed, n_params
+        ctx.save_for_backward(x, *params)
+        return packed.run(x)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, *params = ctx.saved_tensors
+        packed = ctx.packed
+        with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            xin = x.detach().requires_grad_(x.is_floating_point())
+            leaves = [p.detach().requires_grad_() for p in params]
+            pairs, it = [], iter(leaves)
+            for w, b, _ in packed.layers:
+                pairs.append((next(it), next(it) if b is not None else None))
+            k0 = packed.layers[0][0].shape[1]
+            out = _torch_mlp(xin[:, :k0], pairs, [a for _, _, a in packed.layers]).float()
+            grads = torch.autograd.grad(out[:, : packed.out_dim], [xin] + leaves, dout, allow_unused=True)
+        return (grads[0], None, None, *grads[1:])
 
 
 def mlp_forward(decoder, features: torch.Tensor) -> torch.Tensor:
-    raise NotImplementedError
+    packed = getattr(decoder, "_lmb_packed", None)
+    layers = _decoder_layers(decoder)
+    in_width = (layers[0][0].shape[1] + 7) // 8 * 8
+    if packed is None or packed.layers[0][0] is not layers[0][0]:
+        packed = PackedMLP(layers, in_width=_pad16(layers[0][0].shape[1]), out_dim=layers[-1][0].shape[0])
+        decoder._lmb_packed = packed
+    x = features
+    if x.shape[1] != packed.in_width or x.dtype != torch.bfloat16:
+        x = torch.nn.functional.pad(x, (0, packed.in_width - x.shape[1])).to(torch.bfloat16)
+    x = x.contiguous()
+    params = [t for w, b, _ in layers for t in ((w, b) if b is not None else (w,))]
+    if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
+        return _FusedMLPFn.apply(x, packed, len(params), *params)
+    return packed.run(x)
+
+
+# -- GridNeRF colour head ---------------------------------------------------------------------------
+RGB_IN_WIDTH = 160
 
 
 def rgb_decoder_supported(decoder) -> bool:
-    return False
+    if not native.available() or decoder.encode_app:
+        return False
+    lin = decoder.decoder.linears()
+    return (decoder.app_dim == 27 and decoder.feape == 2 and decoder.viewpe == 2 and len(lin) == 3
+            and decoder.basis_mat.weight.shape[1] <= 144 and lin[0].weight.shape == (lin[0].weight.shape[0], 150)
+            and lin[0].weight.shape[0] <= 128 and isinstance(decoder.decoder.out_activation, torch.nn.Sigmoid))
 
 
-def rgb_decoder_forward(decoder, dirs, feats):
-    raise NotImplementedError
+def _rgb_packed(decoder) -> PackedMLP:
+    packed = getattr(decoder, "_lmb_packed", None)
+    if packed is None or packed.layers[0][0] is not decoder.basis_mat.weight:
+        lin = decoder.decoder.linears()
+        layers = [(decoder.basis_mat.weight, None, "none"), (lin[0].weight, lin[0].bias, "relu"),
+                  (lin[1].weight, lin[1].bias, "relu"), (lin[2].weight, lin[2].bias, "sigmoid")]
+        packed = PackedMLP(layers, in_width=RGB_IN_WIDTH, out_dim=3, pe_stage=True, dir_col=144,
+                           k_override=[144, 160, _pad16(lin[1].weight.shape[1]), _pad16(lin[2].weight.shape[1])])
+        decoder._lmb_packed = packed
+    return packed
 
 
+class _RGBDecoderFn(torch.autograd.Function):
+    """x: [N, 160] bf16 rows = [features(<=144), dir(3) at col 144, zeros]."""
+
+    @staticmethod
+    def forward(ctx, x, decoder, *params):
+        ctx.decoder = decoder
+        ctx.save_for_backward(x)
+        return _rgb_packed(decoder).run(x)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x,) = ctx.saved_tensors
+        dec = ctx.decoder
+        from ..components.fields.mlp_decoder import positional_encoding
+
+        with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            xin = x.detach().float().requires_grad_()
+            kf = dec.basis_mat.weight.shape[1]
+            f = dec.basis_mat(xin[:, :kf])
+            d = xin[:, 144:147]
+            mlp_in = torch.cat((f, d, positional_encoding(f.float(), 2), positional_encoding(d, 2)), dim=-1)
+            out = dec.decoder.mlp(mlp_in).float()
+            params = list(dec.basis_mat.parameters()) + list(dec.decoder.parameters())
+            grads = torch.autograd.grad(out, [xin] + params, dout)
+        return (grads[0].to(x.dtype), None, *grads[1:])
+
+
+def rgb_decoder_forward(decoder, dirs: torch.Tensor, feats: torch.Tensor) -> torch.Tensor:
+    """``feats``: either ``[N, 160]`` bf16 rows produced by ``vm_encode(out_width=160)`` or plain
+    ``[N, C]`` features; ``dirs [N, 3]``."""
+    if feats.shape[1] == RGB_IN_WIDTH and feats.dtype == torch.bfloat16:
+        x = feats
+        x[:, 144:147] = dirs.to(torch.bfloat16)
+    else:
+        x = torch.cat((feats.to(torch.bfloat16), torch.zeros(feats.shape[0], 144 - feats.shape[1], device=feats.device,
+                                                              dtype=torch.bfloat16),
+                       dirs.to(torch.bfloat16),
+                       torch.zeros(feats.shape[0], RGB_IN_WIDTH - 147, device=feats.device, dtype=torch.bfloat16)), dim=-1)
+    params = list(decoder.basis_mat.parameters()) + list(decoder.decoder.parameters())
+    if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
+        return _RGBDecoderFn.apply(x.contiguous(), decoder, *params)
+    return _rgb_packed(decoder).run(x.contiguous())
+
+
+# -- Scaffold / Octree anchor heads -------------------------------------------------------------------
 def anchor_heads_supported(decoder, *inputs) -> bool:
-    return False
+    if not native.available():
+        return False
+    for seq in (decoder.mlp_opacity, decoder.mlp_cov, decoder.mlp_color):
+        lin = [m for m in seq if isinstance(m, torch.nn.Linear)]
+        if len(lin) != 2 or any(_pad16(l.weight.shape[0]) > MAX_N or _pad16(l.weight.shape[1]) > MAX_K for l in lin):
+            return False
+    return True
 
 
-def anchor_heads_forward(decoder, *inputs):
-    raise NotImplementedError
+def _head_packed(decoder, name: str, seq, out_act: str) -> PackedMLP:
+    key = f"_lmb_packed_{name}"
+    lin = [m for m in seq if isinstance(m, torch.nn.Linear)]
+    packed = getattr(decoder, key, None)
+    if packed is None or packed.layers[0][0] is not lin[0].weight:
+        packed = PackedMLP([(lin[0].weight, lin[0].bias, "relu"), (lin[1].weight, lin[1].bias, out_act)],
+                           in_width=_pad16(lin[0].weight.shape[1]), out_dim=lin[1].weight.shape[0])
+        setattr(decoder, key, packed)
+    return packed
+
+
+def anchor_heads_forward(decoder, op_in, cov_in, col_in):
+    outs = []
+    for name, seq, act, x in (("opacity", decoder.mlp_opacity, "tanh", op_in), ("cov", decoder.mlp_cov, "none", cov_in),
+                              ("color", decoder.mlp_color, "sigmoid", col_in)):
+        packed = _head_packed(decoder, name, seq, act)
+        xb = torch.nn.functional.pad(x, (0, packed.in_width - x.shape[1])).to(torch.bfloat16).contiguous()
+        outs.append(packed.run(xb))
+    return tuple(outs)

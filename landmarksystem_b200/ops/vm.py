@@ -71,21 +71,22 @@ class _VMEncode(torch.autograd.Function):
     (planes..., lines...) and optionally 2*L bf16 shadow tensors that the kernels read instead."""
 
     @staticmethod
-    def forward(ctx, coords, count, out_dtype, n_levels, *grids):
+    def forward(ctx, coords, count, out_dtype, n_levels, out_width, *grids):
         masters = grids[: 2 * n_levels]
         shadows = grids[2 * n_levels:]
         read = shadows if shadows else masters
         planes, lines = list(read[:n_levels]), list(read[n_levels:])
         N = coords.shape[0]
         C = planes[0].shape[-1]
-        out = torch.empty((N, n_levels * C), device=coords.device, dtype=out_dtype)
-        if count is not None:
+        width = max(out_width, n_levels * C)
+        out = torch.empty((N, width), device=coords.device, dtype=out_dtype)
+        if count is not None or width > n_levels * C:
             out.zero_()
         lv = _levels_struct(planes, lines)
         native.check(
             native.lib().lmb_vm_encode_fwd(coords.data_ptr(), native.ptr(count), N, byref(lv),
                                            native.DTYPE_CODE[planes[0].dtype], out.data_ptr(),
-                                           native.DTYPE_CODE[out_dtype], native.stream_ptr()),
+                                           native.DTYPE_CODE[out_dtype], width, native.stream_ptr()),
             "vm_encode_fwd")
         ctx.save_for_backward(coords, count, *read)
         ctx.n_levels = n_levels
@@ -113,21 +114,26 @@ class _VMEncode(torch.autograd.Function):
         native.check(
             native.lib().lmb_vm_encode_bwd(coords.data_ptr(), native.ptr(count), coords.shape[0], byref(lv),
                                            native.DTYPE_CODE[planes[0].dtype], dout.data_ptr(),
-                                           native.DTYPE_CODE[dout.dtype], native.stream_ptr()),
+                                           native.DTYPE_CODE[dout.dtype], dout.shape[1], native.stream_ptr()),
             "vm_encode_bwd")
         out_grads = [None if s else g for s, g in zip(sunk, grads)]
-        return (None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+        return (None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
 
 
 def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torch.Tensor],
               shadow_planes: Optional[List[torch.Tensor]] = None, shadow_lines: Optional[List[torch.Tensor]] = None,
-              count: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+              count: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32,
+              out_width: int = 0) -> torch.Tensor:
     """Look up ``[N, L*C]`` features.  ``shadow_*`` (bf16 copies of the fp32 masters) are what the
-    CUDA kernels read when given; gradients always flow to the fp32 masters."""
+    CUDA kernels read when given; gradients always flow to the fp32 masters.  ``out_width`` > L*C
+    returns a wider, zero-padded row (room for columns a consumer kernel wants appended)."""
     if not coords.is_cuda:
-        return vm_encode_reference(coords, planes, lines).to(out_dtype)
+        feat = vm_encode_reference(coords, planes, lines).to(out_dtype)
+        if out_width > feat.shape[1]:
+            feat = torch.nn.functional.pad(feat, (0, out_width - feat.shape[1]))
+        return feat
     coords = coords.contiguous().float()
     grids = list(planes) + list(lines)
     if shadow_planes is not None:
         grids += list(shadow_planes) + list(shadow_lines)
-    return _VMEncode.apply(coords, count, out_dtype, len(planes), *grids)
+    return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, *grids)

@@ -1,0 +1,71 @@
+"""tcgen05 fused MLP kernel vs a plain PyTorch fp32 reference (bf16-rounded operands)."""
+import pytest
+import torch
+
+from landmarksystem_b200.components.fields.mlp_decoder import MLPDecoder, positional_encoding
+from landmarksystem_b200.models.gridnerf.gridnerf import RGBDecoder
+from landmarksystem_b200.ops import fused_mlp
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _bf(t):
+    return t.to(torch.bfloat16).float()
+
+
+def _ref_mlp(dec, x):
+    h = _bf(x)
+    lin = dec.linears()
+    for i, l in enumerate(lin):
+        h = h @ _bf(l.weight).t() + (l.bias if l.bias is not None else 0)
+        if i < len(lin) - 1:
+            h = _bf(torch.relu(h))
+    return dec.out_activation(h) if dec.out_activation is not None else h
+
+
+@pytest.mark.parametrize("n", [1, 127, 128, 1000, 70000])
+def test_generic_mlp_forward(n):
+    torch.manual_seed(0)
+    dec = MLPDecoder(inChanel=35, layer_width=64, num_layers=3, out_dim=7, out_activation=torch.nn.Sigmoid()).to(DEV)
+    x = torch.randn(n, 35, device=DEV)
+    assert fused_mlp.fused_mlp_supported(dec)
+    with torch.no_grad():
+        out = fused_mlp.mlp_forward(dec, x)
+        ref = _ref_mlp(dec, x)
+    dec._lmb_packed.check_status()
+    assert out.shape == (n, 7)
+    assert torch.allclose(out, ref, atol=2e-2), (out - ref).abs().max()
+
+
+def test_generic_mlp_no_bias_tanh_and_backward():
+    torch.manual_seed(0)
+    dec = MLPDecoder(inChanel=32, layer_width=64, num_layers=2, out_dim=16, out_activation=torch.nn.Tanh(),
+                     mlp_bias=False).to(DEV)
+    x = torch.randn(777, 32, device=DEV, requires_grad=True)
+    out = fused_mlp.mlp_forward(dec, x)
+    ref = _ref_mlp(dec, x.detach())
+    assert torch.allclose(out, ref, atol=2e-2)
+    out.square().sum().backward()
+    g_fused = dec.linears()[0].weight.grad.clone()
+    dec.zero_grad()
+    dec.mlp(x.detach()).square().sum().backward()
+    g_ref = dec.linears()[0].weight.grad
+    assert torch.allclose(g_fused, g_ref, atol=0.05 * g_ref.abs().max().item())
+
+
+def test_rgb_decoder_forward_matches_module():
+    torch.manual_seed(0)
+    dec = RGBDecoder([48], [1, 2, 4], 27, view_pe=2, fea_pe=2, featureC=128).to(DEV)
+    n = 5000
+    feats = torch.randn(n, 144, device=DEV) * 0.3
+    dirs = torch.nn.functional.normalize(torch.randn(n, 3, device=DEV), dim=-1)
+    assert fused_mlp.rgb_decoder_supported(dec)
+    with torch.no_grad():
+        out = fused_mlp.rgb_decoder_forward(dec, dirs, feats)
+        f = _bf(feats) @ _bf(dec.basis_mat.weight).t()
+        d = _bf(dirs)
+        x = torch.cat((f, d, positional_encoding(f, 2), positional_encoding(d, 2)), -1)
+        ref = _ref_mlp(dec.decoder, x)
+    dec._lmb_packed.check_status()
+    assert torch.allclose(out, ref, atol=2e-2), (out - ref).abs().max()
