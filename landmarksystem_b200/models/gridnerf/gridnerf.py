@@ -291,8 +291,18 @@ class GridNeRF(BaseNeRF):
         return self.feature2density(feat).squeeze(-1).float()
 
     def _rgb(self, xyzb, dirs, app_latent=None) -> torch.Tensor:
+        dec = self.rgb_decoder
+        if (xyzb.is_cuda and app_latent is None and getattr(dec, "use_fused", False) and self.config.ndims == 1
+                and type(self.rgb_encoding).__name__ in ("TensorVMEncoding", "BranchParallelTensorVMEncoding",
+                                                         "FusedTensorVMEncoding")):
+            from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_supported
+
+            if rgb_decoder_supported(dec):
+                # lookup writes bf16 rows straight into the fused decoder's 160-wide input layout
+                feat = self.rgb_encoding(xyzb, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH)
+                return dec(dirs, feat, None).float()
         feat = self.rgb_encoding(xyzb)
-        return self.rgb_decoder(dirs, feat, app_latent).float()
+        return dec(dirs, feat, app_latent).float()
 
     def compute_alpha(self, xyz_locs: torch.Tensor, length: float = 1.0) -> torch.Tensor:
         valid = None

@@ -237,12 +237,14 @@ LMB_API int lmb_fused_mlp_fwd(const void* x, const int* count_ptr, long long max
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return 10000 + (int)r;
   const size_t smem = ((spec->blob_bytes + 1023) & ~1023) + (size_t)kSlots * kActBytes + 1024;
-  static bool configured = false;
-  if (!configured) {
-    LMB_CUDA_TRY(cudaFuncSetAttribute(fused_mlp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured = true;
+  // static shared memory of the kernel (barriers, padded to the 1 KB alignment of the dynamic window)
+  // counts against the 227 KB per-CTA limit as well
+  if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > configured) {
+    LMB_CUDA_TRY(cudaFuncSetAttribute(fused_mlp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
   }
-  if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
