@@ -110,6 +110,7 @@ class GridNeRFConfig(ConfigClass):
     # additions of this framework (defaults keep the reference behaviour)
     grid_dtype: Literal["fp32", "bf16"] = "fp32"  # bf16: kernels read bf16 shadows of fp32 master grids
     init_grid_size: Optional[list] = None         # explicit [nx, ny, nz] voxel grid instead of N_voxel_init
+    fused_mlp_train: bool = False                 # colour head through the tcgen05 kernel while training too
     fused_optimizer: bool = True
 
     def check_args(self) -> None:
@@ -292,7 +293,9 @@ class GridNeRF(BaseNeRF):
 
     def _rgb(self, xyzb, dirs, app_latent=None) -> torch.Tensor:
         dec = self.rgb_decoder
-        if (xyzb.is_cuda and app_latent is None and getattr(dec, "use_fused", False) and self.config.ndims == 1
+        fused_ok = (not torch.is_grad_enabled()) or bool(self.config.get("fused_mlp_train", False))
+        if (fused_ok and xyzb.is_cuda and app_latent is None and getattr(dec, "use_fused", False)
+                and self.config.ndims == 1
                 and type(self.rgb_encoding).__name__ in ("TensorVMEncoding", "BranchParallelTensorVMEncoding",
                                                          "FusedTensorVMEncoding")):
             from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_supported

@@ -63,7 +63,9 @@ class PackedMLP:
         self.status = None
 
     def _versions(self):
-        return tuple((w._version, None if b is None else b._version) for w, b, _ in self.layers)
+        from . import optim
+
+        return (optim.GENERATION,) + tuple((w._version, None if b is None else b._version) for w, b, _ in self.layers)
 
     def refresh(self):
         if self.versions == self._versions() and self.blob is not None:

@@ -13,6 +13,12 @@ import torch
 from . import native
 
 
+# Bumped by every fused step: the kernel updates parameters through raw pointers, which autograd's
+# per-tensor version counters do not see, so consumers that cache derived data (packed MLP weights)
+# key their caches on this generation as well.
+GENERATION = 0
+
+
 class FusedAdam(torch.optim.Optimizer):
     """Adam (no amsgrad).  Per-group options: ``lr, betas, eps, weight_decay``.
 
@@ -35,6 +41,8 @@ class FusedAdam(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
+        global GENERATION
+        GENERATION += 1
         loss = closure() if closure is not None else None
         for group in self.param_groups:
             beta1, beta2 = group["betas"]

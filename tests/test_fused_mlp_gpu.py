@@ -69,3 +69,23 @@ def test_rgb_decoder_forward_matches_module():
         ref = _ref_mlp(dec.decoder, x)
     dec._lmb_packed.check_status()
     assert torch.allclose(out, ref, atol=2e-2), (out - ref).abs().max()
+
+
+def test_packed_weights_follow_fused_adam():
+    """The fused optimiser writes parameters through raw pointers; the packed blob must still refresh."""
+    from landmarksystem_b200.ops import FusedAdam
+
+    torch.manual_seed(0)
+    dec = MLPDecoder(inChanel=32, layer_width=64, num_layers=2, out_dim=16).to(DEV)
+    opt = FusedAdam(dec.parameters(), lr=0.1)
+    x = torch.randn(256, 32, device=DEV)
+    with torch.no_grad():
+        before = fused_mlp.mlp_forward(dec, x).clone()
+    for p in dec.parameters():
+        p.grad = torch.ones_like(p)
+    opt.step()
+    with torch.no_grad():
+        after = fused_mlp.mlp_forward(dec, x)
+        ref = _ref_mlp(dec, x)
+    assert not torch.allclose(before, after, atol=1e-3)
+    assert torch.allclose(after, ref, atol=2e-2)
