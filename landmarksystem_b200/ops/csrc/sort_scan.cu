@@ -207,3 +207,50 @@ LMB_API int lmb_radix_sort_pairs(uint64_t* keys, uint32_t* vals, const int* coun
   }
   return 0;
 }
+
+// ---- allocation-free scan entry point (declared in lmb_noalloc.h) ---------------------------------------
+#include <mutex>
+#include "lmb_noalloc.h"
+
+namespace {
+
+// Workspace of the allocation-free scan.  It lives in every CUDA context that loads this library
+// (LMB_NOALLOC_SCAN_SCRATCH_BYTES per GPU, until the process exits) and is shared by all calls.
+static __device__ __align__(256) unsigned char g_noalloc_scan_scratch[LMB_NOALLOC_SCAN_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Resolve the device address of the workspace for the current device.  The array's name is only a
+// host-side handle in host code; the address a kernel can use has to come from the runtime.
+int noalloc_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return LMB_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scan_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch_ptr[dev] = p;
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+LMB_API int lmb_exclusive_scan_u32_noalloc(const uint32_t* in, uint32_t* out, long long n, cudaStream_t stream) {
+  if (n < 0 || in == nullptr || out == nullptr) return LMB_NOALLOC_ERR_ARGUMENT;
+  if (n == 0) return 0;
+  if (n > LMB_NOALLOC_SCAN_MAX_ELEMS || scan_scratch_elems(n) * 4 > (long long)LMB_NOALLOC_SCAN_SCRATCH_BYTES)
+    return LMB_NOALLOC_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // Every workspace word that is read (per-tile sums of each level) is written earlier in the same
+  // call, so nothing has to be cleared even though the array keeps the previous call's contents.
+  return exclusive_scan(in, out, n, (uint32_t*)scratch, stream);
+}
