@@ -1,0 +1,55 @@
+"""Mean squared distance to the three nearest neighbours (``distCUDA2`` of the reference's simple_knn
+submodule; call sites gaussian_encoding.py:124-136, scaffoldgs_encoding.py:121-143)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int
+
+import torch
+
+from . import native
+from .gaussian_raster import _lib_ll
+
+P = native.P
+native.register_signature("lmb_knn_mean_dist2", [c_int, P, c_float, c_float, c_float, c_float, c_int, c_int, c_int, P, P, P,
+                                                  P, P, P, P])
+
+
+def knn_mean_dist2_reference(points: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+    out = []
+    for s in range(0, points.shape[0], chunk):
+        d2 = torch.cdist(points[s:s + chunk], points).pow(2)
+        k = min(4, points.shape[0])
+        best = torch.topk(d2, k, dim=1, largest=False).values[:, 1:]   # drop the point itself
+        out.append(best.sum(1) / 3.0)
+    return torch.cat(out)
+
+
+def distCUDA2(points: torch.Tensor) -> torch.Tensor:
+    """``points [N, 3]`` -> ``[N]`` mean of the squared distances to the 3 nearest other points."""
+    if not points.is_cuda:
+        return knn_mean_dist2_reference(points.float())
+    pts = points.contiguous().float()
+    n = pts.shape[0]
+    lo, hi = pts.amin(0), pts.amax(0)
+    ext = (hi - lo).clamp_min(1e-6)
+    # ~2 points per occupied cell on average, capped to 2^24 cells
+    vol = float(ext.prod()) if float(ext.min()) > 1e-5 else float(ext.topk(2).values.prod())
+    dims_guess = 3 if float(ext.min()) > 1e-5 else 2
+    cell = (vol / max(n / 2.0, 1.0)) ** (1.0 / dims_guess)
+    dims = [max(int(float(e) / cell) + 1, 1) for e in ext]
+    while dims[0] * dims[1] * dims[2] > (1 << 24):
+        cell *= 1.26
+        dims = [max(int(float(e) / cell) + 1, 1) for e in ext]
+    n_cells = dims[0] * dims[1] * dims[2]
+    dev = pts.device
+    keys = torch.empty(n, dtype=torch.int64, device=dev)
+    vals = torch.empty(n, dtype=torch.int32, device=dev)
+    cs = torch.empty(n_cells, dtype=torch.int32, device=dev)
+    ce = torch.empty(n_cells, dtype=torch.int32, device=dev)
+    ws = torch.empty(_lib_ll("lmb_radix_sort_scratch_bytes")(n), dtype=torch.uint8, device=dev)
+    out = torch.empty(n, device=dev)
+    l = lo.tolist()
+    native.check(native.lib().lmb_knn_mean_dist2(n, pts.data_ptr(), l[0], l[1], l[2], cell, dims[0], dims[1], dims[2],
+                                                 keys.data_ptr(), vals.data_ptr(), cs.data_ptr(), ce.data_ptr(),
+                                                 ws.data_ptr(), out.data_ptr(), native.stream_ptr()), "knn_mean_dist2")
+    return out

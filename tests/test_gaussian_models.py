@@ -1,0 +1,198 @@
+"""Gaussian-splatting family: encodings, PLY formats, densification surgery and short training runs."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from landmarksystem_b200.components.fields.encodings.gaussian_encoding import GaussianEncoding
+from landmarksystem_b200.components.fields.encodings.octreegs_encoding import OctreeGSEncoding
+from landmarksystem_b200.components.fields.encodings.scaffoldgs_encoding import ScaffoldGSEncoding, voxel_keys
+from landmarksystem_b200.components.utils.graphics_utils import BasicPointCloud
+from landmarksystem_b200.components.utils.ply_utils import read_ply
+from landmarksystem_b200.configs import BaseConfig
+from landmarksystem_b200.ops.knn import distCUDA2, knn_mean_dist2_reference
+
+ROOT = os.path.join(os.path.dirname(__file__), "..", "landmarksystem_b200", "models")
+
+
+def _pcd(n=200, seed=0):
+    rng = np.random.default_rng(seed)
+    return BasicPointCloud(rng.random((n, 3), dtype=np.float32) * 2 - 1, rng.random((n, 3), dtype=np.float32),
+                           np.zeros((n, 3), np.float32))
+
+
+def test_gaussian_encoding_ply_roundtrip_and_properties(tmp_path):
+    enc = GaussianEncoding(3, device="cpu")
+    enc.create_from_pcd(_pcd())
+    path = str(tmp_path / "point_cloud.ply")
+    enc.save_ply(path)
+    names = read_ply(path).dtype.names
+    assert names[:6] == ("x", "y", "z", "nx", "ny", "nz") and "f_dc_2" in names and "f_rest_44" in names
+    assert "opacity" in names and "scale_2" in names and "rot_3" in names
+    other = GaussianEncoding(3, device="cpu")
+    other.load_ply(path)
+    for a, b in zip(enc.parameters(), other.parameters()):
+        assert torch.allclose(a, b)
+    cache = str(tmp_path / "cache.ply")
+    enc.save_ply(cache, cache=True)
+    assert "cache_opacity" in read_ply(cache).dtype.names
+    third = GaussianEncoding(3, device="cpu")
+    third.load_ply(cache)
+    assert torch.allclose(third.get_opacity, enc.get_opacity, atol=1e-5)
+    assert torch.allclose(third.get_scaling, enc.get_scaling, rtol=1e-4)
+
+
+def test_densify_and_prune_keeps_optimizer_in_sync():
+    torch.manual_seed(0)
+    enc = GaussianEncoding(1, device="cpu")
+    enc.create_from_pcd(_pcd(100))
+    groups = [{"params": [getattr(enc, a)], "lr": 1e-3, "name": n} for n, a in
+              (("xyz", "_xyz"), ("f_dc", "_features_dc"), ("f_rest", "_features_rest"), ("opacity", "_opacity"),
+               ("scaling", "_scaling"), ("rotation", "_rotation"))]
+    opt = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
+    for p in enc.parameters():
+        p.grad = torch.randn_like(p)
+    opt.step()
+    enc.xyz_gradient_accum[:] = torch.rand(100, 1)
+    enc.denom[:] = 1
+    enc.densify_and_prune(0.5, 0.005, 4.0, None, opt)
+    n = enc._xyz.shape[0]
+    assert n != 100
+    for g in opt.param_groups:
+        p = g["params"][0]
+        assert p.shape[0] == n and opt.state[p]["exp_avg"].shape == p.shape
+    assert enc.denom.shape[0] == n and enc.max_radii2D.shape[0] == n
+    enc.reset_opacity(opt)
+    assert enc.get_opacity.max() <= 0.0101
+
+
+def test_knn_reference_small():
+    pts = torch.tensor([[0.0, 0, 0], [1, 0, 0], [0, 2, 0], [0, 0, 3], [5, 5, 5]])
+    d = knn_mean_dist2_reference(pts)
+    assert torch.allclose(d[0], torch.tensor((1 + 4 + 9) / 3.0))
+
+
+@pytest.mark.gpu
+def test_knn_cuda_matches_reference():
+    torch.manual_seed(0)
+    pts = torch.rand(20000, 3) * torch.tensor([10.0, 4.0, 1.0])
+    ref = knn_mean_dist2_reference(pts)
+    got = distCUDA2(pts.cuda()).cpu()
+    assert torch.allclose(got, ref, rtol=1e-4, atol=1e-7)
+    flat = pts.clone(); flat[:, 2] = 0
+    assert torch.allclose(distCUDA2(flat.cuda()).cpu(), knn_mean_dist2_reference(flat), rtol=1e-4, atol=1e-7)
+
+
+def test_scaffold_encoding_ply_and_growing(tmp_path):
+    torch.manual_seed(0)
+    enc = ScaffoldGSEncoding(feat_dim=8, n_offsets=4, voxel_size=0.25, device="cpu")
+    enc.create_from_pcd(_pcd(400))
+    n0 = len(enc)
+    assert n0 > 0 and len(torch.unique(voxel_keys(torch.round(enc._anchor / 0.25)))) == n0
+    path = str(tmp_path / "pc.ply")
+    enc.save_ply(path)
+    names = read_ply(path).dtype.names
+    assert "f_offset_11" in names and "f_anchor_feat_7" in names and "scale_5" in names
+    other = ScaffoldGSEncoding(feat_dim=8, n_offsets=4, voxel_size=0.25, device="cpu")
+    other.load_ply(path)
+    assert torch.allclose(other._offset, enc._offset) and torch.allclose(other._scaling, enc._scaling)
+    groups = [{"params": [getattr(enc, a)], "lr": 1e-3, "name": n} for n, a in
+              (("anchor", "_anchor"), ("offset", "_offset"), ("anchor_feat", "_anchor_feat"), ("opacity", "_opacity"),
+               ("scaling", "_scaling"), ("rotation", "_rotation"))]
+    opt = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
+    enc._offset.data.normal_(0, 3.0)            # push neural Gaussians into empty voxels
+    enc.offset_gradient_accum[:] = 1.0
+    enc.offset_denom[:] = 100
+    enc.anchor_demon[:] = 100
+    enc.opacity_accum[:] = 100
+    enc.opacity_accum[:5] = 0                   # these anchors get pruned
+    enc.adjust_anchor(check_interval=100, success_threshold=0.8, grad_threshold=0.0002, min_opacity=0.005, optimizer=opt)
+    n1 = len(enc)
+    assert n1 > n0 - 5
+    assert enc.offset_denom.shape[0] == n1 * 4 and enc.opacity_accum.shape[0] == n1
+    for g in opt.param_groups:
+        assert g["params"][0].shape[0] == n1
+
+
+def test_octree_levels_and_lod_mask():
+    from landmarksystem_b200.components.data.cameras import Camera
+    from landmarksystem_b200.synthetic import ring_cameras
+
+    enc = OctreeGSEncoding(feat_dim=8, n_offsets=4, base_layer=3, device="cpu", visible_threshold=0.0)
+    cams = [Camera.from_c2w(p.numpy(), 32, 32, 30.0, uid=i) for i, p in enumerate(ring_cameras(6, 3.0))]
+    pcd = _pcd(500)
+    enc.set_level(torch.from_numpy(pcd.points), cams, [1.0], dist_ratio=0.95, levels=3)
+    enc.set_coarse_interval(300, 1.5)
+    assert enc.levels == 3 and len(enc.coarse_intervals) == 3 - 1 - enc.init_level
+    enc.create_from_pcd(pcd)
+    assert set(enc.get_level.unique().tolist()) <= {0.0, 1.0, 2.0}
+    enc.set_anchor_mask(torch.tensor([0.0, 0.0, 0.5]), 10 ** 6, 1.0, True)
+    near = enc._anchor_mask.sum()
+    enc.set_anchor_mask(torch.tensor([0.0, 0.0, 50.0]), 10 ** 6, 1.0, True)
+    far = enc._anchor_mask.sum()
+    assert near > far > 0          # a distant camera selects only coarse levels
+
+
+@pytest.mark.gpu
+def test_octree_lod_kernel_matches_torch():
+    from landmarksystem_b200.components.data.cameras import Camera
+    from landmarksystem_b200.synthetic import ring_cameras
+
+    cams = [Camera.from_c2w(p.numpy(), 32, 32, 30.0, uid=i) for i, p in enumerate(ring_cameras(6, 3.0))]
+    pcd = _pcd(3000)
+    for mode in ("round", "floor", "progressive"):
+        cpu = OctreeGSEncoding(feat_dim=8, n_offsets=4, base_layer=4, device="cpu", dist2level=mode)
+        cpu.set_level(torch.from_numpy(pcd.points), cams, [1.0], levels=4)
+        cpu.create_from_pcd(pcd)
+        gpu = OctreeGSEncoding(feat_dim=8, n_offsets=4, base_layer=4, device="cuda", dist2level=mode)
+        gpu.levels, gpu.standard_dist, gpu.init_level = cpu.levels, cpu.standard_dist, cpu.init_level
+        gpu.voxel_size = cpu.voxel_size
+        gpu.load_encoding_state({k: v.detach() for k, v in [("_anchor", cpu._anchor), ("_offset", cpu._offset),
+                                 ("_anchor_feat", cpu._anchor_feat), ("_scaling", cpu._scaling),
+                                 ("_rotation", cpu._rotation), ("_opacity", cpu._opacity), ("_level", cpu._level),
+                                 ("_extra_level", cpu._extra_level)]})
+        gpu.voxel_size, gpu.standard_dist, gpu.levels = cpu.voxel_size, cpu.standard_dist, cpu.levels
+        c = torch.tensor([0.4, -0.3, 2.0])
+        cpu.set_anchor_mask(c, 10 ** 6, 1.0, False)
+        gpu.set_anchor_mask(c, 10 ** 6, 1.0, False)
+        assert (cpu._anchor_mask != gpu._anchor_mask.cpu()).float().mean() < 1e-3
+
+
+@pytest.mark.parametrize("family,trainer_name", [("origin_gs", "Gaussian3DTrainer"), ("scaffold_gs", "ScaffoldGSTrainer"),
+                                                  ("octree_gs", "OctreeGSTrainer")])
+def test_cpu_smoke_training_and_checkpoint(family, trainer_name, tmp_path):
+    import importlib
+
+    mod = importlib.import_module(f"landmarksystem_b200.models.{family}.gs_trainer")
+    conf = os.path.join(ROOT, family, "confs", "synthetic_train.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": str(tmp_path), "device": "cpu", "n_iters": "3",
+                                      "datadir": "ring:3:16x16:18:3", "init_points_num": "60",
+                                      "progress_refresh_rate": "100"})
+    trainer = getattr(mod, trainer_name)(cfg)
+    ps = trainer.train()
+    assert np.isfinite(ps)
+    folder = os.path.join(trainer.logfolder, "point_cloud", "iteration_3")
+    assert os.path.exists(os.path.join(folder, "point_cloud.ply")) and os.path.exists(os.path.join(folder, "opt.th"))
+    # checkpoint round trip through the model-level API
+    fresh = trainer.build_model()
+    fresh.load_from_state_dict(fresh.get_state_dict_from_ckpt(os.path.join(folder, "point_cloud.ply"), "cpu"))
+    assert fresh.get_primitives_num == trainer.model.get_primitives_num
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("family,trainer_name,gain", [("origin_gs", "Gaussian3DTrainer", 3.0),
+                                                       ("scaffold_gs", "ScaffoldGSTrainer", 2.0),
+                                                       ("octree_gs", "OctreeGSTrainer", 2.0)])
+def test_gpu_training_improves_psnr(family, trainer_name, gain, tmp_path):
+    import importlib
+
+    mod = importlib.import_module(f"landmarksystem_b200.models.{family}.gs_trainer")
+    conf = os.path.join(ROOT, family, "confs", "synthetic_train.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": str(tmp_path), "device": "cuda", "n_iters": "400",
+                                      "datadir": "ring:12:64x64:75:3", "init_points_num": "3000",
+                                      "progress_refresh_rate": "1000", "skip_save_imgs": "true"})
+    trainer = getattr(mod, trainer_name)(cfg)
+    before = trainer.evaluation(str(tmp_path / "before"), stride=1)
+    after = trainer.train()
+    assert after > before + gain, (before, after)
