@@ -1,0 +1,121 @@
+"""InstantNGP / Nerfacto: occupancy marching, proposal sampling, scene contraction and short trainings."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from landmarksystem_b200.components.ray_samplers.proposal_network_sampler import (PropPDFSampler, SpacedSampler,
+                                                                                  spacing_fn, spacing_fn_inv)
+from landmarksystem_b200.configs import BaseConfig
+from landmarksystem_b200.models.nerfacto.nerfacto import scene_contraction
+from landmarksystem_b200.ops.occgrid import OccGridEstimator
+
+ROOT = os.path.join(os.path.dirname(__file__), "..", "landmarksystem_b200", "models")
+
+
+def _grid(levels=2, res=8, seed=0):
+    est = OccGridEstimator([-1.0, -1, -1, 1, 1, 1], res, levels)
+    g = torch.Generator().manual_seed(seed)
+    est.binaries = torch.rand(levels, res, res, res, generator=g) > 0.6
+    return est
+
+
+def _rays(n=64, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    o = torch.tensor([0.0, 0.0, 3.0]) + 0.3 * torch.randn(n, 3, generator=g)
+    d = torch.nn.functional.normalize(-o + 0.8 * torch.randn(n, 3, generator=g), dim=-1)
+    return o, d
+
+
+def test_march_reference_samples_lie_in_occupied_cells():
+    est = _grid(levels=1)
+    o, d = _rays(16)
+    counts, ts, te = est.sampling(o, d, near_plane=0.1, far_plane=10.0, render_step_size=0.05, max_samples=64)
+    assert counts.sum() > 0
+    for r in range(16):
+        for s in range(int(counts[r])):
+            p = o[r] + d[r] * 0.5 * (ts[r, s] + te[r, s])
+            idx = ((p * 0.5 + 0.5) * 8).long().clamp(0, 7)
+            assert est.binaries[0, idx[0], idx[1], idx[2]]
+            assert abs(float(te[r, s] - ts[r, s]) - 0.05) < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cone", [0.0, 0.01])
+def test_march_kernel_matches_reference(cone):
+    est = _grid(levels=2)
+    o, d = _rays(200)
+    c0, ts0, te0 = est.sampling(o, d, near_plane=0.1, far_plane=10.0, render_step_size=0.04, cone_angle=cone, max_samples=96)
+    est_g = _grid(levels=2).cuda()
+    c1, ts1, te1 = est_g.sampling(o.cuda(), d.cuda(), near_plane=0.1, far_plane=10.0, render_step_size=0.04, cone_angle=cone,
+                                  max_samples=96)
+    same = (c0 == c1.cpu())
+    assert same.float().mean() > 0.97          # fp rounding at cell borders may flip isolated samples
+    rows = same.nonzero().squeeze(-1)
+    assert torch.allclose(ts0[rows], ts1.cpu()[rows], atol=1e-3)
+
+
+def test_grid_update_marks_dense_region():
+    est = OccGridEstimator([-1.0, -1, -1, 1, 1, 1], 16, 1)
+    est.train()
+    est.update_every_n_steps(0, lambda x: (x.norm(dim=-1) < 0.5).float(), occ_thre=0.01)
+    frac = est.binaries.float().mean()
+    assert 0.02 < frac < 0.2                   # ~ volume of the radius-0.5 ball inside the cube
+    assert est.binaries[0, 8, 8, 8] and not est.binaries[0, 0, 0, 0]
+
+
+def test_spacing_and_pdf_sampler():
+    x = torch.tensor([0.1, 0.9, 1.0, 3.0, 50.0])
+    assert torch.allclose(spacing_fn_inv(spacing_fn(x)), x, rtol=1e-5)
+    sp = SpacedSampler().eval()
+    o, d = _rays(8)
+    rs = sp(o, d, 0.5, 20.0, 32)
+    assert rs.starts.shape == (8, 32, 1) and torch.all(rs.ends >= rs.starts)
+    assert abs(float(rs.starts[0, 0, 0]) - 0.5) < 1e-4 and abs(float(rs.ends[0, -1, 0]) - 20.0) < 1e-3
+    w = torch.zeros(8, 32, 1)
+    w[:, 10:12] = 1.0
+    fine = PropPDFSampler(include_original=False).eval()(rs, w, 16)
+    inside = (fine.spacing_starts[..., 0] >= rs.spacing_starts[:, 9:10, 0]) & (fine.spacing_ends[..., 0] <= rs.spacing_ends[:, 12:13, 0])
+    assert inside.float().mean() > 0.8         # resampled intervals concentrate where the weight is
+
+
+def test_scene_contraction():
+    x = torch.tensor([[0.5, -0.2, 0.1], [4.0, 0.0, 0.0], [0.0, -100.0, 50.0]])
+    y = scene_contraction(x)
+    assert torch.allclose(y[0], x[0]) and torch.allclose(y[1], torch.tensor([1.75, 0.0, 0.0]))
+    assert y.abs().max() < 2.0
+
+
+@pytest.mark.parametrize("family,module,cls", [("instant_ngp", "instant_ngp_trainer", "NGPTrainer"),
+                                                ("nerfacto", "nerfacto_trainer", "NerfactoTrainer")])
+def test_cpu_smoke(family, module, cls, tmp_path):
+    import importlib
+
+    mod = importlib.import_module(f"landmarksystem_b200.models.{family}.{module}")
+    cfg = BaseConfig.from_file(os.path.join(ROOT, family, "confs", "synthetic_tiny.py"),
+                               {"basedir": str(tmp_path), "device": "cpu", "n_iters": "3", "datadir": "ring:3:12x12:14:3",
+                                "batch_size": "64", "progress_refresh_rate": "100"})
+    trainer = getattr(mod, cls)(cfg)
+    trainer.train()
+    assert os.path.exists(os.path.join(trainer.logfolder, "state_dict.th"))
+    state = torch.load(os.path.join(trainer.logfolder, "state_dict.th"), weights_only=False)
+    assert "mlp_base_grid.tcnn_encoding.params" in state      # reference checkpoint key of the hash table
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("family,module,cls", [("instant_ngp", "instant_ngp_trainer", "NGPTrainer"),
+                                                ("nerfacto", "nerfacto_trainer", "NerfactoTrainer")])
+def test_gpu_training_reduces_loss(family, module, cls, tmp_path):
+    import importlib
+
+    mod = importlib.import_module(f"landmarksystem_b200.models.{family}.{module}")
+    cfg = BaseConfig.from_file(os.path.join(ROOT, family, "confs", "synthetic_tiny.py"),
+                               {"basedir": str(tmp_path), "device": "cuda", "n_iters": "300", "progress_refresh_rate": "1000",
+                                "runtime": "Kernel"})
+    trainer = getattr(mod, cls)(cfg)
+    trainer.model.train()
+    losses = []
+    for trainer.iteration in range(300):
+        losses.append(float(trainer.train_step(*trainer.data_mgr.get_rays(trainer.iteration))))
+    assert np.mean(losses[-20:]) < 0.5 * np.mean(losses[:20]), (np.mean(losses[:20]), np.mean(losses[-20:]))
