@@ -115,6 +115,15 @@ class TensorVMEncoding(VolumeEncoding):
                 if name in state and tuple(state[name].shape) != tuple(param.shape):
                     param.data = torch.empty_like(state[name], device=param.device)  # adopt checkpoint shape
 
+    @staticmethod
+    def block_to_internal(name: str, piece: torch.Tensor) -> torch.Tensor:
+        """One-block slice in checkpoint layout -> the in-memory (channels-last) layout, for dynamic loading."""
+        if name.startswith("plane_coef") and piece.dim() == 5:
+            return _plane_from_ref(piece)
+        if name.startswith("line_coef") and piece.dim() == 4:
+            return _line_from_ref(piece)
+        return piece
+
     def param_shape(self) -> Dict[str, List[int]]:
         """Reference-layout parameter shapes (what ``kwargs.th`` stores under ``grid_shape``)."""
         shapes = {}
