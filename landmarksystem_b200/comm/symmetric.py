@@ -1,0 +1,110 @@
+"""Symmetric peer memory over NVLink: every rank allocates the same-sized buffer, the CUDA IPC handles
+are exchanged once through ``torch.distributed`` and each rank maps all peers' buffers.  Kernels
+then take an array of peer pointers and read / write remote HBM with ordinary loads and stores.
+
+Also provides :class:`PeerBarrier`, a device-side barrier (release/acquire flags in peer memory, bounded
+waits) that orders such kernels across GPUs without a host round trip or an NCCL call.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_uint, c_void_p
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+P = native.P
+for _name, _sig in (("lmb_symm_alloc", [c_longlong, ctypes.POINTER(c_void_p)]), ("lmb_symm_free", [P]),
+                    ("lmb_ipc_get_handle", [P, P]), ("lmb_ipc_open", [P, ctypes.POINTER(c_void_p)]),
+                    ("lmb_ipc_close", [P]), ("lmb_peer_barrier", [P, P, c_int, c_int, c_uint, P, P])):
+    native.register_signature(_name, _sig)
+
+
+class _RawCuda:
+    """Minimal ``__cuda_array_interface__`` carrier so torch can wrap a raw device pointer."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricBuffer:
+    """``nbytes`` of device memory on every rank of ``group``, each mapped into every other rank."""
+
+    def __init__(self, nbytes: int, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.nbytes = int((nbytes + 255) // 256 * 256)
+        lib = native.lib()
+        ptr = c_void_p()
+        native.check(lib.lmb_symm_alloc(self.nbytes, ctypes.byref(ptr)), "symm_alloc")
+        self.local_ptr = ptr.value
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        handle = (ctypes.c_ubyte * 64)()
+        native.check(lib.lmb_ipc_get_handle(self.local_ptr, handle), "ipc_get_handle")
+        handles: List[Optional[bytes]] = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        else:
+            handles = [bytes(handle)]
+        self.peer_ptrs: List[int] = []
+        self._opened: List[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.peer_ptrs.append(self.local_ptr)
+                continue
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            out = c_void_p()
+            native.check(lib.lmb_ipc_open(buf, ctypes.byref(out)), "ipc_open")
+            self.peer_ptrs.append(out.value)
+            self._opened.append(out.value)
+        self._keep = _RawCuda(self.local_ptr, self.nbytes)
+        self.local = torch.as_tensor(self._keep, device=self.device)            # uint8 view of the local buffer
+        self.ptr_table = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
+
+    def view(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Typed view of the local buffer starting at byte ``offset`` (must be suitably aligned)."""
+        n = int(torch.tensor(shape).prod()) * torch.empty((), dtype=dtype).element_size()
+        return self.local[offset:offset + n].view(dtype).view(*shape)
+
+    def peer_table(self, offset: int = 0) -> torch.Tensor:
+        """Device ``int64 [world]`` array of peer addresses of byte ``offset`` inside the buffer."""
+        return self.ptr_table + offset
+
+    def close(self):
+        lib = native.lib()
+        for p in self._opened:
+            lib.lmb_ipc_close(p)
+        self._opened = []
+        if self.local_ptr:
+            self.local = None
+            lib.lmb_symm_free(self.local_ptr)
+            self.local_ptr = 0
+
+
+class PeerBarrier:
+    """Stream-ordered barrier across the ranks of a group, executed by a one-block kernel per rank."""
+
+    def __init__(self, group=None):
+        self.buf = SymmetricBuffer(256, group)
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.buf.device)
+        self.flag_table = self.buf.peer_table(0)
+        if self.buf.world > 1:
+            dist.barrier(group)          # every rank has mapped every flag array before the first signal
+
+    def __call__(self) -> None:
+        if self.buf.world == 1:
+            return
+        self.epoch += 1
+        native.check(native.lib().lmb_peer_barrier(self.buf.local_ptr, self.flag_table.data_ptr(), self.buf.rank,
+                                                   self.buf.world, self.epoch, self.status.data_ptr(),
+                                                   native.stream_ptr()), "peer_barrier")
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"peer barrier timed out waiting for rank {code - 100}")

@@ -1,0 +1,167 @@
+// Fused compute + collective kernels over NVLink peer memory (plain P2P loads / stores).
+//
+// (1) zero_adam_p2p - data-parallel gradient reduce-scatter + partitioned Adam + parameter all-gather in
+//     ONE kernel.  Rank r owns the r-th shard of every flat parameter buffer: it loads that shard of
+//     every rank's gradient straight from peer HBM, reduces, applies Adam to its fp32 master shard
+//     (moments live only on the owner), stores the updated values into every rank's parameter buffer
+//     (and bf16 shadow) and clears the gradients it consumed.  The reference does a bucketed NCCL
+//     all-reduce inside DistributedDataParallel followed by a replicated torch.optim.Adam
+//     (benchmarks/nerf/gridnerf/gridnerf_trainer.py:120-154).
+// (2) composite_merge_p2p - model-parallel rendering: every GPU holds, for every ray, the partial
+//     colour / transmittance / depth of the ray segment that crosses ITS spatial blocks plus the
+//     segment's entry distance.  Rank r merges the r-th slice of rays: it pulls the P partials of each
+//     ray from the peers, orders them by entry distance and alpha-composites them front to back, then
+//     stores the finished pixels into the output image of the root (or of every rank).  The reference
+//     has no model-parallel rendering merge (its engine only gathers data-parallel ray slices,
+//     landmark/render/parallel_module/parallel_module.py:105-135).
+// Cross-GPU ordering around both kernels comes from the device-side barrier in symm.cu.
+#include "common.cuh"
+
+namespace lmb {
+
+constexpr int kMaxPeers = 8;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+struct AdamP2PArgs {
+  float lr, beta1, beta2, eps, bias1, bias2, grad_scale;
+};
+
+// n4: number of float4 elements of the whole flat buffer; shard = [begin4, end4)
+__global__ void __launch_bounds__(256)
+zero_adam_p2p_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs shadows, float4* __restrict__ m, float4* __restrict__ v,
+                     int world, long long begin4, long long end4, AdamP2PArgs a, int has_shadow) {
+  const float step = a.lr / a.bias1;
+  const float inv_sqrt_b2 = rsqrtf(a.bias2);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long i = begin4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 g = zero;
+#pragma unroll
+    for (int p = 0; p < kMaxPeers; ++p) {
+      if (p >= world) break;
+      float4* gp = reinterpret_cast<float4*>(grads.p[p]) + i;
+      const float4 x = *gp;                 // peer load over NVLink
+      g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      *gp = zero;                           // the owner of the shard is the only reader: clear in place
+    }
+    const long long li = i - begin4;
+    float4 pp = reinterpret_cast<float4*>(params.p[0])[i];   // params.p[0] is the local copy
+    float4 mm = m[li], vv = v[li];
+    float* G = &g.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gr = G[k] * a.grad_scale;
+      M[k] = a.beta1 * M[k] + (1.f - a.beta1) * gr;
+      V[k] = a.beta2 * V[k] + (1.f - a.beta2) * gr * gr;
+      P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + a.eps);
+    }
+    m[li] = mm; v[li] = vv;
+    uint2 sh;
+    if (has_shadow) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+      sh.x = *reinterpret_cast<unsigned*>(&lo); sh.y = *reinterpret_cast<unsigned*>(&hi);
+    }
+#pragma unroll
+    for (int p = 0; p < kMaxPeers; ++p) {   // all-gather: push the new values to every rank
+      if (p >= world) break;
+      reinterpret_cast<float4*>(params.p[p])[i] = pp;
+      if (has_shadow) reinterpret_cast<uint2*>(shadows.p[p])[i] = sh;
+    }
+  }
+}
+
+// partial layout per ray: 8 floats = r, g, b, T, depth, acc, t_entry, pad
+__global__ void __launch_bounds__(256)
+composite_merge_p2p_kernel(PeerPtrs partials, PeerPtrs outs, int world, int rank, int root, long long ray_begin,
+                           long long ray_end, float bg) {
+  const long long r = ray_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= ray_end) return;
+  float4 a[kMaxPeers], b[kMaxPeers];
+  int order[kMaxPeers];
+#pragma unroll
+  for (int p = 0; p < kMaxPeers; ++p) {
+    if (p >= world) break;
+    const float4* src = reinterpret_cast<const float4*>(partials.p[p]) + 2 * r;
+    a[p] = src[0];   // r g b T
+    b[p] = src[1];   // depth acc t_entry pad
+    order[p] = p;
+  }
+  // insertion sort of at most 8 segments by entry distance
+  for (int i = 1; i < world; ++i) {
+    const int k = order[i];
+    int j = i - 1;
+    while (j >= 0 && b[order[j]].z > b[k].z) { order[j + 1] = order[j]; --j; }
+    order[j + 1] = k;
+  }
+  float T = 1.f, C0 = 0.f, C1 = 0.f, C2 = 0.f, D = 0.f, A = 0.f;
+  for (int i = 0; i < world; ++i) {
+    const int k = order[i];
+    C0 += T * a[k].x; C1 += T * a[k].y; C2 += T * a[k].z;
+    D += T * b[k].x; A += T * b[k].y;
+    T *= a[k].w;
+  }
+  const float4 px = make_float4(C0 + T * bg, C1 + T * bg, C2 + T * bg, T);
+  const float2 da = make_float2(D, A);
+#pragma unroll
+  for (int p = 0; p < kMaxPeers; ++p) {
+    if (p >= world) break;
+    if (root >= 0 && p != root) continue;
+    float* o = reinterpret_cast<float*>(outs.p[p]) + 6 * r;
+    reinterpret_cast<float2*>(o)[0] = make_float2(px.x, px.y);
+    reinterpret_cast<float2*>(o)[1] = make_float2(px.z, px.w);
+    reinterpret_cast<float2*>(o)[2] = da;
+  }
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+static void fill_peers(PeerPtrs& dst, const long long* table, int world, int rank_first) {
+  // rotate so that entry 0 is the local rank (kernels treat p[0] as "mine" where it matters)
+  for (int i = 0; i < kMaxPeers; ++i) dst.p[i] = nullptr;
+  for (int i = 0; i < world; ++i) dst.p[i] = (void*)table[(rank_first + i) % world];
+}
+
+// grad_table / param_table / shadow_table: host arrays of `world` peer addresses (same byte offset in
+// every rank's symmetric buffer).  n must be a multiple of 4 * world.  m, v: local, n / world floats.
+LMB_API int lmb_zero_adam_p2p(const long long* grad_table, const long long* param_table, const long long* shadow_table,
+                              float* m, float* v, long long n, int rank, int world, float lr, float beta1, float beta2,
+                              float eps, int step, float grad_scale, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers || n % (4LL * world) != 0) return (int)cudaErrorInvalidValue;
+  PeerPtrs g, p, s;
+  fill_peers(g, grad_table, world, rank);
+  fill_peers(p, param_table, world, rank);
+  if (shadow_table) fill_peers(s, shadow_table, world, rank); else for (int i = 0; i < kMaxPeers; ++i) s.p[i] = nullptr;
+  AdamP2PArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale;
+  a.bias1 = 1.f - powf(beta1, (float)step);
+  a.bias2 = 1.f - powf(beta2, (float)step);
+  const long long shard4 = n / 4 / world;
+  const long long begin4 = shard4 * rank, end4 = begin4 + shard4;
+  if (shard4 == 0) return 0;
+  long long want = (shard4 + 255) / 256;
+  const int blocks = (int)(want < 148LL * 8 ? want : 148LL * 8);
+  zero_adam_p2p_kernel<<<blocks, 256, 0, stream>>>(g, p, s, (float4*)m, (float4*)v, world, begin4, end4, a,
+                                                  shadow_table != nullptr);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// partial_table / out_table: peer addresses of the [R, 8] partial and [R, 6] output buffers.
+LMB_API int lmb_composite_merge_p2p(const long long* partial_table, const long long* out_table, long long n_rays, int rank,
+                                    int world, int root, float bg, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers) return (int)cudaErrorInvalidValue;
+  PeerPtrs part, out;
+  for (int i = 0; i < kMaxPeers; ++i) { part.p[i] = nullptr; out.p[i] = nullptr; }
+  for (int i = 0; i < world; ++i) { part.p[i] = (void*)partial_table[i]; out.p[i] = (void*)out_table[i]; }
+  const long long per = (n_rays + world - 1) / world;
+  const long long begin = per * rank, end = begin + per < n_rays ? begin + per : n_rays;
+  if (end <= begin) return 0;
+  composite_merge_p2p_kernel<<<ceil_div(end - begin, 256), 256, 0, stream>>>(part, out, world, rank, root, begin, end, bg);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
