@@ -45,7 +45,8 @@ zero_adam_p2p_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs shadows, float4* 
       float4* gp = reinterpret_cast<float4*>(grads.p[p]) + i;
       const float4 x = *gp;                 // peer load over NVLink
       g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
-      *gp = zero;                           // the owner of the shard is the only reader: clear in place
+      if (p == 0) *gp = zero;               // local gradient: clear in place (remote ones are cleared by
+                                            // their owners after the closing barrier - no NVLink bytes)
     }
     const long long li = i - begin4;
     float4 pp = reinterpret_cast<float4*>(params.p[0])[i];   // params.p[0] is the local copy
@@ -148,6 +149,16 @@ LMB_API int lmb_zero_adam_p2p(const long long* grad_table, const long long* para
   zero_adam_p2p_kernel<<<blocks, 256, 0, stream>>>(g, p, s, (float4*)m, (float4*)v, world, begin4, end4, a,
                                                   shadow_table != nullptr);
   LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// After the closing barrier: clear the part of the LOCAL gradient buffer that other ranks own (they have
+// finished reading it).  grad_local is this rank's flat gradient buffer of n floats.
+LMB_API int lmb_zero_adam_clear_remote_shards(float* grad_local, long long n, int rank, int world, cudaStream_t stream) {
+  const long long shard = n / world;
+  if (rank > 0) LMB_CUDA_TRY(cudaMemsetAsync(grad_local, 0, (size_t)(shard * rank) * 4, stream));
+  if (rank < world - 1)
+    LMB_CUDA_TRY(cudaMemsetAsync(grad_local + shard * (rank + 1), 0, (size_t)(shard * (world - 1 - rank)) * 4, stream));
   return 0;
 }
 

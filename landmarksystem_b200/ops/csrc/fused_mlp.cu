@@ -45,6 +45,17 @@ struct MLPSpec {
   int dir_col;              // column of the input row that holds the view direction (pe_stage)
 };
 
+// Input rows may be assembled from several tensors ("sources"), each contributing a contiguous range of
+// 16-byte column chunks of the A tile.  A source can live in a peer GPU's memory: the tile is then
+// pulled over NVLink by the (non-multicast) TMA load itself, which fuses an all-gather of column
+// slices into the first GEMM of the network.
+constexpr int kMaxSources = 4;
+struct alignas(64) MLPInputs {
+  CUtensorMap map[kMaxSources];
+  int chunk_begin[kMaxSources + 1];
+  int n_src;
+};
+
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {
     case ACT_RELU: return fmaxf(x, 0.f);
@@ -70,7 +81,7 @@ __device__ __forceinline__ float load_elem(const unsigned char* buf, int col, in
 
 // status words: 0 ok, 1 weight load timed out, 2 input tile load timed out, 3 MMA completion timed out
 __global__ void __launch_bounds__(kSlots * kSlotThreads, 1)
-fused_mlp_kernel(const __grid_constant__ CUtensorMap in_map, const unsigned char* __restrict__ blob, MLPSpec spec,
+fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* __restrict__ blob, MLPSpec spec,
                  const int* __restrict__ count_ptr, long long max_rows, float* __restrict__ out, int out_stride,
                  int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -119,8 +130,12 @@ fused_mlp_kernel(const __grid_constant__ CUtensorMap in_map, const unsigned char
     // ---- input tile: one TMA box [8 elems, 1 chunk, 128 rows] per 16-byte column chunk -------------
     if (row == 0) {
       tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
-      for (int c = 0; c < in_chunks; ++c)
-        tc05::tma_load_3d(act + (size_t)c * kTileRows * 16, &in_map, 0, c, (int)row0, &bar_in[slot]);
+      int src = 0;
+      for (int c = 0; c < in_chunks; ++c) {
+        while (src + 1 < inputs.n_src && c >= inputs.chunk_begin[src + 1]) ++src;
+        tc05::tma_load_3d(act + (size_t)c * kTileRows * 16, &inputs.map[src], 0, c - inputs.chunk_begin[src], (int)row0,
+                          &bar_in[slot]);
+      }
     }
     bool got = tc05::mbar_wait(&bar_in[slot], ph_in);
     ph_in ^= 1;
@@ -216,29 +231,44 @@ fused_mlp_kernel(const __grid_constant__ CUtensorMap in_map, const unsigned char
 
 using namespace lmb;
 
-// x: [max_rows, spec.in_width] bf16 row-major (16-byte aligned rows).  out: fp32 [max_rows, out_stride].
-// status: one int in device memory, written non-zero if a bounded wait expired.
-LMB_API int lmb_fused_mlp_fwd(const void* x, const int* count_ptr, long long max_rows, const void* blob,
-                              const MLPSpec* spec, float* out, int out_stride, int* status, cudaStream_t stream) {
+static int encode_input_map(CUtensorMap* map, const void* x, int width, long long rows) {
+  const cuuint64_t gdim[3] = {8, (cuuint64_t)(width / 8), (cuuint64_t)rows};
+  const cuuint64_t gstride[2] = {16, (cuuint64_t)width * 2};
+  const cuuint32_t box[3] = {8, 1, (cuuint32_t)kTileRows};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride, box,
+                                      estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 10000 + (int)r;
+}
+
+// xs[s]: [max_rows, widths[s]] bf16 row-major (widths multiples of 8, summing to spec.in_width); a source may
+// be a peer GPU's buffer.  out: fp32 [max_rows, out_stride].  status: device int, set non-zero if a
+// bounded wait expired.
+LMB_API int lmb_fused_mlp_fwd_multi(const void* const* xs, const int* widths, int n_src, const int* count_ptr,
+                                    long long max_rows, const void* blob, const MLPSpec* spec, float* out, int out_stride,
+                                    int* status, cudaStream_t stream) {
   if (max_rows <= 0) return 0;
+  if (n_src < 1 || n_src > kMaxSources) return (int)cudaErrorInvalidValue;
   if (spec->n_layers < 1 || spec->n_layers > kMaxLayers || spec->in_width % 8 || spec->in_width > kMaxK ||
       spec->blob_bytes % 16)
     return (int)cudaErrorInvalidValue;
   for (int l = 0; l < spec->n_layers; ++l)
     if (spec->K[l] % 16 || spec->K[l] > kMaxK || spec->N[l] % 16 || spec->N[l] > kSlotCols || spec->N[l] < 16)
       return (int)cudaErrorInvalidValue;
-  CUtensorMap map;
-  const cuuint64_t gdim[3] = {8, (cuuint64_t)(spec->in_width / 8), (cuuint64_t)max_rows};
-  const cuuint64_t gstride[2] = {16, (cuuint64_t)spec->in_width * 2};
-  const cuuint32_t box[3] = {8, 1, (cuuint32_t)kTileRows};
-  const cuuint32_t estride[3] = {1, 1, 1};
-  CUresult r = cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride,
-                                      box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return 10000 + (int)r;
+  MLPInputs inputs;
+  inputs.n_src = n_src;
+  int chunk = 0;
+  for (int s = 0; s < n_src; ++s) {
+    if (widths[s] % 8 || widths[s] <= 0) return (int)cudaErrorInvalidValue;
+    inputs.chunk_begin[s] = chunk;
+    int rc = encode_input_map(&inputs.map[s], xs[s], widths[s], max_rows);
+    if (rc) return rc;
+    chunk += widths[s] / 8;
+  }
+  for (int s = n_src; s <= kMaxSources; ++s) inputs.chunk_begin[s] = chunk;
+  if (chunk * 8 != spec->in_width) return (int)cudaErrorInvalidValue;
   const size_t smem = ((spec->blob_bytes + 1023) & ~1023) + (size_t)kSlots * kActBytes + 1024;
-  // static shared memory of the kernel (barriers, padded to the 1 KB alignment of the dynamic window)
-  // counts against the 227 KB per-CTA limit as well
   if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
   static size_t configured = 0;
   if (smem > configured) {
@@ -250,8 +280,15 @@ LMB_API int lmb_fused_mlp_fwd(const void* x, const int* count_ptr, long long max
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = (max_rows + kTileRows - 1) / kTileRows;
   const int grid = (int)((tiles + kSlots - 1) / kSlots < sms ? (tiles + kSlots - 1) / kSlots : sms);
-  fused_mlp_kernel<<<grid, kSlots * kSlotThreads, smem, stream>>>(map, (const unsigned char*)blob, *spec, count_ptr,
+  fused_mlp_kernel<<<grid, kSlots * kSlotThreads, smem, stream>>>(inputs, (const unsigned char*)blob, *spec, count_ptr,
                                                                 max_rows, out, out_stride, status);
   LMB_LAUNCH_CHECK();
   return 0;
+}
+
+LMB_API int lmb_fused_mlp_fwd(const void* x, const int* count_ptr, long long max_rows, const void* blob,
+                              const MLPSpec* spec, float* out, int out_stride, int* status, cudaStream_t stream) {
+  const void* xs[1] = {x};
+  const int widths[1] = {spec->in_width};
+  return lmb_fused_mlp_fwd_multi(xs, widths, 1, count_ptr, max_rows, blob, spec, out, out_stride, status, stream);
 }

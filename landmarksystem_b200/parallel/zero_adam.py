@@ -24,6 +24,10 @@ native.register_signature("lmb_zero_adam_p2p", [native.P, native.P, native.P, na
                                                  ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_float, native.P])
 
 
+native.register_signature("lmb_zero_adam_clear_remote_shards", [native.P, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                                                 native.P])
+
+
 def _table(t: torch.Tensor):
     vals = t.tolist()
     return (ctypes.c_longlong * len(vals))(*vals)
@@ -96,6 +100,8 @@ class P2PZeroAdam:
                                                     self.step_count, (1.0 / self.world) if self.average else 1.0,
                                                     native.stream_ptr()), "zero_adam_p2p")
         self.barrier()                                   # every shard has landed in every replica
+        native.check(native.lib().lmb_zero_adam_clear_remote_shards(f.flat_grad.data_ptr(), f.n, self.rank, self.world,
+                                                                    native.stream_ptr()), "zero_adam_clear")
 
     def zero_grad(self, set_to_none=True):
         for p in self.flat.params:

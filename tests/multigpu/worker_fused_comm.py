@@ -68,8 +68,7 @@ def main():
     opt_big = P2PZeroAdam(big, lr=0.01, shadow=True)
     ms = timed(opt_big.step, iters=5)
     shard = n // world
-    # bytes over NVLink per rank: (world-1) * shard * (4 read + 4 clear + 4 param + 2 shadow)
-    nvlink = (world - 1) * shard * 14
+    nvlink = (world - 1) * shard * 6     # outgoing per rank: new fp32 value + bf16 shadow to every peer
     hbm = shard * (world * 8 + 4 + 8 + 8 + world * 6)
     results["zero_adam_p2p"] = {"ms": ms, "params": n, "nvlink_GBps_per_rank": nvlink / ms / 1e6,
                                 "hbm_GBps_per_rank": hbm / ms / 1e6}
@@ -92,7 +91,9 @@ def main():
     depth = torch.rand(R, device="cuda", generator=g)
     acc = 1 - trans
     t_entry = torch.rand(R, device="cuda", generator=g) * 100
-    t_entry[torch.rand(R, device="cuda", generator=g) < 0.3] = float("inf")
+    empty = torch.rand(R, device="cuda", generator=g) < 0.3          # rays that miss this rank's blocks
+    t_entry[empty] = float("inf")
+    rgb[empty], trans[empty], depth[empty], acc[empty] = 0.0, 1.0, 0.0, 0.0
     mine = pack_partial(rgb, trans, depth, acc, t_entry)
     merger = CompositeMerger(R)
     out = merger.merge(mine, bg=1.0, root=-1).clone()

@@ -28,3 +28,11 @@ def test_fused_comm_kernels():
     sys.stdout.write(res.stdout[-3000:])
     assert res.returncode == 0, res.stderr[-3000:]
     assert "FUSED_COMM_RESULTS" in res.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_channel_gather_fused_into_mlp():
+    res = _launch("worker_channel_gather.py", 2)
+    sys.stdout.write(res.stdout[-2000:])
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "CHANNEL_GATHER_RESULTS" in res.stdout
