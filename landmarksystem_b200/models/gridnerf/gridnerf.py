@@ -111,6 +111,8 @@ class GridNeRFConfig(ConfigClass):
     grid_dtype: Literal["fp32", "bf16"] = "fp32"  # bf16: kernels read bf16 shadows of fp32 master grids
     init_grid_size: Optional[list] = None         # explicit [nx, ny, nz] voxel grid instead of N_voxel_init
     fused_mlp_train: bool = False                 # colour head through the tcgen05 kernel while training too
+    branch_dispatch: Literal["allreduce", "a2a"] = "allreduce"   # a2a: every rank brings its own rays; samples
+                                                  # travel to the GPU owning their block over NVLink peer memory
     fused_optimizer: bool = True
 
     def check_args(self) -> None:
@@ -287,6 +289,41 @@ class GridNeRF(BaseNeRF):
             block = torch.where(mine, torch.zeros_like(block), torch.full_like(block, -1.0))
         return torch.cat((local, block[:, None]), dim=-1)
 
+    # -- branch parallel through the peer-memory all-to-all -------------------------------------------------
+    def _use_a2a(self) -> bool:
+        c = self.config
+        return bool(c.get("branch_parallel", False) and c.get("is_train", False) and c.get("branch_dispatch") == "a2a"
+                    and self.aabb.is_cuda and torch.distributed.is_initialized())
+
+    def _dispatcher(self, n_rows: int):
+        disp = getattr(self, "_a2a", None)
+        if disp is None or disp.cap < n_rows:
+            from ...parallel.branch_dispatch import BlockDispatcher
+
+            disp = BlockDispatcher(n_rows, max_w=6, max_v=3, group=self.config.mp_group)
+            self._a2a = disp
+        return disp
+
+    class _OwnerFn:
+        """Callable evaluated on the owning rank; exposes the parameters its backward feeds."""
+
+        def __init__(self, model, kind):
+            self.model, self.kind = model, kind
+
+        def parameters_for_autograd(self):
+            m = self.model
+            mods = [m.density_encoding, m.feature2density] if self.kind == "sigma" else [m.rgb_encoding, m.rgb_decoder]
+            return [p for mod in mods for p in mod.parameters()]
+
+        def __call__(self, rows):
+            m = self.model
+            xyzb = torch.cat((rows[:, :3], torch.zeros_like(rows[:, :1])), dim=-1)
+            if self.kind == "sigma":
+                m.sigma_batch = torch.tensor(rows.shape[0], device=rows.device)
+                return m._density(xyzb)[:, None]
+            m.app_batch = torch.tensor(rows.shape[0], device=rows.device)
+            return m._rgb(xyzb, rows[:, 3:6].contiguous(), None)
+
     def _density(self, xyzb: torch.Tensor) -> torch.Tensor:
         feat = self.density_encoding(xyzb)
         return self.feature2density(feat).squeeze(-1).float()
@@ -369,14 +406,29 @@ class GridNeRF(BaseNeRF):
         valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
         if self.alphaMask is not None:
             valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
-        xyzb = self._xyzb(xyz, valid)
-        self.sigma_batch = (xyzb[:, 3] >= 0).sum()
-        sigma = self._mp_sum(self._density(xyzb)).view(R, S)
+        a2a = self._use_a2a()
+        if a2a:
+            local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
+            owner = torch.where(valid, block, torch.full_like(block, -1.0))
+            xyzb = torch.cat((local, owner[:, None]), dim=-1)
+            disp = self._dispatcher(R * S)
+            sigma = disp.query(local, owner, GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+        else:
+            xyzb = self._xyzb(xyz, valid)
+            self.sigma_batch = (xyzb[:, 3] >= 0).sum()
+            sigma = self._mp_sum(self._density(xyzb)).view(R, S)
         dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
         weight = self.renderer.get_weights(sigma, dists * cfg.distance_scale)
         app_mask = (weight > cfg.rayMarch_weight_thres).reshape(-1)
         rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)
         idx = app_mask.nonzero(as_tuple=True)[0]
+        if a2a:
+            ray_of = idx // S
+            payload = torch.cat((xyzb[idx, :3], dirs[ray_of]), dim=-1)
+            vals = self._dispatcher(R * S).query(payload, xyzb[idx, 3], GridNeRF._OwnerFn(self, "rgb"), 3)
+            rgb = rgb.index_put((idx,), vals)
+            rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
+            return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists
         self.app_batch = (xyzb[idx, 3] >= 0).sum()
         if idx.numel() > 0 or (train and getattr(cfg, "branch_parallel", False)):
             if idx.numel() == 0:

@@ -1,0 +1,156 @@
+// All-to-all dispatch / combine over NVLink peer memory for spatial-block (branch) model parallelism.
+//
+// Every sample is routed to the GPU that owns the spatial block it falls into.  The reference instead
+// has every rank of the model-parallel group process the SAME rays, evaluate only its own block and
+// exchange the results with variable-length list all-gathers preceded by host syncs
+// (landmark/nerf_components/data/samples.py:283-309).  Here:
+//   dispatch: a source thread appends its record (payload + source slot) to the owner's inbox segment
+//             reserved for that source with a plain peer store; slots come from a local counter, so no
+//             remote atomics and no pre-exchange of counts are needed;
+//   collect : the owner compacts the P inbox segments (their counts arrive with the barrier);
+//   combine : the owner stores each result row straight into the source's output buffer at the
+//             sample's slot - the "scatter back" costs no kernel on the source.
+// The same three kernels run the backward with the roles of payload and result swapped.
+#include "common.cuh"
+
+namespace lmb {
+
+constexpr int kA2AMaxPeers = 8;
+
+struct A2APeers {
+  void* p[kA2AMaxPeers];
+};
+
+// payload: [n, W] floats; dst[n]: owner rank or -1.  inbox layout on every rank: [world][cap][W + 1] floats.
+// pos_out[n]: position inside the (dst, src) segment (needed to route gradients back).
+__global__ void __launch_bounds__(256)
+a2a_dispatch_kernel(const float* __restrict__ payload, const int* __restrict__ dst, long long n, int W, A2APeers inbox,
+                    int src_rank, long long cap, int* __restrict__ counts, int* __restrict__ pos_out, int* overflow) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst[i];
+  if (d < 0) { pos_out[i] = -1; return; }
+  const int pos = atomicAdd(&counts[d], 1);
+  if (pos >= cap) { pos_out[i] = -1; atomicExch(overflow, 1); return; }
+  pos_out[i] = pos;
+  float* rec = reinterpret_cast<float*>(inbox.p[d]) + ((long long)src_rank * cap + pos) * (W + 1);
+  for (int k = 0; k < W; ++k) rec[k] = payload[i * W + k];
+  rec[W] = __int_as_float((int)i);
+}
+
+// counts of this rank are copied into every peer's incoming[src_rank]
+__global__ void a2a_publish_kernel(const int* __restrict__ counts, A2APeers incoming, int src_rank, int world, long long cap) {
+  const int d = threadIdx.x;
+  if (d >= world) return;
+  const int c = counts[d];
+  reinterpret_cast<int*>(incoming.p[d])[src_rank] = c < cap ? c : (int)cap;
+}
+
+// Compact the inbox segments: offsets[s] = exclusive prefix of incoming[s]; out rows [M, W], route (src, slot).
+__global__ void __launch_bounds__(256)
+a2a_collect_kernel(const float* __restrict__ inbox, const int* __restrict__ incoming, int world, long long cap, int W,
+                   float* __restrict__ rows, int* __restrict__ route_src, int* __restrict__ route_slot) {
+  long long base = 0;
+  for (int s = 0; s < world; ++s) {
+    const int c = incoming[s];
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < c; k += (long long)gridDim.x * blockDim.x) {
+      const float* rec = inbox + ((long long)s * cap + k) * (W + 1);
+      for (int j = 0; j < W; ++j) rows[(base + k) * W + j] = rec[j];
+      route_src[base + k] = s;
+      route_slot[base + k] = __float_as_int(rec[W]);
+    }
+    base += c;
+  }
+}
+
+// values: [M, V]; written to outs[src] + slot * V
+__global__ void __launch_bounds__(256)
+a2a_combine_kernel(const float* __restrict__ values, const int* __restrict__ route_src, const int* __restrict__ route_slot,
+                   long long m, int V, A2APeers outs) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  float* o = reinterpret_cast<float*>(outs.p[route_src[i]]) + (long long)route_slot[i] * V;
+  for (int k = 0; k < V; ++k) o[k] = values[i * V + k];
+}
+
+// Backward of combine: a source sends d_out[i, :V] to the owner's gradient inbox at (src, pos[i]).
+__global__ void __launch_bounds__(256)
+a2a_grad_dispatch_kernel(const float* __restrict__ dout, const int* __restrict__ dst, const int* __restrict__ pos, long long n,
+                         int V, A2APeers ginbox, int src_rank, long long cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst[i], p = pos[i];
+  if (d < 0 || p < 0) return;
+  float* rec = reinterpret_cast<float*>(ginbox.p[d]) + ((long long)src_rank * cap + p) * V;
+  for (int k = 0; k < V; ++k) rec[k] = dout[i * V + k];
+}
+
+__global__ void __launch_bounds__(256)
+a2a_grad_collect_kernel(const float* __restrict__ ginbox, const int* __restrict__ incoming, int world, long long cap, int V,
+                        float* __restrict__ rows) {
+  long long base = 0;
+  for (int s = 0; s < world; ++s) {
+    const int c = incoming[s];
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < c; k += (long long)gridDim.x * blockDim.x) {
+      const float* rec = ginbox + ((long long)s * cap + k) * V;
+      for (int j = 0; j < V; ++j) rows[(base + k) * V + j] = rec[j];
+    }
+    base += c;
+  }
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+static void fill(A2APeers& dst, const long long* table, int world) {
+  for (int i = 0; i < kA2AMaxPeers; ++i) dst.p[i] = i < world ? (void*)table[i] : nullptr;
+}
+
+LMB_API int lmb_a2a_dispatch(const float* payload, const int* dst, long long n, int W, const long long* inbox_table,
+                             const long long* incoming_table, int rank, int world, long long cap, int* counts, int* pos_out,
+                             int* overflow, cudaStream_t stream) {
+  if (world > kA2AMaxPeers) return (int)cudaErrorInvalidValue;
+  A2APeers inbox, incoming;
+  fill(inbox, inbox_table, world);
+  fill(incoming, incoming_table, world);
+  LMB_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * world, stream));
+  if (n > 0) a2a_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(payload, dst, n, W, inbox, rank, cap, counts, pos_out, overflow);
+  a2a_publish_kernel<<<1, 32, 0, stream>>>(counts, incoming, rank, world, cap);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_a2a_collect(const float* inbox, const int* incoming, int world, long long cap, int W, float* rows,
+                            int* route_src, int* route_slot, cudaStream_t stream) {
+  a2a_collect_kernel<<<148 * 4, 256, 0, stream>>>(inbox, incoming, world, cap, W, rows, route_src, route_slot);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_a2a_combine(const float* values, const int* route_src, const int* route_slot, long long m, int V,
+                            const long long* out_table, int world, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  A2APeers outs;
+  fill(outs, out_table, world);
+  a2a_combine_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(values, route_src, route_slot, m, V, outs);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_a2a_grad_dispatch(const float* dout, const int* dst, const int* pos, long long n, int V,
+                                  const long long* ginbox_table, int rank, int world, long long cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  A2APeers g;
+  fill(g, ginbox_table, world);
+  a2a_grad_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(dout, dst, pos, n, V, g, rank, cap);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_a2a_grad_collect(const float* ginbox, const int* incoming, int world, long long cap, int V, float* rows,
+                                 cudaStream_t stream) {
+  a2a_grad_collect_kernel<<<148 * 4, 256, 0, stream>>>(ginbox, incoming, world, cap, V, rows);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}

@@ -29,47 +29,69 @@ struct AdamP2PArgs {
   float lr, beta1, beta2, eps, bias1, bias2, grad_scale;
 };
 
-// n4: number of float4 elements of the whole flat buffer; shard = [begin4, end4)
+// n4: number of float4 elements of the whole flat buffer; shard = [begin4, end4).
+// Each thread handles kUnroll float4 per trip and issues all of their peer loads before using any, so
+// that enough NVLink requests are in flight to cover the link latency.
+constexpr int kAdamUnroll = 4;
+
 __global__ void __launch_bounds__(256)
 zero_adam_p2p_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs shadows, float4* __restrict__ m, float4* __restrict__ v,
                      int world, long long begin4, long long end4, AdamP2PArgs a, int has_shadow) {
   const float step = a.lr / a.bias1;
   const float inv_sqrt_b2 = rsqrtf(a.bias2);
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (long long i = begin4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end4;
-       i += (long long)gridDim.x * blockDim.x) {
-    float4 g = zero;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long base = begin4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; base < end4; base += stride * kAdamUnroll) {
+    float4 g[kAdamUnroll], pp[kAdamUnroll], mm[kAdamUnroll], vv[kAdamUnroll];
+#pragma unroll
+    for (int u = 0; u < kAdamUnroll; ++u) g[u] = zero;
 #pragma unroll
     for (int p = 0; p < kMaxPeers; ++p) {
       if (p >= world) break;
-      float4* gp = reinterpret_cast<float4*>(grads.p[p]) + i;
-      const float4 x = *gp;                 // peer load over NVLink
-      g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
-      if (p == 0) *gp = zero;               // local gradient: clear in place (remote ones are cleared by
-                                            // their owners after the closing barrier - no NVLink bytes)
-    }
-    const long long li = i - begin4;
-    float4 pp = reinterpret_cast<float4*>(params.p[0])[i];   // params.p[0] is the local copy
-    float4 mm = m[li], vv = v[li];
-    float* G = &g.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float gr = G[k] * a.grad_scale;
-      M[k] = a.beta1 * M[k] + (1.f - a.beta1) * gr;
-      V[k] = a.beta2 * V[k] + (1.f - a.beta2) * gr * gr;
-      P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + a.eps);
-    }
-    m[li] = mm; v[li] = vv;
-    uint2 sh;
-    if (has_shadow) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
-      sh.x = *reinterpret_cast<unsigned*>(&lo); sh.y = *reinterpret_cast<unsigned*>(&hi);
+      for (int u = 0; u < kAdamUnroll; ++u) {
+        const long long i = base + u * stride;
+        if (i < end4) {
+          const float4 x = __ldcv(reinterpret_cast<const float4*>(grads.p[p]) + i);   // peer load over NVLink
+          g[u].x += x.x; g[u].y += x.y; g[u].z += x.z; g[u].w += x.w;
+        }
+      }
     }
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p) {   // all-gather: push the new values to every rank
-      if (p >= world) break;
-      reinterpret_cast<float4*>(params.p[p])[i] = pp;
-      if (has_shadow) reinterpret_cast<uint2*>(shadows.p[p])[i] = sh;
+    for (int u = 0; u < kAdamUnroll; ++u) {
+      const long long i = base + u * stride;
+      if (i < end4) {
+        pp[u] = reinterpret_cast<float4*>(params.p[0])[i];   // params.p[0] is the local replica
+        mm[u] = m[i - begin4];
+        vv[u] = v[i - begin4];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kAdamUnroll; ++u) {
+      const long long i = base + u * stride;
+      if (i >= end4) continue;
+      float* G = &g[u].x; float* P = &pp[u].x; float* M = &mm[u].x; float* V = &vv[u].x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gr = G[k] * a.grad_scale;
+        M[k] = a.beta1 * M[k] + (1.f - a.beta1) * gr;
+        V[k] = a.beta2 * V[k] + (1.f - a.beta2) * gr * gr;
+        P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + a.eps);
+      }
+      m[i - begin4] = mm[u]; v[i - begin4] = vv[u];
+      reinterpret_cast<float4*>(grads.p[0])[i] = zero;   // local gradient shard; remote ones are cleared by
+                                                         // their owners after the closing barrier
+      uint2 sh;
+      if (has_shadow) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(pp[u].x, pp[u].y), hi = __floats2bfloat162_rn(pp[u].z, pp[u].w);
+        sh.x = *reinterpret_cast<unsigned*>(&lo); sh.y = *reinterpret_cast<unsigned*>(&hi);
+      }
+#pragma unroll
+      for (int p = 0; p < kMaxPeers; ++p) {   // all-gather: push the new values to every rank
+        if (p >= world) break;
+        reinterpret_cast<float4*>(params.p[p])[i] = pp[u];
+        if (has_shadow) reinterpret_cast<uint2*>(shadows.p[p])[i] = sh;
+      }
     }
   }
 }

@@ -179,18 +179,18 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
 #pragma unroll
         for (int i = 0; i < 27; ++i) {
           x[i] = f[i];
-          float s1, c1, s2, c2;
+          float s1, c1;
           __sincosf(f[i], &s1, &c1);
-          __sincosf(2.f * f[i], &s2, &c2);
+          const float s2 = 2.f * s1 * c1, c2 = 1.f - 2.f * s1 * s1;   // double-angle: half the SFU work
           x[30 + 2 * i] = s1; x[31 + 2 * i] = s2;
           x[84 + 2 * i] = c1; x[85 + 2 * i] = c2;
         }
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
           x[27 + i] = dir[i];
-          float s1, c1, s2, c2;
+          float s1, c1;
           __sincosf(dir[i], &s1, &c1);
-          __sincosf(2.f * dir[i], &s2, &c2);
+          const float s2 = 2.f * s1 * c1, c2 = 1.f - 2.f * s1 * s1;
           x[138 + 2 * i] = s1; x[139 + 2 * i] = s2;
           x[144 + 2 * i] = c1; x[145 + 2 * i] = c2;
         }
@@ -202,8 +202,31 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
         for (int n0 = 0; n0 < N; n0 += 16) {
           float v[16];
           tc05::tmem_ld16(tmem_lane + n0, v);
+          if (bias) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i] + (bias ? bias[n0 + i] : 0.f), spec.act[l]);
+            for (int i = 0; i < 16; ++i) v[i] += bias[n0 + i];
+          }
+          // the activation is uniform per layer: branch once per 16 columns instead of letting the
+          // compiler evaluate every transcendental for every element and select
+          switch (spec.act[l]) {
+            case ACT_RELU:
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+              break;
+            case ACT_SIGMOID:
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = __fdividef(1.f, 1.f + __expf(-v[i]));
+              break;
+            case ACT_TANH:
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = tanhf(v[i]);
+              break;
+            case ACT_EXP:
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = __expf(v[i]);
+              break;
+            default: break;
+          }
           if (!last) {
             store_chunk(act, (n0 >> 3), row, v);
             store_chunk(act, (n0 >> 3) + 1, row, v + 8);

@@ -1,0 +1,117 @@
+"""Spatial-block all-to-all over peer memory (north-star path "b").
+
+``BlockDispatcher.query(payload, owner, fn, out_width)`` sends each row of ``payload`` to the rank that
+owns it, runs ``fn`` there on the compacted rows (a differentiable PyTorch callable - grid lookup +
+MLP head), and returns the results in the caller's row order.  Gradients w.r.t. the results travel the
+reverse route and ``fn``'s backward runs on the owner, so grid gradients stay local to the owner.
+CPU / single-rank calls degenerate to ``fn(payload)``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+from ..comm.symmetric import PeerBarrier, SymmetricBuffer
+from ..ops import native
+from .zero_adam import _table
+
+P = native.P
+native.register_signature("lmb_a2a_dispatch", [P, P, c_longlong, c_int, P, P, c_int, c_int, c_longlong, P, P, P, P])
+native.register_signature("lmb_a2a_collect", [P, P, c_int, c_longlong, c_int, P, P, P, P])
+native.register_signature("lmb_a2a_combine", [P, P, P, c_longlong, c_int, P, c_int, P])
+native.register_signature("lmb_a2a_grad_dispatch", [P, P, P, c_longlong, c_int, P, c_int, c_int, c_longlong, P])
+native.register_signature("lmb_a2a_grad_collect", [P, P, c_int, c_longlong, c_int, P, P])
+
+
+class BlockDispatcher:
+    """``cap`` = max rows one source may send to one owner; ``max_w`` / ``max_v`` = widest payload / result."""
+
+    def __init__(self, cap: int, max_w: int = 8, max_v: int = 4, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.cap, self.max_w, self.max_v = int(cap), max_w, max_v
+        w = self.world
+        self.off_inbox = 0
+        self.off_ginbox = self.off_inbox + w * cap * (max_w + 1) * 4
+        self.off_out = self.off_ginbox + w * cap * max_v * 4
+        self.off_incoming = self.off_out + cap * max_v * 4
+        total = self.off_incoming + 256
+        self.buf = SymmetricBuffer(total, group)
+        self.inbox_table = _table(self.buf.peer_table(self.off_inbox))
+        self.ginbox_table = _table(self.buf.peer_table(self.off_ginbox))
+        self.out_table = _table(self.buf.peer_table(self.off_out))
+        self.incoming_table = _table(self.buf.peer_table(self.off_incoming))
+        self.incoming = self.buf.view(self.off_incoming, (w,), torch.int32)
+        dev = self.buf.device
+        self.counts = torch.zeros(w, dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier = PeerBarrier(group)
+
+    def query(self, payload: torch.Tensor, owner: torch.Tensor, fn: Callable[[torch.Tensor], torch.Tensor],
+              out_width: int) -> torch.Tensor:
+        return _Query.apply(payload, owner, self, fn, out_width, *_fn_params(fn))
+
+
+def _fn_params(fn):
+    params = getattr(fn, "parameters_for_autograd", None)
+    return tuple(params()) if params is not None else ()
+
+
+class _Query(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, payload, owner, disp: BlockDispatcher, fn, out_width, *params):
+        lib, st = native.lib(), native.stream_ptr()
+        n, W = payload.shape
+        assert W <= disp.max_w and out_width <= disp.max_v and n <= disp.cap
+        payload = payload.contiguous().float()
+        owner = owner.to(torch.int32).contiguous()
+        pos = torch.empty(n, dtype=torch.int32, device=payload.device)
+        disp.barrier()                                           # previous round's buffers are free again
+        native.check(lib.lmb_a2a_dispatch(payload.data_ptr(), owner.data_ptr(), n, W, disp.inbox_table, disp.incoming_table,
+                                          disp.rank, disp.world, disp.cap, disp.counts.data_ptr(), pos.data_ptr(),
+                                          disp.overflow.data_ptr(), st), "a2a_dispatch")
+        disp.barrier()                                           # records and counts have landed everywhere
+        incoming = disp.incoming.clone()
+        m = int(incoming.sum().item())                           # one small D2H read per round
+        rows = torch.empty(max(m, 1), W, device=payload.device)
+        route_src = torch.empty(max(m, 1), dtype=torch.int32, device=payload.device)
+        route_slot = torch.empty(max(m, 1), dtype=torch.int32, device=payload.device)
+        inbox = disp.buf.local_ptr + disp.off_inbox
+        native.check(lib.lmb_a2a_collect(inbox, incoming.data_ptr(), disp.world, disp.cap, W, rows.data_ptr(),
+                                         route_src.data_ptr(), route_slot.data_ptr(), st), "a2a_collect")
+        rows = rows[:m]
+        with torch.enable_grad():
+            rows_in = rows.detach()
+            values = fn(rows_in).float().reshape(m, out_width)
+        out = disp.buf.view(disp.off_out, (n, out_width), torch.float32)
+        out.zero_()
+        disp.barrier()                                           # everybody zeroed its output buffer
+        native.check(lib.lmb_a2a_combine(values.detach().contiguous().data_ptr(), route_src.data_ptr(), route_slot.data_ptr(),
+                                         m, out_width, disp.out_table, disp.world, st), "a2a_combine")
+        disp.barrier()                                           # all results are in place
+        ctx.disp, ctx.values, ctx.m, ctx.V, ctx.n = disp, values, m, out_width, n
+        ctx.save_for_backward(owner, pos, incoming)
+        ctx.n_params = len(params)
+        return out.clone()
+
+    @staticmethod
+    def backward(ctx, dout):
+        owner, pos, incoming = ctx.saved_tensors
+        disp, lib, st = ctx.disp, native.lib(), native.stream_ptr()
+        V, m, n = ctx.V, ctx.m, ctx.n
+        dout = dout.contiguous().float()
+        disp.barrier()
+        native.check(lib.lmb_a2a_grad_dispatch(dout.data_ptr(), owner.data_ptr(), pos.data_ptr(), n, V, disp.ginbox_table,
+                                               disp.rank, disp.world, disp.cap, st), "a2a_grad_dispatch")
+        disp.barrier()
+        dvals = torch.empty(max(m, 1), V, device=dout.device)
+        native.check(lib.lmb_a2a_grad_collect(disp.buf.local_ptr + disp.off_ginbox, incoming.data_ptr(), disp.world,
+                                              disp.cap, V, dvals.data_ptr(), st), "a2a_grad_collect")
+        if m > 0 and ctx.values.requires_grad:
+            ctx.values.backward(dvals[:m].view_as(ctx.values))    # owner-side backward: grads land in local params
+        return (None, None, None, None, None) + (None,) * ctx.n_params

@@ -36,3 +36,11 @@ def test_channel_gather_fused_into_mlp():
     sys.stdout.write(res.stdout[-2000:])
     assert res.returncode == 0, res.stderr[-3000:]
     assert "CHANNEL_GATHER_RESULTS" in res.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_branch_parallel_all_to_all():
+    res = _launch("worker_branch_a2a.py", 2)
+    sys.stdout.write(res.stdout[-2000:])
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "BRANCH_A2A_RESULTS" in res.stdout
