@@ -115,6 +115,7 @@ def run_ours(args):
     cfg.ub = [BLOCK_M[0] * nx, BLOCK_M[1] * ny, BLOCK_M[2]]
     cfg.init_grid_size = [PLANE * nx, PLANE * ny, LINE]
     cfg.branch_parallel = n > 1
+    cfg.branch_dispatch = "a2a"      # every rank brings its own rays; samples travel to the block's owner
     cfg.batch_size = RAYS_PER_GPU * n
     trainer = GridNeRFTrainer(cfg)
     trainer.model.train()
@@ -122,9 +123,9 @@ def run_ours(args):
     steps, warmup = args.steps, args.warmup
     global_batch = RAYS_PER_GPU * n
     pool_steps = min(steps + warmup, 16)
-    # every rank sees the same global batch (seeded pool); model-parallel ranks evaluate their own block
-    rays, rgbs, idxs = make_ray_pool(global_batch * pool_steps, cfg.lb, cfg.ub, seed=1234)
-    host = torch.cat((rays, rgbs, idxs[:, None]), -1).view(pool_steps, global_batch, 10).pin_memory()
+    # every rank draws its own RAYS_PER_GPU rays per step from the whole scene (global batch = n x that)
+    rays, rgbs, idxs = make_ray_pool(RAYS_PER_GPU * pool_steps, cfg.lb, cfg.ub, seed=1234 + rank)
+    host = torch.cat((rays, rgbs, idxs[:, None]), -1).view(pool_steps, RAYS_PER_GPU, 10).pin_memory()
     resident = host.to(dev)
 
     def step_resident(k):
@@ -178,7 +179,8 @@ def run_ours(args):
                        "l2_policy": "inputs larger than L2: 6.4 GB of plane parameters touched per step"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "rays/s", "ms_per_step": ms_e2e / steps,
-                    "h2d_bytes_per_step": global_batch * 10 * 4, "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": RAYS_PER_GPU * 10 * 4, "d2h_bytes_per_step": 4,
+                    "note": "bytes are per rank"},
             "gpu_launches": launches,
         }), flush=True)
     if world > 1:

@@ -180,6 +180,8 @@ class GridNeRFTrainer(NeRFTrainer):
             rays_chunk = torch.cat((rays_train, idxs_train[:, None]), dim=-1)
             all_ret = self.model(rays_chunk, N_samples=self.nsamples)
             total, loss = self.compute_loss(all_ret, rgb_train)
+            if cfg.branch_parallel and cfg.get("branch_dispatch") == "a2a":
+                total = total / cfg.model_parallel_degree   # ranks hold different rays: objective is their mean
         with self.timer.stage("backward"):
             total.backward()
         with self.timer.stage("grad_sync"):
