@@ -47,6 +47,10 @@ class TrainConfig(ConfigClass):
 
     print_timestamp: bool = True
 
+    # additions of this framework
+    dp_optimizer: Literal["p2p_zero", "nccl_allreduce"] = "p2p_zero"   # data-parallel gradient path on GPUs
+    profile: bool = False                                              # CUDA-event stage timers + NVTX ranges
+
     def check_args(self) -> None:
         super().check_args()
         if self.plane_division is not None:

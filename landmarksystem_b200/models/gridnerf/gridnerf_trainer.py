@@ -101,12 +101,25 @@ class GridNeRFTrainer(NeRFTrainer):
             mods.append(m.nerf)
         return [p for mod in mods for p in mod.parameters()]
 
+    def _make_optimizer(self, groups):
+        """Adam over ``groups``.  CUDA + data parallel: gradient reduce-scatter, partitioned Adam and parameter
+        all-gather fused in one peer-memory kernel per learning-rate group; CUDA single replica: fused
+        Adam; CPU: ``torch.optim.Adam``."""
+        cfg = self.config
+        on_cuda = torch.device(cfg.device).type == "cuda"
+        if on_cuda and cfg.DDP and cfg.get("dp_optimizer", "p2p_zero") == "p2p_zero" and dist.is_initialized():
+            from ...parallel.zero_adam import GroupedP2PZeroAdam
+
+            self.dp_sync = None        # the fused kernel does the reduction
+            return GroupedP2PZeroAdam(groups, betas=(0.9, 0.99), group=cfg.dp_group if cfg.model_parallel else None,
+                                      shadow=cfg.get("grid_dtype") == "bf16")
+        use_fused = bool(cfg.get("fused_optimizer", True)) and on_cuda
+        return (FusedAdam if use_fused else torch.optim.Adam)(groups, betas=(0.9, 0.99))
+
     def create_optimizer(self):
         cfg = self.config
         groups = self.module.get_optparam_groups(cfg.lr_init, cfg.lr_basis)
-        use_fused = bool(cfg.get("fused_optimizer", True)) and torch.device(cfg.device).type == "cuda"
-        cls = FusedAdam if use_fused else torch.optim.Adam
-        self.optimizer = cls(groups, betas=(0.9, 0.99))
+        self.optimizer = self._make_optimizer(groups)
         optim_file = self._optim_path()
         if cfg.get("ckpt") and os.path.exists(optim_file):
             self.optimizer.load_state_dict(torch.load(optim_file, map_location=cfg.device, weights_only=False)["optimizer"])
@@ -145,7 +158,7 @@ class GridNeRFTrainer(NeRFTrainer):
         self.module.upsample_volume_grid(reso)
         lr_scale = 1.0 if cfg.lr_upsample_reset else cfg.lr_decay_target_ratio ** (self.iteration / cfg.n_iters)
         groups = self.module.get_optparam_groups(cfg.lr_init * lr_scale, cfg.lr_basis * lr_scale)
-        self.optimizer = type(self.optimizer)(groups, betas=(0.9, 0.99))  # parameters were replaced: new state
+        self.optimizer = self._make_optimizer(groups)  # parameters were replaced: new state
 
     # -- one optimisation step -------------------------------------------------------------------
     def compute_loss(self, all_ret, rgb_train):
@@ -207,8 +220,8 @@ class GridNeRFTrainer(NeRFTrainer):
                 self.enable_distort = True
             if cfg.add_nerf > 0 and it == cfg.add_nerf:
                 self.module.run_nerf = True
-                self.optimizer = type(self.optimizer)(self.module.get_optparam_groups(
-                    self.optimizer.param_groups[0]["lr"], self.optimizer.param_groups[2]["lr"]), betas=(0.9, 0.99))
+                self.optimizer = self._make_optimizer(self.module.get_optparam_groups(
+                    self.optimizer.param_groups[0]["lr"], self.optimizer.param_groups[2]["lr"]))
             loss = self.train_step(rays_train, rgb_train, idxs_train)
             if it % cfg.progress_refresh_rate == 0:
                 mse = float(loss)

@@ -168,3 +168,31 @@ class NcclZeroAdam:
     def zero_grad(self, set_to_none=True):
         for p in self.params:
             p.grad = None
+
+
+class GroupedP2PZeroAdam:
+    """One :class:`P2PZeroAdam` per distinct learning rate, behind the ``param_groups`` / ``step`` /
+    ``zero_grad`` / ``state_dict`` surface the trainers use."""
+
+    def __init__(self, groups, betas=(0.9, 0.999), eps=1e-8, group=None, shadow=False):
+        by_lr = {}
+        for g in groups:
+            by_lr.setdefault(float(g["lr"]), []).extend(list(g["params"]))
+        self.opts = [P2PZeroAdam(params, lr=lr, betas=betas, eps=eps, group=group, shadow=shadow)
+                     for lr, params in by_lr.items()]
+        self.param_groups = [o.param_groups[0] for o in self.opts]
+
+    def step(self):
+        for o in self.opts:
+            o.step()
+
+    def zero_grad(self, set_to_none=True):
+        for o in self.opts:
+            o.zero_grad(set_to_none)
+
+    def state_dict(self):
+        return {"groups": [{"m": o.m, "v": o.v, "step": o.step_count, "lr": o.param_groups[0]["lr"]} for o in self.opts]}
+
+    def load_state_dict(self, state):
+        for o, s in zip(self.opts, state["groups"]):
+            o.m.copy_(s["m"]); o.v.copy_(s["v"]); o.step_count = s["step"]; o.param_groups[0]["lr"] = s["lr"]
