@@ -1,0 +1,22 @@
+"""ScaffoldGSEvaluator: evaluation entry point of this model family (reference: benchmarks/nerf/scaffold_gs/gs_evaluator.py).  Launch:
+``torchrun ... -m landmarksystem_b200.models.scaffold_gs.gs_evaluator --config <render conf.py> [--key value]``."""
+import sys
+
+from ...configs import BaseConfig, get_default_parser, parse_console_args
+from ...train.nerf_evaluator import GaussianEvaluator
+from ..scaffold_gs.gs_model import ScaffoldGS
+
+
+class ScaffoldGSEvaluator(GaussianEvaluator):
+    model_cls = ScaffoldGS
+
+
+def main(argv=None):
+    args, unknown = get_default_parser().parse_known_args(argv)
+    config = BaseConfig.from_file(args.config, parse_console_args(unknown))
+    config.is_train = False
+    return ScaffoldGSEvaluator(config).eval()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

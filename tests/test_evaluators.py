@@ -1,0 +1,35 @@
+"""Train briefly, then evaluate from the checkpoint through the evaluator entry points."""
+import os
+
+import numpy as np
+import pytest
+
+from landmarksystem_b200.configs import BaseConfig
+
+ROOT = os.path.join(os.path.dirname(__file__), "..", "landmarksystem_b200", "models")
+CASES = [("gridnerf", "gridnerf_trainer", "GridNeRFTrainer", "gridnerf_evaluator", "GridNeRFEvaluator", "synthetic_tiny.py", {"nSamples": "24"}),
+         ("instant_ngp", "instant_ngp_trainer", "NGPTrainer", "instant_ngp_evaluator", "NGPEvaluator", "synthetic_tiny.py", {}),
+         ("origin_gs", "gs_trainer", "Gaussian3DTrainer", "gs_evaluator", "Gaussian3DEvaluator", "synthetic_train.py", {"init_points_num": "60"}),
+         ("octree_gs", "gs_trainer", "OctreeGSTrainer", "gs_evaluator", "OctreeGSEvaluator", "synthetic_train.py", {"init_points_num": "60"})]
+
+
+@pytest.mark.parametrize("family,tmod,tcls,emod,ecls,conf,extra", CASES)
+def test_train_then_evaluate_cpu(family, tmod, tcls, emod, ecls, conf, extra, tmp_path):
+    import importlib
+
+    over = {"basedir": str(tmp_path), "device": "cpu", "n_iters": "3", "datadir": "ring:3:12x12:14:3", "batch_size": "64",
+            "progress_refresh_rate": "100", "N_vis": "-1"}
+    over.update(extra)
+    gaussian = family.endswith("_gs")
+    if gaussian:
+        over["batch_size"] = "1"
+    path = os.path.join(ROOT, family, "confs", conf)
+    trainer = getattr(importlib.import_module(f"landmarksystem_b200.models.{family}.{tmod}"), tcls)(BaseConfig.from_file(path, over))
+    trainer.train()
+    cfg = BaseConfig.from_file(path, over)
+    cfg.is_train = False
+    cfg.ckpt = (os.path.join(trainer.logfolder, "point_cloud", "iteration_3", "point_cloud.ply") if gaussian
+                else os.path.join(trainer.logfolder, "state_dict.th"))
+    ev = getattr(importlib.import_module(f"landmarksystem_b200.models.{family}.{emod}"), ecls)(cfg)
+    assert np.isfinite(ev.eval())
+    assert any(f.endswith(".png") for f in os.listdir(ev.save_folder))
