@@ -91,6 +91,7 @@ class TensorVMEncoding(VolumeEncoding):
     # -- reference checkpoint layout --------------------------------------------------
     @staticmethod
     def _to_reference_layout(module, state, prefix, _local):
+        module.flush_lazy()
         for key in list(state.keys()):
             tail = key[len(prefix):]
             if tail.startswith("plane_coef."):
@@ -134,17 +135,31 @@ class TensorVMEncoding(VolumeEncoding):
         return shapes
 
     # -- bf16 shadows -----------------------------------------------------------------
-    def enable_shadow(self, fused_optimizer: bool = True) -> None:
+    def enable_shadow(self, fused_optimizer: bool = True, lazy: bool = False) -> None:
         """Keep bf16 copies of the grids for the lookup kernels (fp32 masters keep the gradients).
-        With ``fused_optimizer`` the masters also get persistent gradient accumulators."""
+        With ``fused_optimizer`` the masters also get persistent gradient accumulators; ``lazy`` turns on
+        the deferred Adam update for the planes (lines are small and stay dense)."""
         from ....ops import FusedAdam
 
         self.use_shadow = True
-        for p in list(self.plane_coef) + list(self.line_coef):
+        self.lazy = bool(lazy and fused_optimizer)
+        for p in self.plane_coef:
+            if fused_optimizer:
+                FusedAdam.attach_sink(p, shadow=True, lazy=self.lazy)
+            else:
+                p._lmb_shadow = p.detach().to(torch.bfloat16)
+        for p in self.line_coef:
             if fused_optimizer:
                 FusedAdam.attach_sink(p, shadow=True)
             else:
                 p._lmb_shadow = p.detach().to(torch.bfloat16)
+
+    def flush_lazy(self) -> None:
+        """Make every plane texel current (deferred Adam); no-op otherwise."""
+        for p in self.plane_coef:
+            state = getattr(p, "_lmb_lazy", None)
+            if state is not None:
+                state.flush(p)
 
     def refresh_shadow(self) -> None:
         for p in list(self.plane_coef) + list(self.line_coef):
@@ -159,6 +174,13 @@ class TensorVMEncoding(VolumeEncoding):
                 out_width: int = 0) -> torch.Tensor:
         planes = [self.plane_coef[k] for k in ks]
         lines = [self.line_coef[k] for k in ks]
+        if getattr(self, "lazy", False) and coords.is_cuda:
+            coords = coords.contiguous().float()
+            if self.training and torch.is_grad_enabled():
+                for p in planes:
+                    p._lmb_lazy.prepare(p, coords, count)
+            else:
+                self.flush_lazy()
         if self.use_shadow and coords.is_cuda:
             return vm_encode(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines],
                              count=count, out_dtype=out_dtype, out_width=out_width)
@@ -183,6 +205,7 @@ class TensorVMEncoding(VolumeEncoding):
         are replaced, so optimiser state must be rebuilt by the caller (as in the reference)."""
         grid = [int(v) for v in grid_size]
         n_levels = len(self.reso_mode)
+        self.flush_lazy()
         for i, (vec_id, (m0, m1)) in enumerate(zip(self.vector_mode, self.matrix_mode)):
             for idx, j in enumerate(self.reso_mode):
                 k = i * n_levels + idx
@@ -193,7 +216,7 @@ class TensorVMEncoding(VolumeEncoding):
                 self.plane_coef[k] = torch.nn.Parameter(p.permute(0, 2, 3, 1).contiguous())
                 self.line_coef[k] = torch.nn.Parameter(l.permute(0, 2, 1).contiguous())
         if self.use_shadow:
-            self.enable_shadow()
+            self.enable_shadow(lazy=getattr(self, "lazy", False))
 
     # -- regularisers ---------------------------------------------------------------------
     def L1_loss(self) -> torch.Tensor:

@@ -43,6 +43,8 @@ model_config = GridNeRFConfig(
     lr_basis=1e-3,
     distance_scale=25,
     grid_dtype="bf16",
+    fused_mlp_train=True,    # colour head forward AND backward run as tcgen05 kernels
+    lazy_adam=True,          # exact deferred Adam: only texels the step touched are visited
     runtime="Kernel",
     appearance_embedding_size=8,
 )

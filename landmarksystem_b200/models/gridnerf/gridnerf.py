@@ -114,6 +114,7 @@ class GridNeRFConfig(ConfigClass):
     branch_dispatch: Literal["allreduce", "a2a"] = "allreduce"   # a2a: every rank brings its own rays; samples
                                                   # travel to the GPU owning their block over NVLink peer memory
     fused_optimizer: bool = True
+    lazy_adam: bool = False                       # deferred (exact) Adam on the planes: visit touched texels only
 
     def check_args(self) -> None:
         super().check_args()
@@ -242,8 +243,14 @@ class GridNeRF(BaseNeRF):
             self.enable_shadow()
 
     def enable_shadow(self):
-        self.density_encoding.enable_shadow(self.config.fused_optimizer)
-        self.rgb_encoding.enable_shadow(self.config.fused_optimizer)
+        cfg = self.config
+        # the deferred update is exact only when every gradient comes from sample lookups, i.e. no dense
+        # regulariser (L1 / TV over whole planes) is active
+        dense_reg = any(float(cfg.get(k, 0.0) or 0.0) > 0 for k in
+                        ("L1_weight_inital", "L1_weight_rest", "TV_weight_density", "TV_weight_app", "Ortho_weight"))
+        lazy = bool(cfg.get("lazy_adam", False)) and not dense_reg
+        self.density_encoding.enable_shadow(self.config.fused_optimizer, lazy)
+        self.rgb_encoding.enable_shadow(self.config.fused_optimizer, lazy)
 
     def use_shadow(self) -> bool:
         return bool(self.density_encoding.use_shadow)

@@ -119,6 +119,8 @@ class GridNeRFTrainer(NeRFTrainer):
     def create_optimizer(self):
         cfg = self.config
         groups = self.module.get_optparam_groups(cfg.lr_init, cfg.lr_basis)
+        for g in groups:
+            g["lr_decay"] = cfg.lr_decay_target_ratio ** (1.0 / (cfg.lr_decay_iters if cfg.lr_decay_iters > 0 else cfg.n_iters))
         self.optimizer = self._make_optimizer(groups)
         optim_file = self._optim_path()
         if cfg.get("ckpt") and os.path.exists(optim_file):
@@ -207,6 +209,7 @@ class GridNeRFTrainer(NeRFTrainer):
             self.optimizer.zero_grad(set_to_none=True)
             for group in self.optimizer.param_groups:
                 group["lr"] *= self.lr_factor
+                group["lr_decay"] = self.lr_factor      # lets the deferred Adam reconstruct skipped steps
         return loss.detach()
 
     def train(self):

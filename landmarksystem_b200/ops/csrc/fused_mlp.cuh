@@ -1,0 +1,80 @@
+// Definitions shared by the tcgen05 fused-MLP kernels (forward: fused_mlp.cu, training backward:
+// fused_mlp_bwd.cu): network description, multi-source input descriptor, shared-memory tile helpers.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace lmb {
+
+constexpr int kTileRows = 128;
+constexpr int kMaxLayers = 5;
+constexpr int kMaxK = 160;            // widest activation row kept in shared memory
+constexpr int kSlotCols = 160;        // TMEM columns per slot (>= widest layer output)
+constexpr int kActBytes = kTileRows * kMaxK * 2;
+
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_TANH = 3, ACT_EXP = 4 };
+
+struct MLPSpec {
+  int n_layers;
+  int K[kMaxLayers];        // padded input width of each layer (multiple of 16, <= kMaxK)
+  int N[kMaxLayers];        // padded output width (multiple of 16, <= kSlotCols)
+  int act[kMaxLayers];
+  int w_off[kMaxLayers];    // byte offset of the packed [K/8][N][8] bf16 weights inside the blob
+  int b_off[kMaxLayers];    // byte offset of N fp32 biases inside the blob (-1: no bias)
+  int blob_bytes;           // multiple of 16
+  int in_width;             // row width of the input tensor (multiple of 8)
+  int out_dim;              // number of valid output columns of the last layer
+  int pe_stage;             // 1: GridNeRF colour expansion between layer 0 and layer 1
+  int dir_col;              // column of the input row that holds the view direction (pe_stage)
+};
+
+// Input rows may be assembled from several tensors ("sources"), each contributing a contiguous range of
+// 16-byte column chunks of the A tile.  A source can live in a peer GPU's memory: the tile is then
+// pulled over NVLink by the (non-multicast) TMA load itself, which fuses an all-gather of column
+// slices into the first GEMM of the network.
+constexpr int kMaxSources = 4;
+struct alignas(64) MLPInputs {
+  CUtensorMap map[kMaxSources];
+  int chunk_begin[kMaxSources + 1];
+  int n_src;
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+    case ACT_TANH: return tanhf(x);
+    case ACT_EXP: return __expf(x);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ void store_chunk(unsigned char* buf, int chunk, int row, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(buf + ((size_t)chunk * kTileRows + row) * 16) = u;
+}
+
+__device__ __forceinline__ float load_elem(const unsigned char* buf, int col, int row) {
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(buf + ((size_t)(col >> 3) * kTileRows + row) * 16);
+  return __bfloat162float(p[col & 7]);
+}
+
+
+// 3-D tensor map over a row-major bf16 [rows, width] matrix: (8 elements, width/8 chunks, rows), box
+// = one 16-byte chunk of 128 rows, so a tile lands in shared memory in the chunked operand layout.
+inline int encode_input_map(CUtensorMap* map, const void* x, int width, long long rows) {
+  const cuuint64_t gdim[3] = {8, (cuuint64_t)(width / 8), (cuuint64_t)rows};
+  const cuuint64_t gstride[2] = {16, (cuuint64_t)width * 2};
+  const cuuint32_t box[3] = {8, 1, (cuuint32_t)kTileRows};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride, box,
+                                      estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 10000 + (int)r;
+}
+
+}  // namespace lmb

@@ -6,8 +6,9 @@ kernel pulls in with a single TMA bulk copy.  Supported: up to 5 layers, every p
 <= 160, activations none/relu/sigmoid/tanh/exp.  ``rgb_decoder_*`` drives the GridNeRF colour head
 (basis projection + sin/cos expansion + 3-layer decoder) as one kernel.
 
-Backward currently recomputes the network with PyTorch ops under bf16 autocast (cuBLAS); the forward
-of training and all of rendering run the fused kernel.
+Training backward of the GridNeRF colour head is its own tcgen05 kernel (``csrc/fused_mlp_bwd.cu``:
+recompute, data gradients and weight gradients in one launch); other networks recompute with PyTorch
+ops under bf16 autocast.
 """
 from __future__ import annotations
 
@@ -30,6 +31,9 @@ class MLPSpec(Structure):
 
 native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P,
                                                  c_int, native.P, native.P])
+native.register_signature("lmb_rgb_mlp_bwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
+                                               native.P, native.P, native.P, native.P])
+native.register_signature("lmb_rgb_mlp_bwd_gbuf_floats", [])
 
 
 def _pad16(v: int) -> int:
@@ -217,9 +221,41 @@ def _rgb_packed(decoder) -> PackedMLP:
         layers = [(decoder.basis_mat.weight, None, "none"), (lin[0].weight, lin[0].bias, "relu"),
                   (lin[1].weight, lin[1].bias, "relu"), (lin[2].weight, lin[2].bias, "sigmoid")]
         packed = PackedMLP(layers, in_width=RGB_IN_WIDTH, out_dim=3, pe_stage=True, dir_col=144,
-                           k_override=[144, 160, _pad16(lin[1].weight.shape[1]), _pad16(lin[2].weight.shape[1])])
+                           k_override=[_pad16(decoder.basis_mat.weight.shape[1]), 160, _pad16(lin[1].weight.shape[1]),
+                                       _pad16(lin[2].weight.shape[1])])
         decoder._lmb_packed = packed
     return packed
+
+
+def rgb_backward_supported(decoder) -> bool:
+    """The backward kernel is specialised to 27 basis outputs and two 128-wide hidden layers."""
+    lin = decoder.decoder.linears()
+    return (rgb_decoder_supported(decoder) and lin[0].weight.shape[0] == 128 and lin[1].weight.shape == (128, 128)
+            and lin[2].weight.shape == (3, 128) and all(l.bias is not None for l in lin))
+
+
+def rgb_decoder_backward(decoder, x: torch.Tensor, dout: torch.Tensor, count: Optional[torch.Tensor] = None):
+    """One launch: ``dL/dx`` (bf16 ``[N, 160]``, feature columns filled) and the gradients of
+    ``(basis.weight, lin0.weight, lin0.bias, lin1.weight, lin1.bias, lin2.weight, lin2.bias)``."""
+    packed = _rgb_packed(decoder)
+    packed.refresh()
+    lib = native.lib()
+    n_floats = int(lib.lmb_rgb_mlp_bwd_gbuf_floats())
+    gbuf = torch.zeros(n_floats, device=x.device, dtype=torch.float32)
+    dx = torch.empty_like(x) if count is None else torch.zeros_like(x)
+    dout = dout.contiguous().float()
+    native.check(lib.lmb_rgb_mlp_bwd(x.data_ptr(), native.ptr(count), x.shape[0], packed.blob.data_ptr(), byref(packed.spec),
+                                     dout.data_ptr(), dout.shape[1], dx.data_ptr(), gbuf.data_ptr(),
+                                     packed.status.data_ptr(), native.stream_ptr()), "rgb_mlp_bwd")
+    kf = decoder.basis_mat.weight.shape[1]
+    o = 0
+    g1 = gbuf[o:o + 128 * 160].view(128, 160); o += 128 * 160
+    g2 = gbuf[o:o + 128 * 144].view(128, 144); o += 128 * 144
+    g3t = gbuf[o:o + 128 * 16].view(128, 16); o += 128 * 16
+    g0t = gbuf[o:o + 144 * 32].view(144, 32); o += 144 * 32
+    db3 = gbuf[o:o + 16]
+    grads = (g0t[:kf, :27].t(), g1[:, :150], g1[:, 150], g2[:, :128], g2[:, 128], g3t[:, :3].t(), db3[:3])
+    return dx, grads
 
 
 class _RGBDecoderFn(torch.autograd.Function):
@@ -235,6 +271,14 @@ class _RGBDecoderFn(torch.autograd.Function):
     def backward(ctx, dout):
         (x,) = ctx.saved_tensors
         dec = ctx.decoder
+        if rgb_backward_supported(dec):
+            dx, grads = rgb_decoder_backward(dec, x, dout)
+            lin = dec.decoder.linears()
+            by_param = {id(dec.basis_mat.weight): grads[0], id(lin[0].weight): grads[1], id(lin[0].bias): grads[2],
+                        id(lin[1].weight): grads[3], id(lin[1].bias): grads[4], id(lin[2].weight): grads[5],
+                        id(lin[2].bias): grads[6]}
+            params = list(dec.basis_mat.parameters()) + list(dec.decoder.parameters())
+            return (dx, None, *[by_param.get(id(p)) for p in params])
         from ..components.fields.mlp_decoder import positional_encoding
 
         with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):

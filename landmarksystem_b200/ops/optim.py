@@ -33,11 +33,16 @@ class FusedAdam(torch.optim.Optimizer):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
 
     @staticmethod
-    def attach_sink(param: torch.Tensor, shadow: bool = False) -> None:
-        """Give ``param`` a persistent zeroed fp32 accumulator (and a bf16 shadow if asked)."""
+    def attach_sink(param: torch.Tensor, shadow: bool = False, lazy: bool = False) -> None:
+        """Give ``param`` a persistent zeroed fp32 accumulator (and a bf16 shadow if asked).  ``lazy``
+        (4-D channels-last planes on CUDA only) additionally enables the deferred update."""
         param._lmb_grad_sink = torch.zeros_like(param, dtype=torch.float32)
         if shadow:
             param._lmb_shadow = param.detach().to(torch.bfloat16)
+        if lazy and shadow and param.is_cuda and param.dim() == 4:
+            from .lazy_adam import LazyPlaneState
+
+            param._lmb_lazy = LazyPlaneState(param)
 
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
@@ -50,6 +55,14 @@ class FusedAdam(torch.optim.Optimizer):
                 sink = getattr(p, "_lmb_grad_sink", None)
                 grad = sink if sink is not None else p.grad
                 if grad is None:
+                    continue
+                lazy = getattr(p, "_lmb_lazy", None)
+                if lazy is not None and sink is not None:
+                    # deferred update: only the texels this step's samples touched are visited
+                    decay = float(group.get("lr_decay", 1.0))
+                    lazy.sched.update(lr_ref=group["lr"], t_ref=lazy.steps_done + 1, decay=decay, beta1=beta1, beta2=beta2,
+                                      eps=group["eps"])
+                    lazy.step(p, sink, grad_scale)
                     continue
                 state = self.state[p]
                 if not state:

@@ -89,3 +89,63 @@ def test_packed_weights_follow_fused_adam():
         ref = _ref_mlp(dec, x)
     assert not torch.allclose(before, after, atol=1e-3)
     assert torch.allclose(after, ref, atol=2e-2)
+
+
+@pytest.mark.parametrize("n_feat,n", [(144, 5000), (48, 333), (48, 40000)])
+def test_rgb_decoder_backward_kernel(n_feat, n):
+    """tcgen05 backward (recompute + dgrad + wgrad in one launch) vs fp32 autograd on bf16-rounded operands."""
+    torch.manual_seed(0)
+    dec = RGBDecoder([n_feat // 3], [1, 2, 4], 27, view_pe=2, fea_pe=2, featureC=128).to(DEV)
+    with torch.no_grad():
+        for l in dec.decoder.linears():
+            l.bias.uniform_(-0.2, 0.2)
+    assert dec.basis_mat.weight.shape[1] == n_feat and fused_mlp.rgb_backward_supported(dec)
+    feats = torch.randn(n, n_feat, device=DEV) * 0.3
+    dirs = torch.nn.functional.normalize(torch.randn(n, 3, device=DEV), dim=-1)
+    dout = torch.randn(n, 3, device=DEV)
+    x = torch.zeros(n, fused_mlp.RGB_IN_WIDTH, device=DEV, dtype=torch.bfloat16)
+    x[:, :n_feat] = feats.to(torch.bfloat16)
+    x[:, 144:147] = dirs.to(torch.bfloat16)
+    dx, grads = fused_mlp.rgb_decoder_backward(dec, x, dout)
+    dec._lmb_packed.check_status()
+
+    lin = dec.decoder.linears()
+    leaves = [_bf(dec.basis_mat.weight).requires_grad_()]
+    for l in lin:
+        leaves += [_bf(l.weight).requires_grad_(), l.bias.detach().clone().requires_grad_()]
+    xin = x[:, :n_feat].float().requires_grad_()
+    f = xin @ leaves[0].t()
+    d = x[:, 144:147].float()
+    h = torch.cat((f, d, positional_encoding(f, 2), positional_encoding(d, 2)), -1)
+    h = torch.relu(h @ leaves[1].t() + leaves[2])
+    h = torch.relu(h @ leaves[3].t() + leaves[4])
+    out = torch.sigmoid(h @ leaves[5].t() + leaves[6])
+    ref = torch.autograd.grad(out, [xin] + leaves, dout)
+
+    def rel(a, b):
+        return float((a.float() - b).norm() / (b.norm() + 1e-12))
+
+    # the kernel keeps activations and the dz chain in bf16 (fp32 accumulation); the reference is pure fp32
+    errs = {"dx": rel(dx[:, :n_feat], ref[0])}
+    for name, got, want in zip(("basis", "w1", "b1", "w2", "b2", "w3", "b3"), grads, ref[1:]):
+        assert got.shape == want.shape, name
+        errs[name] = rel(got, want)
+    assert float(dx[:, n_feat:].float().abs().max()) == 0.0
+    assert errs["dx"] < 6e-2 and all(v < 3e-2 for k, v in errs.items() if k != "dx"), errs
+
+
+def test_rgb_decoder_backward_respects_count():
+    torch.manual_seed(0)
+    dec = RGBDecoder([16], [1, 2, 4], 27, view_pe=2, fea_pe=2, featureC=128).to(DEV)
+    n, used = 1000, 300
+    x = torch.zeros(n, fused_mlp.RGB_IN_WIDTH, device=DEV, dtype=torch.bfloat16)
+    x[:, :48] = (torch.randn(n, 48, device=DEV) * 0.3).to(torch.bfloat16)
+    x[used:] = float("nan")                       # rows past the count must not leak into any gradient
+    dout = torch.randn(n, 3, device=DEV)
+    count = torch.tensor([used], device=DEV, dtype=torch.int32)
+    dx_c, g_c = fused_mlp.rgb_decoder_backward(dec, x, dout, count)
+    dx_r, g_r = fused_mlp.rgb_decoder_backward(dec, x[:used].contiguous(), dout[:used].contiguous())
+    dec._lmb_packed.check_status()
+    assert torch.equal(dx_c[:used], dx_r) and float(dx_c[used:].float().abs().max()) == 0.0
+    for a, b in zip(g_c, g_r):
+        assert torch.isfinite(a).all() and torch.allclose(a, b, atol=1e-3, rtol=1e-3)

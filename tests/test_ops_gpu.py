@@ -115,3 +115,45 @@ def test_hashgrid_fwd_bwd(log2):
     assert torch.allclose(out.cpu(), ref.detach(), atol=1e-5)
     out.backward(gout.to(DEV))
     assert torch.allclose(t_gpu.grad.cpu(), t_ref.grad, atol=1e-4, rtol=1e-4)
+
+
+def test_lazy_adam_matches_dense_adam():
+    """Deferred Adam on planes: fed the same gradients, the touched texels' shadows are current before every
+    step and after a flush every parameter equals the dense fused Adam result."""
+    torch.manual_seed(0)
+    B, H, W, C = 2, 40, 36, 16
+    plane0 = torch.randn(B, H, W, C, device=DEV) * 0.1
+    dense = torch.nn.Parameter(plane0.clone())
+    lazy = torch.nn.Parameter(plane0.clone())
+    FusedAdam.attach_sink(dense, shadow=True)
+    FusedAdam.attach_sink(lazy, shadow=True, lazy=True)
+    opts = [FusedAdam([{"params": [p], "lr": 0.02, "lr_decay": 0.97}], betas=(0.9, 0.99), eps=1e-8) for p in (dense, lazy)]
+    state = lazy._lmb_lazy
+    g = torch.Generator(device=DEV).manual_seed(1)
+    for it in range(14):
+        # every step looks at a small random region, so most texels are skipped most of the time
+        n = 300
+        coords = torch.rand(n, 4, device=DEV, generator=g) * 0.5 - 1.0 + 1.5 * torch.rand(1, 4, device=DEV, generator=g)
+        coords = coords.clamp(-1, 1)
+        coords[:, 3] = torch.randint(0, B, (n,), device=DEV, generator=g).float()
+        coords = coords.contiguous()
+        state.prepare(lazy, coords)
+        count = int(state.list_count.item())
+        touched = state.need.view(B, H, W) != 0
+        assert 0 < count == int(touched.sum()) < B * H * W
+        assert sorted(state.list[:count].tolist()) == touched.view(-1).nonzero().view(-1).tolist()
+        # shadows of the texels about to be read are what a dense optimiser would hold
+        assert torch.equal(lazy._lmb_shadow[touched], dense._lmb_shadow[touched]) or \
+            (lazy._lmb_shadow[touched].float() - dense._lmb_shadow[touched].float()).abs().max() < 2e-3
+        grad = torch.randn(B, H, W, C, device=DEV, generator=g) * touched[..., None]
+        dense._lmb_grad_sink.copy_(grad)
+        lazy._lmb_grad_sink.copy_(grad)
+        for opt in opts:
+            opt.step()
+            opt.param_groups[0]["lr"] *= 0.97
+        assert int(state.list_count.item()) == 0 and int(state.need.sum()) == 0
+    assert state.last_step.min() < 14      # something was actually deferred
+    state.flush(lazy)
+    assert torch.allclose(lazy, dense, atol=2e-6, rtol=1e-5)
+    assert (lazy._lmb_shadow.float() - dense._lmb_shadow.float()).abs().max() < 2e-3
+    assert float(lazy._lmb_grad_sink.abs().max()) == 0.0
