@@ -97,8 +97,13 @@ def test_rgb_decoder_backward_kernel(n_feat, n):
     torch.manual_seed(0)
     dec = RGBDecoder([n_feat // 3], [1, 2, 4], 27, view_pe=2, fea_pe=2, featureC=128).to(DEV)
     with torch.no_grad():
-        for l in dec.decoder.linears():
-            l.bias.uniform_(-0.2, 0.2)
+        # hidden units sit firmly on one side of the relu (|bias| >> spread of the weighted sum): a unit whose
+        # pre-activation is within rounding noise of zero would otherwise flip between the two implementations
+        # and change that row's gradient by ~10 %
+        for l in dec.decoder.linears()[:2]:
+            l.weight.mul_(0.3)
+            l.bias.copy_((torch.rand_like(l.bias) * 0.4 + 0.4) * torch.sign(torch.randn_like(l.bias)))
+        dec.decoder.linears()[2].bias.uniform_(-0.2, 0.2)
     assert dec.basis_mat.weight.shape[1] == n_feat and fused_mlp.rgb_backward_supported(dec)
     feats = torch.randn(n, n_feat, device=DEV) * 0.3
     dirs = torch.nn.functional.normalize(torch.randn(n, 3, device=DEV), dim=-1)
@@ -109,29 +114,39 @@ def test_rgb_decoder_backward_kernel(n_feat, n):
     dx, grads = fused_mlp.rgb_decoder_backward(dec, x, dout)
     dec._lmb_packed.check_status()
 
+    # plain fp32 PyTorch restatement with operands rounded to bf16 where the kernel keeps them in bf16
+    # (activations x1/h1/h2 and the dz chain); accumulation in fp32
     lin = dec.decoder.linears()
-    leaves = [_bf(dec.basis_mat.weight).requires_grad_()]
-    for l in lin:
-        leaves += [_bf(l.weight).requires_grad_(), l.bias.detach().clone().requires_grad_()]
-    xin = x[:, :n_feat].float().requires_grad_()
-    f = xin @ leaves[0].t()
-    d = x[:, 144:147].float()
-    h = torch.cat((f, d, positional_encoding(f, 2), positional_encoding(d, 2)), -1)
-    h = torch.relu(h @ leaves[1].t() + leaves[2])
-    h = torch.relu(h @ leaves[3].t() + leaves[4])
-    out = torch.sigmoid(h @ leaves[5].t() + leaves[6])
-    ref = torch.autograd.grad(out, [xin] + leaves, dout)
+    with torch.no_grad():
+        W0 = _bf(dec.basis_mat.weight)
+        W = [_bf(l.weight) for l in lin]
+        b = [l.bias for l in lin]
+        x0 = x[:, :n_feat].float()
+        d = x[:, 144:147].float()
+        f = _bf(x0 @ W0.t())
+        s1, c1 = torch.sin(f), torch.cos(f)
+        x1 = _bf(torch.cat((f, d, positional_encoding(f, 2), positional_encoding(d, 2)), -1))
+        h1 = _bf(torch.relu(x1 @ W[0].t() + b[0]))
+        h2 = _bf(torch.relu(h1 @ W[1].t() + b[1]))
+        o = torch.sigmoid(h2 @ W[2].t() + b[2])
+        dz3 = _bf(dout * o * (1 - o))
+        dz2 = _bf((dz3 @ W[2]) * (h2 > 0))
+        dz1 = _bf((dz2 @ W[1]) * (h1 > 0))
+        dx1 = dz1 @ W[0]
+        i = torch.arange(27, device=DEV)
+        df = _bf(dx1[:, :27] + dx1[:, 30 + 2 * i] * c1 + dx1[:, 31 + 2 * i] * 2 * (1 - 2 * s1 * s1)
+                 - dx1[:, 84 + 2 * i] * s1 - dx1[:, 85 + 2 * i] * 4 * s1 * c1)
+        ref = (df @ W0, df.t() @ x0, dz1.t() @ x1, dz1.sum(0), dz2.t() @ h1, dz2.sum(0), dz3.t() @ h2, dz3.sum(0))
 
-    def rel(a, b):
-        return float((a.float() - b).norm() / (b.norm() + 1e-12))
+    def rel(a, b_):
+        return float((a.float() - b_).norm() / (b_.norm() + 1e-12))
 
-    # the kernel keeps activations and the dz chain in bf16 (fp32 accumulation); the reference is pure fp32
     errs = {"dx": rel(dx[:, :n_feat], ref[0])}
     for name, got, want in zip(("basis", "w1", "b1", "w2", "b2", "w3", "b3"), grads, ref[1:]):
         assert got.shape == want.shape, name
         errs[name] = rel(got, want)
     assert float(dx[:, n_feat:].float().abs().max()) == 0.0
-    assert errs["dx"] < 6e-2 and all(v < 3e-2 for k, v in errs.items() if k != "dx"), errs
+    assert all(v < 1.5e-2 for v in errs.values()), errs
 
 
 def test_rgb_decoder_backward_respects_count():
