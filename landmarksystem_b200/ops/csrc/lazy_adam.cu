@@ -7,7 +7,7 @@
 //     m <- b1 m,  v <- b2 v,  p <- p - lr_k / (1 - b1^k) * m / (sqrt(v / (1 - b2^k)) + eps),
 // so an untouched texel can be left alone and caught up later by replaying the skipped steps in
 // registers.  Per step:
-//   mark     every texel the step's samples will read is claimed (need = 1) and appended to a list (vm_mark)
+//   mark     every texel the step's samples will read gets need = 1                         (vm_mark)
 //   prepare  needed texels that are behind get their bf16 shadow value brought to "after step t-1"
 //            (reads p, m, v; writes only the 2-byte shadow)
 //   step     after backward, needed texels replay their skipped steps, apply step t with the real
@@ -61,87 +61,82 @@ __device__ __forceinline__ uint2 to_bf16x4(const float4& p) {
   return u;
 }
 
-// The texels a step touches are kept as a compact list (filled by vm_mark, which claims a texel with an
-// atomic compare-and-swap on its flag), so prepare / step cost scales with the touched set and never scan
-// the plane.  need: 0 idle, 1 marked, 2 prepared.  One thread per (list entry, 4-channel group).
-__global__ void __launch_bounds__(256)
-lazy_prepare_kernel(const int* __restrict__ need, const int* __restrict__ last_step, const int* __restrict__ list,
-                    const int* __restrict__ list_count, const float4* __restrict__ p, const float4* __restrict__ m,
-                    const float4* __restrict__ v, uint2* __restrict__ shadow, int c4, LazySched s) {
-  const long long total = (long long)(*list_count) * c4;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int texel = list[i / c4];
-    if (need[texel] != 1) continue;
-    const int last = last_step[texel];
-    if (last >= s.t - 1) continue;
-    const long long e = (long long)texel * c4 + (i % c4);
-    float4 pp = p[e], mm = m[e], vv = v[e];
-    Replay r = replay_start(s, last + 1);
-    for (int k = last + 1; k < s.t; ++k) zero_grad_step(pp, mm, vv, s, r);
-    shadow[e] = to_bf16x4(pp);
-  }
-}
+// Kernels walk the plane's one-byte flags in texel order, one warp per 32 texels: the warp compacts the
+// flagged texels of its chunk with a ballot and spreads their (texel, 4-channel group) work items over its
+// lanes, so every texel's channels are read and written as one contiguous run and addresses only ever
+// increase (the flags themselves are 1/64th .. 1/192th of the parameter bytes).
+// need: 0 idle, 1 marked, 2 prepared.
+constexpr int kMaxReplay = 192;   // beta1^192 < 2e-9: later zero-gradient steps cannot change an fp32 parameter
 
-// after prepare: marked -> prepared (a separate launch, so every channel group has seen need == 1)
-__global__ void __launch_bounds__(256)
-lazy_mark_prepared_kernel(int* __restrict__ need, const int* __restrict__ list, const int* __restrict__ list_count) {
-  const int total = *list_count;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int texel = list[i];
-    if (need[texel] == 1) need[texel] = 2;
-  }
-}
-
-__device__ __forceinline__ void lazy_apply(long long e, int last, float4* p, float4* g, float4* m, float4* v, uint2* shadow,
-                                           const LazySched& s, float grad_scale, bool flush) {
-  const int upto = flush ? s.t : s.t - 1;        // zero-gradient steps to replay: last+1 .. upto
-  float4 pp = p[e], mm = m[e], vv = v[e];
+__device__ __forceinline__ void replay_steps(float4& pp, float4& mm, float4& vv, const LazySched& s, int last, int upto) {
+  if (last == 0 || upto <= last) return;          // never stepped: both moments are zero and stay zero
+  const int n = upto - last;
+  const int n_explicit = n < kMaxReplay ? n : kMaxReplay;
   Replay r = replay_start(s, last + 1);
-  for (int k = last + 1; k <= upto; ++k) zero_grad_step(pp, mm, vv, s, r);
-  if (!flush) {
-    float4 gg = g[e];
-    const float step = r.lr / (1.f - r.b1p);
-    const float inv_sqrt_b2 = rsqrtf(1.f - r.b2p);
-    float* G = &gg.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
+  for (int k = 0; k < n_explicit; ++k) zero_grad_step(pp, mm, vv, s, r);
+  if (n > n_explicit) {                           // the remaining steps only decay the moments
+    const float d1 = exp2f(s.l2_beta1 * (float)(n - n_explicit)), d2 = exp2f(s.l2_beta2 * (float)(n - n_explicit));
+    mm.x *= d1; mm.y *= d1; mm.z *= d1; mm.w *= d1;
+    vv.x *= d2; vv.y *= d2; vv.z *= d2; vv.w *= d2;
+  }
+}
+
+template <bool kPrepare>
+__global__ void __launch_bounds__(256)
+lazy_scan_kernel(unsigned char* __restrict__ need, int* __restrict__ last_step, float4* __restrict__ p, float4* __restrict__ g,
+                 float4* __restrict__ m, float4* __restrict__ v, uint2* __restrict__ shadow, int c4, long long n_texels,
+                 LazySched s, float grad_scale) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long chunk = warp0; chunk * 32 < n_texels; chunk += n_warps) {
+    const long long texel = chunk * 32 + lane;
+    const unsigned char flag = texel < n_texels ? need[texel] : 0;
+    const int last = flag ? last_step[texel] : 0;
+    const bool mine = kPrepare ? (flag == 1) : (flag != 0);
+    const bool work = kPrepare ? (mine && last > 0 && last < s.t - 1) : mine;
+    const unsigned mask = __ballot_sync(0xffffffffu, work);
+    const int total = __popc(mask) * c4;
+    for (int w0 = 0; w0 < total; w0 += 32) {                     // uniform trip count: every lane joins the shuffle
+      const int w = w0 + lane;
+      const bool on = w < total;
+      const int which = on ? w / c4 : 0, grp = w - which * c4;
+      const int src = __fns(mask, 0, which + 1);                 // lane that owns the which-th flagged texel
+      const int last_t = __shfl_sync(0xffffffffu, last, src);
+      if (!on) continue;
+      const long long e = (chunk * 32 + src) * c4 + grp;
+      float4 pp = p[e], mm = m[e], vv = v[e];
+      replay_steps(pp, mm, vv, s, last_t, s.t - 1);
+      if (kPrepare) {
+        shadow[e] = to_bf16x4(pp);
+      } else {
+        const float4 gg = g[e];
+        Replay r = replay_start(s, s.t);
+        const float step = r.lr / (1.f - r.b1p);
+        const float inv_sqrt_b2 = rsqrtf(1.f - r.b2p);
+        const float* G = &gg.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float gr = G[k] * grad_scale;
-      M[k] = s.beta1 * M[k] + (1.f - s.beta1) * gr;
-      V[k] = s.beta2 * V[k] + (1.f - s.beta2) * gr * gr;
-      P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + s.eps);
+        for (int k = 0; k < 4; ++k) {
+          const float gr = G[k] * grad_scale;
+          M[k] = s.beta1 * M[k] + (1.f - s.beta1) * gr;
+          V[k] = s.beta2 * V[k] + (1.f - s.beta2) * gr * gr;
+          P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + s.eps);
+        }
+        g[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+        p[e] = pp; m[e] = mm; v[e] = vv;
+        if (shadow) shadow[e] = to_bf16x4(pp);
+      }
     }
-    g[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  p[e] = pp; m[e] = mm; v[e] = vv;
-  if (shadow) shadow[e] = to_bf16x4(pp);
-}
-
-// step t over the touched list
-__global__ void __launch_bounds__(256)
-lazy_step_kernel(const int* __restrict__ last_step, const int* __restrict__ list, const int* __restrict__ list_count,
-                 float4* __restrict__ p, float4* __restrict__ g, float4* __restrict__ m, float4* __restrict__ v,
-                 uint2* __restrict__ shadow, int c4, LazySched s, float grad_scale) {
-  const long long total = (long long)(*list_count) * c4;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int texel = list[i / c4];
-    lazy_apply((long long)texel * c4 + (i % c4), last_step[texel], p, g, m, v, shadow, s, grad_scale, false);
+    __syncwarp();
+    if (mine) {
+      if (kPrepare) need[texel] = 2;
+      else { need[texel] = 0; last_step[texel] = s.t; }
+    }
   }
 }
 
-// second half of a step: bookkeeping per touched texel (separate so that all channel groups have read
-// last_step before it changes)
-__global__ void __launch_bounds__(256)
-lazy_commit_kernel(int* __restrict__ need, int* __restrict__ last_step, const int* __restrict__ list,
-                   const int* __restrict__ list_count, int t) {
-  const int total = *list_count;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int texel = list[i];
-    last_step[texel] = t;
-    need[texel] = 0;
-  }
-}
-
-// flush: every texel of the plane that is behind step s.t replays up to it (no gradient)
+// flush: every texel of the plane that is behind step s.t replays up to it (no gradient); one thread
+// per (texel, group), last_step is advanced by a second launch
 __global__ void __launch_bounds__(256)
 lazy_flush_kernel(const int* __restrict__ last_step, float4* __restrict__ p, float4* __restrict__ m, float4* __restrict__ v,
                   uint2* __restrict__ shadow, int c4, long long n_texels, LazySched s) {
@@ -149,47 +144,34 @@ lazy_flush_kernel(const int* __restrict__ last_step, float4* __restrict__ p, flo
   const long long texel = e / c4;
   if (texel >= n_texels) return;
   const int last = last_step[texel];
-  if (last >= s.t) return;
-  lazy_apply(e, last, p, nullptr, m, v, shadow, s, 1.f, true);
+  if (last >= s.t || last == 0) return;
+  float4 pp = p[e], mm = m[e], vv = v[e];
+  replay_steps(pp, mm, vv, s, last, s.t);
+  p[e] = pp; m[e] = mm; v[e] = vv;
+  if (shadow) shadow[e] = to_bf16x4(pp);
 }
 __global__ void __launch_bounds__(256) lazy_flush_commit_kernel(int* __restrict__ last_step, long long n_texels, int t) {
   const long long texel = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (texel < n_texels && last_step[texel] < t) last_step[texel] = t;
 }
 
-// Claim the 4 corner texels of every sample on one plane level (same tap rule as the lookup kernel) and
-// append newly claimed ones to the list; list positions are handed out per warp (one atomic per warp).
+// Flag the 4 corner texels of every sample on one plane level (same tap rule as the lookup kernel).
 __global__ void __launch_bounds__(256)
 vm_mark_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n, int B, int H, int W,
-               int* __restrict__ need, int* __restrict__ list, int* __restrict__ list_count, int list_cap) {
+               unsigned char* __restrict__ need) {
   const long long n_valid = resolve_count(count_ptr, max_n);
   const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int lane = threadIdx.x & 31;
-  bool active = n < n_valid;
-  float4 q = make_float4(0.f, 0.f, 0.f, -1.f);
-  if (active) q = __ldg(coords + n);
+  if (n >= n_valid) return;
+  const float4 q = __ldg(coords + n);
   const int b = (int)q.w;
-  active = active && b >= 0 && b < B;
+  if (b < 0 || b >= B) return;
   const float fx = (q.x + 1.f) * 0.5f * (float)(W - 1), fy = (q.y + 1.f) * 0.5f * (float)(H - 1);
   const int x0 = (int)floorf(fx), y0 = (int)floorf(fy);
 #pragma unroll
   for (int corner = 0; corner < 4; ++corner) {
-    int texel = -1;
-    if (active) {
-      const int x = min(max(x0 + (corner & 1), 0), W - 1), y = min(max(y0 + (corner >> 1), 0), H - 1);
-      const int t = (b * H + y) * W + x;
-      if (need[t] == 0 && atomicCAS(need + t, 0, 1) == 0) texel = t;
-    }
-    const unsigned won = __ballot_sync(0xffffffffu, texel >= 0);
-    if (won) {
-      int base = 0;
-      if (lane == __ffs(won) - 1) base = atomicAdd(list_count, __popc(won));
-      base = __shfl_sync(0xffffffffu, base, __ffs(won) - 1);
-      if (texel >= 0) {
-        const int pos = base + __popc(won & ((1u << lane) - 1u));
-        if (pos < list_cap) list[pos] = texel;
-      }
-    }
+    const int x = min(max(x0 + (corner & 1), 0), W - 1), y = min(max(y0 + (corner >> 1), 0), H - 1);
+    unsigned char* f = need + ((long long)b * H + y) * W + x;
+    if (*f == 0) *f = 1;
   }
 }
 
@@ -204,55 +186,46 @@ static LazySched make_sched(float lr_ref, int t_ref, float decay, float beta1, f
   return s;
 }
 
-static int list_grid(long long work) {
-  const long long blocks = (work + 255) / 256;
-  return (int)(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
+static int scan_grid(long long n_texels) {
+  const long long blocks = (n_texels + 255) / 256;     // one warp per 32 texels, 8 warps per block
+  return (int)(blocks < 148 * 32 ? (blocks > 0 ? blocks : 1) : 148 * 32);
 }
 
-// need: int32 [B*H*W]; list: int32 [list_cap] with *list_count entries in use (list_cap >= 4 * max_n per call
-// outstanding guarantees no overflow; entries past the capacity are dropped and reported by lmb_lazy_list_ok).
-LMB_API int lmb_vm_mark(const float* coords, const int* count_ptr, long long max_n, int B, int H, int W, int* need, int* list,
-                        int* list_count, int list_cap, cudaStream_t stream) {
+// need: uint8 [B*H*W]
+LMB_API int lmb_vm_mark(const float* coords, const int* count_ptr, long long max_n, int B, int H, int W, unsigned char* need,
+                        cudaStream_t stream) {
   if (max_n <= 0) return 0;
-  vm_mark_kernel<<<ceil_div(max_n, 256), 256, 0, stream>>>((const float4*)coords, count_ptr, max_n, B, H, W, need, list,
-                                                          list_count, list_cap);
+  vm_mark_kernel<<<ceil_div(max_n, 256), 256, 0, stream>>>((const float4*)coords, count_ptr, max_n, B, H, W, need);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
-// work_hint: upper bound of list entries (sizes the grid; the kernels read the true count on the device)
-LMB_API int lmb_lazy_adam_prepare(int* need, const int* last_step, const int* list, const int* list_count, long long work_hint,
-                                  const float* p, const float* m, const float* v, void* shadow, int C, float lr_ref, int t_ref,
-                                  float decay, float beta1, float beta2, float eps, int t, cudaStream_t stream) {
+LMB_API int lmb_lazy_adam_prepare(unsigned char* need, int* last_step, const float* p, const float* m, const float* v,
+                                  void* shadow, int C, long long n_texels, float lr_ref, int t_ref, float decay, float beta1,
+                                  float beta2, float eps, int t, cudaStream_t stream) {
   if (C % 4) return (int)cudaErrorInvalidValue;
-  const int c4 = C / 4;
-  lazy_prepare_kernel<<<list_grid(work_hint * c4), 256, 0, stream>>>(need, last_step, list, list_count, (const float4*)p,
-                                                                    (const float4*)m, (const float4*)v, (uint2*)shadow, c4,
-                                                                    make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t));
-  LMB_LAUNCH_CHECK();
-  lazy_mark_prepared_kernel<<<list_grid(work_hint), 256, 0, stream>>>(need, list, list_count);
+  if (n_texels <= 0) return 0;
+  lazy_scan_kernel<true><<<scan_grid(n_texels), 256, 0, stream>>>(need, last_step, (float4*)p, nullptr, (float4*)m, (float4*)v,
+                                                                 (uint2*)shadow, C / 4, n_texels,
+                                                                 make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t), 1.f);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
-// One optimiser step over the touched list; clears the list afterwards.
-LMB_API int lmb_lazy_adam_step(int* need, int* last_step, const int* list, int* list_count, long long work_hint, float* p,
-                               float* g, float* m, float* v, void* shadow, int C, float lr_ref, int t_ref, float decay,
-                               float beta1, float beta2, float eps, int t, float grad_scale, cudaStream_t stream) {
+LMB_API int lmb_lazy_adam_step(unsigned char* need, int* last_step, float* p, float* g, float* m, float* v, void* shadow,
+                               int C, long long n_texels, float lr_ref, int t_ref, float decay, float beta1, float beta2,
+                               float eps, int t, float grad_scale, cudaStream_t stream) {
   if (C % 4) return (int)cudaErrorInvalidValue;
-  const int c4 = C / 4;
-  lazy_step_kernel<<<list_grid(work_hint * c4), 256, 0, stream>>>(last_step, list, list_count, (float4*)p, (float4*)g,
-                                                                 (float4*)m, (float4*)v, (uint2*)shadow, c4,
-                                                                 make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t),
-                                                                 grad_scale);
+  if (n_texels <= 0) return 0;
+  lazy_scan_kernel<false><<<scan_grid(n_texels), 256, 0, stream>>>(need, last_step, (float4*)p, (float4*)g, (float4*)m,
+                                                                  (float4*)v, (uint2*)shadow, C / 4, n_texels,
+                                                                  make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t),
+                                                                  grad_scale);
   LMB_LAUNCH_CHECK();
-  lazy_commit_kernel<<<list_grid(work_hint), 256, 0, stream>>>(need, last_step, list, list_count, t);
-  LMB_LAUNCH_CHECK();
-  LMB_CUDA_TRY(cudaMemsetAsync(list_count, 0, sizeof(int), stream));
   return 0;
 }
 
-// Bring every texel up to step t (zero-gradient replay); call between steps (empty list).
+// Bring every texel up to step t (zero-gradient replay); call between steps (no flags set).
 LMB_API int lmb_lazy_adam_flush(int* last_step, float* p, float* m, float* v, void* shadow, int C, long long n_texels,
                                 float lr_ref, int t_ref, float decay, float beta1, float beta2, float eps, int t,
                                 cudaStream_t stream) {

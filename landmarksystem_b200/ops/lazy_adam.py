@@ -16,11 +16,11 @@ import torch
 from . import native
 
 P = native.P
-native.register_signature("lmb_vm_mark", [P, P, c_longlong, c_int, c_int, c_int, P, P, P, c_int, P])
-native.register_signature("lmb_lazy_adam_prepare", [P, P, P, P, c_longlong, P, P, P, P, c_int, c_float, c_int, c_float,
-                                                     c_float, c_float, c_float, c_int, P])
-native.register_signature("lmb_lazy_adam_step", [P, P, P, P, c_longlong, P, P, P, P, P, c_int, c_float, c_int, c_float,
-                                                  c_float, c_float, c_float, c_int, c_float, P])
+native.register_signature("lmb_vm_mark", [P, P, c_longlong, c_int, c_int, c_int, P, P])
+native.register_signature("lmb_lazy_adam_prepare", [P, P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
+                                                     c_float, c_float, c_int, P])
+native.register_signature("lmb_lazy_adam_step", [P, P, P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
+                                                  c_float, c_float, c_int, c_float, P])
 native.register_signature("lmb_lazy_adam_flush", [P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
                                                    c_float, c_float, c_int, P])
 
@@ -28,18 +28,16 @@ native.register_signature("lmb_lazy_adam_flush", [P, P, P, P, P, c_int, c_longlo
 class LazyPlaneState:
     def __init__(self, param: torch.Tensor):
         B, H, W, C = param.shape
-        assert C % 4 == 0 and B * H * W < 2 ** 31
+        assert C % 4 == 0
         self.shape = (B, H, W, C)
         dev = param.device
         n = B * H * W
-        self.need = torch.zeros(n, dtype=torch.int32, device=dev)         # 0 idle, 1 marked, 2 prepared
+        self.need = torch.zeros(n, dtype=torch.uint8, device=dev)         # 0 idle, 1 marked, 2 prepared
         self.last_step = torch.zeros(n, dtype=torch.int32, device=dev)    # last optimiser step applied to the texel
-        self.list = torch.empty(n, dtype=torch.int32, device=dev)         # texels touched since the last step
-        self.list_count = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.hint = 0                                                     # host-side upper bound of list_count
         self.m = torch.zeros_like(param, dtype=torch.float32)
         self.v = torch.zeros_like(param, dtype=torch.float32)
         self.steps_done = 0
+        self.marked = False
         # schedule published by the optimiser: lr of step `t_ref`, geometric decay, Adam constants
         self.sched = {"lr_ref": 0.0, "t_ref": 1, "decay": 1.0, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8}
         self.dirty = False
@@ -49,30 +47,27 @@ class LazyPlaneState:
         return (float(s["lr_ref"]), int(s["t_ref"]), float(s["decay"]), float(s["beta1"]), float(s["beta2"]), float(s["eps"]))
 
     def prepare(self, param, coords: torch.Tensor, count: Optional[torch.Tensor] = None) -> None:
-        """Claim the texels ``coords [N, 4]`` will read and bring their bf16 shadows up to date."""
+        """Flag the texels ``coords [N, 4]`` will read and bring their bf16 shadows up to date."""
         B, H, W, C = self.shape
         lib, st = native.lib(), native.stream_ptr()
-        n = B * H * W
-        native.check(lib.lmb_vm_mark(coords.data_ptr(), native.ptr(count), coords.shape[0], B, H, W, self.need.data_ptr(),
-                                     self.list.data_ptr(), self.list_count.data_ptr(), n, st), "vm_mark")
-        self.hint = min(n, self.hint + 4 * coords.shape[0])
+        native.check(lib.lmb_vm_mark(coords.data_ptr(), native.ptr(count), coords.shape[0], B, H, W, self.need.data_ptr(), st),
+                     "vm_mark")
+        self.marked = True
         if self.steps_done > 0:
-            native.check(lib.lmb_lazy_adam_prepare(self.need.data_ptr(), self.last_step.data_ptr(), self.list.data_ptr(),
-                                                   self.list_count.data_ptr(), self.hint, param.data_ptr(),
+            native.check(lib.lmb_lazy_adam_prepare(self.need.data_ptr(), self.last_step.data_ptr(), param.data_ptr(),
                                                    self.m.data_ptr(), self.v.data_ptr(), param._lmb_shadow.data_ptr(), C,
-                                                   *self._sched_args(), self.steps_done + 1, st), "lazy_prepare")
+                                                   B * H * W, *self._sched_args(), self.steps_done + 1, st), "lazy_prepare")
 
     def step(self, param, grad, grad_scale: float = 1.0) -> None:
-        C = self.shape[3]
+        B, H, W, C = self.shape
         t = self.steps_done + 1
-        if self.hint > 0:
-            native.check(native.lib().lmb_lazy_adam_step(self.need.data_ptr(), self.last_step.data_ptr(), self.list.data_ptr(),
-                                                         self.list_count.data_ptr(), self.hint, param.data_ptr(),
+        if self.marked:
+            native.check(native.lib().lmb_lazy_adam_step(self.need.data_ptr(), self.last_step.data_ptr(), param.data_ptr(),
                                                          grad.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
-                                                         native.ptr(getattr(param, "_lmb_shadow", None)), C,
+                                                         native.ptr(getattr(param, "_lmb_shadow", None)), C, B * H * W,
                                                          *self._sched_args(), t, float(grad_scale), native.stream_ptr()),
                          "lazy_step")
-        self.hint = 0
+        self.marked = False
         self.steps_done = t
         self.dirty = True
 

@@ -138,10 +138,8 @@ def test_lazy_adam_matches_dense_adam():
         coords[:, 3] = torch.randint(0, B, (n,), device=DEV, generator=g).float()
         coords = coords.contiguous()
         state.prepare(lazy, coords)
-        count = int(state.list_count.item())
         touched = state.need.view(B, H, W) != 0
-        assert 0 < count == int(touched.sum()) < B * H * W
-        assert sorted(state.list[:count].tolist()) == touched.view(-1).nonzero().view(-1).tolist()
+        assert 0 < int(touched.sum()) < B * H * W
         # shadows of the texels about to be read are what a dense optimiser would hold
         assert torch.equal(lazy._lmb_shadow[touched], dense._lmb_shadow[touched]) or \
             (lazy._lmb_shadow[touched].float() - dense._lmb_shadow[touched].float()).abs().max() < 2e-3
@@ -151,9 +149,37 @@ def test_lazy_adam_matches_dense_adam():
         for opt in opts:
             opt.step()
             opt.param_groups[0]["lr"] *= 0.97
-        assert int(state.list_count.item()) == 0 and int(state.need.sum()) == 0
+        assert int(state.need.sum()) == 0
     assert state.last_step.min() < 14      # something was actually deferred
     state.flush(lazy)
     assert torch.allclose(lazy, dense, atol=2e-6, rtol=1e-5)
     assert (lazy._lmb_shadow.float() - dense._lmb_shadow.float()).abs().max() < 2e-3
     assert float(lazy._lmb_grad_sink.abs().max()) == 0.0
+
+
+def test_lazy_adam_long_gap():
+    """A texel left alone for hundreds of steps: the replay is cut off once beta1^k is below fp32 resolution
+    and only decays the moments afterwards; the result still equals dense Adam."""
+    torch.manual_seed(0)
+    B, H, W, C = 1, 8, 8, 8
+    p0 = torch.randn(B, H, W, C, device=DEV) * 0.1
+    dense, lazy = torch.nn.Parameter(p0.clone()), torch.nn.Parameter(p0.clone())
+    FusedAdam.attach_sink(dense, shadow=True)
+    FusedAdam.attach_sink(lazy, shadow=True, lazy=True)
+    opts = [FusedAdam([{"params": [p], "lr": 0.01, "lr_decay": 0.999}], betas=(0.9, 0.99), eps=1e-15) for p in (dense, lazy)]
+    everywhere = torch.rand(4000, 4, device=DEV) * 2 - 1
+    everywhere[:, 3] = 0
+    corner = torch.tensor([[-1.0, -1.0, 0.0, 0.0]], device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for it in range(420):
+        coords = everywhere if it in (0, 1, 419) else corner
+        lazy._lmb_lazy.prepare(lazy, coords.contiguous())
+        touched = lazy._lmb_lazy.need.view(B, H, W) != 0
+        grad = torch.randn(B, H, W, C, device=DEV, generator=g) * touched[..., None]
+        if it == 419:
+            assert (lazy._lmb_shadow.float() - dense._lmb_shadow.float()).abs().max() < 2e-3
+        for p, opt in zip((dense, lazy), opts):
+            p._lmb_grad_sink.copy_(grad)
+            opt.step()
+            opt.param_groups[0]["lr"] *= 0.999
+    assert torch.allclose(lazy, dense, atol=5e-6, rtol=1e-5), (lazy - dense).abs().max()
