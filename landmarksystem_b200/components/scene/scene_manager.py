@@ -29,9 +29,10 @@ class SceneManager:
         self.aabb_norm_size = float(rng[1] - rng[0])
         part = getattr(config, "plane_division", None) or [1, 1]
         self.block_partition = torch.tensor(list(part), dtype=torch.long, device=self.device)
+        self._partition = (int(part[0]), int(part[1]))     # host copy: reading the tensor would synchronise
         self._refresh()
         local = getattr(config, "local_block_partition", None)
-        self.local_block_partition = list(local) if local is not None else [int(v) for v in self.block_partition]
+        self.local_block_partition = list(local) if local is not None else [int(v) for v in part]
         self.assign_relative_block_idx(getattr(config, "relative_block_idx", 0))
 
     def _refresh(self) -> None:
@@ -42,7 +43,7 @@ class SceneManager:
 
     @property
     def n_blocks(self) -> int:
-        return int(self.block_partition[0] * self.block_partition[1])
+        return self._partition[0] * self._partition[1]
 
     @property
     def n_local_blocks(self) -> int:
@@ -59,13 +60,14 @@ class SceneManager:
     # -- partition bookkeeping ---------------------------------------------------
     def assign_block_partition(self, block_partition: Sequence[int]) -> None:
         self.block_partition = torch.tensor(list(block_partition), dtype=torch.long, device=self.device)
+        self._partition = (int(block_partition[0]), int(block_partition[1]))
         self._refresh()
 
     def assign_local_block_partition(self, local_block_partition: Sequence[int]) -> None:
         self.local_block_partition = [int(v) for v in local_block_partition]
 
     def assign_relative_block_idx(self, relative_block_idx: int = 0) -> None:
-        ny = int(self.block_partition[1])
+        ny = self._partition[1]
         self.relative_block_idx = int(relative_block_idx)
         self.relative_block_idx_x = self.relative_block_idx // ny
         self.relative_block_idx_y = self.relative_block_idx % ny
@@ -91,7 +93,7 @@ class SceneManager:
         """Map globally-normalised xyz to ``(block-local xyz in [-1, 1], window-relative block id)``.
         Samples outside the resident window get id ``-1``."""
         lo = self.aabb_norm_range[0]
-        nx, ny = int(self.block_partition[0]), int(self.block_partition[1])
+        nx, ny = self._partition
         lx, ly = self.local_block_partition
         u = (xyz_norm[..., 0] - lo) / self.norm_block_width[0]
         v = (xyz_norm[..., 1] - lo) / self.norm_block_width[1]

@@ -68,14 +68,15 @@ __device__ __forceinline__ uint2 to_bf16x4(const float4& p) {
 // need: 0 idle, 1 marked, 2 prepared.
 constexpr int kMaxReplay = 192;   // beta1^192 < 2e-9: later zero-gradient steps cannot change an fp32 parameter
 
-__device__ __forceinline__ void replay_steps(float4& pp, float4& mm, float4& vv, const LazySched& s, int last, int upto) {
-  if (last == 0 || upto <= last) return;          // never stepped: both moments are zero and stay zero
-  const int n = upto - last;
-  const int n_explicit = n < kMaxReplay ? n : kMaxReplay;
-  Replay r = replay_start(s, last + 1);
-  for (int k = 0; k < n_explicit; ++k) zero_grad_step(pp, mm, vv, s, r);
-  if (n > n_explicit) {                           // the remaining steps only decay the moments
-    const float d1 = exp2f(s.l2_beta1 * (float)(n - n_explicit)), d2 = exp2f(s.l2_beta2 * (float)(n - n_explicit));
+// number of zero-gradient steps to run explicitly / to fold into a moment decay afterwards
+__device__ __forceinline__ void replay_plan(int last, int upto, int& n_explicit, int& n_rest) {
+  const int n = (last == 0 || upto <= last) ? 0 : upto - last;   // never stepped: both moments are zero and stay zero
+  n_explicit = n < kMaxReplay ? n : kMaxReplay;
+  n_rest = n - n_explicit;
+}
+__device__ __forceinline__ void decay_moments(float4& mm, float4& vv, const LazySched& s, int n_rest) {
+  if (n_rest > 0) {                               // the remaining steps only decay the moments
+    const float d1 = exp2f(s.l2_beta1 * (float)n_rest), d2 = exp2f(s.l2_beta2 * (float)n_rest);
     mm.x *= d1; mm.y *= d1; mm.z *= d1; mm.w *= d1;
     vv.x *= d2; vv.y *= d2; vv.z *= d2; vv.w *= d2;
   }
@@ -97,23 +98,37 @@ lazy_scan_kernel(unsigned char* __restrict__ need, int* __restrict__ last_step, 
     const bool work = kPrepare ? (mine && last > 0 && last < s.t - 1) : mine;
     const unsigned mask = __ballot_sync(0xffffffffu, work);
     const int total = __popc(mask) * c4;
-    for (int w0 = 0; w0 < total; w0 += 32) {                     // uniform trip count: every lane joins the shuffle
+    // Every lane runs every statement below (loads, stores and arithmetic are predicated on `on`): the
+    // replay loop has ONE trip count per warp, so lanes never split and each memory instruction is issued
+    // once per warp with all its addresses together.
+    for (int w0 = 0; w0 < total; w0 += 32) {
       const int w = w0 + lane;
       const bool on = w < total;
       const int which = on ? w / c4 : 0, grp = w - which * c4;
       const int src = __fns(mask, 0, which + 1);                 // lane that owns the which-th flagged texel
       const int last_t = __shfl_sync(0xffffffffu, last, src);
-      if (!on) continue;
       const long long e = (chunk * 32 + src) * c4 + grp;
-      float4 pp = p[e], mm = m[e], vv = v[e];
-      replay_steps(pp, mm, vv, s, last_t, s.t - 1);
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 pp = on ? p[e] : zero, mm = on ? m[e] : zero, vv = on ? v[e] : zero;
+      float4 gg = zero;
+      if (!kPrepare && on) gg = g[e];
+      int n_explicit, n_rest;
+      replay_plan(on ? last_t : 0, s.t - 1, n_explicit, n_rest);
+      const int n_warp = __reduce_max_sync(0xffffffffu, n_explicit);
+      Replay r = replay_start(s, last_t + 1);
+      for (int k = 0; k < n_warp; ++k) {
+        float4 p2 = pp, m2 = mm, v2 = vv;
+        Replay r2 = r;
+        zero_grad_step(p2, m2, v2, s, r2);
+        if (k < n_explicit) { pp = p2; mm = m2; vv = v2; r = r2; }   // selects, not branches
+      }
+      decay_moments(mm, vv, s, n_rest);
       if (kPrepare) {
-        shadow[e] = to_bf16x4(pp);
+        if (on) shadow[e] = to_bf16x4(pp);
       } else {
-        const float4 gg = g[e];
-        Replay r = replay_start(s, s.t);
-        const float step = r.lr / (1.f - r.b1p);
-        const float inv_sqrt_b2 = rsqrtf(1.f - r.b2p);
+        Replay rt = replay_start(s, s.t);
+        const float step = rt.lr / (1.f - rt.b1p);
+        const float inv_sqrt_b2 = rsqrtf(1.f - rt.b2p);
         const float* G = &gg.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -122,9 +137,11 @@ lazy_scan_kernel(unsigned char* __restrict__ need, int* __restrict__ last_step, 
           V[k] = s.beta2 * V[k] + (1.f - s.beta2) * gr * gr;
           P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + s.eps);
         }
-        g[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-        p[e] = pp; m[e] = mm; v[e] = vv;
-        if (shadow) shadow[e] = to_bf16x4(pp);
+        if (on) {
+          g[e] = zero;
+          p[e] = pp; m[e] = mm; v[e] = vv;
+          if (shadow) shadow[e] = to_bf16x4(pp);
+        }
       }
     }
     __syncwarp();
@@ -146,7 +163,11 @@ lazy_flush_kernel(const int* __restrict__ last_step, float4* __restrict__ p, flo
   const int last = last_step[texel];
   if (last >= s.t || last == 0) return;
   float4 pp = p[e], mm = m[e], vv = v[e];
-  replay_steps(pp, mm, vv, s, last, s.t);
+  int n_explicit, n_rest;
+  replay_plan(last, s.t, n_explicit, n_rest);
+  Replay r = replay_start(s, last + 1);
+  for (int k = 0; k < n_explicit; ++k) zero_grad_step(pp, mm, vv, s, r);
+  decay_moments(mm, vv, s, n_rest);
   p[e] = pp; m[e] = mm; v[e] = vv;
   if (shadow) shadow[e] = to_bf16x4(pp);
 }
