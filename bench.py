@@ -19,6 +19,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -58,7 +59,10 @@ def make_ray_pool(n_rays: int, lb, ub, seed: int):
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi polling every 20 ms in its own process (started before the warm-up so that it is already
+    reporting when the timed region begins); ``stop`` keeps the samples whose timestamp falls inside the
+    marked window, or all of them if the window was shorter than one period."""
+    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -66,15 +70,21 @@ class ClockSampler:
         self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
         self.idx = device_index
+        self.windows = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+                                          "-lms", "20", "-i", str(self.idx)], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
+    def mark(self, t0: float, t1: float):
+        self.windows.append((t0, t1))
+
     def stop(self):
+        import datetime
+
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -82,18 +92,22 @@ class ClockSampler:
         self.tmp.flush()
         rows = [r.split(", ") for r in open(self.tmp.name).read().strip().splitlines() if r.strip()]
         os.unlink(self.tmp.name)
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        parsed = []
         for r in rows:
             try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
+                ts = datetime.datetime.strptime(r[0].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                parsed.append((ts, float(r[2]), float(r[3]), float(r[4]),
+                               [n for n, v in zip(names, r[6:10]) if v.strip().lower().startswith("active")]))
             except (ValueError, IndexError):
                 continue
-            for name, val in zip(names, r[5:9]):
-                if val.strip().lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        inside = [p for p in parsed if any(t0 <= p[0] <= t1 for t0, t1 in self.windows)]
+        use = inside or parsed
+        sm = [p[1] for p in use]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(p[2] for p in use) if use else None,
+                "power_w": statistics.median(p[3] for p in use) if use else None,
+                "reasons": sorted({n for p in use for n in p[4]}), "samples": len(use),
+                "window": "timed region" if inside else "whole run (timed region shorter than a sample period)"}
 
 
 def run_ours(args):
@@ -153,17 +167,21 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms)
 
-    for k in range(warmup):
-        step_resident(k)
     sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
+    for k in range(warmup):
+        step_resident(k)
     launches0 = native.LAUNCH_CALLS
+    t0 = time.time()
     ms = timed(step_resident, steps)
+    sampler.mark(t0, time.time())
     launches = native.LAUNCH_CALLS - launches0
-    for k in range(min(warmup, 3)):
+    for k in range(max(warmup, 3)):
         step_e2e(k)
+    t0 = time.time()
     ms_e2e = timed(step_e2e, steps)
+    sampler.mark(t0, time.time())
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         value = global_batch * steps / (ms / 1e3)
@@ -176,7 +194,7 @@ def run_ours(args):
             "config": {"model": "GridNeRF branch-parallel large scene", "global_batch": global_batch,
                        "seq_len": SAMPLES, "parallelism": f"branch{nx}x{ny}" if n > 1 else "single",
                        "planes": f"{PLANE}^2 x (16+48)ch bf16 + fp32 master per GPU", "lines": LINE,
-                       "l2_policy": "inputs larger than L2: 6.4 GB of plane parameters touched per step"},
+                       "l2_policy": "inputs larger than L2: each step touches ~3 GB of plane texels, moments and gradients scattered over 21 GB of parameters and optimiser state"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "rays/s", "ms_per_step": ms_e2e / steps,
                     "h2d_bytes_per_step": RAYS_PER_GPU * 10 * 4, "d2h_bytes_per_step": 4,
@@ -191,8 +209,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     assert args.gpus in DIVISIONS, "supported GPU counts: 1, 2, 4, 8"

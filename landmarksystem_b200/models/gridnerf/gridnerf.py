@@ -351,6 +351,37 @@ class GridNeRF(BaseNeRF):
         feat = self.rgb_encoding(xyzb)
         return dec(dirs, feat, app_latent).float()
 
+    # -- colour stage on compacted rows, no host synchronisation ------------------------------------------
+    def _fused_app_stage_ok(self, xyzb: torch.Tensor) -> bool:
+        dec = self.rgb_decoder
+        if not (xyzb.is_cuda and getattr(dec, "use_fused", False) and not self.config.encode_app and self.config.ndims == 1
+                and type(self.rgb_encoding).__name__ in ("TensorVMEncoding", "BranchParallelTensorVMEncoding",
+                                                         "FusedTensorVMEncoding")):
+            return False
+        from ...ops.fused_mlp import rgb_backward_supported, rgb_decoder_supported
+
+        if not rgb_decoder_supported(dec):
+            return False
+        if not torch.is_grad_enabled():
+            return True
+        return bool(self.config.get("fused_mlp_train", False)) and rgb_backward_supported(dec)
+
+    def _fused_app_stage(self, xyzb, dirs, app_mask, samples_per_ray: int) -> torch.Tensor:
+        """Samples above the weight threshold are compacted on the device (count stays there), looked up,
+        decoded by the tcgen05 colour head and scattered back to ``[R*S, 3]``: the reference's
+        ``nonzero`` + gathers + ``index_put`` (benchmarks/nerf/gridnerf/gridnerf.py:846-871) without the
+        host round trip, with static shapes."""
+        from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_forward
+        from ...ops.select import ScatterRows3, compact_rows, put_dirs
+
+        idx, coords, count = compact_rows(app_mask, xyzb)
+        self.app_batch = count
+        # the colour head reads only the feature and direction columns of the first `count` rows
+        feat = self.rgb_encoding(coords, count=count, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False)
+        put_dirs(feat, 144, dirs, idx, count, samples_per_ray)
+        vals = rgb_decoder_forward(self.rgb_decoder, None, feat, count)
+        return ScatterRows3.apply(vals, idx, coords, count, xyzb.shape[0])
+
     def compute_alpha(self, xyz_locs: torch.Tensor, length: float = 1.0) -> torch.Tensor:
         valid = None
         if self.alphaMask is not None:
@@ -428,14 +459,20 @@ class GridNeRF(BaseNeRF):
         weight = self.renderer.get_weights(sigma, dists * cfg.distance_scale)
         app_mask = (weight > cfg.rayMarch_weight_thres).reshape(-1)
         rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)
-        idx = app_mask.nonzero(as_tuple=True)[0]
         if a2a:
+            idx = app_mask.nonzero(as_tuple=True)[0]
             ray_of = idx // S
             payload = torch.cat((xyzb[idx, :3], dirs[ray_of]), dim=-1)
             vals = self._dispatcher(R * S).query(payload, xyzb[idx, 3], GridNeRF._OwnerFn(self, "rgb"), 3)
             rgb = rgb.index_put((idx,), vals)
             rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
             return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists
+        if self._fused_app_stage_ok(xyzb):
+            rgb = self._fused_app_stage(xyzb, dirs, app_mask, S)
+            rgb = self._mp_sum(rgb)
+            rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
+            return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists
+        idx = app_mask.nonzero(as_tuple=True)[0]
         self.app_batch = (xyzb[idx, 3] >= 0).sum()
         if idx.numel() > 0 or (train and getattr(cfg, "branch_parallel", False)):
             if idx.numel() == 0:

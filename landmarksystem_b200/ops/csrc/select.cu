@@ -1,0 +1,102 @@
+// Row selection without a host round trip: stream compaction of a sample mask (the reference's
+// `app_mask.nonzero()` + index gathers, benchmarks/nerf/gridnerf/gridnerf.py:846-871, make the host wait
+// for the element count), plus the gathers / scatters that move per-sample rows between the full
+// [rays x samples] layout and the compacted one.  Every consumer takes the device-side count, so buffer
+// shapes are static (capacity = number of samples) and the whole training step can be captured in a
+// CUDA graph.
+#include "common.cuh"
+
+namespace lmb {
+
+// idx[pos] = i and coords_out[pos] = xyzb[i] for every i with mask[i] != 0; *count ends as the number of
+// selected rows.  Positions are handed out per warp (one atomic per warp), so rows of one warp stay
+// adjacent and in order.
+__global__ void __launch_bounds__(256)
+compact_kernel(const unsigned char* __restrict__ mask, long long n, const float4* __restrict__ xyzb, int* __restrict__ idx,
+               float4* __restrict__ coords_out, int* __restrict__ count) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const bool sel = i < n && mask[i] != 0;
+  const unsigned won = __ballot_sync(0xffffffffu, sel);
+  if (won == 0) return;
+  const int leader = __ffs(won) - 1;
+  int base = 0;
+  if (lane == leader) base = atomicAdd(count, __popc(won));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  if (sel) {
+    const int pos = base + __popc(won & ((1u << lane) - 1u));
+    idx[pos] = (int)i;
+    coords_out[pos] = xyzb[i];
+  }
+}
+
+// x[j, col .. col+2] = dirs[idx[j] / S] (bf16 rows of width x_stride) for the first *count rows
+__global__ void __launch_bounds__(256)
+put_dirs_kernel(__nv_bfloat16* __restrict__ x, int x_stride, int col, const float* __restrict__ dirs, const int* __restrict__ idx,
+                const int* __restrict__ count_ptr, long long max_n, int S) {
+  const long long n = resolve_count(count_ptr, max_n);
+  const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const float* d = dirs + (long long)(idx[j] / S) * 3;
+  __nv_bfloat16* o = x + j * x_stride + col;
+  o[0] = __float2bfloat16_rn(d[0]); o[1] = __float2bfloat16_rn(d[1]); o[2] = __float2bfloat16_rn(d[2]);
+}
+
+// kScatter: out[idx[j], :] = vals[j, :] (rows whose block id coords[j].w < 0 contribute zeros; out is pre-zeroed)
+// else    : vals[j, :] = out[idx[j], :] (same rule) - the adjoint
+template <bool kScatter>
+__global__ void __launch_bounds__(256)
+rows3_kernel(float* __restrict__ vals, const int* __restrict__ idx, const float4* __restrict__ coords,
+             const int* __restrict__ count_ptr, long long max_n, float* __restrict__ full) {
+  const long long n = resolve_count(count_ptr, max_n);
+  const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const bool live = coords[j].w >= 0.f;
+  float* f = full + (long long)idx[j] * 3;
+  float* v = vals + j * 3;
+  if (kScatter) {
+    if (live) { f[0] = v[0]; f[1] = v[1]; f[2] = v[2]; }
+  } else {
+    v[0] = live ? f[0] : 0.f; v[1] = live ? f[1] : 0.f; v[2] = live ? f[2] : 0.f;
+  }
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+// mask: uint8/bool [n]; xyzb: float [n, 4]; idx: int32 [n]; coords_out: float [n, 4]; count: int32 [1]
+LMB_API int lmb_compact_rows(const unsigned char* mask, long long n, const float* xyzb, int* idx, float* coords_out, int* count,
+                             cudaStream_t stream) {
+  LMB_CUDA_TRY(cudaMemsetAsync(count, 0, sizeof(int), stream));
+  if (n <= 0) return 0;
+  compact_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(mask, n, (const float4*)xyzb, idx, (float4*)coords_out, count);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_put_dirs(void* x, int x_stride, int col, const float* dirs, const int* idx, const int* count_ptr,
+                         long long max_n, int S, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  put_dirs_kernel<<<ceil_div(max_n, 256), 256, 0, stream>>>((__nv_bfloat16*)x, x_stride, col, dirs, idx, count_ptr, max_n, S);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_scatter_rows3(const float* vals, const int* idx, const float* coords, const int* count_ptr, long long max_n,
+                              float* out, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  rows3_kernel<true><<<ceil_div(max_n, 256), 256, 0, stream>>>(const_cast<float*>(vals), idx, (const float4*)coords, count_ptr,
+                                                              max_n, out);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_gather_rows3(const float* full, const int* idx, const float* coords, const int* count_ptr, long long max_n,
+                             float* vals, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  rows3_kernel<false><<<ceil_div(max_n, 256), 256, 0, stream>>>(vals, idx, (const float4*)coords, count_ptr, max_n,
+                                                               const_cast<float*>(full));
+  LMB_LAUNCH_CHECK();
+  return 0;
+}

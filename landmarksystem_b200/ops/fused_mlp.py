@@ -234,7 +234,8 @@ def rgb_backward_supported(decoder) -> bool:
             and lin[2].weight.shape == (3, 128) and all(l.bias is not None for l in lin))
 
 
-def rgb_decoder_backward(decoder, x: torch.Tensor, dout: torch.Tensor, count: Optional[torch.Tensor] = None):
+def rgb_decoder_backward(decoder, x: torch.Tensor, dout: torch.Tensor, count: Optional[torch.Tensor] = None,
+                         zero_tail: bool = True):
     """One launch: ``dL/dx`` (bf16 ``[N, 160]``, feature columns filled) and the gradients of
     ``(basis.weight, lin0.weight, lin0.bias, lin1.weight, lin1.bias, lin2.weight, lin2.bias)``."""
     packed = _rgb_packed(decoder)
@@ -242,7 +243,7 @@ def rgb_decoder_backward(decoder, x: torch.Tensor, dout: torch.Tensor, count: Op
     lib = native.lib()
     n_floats = int(lib.lmb_rgb_mlp_bwd_gbuf_floats())
     gbuf = torch.zeros(n_floats, device=x.device, dtype=torch.float32)
-    dx = torch.empty_like(x) if count is None else torch.zeros_like(x)
+    dx = torch.zeros_like(x) if (count is not None and zero_tail) else torch.empty_like(x)
     dout = dout.contiguous().float()
     native.check(lib.lmb_rgb_mlp_bwd(x.data_ptr(), native.ptr(count), x.shape[0], packed.blob.data_ptr(), byref(packed.spec),
                                      dout.data_ptr(), dout.shape[1], dx.data_ptr(), gbuf.data_ptr(),
@@ -262,24 +263,28 @@ class _RGBDecoderFn(torch.autograd.Function):
     """x: [N, 160] bf16 rows = [features(<=144), dir(3) at col 144, zeros]."""
 
     @staticmethod
-    def forward(ctx, x, decoder, *params):
-        ctx.decoder = decoder
+    def forward(ctx, x, decoder, count, *params):
+        ctx.decoder, ctx.count = decoder, count
         ctx.save_for_backward(x)
-        return _rgb_packed(decoder).run(x)
+        return _rgb_packed(decoder).run(x, count)
 
     @staticmethod
     def backward(ctx, dout):
         (x,) = ctx.saved_tensors
-        dec = ctx.decoder
+        dec, count = ctx.decoder, ctx.count
         if rgb_backward_supported(dec):
-            dx, grads = rgb_decoder_backward(dec, x, dout)
+            # rows past the device-side count are never read by the consumer of dx
+            dx, grads = rgb_decoder_backward(dec, x, dout, count, zero_tail=False)
             lin = dec.decoder.linears()
             by_param = {id(dec.basis_mat.weight): grads[0], id(lin[0].weight): grads[1], id(lin[0].bias): grads[2],
                         id(lin[1].weight): grads[3], id(lin[1].bias): grads[4], id(lin[2].weight): grads[5],
                         id(lin[2].bias): grads[6]}
             params = list(dec.basis_mat.parameters()) + list(dec.decoder.parameters())
-            return (dx, None, *[by_param.get(id(p)) for p in params])
+            return (dx, None, None, *[by_param.get(id(p)) for p in params])
         from ..components.fields.mlp_decoder import positional_encoding
+
+        if count is not None:
+            raise RuntimeError("colour head: a device-side row count needs the fused backward kernel (128-wide hidden layers)")
 
         with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             xin = x.detach().float().requires_grad_()
@@ -290,15 +295,18 @@ class _RGBDecoderFn(torch.autograd.Function):
             out = dec.decoder.mlp(mlp_in).float()
             params = list(dec.basis_mat.parameters()) + list(dec.decoder.parameters())
             grads = torch.autograd.grad(out, [xin] + params, dout)
-        return (grads[0].to(x.dtype), None, *grads[1:])
+        return (grads[0].to(x.dtype), None, None, *grads[1:])
 
 
-def rgb_decoder_forward(decoder, dirs: torch.Tensor, feats: torch.Tensor) -> torch.Tensor:
+def rgb_decoder_forward(decoder, dirs: Optional[torch.Tensor], feats: torch.Tensor,
+                        count: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``feats``: either ``[N, 160]`` bf16 rows produced by ``vm_encode(out_width=160)`` or plain
-    ``[N, C]`` features; ``dirs [N, 3]``."""
+    ``[N, C]`` features; ``dirs [N, 3]`` (``None``: the caller already wrote the direction columns).
+    ``count``: device-side number of valid rows."""
     if feats.shape[1] == RGB_IN_WIDTH and feats.dtype == torch.bfloat16:
         x = feats
-        x[:, 144:147] = dirs.to(torch.bfloat16)
+        if dirs is not None:
+            x[:, 144:147] = dirs.to(torch.bfloat16)
     else:
         x = torch.cat((feats.to(torch.bfloat16), torch.zeros(feats.shape[0], 144 - feats.shape[1], device=feats.device,
                                                               dtype=torch.bfloat16),
@@ -306,8 +314,8 @@ def rgb_decoder_forward(decoder, dirs: torch.Tensor, feats: torch.Tensor) -> tor
                        torch.zeros(feats.shape[0], RGB_IN_WIDTH - 147, device=feats.device, dtype=torch.bfloat16)), dim=-1)
     params = list(decoder.basis_mat.parameters()) + list(decoder.decoder.parameters())
     if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
-        return _RGBDecoderFn.apply(x.contiguous(), decoder, *params)
-    return _rgb_packed(decoder).run(x.contiguous())
+        return _RGBDecoderFn.apply(x.contiguous(), decoder, count, *params)
+    return _rgb_packed(decoder).run(x.contiguous(), count)
 
 
 # -- Scaffold / Octree anchor heads -------------------------------------------------------------------

@@ -71,7 +71,7 @@ class _VMEncode(torch.autograd.Function):
     (planes..., lines...) and optionally 2*L bf16 shadow tensors that the kernels read instead."""
 
     @staticmethod
-    def forward(ctx, coords, count, out_dtype, n_levels, out_width, *grids):
+    def forward(ctx, coords, count, out_dtype, n_levels, out_width, zero_fill, *grids):
         masters = grids[: 2 * n_levels]
         shadows = grids[2 * n_levels:]
         read = shadows if shadows else masters
@@ -80,7 +80,7 @@ class _VMEncode(torch.autograd.Function):
         C = planes[0].shape[-1]
         width = max(out_width, n_levels * C)
         out = torch.empty((N, width), device=coords.device, dtype=out_dtype)
-        if count is not None or width > n_levels * C:
+        if zero_fill and (count is not None or width > n_levels * C):
             out.zero_()
         lv = _levels_struct(planes, lines)
         native.check(
@@ -117,16 +117,18 @@ class _VMEncode(torch.autograd.Function):
                                            native.DTYPE_CODE[dout.dtype], dout.shape[1], native.stream_ptr()),
             "vm_encode_bwd")
         out_grads = [None if s else g for s, g in zip(sunk, grads)]
-        return (None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+        return (None, None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
 
 
 def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torch.Tensor],
               shadow_planes: Optional[List[torch.Tensor]] = None, shadow_lines: Optional[List[torch.Tensor]] = None,
               count: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32,
-              out_width: int = 0) -> torch.Tensor:
+              out_width: int = 0, zero_fill: bool = True) -> torch.Tensor:
     """Look up ``[N, L*C]`` features.  ``shadow_*`` (bf16 copies of the fp32 masters) are what the
     CUDA kernels read when given; gradients always flow to the fp32 masters.  ``out_width`` > L*C
-    returns a wider, zero-padded row (room for columns a consumer kernel wants appended)."""
+    returns a wider, zero-padded row (room for columns a consumer kernel wants appended).  With
+    ``zero_fill=False`` padding columns and rows past ``count`` are left uninitialised (for consumers
+    that never read them)."""
     if not coords.is_cuda:
         feat = vm_encode_reference(coords, planes, lines).to(out_dtype)
         if out_width > feat.shape[1]:
@@ -136,4 +138,4 @@ def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torc
     grids = list(planes) + list(lines)
     if shadow_planes is not None:
         grids += list(shadow_planes) + list(shadow_lines)
-    return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, *grids)
+    return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, zero_fill, *grids)

@@ -74,3 +74,40 @@ def test_gpu_training_bf16_fused(tmp_path):
     tr.model.train()
     losses = [float(tr.train_step(*tr.data_mgr.get_rays(it))) for it in range(60)]
     assert losses[-1] < 0.6 * losses[0]
+
+
+@pytest.mark.gpu
+def test_gpu_fused_colour_stage_matches_index_path(tmp_path):
+    """Device-side compaction + tcgen05 colour head (forward and backward kernels) against the
+    nonzero / gather / index_put path with the PyTorch MLP: same image, same gradients."""
+    ref = _trainer(tmp_path / "r", "cuda", grid_dtype="bf16", fused_optimizer="false")
+    fus = _trainer(tmp_path / "f", "cuda", grid_dtype="bf16", fused_optimizer="false", fused_mlp_train="true",
+                   runtime="Kernel")
+    fus.module.load_state_dict(ref.module.state_dict())
+    for t in (ref, fus):
+        t.module.eval()                      # no jitter, no random background
+        t.config.is_train = True
+    ref.module.rgb_decoder.use_fused = False
+    rays, rgbs, idxs = ref.data_mgr.get_rays(0)
+    r7 = torch.cat((rays, idxs[:, None]), -1).cuda()
+    outs = []
+    for t in (ref, fus):
+        torch.manual_seed(7)                 # same stratified-sampling jitter in both passes
+        out = t.module(r7, N_samples=48)["rgb_map"]
+        (out * torch.linspace(0.5, 1.5, out.numel(), device="cuda").view_as(out)).sum().backward()
+        outs.append(out.detach())
+    assert fus.module._fused_app_stage_ok(torch.zeros(1, 4, device="cuda"))
+    assert torch.allclose(outs[0], outs[1], atol=2e-2), (outs[0] - outs[1]).abs().max()
+
+    def rel(a, b):
+        return float((a - b).norm() / (b.norm() + 1e-12))
+
+    errs = {}
+    for (name, p_ref), (_, p_fus) in zip(ref.module.named_parameters(), fus.module.named_parameters()):
+        if p_ref.grad is None:
+            continue
+        assert p_fus.grad is not None, name
+        errs[name] = round(rel(p_fus.grad.float(), p_ref.grad.float()), 4)
+    assert len(errs) >= 6
+    bad = {k: v for k, v in errs.items() if not v < 0.12}
+    assert not bad, errs
