@@ -20,6 +20,12 @@ class VolumeRenderer(BaseRenderer):
 
     def forward(self, weights: torch.Tensor, rgbs: torch.Tensor, z_vals: torch.Tensor,
                 random_white_bg_ratio: float = 0.0):
+        if not self.white_bg and random_white_bg_ratio > 0.0 and weights.is_cuda:
+            # the coin is tossed on the device: no host decision is baked in when the step is recorded in a CUDA graph
+            bg = (torch.rand((), device=weights.device) < random_white_bg_ratio).to(weights.dtype)
+            rgb_map, depth_map, _ = composite_render(weights, rgbs, z_vals, 0.0)
+            rgb_map = rgb_map + bg * (1.0 - weights.sum(-1, keepdim=True))
+            return rgb_map.clamp(0, 1), depth_map
         white = self.white_bg or (random_white_bg_ratio > 0.0 and float(torch.rand(())) < random_white_bg_ratio)
         rgb_map, depth_map, _ = composite_render(weights, rgbs, z_vals, 1.0 if white else 0.0)
         return rgb_map.clamp(0, 1), depth_map

@@ -49,6 +49,7 @@ class TrainConfig(ConfigClass):
 
     # additions of this framework
     dp_optimizer: Literal["p2p_zero", "nccl_allreduce"] = "p2p_zero"   # data-parallel gradient path on GPUs
+    cuda_graph: bool = False     # record the whole training step once in a CUDA graph and replay it (single-GPU fused path)
     profile: bool = False                                              # CUDA-event stage timers + NVTX ranges
 
     def check_args(self) -> None:

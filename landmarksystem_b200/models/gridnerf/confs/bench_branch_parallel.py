@@ -16,6 +16,7 @@ train_config = TrainConfig(
     N_vis=0,
     random_seed=0,
     print_timestamp=False,
+    cuda_graph=True,         # single-GPU runs replay the whole step from one CUDA graph
 )
 
 dataset_config = DatasetConfig(

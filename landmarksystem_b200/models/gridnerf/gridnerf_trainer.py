@@ -107,6 +107,9 @@ class GridNeRFTrainer(NeRFTrainer):
         Adam; CPU: ``torch.optim.Adam``."""
         cfg = self.config
         on_cuda = torch.device(cfg.device).type == "cuda"
+        decay = cfg.lr_decay_target_ratio ** (1.0 / (cfg.lr_decay_iters if cfg.lr_decay_iters > 0 else cfg.n_iters))
+        for g in groups:
+            g["lr_decay"] = decay              # per-step factor; fused optimisers need it to reconstruct / advance the schedule
         if on_cuda and cfg.DDP and cfg.get("dp_optimizer", "p2p_zero") == "p2p_zero" and dist.is_initialized():
             from ...parallel.zero_adam import GroupedP2PZeroAdam
 
@@ -114,13 +117,13 @@ class GridNeRFTrainer(NeRFTrainer):
             return GroupedP2PZeroAdam(groups, betas=(0.9, 0.99), group=cfg.dp_group if cfg.model_parallel else None,
                                       shadow=cfg.get("grid_dtype") == "bf16")
         use_fused = bool(cfg.get("fused_optimizer", True)) and on_cuda
-        return (FusedAdam if use_fused else torch.optim.Adam)(groups, betas=(0.9, 0.99))
+        if use_fused:
+            return FusedAdam(groups, betas=(0.9, 0.99), capturable=bool(cfg.get("cuda_graph", False)))
+        return torch.optim.Adam(groups, betas=(0.9, 0.99))
 
     def create_optimizer(self):
         cfg = self.config
         groups = self.module.get_optparam_groups(cfg.lr_init, cfg.lr_basis)
-        for g in groups:
-            g["lr_decay"] = cfg.lr_decay_target_ratio ** (1.0 / (cfg.lr_decay_iters if cfg.lr_decay_iters > 0 else cfg.n_iters))
         self.optimizer = self._make_optimizer(groups)
         optim_file = self._optim_path()
         if cfg.get("ckpt") and os.path.exists(optim_file):
@@ -189,7 +192,55 @@ class GridNeRFTrainer(NeRFTrainer):
 
     def train_step(self, rays_train, rgb_train, idxs_train):
         """Forward, backward, gradient sync and optimiser step on one device-resident batch.
-        Returns the (detached, device) photometric MSE."""
+        Returns the (detached, device) photometric MSE.  With ``cuda_graph`` the whole step is recorded
+        once into a CUDA graph and replayed (one launch per step instead of a few hundred)."""
+        if self._graph_ok(rays_train):
+            return self._train_step_graphed(rays_train, rgb_train, idxs_train)
+        return self._train_step_eager(rays_train, rgb_train, idxs_train)
+
+    # -- whole-step CUDA graph ---------------------------------------------------------------------
+    _GRAPH_WARMUP = 3
+
+    def _graph_ok(self, rays) -> bool:
+        cfg = self.config
+        return bool(cfg.get("cuda_graph", False)) and rays.is_cuda and isinstance(self.optimizer, FusedAdam) \
+            and self.optimizer.capturable and self.mp_sync is None and self.dp_sync is None \
+            and not (cfg.branch_parallel or cfg.channel_parallel or cfg.DDP) and not self.timer.enabled
+
+    def _train_step_graphed(self, rays, rgbs, idxs):
+        """Inputs are copied into fixed buffers; the first steps run eagerly (allocator and lazily built state
+        settle), then one step is captured - forward, backward, deferred Adam and the schedule advance, all
+        on device-resident counters - and every later call is a copy + one graph launch.  The graph is
+        rebuilt when the batch shape, the sample count or the optimiser object changes (grid upsampling)."""
+        st = getattr(self, "_graph_state", None)
+        key = (tuple(rays.shape), self.nsamples, id(self.optimizer), bool(self.module.run_nerf))
+        if st is None or st["key"] != key:
+            st = {"key": key, "rays": torch.empty_like(rays), "rgbs": torch.empty_like(rgbs), "idxs": torch.empty_like(idxs),
+                  "graph": None, "warm": 0, "loss": None}
+            self._graph_state = st
+        st["rays"].copy_(rays); st["rgbs"].copy_(rgbs); st["idxs"].copy_(idxs)
+        if st["graph"] is None:
+            if st["warm"] < self._GRAPH_WARMUP:
+                st["warm"] += 1
+                return self._train_step_eager(st["rays"], st["rgbs"], st["idxs"])
+            torch.cuda.synchronize()
+            from ...ops import native
+
+            graph = torch.cuda.CUDAGraph()
+            launches0 = native.LAUNCH_CALLS
+            with torch.cuda.graph(graph):
+                st["loss"] = self._train_step_eager(st["rays"], st["rgbs"], st["idxs"])
+            st["graph"], st["launches"] = graph, native.LAUNCH_CALLS - launches0   # library kernels recorded in the graph
+            graph.replay()          # capture records without executing; the host-side counters advanced once above
+            return st["loss"]
+        from ...ops import native
+
+        st["graph"].replay()
+        native.LAUNCH_CALLS += st["launches"]   # the replay launches every recorded kernel again
+        self.optimizer.host_advance()
+        return st["loss"]
+
+    def _train_step_eager(self, rays_train, rgb_train, idxs_train):
         cfg = self.config
         with self.timer.stage("forward"):
             rays_chunk = torch.cat((rays_train, idxs_train[:, None]), dim=-1)

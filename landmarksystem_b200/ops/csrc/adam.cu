@@ -5,17 +5,33 @@
 // separate zero_grad; for 10^9-parameter plane grids the update is purely HBM-bound, so every extra
 // pass costs milliseconds.  Bytes per parameter here: read 16 (g, p, m, v), write 12 + 2 + 4.
 #include "common.cuh"
+#include <cmath>
 
 namespace lmb {
 
 struct AdamArgs {
   float lr, beta1, beta2, eps, bias1, bias2, grad_scale, weight_decay;
+  // Optional device-resident schedule {learning rate, step number (1-based) of the step being applied}:
+  // when set it overrides lr / bias1 / bias2, so a launch recorded in a CUDA graph follows the schedule
+  // on every replay.  l2_beta* = log2(beta*).
+  const float* dyn;
+  float l2_beta1, l2_beta2;
 };
+
+__device__ __forceinline__ void resolve_dyn(AdamArgs& a) {
+  if (a.dyn != nullptr) {
+    const float step = a.dyn[1];
+    a.lr = a.dyn[0];
+    a.bias1 = 1.f - exp2f(a.l2_beta1 * step);
+    a.bias2 = 1.f - exp2f(a.l2_beta2 * step);
+  }
+}
 
 template <bool kShadow>
 __global__ void __launch_bounds__(256)
 adam_kernel(float4* __restrict__ p, float4* __restrict__ g, float4* __restrict__ m, float4* __restrict__ v,
             uint2* __restrict__ shadow, long long n4, AdamArgs a) {
+  resolve_dyn(a);
   const float step = a.lr / a.bias1;
   const float inv_sqrt_b2 = rsqrtf(a.bias2);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -43,12 +59,18 @@ __global__ void adam_tail_kernel(float* p, float* g, float* m, float* v, __nv_bf
                                  long long n, AdamArgs a) {
   long long i = start + blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  resolve_dyn(a);
   float gr = g[i] * a.grad_scale + a.weight_decay * p[i];
   float mm = a.beta1 * m[i] + (1.f - a.beta1) * gr;
   float vv = a.beta2 * v[i] + (1.f - a.beta2) * gr * gr;
   float pp = p[i] - (a.lr / a.bias1) * mm / (sqrtf(vv) * rsqrtf(a.bias2) + a.eps);
   p[i] = pp; m[i] = mm; v[i] = vv; g[i] = 0.f;
   if (shadow) shadow[i] = __float2bfloat16_rn(pp);
+}
+
+__global__ void adam_dyn_advance_kernel(float* dyn, float decay) {
+  dyn[0] *= decay;
+  dyn[1] += 1.f;
 }
 
 __global__ void __launch_bounds__(256) cast_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, long long n4) {
@@ -65,15 +87,8 @@ __global__ void __launch_bounds__(256) cast_bf16_kernel(const float4* __restrict
 
 using namespace lmb;
 
-// step >= 1.  shadow may be null.  All pointers 16-byte aligned (torch allocations are).
-LMB_API int lmb_adam_step(float* p, float* g, float* m, float* v, void* shadow_bf16, long long n, float lr,
-                          float beta1, float beta2, float eps, int step, float grad_scale, float weight_decay,
-                          cudaStream_t stream) {
-  if (n <= 0) return 0;
-  AdamArgs a;
-  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
-  a.bias1 = 1.f - powf(beta1, (float)step);
-  a.bias2 = 1.f - powf(beta2, (float)step);
+static int adam_launch(float* p, float* g, float* m, float* v, void* shadow_bf16, long long n, const AdamArgs& a,
+                       cudaStream_t stream) {
   const long long n4 = n / 4;
   if (n4 > 0) {
     long long want = (n4 + 255) / 256;
@@ -88,6 +103,38 @@ LMB_API int lmb_adam_step(float* p, float* g, float* m, float* v, void* shadow_b
     adam_tail_kernel<<<1, 32, 0, stream>>>(p, g, m, v, (__nv_bfloat16*)shadow_bf16, n4 * 4, n, a);
     LMB_LAUNCH_CHECK();
   }
+  return 0;
+}
+
+// step >= 1.  shadow may be null.  All pointers 16-byte aligned (torch allocations are).
+LMB_API int lmb_adam_step(float* p, float* g, float* m, float* v, void* shadow_bf16, long long n, float lr,
+                          float beta1, float beta2, float eps, int step, float grad_scale, float weight_decay,
+                          cudaStream_t stream) {
+  if (n <= 0) return 0;
+  AdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, (float)step);
+  a.bias2 = 1.f - powf(beta2, (float)step);
+  a.dyn = nullptr; a.l2_beta1 = a.l2_beta2 = 0.f;
+  return adam_launch(p, g, m, v, shadow_bf16, n, a, stream);
+}
+
+// Same update with the learning rate and step number read from device memory (dyn = {lr, step}); the
+// launch can be replayed from a CUDA graph while lmb_adam_dyn_advance moves the schedule.
+LMB_API int lmb_adam_step_dyn(float* p, float* g, float* m, float* v, void* shadow_bf16, long long n, const float* dyn,
+                              float beta1, float beta2, float eps, float grad_scale, float weight_decay, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  AdamArgs a;
+  a.lr = 0.f; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
+  a.bias1 = a.bias2 = 1.f;
+  a.dyn = dyn; a.l2_beta1 = (float)log2((double)beta1); a.l2_beta2 = (float)log2((double)beta2);
+  return adam_launch(p, g, m, v, shadow_bf16, n, a, stream);
+}
+
+// dyn[0] *= decay (next step's learning rate); dyn[1] += 1 (next step's number)
+LMB_API int lmb_adam_dyn_advance(float* dyn, float decay, cudaStream_t stream) {
+  adam_dyn_advance_kernel<<<1, 1, 0, stream>>>(dyn, decay);
+  LMB_LAUNCH_CHECK();
   return 0;
 }
 

@@ -26,7 +26,15 @@ struct LazySched {
   float beta1, beta2, eps;
   float l2_decay, l2_beta1, l2_beta2;   // log2 of the three bases (host, double precision)
   int t;           // step being prepared / applied, or (flush) the last completed step (1-based)
+  const float* dyn;  // optional device-resident {lr of the step being applied, its number}: overrides lr_ref, t_ref, t
 };
+
+__device__ __forceinline__ void resolve_dyn(LazySched& s) {
+  if (s.dyn != nullptr) {
+    s.lr_ref = s.dyn[0];
+    s.t_ref = s.t = (int)s.dyn[1];
+  }
+}
 
 struct Replay {
   float lr, b1p, b2p;   // lr_k, beta1^k, beta2^k of the NEXT step to replay
@@ -87,6 +95,7 @@ __global__ void __launch_bounds__(256)
 lazy_scan_kernel(unsigned char* __restrict__ need, int* __restrict__ last_step, float4* __restrict__ p, float4* __restrict__ g,
                  float4* __restrict__ m, float4* __restrict__ v, uint2* __restrict__ shadow, int c4, long long n_texels,
                  LazySched s, float grad_scale) {
+  resolve_dyn(s);
   const int lane = threadIdx.x & 31;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -200,8 +209,10 @@ vm_mark_kernel(const float4* __restrict__ coords, const int* __restrict__ count_
 
 using namespace lmb;
 
-static LazySched make_sched(float lr_ref, int t_ref, float decay, float beta1, float beta2, float eps, int t) {
+static LazySched make_sched(float lr_ref, int t_ref, float decay, float beta1, float beta2, float eps, int t,
+                            const float* dyn = nullptr) {
   LazySched s;
+  s.dyn = dyn;
   s.lr_ref = lr_ref; s.t_ref = t_ref; s.decay = decay; s.beta1 = beta1; s.beta2 = beta2; s.eps = eps; s.t = t;
   s.l2_decay = (float)log2((double)decay); s.l2_beta1 = (float)log2((double)beta1); s.l2_beta2 = (float)log2((double)beta2);
   return s;
@@ -223,24 +234,24 @@ LMB_API int lmb_vm_mark(const float* coords, const int* count_ptr, long long max
 
 LMB_API int lmb_lazy_adam_prepare(unsigned char* need, int* last_step, const float* p, const float* m, const float* v,
                                   void* shadow, int C, long long n_texels, float lr_ref, int t_ref, float decay, float beta1,
-                                  float beta2, float eps, int t, cudaStream_t stream) {
+                                  float beta2, float eps, int t, const float* dyn, cudaStream_t stream) {
   if (C % 4) return (int)cudaErrorInvalidValue;
   if (n_texels <= 0) return 0;
   lazy_scan_kernel<true><<<scan_grid(n_texels), 256, 0, stream>>>(need, last_step, (float4*)p, nullptr, (float4*)m, (float4*)v,
                                                                  (uint2*)shadow, C / 4, n_texels,
-                                                                 make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t), 1.f);
+                                                                 make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t, dyn), 1.f);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
 LMB_API int lmb_lazy_adam_step(unsigned char* need, int* last_step, float* p, float* g, float* m, float* v, void* shadow,
                                int C, long long n_texels, float lr_ref, int t_ref, float decay, float beta1, float beta2,
-                               float eps, int t, float grad_scale, cudaStream_t stream) {
+                               float eps, int t, float grad_scale, const float* dyn, cudaStream_t stream) {
   if (C % 4) return (int)cudaErrorInvalidValue;
   if (n_texels <= 0) return 0;
   lazy_scan_kernel<false><<<scan_grid(n_texels), 256, 0, stream>>>(need, last_step, (float4*)p, (float4*)g, (float4*)m,
                                                                   (float4*)v, (uint2*)shadow, C / 4, n_texels,
-                                                                  make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t),
+                                                                  make_sched(lr_ref, t_ref, decay, beta1, beta2, eps, t, dyn),
                                                                   grad_scale);
   LMB_LAUNCH_CHECK();
   return 0;

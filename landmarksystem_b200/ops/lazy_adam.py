@@ -18,9 +18,9 @@ from . import native
 P = native.P
 native.register_signature("lmb_vm_mark", [P, P, c_longlong, c_int, c_int, c_int, P, P])
 native.register_signature("lmb_lazy_adam_prepare", [P, P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
-                                                     c_float, c_float, c_int, P])
+                                                     c_float, c_float, c_int, P, P])
 native.register_signature("lmb_lazy_adam_step", [P, P, P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
-                                                  c_float, c_float, c_int, c_float, P])
+                                                  c_float, c_float, c_int, c_float, P, P])
 native.register_signature("lmb_lazy_adam_flush", [P, P, P, P, P, c_int, c_longlong, c_float, c_int, c_float, c_float,
                                                    c_float, c_float, c_int, P])
 
@@ -40,6 +40,8 @@ class LazyPlaneState:
         self.marked = False
         # schedule published by the optimiser: lr of step `t_ref`, geometric decay, Adam constants
         self.sched = {"lr_ref": 0.0, "t_ref": 1, "decay": 1.0, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8}
+        # device-resident {lr, step} of a capturable optimiser (None: the host values above are passed by value)
+        self.dyn: Optional[torch.Tensor] = None
         self.dirty = False
 
     def _sched_args(self):
@@ -56,7 +58,8 @@ class LazyPlaneState:
         if self.steps_done > 0:
             native.check(lib.lmb_lazy_adam_prepare(self.need.data_ptr(), self.last_step.data_ptr(), param.data_ptr(),
                                                    self.m.data_ptr(), self.v.data_ptr(), param._lmb_shadow.data_ptr(), C,
-                                                   B * H * W, *self._sched_args(), self.steps_done + 1, st), "lazy_prepare")
+                                                   B * H * W, *self._sched_args(), self.steps_done + 1, native.ptr(self.dyn), st),
+                         "lazy_prepare")
 
     def step(self, param, grad, grad_scale: float = 1.0) -> None:
         B, H, W, C = self.shape
@@ -65,8 +68,8 @@ class LazyPlaneState:
             native.check(native.lib().lmb_lazy_adam_step(self.need.data_ptr(), self.last_step.data_ptr(), param.data_ptr(),
                                                          grad.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
                                                          native.ptr(getattr(param, "_lmb_shadow", None)), C, B * H * W,
-                                                         *self._sched_args(), t, float(grad_scale), native.stream_ptr()),
-                         "lazy_step")
+                                                         *self._sched_args(), t, float(grad_scale), native.ptr(self.dyn),
+                                                         native.stream_ptr()), "lazy_step")
         self.marked = False
         self.steps_done = t
         self.dirty = True
@@ -75,6 +78,10 @@ class LazyPlaneState:
         """Bring every texel to ``steps_done`` (zero-gradient replay of whatever it skipped)."""
         if not self.dirty or self.steps_done == 0:
             return
+        if self.dyn is not None:                 # steps replayed from a CUDA graph advance only the device copy
+            lr, nxt = self.dyn.tolist()
+            self.steps_done = int(round(nxt)) - 1
+            self.sched.update(lr_ref=lr, t_ref=int(round(nxt)))
         B, H, W, C = self.shape
         native.check(native.lib().lmb_lazy_adam_flush(self.last_step.data_ptr(), param.data_ptr(), self.m.data_ptr(),
                                                       self.v.data_ptr(), native.ptr(getattr(param, "_lmb_shadow", None)), C,

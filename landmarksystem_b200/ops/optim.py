@@ -29,8 +29,44 @@ class FusedAdam(torch.optim.Optimizer):
     * ``_lmb_shadow`` - bf16 copy of the parameter, refreshed in the same kernel that updates it.
     """
 
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, capturable: bool = False):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        # capturable: every group's {learning rate, step number} lives on the device and is advanced by a
+        # kernel at the end of step() (lr *= group["lr_decay"]), so a step recorded in a CUDA graph follows
+        # the schedule on replay.  group["lr"] then only mirrors the device value for logging; call
+        # ``sync_dyn`` after changing it by hand and ``host_advance`` after every graph replay.
+        self.capturable = capturable
+        if capturable:
+            self.sync_dyn()
+
+    def sync_dyn(self) -> None:
+        """Push every group's host-side learning rate and step count to its device-resident schedule."""
+        for group in self.param_groups:
+            dev = next((p.device for p in group["params"] if p.is_cuda), None)
+            if dev is None:
+                continue
+            steps = [self.state[p].get("step", 0) for p in group["params"] if p in self.state and self.state[p]]
+            steps += [p._lmb_lazy.steps_done for p in group["params"] if getattr(p, "_lmb_lazy", None) is not None]
+            nxt = float(max(steps) + 1 if steps else 1)
+            if group.get("_dyn") is None:
+                group["_dyn"] = torch.tensor([group["lr"], nxt], device=dev, dtype=torch.float32)
+            else:
+                group["_dyn"].copy_(torch.tensor([group["lr"], nxt], dtype=torch.float32))
+            for p in group["params"]:
+                if getattr(p, "_lmb_lazy", None) is not None:
+                    p._lmb_lazy.dyn = group["_dyn"]
+
+    def host_advance(self) -> None:
+        """Mirror one graph-replayed step in the host-side bookkeeping (no kernel is launched)."""
+        for group in self.param_groups:
+            group["lr"] *= float(group.get("lr_decay", 1.0))
+            for p in group["params"]:
+                lazy = getattr(p, "_lmb_lazy", None)
+                if lazy is not None:
+                    lazy.steps_done += 1
+                    lazy.dirty = True
+                elif p in self.state and self.state[p]:
+                    self.state[p]["step"] += 1
 
     @staticmethod
     def attach_sink(param: torch.Tensor, shadow: bool = False, lazy: bool = False) -> None:
@@ -51,6 +87,8 @@ class FusedAdam(torch.optim.Optimizer):
         loss = closure() if closure is not None else None
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
+            dyn = group.get("_dyn") if self.capturable else None
+            stepped = False
             for p in group["params"]:
                 sink = getattr(p, "_lmb_grad_sink", None)
                 grad = sink if sink is not None else p.grad
@@ -63,6 +101,7 @@ class FusedAdam(torch.optim.Optimizer):
                     lazy.sched.update(lr_ref=group["lr"], t_ref=lazy.steps_done + 1, decay=decay, beta1=beta1, beta2=beta2,
                                       eps=group["eps"])
                     lazy.step(p, sink, grad_scale)
+                    stepped = True
                     continue
                 state = self.state[p]
                 if not state:
@@ -71,7 +110,14 @@ class FusedAdam(torch.optim.Optimizer):
                     state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
                 state["step"] += 1
                 shadow = getattr(p, "_lmb_shadow", None)
+                stepped = True
                 if p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
+                        and grad.dtype == torch.float32 and dyn is not None:
+                    native.check(native.lib().lmb_adam_step_dyn(
+                        p.data_ptr(), grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
+                        native.ptr(shadow), p.numel(), dyn.data_ptr(), beta1, beta2, group["eps"], grad_scale,
+                        group["weight_decay"], native.stream_ptr()), "adam_step_dyn")
+                elif p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
                         and grad.dtype == torch.float32:
                     native.check(native.lib().lmb_adam_step(
                         p.data_ptr(), grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
@@ -88,6 +134,9 @@ class FusedAdam(torch.optim.Optimizer):
                     grad.zero_()
                     if shadow is not None:
                         shadow.copy_(p)
+            if dyn is not None and stepped:
+                native.check(native.lib().lmb_adam_dyn_advance(dyn.data_ptr(), float(group.get("lr_decay", 1.0)),
+                                                               native.stream_ptr()), "adam_dyn_advance")
         return loss
 
     def zero_grad(self, set_to_none: bool = True):  # gradients are cleared inside step()
