@@ -1,0 +1,251 @@
+"""Kernel micro-benchmarks: ``python -m landmarksystem_b200.ops.microbench <name> [--rows N] [--iters K]``.
+
+Each case times one library kernel in isolation with CUDA events (after warm-up, inputs larger than the
+126 MB L2 or an L2 flush between launches) and prints one JSON line with the algorithmic bytes / FLOPs,
+the achieved rate and its fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root
+when present: STREAM-style copy bandwidth and cuBLAS bf16 throughput on the same GPU model).  The same
+command line is what the profiler captures are taken from.
+
+Cases: ``adam`` (dense fused Adam), ``lazy_adam`` (deferred Adam step over the touched texels of a plane),
+``vm_fwd`` / ``vm_bwd`` (plane x line lookup), ``mlp_fwd`` / ``mlp_bwd`` (tcgen05 colour head),
+``composite`` (volume-render weights + colour), ``hash_fwd`` (multiresolution hash grid).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable, Dict
+
+import torch
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def measured_peaks() -> Dict[str, float]:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path, encoding="utf-8") as fh:
+            data = json.load(fh)
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS)
+
+
+class _L2Flush:
+    def __init__(self, enabled: bool):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if enabled else None
+
+    def __call__(self):
+        if self.buf is not None:
+            self.buf.zero_()
+
+
+def time_kernel(fn: Callable[[], None], iters: int, warmup: int = 3, flush_l2: bool = False, setup: Callable[[], None] = None):
+    """Median and best device time (ms) of ``fn`` over ``iters`` launches; ``setup`` runs untimed before each."""
+    flush = _L2Flush(flush_l2)
+    for _ in range(warmup):
+        if setup:
+            setup()
+        fn()
+    times = []
+    for _ in range(iters):
+        if setup:
+            setup()
+        flush()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def _report(name, ms, best, bytes_=0.0, flops=0.0, **extra):
+    peaks = measured_peaks()
+    out = {"kernel": name, "ms_median": round(ms, 4), "ms_best": round(best, 4)}
+    if bytes_:
+        gbs = bytes_ / (ms * 1e-3) / 1e9
+        out.update(algorithmic_gb=round(bytes_ / 1e9, 3), gbs=round(gbs, 1),
+                   frac_of_hbm_peak=round(gbs / peaks["hbm_gbs"], 3))
+    if flops:
+        tf = flops / (ms * 1e-3) / 1e12
+        out.update(algorithmic_gflop=round(flops / 1e9, 2), tflops=round(tf, 1),
+                   frac_of_bf16_peak=round(tf / peaks["bf16_tflops"], 3))
+    out["peaks"] = f'{peaks["source"]}: {peaks["hbm_gbs"]} GB/s, {peaks["bf16_tflops"]} TFLOP/s'
+    out.update(extra)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+# -- cases ----------------------------------------------------------------------------------------
+def case_adam(args):
+    from . import FusedAdam
+
+    n = args.rows * 64
+    p = torch.nn.Parameter(torch.randn(n, device="cuda"))
+    FusedAdam.attach_sink(p, shadow=True)
+    opt = FusedAdam([p], lr=1e-3)
+    p._lmb_grad_sink.normal_()
+    ms, best = time_kernel(opt.step, args.iters)
+    return _report("adam_kernel<shadow>", ms, best, bytes_=n * 34.0, params=n)
+
+
+def case_lazy_adam(args):
+    from . import FusedAdam
+
+    C, side = args.channels, args.plane
+    p = torch.nn.Parameter(torch.randn(1, side, side, C, device="cuda") * 0.1)
+    FusedAdam.attach_sink(p, shadow=True, lazy=True)
+    opt = FusedAdam([{"params": [p], "lr": 0.02, "lr_decay": 0.999}])
+    state = p._lmb_lazy
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    touched = [0]
+
+    def setup():
+        coords = torch.rand(args.rows, 4, device="cuda", generator=gen) * 2 - 1
+        coords[:, 3] = 0
+        state.prepare(p, coords)
+        mask = state.need != 0
+        touched[0] = int(mask.sum())
+        p._lmb_grad_sink.view(-1, C)[mask] = 0.01
+
+    ms, best = time_kernel(opt.step, args.iters, warmup=6, setup=setup)
+    # per touched texel: read p, g, m, v; write p, g, m, v (fp32) + bf16 shadow + flag/last-step; plus one flag byte per texel
+    bytes_ = touched[0] * (C * 4 * 8 + C * 2 + 6) + side * side
+    return _report("lazy_scan_kernel<step>", ms, best, bytes_=float(bytes_), touched_texels=touched[0],
+                   touched_fraction=round(touched[0] / side ** 2, 3), channels=C)
+
+
+def _vm_setup(args):
+    C, side = args.channels, args.plane
+    planes = [torch.nn.Parameter(torch.randn(1, side, side, C, device="cuda") * 0.1)]
+    lines = [torch.nn.Parameter(torch.randn(1, 512, C, device="cuda") * 0.1)]
+    from . import FusedAdam
+
+    for t in planes + lines:
+        FusedAdam.attach_sink(t, shadow=True)
+    coords = torch.rand(args.rows, 4, device="cuda") * 2 - 1
+    coords[:, 3] = 0
+    return planes, lines, coords.contiguous()
+
+
+def case_vm_fwd(args):
+    from .vm import vm_encode
+
+    planes, lines, coords = _vm_setup(args)
+    C = args.channels
+    with torch.no_grad():
+        fn = lambda: vm_encode(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines],
+                               out_dtype=torch.bfloat16)
+        ms, best = time_kernel(fn, args.iters)
+    # per sample: 4 plane texels + 2 line entries (bf16) in, one bf16 feature row out, 16 B coordinate
+    return _report("vm_encode_fwd_kernel<bf16,bf16>", ms, best, bytes_=args.rows * (6 * C * 2 + C * 2 + 16.0), channels=C)
+
+
+def case_vm_bwd(args):
+    from .vm import vm_encode
+
+    planes, lines, coords = _vm_setup(args)
+    C = args.channels
+    out = vm_encode(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines], out_dtype=torch.bfloat16)
+    dout = torch.randn_like(out)
+    ms, best = time_kernel(lambda: out.backward(dout, retain_graph=True), args.iters)
+    # per sample: re-read 6 bf16 rows + bf16 dout row, reduce 6 fp32 rows into the accumulators
+    return _report("vm_encode_bwd_kernel<bf16,bf16>", ms, best, bytes_=args.rows * (6 * C * 2 + C * 2 + 6 * C * 4 + 16.0), channels=C)
+
+
+def _rgb_decoder(n_feat: int):
+    from ..models.gridnerf.gridnerf import RGBDecoder
+
+    torch.manual_seed(0)
+    return RGBDecoder([n_feat], [1], 27, view_pe=2, fea_pe=2, featureC=128).cuda()
+
+
+def _mlp_flops(n_feat: int, rows: int, backward: bool) -> float:
+    fwd = 2.0 * rows * (n_feat * 27 + 150 * 128 + 128 * 128 + 128 * 3)
+    return fwd * 3.0 if backward else fwd       # recompute + data gradients + weight gradients
+
+
+def case_mlp_fwd(args):
+    from . import fused_mlp
+
+    dec = _rgb_decoder(args.channels)
+    x = (torch.randn(args.rows, fused_mlp.RGB_IN_WIDTH, device="cuda") * 0.3).to(torch.bfloat16)
+    with torch.no_grad():
+        ms, best = time_kernel(lambda: fused_mlp.rgb_decoder_forward(dec, None, x), args.iters)
+    dec._lmb_packed.check_status()
+    return _report("fused_mlp_kernel", ms, best, flops=_mlp_flops(args.channels, args.rows, False),
+                   bytes_=args.rows * (fused_mlp.RGB_IN_WIDTH * 2 + 12.0), rows=args.rows)
+
+
+def case_mlp_bwd(args):
+    from . import fused_mlp
+
+    dec = _rgb_decoder(args.channels)
+    x = (torch.randn(args.rows, fused_mlp.RGB_IN_WIDTH, device="cuda") * 0.3).to(torch.bfloat16)
+    dout = torch.randn(args.rows, 3, device="cuda")
+    ms, best = time_kernel(lambda: fused_mlp.rgb_decoder_backward(dec, x, dout), args.iters)
+    dec._lmb_packed.check_status()
+    return _report("rgb_mlp_bwd_kernel", ms, best, flops=_mlp_flops(args.channels, args.rows, True),
+                   bytes_=args.rows * (fused_mlp.RGB_IN_WIDTH * 4 + 12.0), rows=args.rows)
+
+
+def case_composite(args):
+    from .composite import composite_render, composite_weights
+
+    rays, S = max(args.rows // 128, 1), 128
+    sigma = torch.rand(rays, S, device="cuda")
+    dists = torch.full((rays, S), 0.1, device="cuda")
+    rgbs = torch.rand(rays, S, 3, device="cuda")
+    z = torch.rand(rays, S, device="cuda").sort(-1).values
+
+    def fn():
+        w, _ = composite_weights(sigma, dists)
+        composite_render(w, rgbs, z, 0.0)
+
+    with torch.no_grad():
+        ms, best = time_kernel(fn, args.iters, flush_l2=True)
+    return _report("composite weights+render", ms, best, bytes_=rays * S * (4 * 3 + 4 * 5.0), rays=rays)
+
+
+def case_hash_fwd(args):
+    import math
+
+    from .hashgrid import hashgrid_encode, make_meta
+
+    meta = make_meta(16, 2, 22, 16, math.exp(math.log(8192 / 16) / 15))
+    table = torch.rand(meta.n_params, device="cuda") * 2e-4 - 1e-4
+    table._lmb_shadow = table.to(torch.bfloat16)          # the kernels read the bf16 copy
+    x = torch.rand(args.rows, 3, device="cuda")
+    with torch.no_grad():
+        ms, best = time_kernel(lambda: hashgrid_encode(x, table, meta), args.iters)
+    # per sample and level: 8 corners x 2 bf16 features in, 2 fp32 features out
+    return _report("hashgrid fwd", ms, best, bytes_=args.rows * 16 * (8 * 4 + 8.0), rows=args.rows)
+
+
+CASES = {"adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd,
+         "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--rows", type=int, default=1 << 20, help="samples / rows per launch")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--channels", type=int, default=48, help="feature channels of the plane / appearance features")
+    ap.add_argument("--plane", type=int, default=4096, help="plane side length (lazy_adam, vm_*)")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    names = sorted(CASES) if args.case == "all" else [args.case]
+    for name in names:
+        CASES[name](args)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
