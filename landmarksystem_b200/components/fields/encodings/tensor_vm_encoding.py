@@ -186,6 +186,32 @@ class TensorVMEncoding(VolumeEncoding):
                              count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill)
         return vm_encode(coords, planes, lines, count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill)
 
+    def fused_density_ok(self, xyzb: torch.Tensor) -> bool:
+        from ....ops.vm import vm_density_supported
+
+        return xyzb.is_cuda and self.ndims == 1 and type(self).forward is TensorVMEncoding.forward \
+            and vm_density_supported(self.plane_coef)
+
+    def density(self, xyzb: torch.Tensor, weight, inner_relu: bool, act: str, shift: float, count=None) -> torch.Tensor:
+        """``sigma [N]`` straight from the lookup kernel: channel-weighted sum (``weight [1, L*C]`` or ``None``)
+        and activation are applied in registers, the feature matrix is never written."""
+        from ....ops.vm import vm_density
+
+        ks = range(len(self.reso_mode))
+        planes = [self.plane_coef[k] for k in ks]
+        lines = [self.line_coef[k] for k in ks]
+        coords = xyzb.contiguous().float()
+        if getattr(self, "lazy", False):
+            if self.training and torch.is_grad_enabled():
+                for p in planes:
+                    p._lmb_lazy.prepare(p, coords, count)
+            else:
+                self.flush_lazy()
+        if self.use_shadow:
+            return vm_density(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines],
+                              weight, inner_relu, act, shift, count)
+        return vm_density(coords, planes, lines, None, None, weight, inner_relu, act, shift, count)
+
     def forward(self, xyzb: torch.Tensor, count=None, out_dtype=torch.float32, out_width: int = 0,
                 zero_fill: bool = True) -> torch.Tensor:
         """``xyzb [N, 4]`` = block-local xyz in ``[-1, 1]`` + block index -> ``[N, sum(C) * n_levels]``

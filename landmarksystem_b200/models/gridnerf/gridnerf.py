@@ -114,6 +114,7 @@ class GridNeRFConfig(ConfigClass):
     branch_dispatch: Literal["allreduce", "a2a"] = "allreduce"   # a2a: every rank brings its own rays; samples
                                                   # travel to the GPU owning their block over NVLink peer memory
     fused_optimizer: bool = True
+    fused_density: bool = True                    # density lookup + head in one kernel on CUDA
     lazy_adam: bool = False                       # deferred (exact) Adam on the planes: visit touched texels only
 
     def check_args(self) -> None:
@@ -179,6 +180,14 @@ class Feature2Density(nn.Module):
         if not self.nonlinear:
             sigma_feature = sigma_feature.sum(dim=-1, keepdim=True)
         return self.feature2density(sigma_feature)
+
+    def kernel_args(self):
+        """``(weight or None, inner_relu, activation name, shift)`` for the fused lookup + head kernel."""
+        last = self.feature2density[-1]
+        weight = self.feature2density[0].weight if self.nonlinear else None
+        if isinstance(last, _ShiftedSoftplus):
+            return weight, self.nonlinear, "softplus", float(last.shift)
+        return weight, self.nonlinear, "relu", 0.0
 
 
 def n_to_reso(n_voxels, bbox):
@@ -331,9 +340,12 @@ class GridNeRF(BaseNeRF):
             m.app_batch = torch.tensor(rows.shape[0], device=rows.device)
             return m._rgb(xyzb, rows[:, 3:6].contiguous(), None)
 
-    def _density(self, xyzb: torch.Tensor) -> torch.Tensor:
-        feat = self.density_encoding(xyzb)
-        return self.feature2density(feat).squeeze(-1).float()
+    def _density(self, xyzb: torch.Tensor, count=None) -> torch.Tensor:
+        enc, head = self.density_encoding, self.feature2density
+        if bool(self.config.get("fused_density", True)) and hasattr(enc, "fused_density_ok") and enc.fused_density_ok(xyzb):
+            return enc.density(xyzb, *head.kernel_args(), count=count)
+        feat = enc(xyzb, count=count) if count is not None else enc(xyzb)
+        return head(feat).squeeze(-1).float()
 
     def _rgb(self, xyzb, dirs, app_latent=None) -> torch.Tensor:
         dec = self.rgb_decoder

@@ -135,6 +135,145 @@ vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
   }
 }
 
+// ---- fused density head --------------------------------------------------------------------------
+// sigma = act(relu?(sum_c w_c * feature_c)): the lookup, the 1-wide linear layer (or plain channel sum)
+// and the activation of the reference's density path (benchmarks/nerf/gridnerf/gridnerf.py:177-197,
+// compute_densityfeature + feature2density) in one kernel; the [N, L*C] feature matrix is never written.
+// The C/8 threads of a sample are adjacent lanes (C/8 must be a power of two <= 32).
+struct DensityHead {
+  const float* w;     // [L*C] weights of the 1-wide linear layer, or nullptr for a plain sum
+  int inner_relu;     // relu between the linear layer and the activation
+  int act;            // 0 relu, 1 softplus(x + shift)
+  float shift;
+};
+
+template <typename T>
+__device__ __forceinline__ void vm_features(const VMLevels& lv, int l, const float4& q, int b, int ch, F8& f, F8& pv8, F8& lv8,
+                                            Corner2& cx, Corner2& cy, Corner2& cz) {
+  const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+  cx = taps(q.x, W); cy = taps(q.y, H); cz = taps(q.z, Z);
+  const T* pl = reinterpret_cast<const T*>(lv.plane[l]) + ((long long)b * H * W) * lv.C + ch * 8;
+  const T* ln = reinterpret_cast<const T*>(lv.line[l]) + ((long long)b * Z) * lv.C + ch * 8;
+  F8 p00 = load8(pl + ((long long)cy.i0 * W + cx.i0) * lv.C), p01 = load8(pl + ((long long)cy.i0 * W + cx.i1) * lv.C);
+  F8 p10 = load8(pl + ((long long)cy.i1 * W + cx.i0) * lv.C), p11 = load8(pl + ((long long)cy.i1 * W + cx.i1) * lv.C);
+  F8 l0 = load8(ln + (long long)cz.i0 * lv.C), l1 = load8(ln + (long long)cz.i1 * lv.C);
+  const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    pv8.v[i] = w00 * p00.v[i] + w01 * p01.v[i] + w10 * p10.v[i] + w11 * p11.v[i];
+    lv8.v[i] = cz.w0 * l0.v[i] + cz.w1 * l1.v[i];
+    f.v[i] = pv8.v[i] * lv8.v[i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+vm_density_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n, VMLevels lv,
+                      DensityHead head, float* __restrict__ sigma, float* __restrict__ pre) {
+  const int CH = lv.C >> 3;
+  const long long n_valid = resolve_count(count_ptr, max_n);
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n = tid / CH;
+  const int ch = (int)(tid - n * CH);
+  const bool live = n < n_valid;
+  float acc = 0.f;
+  if (live) {
+    const float4 q = __ldg(coords + n);
+    const int b = (int)q.w;
+    if (b >= 0 && b < lv.B) {
+      for (int l = 0; l < lv.L; ++l) {
+        F8 f, pv8, lv8;
+        Corner2 cx, cy, cz;
+        vm_features<T>(lv, l, q, b, ch, f, pv8, lv8, cx, cy, cz);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc += f.v[i] * (head.w ? __ldg(head.w + l * lv.C + ch * 8 + i) : 1.f);
+      }
+    }
+  }
+  for (int o = CH >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (live && ch == 0) {
+    const float r = head.inner_relu ? fmaxf(acc, 0.f) : acc;
+    const float x = r + head.shift;
+    sigma[n] = head.act == 0 ? fmaxf(r, 0.f) : (x > 20.f ? x : log1pf(__expf(x)));
+    pre[n] = acc;
+  }
+}
+
+// dsigma [N] -> plane / line gradient accumulators (as vm_encode_bwd) and dw [L*C] (block-reduced, one
+// atomic per block and channel)
+template <typename T>
+__global__ void __launch_bounds__(256)
+vm_density_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n, VMLevels lv,
+                      DensityHead head, const float* __restrict__ dsigma, const float* __restrict__ pre, float* __restrict__ dw) {
+  extern __shared__ float dw_sh[];               // [L*C]
+  const int CH = lv.C >> 3;
+  const int n_w = lv.L * lv.C;
+  for (int i = threadIdx.x; i < n_w; i += blockDim.x) dw_sh[i] = 0.f;
+  __syncthreads();
+  const long long n_valid = resolve_count(count_ptr, max_n);
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n = tid / CH;
+  const int ch = (int)(tid - n * CH);
+  const int lane = threadIdx.x & 31;
+  bool live = n < n_valid;
+  float4 q = make_float4(0.f, 0.f, 0.f, -1.f);
+  float dz = 0.f;
+  if (live) {
+    q = __ldg(coords + n);
+    const int b = (int)q.w;
+    live = b >= 0 && b < lv.B;
+    if (live) {
+      const float z = pre[n];
+      const float r = head.inner_relu ? fmaxf(z, 0.f) : z;
+      const float dact = head.act == 0 ? (r > 0.f ? 1.f : 0.f) : __fdividef(1.f, 1.f + __expf(-(r + head.shift)));
+      dz = dsigma[n] * dact * ((head.inner_relu && z <= 0.f) ? 0.f : 1.f);
+    }
+  }
+  for (int l = 0; l < lv.L; ++l) {
+    F8 dwp;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwp.v[i] = 0.f;
+    if (live && dz != 0.f) {
+      const int b = (int)q.w;
+      F8 f, pv8, lv8;
+      Corner2 cx, cy, cz;
+      vm_features<T>(lv, l, q, b, ch, f, pv8, lv8, cx, cy, cz);
+      const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+      F8 dp, dl;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float g = dz * (head.w ? __ldg(head.w + l * lv.C + ch * 8 + i) : 1.f);
+        dp.v[i] = g * lv8.v[i];
+        dl.v[i] = g * pv8.v[i];
+        dwp.v[i] = dz * f.v[i];
+      }
+      float* gp = lv.gplane[l] + ((long long)b * H * W) * lv.C + ch * 8;
+      float* gl = lv.gline[l] + ((long long)b * Z) * lv.C + ch * 8;
+      const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+      if (w00 != 0.f) red_add8(gp + ((long long)cy.i0 * W + cx.i0) * lv.C, dp, w00);
+      if (w01 != 0.f) red_add8(gp + ((long long)cy.i0 * W + cx.i1) * lv.C, dp, w01);
+      if (w10 != 0.f) red_add8(gp + ((long long)cy.i1 * W + cx.i0) * lv.C, dp, w10);
+      if (w11 != 0.f) red_add8(gp + ((long long)cy.i1 * W + cx.i1) * lv.C, dp, w11);
+      if (cz.w0 != 0.f) red_add8(gl + (long long)cz.i0 * lv.C, dl, cz.w0);
+      if (cz.w1 != 0.f) red_add8(gl + (long long)cz.i1 * lv.C, dl, cz.w1);
+    }
+    if (head.w != nullptr && dw != nullptr) {
+      // lanes with the same channel group are CH apart: fold them, then one shared-memory atomic per warp
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v = dwp.v[i];
+        for (int o = CH; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane < CH) atomicAdd(&dw_sh[l * lv.C + (lane % CH) * 8 + i], v);
+      }
+    }
+  }
+  if (head.w != nullptr && dw != nullptr) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_w; i += blockDim.x)
+      if (dw_sh[i] != 0.f) atomicAdd(dw + i, dw_sh[i]);
+  }
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -172,6 +311,44 @@ LMB_API int lmb_vm_encode_bwd(const float* coords, const int* count_ptr, long lo
   else if (param_dtype == 1 && dout_dtype == 0) LAUNCH(__nv_bfloat16, float);
   else LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+static bool density_shape_ok(const VMLevels* lv) {
+  const int CH = lv->C / 8;
+  return lv->C % 8 == 0 && lv->L >= 1 && lv->L <= kMaxLevels && CH >= 1 && CH <= 32 && (CH & (CH - 1)) == 0;
+}
+
+// sigma, pre: fp32 [max_n]; w: fp32 [L*C] or null (plain channel sum); act: 0 relu, 1 softplus(x + shift)
+LMB_API int lmb_vm_density_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
+                               int param_dtype, const float* w, int inner_relu, int act, float shift, float* sigma, float* pre,
+                               cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  if (!density_shape_ok(levels)) return (int)cudaErrorInvalidValue;
+  const DensityHead head{w, inner_relu, act, shift};
+  const int blocks = ceil_div(max_n * (levels->C / 8), 256);
+  const float4* c4 = reinterpret_cast<const float4*>(coords);
+  if (param_dtype == 0) vm_density_fwd_kernel<float><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
+  else vm_density_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// dw: fp32 [L*C] accumulator (may be null when w is null)
+LMB_API int lmb_vm_density_bwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
+                               int param_dtype, const float* w, int inner_relu, int act, float shift, const float* dsigma,
+                               const float* pre, float* dw, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  if (!density_shape_ok(levels)) return (int)cudaErrorInvalidValue;
+  const DensityHead head{w, inner_relu, act, shift};
+  const int blocks = ceil_div(max_n * (levels->C / 8), 256);
+  const size_t smem = sizeof(float) * levels->L * levels->C;
+  const float4* c4 = reinterpret_cast<const float4*>(coords);
+  if (param_dtype == 0)
+    vm_density_bwd_kernel<float><<<blocks, 256, smem, stream>>>(c4, count_ptr, max_n, *levels, head, dsigma, pre, dw);
+  else
+    vm_density_bwd_kernel<__nv_bfloat16><<<blocks, 256, smem, stream>>>(c4, count_ptr, max_n, *levels, head, dsigma, pre, dw);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -9,7 +9,7 @@ Output is ``[N, L*C]`` with level-major channel order, i.e. the concat-over-leve
 """
 from __future__ import annotations
 
-from ctypes import byref
+from ctypes import POINTER, byref, c_float, c_int, c_longlong
 from typing import List, Optional, Sequence
 
 import torch
@@ -139,3 +139,82 @@ def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torc
     if shadow_planes is not None:
         grids += list(shadow_planes) + list(shadow_lines)
     return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, zero_fill, *grids)
+
+
+# -- fused density head: lookup + 1-wide linear (or channel sum) + activation -> sigma [N] ---------------------
+native.register_signature("lmb_vm_density_fwd", [native.P, native.P, c_longlong, POINTER(native.VMLevels), c_int, native.P,
+                                                  c_int, c_int, c_float, native.P, native.P, native.P])
+native.register_signature("lmb_vm_density_bwd", [native.P, native.P, c_longlong, POINTER(native.VMLevels), c_int, native.P,
+                                                  c_int, c_int, c_float, native.P, native.P, native.P, native.P])
+
+
+def vm_density_supported(planes) -> bool:
+    ch = planes[0].shape[-1] // 8
+    return planes[0].is_cuda and planes[0].shape[-1] % 8 == 0 and 1 <= ch <= 32 and (ch & (ch - 1)) == 0
+
+
+def vm_density_reference(coords, planes, lines, weight, inner_relu: bool, act: str, shift: float) -> torch.Tensor:
+    feat = vm_encode_reference(coords, planes, lines)
+    z = feat @ weight.reshape(-1).float() if weight is not None else feat.sum(-1)
+    r = torch.relu(z) if inner_relu else z
+    return torch.relu(r) if act == "relu" else torch.nn.functional.softplus(r + shift)
+
+
+class _VMDensity(torch.autograd.Function):
+    """Inputs: coords, count, weight (or None), inner_relu, act code, shift, n_levels, then the grids as in
+    ``_VMEncode``.  Output: sigma ``[N]`` fp32 (rows past ``count`` undefined)."""
+
+    @staticmethod
+    def forward(ctx, coords, count, weight, inner_relu, act, shift, n_levels, *grids):
+        masters = grids[: 2 * n_levels]
+        shadows = grids[2 * n_levels:]
+        read = shadows if shadows else masters
+        planes, lines = list(read[:n_levels]), list(read[n_levels:])
+        N = coords.shape[0]
+        sigma = torch.empty(N, device=coords.device, dtype=torch.float32)
+        pre = torch.empty(N, device=coords.device, dtype=torch.float32)
+        w = None if weight is None else weight.detach().reshape(-1).float().contiguous()
+        lv = _levels_struct(planes, lines)
+        native.check(native.lib().lmb_vm_density_fwd(coords.data_ptr(), native.ptr(count), N, byref(lv),
+                                                     native.DTYPE_CODE[planes[0].dtype], native.ptr(w), int(inner_relu), act,
+                                                     float(shift), sigma.data_ptr(), pre.data_ptr(), native.stream_ptr()),
+                     "vm_density_fwd")
+        ctx.save_for_backward(coords, count, pre, w, *read)
+        ctx.n_levels, ctx.masters, ctx.n_shadow = n_levels, masters, len(shadows)
+        ctx.head = (int(inner_relu), act, float(shift))
+        ctx.weight_shape = None if weight is None else weight.shape
+        return sigma
+
+    @staticmethod
+    def backward(ctx, dsigma):
+        coords, count, pre, w, *read = ctx.saved_tensors
+        L = ctx.n_levels
+        planes, lines = read[:L], read[L:]
+        grads, sunk = [], []
+        for m in ctx.masters:
+            sink = getattr(m, "_lmb_grad_sink", None)
+            sunk.append(sink is not None)
+            grads.append(sink if sink is not None else torch.zeros(m.shape, device=m.device, dtype=torch.float32))
+        lv = _levels_struct(planes, lines, grads[:L], grads[L:])
+        dw = None if w is None else torch.zeros_like(w)
+        dsigma = dsigma.contiguous().float()
+        native.check(native.lib().lmb_vm_density_bwd(coords.data_ptr(), native.ptr(count), coords.shape[0], byref(lv),
+                                                     native.DTYPE_CODE[planes[0].dtype], native.ptr(w), *ctx.head,
+                                                     dsigma.data_ptr(), pre.data_ptr(), native.ptr(dw), native.stream_ptr()),
+                     "vm_density_bwd")
+        out_grads = [None if s else g for s, g in zip(sunk, grads)]
+        dweight = None if dw is None else dw.view(ctx.weight_shape)
+        return (None, None, dweight, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+
+
+def vm_density(coords: torch.Tensor, planes, lines, shadow_planes=None, shadow_lines=None, weight=None,
+               inner_relu: bool = False, act: str = "softplus", shift: float = 0.0, count=None) -> torch.Tensor:
+    """``sigma [N] = act(relu?(features @ weight))`` (``weight=None``: plain channel sum) without materialising
+    the features.  ``act``: ``"relu"`` or ``"softplus"`` (of ``x + shift``)."""
+    if not coords.is_cuda:
+        return vm_density_reference(coords, planes, lines, weight, inner_relu, act, shift)
+    coords = coords.contiguous().float()
+    grids = list(planes) + list(lines)
+    if shadow_planes is not None:
+        grids += list(shadow_planes) + list(shadow_lines)
+    return _VMDensity.apply(coords, count, weight, inner_relu, 0 if act == "relu" else 1, shift, len(planes), *grids)

@@ -183,3 +183,32 @@ def test_lazy_adam_long_gap():
             opt.step()
             opt.param_groups[0]["lr"] *= 0.999
     assert torch.allclose(lazy, dense, atol=5e-6, rtol=1e-5), (lazy - dense).abs().max()
+
+
+@pytest.mark.parametrize("nonlinear,act", [(True, "softplus"), (True, "relu"), (False, "softplus")])
+def test_vm_density_matches_reference(nonlinear, act):
+    """Fused lookup + density head (forward, grid / line / weight gradients) vs the PyTorch restatement."""
+    from landmarksystem_b200.ops.vm import vm_density, vm_density_reference
+
+    torch.manual_seed(0)
+    B, H, W, Z, C, L, n = 2, 24, 20, 16, 16, 2, 3000
+    planes = [torch.nn.Parameter(torch.randn(B, H * (l + 1), W * (l + 1), C, device=DEV) * 0.3) for l in range(L)]
+    lines = [torch.nn.Parameter(torch.randn(B, Z * (l + 1), C, device=DEV) * 0.3) for l in range(L)]
+    weight = torch.nn.Parameter(torch.randn(1, L * C, device=DEV) * 0.3) if nonlinear else None
+    coords = torch.rand(n, 4, device=DEV) * 2.2 - 1.1
+    coords[:, 3] = torch.randint(-1, B, (n,), device=DEV).float()
+    count = torch.tensor([n - 500], device=DEV, dtype=torch.int32)
+    dsig = torch.randn(n, device=DEV)
+    dsig[n - 500:] = 0
+    shift = -0.5
+    out = vm_density(coords, planes, lines, None, None, weight, nonlinear, act, shift, count)
+    (out[: n - 500] * dsig[: n - 500]).sum().backward()
+    got = [p.grad.clone() for p in planes + lines] + ([weight.grad.clone()] if nonlinear else [])
+    for p in planes + lines + ([weight] if nonlinear else []):
+        p.grad = None
+    ref = vm_density_reference(coords[: n - 500], planes, lines, weight, nonlinear, act, shift)
+    (ref * dsig[: n - 500]).sum().backward()
+    want = [p.grad for p in planes + lines] + ([weight.grad] if nonlinear else [])
+    assert torch.allclose(out[: n - 500], ref, atol=1e-5, rtol=1e-4)
+    for g, w in zip(got, want):
+        assert torch.allclose(g, w, atol=1e-4, rtol=1e-3), (g - w).abs().max()
