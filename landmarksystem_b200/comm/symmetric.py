@@ -19,7 +19,7 @@ from ..ops import native
 P = native.P
 for _name, _sig in (("lmb_symm_alloc", [c_longlong, ctypes.POINTER(c_void_p)]), ("lmb_symm_free", [P]),
                     ("lmb_ipc_get_handle", [P, P]), ("lmb_ipc_open", [P, ctypes.POINTER(c_void_p)]),
-                    ("lmb_ipc_close", [P]), ("lmb_peer_barrier", [P, P, c_int, c_int, c_uint, P, P])):
+                    ("lmb_ipc_close", [P]), ("lmb_peer_barrier", [P, P, c_int, c_int, P, P, P])):
     native.register_signature(_name, _sig)
 
 
@@ -90,7 +90,7 @@ class PeerBarrier:
 
     def __init__(self, group=None):
         self.buf = SymmetricBuffer(256, group)
-        self.epoch = 0
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.buf.device)   # barriers passed, kept on the device
         self.status = torch.zeros(1, dtype=torch.int32, device=self.buf.device)
         self.flag_table = self.buf.peer_table(0)
         if self.buf.world > 1:
@@ -99,9 +99,8 @@ class PeerBarrier:
     def __call__(self) -> None:
         if self.buf.world == 1:
             return
-        self.epoch += 1
         native.check(native.lib().lmb_peer_barrier(self.buf.local_ptr, self.flag_table.data_ptr(), self.buf.rank,
-                                                   self.buf.world, self.epoch, self.status.data_ptr(),
+                                                   self.buf.world, self.epoch.data_ptr(), self.status.data_ptr(),
                                                    native.stream_ptr()), "peer_barrier")
 
     def check(self) -> None:

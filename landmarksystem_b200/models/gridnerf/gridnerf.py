@@ -331,14 +331,27 @@ class GridNeRF(BaseNeRF):
             mods = [m.density_encoding, m.feature2density] if self.kind == "sigma" else [m.rgb_encoding, m.rgb_decoder]
             return [p for mod in mods for p in mod.parameters()]
 
-        def __call__(self, rows):
+        def __call__(self, coords, extra, m_dev):
+            """``coords [M_cap, 4]`` / ``extra [M_cap, 3]`` hold ``m_dev`` (device int) received rows; the result has
+            ``M_cap`` rows of which the first ``m_dev`` are valid.  Kernel paths never learn ``m_dev`` on the host."""
             m = self.model
-            xyzb = torch.cat((rows[:, :3], torch.zeros_like(rows[:, :1])), dim=-1)
             if self.kind == "sigma":
-                m.sigma_batch = torch.tensor(rows.shape[0], device=rows.device)
-                return m._density(xyzb)[:, None]
-            m.app_batch = torch.tensor(rows.shape[0], device=rows.device)
-            return m._rgb(xyzb, rows[:, 3:6].contiguous(), None)
+                m.sigma_batch = m_dev
+                enc = m.density_encoding
+                if bool(m.config.get("fused_density", True)) and enc.fused_density_ok(coords):
+                    return m._density(coords, count=m_dev)[:, None]
+                k = int(m_dev.item())
+                return F.pad(m._density(coords[:k])[:, None], (0, 0, 0, coords.shape[0] - k))
+            m.app_batch = m_dev
+            if m._fused_app_stage_ok(coords):
+                from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_forward
+                from ...ops.select import put_dirs
+
+                feat = m.rgb_encoding(coords, count=m_dev, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False)
+                put_dirs(feat, 144, extra, None, m_dev)
+                return rgb_decoder_forward(m.rgb_decoder, None, feat, m_dev)
+            k = int(m_dev.item())
+            return F.pad(m._rgb(coords[:k], extra[:k].contiguous(), None), (0, 0, 0, coords.shape[0] - k))
 
     def _density(self, xyzb: torch.Tensor, count=None) -> torch.Tensor:
         enc, head = self.density_encoding, self.feature2density
@@ -472,11 +485,12 @@ class GridNeRF(BaseNeRF):
         app_mask = (weight > cfg.rayMarch_weight_thres).reshape(-1)
         rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)
         if a2a:
-            idx = app_mask.nonzero(as_tuple=True)[0]
-            ray_of = idx // S
-            payload = torch.cat((xyzb[idx, :3], dirs[ray_of]), dim=-1)
-            vals = self._dispatcher(R * S).query(payload, xyzb[idx, 3], GridNeRF._OwnerFn(self, "rgb"), 3)
-            rgb = rgb.index_put((idx,), vals)
+            from ...ops.select import ScatterRows3, build_payload6, compact_rows
+
+            idx, coords_c, count = compact_rows(app_mask, xyzb)          # stays on the device: no row count reaches the host
+            payload, owner_c = build_payload6(coords_c, dirs, idx, count, S)
+            vals = self._dispatcher(R * S).query(payload, owner_c, GridNeRF._OwnerFn(self, "rgb"), 3, count=count)
+            rgb = ScatterRows3.apply(vals, idx, coords_c, count, R * S)
             rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
             return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists
         if self._fused_app_stage_ok(xyzb):

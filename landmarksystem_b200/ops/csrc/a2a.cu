@@ -22,17 +22,30 @@ struct A2APeers {
 };
 
 // payload: [n, W] floats; dst[n]: owner rank or -1.  inbox layout on every rank: [world][cap][W + 1] floats.
-// pos_out[n]: position inside the (dst, src) segment (needed to route gradients back).
+// pos_out[n]: position inside the (dst, src) segment (needed to route gradients back).  Only the first
+// *count_ptr rows are sent (device-side count; nullptr: all n).  Slots are claimed once per warp and
+// destination (lanes that share a destination are grouped with a match), not once per row.
 __global__ void __launch_bounds__(256)
-a2a_dispatch_kernel(const float* __restrict__ payload, const int* __restrict__ dst, long long n, int W, A2APeers inbox,
-                    int src_rank, long long cap, int* __restrict__ counts, int* __restrict__ pos_out, int* overflow) {
+a2a_dispatch_kernel(const float* __restrict__ payload, const int* __restrict__ dst, const int* __restrict__ count_ptr, long long n,
+                    int W, A2APeers inbox, int src_rank, int world, long long cap, int* __restrict__ counts,
+                    int* __restrict__ pos_out, int* overflow) {
+  const long long n_valid = resolve_count(count_ptr, n);
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const int d = dst[i];
-  if (d < 0) { pos_out[i] = -1; return; }
-  const int pos = atomicAdd(&counts[d], 1);
-  if (pos >= cap) { pos_out[i] = -1; atomicExch(overflow, 1); return; }
-  pos_out[i] = pos;
+  const int lane = threadIdx.x & 31;
+  int d = -1;
+  if (i < n_valid) { d = dst[i]; if (d >= world) d = -1; }
+  const unsigned peers = __match_any_sync(0xffffffffu, d);        // lanes with the same destination
+  int pos = -1;
+  if (d >= 0) {
+    const int leader = __ffs(peers) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(&counts[d], __popc(peers));
+    base = __shfl_sync(peers, base, leader);
+    pos = base + __popc(peers & ((1u << lane) - 1u));
+    if (pos >= cap) { pos = -1; atomicExch(overflow, 1); }
+  }
+  if (i < n) pos_out[i] = pos;
+  if (pos < 0) return;
   float* rec = reinterpret_cast<float*>(inbox.p[d]) + ((long long)src_rank * cap + pos) * (W + 1);
   for (int k = 0; k < W; ++k) rec[k] = payload[i * W + k];
   rec[W] = __int_as_float((int)i);
@@ -46,39 +59,44 @@ __global__ void a2a_publish_kernel(const int* __restrict__ counts, A2APeers inco
   reinterpret_cast<int*>(incoming.p[d])[src_rank] = c < cap ? c : (int)cap;
 }
 
-// Compact the inbox segments: offsets[s] = exclusive prefix of incoming[s]; out rows [M, W], route (src, slot).
+// Compact the inbox segments in source order: coords [M, 4] = (payload xyz, block id 0), extra [M, W - 3] = the
+// remaining payload columns (may be null), route (src, slot); *total = M = sum of incoming.
 __global__ void __launch_bounds__(256)
 a2a_collect_kernel(const float* __restrict__ inbox, const int* __restrict__ incoming, int world, long long cap, int W,
-                   float* __restrict__ rows, int* __restrict__ route_src, int* __restrict__ route_slot) {
+                   float4* __restrict__ coords, float* __restrict__ extra, int* __restrict__ route_src,
+                   int* __restrict__ route_slot, int* __restrict__ total) {
   long long base = 0;
+  const int E = W - 3;
   for (int s = 0; s < world; ++s) {
     const int c = incoming[s];
     for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < c; k += (long long)gridDim.x * blockDim.x) {
       const float* rec = inbox + ((long long)s * cap + k) * (W + 1);
-      for (int j = 0; j < W; ++j) rows[(base + k) * W + j] = rec[j];
+      coords[base + k] = make_float4(rec[0], rec[1], rec[2], 0.f);
+      for (int j = 0; j < E; ++j) extra[(base + k) * E + j] = rec[3 + j];
       route_src[base + k] = s;
       route_slot[base + k] = __float_as_int(rec[W]);
     }
     base += c;
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0) *total = (int)base;
 }
 
 // values: [M, V]; written to outs[src] + slot * V
 __global__ void __launch_bounds__(256)
 a2a_combine_kernel(const float* __restrict__ values, const int* __restrict__ route_src, const int* __restrict__ route_slot,
-                   long long m, int V, A2APeers outs) {
+                   const int* __restrict__ count_ptr, long long m, int V, A2APeers outs) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= m) return;
+  if (i >= resolve_count(count_ptr, m)) return;
   float* o = reinterpret_cast<float*>(outs.p[route_src[i]]) + (long long)route_slot[i] * V;
   for (int k = 0; k < V; ++k) o[k] = values[i * V + k];
 }
 
 // Backward of combine: a source sends d_out[i, :V] to the owner's gradient inbox at (src, pos[i]).
 __global__ void __launch_bounds__(256)
-a2a_grad_dispatch_kernel(const float* __restrict__ dout, const int* __restrict__ dst, const int* __restrict__ pos, long long n,
-                         int V, A2APeers ginbox, int src_rank, long long cap) {
+a2a_grad_dispatch_kernel(const float* __restrict__ dout, const int* __restrict__ dst, const int* __restrict__ pos,
+                         const int* __restrict__ count_ptr, long long n, int V, A2APeers ginbox, int src_rank, long long cap) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  if (i >= resolve_count(count_ptr, n)) return;
   const int d = dst[i], p = pos[i];
   if (d < 0 || p < 0) return;
   float* rec = reinterpret_cast<float*>(ginbox.p[d]) + ((long long)src_rank * cap + p) * V;
@@ -107,43 +125,48 @@ static void fill(A2APeers& dst, const long long* table, int world) {
   for (int i = 0; i < kA2AMaxPeers; ++i) dst.p[i] = i < world ? (void*)table[i] : nullptr;
 }
 
-LMB_API int lmb_a2a_dispatch(const float* payload, const int* dst, long long n, int W, const long long* inbox_table,
-                             const long long* incoming_table, int rank, int world, long long cap, int* counts, int* pos_out,
-                             int* overflow, cudaStream_t stream) {
+LMB_API int lmb_a2a_dispatch(const float* payload, const int* dst, const int* count_ptr, long long n, int W,
+                             const long long* inbox_table, const long long* incoming_table, int rank, int world, long long cap,
+                             int* counts, int* pos_out, int* overflow, cudaStream_t stream) {
   if (world > kA2AMaxPeers) return (int)cudaErrorInvalidValue;
   A2APeers inbox, incoming;
   fill(inbox, inbox_table, world);
   fill(incoming, incoming_table, world);
   LMB_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * world, stream));
-  if (n > 0) a2a_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(payload, dst, n, W, inbox, rank, cap, counts, pos_out, overflow);
+  if (n > 0)
+    a2a_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(payload, dst, count_ptr, n, W, inbox, rank, world, cap, counts,
+                                                             pos_out, overflow);
   a2a_publish_kernel<<<1, 32, 0, stream>>>(counts, incoming, rank, world, cap);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
-LMB_API int lmb_a2a_collect(const float* inbox, const int* incoming, int world, long long cap, int W, float* rows,
-                            int* route_src, int* route_slot, cudaStream_t stream) {
-  a2a_collect_kernel<<<148 * 4, 256, 0, stream>>>(inbox, incoming, world, cap, W, rows, route_src, route_slot);
+// coords: [world * cap, 4]; extra: [world * cap, W - 3] or null when W == 3; total: device int
+LMB_API int lmb_a2a_collect(const float* inbox, const int* incoming, int world, long long cap, int W, float* coords, float* extra,
+                            int* route_src, int* route_slot, int* total, cudaStream_t stream) {
+  if (W < 3 || (W > 3 && extra == nullptr)) return (int)cudaErrorInvalidValue;
+  a2a_collect_kernel<<<148 * 4, 256, 0, stream>>>(inbox, incoming, world, cap, W, (float4*)coords, extra, route_src, route_slot,
+                                                  total);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
-LMB_API int lmb_a2a_combine(const float* values, const int* route_src, const int* route_slot, long long m, int V,
-                            const long long* out_table, int world, cudaStream_t stream) {
+LMB_API int lmb_a2a_combine(const float* values, const int* route_src, const int* route_slot, const int* count_ptr, long long m,
+                            int V, const long long* out_table, int world, cudaStream_t stream) {
   if (m <= 0) return 0;
   A2APeers outs;
   fill(outs, out_table, world);
-  a2a_combine_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(values, route_src, route_slot, m, V, outs);
+  a2a_combine_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(values, route_src, route_slot, count_ptr, m, V, outs);
   LMB_LAUNCH_CHECK();
   return 0;
 }
 
-LMB_API int lmb_a2a_grad_dispatch(const float* dout, const int* dst, const int* pos, long long n, int V,
+LMB_API int lmb_a2a_grad_dispatch(const float* dout, const int* dst, const int* pos, const int* count_ptr, long long n, int V,
                                   const long long* ginbox_table, int rank, int world, long long cap, cudaStream_t stream) {
   if (n <= 0) return 0;
   A2APeers g;
   fill(g, ginbox_table, world);
-  a2a_grad_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(dout, dst, pos, n, V, g, rank, cap);
+  a2a_grad_dispatch_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(dout, dst, pos, count_ptr, n, V, g, rank, cap);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -30,16 +30,32 @@ compact_kernel(const unsigned char* __restrict__ mask, long long n, const float4
   }
 }
 
-// x[j, col .. col+2] = dirs[idx[j] / S] (bf16 rows of width x_stride) for the first *count rows
+// x[j, col .. col+2] = dirs[idx[j] / S] (idx null: dirs[j]) as bf16, rows of width x_stride, first *count rows
 __global__ void __launch_bounds__(256)
 put_dirs_kernel(__nv_bfloat16* __restrict__ x, int x_stride, int col, const float* __restrict__ dirs, const int* __restrict__ idx,
                 const int* __restrict__ count_ptr, long long max_n, int S) {
   const long long n = resolve_count(count_ptr, max_n);
   const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= n) return;
-  const float* d = dirs + (long long)(idx[j] / S) * 3;
+  const float* d = dirs + (idx != nullptr ? (long long)(idx[j] / S) : j) * 3;
   __nv_bfloat16* o = x + j * x_stride + col;
   o[0] = __float2bfloat16_rn(d[0]); o[1] = __float2bfloat16_rn(d[1]); o[2] = __float2bfloat16_rn(d[2]);
+}
+
+// payload[j] = (coords[j].xyz, dirs[idx[j] / S]), owner[j] = (int)coords[j].w for the first *count rows: the rows a
+// rank sends to the owners of the blocks its colour samples fall into
+__global__ void __launch_bounds__(256)
+build_payload6_kernel(const float4* __restrict__ coords, const float* __restrict__ dirs, const int* __restrict__ idx,
+                      const int* __restrict__ count_ptr, long long max_n, int S, float* __restrict__ payload,
+                      int* __restrict__ owner) {
+  const long long n = resolve_count(count_ptr, max_n);
+  const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const float4 c = coords[j];
+  const float* d = dirs + (long long)(idx[j] / S) * 3;
+  float* o = payload + j * 6;
+  o[0] = c.x; o[1] = c.y; o[2] = c.z; o[3] = d[0]; o[4] = d[1]; o[5] = d[2];
+  owner[j] = (int)c.w;
 }
 
 // kScatter: out[idx[j], :] = vals[j, :] (rows whose block id coords[j].w < 0 contribute zeros; out is pre-zeroed)
@@ -97,6 +113,15 @@ LMB_API int lmb_gather_rows3(const float* full, const int* idx, const float* coo
   if (max_n <= 0) return 0;
   rows3_kernel<false><<<ceil_div(max_n, 256), 256, 0, stream>>>(vals, idx, (const float4*)coords, count_ptr, max_n,
                                                                const_cast<float*>(full));
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_build_payload6(const float* coords, const float* dirs, const int* idx, const int* count_ptr, long long max_n,
+                               int S, float* payload, int* owner, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  build_payload6_kernel<<<ceil_div(max_n, 256), 256, 0, stream>>>((const float4*)coords, dirs, idx, count_ptr, max_n, S, payload,
+                                                                 owner);
   LMB_LAUNCH_CHECK();
   return 0;
 }

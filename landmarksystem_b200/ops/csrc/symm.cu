@@ -21,9 +21,14 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 
 // flags_local[p] is written by peer p.  peer_flags[p] points at peer p's flag array.
 // One block: thread p signals peer p then waits for peer p's signal.
-__global__ void barrier_kernel(unsigned* flags_local, unsigned* const* peer_flags, int rank, int world, unsigned epoch,
+// The epoch lives in device memory (*epoch_dev counts the barriers this rank has passed), so the same
+// launch can be replayed from a CUDA graph; every rank runs the same sequence of barriers.
+__global__ void barrier_kernel(unsigned* flags_local, unsigned* const* peer_flags, int rank, int world, unsigned* epoch_dev,
                                long long limit_cycles, int* status) {
   const int p = threadIdx.x;
+  const unsigned epoch = *epoch_dev + 1u;
+  __syncthreads();
+  if (p == 0) *epoch_dev = epoch;
   if (p >= world) return;
   __threadfence_system();
   st_release_sys(peer_flags[p] + rank, epoch);
@@ -72,10 +77,10 @@ LMB_API int lmb_ipc_close(void* p) {
 }
 
 // Device-side barrier over `world` ranks on `stream`.  status: device int, non-zero if a wait expired.
-LMB_API int lmb_peer_barrier(unsigned* flags_local, unsigned* const* peer_flags, int rank, int world, unsigned epoch,
+LMB_API int lmb_peer_barrier(unsigned* flags_local, unsigned* const* peer_flags, int rank, int world, unsigned* epoch_dev,
                              int* status, cudaStream_t stream) {
   if (world > 32) return (int)cudaErrorInvalidValue;
-  barrier_kernel<<<1, 32, 0, stream>>>(flags_local, peer_flags, rank, world, epoch, 2000000000LL, status);
+  barrier_kernel<<<1, 32, 0, stream>>>(flags_local, peer_flags, rank, world, epoch_dev, 2000000000LL, status);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -1,8 +1,8 @@
 """Spatial-block all-to-all over peer memory (north-star path "b").
 
 ``BlockDispatcher.query(payload, owner, fn, out_width)`` sends each row of ``payload`` to the rank that
-owns it, runs ``fn`` there on the compacted rows (a differentiable PyTorch callable - grid lookup +
-MLP head), and returns the results in the caller's row order.  Gradients w.r.t. the results travel the
+owns it, runs ``fn`` there on the compacted rows (a differentiable callable - grid lookup + head - that
+honours a device-side row count), and returns the results in the caller's row order.  Gradients w.r.t. the results travel the
 reverse route and ``fn``'s backward runs on the owner, so grid gradients stay local to the owner.
 CPU / single-rank calls degenerate to ``fn(payload)``.
 """
@@ -20,15 +20,19 @@ from ..ops import native
 from .zero_adam import _table
 
 P = native.P
-native.register_signature("lmb_a2a_dispatch", [P, P, c_longlong, c_int, P, P, c_int, c_int, c_longlong, P, P, P, P])
-native.register_signature("lmb_a2a_collect", [P, P, c_int, c_longlong, c_int, P, P, P, P])
-native.register_signature("lmb_a2a_combine", [P, P, P, c_longlong, c_int, P, c_int, P])
-native.register_signature("lmb_a2a_grad_dispatch", [P, P, P, c_longlong, c_int, P, c_int, c_int, c_longlong, P])
+native.register_signature("lmb_a2a_dispatch", [P, P, P, c_longlong, c_int, P, P, c_int, c_int, c_longlong, P, P, P, P])
+native.register_signature("lmb_a2a_collect", [P, P, c_int, c_longlong, c_int, P, P, P, P, P, P])
+native.register_signature("lmb_a2a_combine", [P, P, P, P, c_longlong, c_int, P, c_int, P])
+native.register_signature("lmb_a2a_grad_dispatch", [P, P, P, P, c_longlong, c_int, P, c_int, c_int, c_longlong, P])
 native.register_signature("lmb_a2a_grad_collect", [P, P, c_int, c_longlong, c_int, P, P])
 
 
 class BlockDispatcher:
-    """``cap`` = max rows one source may send to one owner; ``max_w`` / ``max_v`` = widest payload / result."""
+    """``cap`` = max rows one source may send to one owner; ``max_w`` / ``max_v`` = widest payload / result.
+
+    Nothing on the host ever learns a row count: the owner-side buffers have the static worst-case size
+    ``world * cap`` and every consumer takes the device-side count, so a query is a fixed sequence of
+    launches (and can be recorded in a CUDA graph together with the rest of the step)."""
 
     def __init__(self, cap: int, max_w: int = 8, max_v: int = 4, group=None):
         self.group = group
@@ -52,9 +56,18 @@ class BlockDispatcher:
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier = PeerBarrier(group)
 
-    def query(self, payload: torch.Tensor, owner: torch.Tensor, fn: Callable[[torch.Tensor], torch.Tensor],
-              out_width: int) -> torch.Tensor:
-        return _Query.apply(payload, owner, self, fn, out_width, *_fn_params(fn))
+    @property
+    def owner_rows(self) -> int:
+        """Static row capacity of the owner-side tensors handed to ``fn``."""
+        return self.world * self.cap
+
+    def query(self, payload: torch.Tensor, owner: torch.Tensor, fn: Callable, out_width: int,
+              count: torch.Tensor = None) -> torch.Tensor:
+        """``payload [n, W]`` (first three columns: block-local xyz), ``owner [n]`` (rank or -1); only the first
+        ``count`` rows (device int, ``None`` = all) are sent.  ``fn(coords [M_cap, 4], extra [M_cap, W-3] or None,
+        m)`` runs on the owner with ``m`` a device int and must return ``[M_cap, out_width]`` whose first ``m`` rows
+        are valid; its backward must only read the first ``m`` gradient rows."""
+        return _Query.apply(payload, owner, count, self, fn, out_width, *_fn_params(fn))
 
 
 def _fn_params(fn):
@@ -64,37 +77,39 @@ def _fn_params(fn):
 
 class _Query(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, payload, owner, disp: BlockDispatcher, fn, out_width, *params):
+    def forward(ctx, payload, owner, count, disp: BlockDispatcher, fn, out_width, *params):
         lib, st = native.lib(), native.stream_ptr()
         n, W = payload.shape
-        assert W <= disp.max_w and out_width <= disp.max_v and n <= disp.cap
+        assert 3 <= W <= disp.max_w and out_width <= disp.max_v and n <= disp.cap
         payload = payload.contiguous().float()
         owner = owner.to(torch.int32).contiguous()
-        pos = torch.empty(n, dtype=torch.int32, device=payload.device)
+        dev = payload.device
+        pos = torch.empty(n, dtype=torch.int32, device=dev)
         disp.barrier()                                           # previous round's buffers are free again
-        native.check(lib.lmb_a2a_dispatch(payload.data_ptr(), owner.data_ptr(), n, W, disp.inbox_table, disp.incoming_table,
-                                          disp.rank, disp.world, disp.cap, disp.counts.data_ptr(), pos.data_ptr(),
-                                          disp.overflow.data_ptr(), st), "a2a_dispatch")
+        native.check(lib.lmb_a2a_dispatch(payload.data_ptr(), owner.data_ptr(), native.ptr(count), n, W, disp.inbox_table,
+                                          disp.incoming_table, disp.rank, disp.world, disp.cap, disp.counts.data_ptr(),
+                                          pos.data_ptr(), disp.overflow.data_ptr(), st), "a2a_dispatch")
         disp.barrier()                                           # records and counts have landed everywhere
         incoming = disp.incoming.clone()
-        m = int(incoming.sum().item())                           # one small D2H read per round
-        rows = torch.empty(max(m, 1), W, device=payload.device)
-        route_src = torch.empty(max(m, 1), dtype=torch.int32, device=payload.device)
-        route_slot = torch.empty(max(m, 1), dtype=torch.int32, device=payload.device)
+        M = disp.owner_rows
+        coords = torch.empty(M, 4, device=dev)
+        extra = torch.empty(M, W - 3, device=dev) if W > 3 else None
+        route_src = torch.empty(M, dtype=torch.int32, device=dev)
+        route_slot = torch.empty(M, dtype=torch.int32, device=dev)
+        m_dev = torch.empty(1, dtype=torch.int32, device=dev)
         inbox = disp.buf.local_ptr + disp.off_inbox
-        native.check(lib.lmb_a2a_collect(inbox, incoming.data_ptr(), disp.world, disp.cap, W, rows.data_ptr(),
-                                         route_src.data_ptr(), route_slot.data_ptr(), st), "a2a_collect")
-        rows = rows[:m]
+        native.check(lib.lmb_a2a_collect(inbox, incoming.data_ptr(), disp.world, disp.cap, W, coords.data_ptr(),
+                                         native.ptr(extra), route_src.data_ptr(), route_slot.data_ptr(), m_dev.data_ptr(), st),
+                     "a2a_collect")
         with torch.enable_grad():
-            rows_in = rows.detach()
-            values = fn(rows_in).float().reshape(m, out_width)
+            values = fn(coords, extra, m_dev).float().reshape(M, out_width)
         out = disp.buf.view(disp.off_out, (n, out_width), torch.float32)
         out.zero_()
         disp.barrier()                                           # everybody zeroed its output buffer
         native.check(lib.lmb_a2a_combine(values.detach().contiguous().data_ptr(), route_src.data_ptr(), route_slot.data_ptr(),
-                                         m, out_width, disp.out_table, disp.world, st), "a2a_combine")
+                                         m_dev.data_ptr(), M, out_width, disp.out_table, disp.world, st), "a2a_combine")
         disp.barrier()                                           # all results are in place
-        ctx.disp, ctx.values, ctx.m, ctx.V, ctx.n = disp, values, m, out_width, n
+        ctx.disp, ctx.values, ctx.V, ctx.n, ctx.count = disp, values, out_width, n, count
         ctx.save_for_backward(owner, pos, incoming)
         ctx.n_params = len(params)
         return out.clone()
@@ -103,15 +118,15 @@ class _Query(torch.autograd.Function):
     def backward(ctx, dout):
         owner, pos, incoming = ctx.saved_tensors
         disp, lib, st = ctx.disp, native.lib(), native.stream_ptr()
-        V, m, n = ctx.V, ctx.m, ctx.n
+        V, n = ctx.V, ctx.n
         dout = dout.contiguous().float()
         disp.barrier()
-        native.check(lib.lmb_a2a_grad_dispatch(dout.data_ptr(), owner.data_ptr(), pos.data_ptr(), n, V, disp.ginbox_table,
-                                               disp.rank, disp.world, disp.cap, st), "a2a_grad_dispatch")
+        native.check(lib.lmb_a2a_grad_dispatch(dout.data_ptr(), owner.data_ptr(), pos.data_ptr(), native.ptr(ctx.count), n, V,
+                                               disp.ginbox_table, disp.rank, disp.world, disp.cap, st), "a2a_grad_dispatch")
         disp.barrier()
-        dvals = torch.empty(max(m, 1), V, device=dout.device)
+        dvals = torch.empty(disp.owner_rows, V, device=dout.device)
         native.check(lib.lmb_a2a_grad_collect(disp.buf.local_ptr + disp.off_ginbox, incoming.data_ptr(), disp.world,
                                               disp.cap, V, dvals.data_ptr(), st), "a2a_grad_collect")
-        if m > 0 and ctx.values.requires_grad:
-            ctx.values.backward(dvals[:m].view_as(ctx.values))    # owner-side backward: grads land in local params
-        return (None, None, None, None, None) + (None,) * ctx.n_params
+        if ctx.values.requires_grad:
+            ctx.values.backward(dvals.view_as(ctx.values))        # owner-side backward: grads land in local params
+        return (None, None, None, None, None, None) + (None,) * ctx.n_params

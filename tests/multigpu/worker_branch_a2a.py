@@ -82,6 +82,31 @@ def main():
     assert gerr < 1e-3, gerr
     a2a_model._a2a.barrier.check()
 
+    # the same exchange with the kernel path on the owner (tcgen05 colour head forward + backward, device-side
+    # row counts end to end: no host synchronisation inside the step), against the replicated PyTorch heads
+    fused_model, fcfg = build(division, "a2a")
+    fused_model.load_state_dict(ref_model.state_dict())
+    fcfg.fused_mlp_train = True
+    fused_model.rgb_decoder.use_fused = True
+    assert fused_model._fused_app_stage_ok(mine)
+    for p in ref_model.parameters():
+        p.grad = None
+    out_f = sample_free(fused_model, mine)
+    (((out_f - target) ** 2).mean()).backward()
+    for r in range(world):
+        (((sample_free(ref_model, rays_for(r)) - target) ** 2).mean()).backward()
+    ferr = (out_f.detach() - out_r).abs().max().item()
+    assert ferr < 3e-2, ferr
+    fgerr = 0.0
+    for (n1, p1), (n2, p2) in zip(fused_model.named_parameters(), ref_model.named_parameters()):
+        if "encoding" not in n1:
+            continue
+        fgerr = max(fgerr, float((p1.grad - p2.grad).norm() / (p2.grad.norm() + 1e-12)))
+    assert fgerr < 0.15, fgerr
+    fused_model.rgb_decoder._lmb_packed.check_status()
+    fused_model._a2a.barrier.check()
+    assert int(fused_model._a2a.overflow.item()) == 0
+
     # timing of a training-shaped forward+backward with 8192 rays x 128 samples per rank
     big = rays_for(rank, 8192)
     tgt = torch.rand(8192, 3, device="cuda")
@@ -104,6 +129,7 @@ def main():
         return float(ms)
 
     ms_a2a = timed(lambda: step(a2a_model, big))
+    ms_fused = timed(lambda: step(fused_model, big))
     allrays = torch.cat([rays_for(r, 8192) for r in range(world)])
     tgt_all = torch.rand(8192 * world, 3, device="cuda")
 
@@ -114,7 +140,8 @@ def main():
     ms_ref = timed(step_ref, iters=3)
     if rank == 0:
         print("BRANCH_A2A_RESULTS " + json.dumps({"world": world, "max_err": err, "grad_rel_err": gerr,
-              "a2a_ms_per_step": ms_a2a, "replicate_allreduce_ms_per_step": ms_ref,
+              "a2a_ms_per_step": ms_a2a, "a2a_kernel_path_ms_per_step": ms_fused, "kernel_path_max_err": ferr,
+              "kernel_path_grad_rel_err": fgerr, "replicate_allreduce_ms_per_step": ms_ref,
               "rays_per_step": 8192 * world}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
