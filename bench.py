@@ -131,6 +131,8 @@ def run_ours(args):
     cfg.branch_parallel = n > 1
     cfg.branch_dispatch = "a2a"      # every rank brings its own rays; samples travel to the block's owner
     cfg.batch_size = RAYS_PER_GPU * n
+    if os.environ.get("LMB_CUDA_GRAPH") is not None:          # debugging switch: 0 runs every step eagerly
+        cfg.cuda_graph = os.environ["LMB_CUDA_GRAPH"] not in ("0", "false", "")
     trainer = GridNeRFTrainer(cfg)
     trainer.model.train()
     dev = trainer.config.device

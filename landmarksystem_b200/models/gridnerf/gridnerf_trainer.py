@@ -75,7 +75,8 @@ class GridNeRFTrainer(NeRFTrainer):
             model = ComponentConvertorFactory.get_convertor("runtime").convert(model, cfg)
         self.model = self.module = model
         # replicated parameters are synchronised explicitly between backward and the optimiser step
-        self.mp_sync = GradSynchronizer(cfg.mp_group, average=False) if cfg.branch_parallel else None
+        on_gpu = torch.device(cfg.device).type == "cuda"
+        self.mp_sync = GradSynchronizer(cfg.mp_group, average=False, p2p_small=on_gpu) if cfg.branch_parallel else None
         self.dp_sync = GradSynchronizer(cfg.dp_group if cfg.model_parallel else None, average=True) if cfg.DDP else None
         return model
 
@@ -203,9 +204,19 @@ class GridNeRFTrainer(NeRFTrainer):
 
     def _graph_ok(self, rays) -> bool:
         cfg = self.config
-        return bool(cfg.get("cuda_graph", False)) and rays.is_cuda and isinstance(self.optimizer, FusedAdam) \
-            and self.optimizer.capturable and self.mp_sync is None and self.dp_sync is None \
-            and not (cfg.branch_parallel or cfg.channel_parallel or cfg.DDP) and not self.timer.enabled
+        if not (bool(cfg.get("cuda_graph", False)) and rays.is_cuda and isinstance(self.optimizer, FusedAdam)
+                and self.optimizer.capturable and self.dp_sync is None and not cfg.channel_parallel and not cfg.DDP
+                and not self.timer.enabled):
+            return False
+        if cfg.branch_parallel:
+            # spatial-block model parallelism is graph-safe only on the all-to-all path with kernel-path owner
+            # functions (device-side row counts); every rank records and replays the same sequence of launches,
+            # peer barriers and the NCCL all-reduce of the replicated heads included
+            m = self.module
+            return cfg.get("branch_dispatch") == "a2a" and m._use_a2a() and torch.is_grad_enabled() \
+                and m._fused_app_stage_ok(rays) and m.density_encoding.fused_density_ok(rays) \
+                and bool(cfg.get("fused_density", True))
+        return self.mp_sync is None
 
     def _train_step_graphed(self, rays, rgbs, idxs):
         """Inputs are copied into fixed buffers; the first steps run eagerly (allocator and lazily built state
@@ -228,7 +239,8 @@ class GridNeRFTrainer(NeRFTrainer):
 
             graph = torch.cuda.CUDAGraph()
             launches0 = native.LAUNCH_CALLS
-            with torch.cuda.graph(graph):
+            # thread-local: a process group's watchdog thread may touch the CUDA runtime while this thread records
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 st["loss"] = self._train_step_eager(st["rays"], st["rgbs"], st["idxs"])
             st["graph"], st["launches"] = graph, native.LAUNCH_CALLS - launches0   # library kernels recorded in the graph
             graph.replay()          # capture records without executing; the host-side counters advanced once above

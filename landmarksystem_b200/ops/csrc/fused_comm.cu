@@ -139,6 +139,22 @@ composite_merge_p2p_kernel(PeerPtrs partials, PeerPtrs outs, int world, int rank
   }
 }
 
+// Small all-reduce over peer memory: every rank has copied its values into its staging buffer; each rank
+// sums all staging buffers (plain peer loads, rank order fixed so every rank gets bit-identical sums).
+// Used for the gradients of replicated heads (tens of thousands of floats), where a library collective is
+// all launch latency and cannot be recorded alongside the peer barriers of the same step.
+__global__ void __launch_bounds__(256)
+allreduce_small_kernel(PeerPtrs staging, int world, long long n4, float4* __restrict__ out, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = reinterpret_cast<const float4*>(staging.p[r])[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+  }
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -195,6 +211,22 @@ LMB_API int lmb_composite_merge_p2p(const long long* partial_table, const long l
   const long long begin = per * rank, end = begin + per < n_rays ? begin + per : n_rays;
   if (end <= begin) return 0;
   composite_merge_p2p_kernel<<<ceil_div(end - begin, 256), 256, 0, stream>>>(part, out, world, rank, root, begin, end, bg);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// staging_table: per-rank staging buffer addresses (n floats each, n a multiple of 4); out: local fp32 [n].
+// The caller brackets the launch with peer barriers (staging written everywhere before; nobody overwrites its
+// staging buffer until every rank has read it).
+LMB_API int lmb_allreduce_small_p2p(const long long* staging_table, int world, long long n, float* out, float scale,
+                                    cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 4 || world > kMaxPeers) return (int)cudaErrorInvalidValue;
+  PeerPtrs st;
+  for (int i = 0; i < kMaxPeers; ++i) st.p[i] = i < world ? (void*)staging_table[i] : nullptr;
+  const long long n4 = n / 4;
+  const int blocks = (int)((n4 + 255) / 256 < 148 * 4 ? (n4 + 255) / 256 : 148 * 4);
+  allreduce_small_kernel<<<blocks, 256, 0, stream>>>(st, world, n4, (float4*)out, scale);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -21,9 +21,49 @@ def _grad_of(p: torch.Tensor):
     return sink if sink is not None else p.grad
 
 
+class _P2PSmallAllReduce:
+    """All-reduce of a flat fp32 vector through peer-mapped staging buffers: copy in, peer barrier, every rank
+    sums all staging buffers with plain peer loads, peer barrier.  No library collective is involved, so the
+    call is a fixed sequence of kernel launches that can be recorded in a CUDA graph."""
+
+    def __init__(self, capacity: int, group=None):
+        from ctypes import c_float, c_int, c_longlong
+
+        from ..comm.symmetric import PeerBarrier, SymmetricBuffer
+        from ..ops import native
+        from .zero_adam import _table
+
+        native.register_signature("lmb_allreduce_small_p2p", [native.P, c_int, c_longlong, native.P, c_float, native.P])
+        self.capacity = (capacity + 3) // 4 * 4
+        self.buf = SymmetricBuffer(self.capacity * 4, group)
+        self.table = _table(self.buf.peer_table(0))
+        self.staging = self.buf.view(0, (self.capacity,), torch.float32)
+        self.barrier = PeerBarrier(group)
+        self.native = native
+
+    def __call__(self, flat: torch.Tensor, scale: float) -> torch.Tensor:
+        n = flat.numel()
+        n4 = (n + 3) // 4 * 4
+        assert n4 <= self.capacity
+        self.barrier()                       # peers have finished reading the previous contents
+        self.staging[:n].copy_(flat)
+        if n4 > n:
+            self.staging[n:n4].zero_()
+        self.barrier()                       # every rank's staging buffer is complete
+        out = torch.empty(n4, device=flat.device, dtype=torch.float32)
+        self.native.check(self.native.lib().lmb_allreduce_small_p2p(self.table, self.buf.world, n4, out.data_ptr(), float(scale),
+                                                                  self.native.stream_ptr()), "allreduce_small_p2p")
+        return out[:n]
+
+
 class GradSynchronizer:
-    def __init__(self, group=None, average: bool = True, bucket_elems: int = 1 << 22):
+    """``p2p_small``: on CUDA, coalesced small gradients go through :class:`_P2PSmallAllReduce` instead of the
+    process group's collective (same result; graph-capturable, no library launch)."""
+
+    def __init__(self, group=None, average: bool = True, bucket_elems: int = 1 << 22, p2p_small: bool = False):
         self.group, self.average, self.bucket_elems = group, average, bucket_elems
+        self.p2p_small = p2p_small
+        self._p2p = None
 
     def world(self) -> int:
         return dist.get_world_size(self.group) if dist.is_initialized() else 1
@@ -49,9 +89,14 @@ class GradSynchronizer:
                 small.append(g)
         if small:
             flat = torch.cat([g.reshape(-1) for g in small])
-            dist.all_reduce(flat, group=self.group)
-            if self.average:
-                flat.div_(world)
+            if self.p2p_small and flat.is_cuda:
+                if self._p2p is None or self._p2p.capacity < flat.numel():
+                    self._p2p = _P2PSmallAllReduce(max(flat.numel(), 1 << 16), self.group)
+                flat = self._p2p(flat.float(), 1.0 / world if self.average else 1.0)
+            else:
+                dist.all_reduce(flat, group=self.group)
+                if self.average:
+                    flat.div_(world)
             off = 0
             for g in small:
                 g.copy_(flat[off:off + g.numel()].view_as(g))

@@ -113,6 +113,35 @@ def main():
 
     results["composite_merge_nccl_torch"] = {"ms": timed(nccl_merge, iters=5)}
 
+    # small all-reduce over peer staging buffers (gradients of replicated heads) vs the NCCL collective
+    from landmarksystem_b200.parallel.grad_sync import GradSynchronizer
+
+    shapes = [(128, 150), (128,), (128, 128), (3, 128), (27, 48), (1, 16), (5,)]
+    gg = torch.Generator(device="cuda").manual_seed(50 + rank)
+    params = []
+    for shp in shapes:
+        p = torch.nn.Parameter(torch.zeros(shp, device="cuda"))
+        p.grad = torch.randn(shp, device="cuda", generator=gg)
+        params.append(p)
+    want = []
+    for p in params:
+        t = p.grad.clone()
+        dist.all_reduce(t)
+        want.append(t)
+    sync = GradSynchronizer(None, average=False, p2p_small=True)
+    keep = [p.grad.clone() for p in params]
+
+    def p2p_sync():
+        for p, k in zip(params, keep):
+            p.grad.copy_(k)
+        sync.sync(params)
+
+    p2p_sync()
+    for p, t in zip(params, want):
+        assert torch.allclose(p.grad, t, atol=1e-5), (p.grad - t).abs().max()
+    sync._p2p.barrier.check()
+    results["allreduce_small_p2p"] = {"ms": timed(p2p_sync, iters=20), "floats": sum(p.numel() for p in params)}
+
     if rank == 0:
         print("FUSED_COMM_RESULTS " + json.dumps({"world": world, **results}), flush=True)
     dist.barrier()
