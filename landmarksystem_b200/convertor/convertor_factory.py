@@ -50,7 +50,7 @@ class ParallelConvertor(BaseConvertor):
             new = _reinstantiate(child, new_cls, parallel_degree=degree, parallel_part=part, group=group,
                                  init_state_dict=init_state)
             if getattr(child, "use_shadow", False):
-                new.enable_shadow(getattr(config, "fused_optimizer", True))
+                new.enable_shadow(getattr(config, "fused_optimizer", True), getattr(child, "lazy", False))
             setattr(model, name, new)
         return model
 
