@@ -90,7 +90,8 @@ def main():
     trans = torch.rand(R, device="cuda", generator=g)
     depth = torch.rand(R, device="cuda", generator=g)
     acc = 1 - trans
-    t_entry = torch.rand(R, device="cuda", generator=g) * 100
+    # entry distances are distinct across ranks for every ray (a tie would leave the composite order undefined)
+    t_entry = (torch.randint(0, 1 << 20, (R,), device="cuda", generator=g) * 8 + rank).float() * (100.0 / (1 << 23))
     empty = torch.rand(R, device="cuda", generator=g) < 0.3          # rays that miss this rank's blocks
     t_entry[empty] = float("inf")
     rgb[empty], trans[empty], depth[empty], acc[empty] = 0.0, 1.0, 0.0, 0.0
