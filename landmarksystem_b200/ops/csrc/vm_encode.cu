@@ -49,10 +49,12 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
                      VMLevels lv, OutT* __restrict__ out, int out_stride) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
-  long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // grid-stride: the grid is capped, so a launch sized for a worst-case row capacity costs nothing when
+  // the device-side count is small
+  for (long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x; tid < n_valid * CH;
+       tid += (long long)gridDim.x * blockDim.x) {
   long long n = tid / CH;
   int ch = (int)(tid - n * CH);
-  if (n >= n_valid) return;
   float4 q = __ldg(coords + n);
   int b = (int)q.w;
   if (b < 0 || b >= lv.B) {
@@ -60,7 +62,7 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 8; ++i) z.v[i] = 0.f;
     for (int l = 0; l < lv.L; ++l) store8(out + n * out_stride + l * lv.C + ch * 8, z);
-    return;
+    continue;
   }
   for (int l = 0; l < lv.L; ++l) {
     const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
@@ -83,6 +85,7 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
     }
     store8(out + n * out_stride + l * lv.C + ch * 8, f);
   }
+  }
 }
 
 // Backward: recompute the taps and both interpolants, then push d(plane) and d(line) with
@@ -93,13 +96,13 @@ vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
                      VMLevels lv, const GT* __restrict__ dout, int out_stride) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
-  long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x; tid < n_valid * CH;
+       tid += (long long)gridDim.x * blockDim.x) {
   long long n = tid / CH;
   int ch = (int)(tid - n * CH);
-  if (n >= n_valid) return;
   float4 q = __ldg(coords + n);
   int b = (int)q.w;
-  if (b < 0 || b >= lv.B) return;
+  if (b < 0 || b >= lv.B) continue;
   for (int l = 0; l < lv.L; ++l) {
     const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
     Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
@@ -132,6 +135,7 @@ vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
     if (w11 != 0.f) red_add8(gp + o11, dp, w11);
     if (cz.w0 != 0.f) red_add8(gl + (long long)cz.i0 * lv.C, dl, cz.w0);
     if (cz.w1 != 0.f) red_add8(gl + (long long)cz.i1 * lv.C, dl, cz.w1);
+  }
   }
 }
 
@@ -172,7 +176,9 @@ vm_density_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__
                       DensityHead head, float* __restrict__ sigma, float* __restrict__ pre) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // grid-stride with a trip count that is uniform per block (the shuffles below need whole warps)
+  for (long long base = (long long)blockIdx.x * blockDim.x; base < n_valid * CH; base += (long long)gridDim.x * blockDim.x) {
+  const long long tid = base + threadIdx.x;
   const long long n = tid / CH;
   const int ch = (int)(tid - n * CH);
   const bool live = n < n_valid;
@@ -197,6 +203,7 @@ vm_density_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__
     sigma[n] = head.act == 0 ? fmaxf(r, 0.f) : (x > 20.f ? x : log1pf(__expf(x)));
     pre[n] = acc;
   }
+  }
 }
 
 // dsigma [N] -> plane / line gradient accumulators (as vm_encode_bwd) and dw [L*C] (block-reduced, one
@@ -211,10 +218,11 @@ vm_density_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__
   for (int i = threadIdx.x; i < n_w; i += blockDim.x) dw_sh[i] = 0.f;
   __syncthreads();
   const long long n_valid = resolve_count(count_ptr, max_n);
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  for (long long base = (long long)blockIdx.x * blockDim.x; base < n_valid * CH; base += (long long)gridDim.x * blockDim.x) {
+  const long long tid = base + threadIdx.x;
   const long long n = tid / CH;
   const int ch = (int)(tid - n * CH);
-  const int lane = threadIdx.x & 31;
   bool live = n < n_valid;
   float4 q = make_float4(0.f, 0.f, 0.f, -1.f);
   float dz = 0.f;
@@ -267,6 +275,7 @@ vm_density_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__
       }
     }
   }
+  }
   if (head.w != nullptr && dw != nullptr) {
     __syncthreads();
     for (int i = threadIdx.x; i < n_w; i += blockDim.x)
@@ -278,6 +287,13 @@ vm_density_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__
 
 using namespace lmb;
 
+// enough blocks to fill the GPU several times over, never more than the work needs
+static int capped_grid(long long work_items, int threads) {
+  const long long want = (work_items + threads - 1) / threads;
+  const long long cap = 148LL * 64;
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
 // param_dtype / io_dtype: 0 = fp32, 1 = bf16.
 LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
                               int param_dtype, void* out, int out_dtype, int out_stride, cudaStream_t stream) {
@@ -285,7 +301,7 @@ LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long lo
   if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
   const int CH = levels->C / 8;
   const int threads = 256;
-  const int blocks = ceil_div(max_n * CH, threads);
+  const int blocks = capped_grid(max_n * CH, threads);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
 #define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out, out_stride > 0 ? out_stride : levels->L * levels->C)
   if (param_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
@@ -303,7 +319,7 @@ LMB_API int lmb_vm_encode_bwd(const float* coords, const int* count_ptr, long lo
   if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
   const int CH = levels->C / 8;
   const int threads = 256;
-  const int blocks = ceil_div(max_n * CH, threads);
+  const int blocks = capped_grid(max_n * CH, threads);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
 #define LAUNCH(T, G) vm_encode_bwd_kernel<T, G><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (const G*)dout, dout_stride > 0 ? dout_stride : levels->L * levels->C)
   if (param_dtype == 0 && dout_dtype == 0) LAUNCH(float, float);
@@ -327,7 +343,7 @@ LMB_API int lmb_vm_density_fwd(const float* coords, const int* count_ptr, long l
   if (max_n <= 0) return 0;
   if (!density_shape_ok(levels)) return (int)cudaErrorInvalidValue;
   const DensityHead head{w, inner_relu, act, shift};
-  const int blocks = ceil_div(max_n * (levels->C / 8), 256);
+  const int blocks = capped_grid(max_n * (levels->C / 8), 256);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
   if (param_dtype == 0) vm_density_fwd_kernel<float><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
   else vm_density_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
@@ -342,7 +358,7 @@ LMB_API int lmb_vm_density_bwd(const float* coords, const int* count_ptr, long l
   if (max_n <= 0) return 0;
   if (!density_shape_ok(levels)) return (int)cudaErrorInvalidValue;
   const DensityHead head{w, inner_relu, act, shift};
-  const int blocks = ceil_div(max_n * (levels->C / 8), 256);
+  const int blocks = capped_grid(max_n * (levels->C / 8), 256);
   const size_t smem = sizeof(float) * levels->L * levels->C;
   const float4* c4 = reinterpret_cast<const float4*>(coords);
   if (param_dtype == 0)
