@@ -49,6 +49,9 @@ class TrainConfig(ConfigClass):
 
     # additions of this framework
     dp_optimizer: Literal["p2p_zero", "nccl_allreduce"] = "p2p_zero"   # data-parallel gradient path on GPUs
+    heartbeat: bool = False      # multi-rank failure detection: heartbeats in the rendezvous store, checked every step
+    heartbeat_timeout: float = 30.0
+    async_ckpt_every: int = 0    # > 0: sharded asynchronous snapshot every N iterations (log dir / snapshots)
     cuda_graph: bool = False     # record the whole training step once in a CUDA graph and replay it (single-GPU fused path)
     profile: bool = False                                              # CUDA-event stage timers + NVTX ranges
 

@@ -281,6 +281,8 @@ class GridNeRFTrainer(NeRFTrainer):
         psnrs, t0 = [], time.time()
         for self.iteration in range(cfg.start_iters, cfg.n_iters):
             it = self.iteration
+            if getattr(self, "health", None) is not None:
+                self.health.guard(it)      # raises PeerFailure before any kernel of this step could wait for a dead rank
             rays_train, rgb_train, idxs_train = self.data_mgr.get_rays(it)
             if cfg.add_distort > 0 and it == cfg.add_distort:
                 self.enable_distort = True
@@ -312,10 +314,30 @@ class GridNeRFTrainer(NeRFTrainer):
             if it in cfg.upsamp_list:
                 self._upsample(self.n_voxel_list[cfg.upsamp_list.index(it)])
                 self.l1_weight = cfg.L1_weight_rest
+            every = int(cfg.get("async_ckpt_every", 0) or 0)
+            if every > 0 and (it + 1) % every == 0:
+                self.save_async(it + 1)
+        if getattr(self, "_async_ckpt", None) is not None:
+            self._async_ckpt.wait()
         self.save_ckpt(final=True)
         return psnrs
 
     # -- checkpoints -------------------------------------------------------------------------------
+    def save_async(self, step: int) -> str:
+        """Sharded snapshot (this rank's model and optimiser state, RNG) written off the training thread; the
+        device-to-host copies run on a side stream.  Resume with ``runtime.load_sharded(latest_checkpoint(...))``."""
+        from ...runtime import AsyncCheckpointer
+
+        cfg = self.config
+        if getattr(self, "_async_ckpt", None) is None:
+            self._async_ckpt = AsyncCheckpointer(os.path.join(self.logfolder, "snapshots"), keep_last=2)
+        for enc in (self.module.density_encoding, self.module.rgb_encoding):
+            if hasattr(enc, "flush_lazy"):
+                enc.flush_lazy()
+        state = {"model": self.module.state_dict(), "optimizer": self.optimizer.state_dict(), "iteration": step}
+        return self._async_ckpt.save_step(step, state, rank=int(cfg.rank), world=int(cfg.world_size),
+                                          meta={"expname": cfg.expname, "model": "GridNeRF"})
+
     def save_ckpt(self, final: bool = False):
         cfg = self.config
         if cfg.model_parallel:

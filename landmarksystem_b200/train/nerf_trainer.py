@@ -68,6 +68,13 @@ class NeRFTrainer:
             cfg.rank, cfg.world_size = ctx.get_global_rank(), ctx.get_world_size(CommMode.GLOBAL)
         else:
             cfg.rank, cfg.world_size = 0, 1
+        # failure detection: heartbeats through the job's key-value store, checked between steps
+        self.health = None
+        if cfg.get("heartbeat", False) and cfg.world_size > 1 and torch.distributed.is_initialized():
+            from ..runtime import HeartbeatMonitor
+
+            store = torch.distributed.distributed_c10d._get_default_store()
+            self.health = HeartbeatMonitor(store, cfg.rank, cfg.world_size, timeout=float(cfg.get("heartbeat_timeout", 30.0))).start()
         if want_cuda:
             cfg.local_rank = EnvSetting.LOCAL_RANK % torch.cuda.device_count()
             cfg.device = torch.device("cuda", cfg.local_rank)

@@ -131,3 +131,17 @@ def test_gpu_cuda_graph_training(tmp_path):
     tr.module.density_encoding.flush_lazy()
     assert int(plane._lmb_lazy.last_step.min()) == 60
     tr.module.rgb_decoder._lmb_packed.check_status()
+
+
+def test_cpu_async_snapshots(tmp_path):
+    from landmarksystem_b200.runtime import load_sharded
+    from landmarksystem_b200.runtime.checkpoint import latest_checkpoint
+
+    tr = _trainer(tmp_path, "cpu", n_iters="6", async_ckpt_every="3", N_vis="0")
+    tr.train()
+    snap = latest_checkpoint(os.path.join(tr.logfolder, "snapshots"))
+    assert snap is not None and snap.endswith("step-00000006")
+    got = load_sharded(snap)
+    assert got["state"]["iteration"] == 6 and got["meta"]["model"] == "GridNeRF"
+    for k, v in tr.module.state_dict().items():
+        assert torch.equal(got["state"]["model"][k], v.cpu()), k

@@ -1,0 +1,155 @@
+"""Failure detection (host-side heartbeats, no GPU involved) and sharded / asynchronous checkpoints."""
+import multiprocessing as mp
+import os
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from landmarksystem_b200.runtime import AsyncCheckpointer, HeartbeatMonitor, PeerFailure, StatusWords, load_sharded
+from landmarksystem_b200.runtime.checkpoint import latest_checkpoint
+
+
+def _store():
+    return dist.HashStore()
+
+
+def test_heartbeat_detects_silent_reported_and_departed_peers():
+    store = _store()
+    now = [1000.0]
+    a = HeartbeatMonitor(store, 0, 3, timeout=5.0, clock=lambda: now[0])
+    b = HeartbeatMonitor(store, 1, 3, timeout=5.0, clock=lambda: now[0])
+    with pytest.raises(PeerFailure) as e:
+        a.check()                                   # rank 2 never joined
+    assert e.value.rank == 2 and "never joined" in e.value.reason
+    c = HeartbeatMonitor(store, 2, 3, timeout=5.0, clock=lambda: now[0])
+    a.check()
+    now[0] += 3.0
+    a._publish(); b._publish()                      # rank 2 stays silent
+    a.check()
+    now[0] += 3.0
+    a._publish(); b._publish()
+    with pytest.raises(PeerFailure) as e:
+        a.check()
+    assert e.value.rank == 2 and "no heartbeat" in e.value.reason
+    c._publish()
+    a.check()
+    b.fail("RuntimeError: out of memory")
+    with pytest.raises(PeerFailure) as e:
+        a.check()
+    assert e.value.rank == 1 and "out of memory" in e.value.reason
+    b._state = "ok"; b._publish()
+    c.leave()
+    with pytest.raises(PeerFailure) as e:
+        a.check()
+    assert e.value.rank == 2 and "left" in e.value.reason
+
+
+def test_heartbeat_step_lag():
+    store = _store()
+    a = HeartbeatMonitor(store, 0, 2, max_step_lag=3)
+    b = HeartbeatMonitor(store, 1, 2, max_step_lag=3)
+    b.beat(10); b._publish()
+    a.guard(12)
+    with pytest.raises(PeerFailure) as e:
+        a.guard(14)
+    assert "stalled at step 10" in e.value.reason
+
+
+def _rank_main(rank, world, port, die_at, out):
+    store = dist.TCPStore("127.0.0.1", port, is_master=False, timeout=__import__("datetime").timedelta(seconds=30))
+    mon = HeartbeatMonitor(store, rank, world, interval=0.05, timeout=3.0).start()
+    store.set(f"ready/{rank}", "1")
+    store.wait([f"ready/{r}" for r in range(world)])   # everybody has published once
+    try:
+        for step in range(200):
+            if rank == 1 and step == die_at:
+                os._exit(17)                         # dies between steps without a word
+            mon.guard(step)
+            time.sleep(0.02)
+        out.put((rank, "finished"))
+    except PeerFailure as exc:
+        out.put((rank, f"peer {exc.rank}: {exc.reason}"))
+    finally:
+        mon.stop()
+
+
+def test_heartbeat_across_processes_when_a_rank_dies():
+    """Three host processes; rank 1 exits between steps.  The survivors notice through the store (no collective
+    is in flight) and leave their loops with a PeerFailure naming rank 1."""
+    import datetime
+
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = 29000 + os.getpid() % 900
+    # the key-value store lives outside the ranks (as with a launcher-hosted rendezvous store), so it survives them
+    master = dist.TCPStore("127.0.0.1", port, is_master=True, wait_for_workers=False, timeout=datetime.timedelta(seconds=30))
+    procs = [ctx.Process(target=_rank_main, args=(r, 3, port, 20, out)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = {}
+    deadline = time.time() + 120
+    while len(got) < 2 and time.time() < deadline:
+        if not out.empty():
+            r, msg = out.get()
+            got[r] = msg
+        else:
+            time.sleep(0.05)
+    for p in procs:
+        p.join(timeout=20)
+    assert procs[1].exitcode == 17
+    assert set(got) == {0, 2}, got
+    assert all("peer 1" in m and "no heartbeat" in m for m in got.values()), got
+    del master
+
+
+def test_status_words_poll():
+    words = StatusWords()
+    ok, bad = torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32)
+    words.register("barrier", ok)
+    words.register("fused_mlp", bad, lambda c: {2: "input tile wait expired"}.get(c, str(c)))
+    words.poll()
+    bad.fill_(2)
+    with pytest.raises(RuntimeError, match="fused_mlp: input tile wait expired"):
+        words.poll()
+
+
+def test_async_sharded_checkpoint_roundtrip(tmp_path):
+    ck = AsyncCheckpointer(str(tmp_path), keep_last=2)
+    state = {"model": {"w": torch.randn(4, 5), "nested": [torch.arange(3), {"b": torch.ones(2)}]}, "iteration": 7}
+    torch.manual_seed(123)
+    expect = None
+    for step in (10, 20, 30):
+        state["iteration"] = step
+        path = ck.save_step(step, state, meta={"expname": "t"})
+        if step == 30:
+            expect = torch.rand(3)                   # drawn right after the RNG state was captured
+    ck.wait()
+    assert sorted(os.listdir(tmp_path)) == ["step-00000020", "step-00000030"]      # oldest pruned, no temp dirs left
+    assert latest_checkpoint(str(tmp_path)) == path
+    got = load_sharded(path, restore_rng=True)
+    assert got["meta"]["step"] == 30 and got["meta"]["world"] == 1 and got["state"]["iteration"] == 30
+    assert torch.equal(got["state"]["model"]["w"], state["model"]["w"])
+    assert torch.equal(got["state"]["model"]["nested"][1]["b"], torch.ones(2))
+    assert torch.equal(torch.rand(3), expect)        # RNG stream continues where the checkpoint was taken
+
+
+def test_incomplete_checkpoint_is_ignored(tmp_path):
+    os.makedirs(tmp_path / "step-00000005")
+    (tmp_path / "step-00000005" / "meta.json").write_text("{}")
+    assert latest_checkpoint(str(tmp_path)) is None
+    with pytest.raises(FileNotFoundError):
+        load_sharded(str(tmp_path / "step-00000005"))
+
+
+@pytest.mark.gpu
+def test_async_checkpoint_from_device_is_a_snapshot(tmp_path):
+    """The device-to-host copies are ordered after the training stream at the time of save(): later updates of the
+    parameters do not leak into the checkpoint."""
+    ck = AsyncCheckpointer(str(tmp_path))
+    w = torch.full((1 << 22,), 1.0, device="cuda")
+    path = ck.save_step(1, {"w": w})
+    w.add_(1.0)
+    ck.wait()
+    assert float(load_sharded(path)["state"]["w"].max()) == 1.0
