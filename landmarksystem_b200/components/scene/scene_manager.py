@@ -27,6 +27,7 @@ class SceneManager:
         rng = getattr(config, "aabb_norm_range", None) or [-1.0, 1.0]
         self.aabb_norm_range = torch.tensor(rng, dtype=torch.float32, device=self.device)
         self.aabb_norm_size = float(rng[1] - rng[0])
+        self._norm_lo = float(rng[0])
         part = getattr(config, "plane_division", None) or [1, 1]
         self.block_partition = torch.tensor(list(part), dtype=torch.long, device=self.device)
         self._partition = (int(part[0]), int(part[1]))     # host copy: reading the tensor would synchronise

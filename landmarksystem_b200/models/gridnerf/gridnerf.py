@@ -114,6 +114,7 @@ class GridNeRFConfig(ConfigClass):
     branch_dispatch: Literal["allreduce", "a2a"] = "allreduce"   # a2a: every rank brings its own rays; samples
                                                   # travel to the GPU owning their block over NVLink peer memory
     fused_optimizer: bool = True
+    fused_sampler: bool = True                    # sampling + block assignment in one kernel on CUDA
     fused_density: bool = True                    # density lookup + head in one kernel on CUDA
     lazy_adam: bool = False                       # deferred (exact) Adam on the planes: visit touched texels only
 
@@ -462,25 +463,47 @@ class GridNeRF(BaseNeRF):
         """One sampling + density + weights + colour + composite pass over ``rays [R, 7]``."""
         cfg = self.config
         train = bool(cfg.is_train)
-        z = self.sampler.compute_z_vals(rays, n_samples if n_samples > 0 else self.sampler.num_samples, train, hull)
-        R, S = z.shape
-        origin, dirs = rays[:, :3], rays[:, 3:6]
-        xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
-        valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
-        if self.alphaMask is not None:
-            valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
+        S_req = n_samples if n_samples > 0 else self.sampler.num_samples
         a2a = self._use_a2a()
-        if a2a:
-            local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
-            owner = torch.where(valid, block, torch.full_like(block, -1.0))
-            xyzb = torch.cat((local, owner[:, None]), dim=-1)
-            disp = self._dispatcher(R * S)
-            sigma = disp.query(local, owner, GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+        mp_train = bool(getattr(cfg, "branch_parallel", False)) and train
+        fused_front = (rays.is_cuda and not hull and self.alphaMask is None and self.scene_manager is not None
+                       and bool(cfg.get("fused_sampler", True)) and (a2a or not mp_train) and not cfg.encode_app)
+        origin, dirs = rays[:, :3], rays[:, 3:6]
+        if fused_front:
+            # sampling, box test, block assignment and block-local coordinates in one kernel
+            from ...ops.sampler import uniform_sample_blocks
+
+            sm = self.scene_manager
+            jitter = torch.rand(rays.shape[0], device=rays.device) if train else None
+            z, dists, xyzb, valid = uniform_sample_blocks(
+                rays, S_req, self.aabb, float(self.sampler.near_far[0]), float(self.sampler.near_far[1]),
+                float(self.sampler.step_size), sm._norm_lo, sm.aabb_norm_size, sm._partition,
+                (sm.relative_block_idx_x, sm.relative_block_idx_y), tuple(sm.local_block_partition), jitter)
+            R, S = z.shape
+            if a2a:
+                disp = self._dispatcher(R * S)
+                sigma = disp.query(xyzb[:, :3], xyzb[:, 3], GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+            else:
+                self.sigma_batch = None
+                sigma = self._mp_sum(self._density(xyzb)).view(R, S)
         else:
-            xyzb = self._xyzb(xyz, valid)
-            self.sigma_batch = (xyzb[:, 3] >= 0).sum()
-            sigma = self._mp_sum(self._density(xyzb)).view(R, S)
-        dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
+            z = self.sampler.compute_z_vals(rays, S_req, train, hull)
+            R, S = z.shape
+            xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
+            valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
+            if self.alphaMask is not None:
+                valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
+            if a2a:
+                local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
+                owner = torch.where(valid, block, torch.full_like(block, -1.0))
+                xyzb = torch.cat((local, owner[:, None]), dim=-1)
+                disp = self._dispatcher(R * S)
+                sigma = disp.query(local, owner, GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+            else:
+                xyzb = self._xyzb(xyz, valid)
+                self.sigma_batch = (xyzb[:, 3] >= 0).sum()
+                sigma = self._mp_sum(self._density(xyzb)).view(R, S)
+            dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
         weight = self.renderer.get_weights(sigma, dists * cfg.distance_scale)
         app_mask = (weight > cfg.rayMarch_weight_thres).reshape(-1)
         rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)

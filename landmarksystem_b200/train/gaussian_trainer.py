@@ -85,9 +85,13 @@ class GaussianTrainerBase(NeRFTrainer):
         self.update_learning_rate()
         self.before_step(viewpoint_cam)
         image = self.model(viewpoint_cam)
-        Ll1 = l1_loss(image, gt_image)
-        loss = (1.0 - cfg.lambda_dssim) * Ll1 + cfg.lambda_dssim * (1.0 - ssim(image, gt_image)) \
-            + self.extra_loss(image, gt_image)
+        if image.is_cuda and image.dtype == torch.float32:
+            from ..ops.ssim import fused_l1_ssim      # both terms and their gradient from one kernel each way
+
+            Ll1, ssim_val = fused_l1_ssim(image, gt_image)
+        else:
+            Ll1, ssim_val = l1_loss(image, gt_image), ssim(image, gt_image)
+        loss = (1.0 - cfg.lambda_dssim) * Ll1 + cfg.lambda_dssim * (1.0 - ssim_val) + self.extra_loss(image, gt_image)
         loss.backward()
         with torch.no_grad():
             self.model.densification(self.optimizer, self.iteration)

@@ -212,3 +212,25 @@ def test_vm_density_matches_reference(nonlinear, act):
     assert torch.allclose(out[: n - 500], ref, atol=1e-5, rtol=1e-4)
     for g, w in zip(got, want):
         assert torch.allclose(g, w, atol=1e-4, rtol=1e-3), (g - w).abs().max()
+
+
+@pytest.mark.parametrize("shape", [(3, 37, 53), (3, 128, 200), (1, 16, 16)])
+def test_fused_l1_ssim_matches_conv_reference(shape):
+    from landmarksystem_b200.components.utils import loss_utils
+    from landmarksystem_b200.ops.ssim import fused_l1_ssim
+
+    torch.manual_seed(0)
+    img = torch.rand(*shape, device=DEV, requires_grad=True)
+    gt = (img.detach() + 0.2 * torch.randn(*shape, device=DEV)).clamp(0, 1)
+    l1, s = fused_l1_ssim(img, gt)
+    (0.8 * l1 + 0.2 * (1 - s)).backward()
+    got = img.grad.clone()
+    img.grad = None
+    # conv2d restatement on the CPU (the CUDA entry point of loss_utils.ssim dispatches to the fused kernel)
+    x = img.detach().cpu().double().requires_grad_()
+    g = gt.cpu().double()
+    l1_ref = (x - g).abs().mean()
+    s_ref = loss_utils.ssim(x, g)
+    (0.8 * l1_ref + 0.2 * (1 - s_ref)).backward()
+    assert abs(float(l1) - float(l1_ref)) < 1e-5 and abs(float(s) - float(s_ref)) < 1e-4
+    assert torch.allclose(got.cpu().double(), x.grad, atol=2e-6, rtol=1e-3), (got.cpu().double() - x.grad).abs().max()
