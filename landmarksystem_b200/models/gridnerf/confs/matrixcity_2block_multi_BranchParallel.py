@@ -1,0 +1,4 @@
+"""GridNeRF on MatrixCity block A: training variant ``multi_BranchParallel`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.gridnerf.confs._matrixcity import train
+
+config = train("multi_BranchParallel")

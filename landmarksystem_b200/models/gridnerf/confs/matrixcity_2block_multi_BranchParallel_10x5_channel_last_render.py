@@ -1,0 +1,4 @@
+"""GridNeRF on MatrixCity block A: render variant ``multi_BranchParallel_10x5_channel_last_render`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.gridnerf.confs._matrixcity import render
+
+config = render("multi_BranchParallel_10x5_channel_last_render")

@@ -1,0 +1,4 @@
+"""GridNeRF on MatrixCity block A: render variant ``multi_ChannelParallel_render`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.gridnerf.confs._matrixcity import render
+
+config = render("multi_ChannelParallel_render")

@@ -1,0 +1,4 @@
+"""InstantNGP on MatrixCity block A: render variant ``ddp_train_render`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.instant_ngp.confs._matrixcity import render
+
+config = render("ddp_train_render")

@@ -1,0 +1,4 @@
+"""InstantNGP on MatrixCity block A: training variant ``lowquality_BranchParallel`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.instant_ngp.confs._matrixcity import train
+
+config = train("lowquality_BranchParallel")

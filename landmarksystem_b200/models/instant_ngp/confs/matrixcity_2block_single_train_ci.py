@@ -1,0 +1,4 @@
+"""InstantNGP on MatrixCity block A: training variant ``single_train_ci`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.instant_ngp.confs._matrixcity import train
+
+config = train("single_train_ci")

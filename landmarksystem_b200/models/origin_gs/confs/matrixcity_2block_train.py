@@ -1,0 +1,4 @@
+"""vanilla 3D Gaussian splatting on MatrixCity block A: ``matrixcity_2block_train`` (see ``_matrixcity.py``)."""
+from landmarksystem_b200.models.origin_gs.confs._matrixcity import train
+
+config = train()

@@ -93,3 +93,27 @@ def test_dataset_config_checks():
         DatasetConfig(datadir="x", dynamic_load=True, dataset_type="nerf").check_args()
     with pytest.raises(AssertionError):
         TrainConfig(model_name="m", expname="e", n_iters=1, channel_parallel=True, branch_parallel=True).check_args()
+
+
+def test_every_shipped_configuration_loads():
+    """Each model family ships the MatrixCity train / render variants (single, DDP, branch / channel parallel and
+    the cross-layout render configurations); every file must parse into a merged, validated configuration."""
+    import glob
+    import os
+
+    from landmarksystem_b200.configs import BaseConfig
+
+    root = os.path.join(os.path.dirname(__file__), "..", "landmarksystem_b200", "models")
+    files = sorted(glob.glob(os.path.join(root, "*", "confs", "matrixcity_*.py")))
+    assert len(files) >= 60
+    seen = {}
+    for f in files:
+        cfg = BaseConfig.from_file(f, {})
+        seen[os.path.relpath(f, root)] = cfg
+        assert cfg.get("expname") and cfg.get("model_name")
+        if f.endswith("render.py"):
+            assert not cfg.is_train and cfg.get("ckpt")
+    bp = seen[os.path.join("gridnerf", "confs", "matrixcity_2block_multi_BranchParallel_10x5.py")]
+    assert bp.branch_parallel and list(bp.plane_division) == [10, 5] and bp.ub[0] > 50
+    b2c = seen[os.path.join("gridnerf", "confs", "matrixcity_2block_lowquality_Branch2ChannelParallel_render.py")]
+    assert b2c.channel_parallel and b2c.channel_parallel_size == 2 and not b2c.branch_parallel and b2c.sampling_opt
