@@ -17,7 +17,7 @@ class DatasetConfig(ConfigClass):
     partition: str = "all"
     datadir: str
     subfolder: Optional[list] = None
-    dataset_name: Literal["city", "matrixcity", "blender", "Colmap", "synthetic"] = "city"
+    dataset_name: Literal["city", "matrixcity", "blender", "Colmap", "colmap", "zhangjiang", "synthetic"] = "city"
     dataset_type: Literal["nerf", "gaussian"] = "nerf"
     use_preprocessed_data: bool = False
     processed_data_type: str = "file"

@@ -1,0 +1,107 @@
+"""COLMAP readers / datasets, pose helpers and ray-shard preprocessing (CPU)."""
+import math
+import os
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from landmarksystem_b200.components.data import pose_utils as pu
+from landmarksystem_b200.components.data.datasets import colmap_loader as cl
+from landmarksystem_b200.components.data.datasets import gaussian_dataset_dict
+from landmarksystem_b200.components.data.datasets.processed_dataset import PreprocessedDataset, dist_preprocess, preprocess
+
+
+def _toy_model(n_images=17):
+    rng = np.random.default_rng(0)
+    cameras = {1: cl.ColmapCamera(1, "PINHOLE", 64, 48, np.array([80.0, 82.0, 32.0, 24.0])),
+               2: cl.ColmapCamera(2, "SIMPLE_RADIAL", 32, 24, np.array([40.0, 16.0, 12.0, 0.01]))}
+    images = {}
+    for k in range(n_images):
+        ang = 2 * math.pi * k / n_images
+        c2w = pu.viewmatrix(lookat=-np.array([math.cos(ang), math.sin(ang), 0.3]), up=np.array([0, 0, 1.0]),
+                            pos=3 * np.array([math.cos(ang), math.sin(ang), 0.3]))
+        c2w = np.concatenate((c2w, [[0, 0, 0, 1]]))
+        c2w[:3, 1:3] *= -1                                    # OpenGL -> COLMAP axes
+        w2c = np.linalg.inv(c2w)
+        n_pts = int(rng.integers(0, 5))
+        images[k + 1] = cl.ColmapImage(k + 1, cl.rotmat2qvec(w2c[:3, :3]), w2c[:3, 3], 1 + k % 2, f"img_{k:03d}.png",
+                                       rng.random((n_pts, 2)) * 40, rng.integers(-1, 50, n_pts))
+    xyz = rng.normal(size=(50, 3))
+    rgb = rng.integers(0, 255, (50, 3)).astype(np.uint8)
+    return cameras, images, (xyz, rgb, rng.random(50))
+
+
+@pytest.mark.parametrize("binary", [True, False])
+def test_colmap_model_roundtrip(tmp_path, binary):
+    cameras, images, points = _toy_model()
+    (cl.write_model_binary if binary else cl.write_model_text)(str(tmp_path), cameras, images, points)
+    c2, i2, (xyz, rgb, err) = cl.read_model(str(tmp_path))
+    assert set(c2) == {1, 2} and c2[2].model == "SIMPLE_RADIAL" and c2[1].focal() == (80.0, 82.0)
+    assert np.allclose(c2[2].params, cameras[2].params)
+    assert set(i2) == set(images)
+    for k, im in images.items():
+        assert i2[k].name == im.name and i2[k].camera_id == im.camera_id
+        assert np.allclose(i2[k].qvec, im.qvec) and np.allclose(i2[k].tvec, im.tvec)
+        assert np.allclose(i2[k].xys, im.xys) and np.array_equal(i2[k].point3D_ids, im.point3D_ids)
+        assert np.allclose(i2[k].rotation(), cl.qvec2rotmat(im.qvec))
+        assert np.allclose(cl.qvec2rotmat(cl.rotmat2qvec(i2[k].rotation())), i2[k].rotation())
+    assert np.allclose(xyz, points[0]) and np.array_equal(rgb, points[1]) and np.allclose(err, points[2])
+
+
+def test_colmap_gaussian_dataset_splits_and_geometry(tmp_path):
+    cameras, images, points = _toy_model()
+    cl.write_model_binary(str(tmp_path / "sparse" / "0"), cameras, images, points)
+    args = SimpleNamespace(datadir=str(tmp_path), eval=True, white_bkgd=False)
+    train = gaussian_dataset_dict["colmap"]("train", 1.0, args)
+    test = gaussian_dataset_dict["Colmap"]("test", 1.0, args)
+    assert len(test) == 3 and len(train) == 14                 # every 8th of 17 images is held out
+    cam = train.cameras[0]
+    assert cam.image_name == "img_001.png" and (cam.image_width, cam.image_height) == (32, 24)
+    assert abs(cam.FoVx - 2 * math.atan(32 / 80.0)) < 1e-6
+    assert abs(float(cam.camera_center.norm()) - 3 * math.sqrt(1 + 0.09)) < 1e-4      # cameras sit on the ring
+    assert abs(train.cameras_extent - 1.1 * float(np.linalg.norm(
+        np.array([c.camera_center.numpy() for c in train.cameras]) + train.translate, axis=1).max())) < 1e-4
+    xyz, rgb = train.initial_point_cloud()
+    assert xyz.shape == (50, 3) and rgb.max() <= 1.0
+    zj = gaussian_dataset_dict["zhangjiang"]("train", 1.0, SimpleNamespace(datadir=str(tmp_path), eval=False, lb=[-2, -2, -9], ub=[9, 9, 9]))
+    assert 0 < len(zj) < 17 and np.allclose(zj.world_shift, -np.array(
+        [-(im.rotation().T @ im.tvec) for im in images.values()]).mean(0))
+
+
+def test_pose_interpolation_and_orientation():
+    a = np.concatenate((pu.viewmatrix([0, 1, 0], [0, 0, 1], [0, -3, 0]), [[0, 0, 0, 1]]))
+    b = np.concatenate((pu.viewmatrix([-1, 0, 0], [0, 0, 1], [3, 0, 1]), [[0, 0, 0, 1]]))
+    path = pu.get_interpolated_poses(a, b, steps=5)
+    assert np.allclose(path[0], a[:3]) and np.allclose(path[-1], b[:3], atol=1e-9)
+    mid = path[2]
+    assert np.allclose(mid[:, 3], [1.5, -1.5, 0.5]) and abs(np.linalg.det(mid[:, :3]) - 1) < 1e-9
+    q = pu.quaternion_from_matrix(mid[:, :3])
+    assert np.allclose(pu.quaternion_matrix(q), mid[:, :3])
+    many, ks = pu.get_interpolated_poses_many([a, b, a], [np.eye(3), 2 * np.eye(3), np.eye(3)], 4)
+    assert many.shape == (8, 3, 4) and ks.shape == (8, 3, 3) and np.allclose(ks[3], 2 * np.eye(3))
+    fly = pu.catmull_rom_path([a, b, a, b], 1000)
+    assert fly.shape == (1000, 3, 4) and np.allclose(fly[0], a[:3]) and np.allclose(fly[-1], b[:3], atol=1e-6)
+    assert np.abs(np.diff(fly[:, :, 3], axis=0)).max() < 0.05            # no jumps
+    ring = np.stack([pu.viewmatrix(-np.array([math.cos(t), 0.2, math.sin(t)]), [0, 1, 0], 2 * np.array([math.cos(t), 0.2, math.sin(t)]))
+                     for t in np.linspace(0, 2 * math.pi, 12, endpoint=False)])
+    new, tf = pu.auto_orient_and_center_poses(ring, method="up", center_method="poses")
+    assert np.allclose(new[:, :, 3].mean(0), 0, atol=1e-9)
+    assert np.allclose(pu.normalize(new[:, :, 1].mean(0)), [0, 0, 1], atol=1e-6)       # mean up is +z now
+    focus = pu.focus_of_attention(np.concatenate((ring, np.tile([[[0, 0, 0, 1.0]]], (12, 1, 1))), 1), np.zeros(3))
+    assert np.allclose(focus, 0, atol=1e-6)
+
+
+def test_shard_preprocessing_single_and_distributed(tmp_path):
+    n = 3 * 512 + 100
+    ds = SimpleNamespace(all_rays=torch.arange(n * 6, dtype=torch.float32).view(n, 6), all_rgbs=torch.rand(n, 3),
+                         all_idxs=torch.arange(n, dtype=torch.float32))
+    assert preprocess(ds, str(tmp_path / "single"), shard_rays=512) == 3
+    loaded = PreprocessedDataset(str(tmp_path / "single"))
+    assert len(loaded) == 3 and loaded[0][0].shape == (512, 6)
+    # two "ranks" run one after the other in this process (world 1 calls exercise the same numbering logic)
+    total = dist_preprocess(ds, str(tmp_path / "dist"), rank=0, world=1, shard_rays=512)
+    assert total == 3
+    rows = torch.cat([PreprocessedDataset(str(tmp_path / "dist"))[k][2] for k in range(3)])
+    assert rows.unique().numel() == 3 * 512                  # no ray is duplicated across shards
