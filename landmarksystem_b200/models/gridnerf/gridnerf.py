@@ -576,6 +576,44 @@ class GridNeRF(BaseNeRF):
         rgb = (extras["rgb_map"] + rgb_map).clamp(0.0, 1.0) if self.residnerf else extras["rgb_map"]
         return {"rgb_map_nerf": rgb, "depth_map_nerf": depth}
 
+    @torch.no_grad()
+    def render_partial(self, rays: torch.Tensor, N_samples: int = -1) -> torch.Tensor:
+        """Model-parallel rendering, per-rank half: composite only the samples that fall into THIS rank's resident
+        blocks (the scene manager's window) and return ``[R, 8]`` records ``(rgb without background, transmittance,
+        depth, opacity, entry distance, 0)``.  Records of all ranks are merged in entry-distance order by
+        :class:`landmarksystem_b200.parallel.composite_merge.CompositeMerger`; the result equals the single-model
+        render as long as a ray crosses each rank's region in one contiguous interval (rectangular block windows)."""
+        from ...ops.composite import composite_render, composite_weights
+        from ...parallel.composite_merge import pack_partial
+
+        cfg = self.config
+        S_req = N_samples if N_samples > 0 else self.sampler.num_samples
+        origin, dirs = rays[:, :3], rays[:, 3:6]
+        z = self.sampler.compute_z_vals(rays, S_req, False, False)
+        R, S = z.shape
+        xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
+        valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
+        if self.alphaMask is not None:
+            valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
+        local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
+        block = torch.where(valid, block, torch.full_like(block, -1.0))
+        xyzb = torch.cat((local, block[:, None]), dim=-1)
+        mine = (block >= 0)
+        sigma = (self._density(xyzb) * mine.to(torch.float32)).view(R, S)      # softplus heads are not zero at no-data
+        dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
+        weight, trans = composite_weights(sigma, dists * cfg.distance_scale)
+        app_mask = ((weight > cfg.rayMarch_weight_thres) & mine.view(R, S)).reshape(-1)
+        if self._fused_app_stage_ok(xyzb):
+            rgb = self._fused_app_stage(xyzb, dirs, app_mask, S)
+        else:
+            rgb = torch.zeros(R * S, 3, device=rays.device, dtype=torch.float32)
+            idx = app_mask.nonzero(as_tuple=True)[0]
+            if idx.numel() > 0:
+                rgb = rgb.index_put((idx,), self._rgb(xyzb[idx], dirs[idx // S], None))
+        rgb_map, depth, acc = composite_render(weight, rgb.view(R, S, 3), z, 0.0)
+        t_entry = torch.where(mine.view(R, S), z, torch.full_like(z, float("inf"))).amin(dim=-1)
+        return pack_partial(rgb_map, trans, depth, acc, t_entry)
+
     def render_all_rays(self, rays, chunk_size: Optional[int] = None, N_samples=-1, idxs=None, app_code=0):
         n_total = rays.shape[0]
         chunk_size = chunk_size or n_total

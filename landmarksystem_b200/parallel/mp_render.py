@@ -1,0 +1,44 @@
+"""Model-parallel rendering by spatial blocks (north-star path "d").
+
+Each rank holds the grids of a rectangular window of scene blocks (what dynamic loading keeps resident on that
+GPU) and renders, for every ray, only the segment that crosses its window; the per-rank records (colour,
+transmittance, depth, opacity, entry distance) are then merged front to back across the ranks by ONE kernel per
+rank that pulls the peers' records over NVLink, orders them by entry distance, composites them and stores the
+finished pixels (``ops/csrc/fused_comm.cu: composite_merge_p2p_kernel``).  The reference has no counterpart: its
+engine forbids model parallelism together with dynamic loading and only gathers data-parallel ray slices
+(landmark/__init__.py:51-54, landmark/render/parallel_module/parallel_module.py:105-135)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .composite_merge import CompositeMerger, merge_reference
+
+
+class ModelParallelRenderer:
+    """``model`` must offer ``render_partial(rays, N_samples) -> [R, 8]`` (see ``GridNeRF.render_partial``)."""
+
+    def __init__(self, model, max_rays: int, group=None, white_bg: Optional[bool] = None):
+        self.model = model
+        if white_bg is None:                              # follow the model's own renderer
+            white_bg = bool(getattr(getattr(model, "renderer", None), "white_bg", False))
+        self.bg = 1.0 if white_bg else 0.0
+        self.group = group
+        self.merger: Optional[CompositeMerger] = None
+        self.max_rays = int(max_rays)
+
+    @torch.no_grad()
+    def render(self, rays: torch.Tensor, N_samples: int = -1, root: int = -1, chunk: Optional[int] = None
+               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """``(rgb [R,3] in [0,1], depth [R], opacity [R])`` on ``root`` (every rank when ``root == -1``)."""
+        R = rays.shape[0]
+        chunk = chunk or R
+        partial = torch.cat([self.model.render_partial(rays[s:s + chunk], N_samples) for s in range(0, R, chunk)])
+        if rays.is_cuda and torch.distributed.is_initialized() and torch.distributed.get_world_size(self.group) > 1:
+            if self.merger is None or self.merger.max_rays < R:
+                self.merger = CompositeMerger(max(R, self.max_rays), self.group)
+            out = self.merger.merge(partial, bg=self.bg, root=root).clone()
+        else:                                            # one rank (or CPU): the same merge in PyTorch
+            out = merge_reference(partial[None], bg=self.bg)
+        return out[:, :3].clamp(0.0, 1.0), out[:, 4], out[:, 5]

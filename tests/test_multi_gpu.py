@@ -44,3 +44,11 @@ def test_branch_parallel_all_to_all():
     sys.stdout.write(res.stdout[-2000:])
     assert res.returncode == 0, res.stderr[-3000:]
     assert "BRANCH_A2A_RESULTS" in res.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_model_parallel_render_merge():
+    res = _launch("worker_mp_render.py", 2)
+    sys.stdout.write(res.stdout[-2000:])
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "MP_RENDER_RESULTS" in res.stdout
