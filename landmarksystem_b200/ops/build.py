@@ -82,7 +82,7 @@ def build_all(verbose: bool = False, force: bool = False) -> Path:
     lib = library_path()
     newest = max(o.stat().st_mtime for o in objs)
     if (not lib.exists()) or lib.stat().st_mtime < newest:
-        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs), "-lcudart", "-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs), "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

@@ -64,6 +64,24 @@ __device__ __forceinline__ float load_elem(const unsigned char* buf, int col, in
 }
 
 
+// cuTensorMapEncodeTiled is a driver-API function; it is resolved through the runtime at first use instead of
+// linking the driver library, so the kernel library loads (and its symbols can be checked) on a machine that has
+// the CUDA toolkit but no driver.
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                           CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline TensorMapEncodeTiledFn tensor_map_encoder() {
+  static TensorMapEncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeTiledFn>(p);
+  }
+  return fn;
+}
+
 // 3-D tensor map over a row-major bf16 [rows, width] matrix: (8 elements, width/8 chunks, rows), box
 // = one 16-byte chunk of 128 rows, so a tile lands in shared memory in the chunked operand layout.
 inline int encode_input_map(CUtensorMap* map, const void* x, int width, long long rows) {
@@ -71,7 +89,9 @@ inline int encode_input_map(CUtensorMap* map, const void* x, int width, long lon
   const cuuint64_t gstride[2] = {16, (cuuint64_t)width * 2};
   const cuuint32_t box[3] = {8, 1, (cuuint32_t)kTileRows};
   const cuuint32_t estride[3] = {1, 1, 1};
-  CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride, box,
+  TensorMapEncodeTiledFn encode = tensor_map_encoder();
+  if (encode == nullptr) return 19999;
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), gdim, gstride, box,
                                       estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 10000 + (int)r;
