@@ -236,12 +236,10 @@ class TensorVMEncoding(VolumeEncoding):
         for i, (vec_id, (m0, m1)) in enumerate(zip(self.vector_mode, self.matrix_mode)):
             for idx, j in enumerate(self.reso_mode):
                 k = i * n_levels + idx
-                p = self.plane_coef[k].data.permute(0, 3, 1, 2)                        # [B,C,H,W]
-                p = F.interpolate(p, size=(grid[m1] * j, grid[m0] * j), mode="bilinear", align_corners=True)
-                l = self.line_coef[k].data.permute(0, 2, 1)                            # [B,C,Z]
-                l = F.interpolate(l, size=grid[vec_id] * j, mode="linear", align_corners=True)
-                self.plane_coef[k] = torch.nn.Parameter(p.permute(0, 2, 3, 1).contiguous())
-                self.line_coef[k] = torch.nn.Parameter(l.permute(0, 2, 1).contiguous())
+                from ....ops.resize import resize_bilinear_nhwc, resize_linear_nlc   # channels-last, no transposes
+
+                self.plane_coef[k] = torch.nn.Parameter(resize_bilinear_nhwc(self.plane_coef[k].data, grid[m1] * j, grid[m0] * j))
+                self.line_coef[k] = torch.nn.Parameter(resize_linear_nlc(self.line_coef[k].data, grid[vec_id] * j))
         if self.use_shadow:
             self.enable_shadow(lazy=getattr(self, "lazy", False))
 

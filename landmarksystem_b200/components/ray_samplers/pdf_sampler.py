@@ -18,7 +18,14 @@ from .base_sampler import BaseSampler
 
 
 def sample_pdf(bins: torch.Tensor, weights: torch.Tensor, n_samples: int, det: bool = False) -> torch.Tensor:
-    """``bins [R, B+1]`` edges, ``weights [R, B]`` -> ``[R, n_samples]`` positions."""
+    """``bins [R, B+1]`` edges, ``weights [R, B]`` -> ``[R, n_samples]`` positions (no gradient on CUDA: the
+    callers detach the result).  CUDA inputs go through one kernel (``ops/csrc/pdf.cu``)."""
+    if weights.is_cuda and weights.dim() == 2 and not (weights.requires_grad and torch.is_grad_enabled()) \
+            and 2 * (weights.shape[-1] + 1) * 4 <= 48 * 1024:
+        from ...ops.pdf import pdf_resample
+
+        u = None if det else torch.rand(weights.shape[0], n_samples, device=weights.device)
+        return pdf_resample(bins, weights, n_samples, u)
     weights = weights + 1e-5
     pdf = weights / weights.sum(-1, keepdim=True)
     cdf = torch.cat((torch.zeros_like(pdf[..., :1]), torch.cumsum(pdf, -1)), -1)

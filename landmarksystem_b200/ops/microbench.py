@@ -8,7 +8,8 @@ command line is what the profiler captures are taken from.
 
 Cases: ``adam`` (dense fused Adam), ``lazy_adam`` (deferred Adam step over the touched texels of a plane),
 ``vm_fwd`` / ``vm_bwd`` (plane x line lookup), ``mlp_fwd`` / ``mlp_bwd`` (tcgen05 colour head),
-``composite`` (volume-render weights + colour), ``hash_fwd`` (multiresolution hash grid).
+``composite`` (volume-render weights + colour), ``hash_fwd`` (multiresolution hash grid), ``zero_adam_emulated`` /
+``merge_emulated`` (the peer-memory kernels with all eight "peers" on one GPU).
 """
 from __future__ import annotations
 
@@ -227,7 +228,67 @@ def case_hash_fwd(args):
     return _report("hashgrid fwd", ms, best, bytes_=args.rows * 16 * (8 * 4 + 8.0), rows=args.rows)
 
 
-CASES = {"adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd,
+# -- peer-memory kernels with the peers emulated on one GPU --------------------------------------------------
+# The fused compute+collective kernels take a table of peer addresses.  Here every "peer" is another buffer on the
+# SAME GPU and ONE launch plays one rank of an 8-rank job (no barrier is needed: nothing else writes the buffers), so
+# the kernel's own behaviour - instruction mix, access pattern, traffic per element - can be profiled on a single
+# GPU.  The loads that would cross NVLink hit local HBM instead; link-level figures come from the multi-GPU tests.
+def _ptr_table(tensors):
+    import ctypes
+
+    return (ctypes.c_longlong * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def case_zero_adam_emulated(args):
+    from . import native
+    from ..parallel import zero_adam  # noqa: F401  (registers the entry point's signature)
+
+    world, n = 8, args.rows * 64
+    grads = [torch.randn(n, device="cuda") for _ in range(world)]
+    params = [torch.zeros(n, device="cuda") for _ in range(world)]
+    shadows = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    m = torch.zeros(n // world, device="cuda")
+    v = torch.zeros(n // world, device="cuda")
+    gt, pt, st = _ptr_table(grads), _ptr_table(params), _ptr_table(shadows)
+    step = [0]
+
+    def fn():
+        step[0] += 1
+        native.check(native.lib().lmb_zero_adam_p2p(gt, pt, st, m.data_ptr(), v.data_ptr(), n, 0, world, 1e-3, 0.9, 0.99, 1e-8,
+                                                    step[0], 1.0, native.stream_ptr()), "zero_adam_p2p")
+
+    ms, best = time_kernel(fn, args.iters)
+    shard = n // world
+    # per shard element: world gradient loads, p / m / v read and written, the new value + bf16 shadow stored to every rank
+    bytes_ = shard * (world * 4 + 12 + 8 + world * 6.0)
+    return _report("zero_adam_p2p_kernel (8 ranks emulated on one GPU, rank 0's shard)", ms, best, bytes_=bytes_,
+                   params=n, shard=shard)
+
+
+def case_merge_emulated(args):
+    from . import native
+    from ..parallel import composite_merge  # noqa: F401
+
+    world, R = 8, 1920 * 1080
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    partials = []
+    for r in range(world):
+        p = torch.rand(R, 8, device="cuda", generator=gen)
+        p[:, 6] = (torch.randint(0, 1 << 20, (R,), device="cuda", generator=gen) * 8 + r).float()
+        partials.append(p.contiguous())
+    outs = [torch.zeros(R, 6, device="cuda") for _ in range(world)]
+    pt, ot = _ptr_table(partials), _ptr_table(outs)
+
+    def fn():
+        native.check(native.lib().lmb_composite_merge_p2p(pt, ot, R, 0, world, -1, 1.0, native.stream_ptr()), "composite_merge_p2p")
+
+    ms, best = time_kernel(fn, args.iters, flush_l2=True)
+    rays = (R + world - 1) // world
+    return _report("composite_merge_p2p_kernel (8 ranks emulated on one GPU, rank 0's ray slice)", ms, best,
+                   bytes_=rays * (world * 32 + world * 24.0), rays=rays)
+
+
+CASES = {"zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd,
          "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
 
 

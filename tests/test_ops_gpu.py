@@ -234,3 +234,49 @@ def test_fused_l1_ssim_matches_conv_reference(shape):
     (0.8 * l1_ref + 0.2 * (1 - s_ref)).backward()
     assert abs(float(l1) - float(l1_ref)) < 1e-5 and abs(float(s) - float(s_ref)) < 1e-4
     assert torch.allclose(got.cpu().double(), x.grad, atol=2e-6, rtol=1e-3), (got.cpu().double() - x.grad).abs().max()
+
+
+@pytest.mark.parametrize("B,n,det", [(62, 32, True), (126, 128, False), (509, 64, False), (1, 7, True)])
+def test_pdf_resample_matches_torch(B, n, det):
+    from landmarksystem_b200.components.ray_samplers import pdf_sampler
+    from landmarksystem_b200.ops.pdf import pdf_resample
+
+    torch.manual_seed(0)
+    R = 300
+    bins = torch.sort(torch.rand(R, B + 1, device=DEV) * 5 + 1, -1).values
+    weights = torch.rand(R, B, device=DEV) ** 4
+    weights[::7] = 0                                      # rays without any mass fall back to the uniform PDF
+    u = None if det else torch.rand(R, n, device=DEV)
+    got = pdf_resample(bins, weights, n, u)
+    # CPU statement of the same construction with the same uniform numbers
+    w = weights.cpu().double() + 1e-5
+    pdf = w / w.sum(-1, keepdim=True)
+    cdf = torch.cat((torch.zeros(R, 1, dtype=torch.float64), pdf.cumsum(-1)), -1)
+    uu = torch.linspace(0, 1, n, dtype=torch.float64).expand(R, n) if det else u.cpu().double()
+    inds = torch.searchsorted(cdf, uu.contiguous(), right=True)
+    below, above = (inds - 1).clamp(min=0), inds.clamp(max=B)
+    c0, c1 = cdf.gather(-1, below), cdf.gather(-1, above)
+    b0, b1 = bins.cpu().double().gather(-1, below), bins.cpu().double().gather(-1, above)
+    den = torch.where(c1 - c0 < 1e-5, torch.ones_like(c0), c1 - c0)
+    ref = b0 + (uu - c0) / den * (b1 - b0)
+    # a sample whose u sits within float rounding of a CDF knot may land in the neighbouring bin: compare positions
+    assert (got.cpu().double() - ref).abs().max() < 2e-3 * 5, (got.cpu().double() - ref).abs().max()
+    assert torch.isfinite(got).all() and (got >= bins[:, :1] - 1e-4).all() and (got <= bins[:, -1:] + 1e-4).all()
+    if det:
+        assert (got[:, 1:] >= got[:, :-1] - 1e-5).all()
+    assert pdf_sampler.sample_pdf(bins, weights, n, det=True).shape == (R, n)
+
+
+def test_resize_nhwc_matches_interpolate():
+    from landmarksystem_b200.ops.resize import resize_bilinear_nhwc, resize_linear_nlc
+
+    torch.manual_seed(0)
+    src = torch.randn(2, 13, 17, 16, device=DEV)
+    for H2, W2 in ((29, 40), (13, 17), (5, 60), (1, 1)):
+        got = resize_bilinear_nhwc(src, H2, W2)
+        ref = torch.nn.functional.interpolate(src.permute(0, 3, 1, 2), size=(H2, W2), mode="bilinear", align_corners=True).permute(0, 2, 3, 1)
+        assert got.shape == ref.shape and torch.allclose(got, ref, atol=1e-5), (H2, W2)
+    line = torch.randn(3, 11, 48, device=DEV)
+    got = resize_linear_nlc(line, 37)
+    ref = torch.nn.functional.interpolate(line.permute(0, 2, 1), size=37, mode="linear", align_corners=True).permute(0, 2, 1)
+    assert torch.allclose(got, ref, atol=1e-5)
