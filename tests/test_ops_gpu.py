@@ -243,7 +243,8 @@ def test_pdf_resample_matches_torch(B, n, det):
 
     torch.manual_seed(0)
     R = 300
-    bins = torch.sort(torch.rand(R, B + 1, device=DEV) * 5 + 1, -1).values
+    # bin widths between 0.5 and 1.5 units (bins far narrower than a float ulp of the position cannot be resolved)
+    bins = 1.0 + torch.cumsum(0.5 + torch.rand(R, B + 1, device=DEV), -1) * (5.0 / (B + 1))
     weights = torch.rand(R, B, device=DEV) ** 4
     weights[::7] = 0                                      # rays without any mass fall back to the uniform PDF
     u = None if det else torch.rand(R, n, device=DEV)
@@ -259,8 +260,18 @@ def test_pdf_resample_matches_torch(B, n, det):
     b0, b1 = bins.cpu().double().gather(-1, below), bins.cpu().double().gather(-1, above)
     den = torch.where(c1 - c0 < 1e-5, torch.ones_like(c0), c1 - c0)
     ref = b0 + (uu - c0) / den * (b1 - b0)
-    # a sample whose u sits within float rounding of a CDF knot may land in the neighbouring bin: compare positions
-    assert (got.cpu().double() - ref).abs().max() < 2e-3 * 5, (got.cpu().double() - ref).abs().max()
+    # The inverse is ill-conditioned where the CDF is flat (bins without mass): a rounding-level change of u moves the
+    # sample across such bins.  Positions therefore agree wherever the CDF has slope, and everywhere the CDF evaluated
+    # at the returned position gives back u.
+    pos = got.cpu().double()
+    edges = bins.cpu().double()
+    b = (torch.searchsorted(edges.contiguous(), pos.contiguous(), right=True) - 1).clamp(0, B - 1)
+    e0, e1 = edges.gather(-1, b), edges.gather(-1, b + 1)
+    f0, f1 = cdf.gather(-1, b), cdf.gather(-1, b + 1)
+    back = f0 + (pos - e0) / (e1 - e0).clamp(min=1e-12) * (f1 - f0)
+    assert (back - uu).abs().max() < 5e-4, (back - uu).abs().max()
+    steep = (c1 - c0) > 1e-3
+    assert ((pos - ref).abs()[steep]).max() < 1e-2
     assert torch.isfinite(got).all() and (got >= bins[:, :1] - 1e-4).all() and (got <= bins[:, -1:] + 1e-4).all()
     if det:
         assert (got[:, 1:] >= got[:, :-1] - 1e-5).all()
