@@ -56,6 +56,52 @@ class FusedAdam(torch.optim.Optimizer):
                 if getattr(p, "_lmb_lazy", None) is not None:
                     p._lmb_lazy.dyn = group["_dyn"]
 
+    # -- checkpointing: the deferred-update state of planes lives outside ``self.state`` -----------------------------
+    def _lazy_params(self):
+        out, k = [], 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                if getattr(p, "_lmb_lazy", None) is not None:
+                    out.append((k, p))
+                k += 1
+        return out
+
+    def state_dict(self):
+        """Standard optimiser state plus, for planes with the deferred update, their moments and step count (every texel
+        is brought up to date first, so the saved moments are those a dense Adam would hold)."""
+        sd = super().state_dict()
+        lazy = {}
+        for k, p in self._lazy_params():
+            st = p._lmb_lazy
+            st.flush(p)
+            lazy[k] = {"exp_avg": st.m, "exp_avg_sq": st.v, "step": st.steps_done}
+        if lazy:
+            sd["lazy"] = lazy
+        return sd
+
+    def load_state_dict(self, state_dict):
+        state_dict = dict(state_dict)
+        lazy = state_dict.pop("lazy", None)
+        for g in state_dict.get("param_groups", []):
+            g.pop("_dyn", None)                     # device-resident schedules are rebuilt below
+        super().load_state_dict(state_dict)
+        if lazy:
+            for k, p in self._lazy_params():
+                rec = lazy.get(k, lazy.get(str(k)))
+                if rec is None:
+                    continue
+                st = p._lmb_lazy
+                st.m.copy_(rec["exp_avg"])
+                st.v.copy_(rec["exp_avg_sq"])
+                st.steps_done = int(rec["step"])
+                st.last_step.fill_(st.steps_done)
+                st.need.zero_()
+                st.dirty = False
+        if self.capturable:
+            for group in self.param_groups:
+                group["_dyn"] = None
+            self.sync_dyn()
+
     def host_advance(self) -> None:
         """Mirror one graph-replayed step in the host-side bookkeeping (no kernel is launched)."""
         for group in self.param_groups:

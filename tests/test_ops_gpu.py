@@ -291,3 +291,45 @@ def test_resize_nhwc_matches_interpolate():
     got = resize_linear_nlc(line, 37)
     ref = torch.nn.functional.interpolate(line.permute(0, 2, 1), size=37, mode="linear", align_corners=True).permute(0, 2, 1)
     assert torch.allclose(got, ref, atol=1e-5)
+
+
+def test_fused_adam_checkpoint_roundtrip_with_deferred_planes():
+    """state_dict / load_state_dict carry the deferred-update moments: a restored optimiser continues exactly."""
+    torch.manual_seed(0)
+
+    def make():
+        plane = torch.nn.Parameter(torch.randn(1, 16, 16, 8, device=DEV) * 0.1)
+        w = torch.nn.Parameter(torch.randn(8, 8, device=DEV) * 0.1)
+        FusedAdam.attach_sink(plane, shadow=True, lazy=True)
+        return plane, w, FusedAdam([{"params": [plane], "lr": 0.02, "lr_decay": 0.99}, {"params": [w], "lr": 0.01, "lr_decay": 0.99}],
+                                   capturable=True)
+
+    def run(plane, w, opt, steps, seed):
+        g = torch.Generator(device=DEV).manual_seed(seed)
+        for _ in range(steps):
+            coords = torch.rand(40, 4, device=DEV, generator=g) * 2 - 1
+            coords[:, 3] = 0
+            plane._lmb_lazy.prepare(plane, coords.contiguous())
+            touched = plane._lmb_lazy.need.view(1, 16, 16) != 0
+            plane._lmb_grad_sink.copy_(torch.randn(1, 16, 16, 8, device=DEV, generator=g) * touched[..., None])
+            w.grad = torch.randn(8, 8, device=DEV, generator=g)
+            opt.step()
+            opt.zero_grad()
+
+    a = make()
+    torch.manual_seed(0)
+    b = make()
+    b[0].data.copy_(a[0].data); b[1].data.copy_(a[1].data)
+    run(*a, 7, seed=1)
+    sd = {k: (v if k != "state" else {i: {n: (t.clone() if torch.is_tensor(t) else t) for n, t in s.items()} for i, s in v.items()})
+          for k, v in a[2].state_dict().items()}
+    b[0].data.copy_(a[0].data); b[1].data.copy_(a[1].data); b[0]._lmb_shadow.copy_(a[0]._lmb_shadow)
+    b[2].load_state_dict(sd)
+    assert b[0]._lmb_lazy.steps_done == 7 and b[2].param_groups[0]["_dyn"].tolist()[1] == 8.0
+    run(*a, 5, seed=2)
+    run(*b, 5, seed=2)
+    for x, y in ((a[0], b[0]), (a[1], b[1])):
+        xs, ys = x, y
+        if getattr(x, "_lmb_lazy", None) is not None:
+            x._lmb_lazy.flush(x); y._lmb_lazy.flush(y)
+        assert torch.allclose(xs, ys, atol=1e-6), (xs - ys).abs().max()
