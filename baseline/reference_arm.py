@@ -227,5 +227,7 @@ def _run(args, ref_root, DIVISIONS, RAYS_PER_GPU, SAMPLES, BLOCK_M, PLANE, LINE,
                     "h2d_bytes_per_step": global_batch * 10 * 4, "d2h_bytes_per_step": 4},
             "gpu_launches": 0,
         }), flush=True)
-    if world > 1 and dist.is_initialized():
-        dist.barrier()
+    if dist.is_initialized():
+        if world > 1:
+            dist.barrier()
+        dist.destroy_process_group()           # the reference initialises a group even for one rank

@@ -270,8 +270,10 @@ class GridNeRFTrainer(NeRFTrainer):
         with self.timer.stage("optimizer"):
             self.optimizer.step()
             self.optimizer.zero_grad(set_to_none=True)
+            owns_schedule = bool(getattr(self.optimizer, "capturable", False))   # capturable Adam decays lr on the device itself
             for group in self.optimizer.param_groups:
-                group["lr"] *= self.lr_factor
+                if not owns_schedule:
+                    group["lr"] *= self.lr_factor
                 group["lr_decay"] = self.lr_factor      # lets the deferred Adam reconstruct skipped steps
         return loss.detach()
 

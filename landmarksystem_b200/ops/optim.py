@@ -33,8 +33,9 @@ class FusedAdam(torch.optim.Optimizer):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         # capturable: every group's {learning rate, step number} lives on the device and is advanced by a
         # kernel at the end of step() (lr *= group["lr_decay"]), so a step recorded in a CUDA graph follows
-        # the schedule on replay.  group["lr"] then only mirrors the device value for logging; call
-        # ``sync_dyn`` after changing it by hand and ``host_advance`` after every graph replay.
+        # the schedule on replay.  The optimiser owns the schedule in this mode: group["lr"] mirrors the device value
+        # (step() and host_advance() keep it in step; callers must not decay it themselves); call ``sync_dyn`` after
+        # changing it by hand and ``host_advance`` after every graph replay.
         self.capturable = capturable
         if capturable:
             self.sync_dyn()
@@ -183,6 +184,7 @@ class FusedAdam(torch.optim.Optimizer):
             if dyn is not None and stepped:
                 native.check(native.lib().lmb_adam_dyn_advance(dyn.data_ptr(), float(group.get("lr_decay", 1.0)),
                                                                native.stream_ptr()), "adam_dyn_advance")
+                group["lr"] *= float(group.get("lr_decay", 1.0))      # host mirror of the device-side schedule
         return loss
 
     def zero_grad(self, set_to_none: bool = True):  # gradients are cleared inside step()
