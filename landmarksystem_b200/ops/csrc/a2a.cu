@@ -23,25 +23,29 @@ struct A2APeers {
 
 // payload: [n, W] floats; dst[n]: owner rank or -1.  inbox layout on every rank: [world][cap][W + 1] floats.
 // pos_out[n]: position inside the (dst, src) segment (needed to route gradients back).  Only the first
-// *count_ptr rows are sent (device-side count; nullptr: all n).  Slots are claimed once per warp and
-// destination (lanes that share a destination are grouped with a match), not once per row.
+// *count_ptr rows are sent (device-side count; nullptr: all n).  Slots are claimed once per BLOCK and destination:
+// rows are ranked per destination with shared-memory counters, then one global atomic per (block, destination)
+// reserves the block's range - 256 times fewer same-address atomics than one per row.
 __global__ void __launch_bounds__(256)
 a2a_dispatch_kernel(const float* __restrict__ payload, const int* __restrict__ dst, const int* __restrict__ count_ptr, long long n,
                     int W, A2APeers inbox, int src_rank, int world, long long cap, int* __restrict__ counts,
                     int* __restrict__ pos_out, int* overflow) {
+  __shared__ int local_count[kA2AMaxPeers], base[kA2AMaxPeers];
+  if (threadIdx.x < kA2AMaxPeers) local_count[threadIdx.x] = 0;
+  __syncthreads();
   const long long n_valid = resolve_count(count_ptr, n);
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int lane = threadIdx.x & 31;
   int d = -1;
   if (i < n_valid) { d = dst[i]; if (d >= world) d = -1; }
-  const unsigned peers = __match_any_sync(0xffffffffu, d);        // lanes with the same destination
+  int local = 0;
+  if (d >= 0) local = atomicAdd(&local_count[d], 1);
+  __syncthreads();
+  if (threadIdx.x < world && local_count[threadIdx.x] > 0)
+    base[threadIdx.x] = atomicAdd(&counts[threadIdx.x], local_count[threadIdx.x]);
+  __syncthreads();
   int pos = -1;
   if (d >= 0) {
-    const int leader = __ffs(peers) - 1;
-    int base = 0;
-    if (lane == leader) base = atomicAdd(&counts[d], __popc(peers));
-    base = __shfl_sync(peers, base, leader);
-    pos = base + __popc(peers & ((1u << lane) - 1u));
+    pos = base[d] + local;
     if (pos >= cap) { pos = -1; atomicExch(overflow, 1); }
   }
   if (i < n) pos_out[i] = pos;
@@ -85,10 +89,11 @@ a2a_collect_kernel(const float* __restrict__ inbox, const int* __restrict__ inco
 __global__ void __launch_bounds__(256)
 a2a_combine_kernel(const float* __restrict__ values, const int* __restrict__ route_src, const int* __restrict__ route_slot,
                    const int* __restrict__ count_ptr, long long m, int V, A2APeers outs) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= resolve_count(count_ptr, m)) return;
-  float* o = reinterpret_cast<float*>(outs.p[route_src[i]]) + (long long)route_slot[i] * V;
-  for (int k = 0; k < V; ++k) o[k] = values[i * V + k];
+  const long long n = resolve_count(count_ptr, m);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float* o = reinterpret_cast<float*>(outs.p[route_src[i]]) + (long long)route_slot[i] * V;
+    for (int k = 0; k < V; ++k) o[k] = values[i * V + k];
+  }
 }
 
 // Backward of combine: a source sends d_out[i, :V] to the owner's gradient inbox at (src, pos[i]).
@@ -156,7 +161,8 @@ LMB_API int lmb_a2a_combine(const float* values, const int* route_src, const int
   if (m <= 0) return 0;
   A2APeers outs;
   fill(outs, out_table, world);
-  a2a_combine_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(values, route_src, route_slot, count_ptr, m, V, outs);
+  const long long want = (m + 255) / 256;            // capped grid: m is the owner-side row capacity
+  a2a_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(values, route_src, route_slot, count_ptr, m, V, outs);
   LMB_LAUNCH_CHECK();
   return 0;
 }

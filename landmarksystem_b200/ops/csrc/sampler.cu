@@ -34,17 +34,19 @@ uniform_sampler_kernel(const float* __restrict__ rays, int stride, long long R, 
   for (int c = 0; c < 3; ++c) {
     o[c] = ray[c]; d[c] = ray[3 + c];
     const float safe = d[c] == 0.f ? 1e-6f : d[c];
-    tmin = fmaxf(tmin, fminf((hi[c] - o[c]) / safe, (lo[c] - o[c]) / safe));
+    // IEEE division / no fused multiply-add: the first sample sits exactly on the box face, so the inside test must
+    // see the same bits as the unfused reference arithmetic (a one-ulp difference flips it)
+    tmin = fmaxf(tmin, fminf(__fdiv_rn(__fsub_rn(hi[c], o[c]), safe), __fdiv_rn(__fsub_rn(lo[c], o[c]), safe)));
   }
   tmin = fminf(fmaxf(tmin, a.near), a.far);
-  const float zk = tmin + a.step * ((float)k + (jitter ? jitter[r] : 0.f));
+  const float zk = __fadd_rn(tmin, __fmul_rn(a.step, __fadd_rn((float)k, jitter ? jitter[r] : 0.f)));
   z[i] = zk;
   dists[i] = k + 1 < a.S ? a.step : 0.f;
   float p[3];
   bool inside = true;
 #pragma unroll
   for (int c = 0; c < 3; ++c) {
-    p[c] = o[c] + d[c] * zk;
+    p[c] = __fadd_rn(o[c], __fmul_rn(d[c], zk));
     inside = inside && !(p[c] < lo[c]) && !(p[c] > hi[c]);
   }
   // scene-normalised coordinates, then block and block-local coordinates
