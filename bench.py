@@ -111,7 +111,7 @@ class ClockSampler:
 
 
 def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = 20):
-    """Secondary figure (second half of the north-star metric): 1080p render rate of the CUDA rasteriser on 6 M random
+    """Secondary figure: 1080p render rate of the CUDA rasteriser on 6 M random
     Gaussians spread over a 400 m x 400 m x 50 m box, SH degree 3, 16x16 tiles, camera on an orbit.  Device time
     per frame by CUDA events after 3 warm-up frames; every frame has a different pose."""
     import torch

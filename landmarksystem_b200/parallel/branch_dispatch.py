@@ -1,4 +1,4 @@
-"""Spatial-block all-to-all over peer memory (north-star path "b").
+"""Spatial-block all-to-all over peer memory.
 
 ``BlockDispatcher.query(payload, owner, fn, out_width)`` sends each row of ``payload`` to the rank that
 owns it, runs ``fn`` there on the compacted rows (a differentiable callable - grid lookup + head - that

@@ -1,4 +1,4 @@
-"""Channel-parallel colour head with the all-gather fused into the first GEMM (north-star path "c").
+"""Channel-parallel colour head with the all-gather fused into the first GEMM.
 
 With feature channels split across P ranks, every rank looks all samples up on its ``C/P`` channel
 slice.  The reference then all-gathers plane and line features (NCCL list all-gather + host sync,

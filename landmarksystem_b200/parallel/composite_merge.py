@@ -1,4 +1,4 @@
-"""Cross-GPU ordered alpha-composite for model-parallel rendering (north-star path "d").
+"""Cross-GPU ordered alpha-composite for model-parallel rendering.
 
 Each rank renders, for ALL rays of the frame, only the samples that fall into its resident spatial
 blocks and writes one partial per ray ``(rgb, T, depth, acc, t_entry)`` into a symmetric buffer.

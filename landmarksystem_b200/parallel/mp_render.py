@@ -1,4 +1,4 @@
-"""Model-parallel rendering by spatial blocks (north-star path "d").
+"""Model-parallel rendering by spatial blocks.
 
 Each rank holds the grids of a rectangular window of scene blocks (what dynamic loading keeps resident on that
 GPU) and renders, for every ray, only the segment that crosses its window; the per-rank records (colour,

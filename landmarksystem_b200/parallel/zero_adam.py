@@ -1,4 +1,4 @@
-"""Data-parallel optimiser step fused with its collectives (north-star path "a").
+"""Data-parallel optimiser step fused with its collectives.
 
 Parameters, gradients (and optional bf16 shadows) of all replicated tensors live in flat symmetric
 buffers that every rank of the data-parallel group maps.  One kernel per step
