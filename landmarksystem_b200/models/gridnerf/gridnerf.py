@@ -114,6 +114,7 @@ class GridNeRFConfig(ConfigClass):
     branch_dispatch: Literal["allreduce", "a2a"] = "allreduce"   # a2a: every rank brings its own rays; samples
                                                   # travel to the GPU owning their block over NVLink peer memory
     fused_optimizer: bool = True
+    deterministic_grid_grad: bool = False         # atomic-free sorted backward of the grid lookup (bit-reproducible, slower)
     fused_sampler: bool = True                    # sampling + block assignment in one kernel on CUDA
     fused_density: bool = True                    # density lookup + head in one kernel on CUDA
     lazy_adam: bool = False                       # deferred (exact) Adam on the planes: visit touched texels only
@@ -254,6 +255,10 @@ class GridNeRF(BaseNeRF):
 
     def enable_shadow(self):
         cfg = self.config
+        if bool(cfg.get("deterministic_grid_grad", False)):
+            from ...ops import vm
+
+            vm.DETERMINISTIC_BACKWARD = True
         # the deferred update is exact only when every gradient comes from sample lookups, i.e. no dense
         # regulariser (L1 / TV over whole planes) is active
         dense_reg = any(float(cfg.get(k, 0.0) or 0.0) > 0 for k in

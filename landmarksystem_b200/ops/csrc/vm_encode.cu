@@ -139,6 +139,149 @@ vm_encode_bwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
   }
 }
 
+// ---- atomic-free (deterministic) backward ------------------------------------------------------------------
+// Samples are sorted by the texel cell they fall into; one thread owns a whole run of equal cells, sums the run in
+// registers in sorted (stable) order and adds the four corner sums to the gradient plane with plain loads and stores.
+// Neighbouring cells share corners, so cells are 4-coloured by the parity of (x0, y0) and the colours run as separate
+// launches: within a launch no two runs touch the same texel.  Lines are handled the same way with cells sorted by z0,
+// two colours, and a warp per run (fixed lane assignment and shuffle tree).  The result is bit-reproducible; the
+// default backward (16-byte reductions into L2) is faster and differs only in summation order.
+constexpr unsigned long long kNoKey = ~0ull;
+
+__global__ void __launch_bounds__(256)
+vm_sort_keys_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n, int B, int H, int W, int Z,
+                    unsigned long long* __restrict__ pkeys, unsigned* __restrict__ pvals, unsigned long long* __restrict__ zkeys,
+                    unsigned* __restrict__ zvals) {
+  const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= max_n) return;
+  const long long n_valid = resolve_count(count_ptr, max_n);
+  unsigned long long pk = kNoKey, zk = kNoKey;
+  if (n < n_valid) {
+    const float4 q = __ldg(coords + n);
+    const int b = (int)q.w;
+    if (b >= 0 && b < B) {
+      const float fx = (q.x + 1.f) * 0.5f * (float)(W - 1), fy = (q.y + 1.f) * 0.5f * (float)(H - 1);
+      const float fz = (q.z + 1.f) * 0.5f * (float)(Z - 1);
+      const int x0 = min(max((int)floorf(fx), -1), W - 1), y0 = min(max((int)floorf(fy), -1), H - 1);
+      const int z0 = min(max((int)floorf(fz), -1), Z - 1);
+      pk = ((unsigned long long)b * (H + 1) + (y0 + 1)) * (W + 1) + (x0 + 1);
+      zk = (unsigned long long)b * (Z + 1) + (z0 + 1);
+    }
+  }
+  pkeys[n] = pk; pvals[n] = (unsigned)n;
+  zkeys[n] = zk; zvals[n] = (unsigned)n;
+}
+
+__device__ __forceinline__ void rmw_add8(float* p, const F8& a) {
+  float4* q = reinterpret_cast<float4*>(p);
+  float4 u = q[0], v = q[1];
+  u.x += a.v[0]; u.y += a.v[1]; u.z += a.v[2]; u.w += a.v[3];
+  v.x += a.v[4]; v.y += a.v[5]; v.z += a.v[6]; v.w += a.v[7];
+  q[0] = u; q[1] = v;
+}
+
+template <typename T, typename GT>
+__global__ void __launch_bounds__(256)
+vm_bwd_sorted_plane_kernel(const float4* __restrict__ coords, VMLevels lv, int l, const GT* __restrict__ dout, int out_stride,
+                           const unsigned long long* __restrict__ keys, const unsigned* __restrict__ vals, long long max_n,
+                           int colour) {
+  const int CH = lv.C >> 3;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = tid / CH;
+  const int ch = (int)(tid - i * CH);
+  if (i >= max_n) return;
+  const unsigned long long key = keys[i];
+  if (key == kNoKey || (i > 0 && keys[i - 1] == key)) return;          // not the head of a run
+  const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+  const int x0p = (int)(key % (unsigned long long)(W + 1));
+  const unsigned long long t = key / (unsigned long long)(W + 1);
+  const int y0p = (int)(t % (unsigned long long)(H + 1));
+  const int b = (int)(t / (unsigned long long)(H + 1));
+  if (((x0p & 1) | ((y0p & 1) << 1)) != colour) return;
+  F8 a00, a01, a10, a11;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a00.v[k] = a01.v[k] = a10.v[k] = a11.v[k] = 0.f;
+  const T* ln = reinterpret_cast<const T*>(lv.line[l]) + ((long long)b * Z) * lv.C + ch * 8;
+  for (long long j = i; j < max_n && keys[j] == key; ++j) {
+    const long long n = vals[j];
+    const float4 q = __ldg(coords + n);
+    const Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
+    const F8 l0 = load8(ln + (long long)cz.i0 * lv.C), l1 = load8(ln + (long long)cz.i1 * lv.C);
+    const F8 g = load8(dout + n * out_stride + l * lv.C + ch * 8);
+    const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float dp = g.v[k] * (cz.w0 * l0.v[k] + cz.w1 * l1.v[k]);
+      a00.v[k] += dp * w00; a01.v[k] += dp * w01; a10.v[k] += dp * w10; a11.v[k] += dp * w11;
+    }
+  }
+  const int x0 = x0p - 1, y0 = y0p - 1;
+  float* gp = lv.gplane[l] + ((long long)b * H * W) * lv.C + ch * 8;
+  const bool xa = x0 >= 0, xb = x0 + 1 < W, ya = y0 >= 0, yb = y0 + 1 < H;
+  if (ya && xa) rmw_add8(gp + ((long long)y0 * W + x0) * lv.C, a00);
+  if (ya && xb) rmw_add8(gp + ((long long)y0 * W + x0 + 1) * lv.C, a01);
+  if (yb && xa) rmw_add8(gp + ((long long)(y0 + 1) * W + x0) * lv.C, a10);
+  if (yb && xb) rmw_add8(gp + ((long long)(y0 + 1) * W + x0 + 1) * lv.C, a11);
+}
+
+__device__ __forceinline__ long long lower_bound_u64(const unsigned long long* a, long long n, unsigned long long v) {
+  long long lo = 0, hi = n;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if (a[mid] < v) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// one warp per (z cell, channel group)
+template <typename T, typename GT>
+__global__ void __launch_bounds__(256)
+vm_bwd_sorted_line_kernel(const float4* __restrict__ coords, VMLevels lv, int l, const GT* __restrict__ dout, int out_stride,
+                          const unsigned long long* __restrict__ keys, const unsigned* __restrict__ vals, long long max_n,
+                          int colour) {
+  const int CH = lv.C >> 3;
+  const int H = lv.H[l], W = lv.W[l], Z = lv.Z[l];
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long cell = warp / CH;
+  const int ch = (int)(warp - cell * CH);
+  if (cell >= (long long)lv.B * (Z + 1)) return;
+  const int z0p = (int)(cell % (Z + 1));
+  if ((z0p & 1) != colour) return;
+  const int b = (int)(cell / (Z + 1));
+  const long long start = lower_bound_u64(keys, max_n, (unsigned long long)cell);
+  const long long end = lower_bound_u64(keys, max_n, (unsigned long long)cell + 1);
+  F8 a0, a1;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a0.v[k] = a1.v[k] = 0.f;
+  const T* pl = reinterpret_cast<const T*>(lv.plane[l]) + ((long long)b * H * W) * lv.C + ch * 8;
+  for (long long j = start + lane; j < end; j += 32) {
+    const long long n = vals[j];
+    const float4 q = __ldg(coords + n);
+    const Corner2 cx = taps(q.x, W), cy = taps(q.y, H), cz = taps(q.z, Z);
+    const F8 p00 = load8(pl + ((long long)cy.i0 * W + cx.i0) * lv.C), p01 = load8(pl + ((long long)cy.i0 * W + cx.i1) * lv.C);
+    const F8 p10 = load8(pl + ((long long)cy.i1 * W + cx.i0) * lv.C), p11 = load8(pl + ((long long)cy.i1 * W + cx.i1) * lv.C);
+    const F8 g = load8(dout + n * out_stride + l * lv.C + ch * 8);
+    const float w00 = cy.w0 * cx.w0, w01 = cy.w0 * cx.w1, w10 = cy.w1 * cx.w0, w11 = cy.w1 * cx.w1;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float dl = g.v[k] * (w00 * p00.v[k] + w01 * p01.v[k] + w10 * p10.v[k] + w11 * p11.v[k]);
+      a0.v[k] += dl * cz.w0; a1.v[k] += dl * cz.w1;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    for (int o = 16; o > 0; o >>= 1) {
+      a0.v[k] += __shfl_xor_sync(0xffffffffu, a0.v[k], o);
+      a1.v[k] += __shfl_xor_sync(0xffffffffu, a1.v[k], o);
+    }
+  if (lane != 0 || start == end) return;
+  const int z0 = z0p - 1;
+  float* gl = lv.gline[l] + ((long long)b * Z) * lv.C + ch * 8;
+  if (z0 >= 0) rmw_add8(gl + (long long)z0 * lv.C, a0);
+  if (z0 + 1 < Z) rmw_add8(gl + (long long)(z0 + 1) * lv.C, a1);
+}
+
 // ---- fused density head --------------------------------------------------------------------------
 // sigma = act(relu?(sum_c w_c * feature_c)): the lookup, the 1-wide linear layer (or plain channel sum)
 // and the activation of the reference's density path (benchmarks/nerf/gridnerf/gridnerf.py:177-197,
@@ -366,5 +509,51 @@ LMB_API int lmb_vm_density_bwd(const float* coords, const int* count_ptr, long l
   else
     vm_density_bwd_kernel<__nv_bfloat16><<<blocks, 256, smem, stream>>>(c4, count_ptr, max_n, *levels, head, dsigma, pre, dw);
   LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int lmb_radix_sort_pairs(uint64_t* keys, uint32_t* vals, const int* count_ptr, long long max_n, int begin_bit, int end_bit,
+                                    void* scratch, cudaStream_t stream);
+
+static int bits_for(unsigned long long n_keys) {      // enough bits that the all-ones "no key" sorts after every real key
+  int bits = 1;
+  while ((1ull << bits) <= n_keys) ++bits;
+  return bits;
+}
+
+// Deterministic backward.  pkeys / zkeys: uint64 [max_n]; pvals / zvals: uint32 [max_n]; sort_scratch: lmb_radix_sort_scratch_bytes(max_n).
+LMB_API int lmb_vm_encode_bwd_sorted(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
+                                     int param_dtype, const void* dout, int dout_dtype, int dout_stride, uint64_t* pkeys,
+                                     uint32_t* pvals, uint64_t* zkeys, uint32_t* zvals, void* sort_scratch, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
+  const int CH = levels->C / 8;
+  const float4* c4 = reinterpret_cast<const float4*>(coords);
+  const int stride = dout_stride > 0 ? dout_stride : levels->L * levels->C;
+  for (int l = 0; l < levels->L; ++l) {
+    const int H = levels->H[l], W = levels->W[l], Z = levels->Z[l], B = levels->B;
+    vm_sort_keys_kernel<<<ceil_div(max_n, 256), 256, 0, stream>>>(c4, count_ptr, max_n, B, H, W, Z, (unsigned long long*)pkeys, pvals,
+                                                                 (unsigned long long*)zkeys, zvals);
+    LMB_LAUNCH_CHECK();
+    int rc = lmb_radix_sort_pairs(pkeys, pvals, nullptr, max_n, 0, bits_for((unsigned long long)B * (H + 1) * (W + 1)), sort_scratch, stream);
+    if (rc) return rc;
+    rc = lmb_radix_sort_pairs(zkeys, zvals, nullptr, max_n, 0, bits_for((unsigned long long)B * (Z + 1)), sort_scratch, stream);
+    if (rc) return rc;
+    const int pblocks = ceil_div(max_n * CH, 256);
+    const int lblocks = ceil_div((long long)B * (Z + 1) * CH * 32, 256);
+#define LAUNCH(T, G)                                                                                                              \
+    for (int colour = 0; colour < 4; ++colour)                                                                                    \
+      vm_bwd_sorted_plane_kernel<T, G><<<pblocks, 256, 0, stream>>>(c4, *levels, l, (const G*)dout, stride,                       \
+                                                                   (const unsigned long long*)pkeys, pvals, max_n, colour);      \
+    for (int colour = 0; colour < 2; ++colour)                                                                                    \
+      vm_bwd_sorted_line_kernel<T, G><<<lblocks, 256, 0, stream>>>(c4, *levels, l, (const G*)dout, stride,                        \
+                                                                  (const unsigned long long*)zkeys, zvals, max_n, colour);
+    if (param_dtype == 0 && dout_dtype == 0) { LAUNCH(float, float) }
+    else if (param_dtype == 0 && dout_dtype == 1) { LAUNCH(float, __nv_bfloat16) }
+    else if (param_dtype == 1 && dout_dtype == 0) { LAUNCH(__nv_bfloat16, float) }
+    else { LAUNCH(__nv_bfloat16, __nv_bfloat16) }
+#undef LAUNCH
+    LMB_LAUNCH_CHECK();
+  }
   return 0;
 }

@@ -159,6 +159,23 @@ def case_vm_bwd(args):
     return _report("vm_encode_bwd_kernel<bf16,bf16>", ms, best, bytes_=args.rows * (6 * C * 2 + C * 2 + 6 * C * 4 + 16.0), channels=C)
 
 
+def case_vm_bwd_sorted(args):
+    from . import vm
+    from .vm import vm_encode
+
+    planes, lines, coords = _vm_setup(args)
+    C = args.channels
+    out = vm_encode(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines], out_dtype=torch.bfloat16)
+    dout = torch.randn_like(out)
+    vm.DETERMINISTIC_BACKWARD = True
+    try:
+        ms, best = time_kernel(lambda: out.backward(dout, retain_graph=True), args.iters)
+    finally:
+        vm.DETERMINISTIC_BACKWARD = False
+    return _report("vm_encode backward, atomic-free (2 radix sorts + 4 plane colours + 2 line colours)", ms, best,
+                   bytes_=args.rows * (6 * C * 2 + C * 2 + 6 * C * 4 + 16.0), channels=C)
+
+
 def _rgb_decoder(n_feat: int):
     from ..models.gridnerf.gridnerf import RGBDecoder
 
@@ -288,7 +305,7 @@ def case_merge_emulated(args):
                    bytes_=rays * (world * 32 + world * 24.0), rays=rays)
 
 
-CASES = {"zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd,
+CASES = {"zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd, "vm_bwd_sorted": case_vm_bwd_sorted,
          "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
 
 

@@ -66,6 +66,31 @@ def _levels_struct(planes, lines, gplanes=None, glines=None) -> native.VMLevels:
     return lv
 
 
+# Backward flavour of the lookup: False = 16-byte vector reductions into the fp32 accumulators (fast, summation order
+# varies from run to run); True = atomic-free sorted segmented sums (bit-reproducible, about 3x slower).
+DETERMINISTIC_BACKWARD = False
+
+native.register_signature("lmb_vm_encode_bwd_sorted", [native.P, native.P, c_longlong, POINTER(native.VMLevels), c_int, native.P,
+                                                        c_int, c_int, native.P, native.P, native.P, native.P, native.P, native.P])
+native.register_signature("lmb_radix_sort_scratch_bytes", [c_longlong])
+
+
+def _sorted_backward(coords, count, lv, param_dtype, dout):
+    n = coords.shape[0]
+    dev = coords.device
+    lib = native.lib()
+    lib.lmb_radix_sort_scratch_bytes.restype = c_longlong
+    scratch = torch.empty(int(lib.lmb_radix_sort_scratch_bytes(n)), dtype=torch.uint8, device=dev)
+    pkeys = torch.empty(n, dtype=torch.int64, device=dev)
+    zkeys = torch.empty(n, dtype=torch.int64, device=dev)
+    pvals = torch.empty(n, dtype=torch.int32, device=dev)
+    zvals = torch.empty(n, dtype=torch.int32, device=dev)
+    native.check(lib.lmb_vm_encode_bwd_sorted(coords.data_ptr(), native.ptr(count), n, byref(lv), native.DTYPE_CODE[param_dtype],
+                                              dout.data_ptr(), native.DTYPE_CODE[dout.dtype], dout.shape[1], pkeys.data_ptr(),
+                                              pvals.data_ptr(), zkeys.data_ptr(), zvals.data_ptr(), scratch.data_ptr(),
+                                              native.stream_ptr()), "vm_encode_bwd_sorted")
+
+
 class _VMEncode(torch.autograd.Function):
     """Inputs: coords, count (or None), out_dtype, n_levels, shadow flag, then 2*L master tensors
     (planes..., lines...) and optionally 2*L bf16 shadow tensors that the kernels read instead."""
@@ -111,11 +136,14 @@ class _VMEncode(torch.autograd.Function):
             grads.append(sink if sink is not None else torch.zeros(m.shape, device=m.device, dtype=torch.float32))
         lv = _levels_struct(planes, lines, grads[:L], grads[L:])
         dout = dout.contiguous()
-        native.check(
-            native.lib().lmb_vm_encode_bwd(coords.data_ptr(), native.ptr(count), coords.shape[0], byref(lv),
-                                           native.DTYPE_CODE[planes[0].dtype], dout.data_ptr(),
-                                           native.DTYPE_CODE[dout.dtype], dout.shape[1], native.stream_ptr()),
-            "vm_encode_bwd")
+        if DETERMINISTIC_BACKWARD:
+            _sorted_backward(coords, count, lv, planes[0].dtype, dout)
+        else:
+            native.check(
+                native.lib().lmb_vm_encode_bwd(coords.data_ptr(), native.ptr(count), coords.shape[0], byref(lv),
+                                               native.DTYPE_CODE[planes[0].dtype], dout.data_ptr(),
+                                               native.DTYPE_CODE[dout.dtype], dout.shape[1], native.stream_ptr()),
+                "vm_encode_bwd")
         out_grads = [None if s else g for s, g in zip(sunk, grads)]
         return (None, None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
 
