@@ -209,6 +209,10 @@ class GridNeRF(BaseNeRF):
                          grid_shape=grid_shape, near_far=list(near_far))
         self.aabb = torch.as_tensor(aabb, dtype=torch.float32, device=device)
         self.run_nerf = config.run_nerf
+        if bool(config.get("deterministic_grid_grad", False)):
+            from ...ops import vm
+
+            vm.DETERMINISTIC_BACKWARD = True        # process-wide: atomic-free sorted backward of every grid lookup
         self.density_n_comp = config.n_lamb_sigma[: config.ndims]
         self.app_n_comp = config.n_lamb_sh[: config.ndims]
         self.app_dim = config.data_dim_color
@@ -255,10 +259,6 @@ class GridNeRF(BaseNeRF):
 
     def enable_shadow(self):
         cfg = self.config
-        if bool(cfg.get("deterministic_grid_grad", False)):
-            from ...ops import vm
-
-            vm.DETERMINISTIC_BACKWARD = True
         # the deferred update is exact only when every gradient comes from sample lookups, i.e. no dense
         # regulariser (L1 / TV over whole planes) is active
         dense_reg = any(float(cfg.get(k, 0.0) or 0.0) > 0 for k in
