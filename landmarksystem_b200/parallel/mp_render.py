@@ -16,6 +16,30 @@ import torch
 from .composite_merge import CompositeMerger, merge_reference
 
 
+def slice_model_to_block_window(model, part: int, parts: int):
+    """Keep only the ``part``-th of ``parts`` equal row bands of the model's spatial blocks (blocks are ordered
+    ``bx * ny + by``): the grids of every plane/line encoding are sliced and the scene manager's resident window is set
+    accordingly, so lookups outside the band return "no data".  Returns ``(first_block, n_blocks)``."""
+    sm = model.scene_manager
+    nx, ny = sm._partition
+    assert nx % parts == 0, f"{nx} block rows cannot be split evenly over {parts} ranks"
+    rows = nx // parts
+    first, count = part * rows * ny, rows * ny
+    for enc in model.modules():
+        planes, lines = getattr(enc, "plane_coef", None), getattr(enc, "line_coef", None)
+        if planes is None or lines is None:
+            continue
+        for plist in (planes, lines):
+            for p in plist:
+                if p.shape[0] == nx * ny:
+                    p.data = p.data[first:first + count].contiguous()
+        if getattr(enc, "use_shadow", False):
+            enc.enable_shadow(False)
+    sm.assign_local_block_partition([rows, ny])
+    sm.assign_relative_block_idx(first)
+    return first, count
+
+
 class ModelParallelRenderer:
     """``model`` must offer ``render_partial(rays, N_samples) -> [R, 8]`` (see ``GridNeRF.render_partial``)."""
 

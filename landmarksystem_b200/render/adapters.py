@@ -29,6 +29,10 @@ class NeRFInferenceModule(InferenceModule):
         return (torch.cat((o, d), -1),), {}
 
     def forward(self, rays):
+        mp = getattr(self.model, "_mp_renderer", None)
+        if mp is not None:                       # block model parallel: partial composites merged across the GPUs
+            rgb, depth, _ = mp.render(rays, chunk=self._chunk)
+            return rgb, depth
         ret = self.model.render_all_rays(rays, chunk_size=self._chunk)
         return ret["rgb_map"], ret["depth_map"].reshape(rays.shape[0], -1)[:, 0]
 

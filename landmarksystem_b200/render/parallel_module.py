@@ -55,6 +55,22 @@ class ParallelModule(Module):
         model.inter_model = ComponentConvertorFactory.get_convertor("parallelize").convert(model.inter_model, cfg)
         return model
 
+    def _block_parallel(self) -> bool:
+        return self._parallel_config is not None and self._parallel_config.get("mode", "channel") == "block"
+
+    def auto_block(self, model):
+        """Model parallelism by spatial blocks (``parallel_config = {"tp_size": N, "mode": "block"}``): every rank of the
+        tensor-parallel group keeps one band of the scene's blocks and renders the ray segments inside it; the per-rank
+        records are merged by the cross-GPU ordered composite (``parallel/mp_render.py``)."""
+        from ..parallel.mp_render import ModelParallelRenderer, slice_model_to_block_window
+
+        assert isinstance(model, InferenceModule), "block parallel needs an InferenceModule"
+        ctx = CommContext()
+        inner = model.inter_model
+        slice_model_to_block_window(inner, ctx.get_local_rank(ParallelMode.TENSOR_PARALLEL), self._tp_size())
+        inner._mp_renderer = ModelParallelRenderer(inner, max_rays=1 << 18, group=ctx.get_group(ParallelMode.TENSOR_PARALLEL))
+        return model
+
     def preprocess(self, *args, **kwargs):
         return self.model.preprocess(*args, **kwargs)
 
@@ -110,7 +126,9 @@ class ParallelModule(Module):
 
 class TorchParallelModule(ParallelModule):
     def _parallize(self, model: Module):
-        return self.auto_tp(model) if self._tp_size() > 1 else model
+        if self._tp_size() > 1:
+            return self.auto_block(model) if self._block_parallel() else self.auto_tp(model)
+        return model
 
 
 class KernelParallelModule(ParallelModule):
@@ -120,5 +138,5 @@ class KernelParallelModule(ParallelModule):
 
     def _parallize(self, model: Module):
         if self._tp_size() > 1:
-            model = self.auto_tp(model)
+            model = self.auto_block(model) if self._block_parallel() else self.auto_tp(model)
         return OptimizationManager(self._inference_config, self.merged_state_dict).build(model)

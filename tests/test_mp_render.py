@@ -5,7 +5,7 @@ import torch
 from landmarksystem_b200.components.scene import SceneManager
 from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF, GridNeRFConfig
 from landmarksystem_b200.parallel.composite_merge import merge_reference
-from landmarksystem_b200.parallel.mp_render import ModelParallelRenderer
+from landmarksystem_b200.parallel.mp_render import ModelParallelRenderer, slice_model_to_block_window
 from landmarksystem_b200.utils import Config
 
 
@@ -44,12 +44,21 @@ def test_block_partials_merge_to_the_full_render():
                 for p in plist:
                     p.data = p.data[r:r + 1].contiguous()
         parts.append(m.render_partial(rays, 64))
+    # the same through the engine's helper: two ranks, one band of block rows each
+    banded = []
+    for r in range(2):
+        m, _ = _build(division)
+        assert slice_model_to_block_window(m, r, 2) == (2 * r, 2)
+        assert m.density_encoding.plane_coef[0].shape[0] == 2
+        banded.append(m.render_partial(rays, 64))
+    out2 = merge_reference(torch.stack(banded), bg=1.0 if full.renderer.white_bg else 0.0)
     out = merge_reference(torch.stack(parts), bg=1.0 if full.renderer.white_bg else 0.0)
     with torch.no_grad():
         ref_rgb, ref_depth = full(rays, N_samples=64)
     assert float(out[:, 5].max()) > 0.2
     assert torch.allclose(out[:, :3].clamp(0, 1), ref_rgb, atol=1e-5)
     assert torch.allclose(out[:, 4], ref_depth, atol=1e-5)
+    assert torch.allclose(out2[:, :3].clamp(0, 1), ref_rgb, atol=1e-5) and torch.allclose(out2[:, 4], ref_depth, atol=1e-5)
 
 
 def test_single_rank_renderer_equals_model():

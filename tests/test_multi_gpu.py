@@ -52,3 +52,11 @@ def test_model_parallel_render_merge():
     sys.stdout.write(res.stdout[-2000:])
     assert res.returncode == 0, res.stderr[-3000:]
     assert "MP_RENDER_RESULTS" in res.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_engine_block_model_parallel_render():
+    res = _launch("worker_engine_block_mp.py", 2)
+    sys.stdout.write(res.stdout[-2000:])
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "ENGINE_BLOCK_MP_RESULTS" in res.stdout
