@@ -55,16 +55,31 @@ class DatasetManager:
             return int(cfg.num_mp_groups), int(cfg.dp_rank)
         return int(cfg.get("world_size", 1)), int(cfg.get("rank", 0))
 
+    _STAGES = 4
+
     def _to_device(self, rays, rgbs, idxs):
-        """Pack into one pinned staging buffer -> one async H2D copy."""
+        """Pack into a pinned staging buffer -> one async H2D copy.  The staging buffers form a ring, each guarded
+        by an event recorded after its copy: the host waits for that event before it overwrites the buffer, so a
+        host thread that runs ahead of the GPU (a training step replayed from a CUDA graph costs it almost nothing)
+        never rewrites a batch whose copy is still queued."""
         device = torch.device(self.config.device)
         packed = torch.cat((rays.reshape(-1, 6), rgbs.reshape(-1, 3), idxs.reshape(-1, 1)), dim=-1)
         if device.type != "cuda":
             return packed[:, :6], packed[:, 6:9], packed[:, 9]
-        if self._stage is None or self._stage.shape != packed.shape:
-            self._stage = torch.empty(packed.shape, dtype=packed.dtype).pin_memory()
-        self._stage.copy_(packed)
-        dev = self._stage.to(device, non_blocking=True)
+        ring = self._stage
+        if ring is None or ring["shape"] != packed.shape:
+            ring = self._stage = {"shape": packed.shape, "next": 0, "events": [None] * self._STAGES,
+                                  "bufs": [torch.empty(packed.shape, dtype=packed.dtype).pin_memory()
+                                           for _ in range(self._STAGES)]}
+        k = ring["next"]
+        ring["next"] = (k + 1) % self._STAGES
+        if ring["events"][k] is not None:
+            ring["events"][k].synchronize()
+        ring["bufs"][k].copy_(packed)
+        dev = ring["bufs"][k].to(device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(device))
+        ring["events"][k] = ev
         return dev[:, :6], dev[:, 6:9], dev[:, 9]
 
     def get_rays(self, iteration: int):

@@ -179,12 +179,17 @@ class GridNeRFTrainer(NeRFTrainer):
             total = total + cfg.Ortho_weight * m.density_encoding.vector_diffs() + m.rgb_encoding.vector_diffs()
         if self.l1_weight > 0:
             total = total + self.l1_weight * m.density_encoding.L1_loss()
-        if self.tv_weight_density > 0:
-            self.tv_weight_density *= self.lr_factor
-            total = total + self.tv_weight_density * m.density_encoding.TV_loss()
-        if self.tv_weight_app > 0:
-            self.tv_weight_app *= self.lr_factor
-            total = total + self.tv_weight_app * m.rgb_encoding.TV_loss()
+        if self.tv_weight_density > 0 or self.tv_weight_app > 0:
+            # the two weights decay with the learning rate; they live in a device tensor that is scaled in place, so a
+            # step replayed from a CUDA graph keeps decaying them (a host float would be frozen at its recorded value)
+            w = getattr(self, "_tv_weights", None)
+            if w is None or w.device != loss.device:
+                w = self._tv_weights = torch.tensor([self.tv_weight_density, self.tv_weight_app], device=loss.device)
+            w.mul_(self.lr_factor)
+            if self.tv_weight_density > 0:
+                total = total + w[0] * m.density_encoding.TV_loss()
+            if self.tv_weight_app > 0:
+                total = total + w[1] * m.rgb_encoding.TV_loss()
         if self.enable_distort:
             for key in ("distort_loss", "distort_loss1", "distort_loss_nerf"):
                 if key in all_ret:
@@ -222,9 +227,12 @@ class GridNeRFTrainer(NeRFTrainer):
         """Inputs are copied into fixed buffers; the first steps run eagerly (allocator and lazily built state
         settle), then one step is captured - forward, backward, deferred Adam and the schedule advance, all
         on device-resident counters - and every later call is a copy + one graph launch.  The graph is
-        rebuilt when the batch shape, the sample count or the optimiser object changes (grid upsampling)."""
+        rebuilt when the batch shape, the sample count, the optimiser object (grid upsampling), the occupancy mask or a
+        loss switch changes."""
         st = getattr(self, "_graph_state", None)
-        key = (tuple(rays.shape), self.nsamples, id(self.optimizer), bool(self.module.run_nerf))
+        # everything the recorded step reads from the host: a change of any of these re-records the graph
+        key = (tuple(rays.shape), self.nsamples, id(self.optimizer), bool(self.module.run_nerf), bool(self.enable_distort),
+               float(self.l1_weight), id(getattr(self.module, "alphaMask", None)))
         if st is None or st["key"] != key:
             st = {"key": key, "rays": torch.empty_like(rays), "rgbs": torch.empty_like(rgbs), "idxs": torch.empty_like(idxs),
                   "graph": None, "warm": 0, "loss": None}

@@ -255,7 +255,8 @@ def rgb_decoder_backward(decoder, x: torch.Tensor, dout: torch.Tensor, count: Op
     g3t = gbuf[o:o + 128 * 16].view(128, 16); o += 128 * 16
     g0t = gbuf[o:o + 144 * 32].view(144, 32); o += 144 * 32
     db3 = gbuf[o:o + 16]
-    grads = (g0t[:kf, :27].t(), g1[:, :150], g1[:, 150], g2[:, :128], g2[:, 128], g3t[:, :3].t(), db3[:3])
+    grads = tuple(g.contiguous() for g in (g0t[:kf, :27].t(), g1[:, :150], g1[:, 150], g2[:, :128], g2[:, 128], g3t[:, :3].t(),
+                                           db3[:3]))
     return dx, grads
 
 

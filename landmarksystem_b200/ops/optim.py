@@ -157,6 +157,12 @@ class FusedAdam(torch.optim.Optimizer):
                     state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
                 state["step"] += 1
                 shadow = getattr(p, "_lmb_shadow", None)
+                if sink is None and p.is_cuda and not grad.is_contiguous():
+                    grad = grad.contiguous()          # e.g. a transposed view handed back by a fused backward
+                if dyn is not None and p.is_cuda and not (p.dtype == torch.float32 and p.is_contiguous()
+                                                          and grad.dtype == torch.float32):
+                    raise RuntimeError("capturable FusedAdam needs contiguous fp32 CUDA parameters and gradients: the PyTorch "
+                                       "fallback would bake the host-side learning rate and step count into a recorded graph")
                 stepped = True
                 if p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
                         and grad.dtype == torch.float32 and dyn is not None:

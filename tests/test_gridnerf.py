@@ -145,3 +145,29 @@ def test_cpu_async_snapshots(tmp_path):
     assert got["state"]["iteration"] == 6 and got["meta"]["model"] == "GridNeRF"
     for k, v in tr.module.state_dict().items():
         assert torch.equal(got["state"]["model"][k], v.cpu()), k
+
+
+@pytest.mark.gpu
+def test_gpu_kernel_path_trains_as_well_as_the_plain_path(tmp_path):
+    """Same scene, same iterations: the kernel path (bf16 grids, fused sampler / density / colour head forward and backward,
+    deferred Adam, whole-step CUDA graph) reaches the photometric quality of the plain fp32 PyTorch path."""
+    from landmarksystem_b200.components.utils.image_utils import mse2psnr_npy
+
+    n = 200
+    plain = _trainer(tmp_path / "p", "cuda", n_iters=str(n), fused_optimizer="false", fused_sampler="false", fused_density="false")
+    fast = _trainer(tmp_path / "k", "cuda", n_iters=str(n), grid_dtype="bf16", runtime="Kernel", fused_mlp_train="true",
+                    lazy_adam="true", cuda_graph="true")
+    fast.module.load_state_dict(plain.module.state_dict())
+    psnr = {}
+    for name, tr in (("plain", plain), ("kernel", fast)):
+        tr.model.train()
+        torch.manual_seed(11)
+        tail = []
+        for it in range(n):
+            loss = tr.train_step(*tr.data_mgr.get_rays(it))
+            if it >= n - 20:
+                tail.append(float(loss))
+        psnr[name] = mse2psnr_npy(sum(tail) / len(tail))
+    assert fast._graph_state["graph"] is not None
+    assert psnr["plain"] > 15.0, psnr
+    assert psnr["kernel"] > psnr["plain"] - 1.0, psnr
