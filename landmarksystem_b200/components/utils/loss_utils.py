@@ -70,7 +70,13 @@ class TVLoss(nn.Module):
 # -- mip-NeRF-360 style losses --------------------------------------------------------------
 def eff_distloss(w: torch.Tensor, m: torch.Tensor, interval: torch.Tensor) -> torch.Tensor:
     """Distortion loss  sum_ij w_i w_j |m_i - m_j| + 1/3 sum_i w_i^2 d_i  (mean over rays), computed
-    with prefix sums assuming ``m`` is sorted along the last dim."""
+    with prefix sums assuming ``m`` is sorted along the last dim.  On CUDA one warp-per-ray kernel returns the loss
+    and its gradient (``ops/csrc/ray_losses.cu``)."""
+    if w.dim() == 2 and not (m.requires_grad or interval.requires_grad):
+        from ...ops import ray_losses
+
+        if ray_losses.kernels_usable(w, m, interval):
+            return ray_losses.distortion_per_ray(w, m, interval).mean()
     loss_uni = (1.0 / 3.0) * (interval * w.pow(2)).sum(dim=-1).mean()
     wm = w * m
     w_cum, wm_cum = w.cumsum(-1), wm.cumsum(-1)
@@ -92,7 +98,13 @@ def lossfun_distortion(t: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 def distortion_loss(weights_list, spacing_starts_list, spacing_ends_list) -> torch.Tensor:
     c = ray_samples_to_sdist(spacing_starts_list[-1], spacing_ends_list[-1])
-    return lossfun_distortion(c, weights_list[-1][..., 0]).mean()
+    w = weights_list[-1][..., 0]
+    if w.dim() == 2 and not c.requires_grad:
+        from ...ops import ray_losses
+
+        if ray_losses.kernels_usable(w, c):      # O(S) prefix sums in one kernel instead of the S x S matrix per ray
+            return ray_losses.distortion_per_ray(w, (c[..., 1:] + c[..., :-1]) / 2, c[..., 1:] - c[..., :-1]).mean()
+    return lossfun_distortion(c, w).mean()
 
 
 def outer(t0_starts, t0_ends, t1_starts, t1_ends, y1):
@@ -112,7 +124,14 @@ def interlevel_loss(weights_list, spacing_starts_list, spacing_ends_list) -> tor
     w = weights_list[-1][..., 0].detach()
     total = 0.0
     for weights, starts, ends in zip(weights_list[:-1], spacing_starts_list[:-1], spacing_ends_list[:-1]):
-        total = total + lossfun_outer(c, w, ray_samples_to_sdist(starts, ends), weights[..., 0]).mean()
+        t_env, w_env = ray_samples_to_sdist(starts, ends), weights[..., 0]
+        if w.dim() == 2 and w_env.shape[-1] <= 1024 and not t_env.requires_grad:
+            from ...ops import ray_losses
+
+            if ray_losses.kernels_usable(w, w_env, c, t_env):
+                total = total + ray_losses.interlevel_per_ray(c, w, t_env, w_env).sum() / w.numel()
+                continue
+        total = total + lossfun_outer(c, w, t_env, w_env).mean()
     return total
 
 

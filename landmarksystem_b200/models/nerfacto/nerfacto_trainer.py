@@ -15,6 +15,10 @@ class NerfactoTrainer(RayModelTrainer):
     model_cls = Nerfacto
 
     def make_optimizer(self, groups):
+        if torch.device(self.config.device).type == "cuda" and bool(self.config.get("fused_optimizer", True)):
+            from ...ops.optim import FusedRAdam
+
+            return FusedRAdam(groups, eps=self.config.eps)     # one device pass per tensor, gradients cleared in it
         return torch.optim.RAdam(groups, eps=self.config.eps)
 
     def before_forward(self, it: int):

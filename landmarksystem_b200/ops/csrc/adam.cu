@@ -16,7 +16,19 @@ struct AdamArgs {
   // on every replay.  l2_beta* = log2(beta*).
   const float* dyn;
   float l2_beta1, l2_beta2;
+  // mode 0: Adam, p -= lr/bias1 * m / (sqrt(v)/sqrt(bias2) + eps).  Modes 1 and 2 take the step size `A` from the host
+  // (rectified Adam): 1: p -= A * m / (sqrt(v) + eps);  2: p -= A * m (variance not yet tractable).
+  int mode;
+  float A;
 };
+
+struct AdamStep { float step, vscale; bool adaptive; };
+__device__ __forceinline__ AdamStep adam_step_of(const AdamArgs& a) {
+  AdamStep s;
+  if (a.mode == 0) { s.step = a.lr / a.bias1; s.vscale = rsqrtf(a.bias2); s.adaptive = true; }
+  else { s.step = a.A; s.vscale = 1.f; s.adaptive = a.mode == 1; }
+  return s;
+}
 
 __device__ __forceinline__ void resolve_dyn(AdamArgs& a) {
   if (a.dyn != nullptr) {
@@ -32,8 +44,7 @@ __global__ void __launch_bounds__(256)
 adam_kernel(float4* __restrict__ p, float4* __restrict__ g, float4* __restrict__ m, float4* __restrict__ v,
             uint2* __restrict__ shadow, long long n4, AdamArgs a) {
   resolve_dyn(a);
-  const float step = a.lr / a.bias1;
-  const float inv_sqrt_b2 = rsqrtf(a.bias2);
+  const AdamStep st = adam_step_of(a);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 gg = g[i], pp = p[i], mm = m[i], vv = v[i];
     float* G = &gg.x; float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
@@ -42,7 +53,7 @@ adam_kernel(float4* __restrict__ p, float4* __restrict__ g, float4* __restrict__
       float gr = G[k] * a.grad_scale + a.weight_decay * P[k];
       M[k] = a.beta1 * M[k] + (1.f - a.beta1) * gr;
       V[k] = a.beta2 * V[k] + (1.f - a.beta2) * gr * gr;
-      P[k] -= step * M[k] / (sqrtf(V[k]) * inv_sqrt_b2 + a.eps);
+      P[k] -= st.step * M[k] / (st.adaptive ? sqrtf(V[k]) * st.vscale + a.eps : 1.f);
     }
     p[i] = pp; m[i] = mm; v[i] = vv;
     g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -63,7 +74,8 @@ __global__ void adam_tail_kernel(float* p, float* g, float* m, float* v, __nv_bf
   float gr = g[i] * a.grad_scale + a.weight_decay * p[i];
   float mm = a.beta1 * m[i] + (1.f - a.beta1) * gr;
   float vv = a.beta2 * v[i] + (1.f - a.beta2) * gr * gr;
-  float pp = p[i] - (a.lr / a.bias1) * mm / (sqrtf(vv) * rsqrtf(a.bias2) + a.eps);
+  const AdamStep st = adam_step_of(a);
+  float pp = p[i] - st.step * mm / (st.adaptive ? sqrtf(vv) * st.vscale + a.eps : 1.f);
   p[i] = pp; m[i] = mm; v[i] = vv; g[i] = 0.f;
   if (shadow) shadow[i] = __float2bfloat16_rn(pp);
 }
@@ -115,7 +127,29 @@ LMB_API int lmb_adam_step(float* p, float* g, float* m, float* v, void* shadow_b
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
   a.bias1 = 1.f - powf(beta1, (float)step);
   a.bias2 = 1.f - powf(beta2, (float)step);
-  a.dyn = nullptr; a.l2_beta1 = a.l2_beta2 = 0.f;
+  a.dyn = nullptr; a.l2_beta1 = a.l2_beta2 = 0.f; a.mode = 0; a.A = 0.f;
+  return adam_launch(p, g, m, v, shadow_bf16, n, a, stream);
+}
+
+// Rectified Adam (Liu et al. 2020; the optimiser of the reference's Nerfacto trainer,
+// benchmarks/nerf/nerfacto/nerfacto_trainer.py:139): the variance rectification term depends only on the step number,
+// so it is folded into the step size on the host and the device pass is the same single sweep as Adam's.
+LMB_API int lmb_radam_step(float* p, float* g, float* m, float* v, void* shadow_bf16, long long n, float lr,
+                           float beta1, float beta2, float eps, int step, float grad_scale, float weight_decay,
+                           cudaStream_t stream) {
+  if (n <= 0) return 0;
+  AdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
+  a.bias1 = a.bias2 = 1.f; a.dyn = nullptr; a.l2_beta1 = a.l2_beta2 = 0.f;
+  const double b1 = 1.0 - pow((double)beta1, step), b2t = pow((double)beta2, step), b2 = 1.0 - b2t;
+  const double rho_inf = 2.0 / (1.0 - (double)beta2) - 1.0;
+  const double rho_t = rho_inf - 2.0 * step * b2t / b2;
+  if (rho_t > 5.0) {
+    const double rect = sqrt((rho_t - 4.0) * (rho_t - 2.0) * rho_inf / ((rho_inf - 4.0) * (rho_inf - 2.0) * rho_t));
+    a.mode = 1; a.A = (float)(lr * rect * sqrt(b2) / b1);
+  } else {
+    a.mode = 2; a.A = (float)(lr / b1);
+  }
   return adam_launch(p, g, m, v, shadow_bf16, n, a, stream);
 }
 
@@ -127,7 +161,7 @@ LMB_API int lmb_adam_step_dyn(float* p, float* g, float* m, float* v, void* shad
   AdamArgs a;
   a.lr = 0.f; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.grad_scale = grad_scale; a.weight_decay = weight_decay;
   a.bias1 = a.bias2 = 1.f;
-  a.dyn = dyn; a.l2_beta1 = (float)log2((double)beta1); a.l2_beta2 = (float)log2((double)beta2);
+  a.dyn = dyn; a.l2_beta1 = (float)log2((double)beta1); a.l2_beta2 = (float)log2((double)beta2); a.mode = 0; a.A = 0.f;
   return adam_launch(p, g, m, v, shadow_bf16, n, a, stream);
 }
 

@@ -155,6 +155,28 @@ allreduce_small_kernel(PeerPtrs staging, int world, long long n4, float4* __rest
   }
 }
 
+// ---- fan-out of streamed scene blocks ------------------------------------------------------------------------
+// Dynamic loading with several GPUs: every rank reads 1/P of a new block from pinned host memory over its own PCIe
+// link, then stores its piece into the same place of every peer's window over NVLink.  The reference has the group
+// leader read everything and broadcast it with NCCL (landmark/render/parameter_loader/buffer_manager.py:68-80).
+constexpr int kMaxFanoutSegs = 32;
+struct FanoutSegs {
+  long long off[kMaxFanoutSegs];     // byte offset inside the window, multiple of 16
+  long long bytes[kMaxFanoutSegs];   // multiple of 16
+};
+
+__global__ void __launch_bounds__(256)
+fanout_push_kernel(const char* __restrict__ local, PeerPtrs peers, FanoutSegs segs, int rank, int world) {
+  const int s = blockIdx.y;
+  const long long n16 = segs.bytes[s] >> 4;
+  const uint4* src = reinterpret_cast<const uint4*>(local + segs.off[s]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int p = 0; p < world; ++p)
+      if (p != rank) reinterpret_cast<uint4*>(reinterpret_cast<char*>(peers.p[p]) + segs.off[s])[i] = v;
+  }
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -228,5 +250,30 @@ LMB_API int lmb_allreduce_small_p2p(const long long* staging_table, int world, l
   const int blocks = (int)((n4 + 255) / 256 < 148 * 4 ? (n4 + 255) / 256 : 148 * 4);
   allreduce_small_kernel<<<blocks, 256, 0, stream>>>(st, world, n4, (float4*)out, scale);
   LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// window_table: per-rank base address of the (symmetric) window; offsets/bytes: this rank's pieces, n_segs of them.
+// The caller orders the launch after its own host-to-device copies and brackets it with peer barriers.
+LMB_API int lmb_fanout_push(const void* local_window, const long long* window_table, const long long* offsets,
+                            const long long* bytes, int n_segs, int rank, int world, cudaStream_t stream) {
+  if (world > kMaxPeers) return (int)cudaErrorInvalidValue;
+  PeerPtrs peers;
+  for (int i = 0; i < kMaxPeers; ++i) peers.p[i] = i < world ? (void*)window_table[i] : nullptr;
+  for (int base = 0; base < n_segs; base += kMaxFanoutSegs) {
+    const int n = n_segs - base < kMaxFanoutSegs ? n_segs - base : kMaxFanoutSegs;
+    FanoutSegs segs;
+    long long longest = 0;
+    for (int k = 0; k < n; ++k) {
+      if ((offsets[base + k] | bytes[base + k]) & 15) return (int)cudaErrorInvalidValue;
+      segs.off[k] = offsets[base + k]; segs.bytes[k] = bytes[base + k];
+      if (bytes[base + k] > longest) longest = bytes[base + k];
+    }
+    if (longest == 0) continue;
+    long long want = ((longest >> 4) + 255) / 256;
+    dim3 grid((unsigned)(want < 148 * 2 ? want : 148 * 2), (unsigned)n);
+    fanout_push_kernel<<<grid, 256, 0, stream>>>((const char*)local_window, peers, segs, rank, world);
+    LMB_LAUNCH_CHECK();
+  }
   return 0;
 }

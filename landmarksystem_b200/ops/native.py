@@ -69,6 +69,7 @@ _SIGNATURES = {
     "lmb_render_fwd": [P, P, P, c_int, c_int, c_float, P, P, P, P],
     "lmb_render_bwd": [P, P, P, c_int, c_int, c_float, P, P, P],
     "lmb_adam_step": [P, P, P, P, P, c_longlong, c_float, c_float, c_float, c_float, c_int, c_float, c_float, P],
+    "lmb_radam_step": [P, P, P, P, P, c_longlong, c_float, c_float, c_float, c_float, c_int, c_float, c_float, P],
     "lmb_adam_step_dyn": [P, P, P, P, P, c_longlong, P, c_float, c_float, c_float, c_float, c_float, P],
     "lmb_adam_dyn_advance": [P, c_float, P],
     "lmb_cast_bf16": [P, P, c_longlong, P],

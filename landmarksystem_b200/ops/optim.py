@@ -19,6 +19,18 @@ from . import native
 GENERATION = 0
 
 
+def radam_step_size(lr: float, beta1: float, beta2: float, step: int):
+    """Step size of rectified Adam at ``step`` and whether the adaptive denominator ``sqrt(v) + eps`` applies
+    (the variance is tractable once rho_t > 5); same arithmetic as ``lmb_radam_step``."""
+    b1, b2t = 1.0 - beta1 ** step, beta2 ** step
+    rho_inf = 2.0 / (1.0 - beta2) - 1.0
+    rho_t = rho_inf - 2.0 * step * b2t / (1.0 - b2t)
+    if rho_t > 5.0:
+        rect = ((rho_t - 4.0) * (rho_t - 2.0) * rho_inf / ((rho_inf - 4.0) * (rho_inf - 2.0) * rho_t)) ** 0.5
+        return lr * rect * (1.0 - b2t) ** 0.5 / b1, True
+    return lr / b1, False
+
+
 class FusedAdam(torch.optim.Optimizer):
     """Adam (no amsgrad).  Per-group options: ``lr, betas, eps, weight_decay``.
 
@@ -29,8 +41,11 @@ class FusedAdam(torch.optim.Optimizer):
     * ``_lmb_shadow`` - bf16 copy of the parameter, refreshed in the same kernel that updates it.
     """
 
+    rectified = False      # FusedRAdam: variance-rectified step size (same device pass)
+
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, capturable: bool = False):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        assert not (capturable and self.rectified), "the rectified variant keeps its schedule on the host"
         # capturable: every group's {learning rate, step number} lives on the device and is advanced by a
         # kernel at the end of step() (lr *= group["lr_decay"]), so a step recorded in a CUDA graph follows
         # the schedule on replay.  The optimiser owns the schedule in this mode: group["lr"] mirrors the device value
@@ -142,7 +157,7 @@ class FusedAdam(torch.optim.Optimizer):
                 if grad is None:
                     continue
                 lazy = getattr(p, "_lmb_lazy", None)
-                if lazy is not None and sink is not None:
+                if lazy is not None and sink is not None and not self.rectified:
                     # deferred update: only the texels this step's samples touched are visited
                     decay = float(group.get("lr_decay", 1.0))
                     lazy.sched.update(lr_ref=group["lr"], t_ref=lazy.steps_done + 1, decay=decay, beta1=beta1, beta2=beta2,
@@ -172,7 +187,8 @@ class FusedAdam(torch.optim.Optimizer):
                         group["weight_decay"], native.stream_ptr()), "adam_step_dyn")
                 elif p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
                         and grad.dtype == torch.float32:
-                    native.check(native.lib().lmb_adam_step(
+                    fn = native.lib().lmb_radam_step if self.rectified else native.lib().lmb_adam_step
+                    native.check(fn(
                         p.data_ptr(), grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
                         native.ptr(shadow), p.numel(), group["lr"], beta1, beta2, group["eps"], state["step"],
                         grad_scale, group["weight_decay"], native.stream_ptr()), "adam_step")
@@ -182,8 +198,15 @@ class FusedAdam(torch.optim.Optimizer):
                     state["exp_avg_sq"].mul_(beta2).addcmul_(g, g, value=1 - beta2)
                     b1 = 1 - beta1 ** state["step"]
                     b2 = 1 - beta2 ** state["step"]
-                    denom = (state["exp_avg_sq"] / b2).sqrt_().add_(group["eps"])
-                    p.addcdiv_(state["exp_avg"], denom, value=-group["lr"] / b1)
+                    if self.rectified:
+                        step_size, adaptive = radam_step_size(group["lr"], beta1, beta2, state["step"])
+                        if adaptive:
+                            p.addcdiv_(state["exp_avg"], state["exp_avg_sq"].sqrt().add_(group["eps"]), value=-step_size)
+                        else:
+                            p.add_(state["exp_avg"], alpha=-step_size)
+                    else:
+                        denom = (state["exp_avg_sq"] / b2).sqrt_().add_(group["eps"])
+                        p.addcdiv_(state["exp_avg"], denom, value=-group["lr"] / b1)
                     grad.zero_()
                     if shadow is not None:
                         shadow.copy_(p)
@@ -201,3 +224,10 @@ class FusedAdam(torch.optim.Optimizer):
                         p.grad = None
                     else:
                         p.grad.zero_()
+
+
+class FusedRAdam(FusedAdam):
+    """Rectified Adam with the same fused device pass (``torch.optim.RAdam`` of the reference's Nerfacto trainer,
+    benchmarks/nerf/nerfacto/nerfacto_trainer.py:139)."""
+
+    rectified = True

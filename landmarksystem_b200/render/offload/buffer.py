@@ -21,15 +21,35 @@ class Buffer:
         return self.local_plane_split[0] * self.local_plane_split[1]
 
 
-def create_buffers(blocks, local_plane_split, device, count: int = BUFFER_SIZE) -> List[Buffer]:
+def create_buffers(blocks, local_plane_split, device, count: int = BUFFER_SIZE, symmetric_group=None) -> List[Buffer]:
+    """``symmetric_group``: allocate every window as one peer-mapped allocation (same layout on every rank of the
+    group) so that ranks can store pieces of a block straight into each other's windows over NVLink; the buffer then
+    carries ``symm`` (the allocation) and ``offsets`` (byte offset of every tensor inside it)."""
     n_slots = int(local_plane_split[0]) * int(local_plane_split[1])
     proto = blocks[0].state_dict
+    shapes = {}
+    for key, t in proto.items():
+        lead = t.shape[0] if t.dim() > 1 and t.shape[0] == 1 else None
+        shapes[key] = (n_slots, *t.shape[1:]) if lead == 1 else (n_slots, *t.shape)
     out = []
     for _ in range(count):
         state = {}
+        if symmetric_group is None:
+            for key, t in proto.items():
+                state[key] = torch.empty(shapes[key], dtype=t.dtype, device=device)
+            out.append(Buffer(local_plane_split, state))
+            continue
+        from ...comm.symmetric import SymmetricBuffer
+
+        offsets, total = {}, 0
         for key, t in proto.items():
-            lead = t.shape[0] if t.dim() > 1 and t.shape[0] == 1 else None
-            shape = (n_slots, *t.shape[1:]) if lead == 1 else (n_slots, *t.shape)
-            state[key] = torch.empty(shape, dtype=t.dtype, device=device)
-        out.append(Buffer(local_plane_split, state))
+            offsets[key] = total
+            nbytes = t.element_size() * int(torch.tensor(shapes[key]).prod())
+            total += (nbytes + 255) // 256 * 256
+        symm = SymmetricBuffer(total, symmetric_group)
+        for key, t in proto.items():
+            state[key] = symm.view(offsets[key], shapes[key], t.dtype)
+        buf = Buffer(local_plane_split, state)
+        buf.symm, buf.offsets = symm, offsets
+        out.append(buf)
     return out

@@ -9,8 +9,12 @@ What differs by design:
   frame (same camera path) and swaps ``swap_delay`` frames later, waiting on its own event if the
   copy has not finished (the reference all-reduces a flag every frame while an update is in flight,
   buffer_manager.py:104);
-* with several ranks per group only the group leader reads the host; the others receive the window
-  by a broadcast on the side stream.
+* with several ranks per group and ``fanout`` (the default on CUDA) every rank reads 1/P of each new block from
+  its own pinned copy over its own PCIe link and stores that piece into every peer's window over NVLink
+  (``fused_comm.cu: fanout_push_kernel``, windows in peer-mapped memory, device-side barriers on the copy stream):
+  the host link, which bounds streaming, is used P times in parallel.  Without ``fanout`` only the group leader reads
+  the host and the others receive the window by a broadcast on the side stream, as in the reference
+  (buffer_manager.py:68-80).
 """
 from __future__ import annotations
 
@@ -25,13 +29,28 @@ from .buffer import BUFFER_SIZE, Buffer, create_buffers
 
 class BufferManager:
     def __init__(self, blocks: List[Block], plane_split: Sequence[int], local_plane_split: Sequence[int], device,
-                 use_nccl: bool = False, use_h2d: bool = True, group=None, swap_delay: int = 0):
+                 use_nccl: bool = False, use_h2d: bool = True, group=None, swap_delay: int = 0, fanout: bool = False):
         self.blocks, self.plane_split, self.local_plane_split = blocks, list(plane_split), list(local_plane_split)
         self.device = torch.device(device)
         self.use_nccl, self.use_h2d, self.group, self.swap_delay = use_nccl, use_h2d, group, int(swap_delay)
-        self.buffers = create_buffers(blocks, local_plane_split, self.device, BUFFER_SIZE)
-        self.active = 0
         self.cuda = self.device.type == "cuda"
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.fanout = bool(fanout) and self.cuda and self.world > 1
+        self.bytes_pushed = 0
+        if self.fanout:
+            from ctypes import c_int
+
+            from ...comm.symmetric import PeerBarrier
+            from ...ops import native
+
+            native.register_signature("lmb_fanout_push", [native.P, native.P, native.P, native.P, c_int, c_int, c_int, native.P])
+            self.use_h2d = True                       # every rank reads its share from its own pinned copy
+            self.buffers = create_buffers(blocks, local_plane_split, self.device, BUFFER_SIZE, symmetric_group=group)
+            self.barrier = PeerBarrier(group)
+        else:
+            self.buffers = create_buffers(blocks, local_plane_split, self.device, BUFFER_SIZE)
+        self.active = 0
         self.copy_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self.event: Optional[torch.cuda.Event] = None
         self.pending: Optional[List[int]] = None
@@ -41,7 +60,54 @@ class BufferManager:
     def get_buffer(self) -> Buffer:
         return self.buffers[self.active]
 
+    FANOUT_MIN_BYTES = 1 << 16      # smaller tensors are read whole by every rank
+
+    def _fill_fanout(self, target: Buffer, block_idxes: List[int]) -> None:
+        """Resident blocks move device-to-device on every rank; of a new block each rank copies piece ``rank`` of
+        every large tensor from its pinned host copy into its own window and pushes it to the peers."""
+        import ctypes
+
+        from ...ops import native
+
+        current = self.get_buffer()
+        resident = {b: s for s, b in enumerate(current.local_block_idxes)} if target is not current else {}
+        offs, sizes = [], []
+        for slot, b in enumerate(block_idxes):
+            for key, dst in target.state_dict.items():
+                if b in resident:
+                    dst[slot].copy_(current.state_dict[key][resident[b]], non_blocking=True)
+                    self.bytes_d2d += dst[slot].numel() * dst.element_size()
+                    continue
+                src = self.blocks[b].state_dict[key]
+                nbytes = src.numel() * src.element_size()
+                if nbytes < self.FANOUT_MIN_BYTES or nbytes % (16 * self.world) or not src.is_contiguous():
+                    dst[slot].copy_(src.reshape(dst[slot].shape), non_blocking=True)
+                    self.bytes_h2d += nbytes
+                    continue
+                piece = nbytes // self.world
+                lo = self.rank * piece
+                base = target.offsets[key] + slot * nbytes
+                target.symm.local[base + lo: base + lo + piece].copy_(src.reshape(-1).view(torch.uint8)[lo: lo + piece],
+                                                                      non_blocking=True)
+                self.bytes_h2d += piece
+                offs.append(base + lo)
+                sizes.append(piece)
+        target.local_block_idxes = list(block_idxes)
+        if not offs:
+            return
+        # every rank has stopped reading this window (its copy stream waited for its render stream) before anyone stores
+        # into it; after the second barrier every piece of every rank has landed
+        self.barrier()
+        arr = ctypes.c_longlong * len(offs)
+        table = (ctypes.c_longlong * self.world)(*target.symm.peer_ptrs)
+        native.check(native.lib().lmb_fanout_push(target.symm.local_ptr, table, arr(*offs), arr(*sizes), len(offs), self.rank, self.world,
+                                                  native.stream_ptr()), "fanout_push")
+        self.bytes_pushed += sum(sizes) * (self.world - 1)
+        self.barrier()
+
     def _fill(self, target: Buffer, block_idxes: List[int]) -> None:
+        if self.fanout:
+            return self._fill_fanout(target, block_idxes)
         current = self.get_buffer()
         resident = {b: s for s, b in enumerate(current.local_block_idxes)} if target is not current else {}
         for slot, b in enumerate(block_idxes):

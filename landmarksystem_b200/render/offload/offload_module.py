@@ -62,6 +62,7 @@ class OffloadModule(nn.Module):
                 group = ctx.get_group(ParallelMode.DYNAMIC_LOAD)
                 use_h2d = ctx.get_local_rank(ParallelMode.DYNAMIC_LOAD) == 0
         use_h2d = bool(config.get("use_h2d", use_h2d))
+        fanout = bool(config.get("fanout", True)) and group is not None and self.device.type == "cuda"
         if config.get("channel_last", False) and hasattr(self.inner, "channel_last"):
             self.inner.channel_last()
         dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, None: None, "fp32": None}[config.get("dtype")]
@@ -71,7 +72,7 @@ class OffloadModule(nn.Module):
         blocks = create_blocks(self.merge_config, merged, plane_split, to_internal=self._to_internal, dtype=dtype,
                                pin_memory=self.device.type == "cuda")
         self.buffer_manager = BufferManager(blocks, plane_split, config.local_plane_split, self.device, use_nccl, use_h2d,
-                                            group, int(config.get("swap_delay", 0 if group is None else 4)))
+                                            group, int(config.get("swap_delay", 0 if group is None else 4)), fanout=fanout)
         # everything that is not streamed is loaded once, the streamed parameters start empty
         rest = {k: v for k, v in merged.items() if k not in self.streamed}
         self.model.load_from_state_dict(rest, False)

@@ -52,6 +52,10 @@ class RayModelTrainer(NeRFTrainer):
         return model
 
     def make_optimizer(self, groups):
+        if torch.device(self.config.device).type == "cuda" and bool(self.config.get("fused_optimizer", True)):
+            from ..ops import FusedAdam
+
+            return FusedAdam(groups, eps=self.config.eps)     # one device pass per tensor, gradients cleared in it
         return torch.optim.Adam(groups, eps=self.config.eps)
 
     def create_optimizer(self):

@@ -60,3 +60,11 @@ def test_engine_block_model_parallel_render():
     sys.stdout.write(res.stdout[-2000:])
     assert res.returncode == 0, res.stderr[-3000:]
     assert "ENGINE_BLOCK_MP_RESULTS" in res.stdout
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_dynamic_loading_nvlink_fanout():
+    res = _launch("worker_offload_fanout.py", 2)
+    sys.stdout.write(res.stdout[-2000:])
+    assert res.returncode == 0, res.stderr[-3000:]
+    assert "OFFLOAD_FANOUT_RESULTS" in res.stdout

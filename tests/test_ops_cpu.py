@@ -59,6 +59,20 @@ def test_fused_adam_cpu_matches_torch_adam():
     assert torch.allclose(a, b, atol=1e-6)
 
 
+def test_fused_radam_cpu_matches_torch_radam():
+    from landmarksystem_b200.ops import FusedRAdam
+
+    torch.manual_seed(0)
+    a = torch.nn.Parameter(torch.randn(37))
+    b = torch.nn.Parameter(a.detach().clone())
+    o1, o2 = FusedRAdam([a], lr=0.02, eps=1e-8), torch.optim.RAdam([b], lr=0.02, eps=1e-8)
+    for _ in range(10):          # crosses the switch to the rectified update (step 6)
+        g = torch.randn(37)
+        a.grad, b.grad = g.clone(), g.clone()
+        o1.step(); o2.step()
+    assert torch.allclose(a, b, atol=1e-6)
+
+
 def test_hashgrid_reference_dense_level_interpolates():
     meta = make_meta(2, 2, 10, 4, 2.0)
     assert meta.resolutions[0] == 4 and meta.offsets[1] == 64   # 4^3 dense entries

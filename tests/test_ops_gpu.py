@@ -370,3 +370,59 @@ def test_vm_encode_sorted_backward_is_exact_and_reproducible(dtype):
     for x, y, r in zip(a, b, ref):
         assert torch.equal(x, y)                                       # reproducible to the bit
         assert torch.allclose(x, r, atol=2e-4, rtol=1e-3), (x - r).abs().max()
+
+
+@pytest.mark.gpu
+def test_fused_radam_matches_torch_radam():
+    """Rectified Adam: the fused single-pass kernel follows torch.optim.RAdam through the unrectified first steps and
+    the rectified ones (the switch happens at step 6 for beta2 = 0.999)."""
+    from landmarksystem_b200.ops import FusedRAdam
+
+    torch.manual_seed(0)
+    w0 = torch.randn(1000, 37, device="cuda")
+    a = torch.nn.Parameter(w0.clone()); b = torch.nn.Parameter(w0.clone())
+    oa, ob = FusedRAdam([a], lr=1e-2, eps=1e-8), torch.optim.RAdam([b], lr=1e-2, eps=1e-8)
+    for step in range(12):
+        g = torch.randn_like(w0) * (0.1 + step)
+        a.grad, b.grad = g.clone(), g.clone()
+        oa.step(); ob.step()
+        assert (a - b).abs().max().item() < 2e-6 * (1 + b.abs().max().item()), step
+
+
+@pytest.mark.gpu
+def test_ray_loss_kernels_match_the_pytorch_statements():
+    """Distortion loss (both spellings) and the proposal inter-level loss: value and gradient against the plain
+    PyTorch formulas on CPU in fp64-free fp32."""
+    from landmarksystem_b200.components.utils import loss_utils as lu
+
+    torch.manual_seed(0)
+    R, S, E = 300, 48, 96
+    edges = torch.sort(torch.rand(R, S + 1), dim=-1).values
+    w = torch.rand(R, S) * 0.1
+    m, d = (edges[:, 1:] + edges[:, :-1]) / 2, edges[:, 1:] - edges[:, :-1]
+    # eff_distloss spelling
+    wc = w.clone().requires_grad_(True)
+    ref = lu.eff_distloss(wc, m, d); ref.backward()
+    wg = w.cuda().requires_grad_(True)
+    out = lu.eff_distloss(wg, m.cuda(), d.cuda()); out.backward()
+    assert abs(out.item() - ref.item()) < 1e-5 * (1 + abs(ref.item()))
+    assert (wg.grad.cpu() - wc.grad).abs().max().item() < 1e-6 + 1e-4 * wc.grad.abs().max().item()
+    # nerfstudio spelling (S x S matrix on the CPU side)
+    starts, ends = edges[:, :-1, None], edges[:, 1:, None]
+    wc = w.clone().requires_grad_(True)
+    ref = lu.distortion_loss([wc[..., None]], [starts], [ends]); ref.backward()
+    wg = w.cuda().requires_grad_(True)
+    out = lu.distortion_loss([wg[..., None]], [starts.cuda()], [ends.cuda()]); out.backward()
+    assert abs(out.item() - ref.item()) < 1e-5 * (1 + abs(ref.item()))
+    assert (wg.grad.cpu() - wc.grad).abs().max().item() < 1e-6 + 1e-4 * wc.grad.abs().max().item()
+    # inter-level: proposal histogram on a coarser, unaligned partition
+    env = torch.sort(torch.rand(R, E + 1), dim=-1).values
+    env[:, 0], env[:, -1] = 0.0, 1.0
+    w_env = torch.rand(R, E) * 0.05
+    ec = w_env.clone().requires_grad_(True)
+    ref = lu.interlevel_loss([ec[..., None], w[..., None]], [env[:, :-1, None], starts], [env[:, 1:, None], ends]); ref.backward()
+    eg = w_env.cuda().requires_grad_(True)
+    out = lu.interlevel_loss([eg[..., None], w.cuda()[..., None]], [env[:, :-1, None].cuda(), starts.cuda()],
+                             [env[:, 1:, None].cuda(), ends.cuda()]); out.backward()
+    assert abs(out.item() - ref.item()) < 1e-5 * (1 + abs(ref.item()))
+    assert (eg.grad.cpu() - ec.grad).abs().max().item() < 1e-7 + 1e-4 * ec.grad.abs().max().item()
