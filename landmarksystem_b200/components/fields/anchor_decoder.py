@@ -89,6 +89,11 @@ class AnchorDecoder(BaseModule):
             prog[~transition_mask[visible_mask]] = 1.0
             neural_opacity = neural_opacity * prog
         k = self.n_offsets
+        if not self.training and not torch.is_grad_enabled() and anchor.is_cuda and neural_opacity.dtype == torch.float32:
+            from ...ops import native
+
+            if native.available():
+                return (*_decode_epilogue(anchor, grid_offsets, grid_scaling, neural_opacity, color, scale_rot, k), None, None)
         neural_opacity = neural_opacity.reshape(-1, 1)
         mask = (neural_opacity > 0.0).view(-1)
         opacity = neural_opacity[mask]
@@ -103,6 +108,33 @@ class AnchorDecoder(BaseModule):
         if self.training:
             return xyz, color, opacity, out_scaling, rot, neural_opacity, mask
         return xyz, color, opacity, out_scaling, rot, None, None
+
+
+def _decode_epilogue(anchor, offsets, scaling, opacity, color, scale_rot, k: int):
+    """Render-time tail of the decoder as one flag / scan / scatter kernel sequence (``ops/csrc/gs_aux.cu``): opacity
+    mask, order-preserving compaction and the Gaussian attributes of the kept candidates.  One host read (the count)."""
+    from ctypes import c_int, c_longlong
+
+    from ...ops import native
+
+    P = native.P
+    native.register_signature("lmb_anchor_epilogue", [P, P, P, P, P, P, c_longlong, c_int, P, P, P, P, P, P, P, P, P, P])
+    lib, dev = native.lib(), anchor.device
+    scratch_bytes = lib.lmb_scan_scratch_bytes
+    scratch_bytes.restype, scratch_bytes.argtypes = c_longlong, [c_longlong]
+    n = anchor.shape[0] * k
+    f = lambda t: t.detach().contiguous().float()  # noqa: E731
+    anchor, offsets, scaling, opacity, color, scale_rot = map(f, (anchor, offsets, scaling, opacity, color, scale_rot))
+    work = torch.empty(2, max(n, 1), dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(int(scratch_bytes(max(n, 1))), 4), dtype=torch.uint8, device=dev)
+    xyz, col, scl, rot, opa = (torch.empty(max(n, 1), w, dtype=torch.float32, device=dev) for w in (3, 3, 3, 4, 1))
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    native.check(lib.lmb_anchor_epilogue(anchor.data_ptr(), offsets.data_ptr(), scaling.data_ptr(), opacity.data_ptr(),
+                                         color.data_ptr(), scale_rot.data_ptr(), n, k, work[0].data_ptr(), work[1].data_ptr(),
+                                         scratch.data_ptr(), xyz.data_ptr(), col.data_ptr(), opa.data_ptr(), scl.data_ptr(),
+                                         rot.data_ptr(), count.data_ptr(), native.stream_ptr()), "anchor_epilogue")
+    m = int(count.item())
+    return xyz[:m], col[:m], opa[:m], scl[:m], rot[:m]
 
 
 class FusedAnchorDecoder(AnchorDecoder):

@@ -98,6 +98,33 @@ class PropPDFSampler(BaseSampler):
     def forward(self, ray_samples: RaySamples, weights: torch.Tensor, num_samples: Optional[int] = None, eps: float = 1e-5):
         n = num_samples or self.num_samples
         num_bins = n + 1
+        existing = torch.cat((ray_samples.spacing_starts[..., 0], ray_samples.spacing_ends[..., -1:, 0]), -1)
+        dev = existing.device
+        lead = existing.shape[:-1]
+        if self.train_stratified and self.training:
+            u = torch.linspace(0.0, 1.0 - 1.0 / num_bins, num_bins, device=dev).expand(*lead, num_bins)
+            rand = torch.rand((*lead, 1 if self.single_jitter else num_bins), device=dev) / num_bins
+            u = u + rand
+        else:
+            u = torch.linspace(0.0, 1.0 - 1.0 / num_bins, num_bins, device=dev) + 1.0 / (2 * num_bins)
+            u = u.expand(*lead, num_bins)
+        u = u.contiguous()
+        bins = None
+        if existing.is_cuda and existing.dim() == 2 and max(existing.shape[-1], num_bins) <= 1025:
+            from ...ops import native
+            from ...ops.pdf import prop_resample
+
+            if native.available():       # histogram, CDF, inverse-CDF search and ordered merge in one warp-per-ray kernel
+                bins = prop_resample(weights[..., 0], existing, u, self.histogram_padding, eps, self.include_original)
+        if bins is None:
+            bins = self._resample_torch(weights, existing, u, eps)
+        eu = ray_samples.spacing_to_euclidean_fn(bins)
+        return RaySamples(ray_samples.origins, ray_samples.directions, eu[:, :-1, None], eu[:, 1:, None],
+                          bins[:, :-1, None], bins[:, 1:, None], ray_samples.spacing_to_euclidean_fn,
+                          ray_samples.camera_indices)
+
+    # the same computation with PyTorch ops (CPU, or shapes beyond the kernel's shared-memory window)
+    def _resample_torch(self, weights, existing, u, eps):
         w = weights[..., 0] + self.histogram_padding
         w_sum = w.sum(-1, keepdim=True)
         padding = torch.relu(eps - w_sum)
@@ -105,16 +132,6 @@ class PropPDFSampler(BaseSampler):
         w_sum = w_sum + padding
         pdf = w / w_sum
         cdf = torch.cat((torch.zeros_like(pdf[..., :1]), torch.cumsum(pdf, -1).clamp(max=1.0)), -1)
-        dev = cdf.device
-        if self.train_stratified and self.training:
-            u = torch.linspace(0.0, 1.0 - 1.0 / num_bins, num_bins, device=dev).expand(*cdf.shape[:-1], num_bins)
-            rand = torch.rand((*cdf.shape[:-1], 1 if self.single_jitter else num_bins), device=dev) / num_bins
-            u = u + rand
-        else:
-            u = torch.linspace(0.0, 1.0 - 1.0 / num_bins, num_bins, device=dev) + 1.0 / (2 * num_bins)
-            u = u.expand(*cdf.shape[:-1], num_bins)
-        u = u.contiguous()
-        existing = torch.cat((ray_samples.spacing_starts[..., 0], ray_samples.spacing_ends[..., -1:, 0]), -1)
         inds = torch.searchsorted(cdf, u, side="right")
         below = (inds - 1).clamp(0, existing.shape[-1] - 1)
         above = inds.clamp(0, existing.shape[-1] - 1)
@@ -124,10 +141,7 @@ class PropPDFSampler(BaseSampler):
         bins = (b0 + t * (b1 - b0)).detach()
         if self.include_original:
             bins, _ = torch.sort(torch.cat((existing, bins), -1), -1)
-        eu = ray_samples.spacing_to_euclidean_fn(bins)
-        return RaySamples(ray_samples.origins, ray_samples.directions, eu[:, :-1, None], eu[:, 1:, None],
-                          bins[:, :-1, None], bins[:, 1:, None], ray_samples.spacing_to_euclidean_fn,
-                          ray_samples.camera_indices)
+        return bins
 
 
 class HashMLPDensityField(BaseModule):

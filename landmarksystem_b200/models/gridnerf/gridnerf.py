@@ -432,31 +432,44 @@ class GridNeRF(BaseNeRF):
         return t
 
     @torch.no_grad()
-    def getDenseAlpha(self, gridSize=None):
+    def getDenseAlpha(self, gridSize=None, with_xyz: bool = True):
+        """Alpha of one step at every vertex of a ``gridSize`` lattice over the scene box, evaluated slab by slab;
+        ``with_xyz=False`` returns only ``alpha [X, Y, Z]`` and never builds the dense coordinate tensor."""
         gridSize = [int(v) for v in (self.gridSize if gridSize is None else gridSize)]
         lin = [torch.linspace(0, 1, g, device=self.aabb.device) for g in gridSize]
-        samples = torch.stack(torch.meshgrid(*lin, indexing="ij"), -1)
-        dense_xyz = self.aabb[0] * (1 - samples) + self.aabb[1] * samples
-        alpha = torch.zeros_like(dense_xyz[..., 0])
+        if with_xyz:
+            samples = torch.stack(torch.meshgrid(*lin, indexing="ij"), -1)
+            dense_xyz = self.aabb[0] * (1 - samples) + self.aabb[1] * samples
+        else:
+            yz = torch.stack(torch.meshgrid(lin[1], lin[2], indexing="ij"), -1).reshape(-1, 2)
+        alpha = torch.zeros(gridSize, device=self.aabb.device)
         for i in range(gridSize[0]):
-            alpha[i] = self.compute_alpha(dense_xyz[i].reshape(-1, 3), self.stepSize).view(gridSize[1], gridSize[2])
-        return alpha, dense_xyz
+            if with_xyz:
+                pts = dense_xyz[i].reshape(-1, 3)
+            else:
+                s = torch.cat((lin[0][i].expand(yz.shape[0], 1), yz), -1)
+                pts = self.aabb[0] * (1 - s) + self.aabb[1] * s
+            alpha[i] = self.compute_alpha(pts, self.stepSize).view(gridSize[1], gridSize[2])
+        return (alpha, dense_xyz) if with_xyz else alpha
 
     @torch.no_grad()
     def updateAlphaMask(self, gridSize=(200, 200, 200), increase_alpha_thresh=0):
         cfg = self.config
         gridSize = [int(v) for v in gridSize]
-        alpha, dense_xyz = self.getDenseAlpha(gridSize)
-        dense_xyz = dense_xyz.transpose(0, 2).contiguous()
-        alpha = alpha.clamp(0, 1).transpose(0, 2).contiguous()[None, None]
-        alpha = F.max_pool3d(alpha, kernel_size=3, padding=1, stride=1).view(gridSize[::-1])
+        from ...ops.resize import alpha_mask_pool
+
+        alpha = self.getDenseAlpha(gridSize, with_xyz=False)
         thre = cfg.alpha_mask_thre * (10 ** increase_alpha_thresh)
-        alpha = (alpha >= thre).float()
-        self.alphaMask = AlphaGridMask(self.device, self.aabb, alpha)
-        valid_xyz = dense_xyz[alpha > 0.5]
-        if valid_xyz.numel() == 0:
+        # clamp, 3x3x3 max-pool, threshold, transpose to [Z, Y, X] and the occupied index box in one pass
+        mask, bbox = alpha_mask_pool(alpha, thre)
+        self.alphaMask = AlphaGridMask(self.device, self.aabb, mask)
+        bbox = bbox.tolist()
+        if bbox[3] < 0:
             return self.aabb.clone()
-        return torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
+        denom = torch.tensor([max(g - 1, 1) for g in gridSize], device=self.aabb.device, dtype=self.aabb.dtype)
+        lo = torch.tensor(bbox[:3], device=self.aabb.device, dtype=self.aabb.dtype) / denom
+        hi = torch.tensor(bbox[3:], device=self.aabb.device, dtype=self.aabb.dtype) / denom
+        return torch.stack((self.aabb[0] * (1 - lo) + self.aabb[1] * lo, self.aabb[0] * (1 - hi) + self.aabb[1] * hi))
 
     def distortion_loss(self, weight, z_vals, dists):
         mids = 0.5 * (z_vals[:, 1:] + z_vals[:, :-1])

@@ -36,6 +36,42 @@ octree_lod_mask_kernel(int n, const float* __restrict__ anchor, const float* __r
   mask[i] = (int)lv <= il;
 }
 
+// ---- Scaffold-GS anchor decode: everything after the three MLP heads -------------------------------------------
+// candidate i = (anchor a, offset j): kept when its opacity is positive; kept candidates are written densely, in
+// candidate order, as Gaussians: xyz = anchor + offset * scaling[:3], scale = scaling[3:] * sigmoid(sr[:3]),
+// rot = normalize(sr[3:7]).  Replaces the mask / boolean-index / repeat_interleave / gather chain of
+// landmark/nerf_components/model_components/fields/decoders/anchor_decoder.py:205-242 at render time.
+__global__ void __launch_bounds__(256)
+anchor_flag_kernel(const float* __restrict__ opacity, long long n, unsigned* __restrict__ flags) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) flags[i] = opacity[i] > 0.f ? 1u : 0u;
+}
+
+__global__ void __launch_bounds__(256)
+anchor_epilogue_kernel(const float* __restrict__ anchor, const float* __restrict__ offsets, const float* __restrict__ scaling,
+                       const float* __restrict__ opacity, const float* __restrict__ color, const float* __restrict__ scale_rot,
+                       long long n, int k, const unsigned* __restrict__ flags, const unsigned* __restrict__ pos,
+                       float* __restrict__ xyz_o, float* __restrict__ color_o, float* __restrict__ opacity_o,
+                       float* __restrict__ scaling_o, float* __restrict__ rot_o, int* __restrict__ count) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (i == n - 1) *count = (int)(pos[i] + flags[i]);
+  if (!flags[i]) return;
+  const long long a = i / k, o = pos[i];
+  const float* sc = scaling + a * 6;
+  const float* sr = scale_rot + i * 7;
+#pragma unroll
+  for (int c = 0; c < 3; ++c) {
+    xyz_o[o * 3 + c] = anchor[a * 3 + c] + offsets[i * 3 + c] * sc[c];
+    color_o[o * 3 + c] = color[i * 3 + c];
+    scaling_o[o * 3 + c] = sc[3 + c] * (1.f / (1.f + __expf(-sr[c])));
+  }
+  const float q0 = sr[3], q1 = sr[4], q2 = sr[5], q3 = sr[6];
+  const float inv = 1.f / fmaxf(sqrtf(q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3), 1e-12f);
+  rot_o[o * 4 + 0] = q0 * inv; rot_o[o * 4 + 1] = q1 * inv; rot_o[o * 4 + 2] = q2 * inv; rot_o[o * 4 + 3] = q3 * inv;
+  opacity_o[o] = opacity[i];
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -48,6 +84,25 @@ LMB_API int lmb_octree_lod_mask(int n, const float* anchor, const float* level, 
   octree_lod_mask_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(n, anchor, level, extra_level, cx, cy, cz, half_voxel, fork,
                                                               standard_dist, resolution_scale, max_level, mode, mask,
                                                               prog_ratio, transition);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_exclusive_scan_u32(const uint32_t* in, uint32_t* out, long long n, void* scratch, cudaStream_t stream);
+
+// n = anchors * k candidates.  flags, pos: uint32 [n] work arrays; scan_scratch: lmb_scan_scratch_bytes(n) bytes.
+// Outputs have capacity n rows; *count = rows written.
+LMB_API int lmb_anchor_epilogue(const float* anchor, const float* offsets, const float* scaling, const float* opacity,
+                                const float* color, const float* scale_rot, long long n, int k, unsigned* flags, unsigned* pos,
+                                void* scan_scratch, float* xyz_o, float* color_o, float* opacity_o, float* scaling_o, float* rot_o,
+                                int* count, cudaStream_t stream) {
+  if (n <= 0) return (int)cudaMemsetAsync(count, 0, sizeof(int), stream);
+  anchor_flag_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(opacity, n, flags);
+  LMB_LAUNCH_CHECK();
+  const int rc = lmb_exclusive_scan_u32(flags, pos, n, scan_scratch, stream);
+  if (rc) return rc;
+  anchor_epilogue_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(anchor, offsets, scaling, opacity, color, scale_rot, n, k, flags, pos,
+                                                              xyz_o, color_o, opacity_o, scaling_o, rot_o, count);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -29,6 +29,51 @@ resize_bilinear_nhwc_kernel(const float4* __restrict__ src, float4* __restrict__
   }
 }
 
+// ---- occupancy (alpha) mask rebuild ----------------------------------------------------------------------------
+// alpha [X, Y, Z] (dense evaluation of the field) -> mask [Z, Y, X] = (max over the 3x3x3 neighbourhood of
+// clamp(alpha, 0, 1) >= thre), plus the index bounding box of the occupied voxels (bbox = {min x, y, z, max x, y, z},
+// initialised by the caller to {X, Y, Z, -1, -1, -1}).  Replaces the clamp / transpose / max_pool3d / compare / boolean
+// gather / amin / amax sequence of benchmarks/nerf/gridnerf/gridnerf.py:380-413 with one pass and no dense coordinate
+// tensor.
+__global__ void __launch_bounds__(256)
+alpha_pool_kernel(const float* __restrict__ alpha, int X, int Y, int Z, float thre, float* __restrict__ mask,
+                  int* __restrict__ bbox) {
+  const long long n = (long long)X * Y * Z;
+  int lo[3] = {X, Y, Z}, hi[3] = {-1, -1, -1};
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int x = (int)(i % X), y = (int)((i / X) % Y), z = (int)(i / ((long long)X * Y));     // output order [Z, Y, X]
+    float m = 0.f;
+    for (int dx = -1; dx <= 1; ++dx) {
+      const int xx = x + dx;
+      if (xx < 0 || xx >= X) continue;
+      for (int dy = -1; dy <= 1; ++dy) {
+        const int yy = y + dy;
+        if (yy < 0 || yy >= Y) continue;
+        const float* row = alpha + ((long long)xx * Y + yy) * Z;
+        for (int dz = -1; dz <= 1; ++dz) {
+          const int zz = z + dz;
+          if (zz < 0 || zz >= Z) continue;
+          m = fmaxf(m, fminf(fmaxf(row[zz], 0.f), 1.f));
+        }
+      }
+    }
+    const bool on = m >= thre;
+    mask[i] = on ? 1.f : 0.f;
+    if (on) {
+      lo[0] = min(lo[0], x); lo[1] = min(lo[1], y); lo[2] = min(lo[2], z);
+      hi[0] = max(hi[0], x); hi[1] = max(hi[1], y); hi[2] = max(hi[2], z);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    for (int o = 16; o > 0; o >>= 1) {
+      lo[k] = min(lo[k], __shfl_xor_sync(0xffffffffu, lo[k], o));
+      hi[k] = max(hi[k], __shfl_xor_sync(0xffffffffu, hi[k], o));
+    }
+    if ((threadIdx.x & 31) == 0 && hi[k] >= 0) { atomicMin(&bbox[k], lo[k]); atomicMax(&bbox[3 + k], hi[k]); }
+  }
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -39,6 +84,15 @@ LMB_API int lmb_resize_bilinear_nhwc(const float* src, float* dst, int B, int H,
   const long long want = (total + 255) / 256;
   const int blocks = (int)(want < 148LL * 32 ? want : 148LL * 32);
   resize_bilinear_nhwc_kernel<<<blocks, 256, 0, stream>>>((const float4*)src, (float4*)dst, B, H, W, H2, W2, C / 4);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+LMB_API int lmb_alpha_pool(const float* alpha, int X, int Y, int Z, float thre, float* mask, int* bbox, cudaStream_t stream) {
+  const long long n = (long long)X * Y * Z;
+  if (n <= 0) return 0;
+  const long long want = (n + 255) / 256;
+  alpha_pool_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(alpha, X, Y, Z, thre, mask, bbox);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -48,6 +48,22 @@ def test_cpu_training_reduces_loss_and_roundtrips(tmp_path):
     assert torch.allclose(a, b, atol=1e-6)
 
 
+def test_cpu_alpha_mask_rebuild_after_training(tmp_path):
+    """Occupancy mask rebuild (dense alpha -> 3^3 max-pool -> threshold): the mask has the [Z, Y, X] layout, the
+    returned box lies inside the scene box and contains the blob, and rendering with the mask still works."""
+    tr = _trainer(tmp_path, "cpu")
+    tr.model.train()
+    for it in range(30):
+        tr.train_step(*tr.data_mgr.get_rays(it))
+    m = tr.module
+    new_aabb = m.updateAlphaMask((20, 24, 28))
+    assert tuple(m.alphaMask.alpha_volume.shape[-3:]) == (28, 24, 20)
+    assert (new_aabb[0] >= m.aabb[0] - 1e-6).all() and (new_aabb[1] <= m.aabb[1] + 1e-6).all()
+    assert (new_aabb[0] <= 0).all() and (new_aabb[1] >= 0).all()          # the blob sits at the origin
+    loss = float(tr.train_step(*tr.data_mgr.get_rays(30)))
+    assert loss == loss
+
+
 @pytest.mark.gpu
 def test_gpu_step_matches_cpu(tmp_path):
     cpu = _trainer(tmp_path / "c", "cpu", fused_optimizer="false")

@@ -426,3 +426,65 @@ def test_ray_loss_kernels_match_the_pytorch_statements():
                              [env[:, 1:, None].cuda(), ends.cuda()]); out.backward()
     assert abs(out.item() - ref.item()) < 1e-5 * (1 + abs(ref.item()))
     assert (eg.grad.cpu() - ec.grad).abs().max().item() < 1e-7 + 1e-4 * ec.grad.abs().max().item()
+
+
+@pytest.mark.gpu
+def test_proposal_resample_kernel_matches_the_pytorch_statement():
+    """Histogram -> CDF -> inverse-CDF samples -> ordered merge with the existing edges, against the PyTorch chain
+    (cumsum, searchsorted, gathers, concatenate + sort) of the same sampler."""
+    from landmarksystem_b200.components.ray_samplers.proposal_network_sampler import PropPDFSampler
+    from landmarksystem_b200.ops.pdf import prop_resample
+
+    torch.manual_seed(0)
+    R, E, n = 500, 96, 48
+    existing = torch.sort(torch.rand(R, E + 1, device="cuda"), dim=-1).values
+    weights = torch.rand(R, E, 1, device="cuda") ** 3
+    weights[::7] = 0.0                                      # rays without any weight: the histogram is its padding
+    for include in (True, False):
+        s = PropPDFSampler(n, include_original=include)
+        u = (torch.arange(n + 1, device="cuda") + torch.rand(R, n + 1, device="cuda")) / (n + 1)
+        ref = s._resample_torch(weights, existing, u.contiguous(), 1e-5)
+        out = prop_resample(weights[..., 0], existing, u, s.histogram_padding, 1e-5, include)
+        assert out.shape == ref.shape
+        assert (out[:, 1:] >= out[:, :-1]).all()
+        assert (out - ref).abs().max().item() < 2e-5
+
+
+@pytest.mark.gpu
+def test_alpha_mask_pool_kernel_matches_max_pool3d():
+    from landmarksystem_b200.ops.resize import alpha_mask_pool
+
+    torch.manual_seed(0)
+    alpha = torch.rand(37, 20, 51) ** 8 * 1.3                  # sparse, some values above 1 (clamped)
+    alpha[:3] = 0; alpha[:, :2] = 0; alpha[..., 45:] = 0       # empty margins: the index box is a strict sub-box
+    mask_ref, box_ref = alpha_mask_pool(alpha, 0.3)
+    mask, box = alpha_mask_pool(alpha.cuda(), 0.3)
+    assert torch.equal(mask.cpu(), mask_ref) and torch.equal(box.cpu(), box_ref)
+    empty, box = alpha_mask_pool(torch.zeros(5, 6, 7, device="cuda"), 0.3)
+    assert empty.sum() == 0 and box.tolist()[3:] == [-1, -1, -1]
+
+
+@pytest.mark.gpu
+def test_anchor_decode_epilogue_kernel_matches_the_indexing_path():
+    """Scaffold-GS decoder at render time: the flag / scan / scatter kernels against the boolean-index path (same
+    module in training mode under no_grad is not an option - it returns extra tensors - so the oracle is the CPU)."""
+    from landmarksystem_b200.components.fields.anchor_decoder import AnchorDecoder
+
+    torch.manual_seed(0)
+    dec = AnchorDecoder(use_feat_bank=True, add_opacity_dist=False, add_color_dist=False, add_cov_dist=False, view_dim=3,
+                        feat_dim=32, n_offsets=5).eval()
+    n = 3000
+    anchor, feat = torch.randn(n, 3), torch.randn(n, 32)
+    offset, scaling = torch.randn(n, 5, 3) * 0.1, torch.rand(n, 6) + 0.1
+    cam = torch.tensor([0.5, -4.0, 1.0])
+    vis = torch.rand(n) > 0.3
+    with torch.no_grad():
+        ref = dec(cam, anchor, feat, offset, scaling, vis)
+        dec_g = dec.cuda()
+        out = dec_g(cam.cuda(), anchor.cuda(), feat.cuda(), offset.cuda(), scaling.cuda(), vis.cuda())
+    assert out[5] is None and out[6] is None
+    # candidates whose opacity is within rounding of zero may be kept on one side only: compare on the common set
+    assert abs(out[0].shape[0] - ref[0].shape[0]) <= 3
+    if out[0].shape[0] == ref[0].shape[0]:
+        for a, b in zip(out[:5], ref[:5]):
+            assert torch.allclose(a.cpu(), b, atol=2e-4, rtol=1e-3)
