@@ -147,8 +147,101 @@ def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = 20):
             if k >= 3:
                 times.append(start.elapsed_time(end))
     ms = statistics.median(times)
+    visible = int((radii > 0).sum())
+    # Training step on the same 6 M Gaussians: render one 1080p view from raw parameters (log-scales, unnormalised
+    # quaternions, opacity logits), L1 + SSIM loss (fused kernel) against an image rendered from perturbed colours,
+    # backward through the rasteriser, fused Adam over all 59 parameters per Gaussian.
+    from landmarksystem_b200.ops import FusedAdam
+    from landmarksystem_b200.ops.ssim import fused_l1_ssim
+
+    raw = [torch.nn.Parameter(t) for t in (means, scales.log(), rots.clone(), torch.logit(opac.clamp(1e-4, 1 - 1e-4)), shs)]
+    opt = FusedAdam([{"params": [raw[0]], "lr": 1.6e-4}, {"params": [raw[1]], "lr": 5e-3}, {"params": [raw[2]], "lr": 1e-3},
+                     {"params": [raw[3]], "lr": 5e-2}, {"params": [raw[4]], "lr": 2.5e-3}], eps=1e-15)
+    train_times = []
+    for k in range(3 + 10):
+        ang = 2 * math.pi * (k * 23 % 300) / 300.0
+        eye = torch.tensor([260.0 * math.cos(ang), 260.0 * math.sin(ang), 120.0])
+        cam = Camera.from_c2w(look_at(eye, torch.zeros(3), up=(0.0, 0.0, 1.0)).numpy(), W, H, focal_x=focal, zfar=2000.0).to(dev)
+        st = GaussianRasterizationSettings(H, W, cam.tanfovx, cam.tanfovy, bg, 1.0, cam.world_view_transform,
+                                           cam.full_proj_transform, 3, cam.camera_center)
+        with torch.no_grad():
+            target, _, _ = GaussianRasterizer(st)(raw[0], None, torch.sigmoid(raw[3]), shs=raw[4] + 0.05, scales=raw[1].exp(),
+                                                  rotations=torch.nn.functional.normalize(raw[2], dim=-1))
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        img, _, _ = GaussianRasterizer(st)(raw[0], None, torch.sigmoid(raw[3]), shs=raw[4], scales=raw[1].exp(),
+                                           rotations=torch.nn.functional.normalize(raw[2], dim=-1))
+        l1, ssim_val = fused_l1_ssim(img, target)
+        loss = 0.8 * l1 + 0.2 * (1.0 - ssim_val)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        end.record()
+        torch.cuda.synchronize()
+        if k >= 3:
+            train_times.append(start.elapsed_time(end))
+    train_ms = statistics.median(train_times)
     return {"metric": "3DGS 1080p render FPS", "value": 1000.0 / ms, "ms_per_frame": ms, "gaussians": n_gauss,
-            "visible": int((radii > 0).sum()), "frames": frames}
+            "visible": visible, "frames": frames,
+            "train": {"metric": "3DGS training iterations/s (1080p view, 6 M Gaussians, L1 + SSIM, fused Adam)",
+                      "value": 1000.0 / train_ms, "ms_per_iter": train_ms, "iters": len(train_times),
+                      "loss_finite": bool(torch.isfinite(loss))}}
+
+
+def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4, profile: bool = False):
+    """Secondary figure: InstantNGP training rays/s on one GPU at the second benchmark shape - 16-level hash grid with
+    2 features per level, 2^22 entries per level, base resolution 16, finest 8192, 1x64 density and 2x64 colour heads with
+    SH degree-4 view encoding, 128^3 occupancy grid, 2^18 rays per step - through ``NGPTrainer.train_step`` on synthetic rays
+    aimed at the unit scene box with random target colours."""
+    import tempfile
+
+    import torch
+
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.instant_ngp.instant_ngp_trainer import NGPTrainer
+
+    conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "landmarksystem_b200", "models", "instant_ngp", "confs",
+                        "synthetic_tiny.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": tempfile.mkdtemp(prefix="lmb_ngp_bench_"), "device": "cuda", "n_iters": "100000",
+                                      "progress_refresh_rate": "1000000", "runtime": "Kernel", "num_levels": "16",
+                                      "base_res": "16", "max_res": "8192", "log2_hashmap_size": "22", "grid_resolution": "128",
+                                      "grid_levels": "1", "batch_size": str(rays_per_step), "datadir": "ring:3:16x16:20:3"})
+    trainer = NGPTrainer(cfg)
+    trainer.model.train()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)
+    pool = 4
+    ang = torch.rand(pool, rays_per_step, device=dev, generator=g) * 2 * math.pi
+    origin = torch.stack((3.0 * torch.cos(ang), 3.0 * torch.sin(ang), torch.rand(pool, rays_per_step, device=dev, generator=g) - 0.5), -1)
+    aim = torch.rand(pool, rays_per_step, 3, device=dev, generator=g) * 1.6 - 0.8
+    rays = torch.cat((origin, torch.nn.functional.normalize(aim - origin, dim=-1)), -1)
+    rgbs = torch.rand(pool, rays_per_step, 3, device=dev, generator=g)
+    idxs = torch.zeros(rays_per_step, device=dev)
+    times = []
+    for k in range(warmup + steps):
+        trainer.iteration = k
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        loss = trainer.train_step(rays[k % pool], rgbs[k % pool], idxs)
+        end.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(start.elapsed_time(end))
+    if profile:
+        from torch.profiler import ProfilerActivity
+        from torch.profiler import profile as torch_profile
+
+        with torch_profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for k in range(2):
+                trainer.iteration = warmup + steps + k
+                trainer.train_step(rays[k % pool], rgbs[k % pool], idxs)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=80), file=sys.stderr)
+    ms = statistics.median(times)
+    return {"metric": "InstantNGP training rays/s (1 GPU, 2^18 rays per step, 16 x 2^22 hash grid)", "value": rays_per_step / ms * 1e3,
+            "ms_per_step": ms, "steps": steps, "loss_finite": bool(torch.isfinite(loss))}
 
 
 def render_fps_gridnerf(trainer, frames: int = 3):
@@ -289,7 +382,8 @@ def run_ours(args):
     if n == 1 and not os.environ.get("LMB_BENCH_NO_EXTRA"):
         also = []
         for name, fn in (("GridNeRF 1080p render FPS", lambda: render_fps_gridnerf(trainer)),
-                         ("3DGS 1080p render FPS", render_fps_3dgs)):
+                         ("3DGS 1080p render FPS", render_fps_3dgs),
+                         ("InstantNGP training rays/s", train_rate_ngp)):
             try:
                 also.append(fn())
             except Exception as exc:  # the headline number must not depend on the secondary ones
@@ -325,7 +419,21 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp"],
+                    help="run one secondary single-GPU benchmark alone and print its JSON (--profile adds the PyTorch "
+                         "profiler's kernel table of two more steps on stderr)")
+    ap.add_argument("--profile", action="store_true")
     args = ap.parse_args()
+    if args.only is not None:
+        import torch
+
+        torch.cuda.set_device(0)
+        fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp}[args.only]
+        if args.profile and args.only == "ngp":
+            print(json.dumps(train_rate_ngp(profile=True)))
+        else:
+            print(json.dumps(fn()))
+        return
     assert args.gpus in DIVISIONS, "supported GPU counts: 1, 2, 4, 8"
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -45,10 +45,15 @@ class MLPDecoder(BaseModule):
     def linears(self):
         return [m for m in self.mlp if isinstance(m, torch.nn.Linear)]
 
-    def forward(self, features: torch.Tensor) -> torch.Tensor:
-        if self.use_fused and features.is_cuda:
+    def forward(self, features) -> torch.Tensor:
+        """``features``: ``[N, K]`` or a sequence of ``[N, k_i]`` parts (concatenated along the last dimension; the
+        fused path writes them straight into the kernel's bf16 input instead of materialising the concatenation)."""
+        first = features[0] if isinstance(features, (tuple, list)) else features
+        if self.use_fused and first.is_cuda:
             from ...ops.fused_mlp import fused_mlp_supported, mlp_forward
 
             if fused_mlp_supported(self):
                 return mlp_forward(self, features)
+        if isinstance(features, (tuple, list)):
+            features = torch.cat([f.to(first.dtype) for f in features], dim=-1)
         return self.mlp(features)

@@ -189,10 +189,13 @@ class InstantNGP(BaseNeRF):
             density, geo = self.get_density(xyz, torch.zeros_like(xyz), torch.zeros_like(xyz[:, :1]))
             d = self.direction_encoding(get_normalized_directions(dirs))
             if self.training:
-                app = self.embedding_appearance(flat[idx, 4].long().clamp(0, c.appearance_embedding_size - 1))
+                # one embedding row per RAY, gathered per sample: the embedding's backward then reduces R rows instead
+                # of sorting R x S sample indices
+                per_ray = self.embedding_appearance(samples.data[:, 0, 4].long().clamp(0, c.appearance_embedding_size - 1))
+                app = per_ray[idx // S]
             else:
                 app = torch.zeros(idx.numel(), c.appearance_embedding_dim, device=rays.device)
-            color = self.mlp_head(torch.cat((d, geo, app), dim=-1)).float()
+            color = self.mlp_head((d, geo, app)).float()
             sigma = sigma.index_put((idx,), density[:, 0])
             rgb = rgb.index_put((idx,), color)
         dists = (samples.t_ends - samples.t_starts) * valid

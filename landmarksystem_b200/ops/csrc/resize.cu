@@ -41,7 +41,8 @@ alpha_pool_kernel(const float* __restrict__ alpha, int X, int Y, int Z, float th
   const long long n = (long long)X * Y * Z;
   int lo[3] = {X, Y, Z}, hi[3] = {-1, -1, -1};
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const int x = (int)(i % X), y = (int)((i / X) % Y), z = (int)(i / ((long long)X * Y));     // output order [Z, Y, X]
+    // threads walk the INPUT order (z fastest): the 27 reads of a warp are contiguous runs, only the one write is strided
+    const int z = (int)(i % Z), y = (int)((i / Z) % Y), x = (int)(i / ((long long)Z * Y));
     float m = 0.f;
     for (int dx = -1; dx <= 1; ++dx) {
       const int xx = x + dx;
@@ -58,7 +59,7 @@ alpha_pool_kernel(const float* __restrict__ alpha, int X, int Y, int Z, float th
       }
     }
     const bool on = m >= thre;
-    mask[i] = on ? 1.f : 0.f;
+    mask[((long long)z * Y + y) * X + x] = on ? 1.f : 0.f;
     if (on) {
       lo[0] = min(lo[0], x); lo[1] = min(lo[1], y); lo[2] = min(lo[2], z);
       hi[0] = max(hi[0], x); hi[1] = max(hi[1], y); hi[2] = max(hi[2], z);

@@ -184,17 +184,47 @@ class _FusedMLPFn(torch.autograd.Function):
         return (grads[0], None, None, *grads[1:])
 
 
-def mlp_forward(decoder, features: torch.Tensor) -> torch.Tensor:
+class _CatPadBf16(torch.autograd.Function):
+    """``[N, w_i]`` parts -> one bf16 ``[N, width]`` row block (zero tail): the concatenate, the padding and the cast of
+    the kernel's input in one write pass; the backward hands each part its slice of the gradient."""
+
+    @staticmethod
+    def forward(ctx, width, *parts):
+        n = parts[0].shape[0]
+        out = torch.empty(n, width, device=parts[0].device, dtype=torch.bfloat16)
+        col = 0
+        for part in parts:
+            out[:, col:col + part.shape[1]].copy_(part)
+            col += part.shape[1]
+        if col < width:
+            out[:, col:].zero_()
+        ctx.meta = [(part.shape[1], part.dtype) for part in parts]
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        grads, col = [], 0
+        for k, (w, dtype) in enumerate(ctx.meta):
+            grads.append(dout[:, col:col + w].to(dtype) if ctx.needs_input_grad[k + 1] else None)
+            col += w
+        return (None, *grads)
+
+
+def mlp_forward(decoder, features) -> torch.Tensor:
+    """``features``: ``[N, K]`` tensor or a sequence of ``[N, k_i]`` tensors that are concatenated along the last
+    dimension while the kernel's bf16 input is written."""
     packed = getattr(decoder, "_lmb_packed", None)
     layers = _decoder_layers(decoder)
     in_width = (layers[0][0].shape[1] + 7) // 8 * 8
     if packed is None or packed.layers[0][0] is not layers[0][0]:
         packed = PackedMLP(layers, in_width=_pad16(layers[0][0].shape[1]), out_dim=layers[-1][0].shape[0])
         decoder._lmb_packed = packed
-    x = features
-    if x.shape[1] != packed.in_width or x.dtype != torch.bfloat16:
-        x = torch.nn.functional.pad(x, (0, packed.in_width - x.shape[1])).to(torch.bfloat16)
-    x = x.contiguous()
+    if isinstance(features, (tuple, list)):
+        x = _CatPadBf16.apply(packed.in_width, *features)
+    elif features.shape[1] != packed.in_width or features.dtype != torch.bfloat16:
+        x = _CatPadBf16.apply(packed.in_width, features)
+    else:
+        x = features.contiguous()
     params = [t for w, b, _ in layers for t in ((w, b) if b is not None else (w,))]
     if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
         return _FusedMLPFn.apply(x, packed, len(params), *params)

@@ -230,6 +230,43 @@ def case_composite(args):
     return _report("composite weights+render", ms, best, bytes_=rays * S * (4 * 3 + 4 * 5.0), rays=rays)
 
 
+def case_ray_losses(args):
+    """Distortion loss (value + gradient) and proposal inter-level loss, one warp per ray."""
+    from .ray_losses import distortion_per_ray, interlevel_per_ray
+
+    rays, S, E = max(args.rows // 128, 1), 128, 256
+    edges = torch.rand(rays, S + 1, device="cuda").sort(-1).values
+    w = (torch.rand(rays, S, device="cuda") * 0.05).requires_grad_(True)
+    m, d = (edges[:, 1:] + edges[:, :-1]) / 2, edges[:, 1:] - edges[:, :-1]
+    ms, best = time_kernel(lambda: distortion_per_ray(w, m, d), args.iters, flush_l2=True)
+    out = [_report("distortion loss fwd+grad", ms, best, bytes_=rays * S * 4 * 4.0, rays=rays)]
+    env = torch.rand(rays, E + 1, device="cuda").sort(-1).values
+    w_env = (torch.rand(rays, E, device="cuda") * 0.02).requires_grad_(True)
+    ms, best = time_kernel(lambda: interlevel_per_ray(edges, w.detach(), env, w_env), args.iters, flush_l2=True)
+    out.append(_report("interlevel loss fwd+grad", ms, best, bytes_=rays * (2 * S + 3 * E) * 4.0, rays=rays))
+    return out
+
+
+def case_prop_resample(args):
+    from .pdf import prop_resample
+
+    rays, E, B = max(args.rows // 128, 1), 256, 97
+    existing = torch.rand(rays, E + 1, device="cuda").sort(-1).values
+    w = torch.rand(rays, E, device="cuda")
+    u = ((torch.arange(B, device="cuda") + torch.rand(rays, B, device="cuda")) / B).contiguous()
+    ms, best = time_kernel(lambda: prop_resample(w, existing, u, 0.01, 1e-5, True), args.iters, flush_l2=True)
+    return _report("proposal resample + merge", ms, best, bytes_=rays * (2 * E + 1 + B + B + E + 1) * 4.0, rays=rays)
+
+
+def case_alpha_pool(args):
+    from .resize import alpha_mask_pool
+
+    n = 320
+    alpha = torch.rand(n, n, n, device="cuda") ** 6
+    ms, best = time_kernel(lambda: alpha_mask_pool(alpha, 0.3), args.iters, flush_l2=True)
+    return _report("alpha-mask pool 320^3", ms, best, bytes_=n ** 3 * 8.0)
+
+
 def case_hash_fwd(args):
     import math
 
@@ -305,7 +342,8 @@ def case_merge_emulated(args):
                    bytes_=rays * (world * 32 + world * 24.0), rays=rays)
 
 
-CASES = {"zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd, "vm_bwd_sorted": case_vm_bwd_sorted,
+CASES = {"ray_losses": case_ray_losses, "prop_resample": case_prop_resample, "alpha_pool": case_alpha_pool,
+         "zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd, "vm_bwd_sorted": case_vm_bwd_sorted,
          "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
 
 
