@@ -110,8 +110,18 @@ __device__ __forceinline__ void pe_backward_cols(const float* v, const float* f,
 }
 
 // status words: 0 ok, 1 weight load timed out, 2 input tile load timed out, 3 MMA completion timed out
+//
+// kPE = true : the colour head described above (4 GEMM layers, positional-encoding stage after the first).
+// kPE = false: a plain three-layer perceptron on the same machinery - x1 [rows, 160] is the input itself (column 159
+//              holds ones so that dW1[:, 159] is the bias gradient), h1 = relu(W1 x1 + b1), h2 = relu(W2 h1 + b2),
+//              out = act(W3 h2 + b3) with up to 16 outputs and act = sigmoid or identity; widths are zero-padded to
+//              160 -> 128 -> 128 -> 16 by the host (padded units stay at relu(0) = 0 and receive no gradient), and a
+//              two-layer network passes W2 = I, b2 = 0 (relu(h1) = h1).  This covers the 64-wide density / colour heads
+//              of the hash-grid models (benchmarks/nerf/instant_ngp/instant_ngp.py:120-170 of the reference, which
+//              trains them through tiny-cuda-nn).  dx receives all 160 input columns.
+template <bool kPE>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restrict__ blob, MLPSpec spec,
+mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restrict__ blob, MLPSpec spec,
                    const int* __restrict__ count_ptr, long long max_rows, const float* __restrict__ dout, int dout_stride,
                    __nv_bfloat16* __restrict__ dx, float* __restrict__ gbuf, int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -143,11 +153,16 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
   const int in_chunks = spec.in_width >> 3, k0_chunks = K0 >> 3;
   const uint32_t in_bytes = (uint32_t)in_chunks * kChunk, x0_bytes = (uint32_t)k0_chunks * kChunk;
   const uint32_t aA = tc05::smem_u32(bufA), aH1 = tc05::smem_u32(bufH1), aHZ = tc05::smem_u32(bufHZ), aS = tc05::smem_u32(bufS);
-  const uint32_t aW0 = tc05::smem_u32(wsm + spec.w_off[0]), aW1 = tc05::smem_u32(wsm + spec.w_off[1]);
-  const uint32_t aW2 = tc05::smem_u32(wsm + spec.w_off[2]), aW3 = tc05::smem_u32(wsm + spec.w_off[3]);
-  const float* b1 = reinterpret_cast<const float*>(wsm + spec.b_off[1]);
-  const float* b2 = reinterpret_cast<const float*>(wsm + spec.b_off[2]);
-  const float* b3 = reinterpret_cast<const float*>(wsm + spec.b_off[3]);
+  constexpr int L1 = kPE ? 1 : 0;                // index of the first 128-wide layer in the spec
+  constexpr int kOut = kPE ? 3 : 16;             // output columns that can carry a gradient
+  const uint32_t aW0 = tc05::smem_u32(wsm + spec.w_off[0]), aW1 = tc05::smem_u32(wsm + spec.w_off[L1]);
+  const uint32_t aW2 = tc05::smem_u32(wsm + spec.w_off[L1 + 1]), aW3 = tc05::smem_u32(wsm + spec.w_off[L1 + 2]);
+  const float* b1 = reinterpret_cast<const float*>(wsm + spec.b_off[L1]);
+  const float* b2 = reinterpret_cast<const float*>(wsm + spec.b_off[L1 + 1]);
+  const float* b3 = reinterpret_cast<const float*>(wsm + spec.b_off[L1 + 2]);
+  const bool out_sigmoid = spec.act[L1 + 2] == ACT_SIGMOID;
+  const int n_out = kPE ? 3 : spec.out_dim;
+  (void)aW0;
 
   bool in_pending = false, x0_pending = false;
   long long tile = blockIdx.x;
@@ -166,7 +181,9 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
 
   uint32_t ph_in = 0, ph_x0 = 0, ph_mma = 0;
   bool first = true;
-  float db3[3] = {0.f, 0.f, 0.f};
+  float db3[kOut];
+#pragma unroll
+  for (int i = 0; i < kOut; ++i) db3[i] = 0.f;
 
   // one MMA group: thread 0 has issued the instructions; commit, bounded wait, agree, fence
 #define LMB_MMA_WAIT()                                                                        \
@@ -196,42 +213,50 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
       in_pending = false;
       if (!__syncthreads_and(got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
     }
-    float dir[3];
-#pragma unroll
-    for (int i = 0; i < 3; ++i) dir[i] = valid ? load_elem(bufA, spec.dir_col + i, row) : 0.f;
+    if constexpr (kPE) {
+      float dir[3];
+  #pragma unroll
+      for (int i = 0; i < 3; ++i) dir[i] = valid ? load_elem(bufA, spec.dir_col + i, row) : 0.f;
 
-    // ================= forward recompute =================
-    if (row == 0) { tc05::fence_after_sync(); issue_fwd(tmem + kColWork, aA, aW0, K0, 32); }
-    LMB_MMA_WAIT();
-    {
-      float f[32];
-      tc05::tmem_ld16(tlane + kColWork, f);
-      tc05::tmem_ld16(tlane + kColWork + 16, f + 16);
-      float x[160];
-#pragma unroll
-      for (int i = 0; i < 27; ++i) {
-        const float fi = valid ? f[i] : 0.f;
-        x[i] = fi;
-        float s1, c1;
-        __sincosf(fi, &s1, &c1);
-        x[30 + 2 * i] = s1; x[31 + 2 * i] = 2.f * s1 * c1;
-        x[84 + 2 * i] = c1; x[85 + 2 * i] = 1.f - 2.f * s1 * s1;
+      // ================= forward recompute =================
+      if (row == 0) { tc05::fence_after_sync(); issue_fwd(tmem + kColWork, aA, aW0, K0, 32); }
+      LMB_MMA_WAIT();
+      {
+        float f[32];
+        tc05::tmem_ld16(tlane + kColWork, f);
+        tc05::tmem_ld16(tlane + kColWork + 16, f + 16);
+        float x[160];
+  #pragma unroll
+        for (int i = 0; i < 27; ++i) {
+          const float fi = valid ? f[i] : 0.f;
+          x[i] = fi;
+          float s1, c1;
+          __sincosf(fi, &s1, &c1);
+          x[30 + 2 * i] = s1; x[31 + 2 * i] = 2.f * s1 * c1;
+          x[84 + 2 * i] = c1; x[85 + 2 * i] = 1.f - 2.f * s1 * s1;
+        }
+  #pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          x[27 + i] = dir[i];
+          float s1, c1;
+          __sincosf(dir[i], &s1, &c1);
+          x[138 + 2 * i] = s1; x[139 + 2 * i] = 2.f * s1 * c1;
+          x[144 + 2 * i] = c1; x[145 + 2 * i] = 1.f - 2.f * s1 * s1;
+        }
+        x[150] = 1.f;                               // ones column: dW1[:, 150] becomes the bias gradient
+  #pragma unroll
+        for (int i = 151; i < 160; ++i) x[i] = 0.f;
+  #pragma unroll
+        for (int c = 0; c < 20; ++c) store_chunk(bufA, c, row, x + 8 * c);
       }
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        x[27 + i] = dir[i];
-        float s1, c1;
-        __sincosf(dir[i], &s1, &c1);
-        x[138 + 2 * i] = s1; x[139 + 2 * i] = 2.f * s1 * c1;
-        x[144 + 2 * i] = c1; x[145 + 2 * i] = 1.f - 2.f * s1 * s1;
+      LMB_EPILOGUE_DONE();
+    } else {
+      if (partial && !valid) {                    // rows past the end hold arbitrary bits: 0 * NaN must not reach dW1
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < in_chunks; ++c) *reinterpret_cast<uint4*>(bufA + ((size_t)c * kTileRows + row) * 16) = z;
       }
-      x[150] = 1.f;                               // ones column: dW1[:, 150] becomes the bias gradient
-#pragma unroll
-      for (int i = 151; i < 160; ++i) x[i] = 0.f;
-#pragma unroll
-      for (int c = 0; c < 20; ++c) store_chunk(bufA, c, row, x + 8 * c);
+      LMB_EPILOGUE_DONE();
     }
-    LMB_EPILOGUE_DONE();
 
     if (row == 0) issue_fwd(tmem + kColWork, aA, aW1, 160, 128);
     LMB_MMA_WAIT();
@@ -274,10 +299,12 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
       if (valid) {
         const float* g = dout + (row0 + row) * (long long)dout_stride;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) {
-          const float o = __fdividef(1.f, 1.f + __expf(-(v[i] + b3[i])));
-          dz[i] = g[i] * o * (1.f - o);
-          db3[i] += dz[i];
+        for (int i = 0; i < kOut; ++i) {
+          if (i < n_out) {
+            const float o = __fdividef(1.f, 1.f + __expf(-(v[i] + b3[i])));
+            dz[i] = out_sigmoid ? g[i] * o * (1.f - o) : g[i];
+            db3[i] += dz[i];
+          }
         }
       }
       store_chunk(bufS, 0, row, dz);
@@ -319,74 +346,119 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
     }
     LMB_EPILOGUE_DONE();
 
-    // ================= layer 1 =================
-    if (row == 0) {
-      // h1 is dead: bring the input tile back (x1 replaced it in A) for the layer-0 weight gradient
-      tc05::mbar_expect_tx(&bar_x0, x0_bytes);
-      for (int c = 0; c < k0_chunks; ++c) tc05::tma_load_3d(bufH1 + (size_t)c * kChunk, &xmap, 0, c, (int)row0, &bar_x0);
-      issue_wgrad(tmem + kColDW1, aHZ, aA, 160, !first);          // dW1 (+ db1) += dz1^T [x1 | 1]
-      issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 0, 128);        // d(x1)[:, 0:128] = dz1 W1
-    }
-    x0_pending = true;
-    LMB_MMA_WAIT();
-    float f[32], df[27];
-    load_chunk2(bufA, 0, row, f);
-    load_chunk2(bufA, 2, row, f + 16);
-#pragma unroll
-    for (int i = 0; i < 27; ++i) df[i] = 0.f;
-    {
-      float v[16];
-      tc05::tmem_ld16(tlane + kColWork + 0, v);   pe_backward_cols<0>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 16, v);  pe_backward_cols<16>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 32, v);  pe_backward_cols<32>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 48, v);  pe_backward_cols<48>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 64, v);  pe_backward_cols<64>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 80, v);  pe_backward_cols<80>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 96, v);  pe_backward_cols<96>(v, f, df);
-      tc05::tmem_ld16(tlane + kColWork + 112, v); pe_backward_cols<112>(v, f, df);
-    }
-    LMB_EPILOGUE_DONE();
-    if (row == 0) issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 16, 16);   // d(x1)[:, 128:144]
-    LMB_MMA_WAIT();
-    {
-      float v[16];
-      tc05::tmem_ld16(tlane + kColWork, v);
-      pe_backward_cols<128>(v, f, df);
-      float o[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[i] = i < 27 ? df[i] : 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) store_chunk(bufS, c, row, o + 8 * c);
-    }
-    {
-      bool got = tc05::mbar_wait(&bar_x0, ph_x0);
-      ph_x0 ^= 1;
-      x0_pending = false;
-      if (!__syncthreads_and(got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
-      if (partial && !valid) {                    // rows past the end hold arbitrary bits: 0 * NaN must not reach dW0
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int c = 0; c < k0_chunks; ++c) *reinterpret_cast<uint4*>(bufH1 + ((size_t)c * kTileRows + row) * 16) = z;
+    if constexpr (kPE) {
+      // ================= layer 1 =================
+      if (row == 0) {
+        // h1 is dead: bring the input tile back (x1 replaced it in A) for the layer-0 weight gradient
+        tc05::mbar_expect_tx(&bar_x0, x0_bytes);
+        for (int c = 0; c < k0_chunks; ++c) tc05::tma_load_3d(bufH1 + (size_t)c * kChunk, &xmap, 0, c, (int)row0, &bar_x0);
+        issue_wgrad(tmem + kColDW1, aHZ, aA, 160, !first);          // dW1 (+ db1) += dz1^T [x1 | 1]
+        issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 0, 128);        // d(x1)[:, 0:128] = dz1 W1
       }
-    }
-    LMB_EPILOGUE_DONE();
+      x0_pending = true;
+      LMB_MMA_WAIT();
+      float f[32], df[27];
+      load_chunk2(bufA, 0, row, f);
+      load_chunk2(bufA, 2, row, f + 16);
+  #pragma unroll
+      for (int i = 0; i < 27; ++i) df[i] = 0.f;
+      {
+        float v[16];
+        tc05::tmem_ld16(tlane + kColWork + 0, v);   pe_backward_cols<0>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 16, v);  pe_backward_cols<16>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 32, v);  pe_backward_cols<32>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 48, v);  pe_backward_cols<48>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 64, v);  pe_backward_cols<64>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 80, v);  pe_backward_cols<80>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 96, v);  pe_backward_cols<96>(v, f, df);
+        tc05::tmem_ld16(tlane + kColWork + 112, v); pe_backward_cols<112>(v, f, df);
+      }
+      LMB_EPILOGUE_DONE();
+      if (row == 0) issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 16, 16);   // d(x1)[:, 128:144]
+      LMB_MMA_WAIT();
+      {
+        float v[16];
+        tc05::tmem_ld16(tlane + kColWork, v);
+        pe_backward_cols<128>(v, f, df);
+        float o[32];
+  #pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = i < 27 ? df[i] : 0.f;
+  #pragma unroll
+        for (int c = 0; c < 4; ++c) store_chunk(bufS, c, row, o + 8 * c);
+      }
+      {
+        bool got = tc05::mbar_wait(&bar_x0, ph_x0);
+        ph_x0 ^= 1;
+        x0_pending = false;
+        if (!__syncthreads_and(got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
+        if (partial && !valid) {                    // rows past the end hold arbitrary bits: 0 * NaN must not reach dW0
+          const uint4 z = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < k0_chunks; ++c) *reinterpret_cast<uint4*>(bufH1 + ((size_t)c * kTileRows + row) * 16) = z;
+        }
+      }
+      LMB_EPILOGUE_DONE();
 
-    // ================= layer 0 =================
-    const long long next = tile + gridDim.x;
-    if (row == 0) {
-      if (next < n_tiles) {                       // x1 is dead: prefetch the next tile's input into A
-        tc05::mbar_expect_tx(&bar_in, in_bytes);
-        for (int c = 0; c < in_chunks; ++c) tc05::tma_load_3d(bufA + (size_t)c * kChunk, &xmap, 0, c, (int)(next * kTileRows), &bar_in);
+      // ================= layer 0 =================
+      const long long next = tile + gridDim.x;
+      if (row == 0) {
+        if (next < n_tiles) {                       // x1 is dead: prefetch the next tile's input into A
+          tc05::mbar_expect_tx(&bar_in, in_bytes);
+          for (int c = 0; c < in_chunks; ++c) tc05::tma_load_3d(bufA + (size_t)c * kChunk, &xmap, 0, c, (int)(next * kTileRows), &bar_in);
+        }
+        issue_wgrad(tmem + kColDW0T, aH1, aS, 32, !first);                         // dW0^T[0:128] += x0^T df
+        if (K0 > 128) issue_wgrad(tmem + kColDW0T + 32, aH1 + 2 * kChunk, aS, 32, !first);   // input columns 16..143
+        issue_dgrad(tmem + kColWork, aS, aW0, 32, 0, K0 < 128 ? K0 : 128);         // d(x0)[:, 0:128] = df W0
       }
-      issue_wgrad(tmem + kColDW0T, aH1, aS, 32, !first);                         // dW0^T[0:128] += x0^T df
-      if (K0 > 128) issue_wgrad(tmem + kColDW0T + 32, aH1 + 2 * kChunk, aS, 32, !first);   // input columns 16..143
-      issue_dgrad(tmem + kColWork, aS, aW0, 32, 0, K0 < 128 ? K0 : 128);         // d(x0)[:, 0:128] = df W0
-    }
-    in_pending = next < n_tiles;
-    LMB_MMA_WAIT();
-    __nv_bfloat16* dxr = dx + (row0 + row) * (long long)spec.in_width;
-    {
-      const int n_main = K0 < 128 ? K0 : 128;
-      for (int n0 = 0; n0 < n_main; n0 += 16) {
+      in_pending = next < n_tiles;
+      LMB_MMA_WAIT();
+      __nv_bfloat16* dxr = dx + (row0 + row) * (long long)spec.in_width;
+      {
+        const int n_main = K0 < 128 ? K0 : 128;
+        for (int n0 = 0; n0 < n_main; n0 += 16) {
+          float v[16];
+          tc05::tmem_ld16(tlane + kColWork + n0, v);
+          if (valid) {
+            uint4 u[2];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(u);
+  #pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(dxr + n0) = u[0];
+            *reinterpret_cast<uint4*>(dxr + n0 + 8) = u[1];
+          }
+        }
+      }
+      LMB_EPILOGUE_DONE();
+      if (K0 > 128) {
+        if (row == 0) issue_dgrad(tmem + kColWork, aS, aW0, 32, 16, K0 - 128);    // d(x0)[:, 128:K0]
+        LMB_MMA_WAIT();
+        for (int n0 = 0; n0 < K0 - 128; n0 += 16) {
+          float v[16];
+          tc05::tmem_ld16(tlane + kColWork + n0, v);
+          if (valid) {
+            uint4 u[2];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(u);
+  #pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(dxr + 128 + n0) = u[0];
+            *reinterpret_cast<uint4*>(dxr + 128 + n0 + 8) = u[1];
+          }
+        }
+        LMB_EPILOGUE_DONE();
+      }
+      if (valid) {                                  // direction / padding columns carry no gradient
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int c = k0_chunks; c < in_chunks; ++c) *reinterpret_cast<uint4*>(dxr + 8 * c) = z;
+      }
+    } else {
+      // ================= layer 1 (plain input) =================
+      if (row == 0) {
+        issue_wgrad(tmem + kColDW1, aHZ, aA, 160, !first);          // dW1 (+ db1) += dz1^T x1   (x1[:, 159] = 1)
+        issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 0, 128);        // d(x1)[:, 0:128] = dz1 W1
+      }
+      LMB_MMA_WAIT();
+      const long long next = tile + gridDim.x;
+      __nv_bfloat16* dxr = dx + (row0 + row) * (long long)spec.in_width;
+      for (int n0 = 0; n0 < 128; n0 += 16) {
         float v[16];
         tc05::tmem_ld16(tlane + kColWork + n0, v);
         if (valid) {
@@ -398,12 +470,17 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
           *reinterpret_cast<uint4*>(dxr + n0 + 8) = u[1];
         }
       }
-    }
-    LMB_EPILOGUE_DONE();
-    if (K0 > 128) {
-      if (row == 0) issue_dgrad(tmem + kColWork, aS, aW0, 32, 16, K0 - 128);    // d(x0)[:, 128:K0]
+      LMB_EPILOGUE_DONE();
+      if (row == 0) {
+        if (next < n_tiles) {                       // x1 is dead (its weight-gradient MMAs completed): prefetch the next tile
+          tc05::mbar_expect_tx(&bar_in, in_bytes);
+          for (int c = 0; c < in_chunks; ++c) tc05::tma_load_3d(bufA + (size_t)c * kChunk, &xmap, 0, c, (int)(next * kTileRows), &bar_in);
+        }
+        issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 16, 32);        // d(x1)[:, 128:160]
+      }
+      in_pending = next < n_tiles;
       LMB_MMA_WAIT();
-      for (int n0 = 0; n0 < K0 - 128; n0 += 16) {
+      for (int n0 = 0; n0 < 32; n0 += 16) {
         float v[16];
         tc05::tmem_ld16(tlane + kColWork + n0, v);
         if (valid) {
@@ -416,10 +493,6 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
         }
       }
       LMB_EPILOGUE_DONE();
-    }
-    if (valid) {                                  // direction / padding columns carry no gradient
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int c = k0_chunks; c < in_chunks; ++c) *reinterpret_cast<uint4*>(dxr + 8 * c) = z;
     }
     first = false;
   }
@@ -454,25 +527,27 @@ rgb_mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char
 #pragma unroll
       for (int i = 0; i < 16; i += 4) red_add_v4(g + i, v[i], v[i + 1], v[i + 2], v[i + 3]);
     }
-    for (int half = 0; half < 2; ++half) {
-      float v[32];
-      tc05::tmem_ld16(tlane + kColDW0T + 32 * half, v);
-      tc05::tmem_ld16(tlane + kColDW0T + 32 * half + 16, v + 16);
-      // second accumulator covers input columns 16..143; only 128..143 (lanes 112..127) are new
-      const int col = half == 0 ? row : row + 16;
-      const bool take = half == 0 ? (col < K0) : (K0 > 128 && row >= 112 && col < K0);
-      if (take) {
-        float* g = gbuf + kG_DW0T + col * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) red_add_v4(g + i, v[i], v[i + 1], v[i + 2], v[i + 3]);
+    if constexpr (kPE) {
+      for (int half = 0; half < 2; ++half) {
+        float v[32];
+        tc05::tmem_ld16(tlane + kColDW0T + 32 * half, v);
+        tc05::tmem_ld16(tlane + kColDW0T + 32 * half + 16, v + 16);
+        // second accumulator covers input columns 16..143; only 128..143 (lanes 112..127) are new
+        const int col = half == 0 ? row : row + 16;
+        const bool take = half == 0 ? (col < K0) : (K0 > 128 && row >= 112 && col < K0);
+        if (take) {
+          float* g = gbuf + kG_DW0T + col * 32;
+  #pragma unroll
+          for (int i = 0; i < 32; i += 4) red_add_v4(g + i, v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
       }
     }
 #pragma unroll
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < kOut; ++i) {
       float s = db3[i];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0) atomicAdd(gbuf + kG_DB3 + i, s);
+      if (lane == 0 && i < n_out) atomicAdd(gbuf + kG_DB3 + i, s);
     }
   }
 
@@ -507,7 +582,7 @@ LMB_API int lmb_rgb_mlp_bwd(const void* x, const int* count_ptr, long long max_r
   if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
   static size_t configured = 0;
   if (smem > configured) {
-    LMB_CUDA_TRY(cudaFuncSetAttribute(rgb_mlp_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LMB_CUDA_TRY(cudaFuncSetAttribute(mlp_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   int dev = 0, sms = 148;
@@ -515,8 +590,42 @@ LMB_API int lmb_rgb_mlp_bwd(const void* x, const int* count_ptr, long long max_r
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = (max_rows + kTileRows - 1) / kTileRows;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  rgb_mlp_bwd_kernel<<<grid, kBwdThreads, smem, stream>>>(xmap, (const unsigned char*)blob, s, count_ptr, max_rows, dout,
+  mlp_bwd_kernel<true><<<grid, kBwdThreads, smem, stream>>>(xmap, (const unsigned char*)blob, s, count_ptr, max_rows, dout,
                                                          dout_stride, (__nv_bfloat16*)dx, gbuf, status);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Plain three-layer perceptron 160 -> 128 -> 128 -> 16 (padded widths, see the kernel's header).  x: bf16
+// [max_rows, 160] with ones in column 159; dout: fp32 [max_rows, dout_stride] (spec.out_dim used); dx: bf16
+// [max_rows, 160]; gbuf as for lmb_rgb_mlp_bwd (dW1 [128][160] with db1 in column 159, dW2 [128][144] with db2 in
+// column 128, dW3^T [128][16], db3 [16]; the dW0^T block stays zero).
+LMB_API int lmb_mlp3_bwd(const void* x, const int* count_ptr, long long max_rows, const void* blob, const MLPSpec* spec,
+                         const float* dout, int dout_stride, void* dx, float* gbuf, int* status, cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  const MLPSpec& s = *spec;
+  if (s.n_layers != 3 || s.pe_stage || s.in_width != 160 || s.K[0] != 160 || s.N[0] != 128 || s.K[1] != 128 || s.N[1] != 128 ||
+      s.K[2] != 128 || s.N[2] != 16 || s.out_dim < 1 || s.out_dim > 16 || s.b_off[0] < 0 || s.b_off[1] < 0 || s.b_off[2] < 0 ||
+      s.blob_bytes % 16 || s.act[0] != ACT_RELU || s.act[1] != ACT_RELU || (s.act[2] != ACT_SIGMOID && s.act[2] != ACT_NONE) ||
+      dout_stride < s.out_dim)
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap xmap;
+  int rc = encode_input_map(&xmap, x, 160, max_rows);
+  if (rc) return rc;
+  const size_t smem = ((s.blob_bytes + 1023) & ~1023) + (size_t)(kBufA + kBufH1 + kBufHZ + kBufS) + 1024;
+  if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > configured) {
+    LMB_CUDA_TRY(cudaFuncSetAttribute(mlp_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = (max_rows + kTileRows - 1) / kTileRows;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  mlp_bwd_kernel<false><<<grid, kBwdThreads, smem, stream>>>(xmap, (const unsigned char*)blob, s, count_ptr, max_rows, dout,
+                                                            dout_stride, (__nv_bfloat16*)dx, gbuf, status);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -6,8 +6,9 @@ kernel pulls in with a single TMA bulk copy.  Supported: up to 5 layers, every p
 <= 160, activations none/relu/sigmoid/tanh/exp.  ``rgb_decoder_*`` drives the GridNeRF colour head
 (basis projection + sin/cos expansion + 3-layer decoder) as one kernel.
 
-Training backward of the GridNeRF colour head is its own tcgen05 kernel (``csrc/fused_mlp_bwd.cu``:
-recompute, data gradients and weight gradients in one launch); other networks recompute with PyTorch
+Training backward runs in one tcgen05 kernel (``csrc/fused_mlp_bwd.cu``: recompute, data gradients and weight
+gradients in one launch) for the GridNeRF colour head and for plain two- / three-layer relu networks up to
+159 -> 128 -> 128 -> 16 (the 64-wide heads of the hash-grid models); other networks recompute with PyTorch
 ops under bf16 autocast.
 """
 from __future__ import annotations
@@ -20,6 +21,7 @@ import torch
 from . import native
 
 MAX_LAYERS, MAX_K, MAX_N = 5, 160, 160
+MLP3_BACKWARD_KERNEL = True      # plain 2/3-layer networks: backward through the tcgen05 kernel instead of PyTorch ops
 ACT = {"none": 0, "relu": 1, "sigmoid": 2, "tanh": 3, "exp": 4}
 
 
@@ -34,6 +36,8 @@ native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, 
 native.register_signature("lmb_rgb_mlp_bwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
                                                native.P, native.P, native.P, native.P])
 native.register_signature("lmb_rgb_mlp_bwd_gbuf_floats", [])
+native.register_signature("lmb_mlp3_bwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
+                                            native.P, native.P, native.P, native.P])
 
 
 def _pad16(v: int) -> int:
@@ -161,6 +165,107 @@ def _torch_mlp(x, layers, acts):
     return h
 
 
+# -- plain two- / three-layer networks: backward in one kernel -----------------------------------------------
+MLP3_IN, MLP3_HID, MLP3_OUT, MLP3_ONES = 160, 128, 16, 159
+
+
+def mlp3_backward_supported(packed: "PackedMLP") -> bool:
+    """Two or three linear layers, relu between them, identity or sigmoid at the end, at most 159 inputs, 128 hidden
+    units and 16 outputs."""
+    layers = packed.layers
+    if not native.available() or packed.pe_stage or len(layers) not in (2, 3):
+        return False
+    if any(a != "relu" for _, _, a in layers[:-1]) or layers[-1][2] not in ("none", "sigmoid"):
+        return False
+    return (layers[0][0].shape[1] <= MLP3_ONES and all(w.shape[0] <= MLP3_HID for w, _, _ in layers[:-1])
+            and layers[-1][0].shape[0] <= MLP3_OUT)
+
+
+class _PackedMLP3:
+    """The network zero-padded to 160 -> 128 -> 128 -> 16 in the kernel's blob layout (a two-layer network gets an
+    identity middle layer: relu(h) = h for h >= 0).  Re-packed when the optimiser generation or a parameter version moves."""
+
+    def __init__(self, layers):
+        self.layers, self.key, self.blob, self.spec, self.status = layers, None, None, None, None
+
+    def refresh(self):
+        from . import optim
+
+        key = (optim.GENERATION,) + tuple((w._version, None if b is None else b._version) for w, b, _ in self.layers)
+        if key == self.key:
+            return
+        dev = self.layers[0][0].device
+        (w1, b1, _), (w3, b3, act3) = self.layers[0], self.layers[-1]
+        if len(self.layers) == 3:
+            w2, b2 = self.layers[1][0], self.layers[1][1]
+        else:
+            w2, b2 = torch.eye(MLP3_HID, device=dev), None
+        spec = MLPSpec()
+        spec.n_layers = 3
+        parts, off = [], 0
+        for l, (w, b, n_pad, k_pad, act) in enumerate(((w1, b1, MLP3_HID, MLP3_IN, "relu"), (w2, b2, MLP3_HID, MLP3_HID, "relu"),
+                                                       (w3, b3, MLP3_OUT, MLP3_HID, act3))):
+            spec.K[l], spec.N[l], spec.act[l] = k_pad, n_pad, ACT[act]
+            packed = pack_weight(w, n_pad, k_pad).view(torch.uint8)
+            spec.w_off[l] = off
+            parts.append(packed)
+            off += packed.numel()
+            bias = torch.zeros(n_pad, device=dev, dtype=torch.float32)
+            if b is not None:
+                bias[: b.shape[0]] = b.detach().float()
+            spec.b_off[l] = off
+            parts.append(bias.view(torch.uint8))
+            off += n_pad * 4
+        spec.blob_bytes, spec.in_width, spec.out_dim, spec.pe_stage, spec.dir_col = off, MLP3_IN, w3.shape[0], 0, 0
+        self.blob, self.spec, self.key = torch.cat(parts).contiguous(), spec, key
+        if self.status is None:
+            self.status = torch.zeros(1, device=dev, dtype=torch.int32)
+
+
+def mlp3_backward(packed: "PackedMLP", x: torch.Tensor, dout: torch.Tensor):
+    """``x [N, in_width]`` bf16 (the forward kernel's input), ``dout [N, out]`` -> (``dx`` bf16 ``[N, in_width]``, gradients
+    in the order of the decoder's parameters: weight, bias (if any) per layer)."""
+    p3 = getattr(packed, "_mlp3", None)
+    if p3 is None:
+        p3 = packed._mlp3 = _PackedMLP3(packed.layers)
+    p3.refresh()
+    if packed.status is not None:
+        p3.status = packed.status          # one status word per network: ``PackedMLP.check_status`` covers both kernels
+    lib = native.lib()
+    n, k0 = x.shape[0], packed.layers[0][0].shape[1]
+    x160 = torch.zeros(n, MLP3_IN, device=x.device, dtype=torch.bfloat16)
+    x160[:, :k0] = x[:, :k0]
+    x160[:, MLP3_ONES] = 1.0
+    gbuf = torch.zeros(int(lib.lmb_rgb_mlp_bwd_gbuf_floats()), device=x.device, dtype=torch.float32)
+    dx = torch.empty_like(x160)
+    dout = dout.contiguous().float()
+    native.check(lib.lmb_mlp3_bwd(x160.data_ptr(), None, n, p3.blob.data_ptr(), byref(p3.spec), dout.data_ptr(), dout.shape[1],
+                                  dx.data_ptr(), gbuf.data_ptr(), p3.status.data_ptr(), native.stream_ptr()), "mlp3_bwd")
+    g1 = gbuf[: 128 * 160].view(128, 160)
+    g2 = gbuf[128 * 160: 128 * 160 + 128 * 144].view(128, 144)
+    o = 128 * 160 + 128 * 144
+    g3t = gbuf[o: o + 128 * 16].view(128, 16)
+    db3 = gbuf[o + 128 * 16 + 144 * 32: o + 128 * 16 + 144 * 32 + 16]
+    layers = packed.layers
+    n1, n_out = layers[0][0].shape[0], layers[-1][0].shape[0]
+    grads = [g1[:n1, :k0].contiguous()]
+    if layers[0][1] is not None:
+        grads.append(g1[:n1, MLP3_ONES].contiguous())
+    if len(layers) == 3:
+        n2 = layers[1][0].shape[0]
+        grads.append(g2[:n2, :n1].contiguous())
+        if layers[1][1] is not None:
+            grads.append(g2[:n2, 128].contiguous())
+    else:
+        n2 = n1
+    grads.append(g3t[:n2, :n_out].t().contiguous())
+    if layers[-1][1] is not None:
+        grads.append(db3[:n_out].contiguous())
+    dx_out = torch.zeros_like(x)
+    dx_out[:, :k0] = dx[:, :k0]
+    return dx_out, grads
+
+
 class _FusedMLPFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, packed, n_params, *params):
@@ -172,6 +277,9 @@ class _FusedMLPFn(torch.autograd.Function):
     def backward(ctx, dout):
         x, *params = ctx.saved_tensors
         packed = ctx.packed
+        if MLP3_BACKWARD_KERNEL and mlp3_backward_supported(packed):
+            dx, grads = mlp3_backward(packed, x, dout)
+            return (dx if ctx.needs_input_grad[0] else None, None, None, *grads)
         with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             xin = x.detach().requires_grad_(x.is_floating_point())
             leaves = [p.detach().requires_grad_() for p in params]

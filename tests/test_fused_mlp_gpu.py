@@ -164,3 +164,56 @@ def test_rgb_decoder_backward_respects_count():
     assert torch.equal(dx_c[:used], dx_r) and float(dx_c[used:].float().abs().max()) == 0.0
     for a, b in zip(g_c, g_r):
         assert torch.isfinite(a).all() and torch.allclose(a, b, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("layers,in_dim,width,out_dim,act,bias,n", [
+    (2, 32, 64, 16, None, False, 3000),                   # hash-grid density head: 32 -> 64 -> 1 + 15, no bias
+    (3, 39, 64, 3, torch.nn.Sigmoid(), False, 70001),     # hash-grid colour head
+    (3, 150, 128, 7, None, True, 515),                    # widest supported shape, with biases
+])
+def test_plain_mlp_backward_kernel(layers, in_dim, width, out_dim, act, bias, n):
+    """Backward of plain relu networks in one tcgen05 launch (the colour-head kernel without its encoding stage) vs
+    an fp32 PyTorch restatement with operands rounded to bf16 where the kernel keeps bf16."""
+    torch.manual_seed(0)
+    dec = MLPDecoder(inChanel=in_dim, layer_width=width, num_layers=layers, out_dim=out_dim, out_activation=act,
+                     mlp_bias=bias).to(DEV)
+    lin = dec.linears()
+    with torch.no_grad():
+        if bias:    # units firmly on one side of the relu, see test_rgb_decoder_backward_kernel
+            for l in lin[:-1]:
+                l.weight.mul_(0.3)
+                l.bias.copy_((torch.rand_like(l.bias) * 0.4 + 0.4) * torch.sign(torch.randn_like(l.bias)))
+    x = (torch.randn(n, in_dim, device=DEV) * 0.5).requires_grad_(True)
+    dout = torch.randn(n, out_dim, device=DEV)
+    out = fused_mlp.mlp_forward(dec, x)
+    assert fused_mlp.mlp3_backward_supported(dec._lmb_packed)
+    out.backward(dout)
+    dec._lmb_packed.check_status()
+    got = [x.grad.clone()] + [p.grad.clone() for l in lin for p in ((l.weight, l.bias) if bias else (l.weight,))]
+
+    with torch.no_grad():
+        W = [_bf(l.weight) for l in lin]
+        b = [l.bias if bias else 0.0 for l in lin]
+        hs = [_bf(x.detach())]
+        for i in range(layers - 1):
+            hs.append(_bf(torch.relu(hs[-1] @ W[i].t() + b[i])))
+        z = hs[-1] @ W[-1].t() + b[-1]
+        if act is not None:
+            o = torch.sigmoid(z)
+            dz = _bf(dout * o * (1 - o))
+        else:
+            dz = _bf(dout)
+        want_rev = []
+        for i in range(layers - 1, -1, -1):
+            want_rev.append((dz.t() @ hs[i], dz.sum(0)))
+            dh = dz @ W[i]
+            dz = _bf(dh * (hs[i] > 0)) if i > 0 else dh
+        want = [dz] + [t for wg, bg in reversed(want_rev) for t in ((wg, bg) if bias else (wg,))]
+
+    def rel(a, b_):
+        return float((a.float() - b_).norm() / (b_.norm() + 1e-12))
+
+    errs = [rel(a, b_) for a, b_ in zip(got, want)]
+    assert len(got) == len(want) and all(a.shape == b_.shape for a, b_ in zip(got, want))
+    # without biases some units sit within rounding of the relu edge and may flip between the two computations
+    assert all(e < (1.5e-2 if bias else 4e-2) for e in errs), errs
