@@ -85,11 +85,16 @@ class _Query(torch.autograd.Function):
         owner = owner.to(torch.int32).contiguous()
         dev = payload.device
         pos = torch.empty(n, dtype=torch.int32, device=dev)
-        disp.barrier()                                           # previous round's buffers are free again
+        # Two device barriers per forward.  The inbox needs none before it is written: every rank read its previous
+        # contents (collect) before the closing barrier of the query that filled it, and this rank passed that barrier.
+        # The output buffer is cleared here, ahead of the first barrier, so that barrier also tells the owners that
+        # every output buffer is ready for their stores (its previous contents were copied out in stream order).
+        out = disp.buf.view(disp.off_out, (n, out_width), torch.float32)
+        out.zero_()
         native.check(lib.lmb_a2a_dispatch(payload.data_ptr(), owner.data_ptr(), native.ptr(count), n, W, disp.inbox_table,
                                           disp.incoming_table, disp.rank, disp.world, disp.cap, disp.counts.data_ptr(),
                                           pos.data_ptr(), disp.overflow.data_ptr(), st), "a2a_dispatch")
-        disp.barrier()                                           # records and counts have landed everywhere
+        disp.barrier()                                           # records and counts have landed everywhere; outputs are cleared
         incoming = disp.incoming.clone()
         M = disp.owner_rows
         coords = torch.empty(M, 4, device=dev)
@@ -103,9 +108,6 @@ class _Query(torch.autograd.Function):
                      "a2a_collect")
         with torch.enable_grad():
             values = fn(coords, extra, m_dev).float().reshape(M, out_width)
-        out = disp.buf.view(disp.off_out, (n, out_width), torch.float32)
-        out.zero_()
-        disp.barrier()                                           # everybody zeroed its output buffer
         native.check(lib.lmb_a2a_combine(values.detach().contiguous().data_ptr(), route_src.data_ptr(), route_slot.data_ptr(),
                                          m_dev.data_ptr(), M, out_width, disp.out_table, disp.world, st), "a2a_combine")
         disp.barrier()                                           # all results are in place
