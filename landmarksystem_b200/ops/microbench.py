@@ -212,6 +212,26 @@ def case_mlp_bwd(args):
                    bytes_=args.rows * (fused_mlp.RGB_IN_WIDTH * 4 + 12.0), rows=args.rows)
 
 
+def case_mlp3_bwd(args):
+    """Backward of a hash-grid colour head (39 -> 64 -> 64 -> 3, sigmoid, no bias) in one tcgen05 launch; the time
+    includes building the kernel's 160-wide input rows and clearing the gradient buffer."""
+    from ..components.fields.mlp_decoder import MLPDecoder
+    from . import fused_mlp
+
+    dec = MLPDecoder(inChanel=39, layer_width=64, num_layers=3, out_dim=3, out_activation=torch.nn.Sigmoid(), mlp_bias=False).cuda()
+    x = (torch.randn(args.rows, 39, device="cuda") * 0.5)
+    dout = torch.randn(args.rows, 3, device="cuda")
+    with torch.no_grad():
+        fused_mlp.mlp_forward(dec, x)                      # packs the weights
+    packed = dec._lmb_packed
+    xb = torch.nn.functional.pad(x, (0, packed.in_width - 39)).to(torch.bfloat16).contiguous()
+    ms, best = time_kernel(lambda: fused_mlp.mlp3_backward(packed, xb, dout), args.iters)
+    packed.check_status()
+    flops = 2.0 * args.rows * (39 * 64 + 64 * 64 + 64 * 3) * 3          # recompute + data + weight gradients, true widths
+    return _report("mlp_bwd_kernel<false> 39-64-64-3", ms, best, flops=flops, bytes_=args.rows * (48 * 2 + 160 * 2 * 3 + 12.0),
+                   rows=args.rows)
+
+
 def case_composite(args):
     from .composite import composite_render, composite_weights
 
@@ -342,7 +362,7 @@ def case_merge_emulated(args):
                    bytes_=rays * (world * 32 + world * 24.0), rays=rays)
 
 
-CASES = {"ray_losses": case_ray_losses, "prop_resample": case_prop_resample, "alpha_pool": case_alpha_pool,
+CASES = {"mlp3_bwd": case_mlp3_bwd, "ray_losses": case_ray_losses, "prop_resample": case_prop_resample, "alpha_pool": case_alpha_pool,
          "zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd, "vm_bwd_sorted": case_vm_bwd_sorted,
          "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
 
