@@ -34,7 +34,21 @@ def voxel_keys(coords: torch.Tensor) -> torch.Tensor:
 
 
 def segment_amax(values: torch.Tensor, index: torch.Tensor, n_segments: int) -> torch.Tensor:
+    """Per-segment maximum ``[n_segments, C]`` of ``values [N, C]`` grouped by ``index [N]`` (``-inf`` for empty
+    segments); an atomic-max kernel on CUDA (``ops/csrc/gs_aux.cu``), ``scatter_reduce`` elsewhere."""
     out = torch.full((n_segments, values.shape[1]), -torch.inf, device=values.device, dtype=values.dtype)
+    if values.is_cuda and values.dtype == torch.float32 and not values.requires_grad:
+        from ctypes import c_int, c_longlong
+
+        from ....ops import native
+
+        if native.available():
+            P = native.P
+            native.register_signature("lmb_segment_amax", [P, P, c_longlong, c_int, c_longlong, P, P])
+            v, ix = values.contiguous(), index.to(torch.int64).contiguous()
+            native.check(native.lib().lmb_segment_amax(v.data_ptr(), ix.data_ptr(), v.shape[0], v.shape[1], n_segments,
+                                                       out.data_ptr(), native.stream_ptr()), "segment_amax")
+            return out
     out.scatter_reduce_(0, index[:, None].expand_as(values), values, reduce="amax", include_self=True)
     return out
 

@@ -72,6 +72,25 @@ anchor_epilogue_kernel(const float* __restrict__ anchor, const float* __restrict
   opacity_o[o] = opacity[i];
 }
 
+// ---- anchor growing helper: per-segment maximum --------------------------------------------------------------
+// out[index[i], c] = max(out[index[i], c], values[i, c]); the reference uses torch_scatter.scatter_max in 4096-row
+// chunks (landmark/nerf_components/model_components/fields/encodings/scaffoldgs_encoding.py:571).  Float maximum as
+// an integer atomic: non-negative floats order like signed ints, negative floats like reversed unsigned ints.
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v + 0.f));      // -0 becomes +0
+  else atomicMin(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
+}
+
+__global__ void __launch_bounds__(256)
+segment_amax_kernel(const float* __restrict__ values, const long long* __restrict__ index, long long n, int C, long long n_seg,
+                    float* __restrict__ out) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n * C) return;
+  const long long i = e / C, s = index[i];
+  if (s < 0 || s >= n_seg) return;
+  atomic_max_float(out + s * C + (e - i * C), values[e]);
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -103,6 +122,15 @@ LMB_API int lmb_anchor_epilogue(const float* anchor, const float* offsets, const
   if (rc) return rc;
   anchor_epilogue_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(anchor, offsets, scaling, opacity, color, scale_rot, n, k, flags, pos,
                                                               xyz_o, color_o, opacity_o, scaling_o, rot_o, count);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// values [n, C] fp32, index [n] int64 in [0, n_seg), out [n_seg, C] pre-filled by the caller (-inf for a plain maximum)
+LMB_API int lmb_segment_amax(const float* values, const long long* index, long long n, int C, long long n_seg, float* out,
+                             cudaStream_t stream) {
+  if (n <= 0 || C <= 0) return 0;
+  segment_amax_kernel<<<ceil_div(n * C, 256), 256, 0, stream>>>(values, index, n, C, n_seg, out);
   LMB_LAUNCH_CHECK();
   return 0;
 }

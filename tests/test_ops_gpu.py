@@ -488,3 +488,16 @@ def test_anchor_decode_epilogue_kernel_matches_the_indexing_path():
     if out[0].shape[0] == ref[0].shape[0]:
         for a, b in zip(out[:5], ref[:5]):
             assert torch.allclose(a.cpu(), b, atol=2e-4, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_segment_amax_kernel_matches_scatter_reduce():
+    from landmarksystem_b200.components.fields.encodings.scaffoldgs_encoding import segment_amax
+
+    torch.manual_seed(0)
+    values = torch.randn(50000, 32) * 3
+    index = torch.randint(0, 700, (50000,))
+    index[index == 13] = 14                                  # an empty segment stays at -inf
+    ref = segment_amax(values, index, 700)
+    out = segment_amax(values.cuda(), index.cuda(), 700)
+    assert torch.equal(out.cpu(), ref) and torch.isinf(ref[13]).all()
