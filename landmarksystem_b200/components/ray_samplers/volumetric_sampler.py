@@ -35,7 +35,9 @@ class VolumetricSampler(BaseSampler):
 
     @torch.no_grad()
     def forward(self, ray_bundle, training: bool = True, render_stratified_sampling: bool = True,
-                near_plane: Optional[float] = None, far_plane: Optional[float] = None):
+                near_plane: Optional[float] = None, far_plane: Optional[float] = None, lean: bool = False):
+        """``lean``: return ``(origins, directions, t_starts, t_ends, valid)`` instead of packed sample records - a caller
+        that only evaluates the valid samples builds their positions itself and never materialises the ``[R, S, 13]`` block."""
         data = ray_bundle.data if isinstance(ray_bundle, Rays) else ray_bundle
         o, d = data[:, :3].contiguous(), data[:, 3:6].contiguous()
         near = self.near_far[0] if near_plane is None else near_plane
@@ -46,6 +48,8 @@ class VolumetricSampler(BaseSampler):
             alpha_thre=self.alpha_thre if training else 0.0, max_samples=self.max_samples)
         S = ts.shape[1]
         valid = torch.arange(S, device=data.device)[None] < counts[:, None]
+        if lean:
+            return o, d, ts, te, valid
         z = 0.5 * (ts + te)
         xyz = o[:, None, :] + d[:, None, :] * z[..., None]
         cam = data[:, 6:7].expand(-1, S) if data.shape[1] > 6 else None

@@ -177,33 +177,37 @@ class InstantNGP(BaseNeRF):
         c = self.config
         rays = rays_chunk.data if isinstance(rays_chunk, Rays) else rays_chunk
         self.sampler.train(self.training)
-        samples, valid = self.sampler(rays, training=self.training,
-                                      render_stratified_sampling=c.render_stratified_sampling)
+        o, dvec, ts, te, valid = self.sampler(rays, training=self.training,
+                                              render_stratified_sampling=c.render_stratified_sampling, lean=True)
         R, S = valid.shape
         idx = valid.reshape(-1).nonzero(as_tuple=True)[0]
-        flat = samples.data.reshape(-1, samples.data.shape[-1])
+        z_vals = 0.5 * (ts + te)
         sigma = torch.zeros(R * S, device=rays.device)
         rgb = torch.zeros(R * S, 3, device=rays.device)
         if idx.numel() > 0:
-            xyz, dirs = flat[idx, 9:12], flat[idx, 6:9]
+            # positions and directions of the valid samples only (no packed [R, S, 13] sample block)
+            ray = idx // S
+            dirs = dvec[ray]
+            xyz = o[ray] + dirs * z_vals.reshape(-1)[idx][:, None]
             density, geo = self.get_density(xyz, torch.zeros_like(xyz), torch.zeros_like(xyz[:, :1]))
             d = self.direction_encoding(get_normalized_directions(dirs))
             if self.training:
                 # one embedding row per RAY, gathered per sample: the embedding's backward then reduces R rows instead
                 # of sorting R x S sample indices
-                per_ray = self.embedding_appearance(samples.data[:, 0, 4].long().clamp(0, c.appearance_embedding_size - 1))
-                app = per_ray[idx // S]
+                cam = rays[:, 6] if rays.shape[1] > 6 else torch.zeros(R, device=rays.device)
+                per_ray = self.embedding_appearance(cam.long().clamp(0, c.appearance_embedding_size - 1))
+                app = per_ray[ray]
             else:
                 app = torch.zeros(idx.numel(), c.appearance_embedding_dim, device=rays.device)
             color = self.mlp_head((d, geo, app)).float()
             sigma = sigma.index_put((idx,), density[:, 0])
             rgb = rgb.index_put((idx,), color)
-        dists = (samples.t_ends - samples.t_starts) * valid
+        dists = (te - ts) * valid
         weight = self.renderer.get_weights(sigma.view(R, S), dists)
         white = 1.0 if (c.white_bkgd or c.background_color == "white") else 0.0
         from ...ops import composite_render
 
-        rgb_map, depth_map, _ = composite_render(weight, rgb.view(R, S, 3), samples.z_vals, white)
+        rgb_map, depth_map, _ = composite_render(weight, rgb.view(R, S, 3), z_vals, white)
         return {"rgb_map": rgb_map.clamp(0, 1), "depth_map": depth_map.unsqueeze(-1)}
 
     # -- optimisation / checkpoints -----------------------------------------------------------------------------------
