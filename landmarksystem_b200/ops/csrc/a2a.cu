@@ -16,12 +16,17 @@
 namespace lmb {
 
 constexpr int kA2AMaxPeers = 8;
+constexpr int kA2AMaxRecord = 12;                       // floats: payload up to 11 wide + slot
+__host__ __device__ inline int record_stride(int W) { return (W + 1 + 3) & ~3; }
+__host__ __device__ inline int grad_stride(int V) { return V == 1 ? 1 : (V + 3) & ~3; }
 
 struct A2APeers {
   void* p[kA2AMaxPeers];
 };
 
-// payload: [n, W] floats; dst[n]: owner rank or -1.  inbox layout on every rank: [world][cap][W + 1] floats.
+// payload: [n, W] floats; dst[n]: owner rank or -1.  inbox layout on every rank: [world][cap][RS] floats with the record
+// stride RS = W + 1 rounded up to 4 floats, so a record is written and read as whole 16-byte words (a remote 4-byte store
+// costs an NVLink packet of its own; the slot index rides in the last used float).
 // pos_out[n]: position inside the (dst, src) segment (needed to route gradients back).  Only the first
 // *count_ptr rows are sent (device-side count; nullptr: all n).  Slots are claimed once per BLOCK and destination:
 // rows are ranked per destination with shared-memory counters, then one global atomic per (block, destination)
@@ -50,9 +55,16 @@ a2a_dispatch_kernel(const float* __restrict__ payload, const int* __restrict__ d
   }
   if (i < n) pos_out[i] = pos;
   if (pos < 0) return;
-  float* rec = reinterpret_cast<float*>(inbox.p[d]) + ((long long)src_rank * cap + pos) * (W + 1);
-  for (int k = 0; k < W; ++k) rec[k] = payload[i * W + k];
-  rec[W] = __int_as_float((int)i);
+  const int RS = record_stride(W);
+  float r[kA2AMaxRecord];
+#pragma unroll
+  for (int k = 0; k < kA2AMaxRecord; ++k) r[k] = k < W ? payload[i * W + k] : 0.f;
+#pragma unroll
+  for (int k = 0; k < kA2AMaxRecord; ++k) if (k == W) r[k] = __int_as_float((int)i);
+  float4* rec = reinterpret_cast<float4*>(reinterpret_cast<float*>(inbox.p[d]) + ((long long)src_rank * cap + pos) * RS);
+#pragma unroll
+  for (int q = 0; q < kA2AMaxRecord / 4; ++q)
+    if (4 * q < RS) rec[q] = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
 }
 
 // counts of this rank are copied into every peer's incoming[src_rank]
@@ -70,15 +82,24 @@ a2a_collect_kernel(const float* __restrict__ inbox, const int* __restrict__ inco
                    float4* __restrict__ coords, float* __restrict__ extra, int* __restrict__ route_src,
                    int* __restrict__ route_slot, int* __restrict__ total) {
   long long base = 0;
-  const int E = W - 3;
+  const int E = W - 3, RS = record_stride(W);
   for (int s = 0; s < world; ++s) {
     const int c = incoming[s];
     for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < c; k += (long long)gridDim.x * blockDim.x) {
-      const float* rec = inbox + ((long long)s * cap + k) * (W + 1);
-      coords[base + k] = make_float4(rec[0], rec[1], rec[2], 0.f);
-      for (int j = 0; j < E; ++j) extra[(base + k) * E + j] = rec[3 + j];
+      const float4* rec4 = reinterpret_cast<const float4*>(inbox + ((long long)s * cap + k) * RS);
+      float r[kA2AMaxRecord];
+#pragma unroll
+      for (int q = 0; q < kA2AMaxRecord / 4; ++q)
+        if (4 * q < RS) { const float4 v = rec4[q]; r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w; }
+      coords[base + k] = make_float4(r[0], r[1], r[2], 0.f);
+      int slot = 0;
+#pragma unroll
+      for (int j = 3; j < kA2AMaxRecord; ++j) {
+        if (j < W) extra[(base + k) * E + (j - 3)] = r[j];
+        if (j == W) slot = __float_as_int(r[j]);
+      }
       route_src[base + k] = s;
-      route_slot[base + k] = __float_as_int(rec[W]);
+      route_slot[base + k] = slot;
     }
     base += c;
   }
@@ -104,8 +125,15 @@ a2a_grad_dispatch_kernel(const float* __restrict__ dout, const int* __restrict__
   if (i >= resolve_count(count_ptr, n)) return;
   const int d = dst[i], p = pos[i];
   if (d < 0 || p < 0) return;
-  float* rec = reinterpret_cast<float*>(ginbox.p[d]) + ((long long)src_rank * cap + p) * V;
-  for (int k = 0; k < V; ++k) rec[k] = dout[i * V + k];
+  const int VS = grad_stride(V);
+  float* rec = reinterpret_cast<float*>(ginbox.p[d]) + ((long long)src_rank * cap + p) * VS;
+  if (V == 1) { rec[0] = dout[i]; return; }
+  for (int q = 0; 4 * q < VS; ++q) {                      // whole 16-byte words, zero tail
+    float4 v;
+    v.x = 4 * q < V ? dout[i * V + 4 * q] : 0.f;         v.y = 4 * q + 1 < V ? dout[i * V + 4 * q + 1] : 0.f;
+    v.z = 4 * q + 2 < V ? dout[i * V + 4 * q + 2] : 0.f; v.w = 4 * q + 3 < V ? dout[i * V + 4 * q + 3] : 0.f;
+    reinterpret_cast<float4*>(rec)[q] = v;
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -115,7 +143,7 @@ a2a_grad_collect_kernel(const float* __restrict__ ginbox, const int* __restrict_
   for (int s = 0; s < world; ++s) {
     const int c = incoming[s];
     for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < c; k += (long long)gridDim.x * blockDim.x) {
-      const float* rec = ginbox + ((long long)s * cap + k) * V;
+      const float* rec = ginbox + ((long long)s * cap + k) * grad_stride(V);
       for (int j = 0; j < V; ++j) rows[(base + k) * V + j] = rec[j];
     }
     base += c;
@@ -133,7 +161,7 @@ static void fill(A2APeers& dst, const long long* table, int world) {
 LMB_API int lmb_a2a_dispatch(const float* payload, const int* dst, const int* count_ptr, long long n, int W,
                              const long long* inbox_table, const long long* incoming_table, int rank, int world, long long cap,
                              int* counts, int* pos_out, int* overflow, cudaStream_t stream) {
-  if (world > kA2AMaxPeers) return (int)cudaErrorInvalidValue;
+  if (world > kA2AMaxPeers || W + 1 > kA2AMaxRecord) return (int)cudaErrorInvalidValue;
   A2APeers inbox, incoming;
   fill(inbox, inbox_table, world);
   fill(incoming, incoming_table, world);
@@ -149,7 +177,7 @@ LMB_API int lmb_a2a_dispatch(const float* payload, const int* dst, const int* co
 // coords: [world * cap, 4]; extra: [world * cap, W - 3] or null when W == 3; total: device int
 LMB_API int lmb_a2a_collect(const float* inbox, const int* incoming, int world, long long cap, int W, float* coords, float* extra,
                             int* route_src, int* route_slot, int* total, cudaStream_t stream) {
-  if (W < 3 || (W > 3 && extra == nullptr)) return (int)cudaErrorInvalidValue;
+  if (W < 3 || W + 1 > kA2AMaxRecord || (W > 3 && extra == nullptr)) return (int)cudaErrorInvalidValue;
   a2a_collect_kernel<<<148 * 4, 256, 0, stream>>>(inbox, incoming, world, cap, W, (float4*)coords, extra, route_src, route_slot,
                                                   total);
   LMB_LAUNCH_CHECK();

@@ -41,8 +41,9 @@ class BlockDispatcher:
         self.cap, self.max_w, self.max_v = int(cap), max_w, max_v
         w = self.world
         self.off_inbox = 0
-        self.off_ginbox = self.off_inbox + w * cap * (max_w + 1) * 4
-        self.off_out = self.off_ginbox + w * cap * max_v * 4
+        record = (max_w + 1 + 3) // 4 * 4              # floats per inbox record: payload + slot, whole 16-byte words
+        self.off_ginbox = self.off_inbox + w * cap * record * 4
+        self.off_out = self.off_ginbox + w * cap * ((max_v + 3) // 4 * 4) * 4
         self.off_incoming = self.off_out + cap * max_v * 4
         total = self.off_incoming + 256
         self.buf = SymmetricBuffer(total, group)
