@@ -308,6 +308,28 @@ def run_ours(args):
         t.model.train()
         return t
 
+    if getattr(args, "profile", False):
+        # kernel table of three eager steps (the CUDA graph replays the same kernels): PyTorch profiler, rank 0, stderr
+        from torch.profiler import ProfilerActivity
+        from torch.profiler import profile as torch_profile
+
+        cfg.cuda_graph = False
+        t = make_trainer()
+        rays, rgbs, idxs = make_ray_pool(RAYS_PER_GPU * 4, cfg.lb, cfg.ub, seed=1234 + rank)
+        b = torch.cat((rays, rgbs, idxs[:, None]), -1).view(4, RAYS_PER_GPU, 10).to(t.config.device)
+        for k in range(4):
+            t.train_step(b[k][:, :6], b[k][:, 6:9], b[k][:, 9])
+        torch.cuda.synchronize()
+        with torch_profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for k in range(3):
+                t.train_step(b[k][:, :6], b[k][:, 6:9], b[k][:, 9])
+            torch.cuda.synchronize()
+        if rank == 0:
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70), file=sys.stderr)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     holder = {"trainer": make_trainer()}
     dev = holder["trainer"].config.device
     steps, warmup = args.steps, args.warmup
