@@ -119,3 +119,20 @@ def test_gpu_training_reduces_loss(family, module, cls, tmp_path):
     for trainer.iteration in range(300):
         losses.append(float(trainer.train_step(*trainer.data_mgr.get_rays(trainer.iteration))))
     assert np.mean(losses[-20:]) < 0.5 * np.mean(losses[:20]), (np.mean(losses[:20]), np.mean(losses[-20:]))
+
+
+def test_volumetric_sampler_lean_output_matches_packed_samples():
+    """The lean return (origins, directions, interval ends, validity) describes the same samples as the packed records."""
+    from landmarksystem_b200.components.ray_samplers.volumetric_sampler import VolumetricSampler
+
+    est = _grid(levels=1)
+    o, d = _rays(32)
+    rays = torch.cat((o, d, torch.arange(32.0)[:, None]), -1)
+    sampler = VolumetricSampler(occupancy_grid=est, near_far=[0.1, 10.0], step_size=0.05, max_samples=64).eval()
+    samples, valid = sampler(rays, training=False, render_stratified_sampling=False)
+    o2, d2, ts, te, valid2 = sampler(rays, training=False, render_stratified_sampling=False, lean=True)
+    assert torch.equal(valid, valid2) and torch.equal(samples.t_starts, ts) and torch.equal(samples.t_ends, te)
+    z = 0.5 * (ts + te)
+    xyz = o2[:, None] + d2[:, None] * z[..., None]
+    assert torch.allclose(samples.data[..., 9:12][valid], xyz[valid]) and torch.allclose(samples.data[..., 6:9][valid], d2[:, None].expand_as(xyz)[valid])
+    assert torch.equal(samples.data[:, 0, 4], rays[:, 6])

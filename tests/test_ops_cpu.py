@@ -82,3 +82,20 @@ def test_hashgrid_reference_dense_level_interpolates():
     out = hashgrid_reference(x, table, meta)
     assert out.shape == (50, 4) and torch.allclose(out[:, 0], torch.ones(50), atol=1e-5)
     assert out[:, 1].abs().max() == 0
+
+
+def test_cat_pad_bf16_concatenates_pads_and_routes_gradients():
+    """Input assembly of the fused MLP path: parts -> one zero-padded bf16 row block; each part gets its gradient slice."""
+    from landmarksystem_b200.ops.fused_mlp import _CatPadBf16
+
+    torch.manual_seed(0)
+    a = torch.randn(7, 3, requires_grad=True)
+    b = torch.randn(7, 5)                                   # no gradient wanted
+    c = torch.randn(7, 2, requires_grad=True)
+    out = _CatPadBf16.apply(16, a, b, c)
+    assert out.dtype == torch.bfloat16 and out.shape == (7, 16)
+    ref = torch.cat((a, b, c), -1).detach().to(torch.bfloat16)
+    assert torch.equal(out[:, :10], ref) and out[:, 10:].abs().max() == 0
+    g = torch.randn(7, 16).to(torch.bfloat16)
+    out.backward(g)
+    assert torch.equal(a.grad, g[:, :3].float()) and torch.equal(c.grad, g[:, 8:10].float()) and b.grad is None
