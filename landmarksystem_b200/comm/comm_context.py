@@ -6,6 +6,7 @@ pickled objects).  The hot-path collectives of the fused kernels use peer memory
 """
 from __future__ import annotations
 
+import dataclasses
 import datetime
 import gc
 import os
@@ -23,72 +24,82 @@ def default_backend() -> str:
     return "nccl" if torch.cuda.is_available() else "gloo"
 
 
+@dataclasses.dataclass(frozen=True)
+class GroupRecord:
+    """What the context knows about one communication mode on this process."""
+
+    rank_in_group: int
+    size: int
+    group: object              # torch.distributed process group handle
+    members: tuple             # global ranks of the group, in group order
+
+
 class CommContext(metaclass=SingletonMeta):
+    """One ``{mode: GroupRecord}`` map behind the reference's accessor names."""
+
     def __init__(self) -> None:
-        self._local_ranks, self._global_ranks, self._world_sizes = {}, {}, {}
-        self._ranks_in_group, self._groups = {}, {}
+        self._records: dict = {}
+        self._rank = None
         self._node_cuda_num = max(torch.cuda.device_count(), 1)
-        self._tensor_parallel_size = 1
-        self._data_parallel_size = 1
+        self._tp = self._dp = 1
         self._owns_pg = False
 
     def is_initialized(self) -> bool:
-        return self._groups.get(CommMode.GLOBAL) is not None
+        return CommMode.GLOBAL in self._records
 
     def init_distributed_env(self, world_size=None, rank=None, backend=None, dist_url="env://", timeout=1800):
-        backend = backend or default_backend()
         if not dist.is_initialized():
-            dist.init_process_group(backend=backend, init_method=dist_url, world_size=world_size, rank=rank,
-                                    timeout=datetime.timedelta(seconds=timeout))
+            dist.init_process_group(backend=backend or default_backend(), init_method=dist_url, world_size=world_size,
+                                    rank=rank, timeout=datetime.timedelta(seconds=timeout))
             self._owns_pg = True
-        world_size, rank = dist.get_world_size(), dist.get_rank()
+        self._rank = dist.get_rank()
+        n = dist.get_world_size()
         if torch.cuda.is_available():
-            local = int(os.environ.get("LOCAL_RANK", rank % torch.cuda.device_count()))
-            torch.cuda.set_device(local % torch.cuda.device_count())
+            ndev = torch.cuda.device_count()
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", self._rank % ndev)) % ndev)
         dist.barrier()
-        self._register_group(rank, world_size, dist.group.WORLD, list(range(world_size)), CommMode.GLOBAL)
-        self._global_ranks[CommMode.GLOBAL] = rank
+        self._records[CommMode.GLOBAL] = GroupRecord(self._rank, n, dist.group.WORLD, tuple(range(n)))
 
-    def _register_group(self, local_rank, world_size, process_group, ranks_in_group, mode):
-        self._local_ranks[mode] = local_rank
-        self._world_sizes[mode] = world_size
-        self._groups[mode] = process_group
-        self._ranks_in_group[mode] = ranks_in_group
+    def _record(self, comm_mode: CommMode) -> GroupRecord:
+        try:
+            return self._records[comm_mode]
+        except KeyError:
+            raise KeyError(f"communication mode {comm_mode} has no group on this process") from None
 
+    # accessor names are the reference's public surface
     def get_group(self, comm_mode: CommMode):
-        return self._groups[comm_mode]
+        return self._record(comm_mode).group
 
     def get_world_size(self, comm_mode: CommMode):
-        return self._world_sizes[comm_mode]
+        return self._record(comm_mode).size
 
     def get_global_rank(self):
-        return self._global_ranks[CommMode.GLOBAL]
+        return self._rank
 
     def get_local_rank(self, comm_mode: CommMode):
-        return self._local_ranks[comm_mode]
+        return self._record(comm_mode).rank_in_group
 
     def get_ranks_in_group(self, comm_mode: CommMode):
-        return self._ranks_in_group[comm_mode]
+        return list(self._record(comm_mode).members)
 
     @property
     def tensor_parallel_size(self):
-        return self._tensor_parallel_size
+        return self._tp
 
     @property
     def data_parallel_size(self):
-        return self._data_parallel_size
+        return self._dp
 
     def init_groups(self, config: Config):
-        rank = self.get_global_rank()
-        world = self.get_world_size(CommMode.GLOBAL)
-        self._tensor_parallel_size = int(config.get("tp_size", 1)) if hasattr(config, "get") else 1
-        assert world % self._tensor_parallel_size == 0, "world size must be a multiple of tp_size"
-        self._data_parallel_size = world // self._tensor_parallel_size
-        for init in (DPGroupInitializer(rank, world, self._data_parallel_size),
-                     TPGroupInitializer(rank, world, self._tensor_parallel_size),
-                     MessageTransferInitializer(rank, world),
-                     DynamicLoadGroupInitializer(rank, world, self._tensor_parallel_size, self._node_cuda_num)):
-            self._register_group(*init.init_dist_group())
+        me, n = self._rank, self._record(CommMode.GLOBAL).size
+        self._tp = int(config.get("tp_size", 1)) if hasattr(config, "get") else 1
+        assert n % self._tp == 0, "world size must be a multiple of tp_size"
+        self._dp = n // self._tp
+        builders = (DPGroupInitializer(me, n, self._dp), TPGroupInitializer(me, n, self._tp),
+                    MessageTransferInitializer(me, n), DynamicLoadGroupInitializer(me, n, self._tp, self._node_cuda_num))
+        for builder in builders:
+            rank_in_group, size, group, members, mode = builder.init_dist_group()
+            self._records[mode] = GroupRecord(rank_in_group, size, group, tuple(members or ()))
 
     def destroy(self):
         if not self.is_initialized():
@@ -96,10 +107,8 @@ class CommContext(metaclass=SingletonMeta):
         dist.barrier()
         if self._owns_pg:
             dist.destroy_process_group()
-        for d in (self._local_ranks, self._global_ranks, self._world_sizes, self._ranks_in_group, self._groups):
-            d.clear()
-        self._tensor_parallel_size = self._data_parallel_size = 1
-        self._owns_pg = False
+        self._records.clear()
+        self._rank, self._tp, self._dp, self._owns_pg = None, 1, 1, False
         gc.collect()
 
 

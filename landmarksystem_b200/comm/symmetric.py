@@ -19,7 +19,7 @@ from ..ops import native
 P = native.P
 for _name, _sig in (("lmb_symm_alloc", [c_longlong, ctypes.POINTER(c_void_p)]), ("lmb_symm_free", [P]),
                     ("lmb_ipc_get_handle", [P, P]), ("lmb_ipc_open", [P, ctypes.POINTER(c_void_p)]),
-                    ("lmb_ipc_close", [P]), ("lmb_peer_barrier", [P, P, c_int, c_int, P, P, P])):
+                    ("lmb_ipc_close", [P]), ("lmb_peer_barrier", [P, P, c_int, c_int, P, P, c_longlong, P])):
     native.register_signature(_name, _sig)
 
 
@@ -75,12 +75,16 @@ class SymmetricBuffer:
         return self.ptr_table + offset
 
     def close(self):
+        """Unmap the peers' buffers and free this rank's.  Safe only when no rank still uses the mappings: callers
+        order it with a barrier across the group after synchronising their devices.  Idempotent.  There is deliberately
+        no finaliser: garbage collection runs at different times on different ranks, and freeing memory that a peer's
+        kernel may still address is worse than holding it until the process ends."""
         lib = native.lib()
         for p in self._opened:
             lib.lmb_ipc_close(p)
         self._opened = []
         if self.local_ptr:
-            self.local = None
+            self.local = self._keep = None
             lib.lmb_symm_free(self.local_ptr)
             self.local_ptr = 0
 
@@ -88,7 +92,8 @@ class SymmetricBuffer:
 class PeerBarrier:
     """Stream-ordered barrier across the ranks of a group, executed by a one-block kernel per rank."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, limit_cycles: int = 0):
+        self.limit_cycles = int(limit_cycles)        # SM clocks a wait may last (0: about one second)
         self.buf = SymmetricBuffer(256, group)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.buf.device)   # barriers passed, kept on the device
         self.status = torch.zeros(1, dtype=torch.int32, device=self.buf.device)
@@ -101,9 +106,12 @@ class PeerBarrier:
             return
         native.check(native.lib().lmb_peer_barrier(self.buf.local_ptr, self.flag_table.data_ptr(), self.buf.rank,
                                                    self.buf.world, self.epoch.data_ptr(), self.status.data_ptr(),
-                                                   native.stream_ptr()), "peer_barrier")
+                                                   self.limit_cycles, native.stream_ptr()), "peer_barrier")
 
     def check(self) -> None:
         code = int(self.status.item())
         if code:
             raise RuntimeError(f"peer barrier timed out waiting for rank {code - 100}")
+
+    def close(self) -> None:
+        self.buf.close()

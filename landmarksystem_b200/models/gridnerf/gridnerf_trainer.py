@@ -132,13 +132,35 @@ class GridNeRFTrainer(NeRFTrainer):
         return self.optimizer
 
     def _optim_path(self):
+        """Model-parallel ranks and ranks of a partitioned (ZeRO) optimiser each own different state and write their own
+        file; replicas of an ordinary optimiser share rank 0's."""
         cfg = self.config
-        suffix = f"-sub{cfg.rank}" if cfg.model_parallel else ""
+        per_rank = cfg.model_parallel or bool(getattr(self.optimizer, "partitioned", False))
+        suffix = f"-sub{cfg.rank}" if per_rank else ""
         return os.path.join(self.optim_dir, f"{cfg.expname}_opt{suffix}.th")
 
     def save_optimizer(self):
         os.makedirs(self.optim_dir, exist_ok=True)
         torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+
+    def _replace_optimizer(self, groups):
+        """New optimiser over ``groups`` (parameters were replaced or added); the old one's peer-mapped buffers are
+        released first - a collective teardown, reached by every rank at the same iteration."""
+        old = getattr(self, "optimizer", None)
+        if old is not None and hasattr(old, "close"):
+            old.close()
+        self.optimizer = self._make_optimizer(groups)
+        return self.optimizer
+
+    def _group_lr(self, params, default):
+        """Current learning rate of the optimiser group holding ``params`` (fused optimisers merge groups by rate)."""
+        opt = self.optimizer
+        if hasattr(opt, "group_lr"):
+            return opt.group_lr(params)
+        for g in opt.param_groups:
+            if any(p is params[0] for p in g["params"]):
+                return g["lr"]
+        return default
 
     # -- schedule ---------------------------------------------------------------------------
     def _init_schedule(self):
@@ -164,7 +186,7 @@ class GridNeRFTrainer(NeRFTrainer):
         self.module.upsample_volume_grid(reso)
         lr_scale = 1.0 if cfg.lr_upsample_reset else cfg.lr_decay_target_ratio ** (self.iteration / cfg.n_iters)
         groups = self.module.get_optparam_groups(cfg.lr_init * lr_scale, cfg.lr_basis * lr_scale)
-        self.optimizer = self._make_optimizer(groups)  # parameters were replaced: new state
+        self._replace_optimizer(groups)                # parameters were replaced: new state
 
     # -- one optimisation step -------------------------------------------------------------------
     def compute_loss(self, all_ret, rgb_train):
@@ -298,8 +320,10 @@ class GridNeRFTrainer(NeRFTrainer):
                 self.enable_distort = True
             if cfg.add_nerf > 0 and it == cfg.add_nerf:
                 self.module.run_nerf = True
-                self.optimizer = self._make_optimizer(self.module.get_optparam_groups(
-                    self.optimizer.param_groups[0]["lr"], self.optimizer.param_groups[2]["lr"]))
+                m = self.module
+                lr_grid = self._group_lr(list(m.density_encoding.parameters()), cfg.lr_init)
+                lr_net = self._group_lr(list(m.rgb_decoder.parameters()), cfg.lr_basis)
+                self._replace_optimizer(m.get_optparam_groups(lr_grid, lr_net))
             loss = self.train_step(rays_train, rgb_train, idxs_train)
             if it % cfg.progress_refresh_rate == 0:
                 mse = float(loss)
@@ -345,7 +369,13 @@ class GridNeRFTrainer(NeRFTrainer):
             if hasattr(enc, "flush_lazy"):
                 enc.flush_lazy()
         state = {"model": self.module.state_dict(), "optimizer": self.optimizer.state_dict(), "iteration": step}
-        return self._async_ckpt.save_step(step, state, rank=int(cfg.rank), world=int(cfg.world_size),
+        store = None
+        if int(cfg.world_size) > 1:
+            # the writer threads meet through the process group's rendezvous store (host side, no collective)
+            from torch.distributed.distributed_c10d import _get_default_store
+
+            store = _get_default_store()
+        return self._async_ckpt.save_step(step, state, rank=int(cfg.rank), world=int(cfg.world_size), store=store,
                                           meta={"expname": cfg.expname, "model": "GridNeRF"})
 
     def save_ckpt(self, final: bool = False):
@@ -362,9 +392,11 @@ class GridNeRFTrainer(NeRFTrainer):
                 torch.save(merged, f"{self.logfolder}/state_dict-merged.th")
                 torch.save(kwargs, f"{self.logfolder}/kwargs-merged.th")
             self.barrier()
-        elif is_main_rank():
-            self.module.save_model(self.logfolder)
-            self.save_optimizer()
+        else:
+            if is_main_rank():
+                self.module.save_model(self.logfolder)
+            if is_main_rank() or bool(getattr(self.optimizer, "partitioned", False)):
+                self.save_optimizer()
 
     # -- evaluation ----------------------------------------------------------------------------------
     @torch.no_grad()

@@ -48,7 +48,9 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* smem, 
 }
 
 __global__ void __launch_bounds__(kScanThreads)
-scan_tiles_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint32_t* __restrict__ tile_sums, long long n) {
+scan_tiles_kernel(const uint32_t* in, uint32_t* out, uint32_t* __restrict__ tile_sums, long long n) {
+  // `out` may be the same buffer as `in` (the recursion scans the tile sums in place): a thread loads all of its
+  // items before it stores any, and it stores only to the positions it loaded, so the two are not marked restrict.
   __shared__ uint32_t sm[32];
   const long long base = (long long)blockIdx.x * kScanTile + threadIdx.x * kScanItems;
   uint32_t v[kScanItems], sum = 0;

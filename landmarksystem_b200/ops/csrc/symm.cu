@@ -76,11 +76,13 @@ LMB_API int lmb_ipc_close(void* p) {
   return 0;
 }
 
-// Device-side barrier over `world` ranks on `stream`.  status: device int, non-zero if a wait expired.
+// Device-side barrier over `world` ranks on `stream`.  status: device int, set to 100 + p if the wait for peer p
+// gave up after `limit_cycles` SM clocks (<= 0: the default of about one second).
 LMB_API int lmb_peer_barrier(unsigned* flags_local, unsigned* const* peer_flags, int rank, int world, unsigned* epoch_dev,
-                             int* status, cudaStream_t stream) {
+                             int* status, long long limit_cycles, cudaStream_t stream) {
   if (world > 32) return (int)cudaErrorInvalidValue;
-  barrier_kernel<<<1, 32, 0, stream>>>(flags_local, peer_flags, rank, world, epoch_dev, 2000000000LL, status);
+  if (limit_cycles <= 0) limit_cycles = 2000000000LL;
+  barrier_kernel<<<1, 32, 0, stream>>>(flags_local, peer_flags, rank, world, epoch_dev, limit_cycles, status);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -55,6 +55,21 @@ class _P2PSmallAllReduce:
                                                                   self.native.stream_ptr()), "allreduce_small_p2p")
         return out[:n]
 
+    def close(self) -> None:
+        """Collective teardown (every rank of the group calls it at the same point): no peer may still address the
+        staging buffer when it is unmapped and freed."""
+        if self.buf is None:
+            return
+        if dist.is_initialized() and self.buf.world > 1:
+            dist.barrier(self.buf.group)
+        torch.cuda.synchronize()
+        if dist.is_initialized() and self.buf.world > 1:
+            dist.barrier(self.buf.group)
+        self.staging = None
+        self.buf.close()
+        self.barrier.close()
+        self.buf = None
+
 
 class GradSynchronizer:
     """``p2p_small``: on CUDA, coalesced small gradients go through :class:`_P2PSmallAllReduce` instead of the
@@ -91,6 +106,8 @@ class GradSynchronizer:
             flat = torch.cat([g.reshape(-1) for g in small])
             if self.p2p_small and flat.is_cuda:
                 if self._p2p is None or self._p2p.capacity < flat.numel():
+                    if self._p2p is not None:
+                        self._p2p.close()            # same parameter sizes on every rank: all ranks regrow together
                     self._p2p = _P2PSmallAllReduce(max(flat.numel(), 1 << 16), self.group)
                 flat = self._p2p(flat.float(), 1.0 / world if self.average else 1.0)
             else:

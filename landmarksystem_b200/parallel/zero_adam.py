@@ -65,6 +65,20 @@ class FlatParams:
         self.grad_table = _table(self.buf.peer_table(self.n * 4))
         self.shadow_table = _table(self.buf.peer_table(self.n * 8)) if shadow else None
 
+    def close(self):
+        """Move the parameters back to ordinary memory and free the symmetric buffer.  The caller has made sure (peer
+        barrier / group barrier) that no peer still reads or writes this rank's buffer."""
+        if self.buf is None:
+            return
+        for p in self.params:
+            p.data = p.data.clone()
+            for name in ("_lmb_grad_sink", "_lmb_shadow"):
+                if hasattr(p, name):
+                    delattr(p, name)
+        self.flat_param = self.flat_grad = self.flat_shadow = None
+        self.buf.close()
+        self.buf = None
+
     def absorb_autograd_grads(self):
         """Parameters whose backward produced an ordinary ``.grad`` (PyTorch ops) are folded into the sink."""
         for p in self.params:
@@ -106,6 +120,21 @@ class P2PZeroAdam:
     def zero_grad(self, set_to_none=True):
         for p in self.flat.params:
             p.grad = None
+
+    def close(self):
+        """Collective teardown: a group barrier (all kernels that touch peer memory have been enqueued by every rank),
+        a device synchronise (they have finished), a second group barrier (they have finished everywhere), then the
+        mappings and the allocation are released."""
+        if self.flat.buf is None:
+            return
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(self.group)
+        torch.cuda.synchronize()
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(self.group)
+        self.flat.close()
+        self.barrier.close()
+        self.m = self.v = None
 
 
 class NcclZeroAdam:
@@ -190,9 +219,36 @@ class GroupedP2PZeroAdam:
         for o in self.opts:
             o.zero_grad(set_to_none)
 
+    #: the moments are this rank's 1/world shard: a checkpoint of this optimiser is per rank
+    partitioned = True
+
     def state_dict(self):
-        return {"groups": [{"m": o.m, "v": o.v, "step": o.step_count, "lr": o.param_groups[0]["lr"]} for o in self.opts]}
+        """This rank's shard of the moments plus the partition it belongs to (checked by ``load_state_dict``)."""
+        return {"partition": {"rank": self.opts[0].rank, "world": self.opts[0].world, "elems": [o.flat.n for o in self.opts]},
+                "groups": [{"m": o.m, "v": o.v, "step": o.step_count, "lr": o.param_groups[0]["lr"]} for o in self.opts]}
 
     def load_state_dict(self, state):
+        part = state.get("partition")
+        if part is None:
+            raise ValueError("optimiser state carries no partition record: it was not written by a partitioned optimiser")
+        mine = {"rank": self.opts[0].rank, "world": self.opts[0].world, "elems": [o.flat.n for o in self.opts]}
+        if part != mine:
+            raise ValueError(f"optimiser shard of partition {part} cannot be loaded into partition {mine}: every rank "
+                             "must read the file its own rank wrote, with the same group size and parameters")
         for o, s in zip(self.opts, state["groups"]):
             o.m.copy_(s["m"]); o.v.copy_(s["v"]); o.step_count = s["step"]; o.param_groups[0]["lr"] = s["lr"]
+
+    def group_lr(self, params) -> float:
+        """Learning rate of the group that holds ``params[0]`` (groups are merged by rate, so indices of the
+        caller's original group list do not apply)."""
+        want = params[0] if isinstance(params, (list, tuple)) else params
+        for o in self.opts:
+            if any(p is want for p in o.flat.params):
+                return o.param_groups[0]["lr"]
+        raise KeyError("parameter is not managed by this optimiser")
+
+    def close(self):
+        """Release the peer-mapped buffers (collective: every rank of the group calls it at the same point)."""
+        for o in self.opts:
+            o.close()
+        self.opts = []

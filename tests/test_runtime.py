@@ -143,13 +143,106 @@ def test_incomplete_checkpoint_is_ignored(tmp_path):
         load_sharded(str(tmp_path / "step-00000005"))
 
 
+def _ckpt_rank(rank, world, root, store_file, delay, q):
+    """One rank of a two-rank save: rank 1 is slow; rank 0 must not publish before rank 1's shard exists."""
+    import time
+
+    import torch.distributed as dist
+
+    store = dist.FileStore(store_file, world)
+    ck = AsyncCheckpointer(root)
+    if delay:
+        real_save = torch.save
+
+        def slow_save(obj, path, *a, **k):
+            time.sleep(delay)
+            return real_save(obj, path, *a, **k)
+
+        torch.save = slow_save
+    try:
+        path = ck.save_step(3, {"w": torch.full((4,), float(rank))}, rank=rank, world=world, store=store)
+        ck.wait()
+        q.put((rank, "ok", path))
+    except BaseException as exc:  # noqa: BLE001 - reported to the parent
+        q.put((rank, "error", repr(exc)))
+
+
+def test_multi_rank_checkpoint_waits_for_the_slow_rank(tmp_path):
+    import multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    store_file = str(tmp_path / "store")
+    root = str(tmp_path / "ck")
+    procs = [ctx.Process(target=_ckpt_rank, args=(r, 2, root, store_file, 1.5 if r == 1 else 0.0, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict((r, (s, m)) for r, s, m in (q.get(timeout=60) for _ in procs))
+    for p in procs:
+        p.join(timeout=20)
+    assert got[0][0] == "ok" and got[1][0] == "ok", got
+    path = got[0][1]
+    assert sorted(os.listdir(path)) == ["COMPLETE", "meta.json", "shard-00000-of-00002.pt", "shard-00001-of-00002.pt"]
+    for r in range(2):
+        assert float(load_sharded(path, rank=r)["state"]["w"][0]) == float(r)
+
+
+def test_multi_rank_checkpoint_without_rendezvous_is_refused(tmp_path):
+    with pytest.raises(ValueError, match="rendezvous"):
+        AsyncCheckpointer(str(tmp_path)).save_step(1, {"w": torch.zeros(1)}, rank=0, world=2)
+
+
 @pytest.mark.gpu
-def test_async_checkpoint_from_device_is_a_snapshot(tmp_path):
-    """The device-to-host copies are ordered after the training stream at the time of save(): later updates of the
-    parameters do not leak into the checkpoint."""
-    ck = AsyncCheckpointer(str(tmp_path))
-    w = torch.full((1 << 22,), 1.0, device="cuda")
-    path = ck.save_step(1, {"w": w})
-    w.add_(1.0)
+@pytest.mark.parametrize("mode", ["clone", "block"])
+def test_async_checkpoint_from_device_is_a_snapshot(tmp_path, mode):
+    """A 1 GiB tensor is saved and then updated in place many times right away (each update is far shorter than the
+    device-to-host copy): the checkpoint must hold the value at the time of the call, in the staging-clone mode and in
+    the mode where the training stream waits for the copies.  A temporary that is freed right after the call (what a
+    ``state_dict`` hook produces) must survive until its copy has been read."""
+    ck = AsyncCheckpointer(str(tmp_path), snapshot=mode)
+    w = torch.full((1 << 28,), 1.0, device="cuda")
+    tmp = torch.full((1 << 24,), 5.0, device="cuda")
+    path = ck.save_step(1, {"w": w, "tmp": tmp * 1.0})
+    del tmp
+    for _ in range(64):
+        w.add_(1.0)
+        junk = torch.full((1 << 24,), -1.0, device="cuda")      # would reuse the freed temporary's memory
+        del junk
     ck.wait()
-    assert float(load_sharded(path)["state"]["w"].max()) == 1.0
+    state = load_sharded(path)["state"]
+    assert float(state["w"].max()) == 1.0 and float(state["w"].min()) == 1.0
+    assert float(state["tmp"].min()) == 5.0 and float(state["tmp"].max()) == 5.0
+    assert float(w[0]) == 65.0
+
+
+@pytest.mark.gpu
+def test_peer_barrier_wait_gives_up_and_reports_the_missing_peer():
+    """A barrier among two ranks of which only rank 0 exists: nothing ever sets the flag that rank 1 would write, the
+    wait for it runs out after a few milliseconds of SM clocks, the kernel returns and the status word names the peer
+    (100 + 1).  A bounded wait, not a hang: the context stays usable and a second barrier reports again."""
+    import ctypes
+
+    from landmarksystem_b200.comm import symmetric  # noqa: F401  (registers the signatures)
+    from landmarksystem_b200.ops import native
+
+    dev = torch.device("cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)                      # this rank's flag array
+    sink = torch.zeros(64, dtype=torch.int32, device=dev)                       # stands in for the absent peer's array
+    table = torch.tensor([flags.data_ptr(), sink.data_ptr()], dtype=torch.int64, device=dev)
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    limit = 10_000_000                                                          # ~5 ms at 2 GHz
+    for expect_epoch in (1, 2):
+        status.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        native.check(native.lib().lmb_peer_barrier(flags.data_ptr(), table.data_ptr(), 0, 2, epoch.data_ptr(),
+                                                   status.data_ptr(), ctypes.c_longlong(limit), native.stream_ptr()),
+                     "peer_barrier")
+        end.record()
+        torch.cuda.synchronize()
+        assert int(status) == 101
+        assert int(epoch) == expect_epoch
+        assert int(flags[0]) == expect_epoch          # the rank's own signal to itself did arrive
+        assert start.elapsed_time(end) < 1000.0       # gave up after milliseconds, not the one-second default
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0                 # the context still works

@@ -65,3 +65,18 @@ def test_noalloc_scan_refuses_oversized_requests():
     rc = lib.lmb_exclusive_scan_u32_noalloc(x.data_ptr(), x.data_ptr(), MAX_ELEMS + 1,
                                             torch.cuda.current_stream().cuda_stream)
     assert rc == ERR_TOO_LARGE
+
+
+def test_noalloc_scan_in_place_and_at_the_size_limit():
+    """Two promises of the header: the output may be the input buffer, and exactly the maximum length is accepted."""
+    lib = _load()
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    for n in (1_000_003, MAX_ELEMS):
+        x = torch.randint(0, 200, (n,), dtype=torch.int32, device="cuda", generator=gen)
+        want = _existing(lib, x)
+        buf = x.clone()
+        rc = lib.lmb_exclusive_scan_u32_noalloc(buf.data_ptr(), buf.data_ptr(), n, stream)
+        assert rc == 0, f"entry point returned {rc}"
+        torch.cuda.synchronize()
+        assert torch.equal(buf, want)
