@@ -30,6 +30,50 @@ SAMPLES = 128
 BLOCK_M = (1000.0, 1000.0, 300.0)
 PLANE, LINE = 4096, 512
 BASELINE_VALUE = None  # the reference publishes no throughput number
+RENDER_HW = (1080, 1920)
+RENDER_FOCAL = 2317.6449482429634     # focal length of the reference's 1080p render tests (tests/utils.py:47-52)
+RENDER_CHUNK = 1 << 18
+
+
+def config_dict(n: int, regularisers: str = "none"):
+    """The ``config`` entry of the JSON line: identical text in both arms (storage precision goes under ``dtype``)."""
+    nx, ny = DIVISIONS[n]
+    return {"model": "GridNeRF branch-parallel large scene", "global_batch": RAYS_PER_GPU * n, "seq_len": SAMPLES,
+            "parallelism": f"branch{nx}x{ny}" if n > 1 else "single",
+            "planes": f"{PLANE}^2 x (16+48)ch per GPU", "lines": LINE, "regularisers": regularisers,
+            "l2_policy": "inputs larger than L2: every step gathers and scatters texels spread over the multi-GB planes "
+                         "(and their optimiser state) of each GPU"}
+
+
+def regulariser_weights(which: str):
+    """``shipped``: the weights every MatrixCity GridNeRF configuration of the reference sets
+    (benchmarks/nerf/gridnerf/confs/matrixcity_2block_multi_BranchParallel.py:42-46)."""
+    if which == "shipped":
+        return {"l1": 8e-5, "l1_rest": 4e-5, "tv_density": 0.1, "tv_app": 0.01}
+    return {"l1": 0.0, "l1_rest": 0.0, "tv_density": 0.0, "tv_app": 0.0}
+
+
+def render_scene(n: int):
+    """Scene of the render figures: the benchmark scene's footprint (one 1 km x 1 km block per GPU) with the grids
+    resampled so that the whole scene holds ``PLANE x PLANE`` texels (a merged checkpoint of 4.3 GB at every N; with
+    4096^2 texels per block the data-parallel replicas of both arms would need 8 x 34 GB of host memory at N = 8)."""
+    nx, ny = DIVISIONS[n]
+    return [0.0, 0.0, 0.0], [BLOCK_M[0] * nx, BLOCK_M[1] * ny, BLOCK_M[2]], [PLANE, PLANE, LINE]
+
+
+def render_poses(lb, ub, frames: int):
+    """Camera-to-world matrices (OpenGL axes: -z forward, +y up) of a short fly-over 400 m above the scene centre,
+    15 m per frame, tilted 10 degrees off nadir, so that every frame straddles the central block boundaries."""
+    import numpy as np
+
+    cx, cy = 0.5 * (lb[0] + ub[0]), 0.5 * (lb[1] + ub[1])
+    t = math.radians(10.0)
+    rot = np.array([[1.0, 0.0, 0.0], [0.0, math.cos(t), -math.sin(t)], [0.0, math.sin(t), math.cos(t)]])
+    poses = np.tile(np.eye(4, dtype=np.float32), (frames, 1, 1))
+    for k in range(frames):
+        poses[k, :3, :3] = rot
+        poses[k, :3, 3] = [cx - 30.0 + 15.0 * k, cy - 40.0 + 7.0 * k, lb[2] + 400.0]
+    return poses
 
 
 def make_ray_pool(n_rays: int, lb, ub, seed: int):
@@ -244,40 +288,97 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
             "ms_per_step": ms, "steps": steps, "loss_finite": bool(torch.isfinite(loss))}
 
 
-def render_fps_gridnerf(trainer, frames: int = 3):
-    """Secondary figure: 1920x1080 frames per second of the benchmark GridNeRF model (the trained grids of this run)
-    through the model's public chunked render call, nadir camera 400 m above the block, 128 samples per ray."""
+def time_engine_frames(engine, poses, rank, world, dev, call):
+    """Device time of ``engine(...)`` per frame: CUDA events on every rank around the call (rank 0 passes the pose, the
+    others call ``engine()``), barrier + synchronise on both sides, max over ranks.  The first two frames warm up.
+    A second pair of events also covers the copy of the finished image into pinned host memory on rank 0."""
     import torch
+    import torch.distributed as dist
 
-    from landmarksystem_b200.synthetic.scene import camera_rays, look_at
+    H, W = RENDER_HW
+    host = torch.empty(H, W, 4, dtype=torch.float32).pin_memory() if rank == 0 else None
+    frame_ms, e2e_ms, out = [], [], None
+    for k in range(len(poses)):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, end, end2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        start.record()
+        out = call(engine, poses[k]) if rank == 0 else engine()
+        end.record()
+        if rank == 0:
+            img = out[0] if isinstance(out, (tuple, list)) else out
+            host.copy_(img.to(torch.float32), non_blocking=True)
+        end2.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(end), start.elapsed_time(end2)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if k >= 2:
+            frame_ms.append(float(ms[0]))
+            e2e_ms.append(float(ms[1]))
+    img = (out[0] if isinstance(out, (tuple, list)) else out) if rank == 0 else None
+    return frame_ms, e2e_ms, img
 
-    model, cfg = trainer.module, trainer.config
-    dev = cfg.device
-    was_train = cfg.is_train
-    cfg.is_train = False
-    model.eval()
-    times = []
-    try:
-        with torch.no_grad():
-            for k in range(frames + 1):
-                cx, cy = 0.5 * (cfg.lb[0] + cfg.ub[0]) + 20.0 * k, 0.5 * (cfg.lb[1] + cfg.ub[1])
-                c2w = look_at(torch.tensor([cx, cy, 400.0]), torch.tensor([cx + 30.0, cy + 10.0, 0.0]), up=(0.0, 1.0, 0.0))
-                rays_o, rays_d = camera_rays(c2w, 1080, 1920, 1400.0, device=dev)       # (c2w, H, W, focal)
-                rays = torch.cat((rays_o, torch.nn.functional.normalize(rays_d, dim=-1)), -1)
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                start.record()
-                out = model.render_all_rays(rays, chunk_size=1 << 18, N_samples=SAMPLES)
-                end.record()
-                torch.cuda.synchronize()
-                if k >= 1:
-                    times.append(start.elapsed_time(end))
-        ms = statistics.median(times)
-        return {"metric": "GridNeRF 1080p render FPS", "value": 1000.0 / ms, "ms_per_frame": ms, "rays": 1920 * 1080,
-                "samples_per_ray": SAMPLES, "finite": bool(torch.isfinite(out["rgb_map"]).all())}
-    finally:
-        cfg.is_train = was_train
-        model.train()
+
+def render_phase_ours(holder, cfg, args, n, rank, world, dev):
+    """1920x1080 frames per second through the public engine (``landmarksystem_b200.init_inference``): the trainer's
+    model is resampled to the render scene, saved with the trainer's own checkpoint call (per-rank files merged by rank
+    0), and rendered (a) data parallel - every GPU holds the scene and renders a slice of the pixels - and, for N > 1,
+    (b) block model parallel - every GPU holds its blocks, renders its ray segments, and the cross-GPU ordered
+    composite merges them.  128 hull samples per ray, kernel runtime, same poses as the reference arm."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    import landmarksystem_b200 as lm
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF
+    from landmarksystem_b200.render.adapters import make_adapter
+    from landmarksystem_b200.utils import Config
+
+    trainer = holder["trainer"]
+    lb, ub, grid = render_scene(n)
+    if n > 1:
+        trainer.module.upsample_volume_grid(grid)         # per-block grids shrink so the scene totals PLANE^2 texels
+    trainer.save_ckpt(final=True, with_optimizer=False)
+    folder = trainer.logfolder
+    suffix = "-merged" if n > 1 else ""
+    holder["trainer"] = trainer = None
+    gc.collect()
+    torch.cuda.empty_cache()
+    poses = render_poses(lb, ub, args.render_frames + 2)
+    H, W = RENDER_HW
+    results = []
+    modes = [("dp", None if n == 1 else {"tp_size": 1})] + ([("block", {"tp_size": n, "mode": "block"})] if n > 1 else [])
+    for mode, parallel in modes:
+        mc = Config({k: v for k, v in dict(cfg).items() if not k.endswith("_group")})
+        mc.update(is_train=False, branch_parallel=False, DDP=False, model_parallel=False, cuda_graph=False, sampling_opt=True,
+                  n_importance=SAMPLES, ckpt=os.path.join(folder, f"state_dict{suffix}.th"),
+                  kwargs=os.path.join(folder, f"kwargs{suffix}.th"), device=str(dev))
+        inf = {"runtime": "Kernel", "kernel_fusion": True}
+        if parallel is not None:
+            inf["parallel_config"] = parallel
+        engine = lm.init_inference(GridNeRF, make_adapter(GridNeRF), mc, Config(inf))
+        frame_ms, e2e_ms, img = time_engine_frames(
+            engine, poses, rank, world, dev, lambda e, pose: e(torch.from_numpy(pose), RENDER_CHUNK, H, W, RENDER_FOCAL))
+        ms, ms2 = statistics.median(frame_ms), statistics.median(e2e_ms)
+        entry = {"metric": "GridNeRF 1080p render FPS through init_inference", "mode": mode, "value": 1000.0 / ms,
+                 "ms_per_frame": ms, "e2e_value": 1000.0 / ms2, "e2e_ms_per_frame": ms2,
+                 "d2h_bytes_per_frame": H * W * 4 * 4, "frames": len(frame_ms), "n_gpus": n, "samples_per_ray": SAMPLES,
+                 "chunk_rays": RENDER_CHUNK, "scene": {"lb": lb, "ub": ub, "texels": grid[:2], "blocks": DIVISIONS[n]}}
+        if rank == 0:
+            rgb = img[..., :3].float()
+            entry["image_mean"] = float(rgb.mean())
+            entry["image_std"] = float(rgb.std())
+        results.append(entry)
+        engine.close()
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+    return results
 
 
 def run_ours(args):
@@ -301,6 +402,9 @@ def run_ours(args):
     cfg.branch_parallel = n > 1
     cfg.branch_dispatch = "a2a"      # every rank brings its own rays; samples travel to the block's owner
     cfg.batch_size = RAYS_PER_GPU * n
+    w = regulariser_weights(args.regularisers)
+    cfg.L1_weight_inital, cfg.L1_weight_rest = w["l1"], w["l1_rest"]
+    cfg.TV_weight_density, cfg.TV_weight_app = w["tv_density"], w["tv_app"]
     if os.environ.get("LMB_CUDA_GRAPH") is not None:          # debugging switch: 0 runs every step eagerly
         cfg.cuda_graph = os.environ["LMB_CUDA_GRAPH"] not in ("0", "false", "")
     def make_trainer():
@@ -340,9 +444,13 @@ def run_ours(args):
     host = torch.cat((rays, rgbs, idxs[:, None]), -1).view(pool_steps, RAYS_PER_GPU, 10).pin_memory()
     resident = host.to(dev)
 
+    losses = []
+
     def step_resident(k):
         b = resident[k % pool_steps]
-        return holder["trainer"].train_step(b[:, :6], b[:, 6:9], b[:, 9])
+        loss = holder["trainer"].train_step(b[:, :6], b[:, 6:9], b[:, 9])
+        losses.append(loss.clone())           # device-side copy; read on the host after the timed region
+        return loss
 
     # End to end: every step copies its batch from pinned host memory and its loss is read back on the host.
     # The read-back is pipelined by one step (async copy into pinned memory + event, consumed after the next
@@ -398,6 +506,7 @@ def run_ours(args):
     ms = timed(step_resident, steps)
     sampler.mark(t0, time.time())
     launches = native.LAUNCH_CALLS - launches0
+    loss_first, loss_last = float(losses[0]), float(losses[-1])      # first warm-up step and last timed step (rank 0's rays)
     # The end-to-end run starts from a freshly initialised model (same seed), so both figures cover the same training
     # steps: the step gets heavier as the field learns (more samples pass the weight threshold and reach the colour
     # stage), and a run that merely continued would time later, slower steps than the device-resident one.
@@ -413,36 +522,66 @@ def run_ours(args):
     ms_e2e = timed(step_e2e, steps, drain_e2e)
     sampler.mark(t0, time.time())
     clocks = sampler.stop() if rank == 0 else None
-    also = None
-    if n == 1 and not os.environ.get("LMB_BENCH_NO_EXTRA"):
-        also = []
-        for name, fn in (("GridNeRF 1080p render FPS", lambda: render_fps_gridnerf(holder["trainer"])),
-                         ("3DGS 1080p render FPS", render_fps_3dgs),
-                         ("InstantNGP training rays/s", train_rate_ngp)):
-            try:
-                also.append(fn())
-            except Exception as exc:  # the headline number must not depend on the secondary ones
-                also.append({"metric": name, "error": f"{type(exc).__name__}: {exc}"[:200]})
-            torch.cuda.empty_cache()
+    value = global_batch * steps / (ms / 1e3)
+    e2e = global_batch * steps / (ms_e2e / 1e3)
+    line = {}
+
+    def emit():
+        if rank == 0 and not line.get("printed"):
+            line["printed"] = True
+            print(json.dumps(line["body"]), flush=True)
+
+    def give_up():
+        # a secondary figure did not finish in time (watchdog thread): the headline line goes out with what is there,
+        # then every rank ends
+        if rank == 0:
+            line["body"]["also"] = list(also) + [{"error": "secondary benchmarks exceeded their time limit"}]
+            emit()
+        os._exit(0)
+
+    also = []
+    extras = not os.environ.get("LMB_BENCH_NO_EXTRA")
     if rank == 0:
-        value = global_batch * steps / (ms / 1e3)
-        e2e = global_batch * steps / (ms_e2e / 1e3)
-        print(json.dumps({
+        line["body"] = ({
             "metric": "train rays/s", "value": value, "unit": "rays/s", "n_gpus": n, "steps": steps, "warmup": warmup,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "GridNeRF branch-parallel large scene", "global_batch": global_batch,
-                       "seq_len": SAMPLES, "parallelism": f"branch{nx}x{ny}" if n > 1 else "single",
-                       "planes": f"{PLANE}^2 x (16+48)ch bf16 + fp32 master per GPU", "lines": LINE,
-                       "l2_policy": "inputs larger than L2: each step touches ~3 GB of plane texels, moments and gradients scattered over 21 GB of parameters and optimiser state"},
+            "config": config_dict(n, args.regularisers),
+            "storage": "bf16 grid shadows + fp32 masters",
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "rays/s", "ms_per_step": ms_e2e / steps,
                     "h2d_bytes_per_step": RAYS_PER_GPU * 10 * 4, "d2h_bytes_per_step": 4,
-                    "note": "bytes are per rank; every step's batch comes from pinned host memory and every step's loss is read on the host, the read lagging one step behind the launch"},
+                    "note": "bytes are per rank; every step's batch comes from pinned host memory and every step's loss "
+                            "is read on the host; the read is pipelined one step behind the launch (the reference arm "
+                            "synchronises on its loss every step)"},
             "gpu_launches": launches,
+            "loss_first": loss_first, "loss_last": loss_last,
             "also": also,
-        }), flush=True)
+        })
+    if extras:
+        import threading
+
+        watchdog = threading.Timer(float(os.environ.get("LMB_BENCH_EXTRA_LIMIT_S", "900")), give_up)
+        watchdog.daemon = True
+        watchdog.start()
+        try:
+            also.extend(render_phase_ours(holder, cfg, args, n, rank, world, dev))
+        except Exception as exc:  # the headline number must not depend on the secondary ones
+            also.append({"metric": "GridNeRF 1080p render FPS through init_inference",
+                         "error": f"{type(exc).__name__}: {exc}"[:300]})
+        holder["trainer"] = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        if n == 1:
+            for name, fn in (("3DGS 1080p render FPS", render_fps_3dgs), ("InstantNGP training rays/s", train_rate_ngp)):
+                try:
+                    also.append(fn())
+                except Exception as exc:
+                    also.append({"metric": name, "error": f"{type(exc).__name__}: {exc}"[:200]})
+                torch.cuda.empty_cache()
+        watchdog.cancel()
+    emit()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -458,6 +597,9 @@ def main():
                     help="run one secondary single-GPU benchmark alone and print its JSON (--profile adds the PyTorch "
                          "profiler's kernel table of two more steps on stderr)")
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--render-frames", type=int, default=5, help="timed 1080p frames of the render figures (after 2 warm-up frames)")
+    ap.add_argument("--regularisers", type=str, default="none", choices=["none", "shipped"],
+                    help="shipped: the L1 / total-variation weights of the reference's MatrixCity GridNeRF configurations")
     args = ap.parse_args()
     if args.only is not None:
         import torch
@@ -474,7 +616,7 @@ def main():
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 
-        run_reference(args, DIVISIONS, RAYS_PER_GPU, SAMPLES, BLOCK_M, PLANE, LINE, make_ray_pool, ClockSampler)
+        run_reference(args, sys.modules[__name__])
     else:
         run_ours(args)
 

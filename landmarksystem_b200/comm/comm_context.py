@@ -115,6 +115,11 @@ class CommContext(metaclass=SingletonMeta):
 def init_communication_context(parallel_config: Config, backend: str = None, dist_url: str = "env://"):
     ctx = CommContext()
     if ctx.is_initialized():
+        # a trainer (or an earlier engine) of this process brought the context up: keep the process group, and build
+        # the render-side groups if they are missing or were laid out for another tensor-parallel size
+        want_tp = int(parallel_config.get("tp_size", 1)) if hasattr(parallel_config, "get") else 1
+        if CommMode.DATA_PARALLEL not in ctx._records or ctx.tensor_parallel_size != want_tp:
+            ctx.init_groups(parallel_config)
         return
     assert hasattr(parallel_config, _RANK_STR) and hasattr(parallel_config, _WORLD_SIZE_STR)
     ctx.init_distributed_env(world_size=parallel_config.world_size, rank=parallel_config.rank, backend=backend,

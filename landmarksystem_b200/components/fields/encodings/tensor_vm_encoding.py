@@ -56,7 +56,8 @@ class TensorVMEncoding(VolumeEncoding):
     _VECTOR_MODE = [2, 1, 0]
 
     def __init__(self, ndims: int, resolution_mode: List[int], n_component, grid_size, device,
-                 param_shape: Optional[Dict[str, Sequence[int]]] = None, n_blocks: int = 1, scale: float = 0.1):
+                 param_shape: Optional[Dict[str, Sequence[int]]] = None, n_blocks: int = 1, scale: float = 0.1,
+                 random_init: bool = True):
         super().__init__()
         self.ndims = ndims
         self.matrix_mode = self._MATRIX_MODE[:ndims]
@@ -76,8 +77,12 @@ class TensorVMEncoding(VolumeEncoding):
                     Z = int(param_shape[f"line_coef.{i * len(self.reso_mode) + idx}"][2])
                 else:
                     C, B, H, W, Z = self.n_component[i], n_blocks, grid[m1] * j, grid[m0] * j, grid[vec_id] * j
-                planes.append(torch.nn.Parameter(scale * torch.randn(B, H, W, C, device=device)))
-                lines.append(torch.nn.Parameter(scale * torch.randn(B, Z, C, device=device)))
+                if random_init:
+                    planes.append(torch.nn.Parameter(scale * torch.randn(B, H, W, C, device=device)))
+                    lines.append(torch.nn.Parameter(scale * torch.randn(B, Z, C, device=device)))
+                else:       # a checkpoint is loaded right after construction: skip the (slow, on the CPU) random fill
+                    planes.append(torch.nn.Parameter(torch.zeros(B, H, W, C, device=device)))
+                    lines.append(torch.nn.Parameter(torch.zeros(B, Z, C, device=device)))
         self.plane_coef = torch.nn.ParameterList(planes)
         self.line_coef = torch.nn.ParameterList(lines)
         self.save_init_kwargs(locals())

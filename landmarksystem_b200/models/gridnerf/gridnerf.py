@@ -242,10 +242,11 @@ class GridNeRF(BaseNeRF):
         grid[0], grid[1] = grid[0] // part[0], grid[1] // part[1]
         n_blocks = self._local_blocks()
         shapes = self.grid_shape or {}
+        fill = not bool(cfg.get("grids_come_from_ckpt", False))
         self.density_encoding = TensorVMEncoding(cfg.ndims, cfg.resMode, cfg.n_lamb_sigma, grid, self.device,
-                                                 param_shape=shapes.get("density_encoding"), n_blocks=n_blocks)
+                                                 param_shape=shapes.get("density_encoding"), n_blocks=n_blocks, random_init=fill)
         self.rgb_encoding = TensorVMEncoding(cfg.ndims, cfg.resMode, cfg.n_lamb_sh, grid, self.device,
-                                             param_shape=shapes.get("rgb_encoding"), n_blocks=n_blocks)
+                                             param_shape=shapes.get("rgb_encoding"), n_blocks=n_blocks, random_init=fill)
         self.feature2density = Feature2Density(sum(self.density_encoding.n_component), len(cfg.resMode),
                                                cfg.nonlinear_density, cfg.density_shift, cfg.fea2denseAct).to(self.device)
         self.rgb_decoder = RGBDecoder(self.rgb_encoding.n_component, cfg.resMode, self.app_dim, cfg.view_pe,
@@ -484,7 +485,7 @@ class GridNeRF(BaseNeRF):
         S_req = n_samples if n_samples > 0 else self.sampler.num_samples
         a2a = self._use_a2a()
         mp_train = bool(getattr(cfg, "branch_parallel", False)) and train
-        fused_front = (rays.is_cuda and not hull and self.alphaMask is None and self.scene_manager is not None
+        fused_front = (rays.is_cuda and not (hull and train) and self.alphaMask is None and self.scene_manager is not None
                        and bool(cfg.get("fused_sampler", True)) and (a2a or not mp_train) and not cfg.encode_app)
         origin, dirs = rays[:, :3], rays[:, 3:6]
         if fused_front:
@@ -496,7 +497,7 @@ class GridNeRF(BaseNeRF):
             z, dists, xyzb, valid = uniform_sample_blocks(
                 rays, S_req, self.aabb, float(self.sampler.near_far[0]), float(self.sampler.near_far[1]),
                 float(self.sampler.step_size), sm._norm_lo, sm.aabb_norm_size, sm._partition,
-                (sm.relative_block_idx_x, sm.relative_block_idx_y), tuple(sm.local_block_partition), jitter)
+                (sm.relative_block_idx_x, sm.relative_block_idx_y), tuple(sm.local_block_partition), jitter, hull=hull)
             R, S = z.shape
             if a2a:
                 disp = self._dispatcher(R * S)
@@ -605,20 +606,32 @@ class GridNeRF(BaseNeRF):
         from ...parallel.composite_merge import pack_partial
 
         cfg = self.config
-        S_req = N_samples if N_samples > 0 else self.sampler.num_samples
+        hull = bool(cfg.sampling_opt)                     # same sampling as the single-model render of this configuration
+        S_req = cfg.n_importance if hull else (N_samples if N_samples > 0 else self.sampler.num_samples)
         origin, dirs = rays[:, :3], rays[:, 3:6]
-        z = self.sampler.compute_z_vals(rays, S_req, False, False)
-        R, S = z.shape
-        xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
-        valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
-        if self.alphaMask is not None:
-            valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
-        local, block = self.scene_manager.block_local_coords(self.scene_manager.normalize_coord(xyz))
-        block = torch.where(valid, block, torch.full_like(block, -1.0))
-        xyzb = torch.cat((local, block[:, None]), dim=-1)
-        mine = (block >= 0)
+        sm = self.scene_manager
+        if rays.is_cuda and self.alphaMask is None and bool(cfg.get("fused_sampler", True)):
+            from ...ops.sampler import uniform_sample_blocks
+
+            z, dists, xyzb, _ = uniform_sample_blocks(
+                rays, S_req, self.aabb, float(self.sampler.near_far[0]), float(self.sampler.near_far[1]),
+                float(self.sampler.step_size), sm._norm_lo, sm.aabb_norm_size, sm._partition,
+                (sm.relative_block_idx_x, sm.relative_block_idx_y), tuple(sm.local_block_partition), None, hull=hull)
+            R, S = z.shape
+            mine = xyzb[:, 3] >= 0
+        else:
+            z = self.sampler.compute_z_vals(rays, S_req, False, hull)
+            R, S = z.shape
+            xyz = (origin[:, None, :] + dirs[:, None, :] * z[..., None]).reshape(-1, 3)
+            valid = ~((xyz < self.aabb[0]) | (xyz > self.aabb[1])).any(dim=-1)
+            if self.alphaMask is not None:
+                valid = valid & (self.alphaMask.sample_alpha(xyz) > cfg.alpha_mask_filter_thre)
+            local, block = sm.block_local_coords(sm.normalize_coord(xyz))
+            block = torch.where(valid, block, torch.full_like(block, -1.0))
+            xyzb = torch.cat((local, block[:, None]), dim=-1)
+            mine = (block >= 0)
+            dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
         sigma = (self._density(xyzb) * mine.to(torch.float32)).view(R, S)      # softplus heads are not zero at no-data
-        dists = torch.cat((z[:, 1:] - z[:, :-1], torch.zeros_like(z[:, :1])), dim=-1)
         weight, trans = composite_weights(sigma, dists * cfg.distance_scale)
         app_mask = ((weight > cfg.rayMarch_weight_thres) & mine.view(R, S)).reshape(-1)
         if self._fused_app_stage_ok(xyzb):

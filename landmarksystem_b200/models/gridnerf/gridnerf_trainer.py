@@ -378,11 +378,14 @@ class GridNeRFTrainer(NeRFTrainer):
         return self._async_ckpt.save_step(step, state, rank=int(cfg.rank), world=int(cfg.world_size), store=store,
                                           meta={"expname": cfg.expname, "model": "GridNeRF"})
 
-    def save_ckpt(self, final: bool = False):
+    def save_ckpt(self, final: bool = False, with_optimizer: bool = True):
+        """Model (and optimiser) files in the reference layout; model-parallel runs write one file per rank and, with
+        ``final``, rank 0 merges them into ``state_dict-merged.th`` / ``kwargs-merged.th``."""
         cfg = self.config
         if cfg.model_parallel:
             self.module.save_model(self.logfolder, rank=cfg.mp_rank) if cfg.dp_rank == 0 else None
-            self.save_optimizer()
+            if with_optimizer:
+                self.save_optimizer()
             self.barrier()
             if final and cfg.rank == 0 and cfg.branch_parallel:
                 n = cfg.model_parallel_degree
@@ -395,7 +398,7 @@ class GridNeRFTrainer(NeRFTrainer):
         else:
             if is_main_rank():
                 self.module.save_model(self.logfolder)
-            if is_main_rank() or bool(getattr(self.optimizer, "partitioned", False)):
+            if with_optimizer and (is_main_rank() or bool(getattr(self.optimizer, "partitioned", False))):
                 self.save_optimizer()
 
     # -- evaluation ----------------------------------------------------------------------------------

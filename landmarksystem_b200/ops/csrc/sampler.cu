@@ -14,6 +14,7 @@ struct SamplerArgs {
   int nx, ny;                   // block partition of the scene footprint
   int rel_x, rel_y, lx, ly;     // resident window: origin block and extent (ids are window-relative)
   int S;
+  int hull;                     // 1: S samples linearly spaced from `near` to the ground-plane hit (render-time sampling)
 };
 
 // rays: [R, stride] (origin 3, direction 3, ...); jitter: [R] in [0,1) or null; aabb: device float[6] (min, max)
@@ -39,9 +40,22 @@ uniform_sampler_kernel(const float* __restrict__ rays, int stride, long long R, 
     tmin = fmaxf(tmin, fminf(__fdiv_rn(__fsub_rn(hi[c], o[c]), safe), __fdiv_rn(__fsub_rn(lo[c], o[c]), safe)));
   }
   tmin = fminf(fmaxf(tmin, a.near), a.far);
-  const float zk = __fadd_rn(tmin, __fmul_rn(a.step, __fadd_rn((float)k, jitter ? jitter[r] : 0.f)));
+  float zk, dk;
+  if (a.hull) {
+    // near -> where the ray meets the ground plane z = lo_z (rays that look up: `far`), linspace over S samples
+    const float dz = d[2];
+    float hit = -((o[2] - lo[2]) / (dz == 0.f ? 1e-6f : dz));
+    if (dz >= 0.f) hit = a.far;
+    const float inv = a.S > 1 ? 1.f / (float)(a.S - 1) : 0.f;
+    const float t0 = (float)k * inv, t1 = (float)(k + 1) * inv;
+    zk = a.near * (1.f - t0) + hit * t0;
+    dk = k + 1 < a.S ? (a.near * (1.f - t1) + hit * t1) - zk : 0.f;
+  } else {
+    zk = __fadd_rn(tmin, __fmul_rn(a.step, __fadd_rn((float)k, jitter ? jitter[r] : 0.f)));
+    dk = k + 1 < a.S ? a.step : 0.f;
+  }
   z[i] = zk;
-  dists[i] = k + 1 < a.S ? a.step : 0.f;
+  dists[i] = dk;
   float p[3];
   bool inside = true;
 #pragma unroll
@@ -68,10 +82,10 @@ using namespace lmb;
 
 LMB_API int lmb_uniform_sampler(const float* rays, int stride, long long R, int S, const float* jitter, const float* aabb,
                                 float near, float far, float step, float norm_lo, float norm_size, int nx, int ny, int rel_x,
-                                int rel_y, int lx, int ly, float* z, float* dists, float* xyzb, unsigned char* valid,
-                                cudaStream_t stream) {
+                                int rel_y, int lx, int ly, int hull, float* z, float* dists, float* xyzb,
+                                unsigned char* valid, cudaStream_t stream) {
   if (R <= 0 || S <= 0) return 0;
-  SamplerArgs a{near, far, step, norm_lo, norm_size, nx, ny, rel_x, rel_y, lx, ly, S};
+  SamplerArgs a{near, far, step, norm_lo, norm_size, nx, ny, rel_x, rel_y, lx, ly, S, hull};
   uniform_sampler_kernel<<<ceil_div(R * S, 256), 256, 0, stream>>>(rays, stride, R, jitter, aabb, a, z, dists, (float4*)xyzb,
                                                                   valid);
   LMB_LAUNCH_CHECK();

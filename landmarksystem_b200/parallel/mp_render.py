@@ -16,15 +16,25 @@ import torch
 from .composite_merge import CompositeMerger, merge_reference
 
 
+def block_window_of(part: int, parts: int, nx: int, ny: int):
+    """Rectangular window of scene blocks kept by rank ``part`` of ``parts``: the ``nx x ny`` block lattice is cut into
+    ``px x py = parts`` equal rectangles, rows first (``px`` is the largest divisor of ``parts`` that also divides
+    ``nx``).  Returns ``(row0, col0, rows, cols)``."""
+    px = max(d for d in range(1, parts + 1) if parts % d == 0 and nx % d == 0)
+    py = parts // px
+    assert ny % py == 0, f"a {nx} x {ny} block lattice cannot be cut into {parts} equal rectangles"
+    rows, cols = nx // px, ny // py
+    return (part // py) * rows, (part % py) * cols, rows, cols
+
+
 def slice_model_to_block_window(model, part: int, parts: int):
-    """Keep only the ``part``-th of ``parts`` equal row bands of the model's spatial blocks (blocks are ordered
+    """Keep only the ``part``-th of ``parts`` equal rectangles of the model's spatial blocks (blocks are ordered
     ``bx * ny + by``): the grids of every plane/line encoding are sliced and the scene manager's resident window is set
-    accordingly, so lookups outside the band return "no data".  Returns ``(first_block, n_blocks)``."""
+    accordingly, so lookups outside the window return "no data".  Returns ``(first_block, n_blocks)``."""
     sm = model.scene_manager
     nx, ny = sm._partition
-    assert nx % parts == 0, f"{nx} block rows cannot be split evenly over {parts} ranks"
-    rows = nx // parts
-    first, count = part * rows * ny, rows * ny
+    row0, col0, rows, cols = block_window_of(part, parts, nx, ny)
+    keep = torch.tensor([(row0 + r) * ny + (col0 + c) for r in range(rows) for c in range(cols)], dtype=torch.long)
     for enc in model.modules():
         planes, lines = getattr(enc, "plane_coef", None), getattr(enc, "line_coef", None)
         if planes is None or lines is None:
@@ -32,12 +42,12 @@ def slice_model_to_block_window(model, part: int, parts: int):
         for plist in (planes, lines):
             for p in plist:
                 if p.shape[0] == nx * ny:
-                    p.data = p.data[first:first + count].contiguous()
+                    p.data = p.data.index_select(0, keep.to(p.device)).contiguous()
         if getattr(enc, "use_shadow", False):
             enc.enable_shadow(False)
-    sm.assign_local_block_partition([rows, ny])
-    sm.assign_relative_block_idx(first)
-    return first, count
+    sm.assign_local_block_partition([rows, cols])
+    sm.assign_relative_block_idx(row0 * ny + col0)
+    return row0 * ny + col0, rows * cols
 
 
 class ModelParallelRenderer:

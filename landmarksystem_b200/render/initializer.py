@@ -29,6 +29,7 @@ class InferenceModuleInitializer:
             if _OFFLOAD_CONFIG_STR in inference_config and issubclass(self.based_model_cls, BaseGaussian):
                 raise AssertionError("not support offload in Gaussian models")
             model_config.device = "cpu"
+            model_config.grids_come_from_ckpt = True      # the engine loads the checkpoint right after construction
             kwargs["scene_manager"] = SceneManager(model_config)
             if "device" in kwargs:
                 kwargs["device"] = "cpu"

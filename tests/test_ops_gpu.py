@@ -501,3 +501,43 @@ def test_segment_amax_kernel_matches_scatter_reduce():
     ref = segment_amax(values, index, 700)
     out = segment_amax(values.cuda(), index.cuda(), 700)
     assert torch.equal(out.cpu(), ref) and torch.isinf(ref[13]).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hull", [False, True])
+def test_fused_sampler_matches_the_unfused_front_end(hull):
+    """Sampling distances, block-local coordinates and window-relative block ids from the one-kernel front end against
+    ``UniformSampler.compute_z_vals`` + ``SceneManager.block_local_coords`` (dense spacing and render-time hull spacing)."""
+    from landmarksystem_b200.components.ray_samplers import UniformSampler
+    from landmarksystem_b200.components.scene import SceneManager
+    from landmarksystem_b200.ops.sampler import uniform_sample_blocks
+    from landmarksystem_b200.utils import Config
+
+    g = torch.Generator().manual_seed(3)
+    cfg = Config(lb=[0.0, 0.0, 0.0], ub=[200.0, 400.0, 30.0], plane_division=[2, 4], device=DEV)
+    sm = SceneManager(cfg)
+    sm.assign_local_block_partition([1, 2])
+    sm.assign_relative_block_idx(1 * 4 + 1)
+    R, S = 777, 48
+    o = torch.stack((torch.rand(R, generator=g) * 200, torch.rand(R, generator=g) * 400, 80 + torch.rand(R, generator=g) * 20), -1)
+    d = torch.nn.functional.normalize(torch.stack((torch.randn(R, generator=g) * 0.4, torch.randn(R, generator=g) * 0.4,
+                                                   -torch.ones(R)), -1), dim=-1)
+    d[:5, 2] = 0.3                                                   # a few rays look up: hull mode ends at `far`
+    rays = torch.cat((o, d), -1).to(DEV)
+    sampler = UniformSampler(num_samples=S, step_size=2.5, aabb=sm.aabb, near_far=[5.0, 300.0])
+    z_ref = sampler.compute_z_vals(rays, S, False, hull)
+    xyz = (rays[:, None, :3] + rays[:, None, 3:6] * z_ref[..., None]).reshape(-1, 3)
+    inside = ~((xyz < sm.aabb[0]) | (xyz > sm.aabb[1])).any(-1)
+    local, block = sm.block_local_coords(sm.normalize_coord(xyz))
+    block = torch.where(inside, block, torch.full_like(block, -1.0))
+    z, dists, xyzb, valid = uniform_sample_blocks(rays, S, sm.aabb, 5.0, 300.0, 2.5, sm._norm_lo, sm.aabb_norm_size, sm._partition,
+                                                  (sm.relative_block_idx_x, sm.relative_block_idx_y),
+                                                  tuple(sm.local_block_partition), None, hull=hull)
+    torch.testing.assert_close(z, z_ref, rtol=1e-5, atol=1e-3)
+    want_d = torch.cat((z_ref[:, 1:] - z_ref[:, :-1], torch.zeros_like(z_ref[:, :1])), -1)
+    torch.testing.assert_close(dists, want_d, rtol=1e-4, atol=1e-3)
+    # samples within a hair of a block or box face may land on the other side; everything else must agree exactly
+    same = xyzb[:, 3] == block
+    assert same.float().mean() > 0.999
+    torch.testing.assert_close(xyzb[same][:, :3], local[same], rtol=1e-4, atol=1e-4)
+    assert (valid == inside).float().mean() > 0.999
