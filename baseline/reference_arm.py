@@ -206,9 +206,24 @@ def _render_phase(bench, args, trainer, cfg, n, rank, world, work):
     torch.cuda.empty_cache()
     from landmark.communicator import destroy_communication_context
 
-    destroy_communication_context()           # the engine brings up its own context (data / tensor parallel groups)
-    if "TORCHELASTIC_RUN_ID" not in os.environ:
-        os.environ["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29533")) + 7)
+    # The engine brings up its own communication context (data / tensor parallel groups), so the trainer's is taken
+    # down first.  The second rendezvous must not reuse the first one's key-value store: a process group that is
+    # re-created over the same store finds the keys the first one left there (the NCCL id exchange among them).
+    # Rank 0 therefore picks a free port and the new group gets a store of its own there.
+    port = [0]
+    if n > 1:
+        if rank == 0:
+            import socket
+
+            with socket.socket() as sock:
+                sock.bind(("127.0.0.1", 0))
+                port[0] = sock.getsockname()[1]
+        dist.broadcast_object_list(port, src=0)
+    destroy_communication_context()
+    if n > 1:
+        os.environ["TORCHELASTIC_USE_AGENT_STORE"] = "False"
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port[0])
     conf_path = os.path.join(work, f"render_conf_rank{rank}.py")
     with open(conf_path, "w", encoding="utf-8") as fh:
         fh.write(_RENDER_CONF.format(basedir=os.path.join(work, "log"), ckpt=ckpt, kwargs=kwargs_fp, division=[nx, ny],
@@ -357,30 +372,49 @@ def _run(args, ref_root, bench):
     ms = float(ms)
     clocks = sampler.stop() if rank == 0 else None
     also = []
+    value = global_batch * steps / (ms / 1e3)
+    body = {
+        "metric": "train rays/s", "value": value, "unit": "rays/s", "n_gpus": n, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16 autocast (reference default)", "data": "synthetic", "impl": "reference",
+        "config": bench.config_dict(n, args.regularisers),
+        "storage": "fp32 grids",
+        "clocks": clocks,
+        "e2e": {"value": value, "unit": "rays/s", "ms_per_step": ms / steps,
+                "h2d_bytes_per_step": global_batch * 10 * 4, "d2h_bytes_per_step": 4,
+                "note": "the stock train() loop copies every batch from pinned host memory and reads its loss on the "
+                        "host every step; value and e2e are the same measurement"},
+        "gpu_launches": 0,
+        "loss_first": float(seen[1]) if 1 in seen else None,
+        "loss_last": float(seen[warmup + steps]) if (warmup + steps) in seen else None,
+        "also": also,
+    }
+    printed = []
+
+    def emit():
+        if rank == 0 and not printed:
+            printed.append(True)
+            print(json.dumps(body), flush=True)
+
+    def give_up():           # watchdog thread: the training figure goes out even if the render figure never finishes
+        body["also"] = list(also) + [{"metric": "GridNeRF 1080p render FPS through init_inference",
+                                      "error": "did not finish within its time limit"}]
+        emit()
+        os._exit(0)
+
     if not os.environ.get("LMB_BENCH_NO_EXTRA"):
+        import threading
+
+        watchdog = threading.Timer(float(os.environ.get("LMB_BENCH_EXTRA_LIMIT_S", "900")), give_up)
+        watchdog.daemon = True
+        watchdog.start()
         try:
-            also = _render_phase(bench, args, trainer, cfg, n, rank, world, work)
+            also.extend(_render_phase(bench, args, trainer, cfg, n, rank, world, work))
         except Exception as exc:  # the training figure must not depend on the render figure
-            also = [{"metric": "GridNeRF 1080p render FPS through init_inference",
-                     "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]}]
-    if rank == 0:
-        value = global_batch * steps / (ms / 1e3)
-        print(json.dumps({
-            "metric": "train rays/s", "value": value, "unit": "rays/s", "n_gpus": n, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp16 autocast (reference default)", "data": "synthetic", "impl": "reference",
-            "config": bench.config_dict(n, args.regularisers),
-            "storage": "fp32 grids",
-            "clocks": clocks,
-            "e2e": {"value": value, "unit": "rays/s", "ms_per_step": ms / steps,
-                    "h2d_bytes_per_step": global_batch * 10 * 4, "d2h_bytes_per_step": 4,
-                    "note": "the stock train() loop copies every batch from pinned host memory and reads its loss on the "
-                            "host every step; value and e2e are the same measurement"},
-            "gpu_launches": 0,
-            "loss_first": float(seen[1]) if 1 in seen else None,
-            "loss_last": float(seen[warmup + steps]) if (warmup + steps) in seen else None,
-            "also": also,
-        }), flush=True)
+            also.append({"metric": "GridNeRF 1080p render FPS through init_inference",
+                         "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]})
+        watchdog.cancel()
+    emit()
     if dist.is_initialized():
         if world > 1:
             dist.barrier()

@@ -287,7 +287,8 @@ class ChannelParallelTensorVMEncoding(TensorVMEncoding):
     i.e. twice the bytes).  ``init_state_dict`` (reference layout, full channels) seeds the slices."""
 
     def __init__(self, ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
-                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None):
+                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None,
+                 random_init: bool = True):
         comps = list(n_component) if isinstance(n_component, (list, tuple)) else [n_component] * 3
         assert all(c % parallel_degree == 0 and (c // parallel_degree) % 8 == 0 for c in comps[:ndims]), \
             "channel-parallel slices must keep a multiple of 8 channels per rank"
@@ -295,7 +296,7 @@ class ChannelParallelTensorVMEncoding(TensorVMEncoding):
         self.full_component = comps[:ndims]
         local = [c // parallel_degree for c in comps]
         super().__init__(ndims, resolution_mode, local, grid_size, device, param_shape=None, n_blocks=n_blocks,
-                         scale=scale)
+                         scale=scale, random_init=random_init and init_state_dict is None)
         if init_state_dict is not None:
             self.load_full_state(init_state_dict)
         self.merge_config = {}  # channel slices are not spatial blocks
@@ -362,10 +363,11 @@ class BranchParallelTensorVMEncoding(TensorVMEncoding):
     as a single-process run with the same seed (reference: tensor_vm_encoding.py:554-636)."""
 
     def __init__(self, ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
-                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None):
+                 scale=0.1, parallel_degree: int = 1, parallel_part: int = 0, group=None, init_state_dict=None,
+                 random_init: bool = True):
         self.parallel_degree, self.parallel_part, self.group = parallel_degree, parallel_part, group
         super().__init__(ndims, resolution_mode, n_component, grid_size, device, param_shape=None, n_blocks=1,
-                         scale=scale)
+                         scale=scale, random_init=random_init and init_state_dict is None)
         if init_state_dict is not None:
             self.load_full_state(init_state_dict)
         elif parallel_degree > 1 and torch.distributed.is_initialized():
