@@ -417,18 +417,28 @@ def run_ours(args):
         from torch.profiler import ProfilerActivity
         from torch.profiler import profile as torch_profile
 
-        cfg.cuda_graph = False
+        # LMB_PROFILE_EAGER=1 profiles eager steps; the default profiles the CUDA-graph replays of the timed benchmark
+        # (kernel durations then include the time a kernel spends waiting for its peers under lock-step replay)
+        if os.environ.get("LMB_PROFILE_EAGER"):
+            cfg.cuda_graph = False
         t = make_trainer()
         rays, rgbs, idxs = make_ray_pool(RAYS_PER_GPU * 4, cfg.lb, cfg.ub, seed=1234 + rank)
         b = torch.cat((rays, rgbs, idxs[:, None]), -1).view(4, RAYS_PER_GPU, 10).to(t.config.device)
-        for k in range(4):
-            t.train_step(b[k][:, :6], b[k][:, 6:9], b[k][:, 9])
+        for k in range(8):
+            t.train_step(b[k % 4][:, :6], b[k % 4][:, 6:9], b[k % 4][:, 9])
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
         with torch_profile(activities=[ProfilerActivity.CUDA]) as prof:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             for k in range(3):
                 t.train_step(b[k][:, :6], b[k][:, 6:9], b[k][:, 9])
+            e1.record()
             torch.cuda.synchronize()
         if rank == 0:
+            print(f"profiled steps: {e0.elapsed_time(e1) / 3:.3f} ms per step (under the profiler)", file=sys.stderr)
             print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70), file=sys.stderr)
         if world > 1:
             dist.barrier()

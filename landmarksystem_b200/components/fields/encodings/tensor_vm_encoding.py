@@ -197,7 +197,7 @@ class TensorVMEncoding(VolumeEncoding):
         return xyzb.is_cuda and self.ndims == 1 and type(self).forward is TensorVMEncoding.forward \
             and vm_density_supported(self.plane_coef)
 
-    def density(self, xyzb: torch.Tensor, weight, inner_relu: bool, act: str, shift: float, count=None) -> torch.Tensor:
+    def density(self, xyzb: torch.Tensor, weight, inner_relu: bool, act: str, shift: float, count=None, route=None) -> torch.Tensor:
         """``sigma [N]`` straight from the lookup kernel: channel-weighted sum (``weight [1, L*C]`` or ``None``)
         and activation are applied in registers, the feature matrix is never written."""
         from ....ops.vm import vm_density
@@ -214,8 +214,8 @@ class TensorVMEncoding(VolumeEncoding):
                 self.flush_lazy()
         if self.use_shadow:
             return vm_density(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines],
-                              weight, inner_relu, act, shift, count)
-        return vm_density(coords, planes, lines, None, None, weight, inner_relu, act, shift, count)
+                              weight, inner_relu, act, shift, count, route)
+        return vm_density(coords, planes, lines, None, None, weight, inner_relu, act, shift, count, route)
 
     def forward(self, xyzb: torch.Tensor, count=None, out_dtype=torch.float32, out_width: int = 0,
                 zero_fill: bool = True) -> torch.Tensor:

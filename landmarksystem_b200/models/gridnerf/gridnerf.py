@@ -323,6 +323,9 @@ class GridNeRF(BaseNeRF):
         if disp is None or disp.cap < n_rows:
             from ...parallel.branch_dispatch import BlockDispatcher
 
+            if disp is not None:
+                disp.close()                 # every rank outgrows the capacity at the same call
+
             disp = BlockDispatcher(n_rows, max_w=6, max_v=3, group=self.config.mp_group)
             self._a2a = disp
         return disp
@@ -338,15 +341,21 @@ class GridNeRF(BaseNeRF):
             mods = [m.density_encoding, m.feature2density] if self.kind == "sigma" else [m.rgb_encoding, m.rgb_decoder]
             return [p for mod in mods for p in mod.parameters()]
 
-        def __call__(self, coords, extra, m_dev):
+        accepts_route = True       # the dispatcher may hand over the rows' return route
+
+        def __call__(self, coords, extra, m_dev, route=None):
             """``coords [M_cap, 4]`` / ``extra [M_cap, 3]`` hold ``m_dev`` (device int) received rows; the result has
-            ``M_cap`` rows of which the first ``m_dev`` are valid.  Kernel paths never learn ``m_dev`` on the host."""
+            ``M_cap`` rows of which the first ``m_dev`` are valid.  Kernel paths never learn ``m_dev`` on the host.
+            ``route``: where each row's result has to go; when the kernel path stores the results there itself,
+            ``self.combined`` is set and the dispatcher skips its own combine kernel."""
             m = self.model
+            self.combined = False
             if self.kind == "sigma":
                 m.sigma_batch = m_dev
                 enc = m.density_encoding
                 if bool(m.config.get("fused_density", True)) and enc.fused_density_ok(coords):
-                    return m._density(coords, count=m_dev)[:, None]
+                    self.combined = route is not None
+                    return m._density(coords, count=m_dev, route=route)[:, None]
                 k = int(m_dev.item())
                 return F.pad(m._density(coords[:k])[:, None], (0, 0, 0, coords.shape[0] - k))
             m.app_batch = m_dev
@@ -360,10 +369,10 @@ class GridNeRF(BaseNeRF):
             k = int(m_dev.item())
             return F.pad(m._rgb(coords[:k], extra[:k].contiguous(), None), (0, 0, 0, coords.shape[0] - k))
 
-    def _density(self, xyzb: torch.Tensor, count=None) -> torch.Tensor:
+    def _density(self, xyzb: torch.Tensor, count=None, route=None) -> torch.Tensor:
         enc, head = self.density_encoding, self.feature2density
         if bool(self.config.get("fused_density", True)) and hasattr(enc, "fused_density_ok") and enc.fused_density_ok(xyzb):
-            return enc.density(xyzb, *head.kernel_args(), count=count)
+            return enc.density(xyzb, *head.kernel_args(), count=count, route=route)
         feat = enc(xyzb, count=count) if count is not None else enc(xyzb)
         return head(feat).squeeze(-1).float()
 
@@ -501,7 +510,8 @@ class GridNeRF(BaseNeRF):
             R, S = z.shape
             if a2a:
                 disp = self._dispatcher(R * S)
-                sigma = disp.query(xyzb[:, :3], xyzb[:, 3], GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+                sigma = disp.query(xyzb, None, GridNeRF._OwnerFn(self, "sigma"), 1, channel=f"sigma{int(hull)}",
+                                   payload_width=3, owner_column=3).view(R, S)
             else:
                 self.sigma_batch = None
                 sigma = self._mp_sum(self._density(xyzb)).view(R, S)
@@ -517,7 +527,7 @@ class GridNeRF(BaseNeRF):
                 owner = torch.where(valid, block, torch.full_like(block, -1.0))
                 xyzb = torch.cat((local, owner[:, None]), dim=-1)
                 disp = self._dispatcher(R * S)
-                sigma = disp.query(local, owner, GridNeRF._OwnerFn(self, "sigma"), 1).view(R, S)
+                sigma = disp.query(local, owner, GridNeRF._OwnerFn(self, "sigma"), 1, channel=f"sigma{int(hull)}").view(R, S)
             else:
                 xyzb = self._xyzb(xyz, valid)
                 self.sigma_batch = (xyzb[:, 3] >= 0).sum()
@@ -531,7 +541,8 @@ class GridNeRF(BaseNeRF):
 
             idx, coords_c, count = compact_rows(app_mask, xyzb)          # stays on the device: no row count reaches the host
             payload, owner_c = build_payload6(coords_c, dirs, idx, count, S)
-            vals = self._dispatcher(R * S).query(payload, owner_c, GridNeRF._OwnerFn(self, "rgb"), 3, count=count)
+            vals = self._dispatcher(R * S).query(payload, owner_c, GridNeRF._OwnerFn(self, "rgb"), 3, count=count,
+                                                 channel=f"rgb{int(hull)}")
             rgb = ScatterRows3.apply(vals, idx, coords_c, count, R * S)
             rgb_map, depth_map = self.renderer(weight, rgb.view(R, S, 3), z, 0.5 if self.training else 0.0)
             return rgb_map, depth_map, weight, app_mask.view(R, S), z, dists

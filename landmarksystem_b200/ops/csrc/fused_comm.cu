@@ -16,6 +16,7 @@
 //     landmark/render/parallel_module/parallel_module.py:105-135).
 // Cross-GPU ordering around both kernels comes from the device-side barrier in symm.cu.
 #include "common.cuh"
+#include "peer_sync.cuh"
 
 namespace lmb {
 
@@ -143,16 +144,34 @@ composite_merge_p2p_kernel(PeerPtrs partials, PeerPtrs outs, int world, int rank
 // sums all staging buffers (plain peer loads, rank order fixed so every rank gets bit-identical sums).
 // Used for the gradients of replicated heads (tens of thousands of floats), where a library collective is
 // all launch latency and cannot be recorded alongside the peer barriers of the same step.
+// The hand-over is a device-side barrier folded into the summing kernel's prologue (peer_sync.cuh): its first block
+// raises this rank's epoch flag on every peer ("my staging copy is complete"), all blocks wait for every rank's flag.  Staging is double-buffered by
+// epoch parity, so no rank can overwrite a buffer that a slower peer is still summing: a rank stages epoch e+2 only after
+// it has summed epoch e+1, for which it needed every peer's flag of e+1, which a peer raises after it summed epoch e.
+// state: [0] epoch, [1] block ticket (zero-initialised local words).
 __global__ void __launch_bounds__(256)
-allreduce_small_kernel(PeerPtrs staging, int world, long long n4, float4* __restrict__ out, float scale) {
+allreduce_stage_kernel(const float4* __restrict__ in, float4* staging_local, long long n4, long long capacity4,
+                       const unsigned* __restrict__ state) {
+  const unsigned epoch = state[0] + 1u;                  // bumped by the summing kernel that follows
+  float4* dst = staging_local + (long long)(epoch & 1u) * capacity4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) dst[i] = in[i];
+}
+
+__global__ void __launch_bounds__(256)
+allreduce_small_kernel(PeerPtrs staging, PeerFlagPtrs flags, int rank, int world, long long n4, long long capacity4,
+                       unsigned* state, const unsigned* flags_local, float4* __restrict__ out, float scale, int* status) {
+  const unsigned epoch = state[0] + 1u;
+  publish_and_wait(flags, 0, flags_local, rank, world, epoch, kSyncDefaultLimit, status, 500);
+  const long long off = (long long)(epoch & 1u) * capacity4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
-      const float4 v = reinterpret_cast<const float4*>(staging.p[r])[i];
+      const float4 v = reinterpret_cast<const float4*>(staging.p[r])[off + i];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     out[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
   }
+  if (grid_last_block(state + 1) && threadIdx.x == 0) state[0] = epoch;
 }
 
 // ---- fan-out of streamed scene blocks ------------------------------------------------------------------------
@@ -237,18 +256,24 @@ LMB_API int lmb_composite_merge_p2p(const long long* partial_table, const long l
   return 0;
 }
 
-// staging_table: per-rank staging buffer addresses (n floats each, n a multiple of 4); out: local fp32 [n].
-// The caller brackets the launch with peer barriers (staging written everywhere before; nobody overwrites its
-// staging buffer until every rank has read it).
-LMB_API int lmb_allreduce_small_p2p(const long long* staging_table, int world, long long n, float* out, float scale,
-                                    cudaStream_t stream) {
+// in: local fp32 [n] (n a multiple of 4); staging_table / flags_table: per-rank addresses of the staging area (2 x capacity
+// floats) and of the flag words (one per source rank); staging_local / flags_local: this rank's; state: 2 zero-initialised
+// local words; out: local fp32 [n].  Two launches, no barrier launches around them.
+LMB_API int lmb_allreduce_small_p2p(const float* in, const long long* staging_table, const long long* flags_table,
+                                    float* staging_local, const unsigned* flags_local, unsigned* state, int rank, int world,
+                                    long long n, long long capacity, float* out, float scale, int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (n % 4 || world > kMaxPeers) return (int)cudaErrorInvalidValue;
+  if (n % 4 || capacity % 4 || n > capacity || world > kMaxPeers || world > kSyncMaxPeers) return (int)cudaErrorInvalidValue;
   PeerPtrs st;
+  PeerFlagPtrs flags;
   for (int i = 0; i < kMaxPeers; ++i) st.p[i] = i < world ? (void*)staging_table[i] : nullptr;
+  for (int i = 0; i < kSyncMaxPeers; ++i) flags.p[i] = i < world ? (unsigned*)flags_table[i] : nullptr;
   const long long n4 = n / 4;
   const int blocks = (int)((n4 + 255) / 256 < 148 * 4 ? (n4 + 255) / 256 : 148 * 4);
-  allreduce_small_kernel<<<blocks, 256, 0, stream>>>(st, world, n4, (float4*)out, scale);
+  allreduce_stage_kernel<<<blocks, 256, 0, stream>>>((const float4*)in, (float4*)staging_local, n4, capacity / 4, state);
+  LMB_LAUNCH_CHECK();
+  allreduce_small_kernel<<<blocks, 256, 0, stream>>>(st, flags, rank, world, n4, capacity / 4, state, flags_local, (float4*)out, scale,
+                                                     status);
   LMB_LAUNCH_CHECK();
   return 0;
 }

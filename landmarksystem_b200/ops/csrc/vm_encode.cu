@@ -294,6 +294,16 @@ struct DensityHead {
   float shift;
 };
 
+// Spatial-block model parallelism: the rows of an owner's batch came from other GPUs (all-to-all dispatch); row n
+// belongs to rank route_src[n], which expects its density at slot route_slot[n] of its landing buffer dest[src].
+// With a route the density kernel stores sigma there itself (a peer store over NVLink) - the "combine" half of the
+// exchange costs no kernel of its own.
+struct DensityRoute {
+  const int* src;     // nullptr: no route
+  const int* slot;
+  float* dest[8];
+};
+
 template <typename T>
 __device__ __forceinline__ void vm_features(const VMLevels& lv, int l, const float4& q, int b, int ch, F8& f, F8& pv8, F8& lv8,
                                             Corner2& cx, Corner2& cy, Corner2& cz) {
@@ -316,7 +326,7 @@ __device__ __forceinline__ void vm_features(const VMLevels& lv, int l, const flo
 template <typename T>
 __global__ void __launch_bounds__(256)
 vm_density_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n, VMLevels lv,
-                      DensityHead head, float* __restrict__ sigma, float* __restrict__ pre) {
+                      DensityHead head, float* __restrict__ sigma, float* __restrict__ pre, DensityRoute route) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
   // grid-stride with a trip count that is uniform per block (the shuffles below need whole warps)
@@ -343,8 +353,10 @@ vm_density_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__
   if (live && ch == 0) {
     const float r = head.inner_relu ? fmaxf(acc, 0.f) : acc;
     const float x = r + head.shift;
-    sigma[n] = head.act == 0 ? fmaxf(r, 0.f) : (x > 20.f ? x : log1pf(__expf(x)));
+    const float sg = head.act == 0 ? fmaxf(r, 0.f) : (x > 20.f ? x : log1pf(__expf(x)));
+    sigma[n] = sg;
     pre[n] = acc;
+    if (route.src != nullptr) route.dest[route.src[n]][route.slot[n]] = sg;
   }
   }
 }
@@ -480,16 +492,21 @@ static bool density_shape_ok(const VMLevels* lv) {
 }
 
 // sigma, pre: fp32 [max_n]; w: fp32 [L*C] or null (plain channel sum); act: 0 relu, 1 softplus(x + shift)
+// route_src / route_slot / dest_table (all null, or int [max_n] x 2 and `world` landing-buffer addresses): see DensityRoute
 LMB_API int lmb_vm_density_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
                                int param_dtype, const float* w, int inner_relu, int act, float shift, float* sigma, float* pre,
+                               const int* route_src, const int* route_slot, const long long* dest_table, int world,
                                cudaStream_t stream) {
   if (max_n <= 0) return 0;
-  if (!density_shape_ok(levels)) return (int)cudaErrorInvalidValue;
+  if (!density_shape_ok(levels) || (route_src != nullptr && (dest_table == nullptr || world > 8))) return (int)cudaErrorInvalidValue;
   const DensityHead head{w, inner_relu, act, shift};
+  DensityRoute route;
+  route.src = route_src; route.slot = route_slot;
+  for (int i = 0; i < 8; ++i) route.dest[i] = (route_src != nullptr && i < world) ? (float*)dest_table[i] : nullptr;
   const int blocks = capped_grid(max_n * (levels->C / 8), 256);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
-  if (param_dtype == 0) vm_density_fwd_kernel<float><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
-  else vm_density_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre);
+  if (param_dtype == 0) vm_density_fwd_kernel<float><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre, route);
+  else vm_density_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(c4, count_ptr, max_n, *levels, head, sigma, pre, route);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -171,7 +171,8 @@ def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torc
 
 # -- fused density head: lookup + 1-wide linear (or channel sum) + activation -> sigma [N] ---------------------
 native.register_signature("lmb_vm_density_fwd", [native.P, native.P, c_longlong, POINTER(native.VMLevels), c_int, native.P,
-                                                  c_int, c_int, c_float, native.P, native.P, native.P])
+                                                  c_int, c_int, c_float, native.P, native.P, native.P, native.P, native.P, c_int,
+                                                  native.P])
 native.register_signature("lmb_vm_density_bwd", [native.P, native.P, c_longlong, POINTER(native.VMLevels), c_int, native.P,
                                                   c_int, c_int, c_float, native.P, native.P, native.P, native.P])
 
@@ -193,7 +194,7 @@ class _VMDensity(torch.autograd.Function):
     ``_VMEncode``.  Output: sigma ``[N]`` fp32 (rows past ``count`` undefined)."""
 
     @staticmethod
-    def forward(ctx, coords, count, weight, inner_relu, act, shift, n_levels, *grids):
+    def forward(ctx, coords, count, weight, inner_relu, act, shift, n_levels, route, *grids):
         masters = grids[: 2 * n_levels]
         shadows = grids[2 * n_levels:]
         read = shadows if shadows else masters
@@ -203,9 +204,12 @@ class _VMDensity(torch.autograd.Function):
         pre = torch.empty(N, device=coords.device, dtype=torch.float32)
         w = None if weight is None else weight.detach().reshape(-1).float().contiguous()
         lv = _levels_struct(planes, lines)
+        # route = (src int32 [N], slot int32 [N], table of landing-buffer addresses, world): sigma also goes to its source rank
+        r_src, r_slot, r_table, r_world = route if route is not None else (None, None, None, 0)
         native.check(native.lib().lmb_vm_density_fwd(coords.data_ptr(), native.ptr(count), N, byref(lv),
                                                      native.DTYPE_CODE[planes[0].dtype], native.ptr(w), int(inner_relu), act,
-                                                     float(shift), sigma.data_ptr(), pre.data_ptr(), native.stream_ptr()),
+                                                     float(shift), sigma.data_ptr(), pre.data_ptr(), native.ptr(r_src),
+                                                     native.ptr(r_slot), r_table, int(r_world), native.stream_ptr()),
                      "vm_density_fwd")
         ctx.save_for_backward(coords, count, pre, w, *read)
         ctx.n_levels, ctx.masters, ctx.n_shadow = n_levels, masters, len(shadows)
@@ -232,17 +236,18 @@ class _VMDensity(torch.autograd.Function):
                      "vm_density_bwd")
         out_grads = [None if s else g for s, g in zip(sunk, grads)]
         dweight = None if dw is None else dw.view(ctx.weight_shape)
-        return (None, None, dweight, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+        return (None, None, dweight, None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
 
 
 def vm_density(coords: torch.Tensor, planes, lines, shadow_planes=None, shadow_lines=None, weight=None,
-               inner_relu: bool = False, act: str = "softplus", shift: float = 0.0, count=None) -> torch.Tensor:
+               inner_relu: bool = False, act: str = "softplus", shift: float = 0.0, count=None, route=None) -> torch.Tensor:
     """``sigma [N] = act(relu?(features @ weight))`` (``weight=None``: plain channel sum) without materialising
-    the features.  ``act``: ``"relu"`` or ``"softplus"`` (of ``x + shift``)."""
+    the features.  ``act``: ``"relu"`` or ``"softplus"`` (of ``x + shift``).  ``route`` (CUDA only): ``(src, slot, table,
+    world)`` - the kernel also stores row ``n``'s density at ``slot[n]`` of rank ``src[n]``'s landing buffer (peer store)."""
     if not coords.is_cuda:
         return vm_density_reference(coords, planes, lines, weight, inner_relu, act, shift)
     coords = coords.contiguous().float()
     grids = list(planes) + list(lines)
     if shadow_planes is not None:
         grids += list(shadow_planes) + list(shadow_lines)
-    return _VMDensity.apply(coords, count, weight, inner_relu, 0 if act == "relu" else 1, shift, len(planes), *grids)
+    return _VMDensity.apply(coords, count, weight, inner_relu, 0 if act == "relu" else 1, shift, len(planes), route, *grids)

@@ -22,38 +22,51 @@ def _grad_of(p: torch.Tensor):
 
 
 class _P2PSmallAllReduce:
-    """All-reduce of a flat fp32 vector through peer-mapped staging buffers: copy in, peer barrier, every rank
-    sums all staging buffers with plain peer loads, peer barrier.  No library collective is involved, so the
-    call is a fixed sequence of kernel launches that can be recorded in a CUDA graph."""
+    """All-reduce of a flat fp32 vector through peer-mapped staging buffers: one kernel copies the vector into this
+    rank's staging buffer and raises its flag on every peer, a second kernel waits for all flags and sums the staging
+    buffers with plain peer loads.  No library collective and no barrier launch is involved, so the call is a fixed
+    pair of kernel launches that can be recorded in a CUDA graph."""
 
     def __init__(self, capacity: int, group=None):
         from ctypes import c_float, c_int, c_longlong
 
-        from ..comm.symmetric import PeerBarrier, SymmetricBuffer
+        from ..comm.symmetric import SymmetricBuffer
         from ..ops import native
         from .zero_adam import _table
 
-        native.register_signature("lmb_allreduce_small_p2p", [native.P, c_int, c_longlong, native.P, c_float, native.P])
+        P = native.P
+        native.register_signature("lmb_allreduce_small_p2p", [P, P, P, P, P, P, c_int, c_int, c_longlong, c_longlong, P,
+                                                               c_float, P, P])
         self.capacity = (capacity + 3) // 4 * 4
-        self.buf = SymmetricBuffer(self.capacity * 4, group)
+        self.off_flags = self.capacity * 4 * 2                    # two staging buffers (epoch parity), then the flag words
+        self.buf = SymmetricBuffer(self.off_flags + 256, group)
         self.table = _table(self.buf.peer_table(0))
-        self.staging = self.buf.view(0, (self.capacity,), torch.float32)
-        self.barrier = PeerBarrier(group)
+        self.flags_table = _table(self.buf.peer_table(self.off_flags))
+        self.state = torch.zeros(4, dtype=torch.int32, device=self.buf.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.buf.device)
         self.native = native
+        if self.buf.world > 1:
+            dist.barrier(group)              # every rank has mapped the staging buffers before the first flag is raised
 
     def __call__(self, flat: torch.Tensor, scale: float) -> torch.Tensor:
         n = flat.numel()
         n4 = (n + 3) // 4 * 4
         assert n4 <= self.capacity
-        self.barrier()                       # peers have finished reading the previous contents
-        self.staging[:n].copy_(flat)
+        src = flat.contiguous().float()
         if n4 > n:
-            self.staging[n:n4].zero_()
-        self.barrier()                       # every rank's staging buffer is complete
+            src = torch.nn.functional.pad(src, (0, n4 - n))
         out = torch.empty(n4, device=flat.device, dtype=torch.float32)
-        self.native.check(self.native.lib().lmb_allreduce_small_p2p(self.table, self.buf.world, n4, out.data_ptr(), float(scale),
-                                                                  self.native.stream_ptr()), "allreduce_small_p2p")
+        nat = self.native
+        nat.check(nat.lib().lmb_allreduce_small_p2p(src.data_ptr(), self.table, self.flags_table, self.buf.local_ptr,
+                                                    self.buf.local_ptr + self.off_flags, self.state.data_ptr(), self.buf.rank,
+                                                    self.buf.world, n4, self.capacity, out.data_ptr(), float(scale),
+                                                    self.status.data_ptr(), nat.stream_ptr()), "allreduce_small_p2p")
         return out[:n]
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"small all-reduce: the wait for rank {code - 500} ran out")
 
     def close(self) -> None:
         """Collective teardown (every rank of the group calls it at the same point): no peer may still address the
@@ -65,9 +78,7 @@ class _P2PSmallAllReduce:
         torch.cuda.synchronize()
         if dist.is_initialized() and self.buf.world > 1:
             dist.barrier(self.buf.group)
-        self.staging = None
         self.buf.close()
-        self.barrier.close()
         self.buf = None
 
 

@@ -80,7 +80,7 @@ def main():
         scale = g2.abs().max().item() + 1e-12
         gerr = max(gerr, (g1 - g2).abs().max().item() / scale)
     assert gerr < 1e-3, gerr
-    a2a_model._a2a.barrier.check()
+    a2a_model._a2a.check()
 
     # the same exchange with the kernel path on the owner (tcgen05 colour head forward + backward, device-side
     # row counts end to end: no host synchronisation inside the step), against the replicated PyTorch heads
@@ -104,7 +104,7 @@ def main():
         fgerr = max(fgerr, float((p1.grad - p2.grad).norm() / (p2.grad.norm() + 1e-12)))
     assert fgerr < 0.15, fgerr
     fused_model.rgb_decoder._lmb_packed.check_status()
-    fused_model._a2a.barrier.check()
+    fused_model._a2a.check()
     assert int(fused_model._a2a.overflow.item()) == 0
 
     # timing of a training-shaped forward+backward with 8192 rays x 128 samples per rank

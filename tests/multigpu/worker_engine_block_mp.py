@@ -1,5 +1,5 @@
-"""Worker (2 GPUs): ``init_inference`` with ``parallel_config = {"tp_size": 2, "mode": "block"}``.  Each rank keeps one
-band of the scene's blocks; the engine broadcasts the pose, both ranks render their ray segments and the cross-GPU
+"""Worker (2, 4 or 8 GPUs): ``init_inference`` with ``parallel_config = {"tp_size": world, "mode": "block"}``.  Each rank keeps one
+rectangle of the scene's blocks; the engine broadcasts the pose, both ranks render their ray segments and the cross-GPU
 composite merges them.  The image is compared with a single-process render of the same checkpoint."""
 import json
 import os
@@ -32,8 +32,9 @@ def main():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     rank = int(os.environ["RANK"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
-    root = os.path.join(tempfile.gettempdir(), "lmb_engine_block_mp")
-    division = [2, 2]
+    world = int(os.environ["WORLD_SIZE"])
+    root = os.path.join(tempfile.gettempdir(), f"lmb_engine_block_mp_{world}")
+    division = {2: [2, 2], 4: [2, 2], 8: [2, 4]}[world]      # 2 ranks: a band of two blocks each; 4 and 8: one block each
     if rank == 0:
         os.makedirs(root, exist_ok=True)
         torch.manual_seed(0)
@@ -52,7 +53,7 @@ def main():
     time.sleep(0.5)
     dev = f"cuda:{int(os.environ['LOCAL_RANK'])}"
     engine = lm.init_inference(GridNeRF, make_adapter(GridNeRF), model_config(root, division, dev),
-                               Config(runtime="Torch", kernel_fusion=False, parallel_config={"tp_size": 2, "mode": "block"}))
+                               Config(runtime="Torch", kernel_fusion=False, parallel_config={"tp_size": world, "mode": "block"}))
     pose = look_at(torch.tensor([0.2, -0.1, 3.0]), torch.tensor([0.25, -0.1, 0.0]), up=(0.0, 1.0, 0.0))
     H, W = 48, 64
     out = engine(pose, 2048, H, W, 60.0) if rank == 0 else engine()

@@ -22,49 +22,44 @@ def _gpus() -> int:
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-def test_fused_comm_kernels():
-    res = _launch("worker_fused_comm.py", min(_gpus(), 8))
-    sys.stdout.write(res.stdout[-3000:])
+def _worlds():
+    """Rank counts to exercise: 2, 4 and 8, as far as the box has GPUs (one entry that skips on a single-GPU box)."""
+    have = [w for w in (2, 4, 8) if w <= _gpus()]
+    return have or [pytest.param(2, marks=pytest.mark.skip(reason="needs at least 2 GPUs"))]
+
+
+def _run_worker(script: str, world: int, marker: str, tail: int = 3000):
+    res = _launch(script, world)
+    sys.stdout.write(res.stdout[-tail:])
     assert res.returncode == 0, res.stderr[-3000:]
-    assert "FUSED_COMM_RESULTS" in res.stdout
+    assert marker in res.stdout
+
+
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_comm_kernels(world):
+    _run_worker("worker_fused_comm.py", world, "FUSED_COMM_RESULTS")
 
 
 @pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
 def test_channel_gather_fused_into_mlp():
-    res = _launch("worker_channel_gather.py", 2)
-    sys.stdout.write(res.stdout[-2000:])
-    assert res.returncode == 0, res.stderr[-3000:]
-    assert "CHANNEL_GATHER_RESULTS" in res.stdout
+    _run_worker("worker_channel_gather.py", 2, "CHANNEL_GATHER_RESULTS", 2000)
 
 
-@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-def test_branch_parallel_all_to_all():
-    res = _launch("worker_branch_a2a.py", 2)
-    sys.stdout.write(res.stdout[-2000:])
-    assert res.returncode == 0, res.stderr[-3000:]
-    assert "BRANCH_A2A_RESULTS" in res.stdout
+@pytest.mark.parametrize("world", _worlds())
+def test_branch_parallel_all_to_all(world):
+    _run_worker("worker_branch_a2a.py", world, "BRANCH_A2A_RESULTS", 2000)
 
 
-@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-def test_model_parallel_render_merge():
-    res = _launch("worker_mp_render.py", 2)
-    sys.stdout.write(res.stdout[-2000:])
-    assert res.returncode == 0, res.stderr[-3000:]
-    assert "MP_RENDER_RESULTS" in res.stdout
+@pytest.mark.parametrize("world", _worlds())
+def test_model_parallel_render_merge(world):
+    _run_worker("worker_mp_render.py", world, "MP_RENDER_RESULTS", 2000)
 
 
-@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-def test_engine_block_model_parallel_render():
-    res = _launch("worker_engine_block_mp.py", 2)
-    sys.stdout.write(res.stdout[-2000:])
-    assert res.returncode == 0, res.stderr[-3000:]
-    assert "ENGINE_BLOCK_MP_RESULTS" in res.stdout
+@pytest.mark.parametrize("world", _worlds())
+def test_engine_block_model_parallel_render(world):
+    _run_worker("worker_engine_block_mp.py", world, "ENGINE_BLOCK_MP_RESULTS", 2000)
 
 
-@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
-def test_dynamic_loading_nvlink_fanout():
-    res = _launch("worker_offload_fanout.py", 2)
-    sys.stdout.write(res.stdout[-2000:])
-    assert res.returncode == 0, res.stderr[-3000:]
-    assert "OFFLOAD_FANOUT_RESULTS" in res.stdout
+@pytest.mark.parametrize("world", _worlds())
+def test_dynamic_loading_nvlink_fanout(world):
+    _run_worker("worker_offload_fanout.py", world, "OFFLOAD_FANOUT_RESULTS", 2000)
