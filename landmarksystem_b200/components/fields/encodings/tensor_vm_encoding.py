@@ -249,6 +249,26 @@ class TensorVMEncoding(VolumeEncoding):
             self.enable_shadow(lazy=getattr(self, "lazy", False))
 
     # -- regularisers ---------------------------------------------------------------------
+    def fused_regulariser_ok(self) -> bool:
+        """The planes' TV / L1 terms can be folded into the optimiser's sweep: CUDA, bf16 shadows, fused dense Adam
+        (gradient sinks, no deferred update), the unpartitioned encoding."""
+        return (self.use_shadow and not getattr(self, "lazy", False) and type(self).L1_loss is TensorVMEncoding.L1_loss
+                and all(p.is_cuda and getattr(p, "_lmb_grad_sink", None) is not None and p.shape[-1] % 4 == 0
+                        for p in self.plane_coef))
+
+    def set_plane_regulariser(self, tv_weight=None, tv_index: int = 0, l1_weight: float = 0.0, loss_scale: float = 1.0,
+                              loss_out=None) -> None:
+        """Ask the fused optimiser to apply ``tv_weight * TV_loss() + l1_weight * (plane part of L1_loss())`` inside its
+        next steps (see ``FusedAdam.attach_plane_regulariser``)."""
+        from ....ops import FusedAdam
+
+        for p in self.plane_coef:
+            FusedAdam.attach_plane_regulariser(p, tv_weight, tv_index, l1_weight, loss_scale, loss_out)
+
+    def L1_loss_lines(self) -> torch.Tensor:
+        """The line part of :meth:`L1_loss` (lines are a few KB: plain PyTorch ops)."""
+        return sum(l.abs().mean() for l in self.line_coef)
+
     def L1_loss(self) -> torch.Tensor:
         return sum(p.abs().mean() + l.abs().mean() for p, l in zip(self.plane_coef, self.line_coef))
 

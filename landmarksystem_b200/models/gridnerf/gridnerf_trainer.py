@@ -199,19 +199,35 @@ class GridNeRFTrainer(NeRFTrainer):
             total = total + torch.mean((all_ret["rgb_map_nerf"] - rgb_train) ** 2)
         if cfg.Ortho_weight > 0:
             total = total + cfg.Ortho_weight * m.density_encoding.vector_diffs() + m.rgb_encoding.vector_diffs()
-        if self.l1_weight > 0:
-            total = total + self.l1_weight * m.density_encoding.L1_loss()
-        if self.tv_weight_density > 0 or self.tv_weight_app > 0:
+        tv_on = self.tv_weight_density > 0 or self.tv_weight_app > 0
+        w = None
+        if tv_on:
             # the two weights decay with the learning rate; they live in a device tensor that is scaled in place, so a
             # step replayed from a CUDA graph keeps decaying them (a host float would be frozen at its recorded value)
             w = getattr(self, "_tv_weights", None)
             if w is None or w.device != loss.device:
                 w = self._tv_weights = torch.tensor([self.tv_weight_density, self.tv_weight_app], device=loss.device)
             w.mul_(self.lr_factor)
+        den, app = m.density_encoding, m.rgb_encoding
+        if (self.l1_weight > 0 or tv_on) and den.fused_regulariser_ok() and app.fused_regulariser_ok() \
+                and isinstance(self.optimizer, FusedAdam):
+            # plane terms are evaluated inside the optimiser's sweep over the planes (one pass over parameters and
+            # moments per step, no regulariser gradient tensor); only the few-KB lines go through autograd
+            # spatial-block model parallelism: the term is the mean over the ranks' blocks (the reference gathers the
+            # per-rank values and averages them, tensor_vm_encoding.py:620-636), so every rank's own planes see 1 / P
+            a2a = bool(cfg.branch_parallel and cfg.get("branch_dispatch") == "a2a")
+            scale = 1.0 / cfg.model_parallel_degree if cfg.branch_parallel else 1.0
+            den.set_plane_regulariser(w if self.tv_weight_density > 0 else None, 0, self.l1_weight, scale)
+            app.set_plane_regulariser(w if self.tv_weight_app > 0 else None, 1, 0.0, scale)
+            if self.l1_weight > 0:      # in all-to-all mode the caller divides the whole objective by P afterwards
+                total = total + self.l1_weight * (1.0 if a2a else scale) * den.L1_loss_lines()
+        else:
+            if self.l1_weight > 0:
+                total = total + self.l1_weight * den.L1_loss()
             if self.tv_weight_density > 0:
-                total = total + w[0] * m.density_encoding.TV_loss()
+                total = total + w[0] * den.TV_loss()
             if self.tv_weight_app > 0:
-                total = total + w[1] * m.rgb_encoding.TV_loss()
+                total = total + w[1] * app.TV_loss()
         if self.enable_distort:
             for key in ("distort_loss", "distort_loss1", "distort_loss_nerf"):
                 if key in all_ret:

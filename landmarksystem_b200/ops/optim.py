@@ -10,7 +10,13 @@ from typing import Dict, Iterable, List, Optional
 
 import torch
 
+from ctypes import c_float, c_int
+
 from . import native
+
+native.register_signature("lmb_adam_plane_reg", [native.P, native.P, native.P, native.P, native.P, native.P, c_int, c_int, c_int,
+                                                  c_int, native.P, c_float, c_int, c_float, c_float, c_float, c_float, native.P,
+                                                  c_float, c_float, c_float, native.P, native.P])
 
 
 # Bumped by every fused step: the kernel updates parameters through raw pointers, which autograd's
@@ -129,6 +135,8 @@ class FusedAdam(torch.optim.Optimizer):
                     lazy.dirty = True
                 elif p in self.state and self.state[p]:
                     self.state[p]["step"] += 1
+                    if self._plane_reg_active(p):
+                        p.data, p._lmb_pong = p._lmb_pong, p.data      # the replayed step wrote the other buffer
 
     @staticmethod
     def attach_sink(param: torch.Tensor, shadow: bool = False, lazy: bool = False) -> None:
@@ -142,6 +150,28 @@ class FusedAdam(torch.optim.Optimizer):
 
             param._lmb_lazy = LazyPlaneState(param)
 
+    @staticmethod
+    def attach_plane_regulariser(param: torch.Tensor, tv_weight=None, tv_index: int = 0, l1_weight: float = 0.0,
+                                 loss_scale: float = 1.0, loss_out: Optional[torch.Tensor] = None) -> None:
+        """Fold the total-variation / L1 regularisers of a channels-last plane ``[B, H, W, C]`` into its Adam step
+        (``csrc/adam.cu: adam_plane_reg_kernel``).  ``tv_weight``: a device tensor whose element ``tv_index`` is the
+        (decaying) weight, a float, or ``None``; ``loss_scale``: the factor the caller applies to its total loss;
+        ``loss_out``: optional device ``float[2]`` that accumulates the TV and L1 loss values.  Needs the gradient sink
+        and the bf16 shadow (``attach_sink(param, shadow=True)``); a second parameter buffer is allocated (the step
+        ping-pongs between the two so that neighbours are read at their old values)."""
+        tv_dev = tv_weight[tv_index:tv_index + 1] if torch.is_tensor(tv_weight) else None
+        tv_host = 0.0 if (tv_weight is None or torch.is_tensor(tv_weight)) else float(tv_weight)
+        param._lmb_reg = {"tv_dev": tv_dev, "tv": tv_host, "l1": float(l1_weight), "scale": float(loss_scale), "loss": loss_out}
+        if getattr(param, "_lmb_pong", None) is None or param._lmb_pong.shape != param.shape:
+            param._lmb_pong = torch.empty_like(param.data)
+
+    @staticmethod
+    def _plane_reg_active(p) -> bool:
+        reg = getattr(p, "_lmb_reg", None)
+        return (reg is not None and (reg["tv_dev"] is not None or reg["tv"] > 0 or reg["l1"] > 0) and p.is_cuda and p.dim() == 4
+                and p.shape[-1] % 4 == 0 and getattr(p, "_lmb_grad_sink", None) is not None
+                and getattr(p, "_lmb_shadow", None) is not None and getattr(p, "_lmb_lazy", None) is None)
+
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
         global GENERATION
@@ -153,6 +183,11 @@ class FusedAdam(torch.optim.Optimizer):
             stepped = False
             for p in group["params"]:
                 sink = getattr(p, "_lmb_grad_sink", None)
+                if sink is not None and p.grad is not None:
+                    # a loss term evaluated with PyTorch ops (a regulariser, say) left an ordinary gradient next to the
+                    # kernels' accumulator: fold it in, or it would be ignored and pile up
+                    sink.add_(p.grad)
+                    p.grad = None
                 grad = sink if sink is not None else p.grad
                 if grad is None:
                     continue
@@ -179,6 +214,18 @@ class FusedAdam(torch.optim.Optimizer):
                     raise RuntimeError("capturable FusedAdam needs contiguous fp32 CUDA parameters and gradients: the PyTorch "
                                        "fallback would bake the host-side learning rate and step count into a recorded graph")
                 stepped = True
+                if self._plane_reg_active(p) and not self.rectified and p.dtype == torch.float32 and p.is_contiguous():
+                    reg = p._lmb_reg
+                    B, H, W, C = p.shape
+                    cur, other = p.data, p._lmb_pong
+                    odd, even = (cur, other) if state["step"] % 2 == 1 else (other, cur)     # `cur` is read at this step number
+                    native.check(native.lib().lmb_adam_plane_reg(
+                        odd.data_ptr(), even.data_ptr(), grad.data_ptr(), state["exp_avg"].data_ptr(),
+                        state["exp_avg_sq"].data_ptr(), shadow.data_ptr(), B, H, W, C, native.ptr(dyn), group["lr"], state["step"],
+                        beta1, beta2, group["eps"], grad_scale, native.ptr(reg["tv_dev"]), reg["tv"], reg["l1"], reg["scale"],
+                        native.ptr(reg["loss"]), native.stream_ptr()), "adam_plane_reg")
+                    p.data, p._lmb_pong = other, cur             # the updated values are in the other buffer now
+                    continue
                 if p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous() \
                         and grad.dtype == torch.float32 and dyn is not None:
                     native.check(native.lib().lmb_adam_step_dyn(

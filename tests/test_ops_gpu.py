@@ -541,3 +541,49 @@ def test_fused_sampler_matches_the_unfused_front_end(hull):
     assert same.float().mean() > 0.999
     torch.testing.assert_close(xyzb[same][:, :3], local[same], rtol=1e-4, atol=1e-4)
     assert (valid == inside).float().mean() > 0.999
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C,tv_dev", [(16, True), (48, False)])
+def test_adam_fused_with_plane_regularisers_matches_autograd_plus_adam(C, tv_dev):
+    """Three optimiser steps on a channels-last plane whose TV and L1 terms are evaluated inside the Adam sweep (ping-pong
+    parameter buffers) against the PyTorch statements of the two terms differentiated by autograd and ``torch.optim.Adam``;
+    also the accumulated loss values, the bf16 shadow and that an ordinary ``.grad`` next to a sink is not dropped."""
+    from landmarksystem_b200.components.fields.encodings.tensor_vm_encoding import tv_term
+
+    g = torch.Generator(device=DEV).manual_seed(C)
+    B, H, W = 2, 37, 53
+    p0 = torch.randn(B, H, W, C, device=DEV, generator=g) * 0.1
+    p0[0, 3, 4, :4] = 0.0                                          # sign(0) = 0 in the L1 gradient
+    l1_w, tv_w0, decay, scale = 8e-5, 0.1, 0.9, 0.5
+    data_grads = [torch.randn(B, H, W, C, device=DEV, generator=g) * 1e-3 for _ in range(3)]
+    # reference: autograd of the statements + torch Adam
+    ref = torch.nn.Parameter(p0.clone())
+    ref_opt = torch.optim.Adam([ref], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    tv_w, want_vals = tv_w0, []
+    for k in range(3):
+        tv_w *= decay
+        tv_val, l1_val = tv_w * tv_term(ref) * 1e-2, l1_w * ref.abs().mean()
+        ((tv_val + l1_val) * scale).backward()
+        ref.grad.add_(data_grads[k])
+        ref_opt.step(); ref_opt.zero_grad()
+        want_vals.append((float(tv_val), float(l1_val)))
+    # fused path
+    p = torch.nn.Parameter(p0.clone())
+    FusedAdam.attach_sink(p, shadow=True)
+    opt = FusedAdam([p], lr=0.02, betas=(0.9, 0.99), eps=1e-8)
+    w_dev = torch.tensor([0.0, tv_w0], device=DEV)
+    loss_out = torch.zeros(2, device=DEV)
+    tv_host = tv_w0
+    for k in range(3):
+        w_dev.mul_(decay); tv_host *= decay
+        FusedAdam.attach_plane_regulariser(p, w_dev if tv_dev else tv_host, 1, l1_w, scale, loss_out)
+        loss_out.zero_()
+        p._lmb_grad_sink.add_(data_grads[k] * 0.25)               # kernels' accumulator ...
+        p.grad = data_grads[k] * 0.75                              # ... and an autograd gradient next to it
+        opt.step()
+        assert p.grad is None and float(p._lmb_grad_sink.abs().max()) == 0.0
+        torch.testing.assert_close(loss_out.tolist(), list(want_vals[k]), rtol=2e-4, atol=1e-9)
+    torch.testing.assert_close(p.data, ref.data, rtol=1e-4, atol=2e-6)
+    torch.testing.assert_close(p._lmb_shadow.float(), p.data, rtol=1e-2, atol=1e-3)
+    assert p._lmb_pong.data_ptr() != p.data.data_ptr()
