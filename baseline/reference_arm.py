@@ -413,6 +413,19 @@ def _run(args, ref_root, bench):
         except Exception as exc:  # the training figure must not depend on the render figure
             also.append({"metric": "GridNeRF 1080p render FPS through init_inference",
                          "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]})
+        if n == 1:
+            # 3DGS figures of the baseline side: the reference's rasteriser extension is an empty submodule, so the arm
+            # times the PyTorch restatement of the same algorithm (no kernel of the framework under test is involved)
+            try:
+                trainer = None
+                import gc
+
+                gc.collect()
+                torch.cuda.empty_cache()
+                also.append(bench.render_fps_3dgs_restatement())
+            except Exception as exc:
+                also.append({"metric": "3DGS 1080p render FPS", "impl": "restatement",
+                             "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]})
         watchdog.cancel()
     emit()
     if dist.is_initialized():

@@ -154,83 +154,167 @@ class ClockSampler:
                 "window": "timed region" if inside else "whole run (timed region shorter than a sample period)"}
 
 
-def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = 20):
-    """Secondary figure: 1080p render rate of the CUDA rasteriser on 6 M random
-    Gaussians spread over a 400 m x 400 m x 50 m box, SH degree 3, 16x16 tiles, camera on an orbit.  Device time
-    per frame by CUDA events after 3 warm-up frames; every frame has a different pose."""
+GS_BOX = (400.0, 400.0, 50.0)
+
+
+def gs_parameters(n_gauss: int, dev, seed: int = 0):
+    """Random Gaussians of the third benchmark shape: means uniform over a 400 m x 400 m x 50 m box, log-scales
+    N(-3, 0.5), random unit quaternions, opacity logits N(0, 1), SH degree 3 with DC in [0, 1] and small higher bands."""
+    import torch
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    means = (torch.rand(n_gauss, 3, device=dev, generator=g) - 0.5) * torch.tensor(GS_BOX, device=dev)
+    log_scales = torch.randn(n_gauss, 3, device=dev, generator=g) * 0.5 - 3.0
+    quats = torch.nn.functional.normalize(torch.randn(n_gauss, 4, device=dev, generator=g), dim=-1)
+    opacity_logits = torch.randn(n_gauss, 1, device=dev, generator=g)
+    shs = torch.randn(n_gauss, 16, 3, device=dev, generator=g) * 0.01
+    shs[:, 0] = torch.rand(n_gauss, 3, device=dev, generator=g)
+    return means, log_scales, quats, opacity_logits, shs
+
+
+def gs_orbit_camera(k: int, dev):
     import torch
 
     from landmarksystem_b200.components.data.cameras import Camera
-    from landmarksystem_b200.ops.gaussian_raster import GaussianRasterizationSettings, GaussianRasterizer
     from landmarksystem_b200.synthetic.scene import look_at
 
+    ang = 2 * math.pi * (k % 300) / 300.0
+    eye = torch.tensor([260.0 * math.cos(ang), 260.0 * math.sin(ang), 120.0])
+    return Camera.from_c2w(look_at(eye, torch.zeros(3), up=(0.0, 0.0, 1.0)).numpy(), 1920, 1080, focal_x=1400.0, zfar=2000.0).to(dev)
+
+
+def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = 20):
+    """Secondary figures on 6 M random Gaussians through the public classes: ``Gaussian3DTrainer`` (its model, its fused
+    optimiser, its ``train_step``: render, L1 + SSIM, rasteriser backward, densification statistics, Adam) and the model's
+    evaluation-mode render call that the evaluator loops over (visibility prefilter, visible subset, rasteriser).
+    1920x1080, 16x16 tiles, camera on an orbit, a different pose every frame; device time per frame / iteration by CUDA
+    events after warm-up."""
+    import tempfile
+
+    import torch
+
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.origin_gs.gs_trainer import Gaussian3DTrainer
+
     dev = torch.device("cuda", torch.cuda.current_device())
-    g = torch.Generator(device=dev).manual_seed(0)
-    means = (torch.rand(n_gauss, 3, device=dev, generator=g) - 0.5) * torch.tensor([400.0, 400.0, 50.0], device=dev)
-    scales = torch.exp(torch.randn(n_gauss, 3, device=dev, generator=g) * 0.5 - 3.0)
-    rots = torch.nn.functional.normalize(torch.randn(n_gauss, 4, device=dev, generator=g), dim=-1)
-    opac = torch.sigmoid(torch.randn(n_gauss, 1, device=dev, generator=g))
-    shs = torch.randn(n_gauss, 16, 3, device=dev, generator=g) * 0.01
-    shs[:, 0] = torch.rand(n_gauss, 3, device=dev, generator=g)
-    W, H, focal = 1920, 1080, 1400.0
-    bg = torch.zeros(3, device=dev)
+    conf = os.path.join(ROOT, "landmarksystem_b200", "models", "origin_gs", "confs", "synthetic_train.py")
+    half = [0.5 * v for v in GS_BOX]
+    cfg = BaseConfig.from_file(conf, {"basedir": tempfile.mkdtemp(prefix="lmb_gs_bench_"), "device": "cuda", "n_iters": "1000",
+                                      "datadir": "ring:3:16x16:18:3", "init_points_num": str(n_gauss),
+                                      "densify_from_iter": "100000", "opacity_reset_interval": "100000",
+                                      "progress_refresh_rate": "1000000"})
+    cfg.lb, cfg.ub = [-h for h in half], half
+    trainer = Gaussian3DTrainer(cfg)
+    model, enc = trainer.model, trainer.model.gaussian_encoding
+    means, log_scales, quats, opacity_logits, shs = gs_parameters(n_gauss, dev)
+    with torch.no_grad():                       # same shapes as the trainer's own initial cloud: optimiser state stays valid
+        enc._xyz.copy_(means); enc._scaling.copy_(log_scales); enc._rotation.copy_(quats); enc._opacity.copy_(opacity_logits)
+        enc._features_dc.copy_(shs[:, :1]); enc._features_rest.copy_(shs[:, 1:])
+    enc.active_sh_degree = enc.max_sh_degree
     times = []
+    model.eval()
     with torch.no_grad():
         for k in range(frames + 3):
-            ang = 2 * math.pi * k / 300.0
-            eye = torch.tensor([260.0 * math.cos(ang), 260.0 * math.sin(ang), 120.0])
-            cam = Camera.from_c2w(look_at(eye, torch.zeros(3), up=(0.0, 0.0, 1.0)).numpy(), W, H, focal_x=focal, zfar=2000.0).to(dev)
-            st = GaussianRasterizationSettings(H, W, cam.tanfovx, cam.tanfovy, bg, 1.0, cam.world_view_transform,
-                                               cam.full_proj_transform, 3, cam.camera_center)
+            cam = gs_orbit_camera(k, dev)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
-            img, radii, _ = GaussianRasterizer(st)(means, None, opac, shs=shs, scales=scales, rotations=rots)
+            img = model(cam)
             end.record()
             torch.cuda.synchronize()
             if k >= 3:
                 times.append(start.elapsed_time(end))
-    ms = statistics.median(times)
-    visible = int((radii > 0).sum())
-    # Training step on the same 6 M Gaussians: render one 1080p view from raw parameters (log-scales, unnormalised
-    # quaternions, opacity logits), L1 + SSIM loss (fused kernel) against an image rendered from perturbed colours,
-    # backward through the rasteriser, fused Adam over all 59 parameters per Gaussian.
-    from landmarksystem_b200.ops import FusedAdam
-    from landmarksystem_b200.ops.ssim import fused_l1_ssim
-
-    raw = [torch.nn.Parameter(t) for t in (means, scales.log(), rots.clone(), torch.logit(opac.clamp(1e-4, 1 - 1e-4)), shs)]
-    opt = FusedAdam([{"params": [raw[0]], "lr": 1.6e-4}, {"params": [raw[1]], "lr": 5e-3}, {"params": [raw[2]], "lr": 1e-3},
-                     {"params": [raw[3]], "lr": 5e-2}, {"params": [raw[4]], "lr": 2.5e-3}], eps=1e-15)
+        visible = int(model.visibility_filter.sum())
+        ms = statistics.median(times)
+        # targets of the training iterations: the same scene rendered with brighter colours
+        targets = []
+        enc._features_dc.add_(0.05)
+        for k in range(3 + 10):
+            targets.append(model(gs_orbit_camera(k * 23, dev)).clone())
+        enc._features_dc.sub_(0.05)
+    model.train()
     train_times = []
     for k in range(3 + 10):
-        ang = 2 * math.pi * (k * 23 % 300) / 300.0
-        eye = torch.tensor([260.0 * math.cos(ang), 260.0 * math.sin(ang), 120.0])
-        cam = Camera.from_c2w(look_at(eye, torch.zeros(3), up=(0.0, 0.0, 1.0)).numpy(), W, H, focal_x=focal, zfar=2000.0).to(dev)
-        st = GaussianRasterizationSettings(H, W, cam.tanfovx, cam.tanfovy, bg, 1.0, cam.world_view_transform,
-                                           cam.full_proj_transform, 3, cam.camera_center)
-        with torch.no_grad():
-            target, _, _ = GaussianRasterizer(st)(raw[0], None, torch.sigmoid(raw[3]), shs=raw[4] + 0.05, scales=raw[1].exp(),
-                                                  rotations=torch.nn.functional.normalize(raw[2], dim=-1))
+        cam = gs_orbit_camera(k * 23, dev)
+        trainer.iteration = k + 1
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        img, _, _ = GaussianRasterizer(st)(raw[0], None, torch.sigmoid(raw[3]), shs=raw[4], scales=raw[1].exp(),
-                                           rotations=torch.nn.functional.normalize(raw[2], dim=-1))
-        l1, ssim_val = fused_l1_ssim(img, target)
-        loss = 0.8 * l1 + 0.2 * (1.0 - ssim_val)
-        loss.backward()
-        opt.step()
-        opt.zero_grad(set_to_none=True)
+        loss, _, _ = trainer.train_step(cam, targets[k])
         end.record()
         torch.cuda.synchronize()
         if k >= 3:
             train_times.append(start.elapsed_time(end))
     train_ms = statistics.median(train_times)
     return {"metric": "3DGS 1080p render FPS", "value": 1000.0 / ms, "ms_per_frame": ms, "gaussians": n_gauss,
-            "visible": visible, "frames": frames,
+            "visible": visible, "frames": frames, "through": "GaussianModel.forward (evaluation mode)",
             "train": {"metric": "3DGS training iterations/s (1080p view, 6 M Gaussians, L1 + SSIM, fused Adam)",
                       "value": 1000.0 / train_ms, "ms_per_iter": train_ms, "iters": len(train_times),
-                      "loss_finite": bool(torch.isfinite(loss))}}
+                      "through": "Gaussian3DTrainer.train_step", "loss_finite": bool(torch.isfinite(loss))}}
+
+
+def render_fps_3dgs_restatement(n_gauss: int = 6_000_000, frames: int = 2):
+    """The same two figures for the PyTorch restatement of the rasteriser (``baseline/gs_restatement.py``; the
+    reference's own rasteriser extension is an empty submodule).  When the autograd graph of a training iteration does
+    not fit, the Gaussian count is halved until it does; the count used is reported."""
+    import torch
+
+    from baseline.gs_restatement import l1_ssim_loss, orbit_camera, render
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    bg = torch.zeros(3, device=dev)
+
+    def frame(params, k):
+        view, proj, campos, tanx, tany = orbit_camera(k, dev)       # same orbit as `gs_orbit_camera`, built without the framework
+        return render(*params, view, proj, campos, 1920, 1080, tanx, tany, bg)
+
+    params = gs_parameters(n_gauss, dev)
+    times = []
+    with torch.no_grad():
+        for k in range(frames + 1):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            frame(params, k)
+            end.record()
+            torch.cuda.synchronize()
+            if k >= 1:
+                times.append(start.elapsed_time(end))
+    ms = statistics.median(times)
+    out = {"metric": "3DGS 1080p render FPS", "impl": "restatement (PyTorch operators; the reference's rasteriser submodule is empty)",
+           "value": 1000.0 / ms, "ms_per_frame": ms, "gaussians": n_gauss, "frames": frames}
+    n_train = n_gauss
+    while n_train >= 100_000:
+        try:
+            leaves = [torch.nn.Parameter(t.clone()) for t in gs_parameters(n_train, dev)]
+            opt = torch.optim.Adam([{"params": [leaves[0]], "lr": 1.6e-4}, {"params": [leaves[1]], "lr": 5e-3},
+                                    {"params": [leaves[2]], "lr": 1e-3}, {"params": [leaves[3]], "lr": 5e-2},
+                                    {"params": [leaves[4]], "lr": 2.5e-3}], eps=1e-15)
+            train_times = []
+            for k in range(1 + 2):
+                with torch.no_grad():
+                    target = frame([leaves[0], leaves[1], leaves[2], leaves[3], leaves[4] + 0.05], k * 23)
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                loss = l1_ssim_loss(frame(leaves, k * 23), target)
+                loss.backward()
+                opt.step()
+                opt.zero_grad(set_to_none=True)
+                end.record()
+                torch.cuda.synchronize()
+                if k >= 1:
+                    train_times.append(start.elapsed_time(end))
+            train_ms = statistics.median(train_times)
+            out["train"] = {"metric": "3DGS training iterations/s (1080p view, L1 + SSIM, torch Adam)", "value": 1000.0 / train_ms,
+                            "ms_per_iter": train_ms, "iters": len(train_times), "gaussians": n_train,
+                            "loss_finite": bool(torch.isfinite(loss))}
+            break
+        except torch.cuda.OutOfMemoryError:
+            del leaves
+            torch.cuda.empty_cache()
+            n_train //= 2
+    return out
 
 
 def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4, profile: bool = False):
@@ -603,7 +687,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp"],
+    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp", "3dgs-restatement"],
                     help="run one secondary single-GPU benchmark alone and print its JSON (--profile adds the PyTorch "
                          "profiler's kernel table of two more steps on stderr)")
     ap.add_argument("--profile", action="store_true")
@@ -615,7 +699,7 @@ def main():
         import torch
 
         torch.cuda.set_device(0)
-        fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp}[args.only]
+        fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp, "3dgs-restatement": render_fps_3dgs_restatement}[args.only]
         if args.profile and args.only == "ngp":
             print(json.dumps(train_rate_ngp(profile=True)))
         else:

@@ -204,12 +204,16 @@ class GroupedP2PZeroAdam:
     ``zero_grad`` / ``state_dict`` surface the trainers use."""
 
     def __init__(self, groups, betas=(0.9, 0.999), eps=1e-8, group=None, shadow=False):
-        by_lr = {}
+        merged = {}
         for g in groups:
-            by_lr.setdefault(float(g["lr"]), []).extend(list(g["params"]))
+            # groups that share a learning rate (and the trainer's "follows the schedule" switch) share one flat buffer
+            key = (float(g["lr"]), bool(g.get("scheduled", True)))
+            merged.setdefault(key, []).extend(list(g["params"]))
         self.opts = [P2PZeroAdam(params, lr=lr, betas=betas, eps=eps, group=group, shadow=shadow)
-                     for lr, params in by_lr.items()]
+                     for (lr, _), params in merged.items()]
         self.param_groups = [o.param_groups[0] for o in self.opts]
+        for pg, (_, scheduled) in zip(self.param_groups, merged.keys()):
+            pg["scheduled"] = scheduled
 
     def step(self):
         for o in self.opts:

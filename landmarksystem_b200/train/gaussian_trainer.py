@@ -72,7 +72,14 @@ class GaussianTrainerBase(NeRFTrainer):
     def create_optimizer(self):
         cfg = self.config
         groups = self.model.get_optparam_groups(cfg)
-        optimizer = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
+        if torch.device(cfg.device).type == "cuda" and bool(cfg.get("fused_optimizer", True)):
+            # one device pass per tensor with the gradient reset folded in; its state uses the keys of torch.optim.Adam
+            # (``exp_avg``, ``exp_avg_sq``, ``step``), so the densification surgery on the optimiser state applies unchanged
+            from ..ops import FusedAdam
+
+            optimizer = FusedAdam(groups, lr=0.0, eps=1e-15)
+        else:
+            optimizer = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
         if cfg.start_checkpoint:
             opt_file = os.path.join(os.path.dirname(cfg.start_checkpoint), "opt.th")
             if os.path.exists(opt_file):

@@ -33,7 +33,10 @@ class RayModelTrainer(NeRFTrainer):
         self.optimizer = self.create_optimizer()
         cfg = self.config
         self.mp_sync = GradSynchronizer(cfg.mp_group, average=False) if cfg.branch_parallel else None
-        self.dp_sync = GradSynchronizer(cfg.dp_group if cfg.model_parallel else None, average=True) if cfg.DDP else None
+        if cfg.DDP and not getattr(self, "_zero_dp", False):
+            self.dp_sync = GradSynchronizer(cfg.dp_group if cfg.model_parallel else None, average=True)
+        else:
+            self.dp_sync = None
 
     def create_model(self):
         cfg = self.config
@@ -52,6 +55,18 @@ class RayModelTrainer(NeRFTrainer):
         return model
 
     def make_optimizer(self, groups):
+        cfg = self.config
+        on_cuda = torch.device(cfg.device).type == "cuda"
+        if on_cuda and cfg.DDP and cfg.get("dp_optimizer", "p2p_zero") == "p2p_zero" and torch.distributed.is_initialized() \
+                and cfg.world_size > 1:
+            # data parallel on NVLink-connected GPUs: gradient reduce-scatter, partitioned Adam and parameter all-gather in
+            # one peer-memory kernel per learning-rate group (the reference wraps the model in DistributedDataParallel,
+            # i.e. a bucketed NCCL all-reduce of the whole hash table, benchmarks/nerf/instant_ngp/instant_ngp_trainer.py:124-125)
+            from ..parallel.zero_adam import GroupedP2PZeroAdam
+
+            self.dp_sync = None        # the fused kernel does the reduction
+            self._zero_dp = True
+            return GroupedP2PZeroAdam(groups, betas=(0.9, 0.999), eps=cfg.eps, group=cfg.dp_group if cfg.model_parallel else None)
         if torch.device(self.config.device).type == "cuda" and bool(self.config.get("fused_optimizer", True)):
             from ..ops import FusedAdam
 
@@ -60,7 +75,7 @@ class RayModelTrainer(NeRFTrainer):
 
     def create_optimizer(self):
         cfg = self.config
-        opt = self.make_optimizer(self.module.get_optparam_groups())
+        opt = self.optimizer = self.make_optimizer(self.module.get_optparam_groups())
         path = self._optim_path()
         if cfg.get("ckpt") and os.path.exists(path):
             opt.load_state_dict(torch.load(path, map_location=cfg.device, weights_only=False)["optimizer"])
@@ -68,7 +83,8 @@ class RayModelTrainer(NeRFTrainer):
 
     def _optim_path(self):
         cfg = self.config
-        suffix = f"-sub{cfg.rank}" if cfg.model_parallel else ""
+        per_rank = cfg.model_parallel or bool(getattr(self.optimizer, "partitioned", False))    # ZeRO shards are per rank
+        suffix = f"-sub{cfg.rank}" if per_rank else ""
         return os.path.join(self.optim_dir, f"{cfg.expname}_opt{suffix}.th")
 
     def _replicated_params(self):
@@ -141,9 +157,11 @@ class RayModelTrainer(NeRFTrainer):
                 torch.save(merged, f"{self.logfolder}/state_dict-merged.th")
                 torch.save(kwargs, f"{self.logfolder}/kwargs-merged.th")
             self.barrier()
-        elif is_main_rank():
-            self.module.save_model(self.logfolder)
-            torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+        else:
+            if is_main_rank():
+                self.module.save_model(self.logfolder)
+            if is_main_rank() or bool(getattr(self.optimizer, "partitioned", False)):
+                torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
 
     @torch.no_grad()
     def evaluation(self, prefix: str = "", n_vis: int = 5, save: bool = True):

@@ -82,3 +82,37 @@ def test_radix_sort_and_scan():
     ws2 = torch.empty(_lib_ll("lmb_scan_scratch_bytes")(n), dtype=torch.uint8, device="cuda")
     native.check(native.lib().lmb_exclusive_scan_u32(x.data_ptr(), out.data_ptr(), n, ws2.data_ptr(), native.stream_ptr()), "scan")
     assert torch.equal(out.long(), torch.cumsum(x.long(), 0) - x.long())
+
+
+def test_baseline_restatement_agrees_with_the_oracle():
+    """The PyTorch restatement timed as the 3DGS baseline (``baseline/gs_restatement.py``, written independently of the
+    oracle in ``ops/gaussian_raster.py``) renders the same image from the same parameters."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from baseline.gs_restatement import render
+
+    means, scales, rots, opac, shs, _, s = _scene(n=80)
+    want, _, _ = GaussianRasterizer(s)(means, None, opac, shs=shs, scales=scales, rotations=rots)
+    got = render(means, scales.log(), rots, torch.logit(opac), shs, s.viewmatrix, s.projmatrix, s.campos, s.image_width,
+                 s.image_height, s.tanfovx, s.tanfovy, s.bg)
+    assert got.shape == want.shape
+    assert float((got - want).abs().max()) < 2e-3, float((got - want).abs().max())
+
+
+def test_baseline_orbit_camera_equals_the_framework_camera():
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    from baseline.gs_restatement import orbit_camera
+
+    for k in (0, 7, 123):
+        cam = bench.gs_orbit_camera(k, "cpu")
+        view, proj, campos, tanx, tany = orbit_camera(k, "cpu")
+        torch.testing.assert_close(view, cam.world_view_transform, rtol=1e-4, atol=1e-3)
+        torch.testing.assert_close(proj, cam.full_proj_transform, rtol=1e-4, atol=1e-3)
+        torch.testing.assert_close(campos, cam.camera_center, rtol=1e-5, atol=1e-3)
+        assert abs(tanx - cam.tanfovx) < 1e-6 and abs(tany - cam.tanfovy) < 1e-6
