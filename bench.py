@@ -331,14 +331,18 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
 
     conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "landmarksystem_b200", "models", "instant_ngp", "confs",
                         "synthetic_tiny.py")
+    world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
+    if world > 1:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     cfg = BaseConfig.from_file(conf, {"basedir": tempfile.mkdtemp(prefix="lmb_ngp_bench_"), "device": "cuda", "n_iters": "100000",
                                       "progress_refresh_rate": "1000000", "runtime": "Kernel", "num_levels": "16",
                                       "base_res": "16", "max_res": "8192", "log2_hashmap_size": "22", "grid_resolution": "128",
-                                      "grid_levels": "1", "batch_size": str(rays_per_step), "datadir": "ring:3:16x16:20:3"})
-    trainer = NGPTrainer(cfg)
+                                      "grid_levels": "1", "batch_size": str(rays_per_step * world), "datadir": "ring:3:16x16:20:3",
+                                      "DDP": "true" if world > 1 else "false"})
+    trainer = NGPTrainer(cfg)       # world > 1: data parallel, gradients reduced and Adam applied by the peer-memory ZeRO kernel
     trainer.model.train()
     dev = torch.device("cuda", torch.cuda.current_device())
-    g = torch.Generator(device=dev).manual_seed(0)
+    g = torch.Generator(device=dev).manual_seed(rank)
     pool = 4
     ang = torch.rand(pool, rays_per_step, device=dev, generator=g) * 2 * math.pi
     origin = torch.stack((3.0 * torch.cos(ang), 3.0 * torch.sin(ang), torch.rand(pool, rays_per_step, device=dev, generator=g) - 0.5), -1)
@@ -347,16 +351,23 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
     rgbs = torch.rand(pool, rays_per_step, 3, device=dev, generator=g)
     idxs = torch.zeros(rays_per_step, device=dev)
     times = []
+    import torch.distributed as dist
+
     for k in range(warmup + steps):
         trainer.iteration = k
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
         start.record()
         loss = trainer.train_step(rays[k % pool], rgbs[k % pool], idxs)
         end.record()
         torch.cuda.synchronize()
+        ms_k = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_k, op=dist.ReduceOp.MAX)
         if k >= warmup:
-            times.append(start.elapsed_time(end))
+            times.append(float(ms_k))
     if profile:
         from torch.profiler import ProfilerActivity
         from torch.profiler import profile as torch_profile
@@ -368,8 +379,10 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
             torch.cuda.synchronize()
         print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=80), file=sys.stderr)
     ms = statistics.median(times)
-    return {"metric": "InstantNGP training rays/s (1 GPU, 2^18 rays per step, 16 x 2^22 hash grid)", "value": rays_per_step / ms * 1e3,
-            "ms_per_step": ms, "steps": steps, "loss_finite": bool(torch.isfinite(loss))}
+    return {"metric": f"InstantNGP training rays/s ({world} GPU, 2^18 rays per GPU and step, 16 x 2^22 hash grid)",
+            "value": world * rays_per_step / ms * 1e3, "ms_per_step": ms, "steps": steps, "n_gpus": world,
+            "parallelism": "single" if world == 1 else f"dp{world} (peer-memory ZeRO Adam)",
+            "loss_finite": bool(torch.isfinite(loss))}
 
 
 def time_engine_frames(engine, poses, rank, world, dev, call):
@@ -698,12 +711,11 @@ def main():
     if args.only is not None:
         import torch
 
-        torch.cuda.set_device(0)
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp, "3dgs-restatement": render_fps_3dgs_restatement}[args.only]
-        if args.profile and args.only == "ngp":
-            print(json.dumps(train_rate_ngp(profile=True)))
-        else:
-            print(json.dumps(fn()))
+        out = train_rate_ngp(profile=True) if (args.profile and args.only == "ngp") else fn()
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps(out))
         return
     assert args.gpus in DIVISIONS, "supported GPU counts: 1, 2, 4, 8"
     args.warmup = max(args.warmup, 3)

@@ -78,3 +78,31 @@ def filtering_rays(aabb: torch.Tensor, all_rays: torch.Tensor, chunk: int = 1 <<
         t_min, t_max = torch.minimum(a, b).amax(-1), torch.maximum(a, b).amin(-1)
         keep.append(t_max > t_min)
     return torch.cat(keep)
+
+
+def load_drone_meta(datadir: str, split: str, image_scale, subfolder=None, stride: int = 1) -> Dict:
+    """Metadata of a drone capture in the ``transforms_{split}.json`` layout whose images live in
+    ``images_{image_scale}/`` and whose focal length is either one ``fl_x`` for the whole capture or one per frame
+    (reference: landmark/nerf_components/data/datasets/dataloader/utils/ray_utils.py:122-170).  ``subfolder`` keeps
+    only frames whose parent folder is listed; ``stride`` thins the frame list (the reference's debug switch keeps
+    every 50th).  Returns ``poses [N,4,4]``, ``focals`` (scalar array or ``[N]``), ``fnames``, ``hw`` (height and width
+    of the first image, ``None`` when it cannot be opened) and ``imgfolder``."""
+    meta = load_transforms(datadir, split)
+    frames = meta["frames"]
+    if subfolder:
+        keep = set(subfolder)
+        frames = [f for f in frames if os.path.basename(os.path.dirname(f["file_path"])) in keep]
+    frames = frames[::max(int(stride), 1)]
+    fnames = [f["file_path"] for f in frames]
+    poses = np.stack([np.asarray(f["transform_matrix"], dtype=np.float64) for f in frames]) if frames else np.zeros((0, 4, 4))
+    focals = np.asarray(meta["fl_x"]) if "fl_x" in meta else np.asarray([f["fl_x"] for f in frames])
+    hw = None
+    if fnames:
+        for cand in (fnames[0], os.path.join(datadir, fnames[0]), os.path.join(datadir, f"images_{image_scale}", os.path.basename(fnames[0]))):
+            if os.path.exists(cand):
+                from PIL import Image
+
+                with Image.open(cand) as im:
+                    hw = [im.height, im.width]
+                break
+    return {"poses": poses, "focals": focals, "fnames": fnames, "hw": hw, "imgfolder": os.path.join(datadir, f"images_{image_scale}")}

@@ -228,11 +228,42 @@ class GridNeRFTrainer(NeRFTrainer):
                 total = total + w[0] * den.TV_loss()
             if self.tv_weight_app > 0:
                 total = total + w[1] * app.TV_loss()
+        if getattr(self, "enable_lpips", False):
+            total = total + self._lpips_term(all_ret, rgb_train)
         if self.enable_distort:
             for key in ("distort_loss", "distort_loss1", "distort_loss_nerf"):
                 if key in all_ret:
                     total = total + torch.mean(all_ret[key])
         return total, loss
+
+    def _lpips_term(self, all_ret, rgb_train):
+        """``0.01 * LPIPS-VGG`` between rendered and target ``patch_size`` x ``patch_size`` patches (the batch is then made
+        of whole patches; reference: benchmarks/nerf/gridnerf/gridnerf_trainer.py:271-291).  The ``lpips`` package is
+        optional: without it the term is skipped with one warning."""
+        net = getattr(self, "_lpips_net", None)
+        if net is None:
+            try:
+                import lpips
+
+                net = self._lpips_net = lpips.LPIPS(net="vgg").to(rgb_train.device)
+            except Exception as exc:  # noqa: BLE001 - package or its weights are not available
+                if not getattr(self, "_lpips_warned", False):
+                    print(f"[{self.config.expname}] LPIPS term requested (add_lpips) but unavailable: {type(exc).__name__}: {exc}")
+                    self._lpips_warned = True
+                self._lpips_net = False
+                return 0.0
+        if net is False:
+            return 0.0
+        ps = int(self.config.patch_size)
+
+        def patches(x):
+            return x.reshape(-1, ps, ps, 3).permute(0, 3, 1, 2).clamp(0, 1) * 2 - 1
+
+        target = patches(rgb_train)
+        term = torch.mean(net(patches(all_ret["rgb_map"]), target))
+        if self.module.run_nerf and "rgb_map_nerf" in all_ret:
+            term = term + torch.mean(net(patches(all_ret["rgb_map_nerf"]), target))
+        return 0.01 * term
 
     def train_step(self, rays_train, rgb_train, idxs_train):
         """Forward, backward, gradient sync and optimiser step on one device-resident batch.
@@ -249,7 +280,7 @@ class GridNeRFTrainer(NeRFTrainer):
         cfg = self.config
         if not (bool(cfg.get("cuda_graph", False)) and rays.is_cuda and isinstance(self.optimizer, FusedAdam)
                 and self.optimizer.capturable and self.dp_sync is None and not cfg.channel_parallel and not cfg.DDP
-                and not self.timer.enabled):
+                and not self.timer.enabled and not getattr(self, "enable_lpips", False)):
             return False
         if cfg.branch_parallel:
             # spatial-block model parallelism is graph-safe only on the all-to-all path with kernel-path owner
@@ -334,6 +365,9 @@ class GridNeRFTrainer(NeRFTrainer):
             rays_train, rgb_train, idxs_train = self.data_mgr.get_rays(it)
             if cfg.add_distort > 0 and it == cfg.add_distort:
                 self.enable_distort = True
+            if cfg.add_lpips > 0 and it == cfg.add_lpips:
+                self.enable_lpips = True               # from here on the data manager serves whole patches
+                self.data_mgr.enable_lpips = True
             if cfg.add_nerf > 0 and it == cfg.add_nerf:
                 self.module.run_nerf = True
                 m = self.module

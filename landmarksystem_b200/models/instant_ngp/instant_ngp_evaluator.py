@@ -2,8 +2,7 @@
 ``torchrun ... -m landmarksystem_b200.models.instant_ngp.instant_ngp_evaluator --config <render conf.py> [--key value]``."""
 import sys
 
-from ...configs import BaseConfig, get_default_parser, parse_console_args
-from ...train.nerf_evaluator import RayModelEvaluator
+from ...train.nerf_evaluator import RayModelEvaluator, evaluator_main
 from ..instant_ngp.instant_ngp import InstantNGP
 
 
@@ -17,10 +16,7 @@ class NGPEvaluator(RayModelEvaluator):
 
 
 def main(argv=None):
-    args, unknown = get_default_parser().parse_known_args(argv)
-    config = BaseConfig.from_file(args.config, parse_console_args(unknown))
-    config.is_train = False
-    return NGPEvaluator(config).eval()
+    return evaluator_main(NGPEvaluator, argv)
 
 
 if __name__ == "__main__":

@@ -2,8 +2,7 @@
 ``torchrun ... -m landmarksystem_b200.models.origin_gs.gs_evaluator --config <render conf.py> [--key value]``."""
 import sys
 
-from ...configs import BaseConfig, get_default_parser, parse_console_args
-from ...train.nerf_evaluator import GaussianEvaluator
+from ...train.nerf_evaluator import GaussianEvaluator, evaluator_main
 from ..origin_gs.gs_model import GaussianModel
 
 
@@ -12,10 +11,7 @@ class Gaussian3DEvaluator(GaussianEvaluator):
 
 
 def main(argv=None):
-    args, unknown = get_default_parser().parse_known_args(argv)
-    config = BaseConfig.from_file(args.config, parse_console_args(unknown))
-    config.is_train = False
-    return Gaussian3DEvaluator(config).eval()
+    return evaluator_main(Gaussian3DEvaluator, argv)
 
 
 if __name__ == "__main__":

@@ -105,9 +105,12 @@ class GaussianModel(BaseGaussian):
     def forward(self, viewpoint_camera, scaling_modifier: float = 1.0, override_color=None, render_exclude_filter=None):
         enc, cfg = self.gaussian_encoding, self.config
         cam = viewpoint_camera.to(self.device)
-        visible = self.prefilter_voxel(cam, scaling_modifier)
-        if render_exclude_filter is not None:
-            visible = visible & render_exclude_filter
+        if self.training or render_exclude_filter is not None or not enc.get_xyz.is_cuda:
+            visible = self.prefilter_voxel(cam, scaling_modifier)
+            if render_exclude_filter is not None:
+                visible = visible & render_exclude_filter
+        else:
+            visible = None       # evaluation on the GPU: the rasteriser's own preprocess kernel does the same frustum test
         means3D = enc.get_xyz
         screenspace = torch.zeros_like(means3D, requires_grad=True) + 0
         if self.training:
@@ -130,18 +133,15 @@ class GaussianModel(BaseGaussian):
         else:
             shs = enc.get_features
         means2D = screenspace
-        if not self.training:  # render only the visible subset
-            idx = visible.nonzero().squeeze(-1)
-            pick = lambda t: None if t is None else t[idx]  # noqa: E731
-            means3D, means2D, opacity = means3D[idx], means2D[idx], opacity[idx]
-            scales, rotations, cov3D, shs, colors = pick(scales), pick(rotations), pick(cov3D), pick(shs), pick(colors)
-            mask = None
-        else:
-            mask = visible
+        # The reference compacts every per-Gaussian tensor to the visible subset before an evaluation render
+        # (benchmarks/nerf/origin_gs/gs_model.py:199-208) because its rasteriser preprocesses whatever it is given; the
+        # rasteriser here takes the visibility mask and skips masked Gaussians in its first kernel, so no index list is
+        # built on the host and no gigabyte of parameters is gathered per frame.
+        mask = visible
         image, radii, _ = self.renderer(means3D=means3D, means2D=means2D, shs=shs, colors_precomp=colors,
                                         opacities=opacity, scales=scales, rotations=rotations, cov3D_precomp=cov3D,
                                         visible_mask=mask)
-        self.viewspace_points, self.visibility_filter, self.radii = screenspace, visible, radii
+        self.viewspace_points, self.visibility_filter, self.radii = screenspace, (visible if visible is not None else radii > 0), radii
         return image
 
     # -- training helpers -------------------------------------------------------------------------------

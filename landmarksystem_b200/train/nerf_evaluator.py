@@ -229,3 +229,13 @@ class GaussianEvaluator(NeRFEvaluator):
             lat = float(np.mean(times[1:] or times))
             print(f"average time {lat * 1e3:.2f} ms, FPS {1.0 / lat:.2f}, primitives {self.model.get_primitives_num}", flush=True)
         return psnrs
+
+
+def evaluator_main(evaluator_cls, argv=None):
+    """Shared command-line entry of the six model evaluators: ``--config <render conf.py> [--key value ...]``."""
+    from ..configs import BaseConfig, get_default_parser, parse_console_args
+
+    args, unknown = get_default_parser().parse_known_args(argv)
+    config = BaseConfig.from_file(args.config, parse_console_args(unknown))
+    config.is_train = False
+    return evaluator_cls(config).eval()

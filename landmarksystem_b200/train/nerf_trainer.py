@@ -42,7 +42,9 @@ class NeRFTrainer:
             src = config.get("config")
             if src and os.path.exists(str(src)):
                 shutil.copyfile(str(src), os.path.join(self.logfolder, "config.txt"))
-        self.logger = MetricsLogger(self.logfolder if main else None, tensorboard=bool(config.get("tensorboard")))
+        self.logger = MetricsLogger(self.logfolder if main else None, tensorboard=bool(config.get("tensorboard")),
+                                    wandb=bool(config.get("wandb")), run_name=str(config.get("expname")),
+                                    run_config={k: v for k, v in dict(config).items() if isinstance(v, (int, float, str, bool, list))})
         self.writer = self.logger.writer
         self.timer = StageTimer(enabled=bool(config.get("profile", False)))
 

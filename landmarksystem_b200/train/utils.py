@@ -51,3 +51,44 @@ def get_local_rank() -> int:
 
 def is_main_rank() -> bool:
     return get_rank() == 0
+
+
+def init_distributed_mode(env: str = "single_node", backend: str = None, timeout_s: int = 1800) -> dict:
+    """Bring up ``torch.distributed`` from the launcher's environment and return ``{rank, world_size, local_rank}``
+    (reference: landmark/train/utils/distributed_utils.py:73-140).  ``env``: ``"single_node"`` / ``"torchrun"`` read
+    ``RANK / WORLD_SIZE / LOCAL_RANK``; ``"slurm"`` derives them from ``SLURM_PROCID / SLURM_NTASKS / SLURM_LOCALID`` and
+    takes the first host of ``SLURM_NODELIST`` as master; ``"aliyun"`` reads the DLC launcher's ``RANK`` (node rank),
+    ``WORLD_SIZE`` (node count) and ``LOCAL_RANK`` with ``NPROC_PER_NODE`` processes per node.  Idempotent."""
+    import datetime
+
+    import torch
+
+    if env == "slurm":
+        rank, world = int(os.environ["SLURM_PROCID"]), int(os.environ["SLURM_NTASKS"])
+        local = int(os.environ.get("SLURM_LOCALID", 0))
+        nodelist = os.environ.get("SLURM_NODELIST", "127.0.0.1")
+        first = nodelist.split(",")[0]
+        if "[" in first:                                  # "node[03-07]" -> "node03"
+            head, rng = first.split("[", 1)
+            first = head + rng.rstrip("]").split("-")[0].split(",")[0]
+        os.environ.setdefault("MASTER_ADDR", first)
+        os.environ.setdefault("MASTER_PORT", "29501")
+    elif env == "aliyun":
+        per_node = int(os.environ.get("NPROC_PER_NODE", max(torch.cuda.device_count(), 1)))
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        rank = int(os.environ.get("RANK", 0)) * per_node + local
+        world = int(os.environ.get("WORLD_SIZE", 1)) * per_node
+    else:
+        rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local))
+    if world > 1 and not dist.is_initialized():
+        backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local % torch.cuda.device_count())
+        dist.init_process_group(backend=backend, init_method="env://", world_size=world, rank=rank,
+                                timeout=datetime.timedelta(seconds=timeout_s))
+        dist.barrier()
+    return {"rank": rank, "world_size": world, "local_rank": local}

@@ -13,10 +13,22 @@ import torch
 
 
 class MetricsLogger:
-    def __init__(self, logfolder: Optional[str], tensorboard: bool = False, enabled: bool = True):
+    def __init__(self, logfolder: Optional[str], tensorboard: bool = False, enabled: bool = True, wandb: bool = False,
+                 run_name: Optional[str] = None, run_config: Optional[dict] = None):
         self.enabled = enabled and logfolder is not None
         self._fh = None
         self.writer = None
+        self.wandb = None
+        if self.enabled and wandb:
+            # the reference starts a wandb run when ``TrainConfig.wandb`` is set (landmark/train/nerf_trainer.py:95-97);
+            # the package is optional here: without it the flag only costs a warning
+            try:
+                import wandb as _wandb
+
+                _wandb.init(project="landmarksystem_b200", name=run_name, dir=logfolder, config=run_config or {})
+                self.wandb = _wandb
+            except Exception as exc:  # noqa: BLE001 - not installed, or no network
+                print(f"[metrics] wandb logging requested but unavailable ({type(exc).__name__}); continuing without it")
         if self.enabled:
             os.makedirs(logfolder, exist_ok=True)
             self._fh = open(os.path.join(logfolder, "metrics.jsonl"), "a", encoding="utf-8")
@@ -38,6 +50,8 @@ class MetricsLogger:
         if self.writer is not None:
             for k, v in scalars.items():
                 self.writer.add_scalar(k, float(v), global_step=step)
+        if self.wandb is not None:
+            self.wandb.log({k: float(v) for k, v in scalars.items()}, step=int(step))
 
     def close(self) -> None:
         if self._fh is not None:

@@ -117,3 +117,27 @@ def test_every_shipped_configuration_loads():
     assert bp.branch_parallel and list(bp.plane_division) == [10, 5] and bp.ub[0] > 40
     b2c = seen[os.path.join("gridnerf", "confs", "matrixcity_2block_lowquality_Branch2ChannelParallel_render.py")]
     assert b2c.channel_parallel and b2c.channel_parallel_size == 2 and not b2c.branch_parallel and b2c.sampling_opt
+
+
+def test_init_distributed_mode_reads_the_launcher_environment(monkeypatch):
+    from landmarksystem_b200.train.utils import init_distributed_mode
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    assert init_distributed_mode("single_node") == {"rank": 0, "world_size": 1, "local_rank": 0}
+    monkeypatch.setenv("SLURM_PROCID", "0"); monkeypatch.setenv("SLURM_NTASKS", "1"); monkeypatch.setenv("SLURM_LOCALID", "0")
+    monkeypatch.setenv("SLURM_NODELIST", "gpu[017-020],gpu033")
+    monkeypatch.delenv("MASTER_ADDR", raising=False)
+    out = init_distributed_mode("slurm")
+    import os
+
+    assert out["world_size"] == 1 and os.environ["MASTER_ADDR"] == "gpu017"
+
+
+def test_metrics_logger_with_wandb_flag_but_no_package(tmp_path, capsys):
+    from landmarksystem_b200.utils.metrics import MetricsLogger
+
+    log = MetricsLogger(str(tmp_path), wandb=True, run_name="t")
+    log.log(1, {"Train/Loss": 0.5})
+    log.close()
+    assert (tmp_path / "metrics.jsonl").read_text().count("Train/Loss") == 1

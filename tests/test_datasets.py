@@ -105,3 +105,30 @@ def test_shard_preprocessing_single_and_distributed(tmp_path):
     assert total == 3
     rows = torch.cat([PreprocessedDataset(str(tmp_path / "dist"))[k][2] for k in range(3)])
     assert rows.unique().numel() == 3 * 512                  # no ray is duplicated across shards
+
+
+def test_drone_metadata_loader(tmp_path):
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    from landmarksystem_b200.components.data.datasets.ray_utils import load_drone_meta
+
+    os.makedirs(tmp_path / "images_4" / "flightA", exist_ok=True)
+    os.makedirs(tmp_path / "images_4" / "flightB", exist_ok=True)
+    frames = []
+    for k, sub in enumerate(("flightA", "flightA", "flightB")):
+        name = str(tmp_path / "images_4" / sub / f"{k:03d}.png")
+        Image.fromarray(np.zeros((6, 8, 3), dtype=np.uint8)).save(name)
+        pose = np.eye(4); pose[0, 3] = k
+        frames.append({"file_path": name, "transform_matrix": pose.tolist(), "fl_x": 100.0 + k})
+    with open(tmp_path / "transforms_train.json", "w", encoding="utf-8") as fh:
+        json.dump({"frames": frames}, fh)
+    meta = load_drone_meta(str(tmp_path), "train", 4, subfolder=["flightA"])
+    assert meta["poses"].shape == (2, 4, 4) and meta["focals"].tolist() == [100.0, 101.0] and meta["hw"] == [6, 8]
+    assert meta["imgfolder"].endswith("images_4")
+    with open(tmp_path / "transforms_test.json", "w", encoding="utf-8") as fh:
+        json.dump({"fl_x": 55.0, "frames": frames}, fh)
+    meta = load_drone_meta(str(tmp_path), "test", 4, stride=2)
+    assert float(meta["focals"]) == 55.0 and len(meta["fnames"]) == 2
