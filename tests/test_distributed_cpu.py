@@ -208,3 +208,100 @@ def _ddp_worker(rank, world, tmp):
 def test_data_parallel_replicas_stay_identical(tmp_path):
     res = _run(_ddp_worker, 2, str(tmp_path))
     assert torch.allclose(torch.from_numpy(res[0]), torch.from_numpy(res[1]), atol=1e-6)
+
+
+def _channel_model(parallel: bool):
+    from landmarksystem_b200.comm.train_groups import init_train_groups
+    from landmarksystem_b200.components.scene import SceneManager
+    from landmarksystem_b200.convertor import ComponentConvertorFactory
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF, GridNeRFConfig
+    from landmarksystem_b200.utils import Config
+
+    mc = GridNeRFConfig(resMode=[1, 2], n_lamb_sigma=[16], n_lamb_sh=[48], nonlinear_density=True, view_pe=2, fea_pe=2,
+                        train_near_far=[0.5, 6.0], step_ratio=2.0)
+    cfg = Config(dict(mc))
+    cfg.update(is_train=True, device="cpu", lb=[-2.0, -2.0, -0.5], ub=[2.0, 2.0, 0.5], plane_division=[1, 1],
+               branch_parallel=False, channel_parallel=parallel, channel_parallel_size=2 if parallel else 1,
+               model_parallel_and_DDP=False, DDP=False)
+    if parallel:
+        init_train_groups(cfg)
+    sm = SceneManager(cfg)
+    torch.manual_seed(0)
+    model = GridNeRF(sm.aabb, [16, 16, 8], "cpu", near_far=[0.5, 6.0], scene_manager=sm, config=cfg)
+    if parallel:
+        model = ComponentConvertorFactory.get_convertor("parallelize").convert(model, cfg)
+    return model.train(), cfg
+
+
+def _train_three_steps(model):
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    target = torch.rand(256, 3, generator=torch.Generator().manual_seed(9))
+    for k in range(3):
+        torch.manual_seed(100 + k)                      # same sample jitter / background draw everywhere
+        out = model(_rays(), N_samples=24)["rgb_map"]
+        loss = ((out - target) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    return float(loss)
+
+
+def _channel_worker(rank, world, full_state):
+    model, cfg = _channel_model(True)
+    for name in ("density_encoding", "rgb_encoding"):
+        getattr(model, name).load_full_state({k[len(name) + 1:]: v for k, v in full_state.items() if k.startswith(name + ".")})
+    model.load_state_dict({k: v for k, v in full_state.items() if "encoding" not in k}, strict=False)
+    loss = _train_three_steps(model)
+    planes = [p.detach().clone() for p in model.rgb_encoding.plane_coef] + [p.detach().clone() for p in model.density_encoding.plane_coef]
+    head = model.rgb_decoder.decoder.linears()[0].weight.detach().clone()
+    return loss, planes, head
+
+
+def test_channel_parallel_training_matches_single_process():
+    """Three Adam steps with the feature channels split over two ranks (each rank trains its channel slice of every
+    plane and line, the replicated heads see the gathered features) against the same three steps in one process."""
+    single, _ = _channel_model(False)
+    state = {k: v.clone() for k, v in single.state_dict().items()}
+    want_loss = _train_three_steps(single)
+    res = _run(_channel_worker, 2, state)
+    want_planes = [p.detach() for p in single.rgb_encoding.plane_coef] + [p.detach() for p in single.density_encoding.plane_coef]
+    for k, want in enumerate(want_planes):
+        got = torch.cat([torch.from_numpy(res[r][1][k]) for r in range(2)], dim=-1)     # channel slices side by side
+        assert got.shape == want.shape
+        assert torch.allclose(got, want, atol=2e-5), (k, float((got - want).abs().max()))
+    for r in range(2):
+        assert abs(res[r][0] - want_loss) < 1e-5
+        assert torch.allclose(torch.from_numpy(res[r][2]), single.rgb_decoder.decoder.linears()[0].weight.detach(), atol=2e-5)
+
+
+def _hybrid_worker(rank, world, tmp):
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.gridnerf.gridnerf_trainer import GridNeRFTrainer
+
+    conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "landmarksystem_b200", "models", "gridnerf",
+                        "confs", "synthetic_tiny.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": tmp, "device": "cpu", "n_iters": "4", "batch_size": "256", "DDP": "true",
+                                      "branch_parallel": "true", "model_parallel_and_DDP": "true",
+                                      "datadir": "ring:3:16x16:20:3", "nSamples": "24", "progress_refresh_rate": "100"})
+    cfg.plane_division = [2, 1]
+    tr = GridNeRFTrainer(cfg)
+    tr.model.train()
+    for it in range(4):
+        tr.train_step(*tr.data_mgr.get_rays(it))
+    grids = torch.cat([p.detach().reshape(-1) for n, p in tr.module.named_parameters() if "encoding" in n])
+    heads = torch.cat([p.detach().reshape(-1) for n, p in tr.module.named_parameters() if "encoding" not in n])
+    return int(cfg.mp_rank), int(cfg.dp_rank), grids, heads
+
+
+def test_hybrid_model_and_data_parallel_groups_train_consistently(tmp_path):
+    """Four ranks = 2 spatial blocks x 2 data-parallel replicas (contiguous model-parallel groups, strided data-parallel
+    groups; reference layout: landmark/nerf_components/components_convertor/comm_groups.py:51-75).  After four steps the
+    two replicas of each block hold identical grids, every rank holds identical heads, and the two blocks differ."""
+    res = _run(_hybrid_worker, 4, str(tmp_path))
+    by = {(res[r][0], res[r][1]): (torch.from_numpy(res[r][2]), torch.from_numpy(res[r][3])) for r in range(4)}
+    assert sorted(by) == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    for mp in (0, 1):
+        assert torch.allclose(by[(mp, 0)][0], by[(mp, 1)][0], atol=1e-6)
+    assert not torch.allclose(by[(0, 0)][0], by[(1, 0)][0], atol=1e-3)
+    for key in by:
+        assert torch.allclose(by[key][1], by[(0, 0)][1], atol=1e-6)
