@@ -385,6 +385,82 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
             "loss_finite": bool(torch.isfinite(loss))}
 
 
+def stream_fps_gridnerf(frames: int = 200, blocks: int = 8, plane: int = 1024):
+    """Dynamic loading figure (fifth benchmark shape at reduced block size): a scene of ``blocks x blocks`` spatial blocks
+    with ``plane``^2 texels x (16 + 48) channels each, bf16 on pinned host memory, rendered through ``init_inference``
+    with an ``offload_config`` (3x3-block resident window, prefetch ahead of the camera) along a fly-through at
+    1920x1080.  Reports frames per second (device time, CUDA events), the host-to-device rate over the whole flight
+    and the fraction of frames that had to wait for a block."""
+    import gc
+    import tempfile
+
+    import torch
+
+    import landmarksystem_b200 as lm
+    from landmarksystem_b200.components.scene import SceneManager
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF, GridNeRFConfig
+    from landmarksystem_b200.render.adapters import make_adapter
+    from landmarksystem_b200.utils import Config
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    root = tempfile.mkdtemp(prefix="lmb_stream_bench_")
+    lb, ub = [0.0, 0.0, 0.0], [1000.0 * blocks, 1000.0 * blocks, 300.0]
+
+    def model_config(device):
+        mc = GridNeRFConfig(resMode=[1], n_lamb_sigma=[16], n_lamb_sh=[48], nonlinear_density=True, view_pe=2, fea_pe=2,
+                            featureC=128, train_near_far=[10.0, 2000.0], step_ratio=10.0, nSamples=SAMPLES, sampling_opt=True,
+                            n_importance=SAMPLES, distance_scale=25, fea2denseAct="relu", grid_dtype="bf16", runtime="Kernel")
+        cfg = Config(dict(mc))
+        cfg.update(is_train=False, device=device, lb=lb, ub=ub, plane_division=[blocks, blocks], branch_parallel=False,
+                   ckpt=os.path.join(root, "state_dict.th"), kwargs=os.path.join(root, "kwargs.th"))
+        return cfg
+
+    cfg = model_config(str(dev))
+    sm = SceneManager(cfg)
+    torch.manual_seed(0)
+    model = GridNeRF(sm.aabb.to(dev), [plane * blocks, plane * blocks, LINE], dev, near_far=[10.0, 2000.0], scene_manager=sm, config=cfg)
+    model.save_model(root)                     # one merged checkpoint in the reference layout, all blocks
+    scene_bytes = sum(p.numel() for n, p in model.named_parameters() if "plane_coef" in n) * 2
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    engine = lm.init_inference(GridNeRF, make_adapter(GridNeRF), model_config(str(dev)),
+                               Config(runtime="Kernel", kernel_fusion=True,
+                                      offload_config={"local_plane_split": [3, 3], "plane_split": [blocks, blocks], "dtype": "bf16",
+                                                      "prefetch_frames": 8, "swap_delay": 2}))
+    import numpy as np
+
+    span = ub[0] - 2000.0
+    times = []
+    H, W = RENDER_HW
+    t_start = None
+    for k in range(frames + 2):
+        u = k / max(frames + 1, 1)
+        pose = np.eye(4, dtype=np.float32)
+        pose[:3, 3] = [1000.0 + span * u, 0.5 * ub[1] + 0.3 * ub[1] * math.sin(2 * math.pi * u), 400.0]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if k == 2:
+            t_start = time.time()
+            bytes0 = engine.model.model.stats()["bytes_h2d"]
+        start.record()
+        engine(torch.from_numpy(pose), RENDER_CHUNK, H, W, RENDER_FOCAL)
+        end.record()
+        torch.cuda.synchronize()
+        if k >= 2:
+            times.append(start.elapsed_time(end))
+    wall = time.time() - t_start
+    st = engine.model.model.stats()
+    ms = statistics.median(times)
+    return {"metric": "GridNeRF 1080p render FPS with dynamic loading (host-resident blocks)", "value": 1000.0 / ms,
+            "ms_per_frame": ms, "ms_per_frame_mean": sum(times) / len(times), "frames": frames,
+            "scene": {"blocks": [blocks, blocks], "texels_per_block": [plane, plane], "channels": 64, "host_bytes_bf16": scene_bytes,
+                      "window": [3, 3]},
+            "h2d_gb_per_s_over_flight": (st["bytes_h2d"] - bytes0) / wall / 1e9, "h2d_bytes": st["bytes_h2d"] - bytes0,
+            "d2d_bytes": st["bytes_d2d"], "stalled_frames": st["stalled_frames"], "late_swaps": st["late_swaps"],
+            "stalled_fraction": st["stalled_frames"] / max(st["frames"], 1)}
+
+
 def time_engine_frames(engine, poses, rank, world, dev, call):
     """Device time of ``engine(...)`` per frame: CUDA events on every rank around the call (rank 0 passes the pose, the
     others call ``engine()``), barrier + synchronise on both sides, max over ranks.  The first two frames warm up.
@@ -700,7 +776,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp", "3dgs-restatement"],
+    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp", "3dgs-restatement", "stream"],
                     help="run one secondary single-GPU benchmark alone and print its JSON (--profile adds the PyTorch "
                          "profiler's kernel table of two more steps on stderr)")
     ap.add_argument("--profile", action="store_true")
@@ -712,7 +788,8 @@ def main():
         import torch
 
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
-        fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp, "3dgs-restatement": render_fps_3dgs_restatement}[args.only]
+        fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp, "3dgs-restatement": render_fps_3dgs_restatement,
+              "stream": stream_fps_gridnerf}[args.only]
         out = train_rate_ngp(profile=True) if (args.profile and args.only == "ngp") else fn()
         if int(os.environ.get("RANK", 0)) == 0:
             print(json.dumps(out))

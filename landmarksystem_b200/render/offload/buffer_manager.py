@@ -161,6 +161,10 @@ class BufferManager:
             return True
         return (not self.cuda) or self.event is None or self.event.query()
 
+    def copy_finished(self) -> bool:
+        """Whether the pending window's copies have completed on the device (always true on the CPU)."""
+        return (not self.cuda) or self.event is None or self.event.query()
+
     def wait_update_done_keep(self) -> None:
         if self.cuda and self.event is not None:
             torch.cuda.current_stream(self.device).wait_event(self.event)

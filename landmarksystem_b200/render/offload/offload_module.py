@@ -4,7 +4,15 @@ window in while the camera moves (reference: landmark/render/parameter_loader/of
 Configuration (``inference_config.offload_config``): ``local_plane_split`` (window size in blocks),
 ``plane_split`` (scene partition), ``use_nccl``, ``use_h2d``, ``channel_last`` (accepted; the native
 layout already is channels-last), ``sync_switch``; additions: ``dtype`` ("bf16" halves the streamed
-bytes, the lookup kernels read bf16 directly) and ``swap_delay`` (frames between issuing and swapping)."""
+bytes, the lookup kernels read bf16 directly), ``swap_delay`` (frames between issuing and swapping) and
+``prefetch_frames`` (how many frames ahead of the camera the window is chosen, see ``_pre_forward``).
+
+The reference starts loading a window when the camera has already crossed into a new block
+(landmark/render/parameter_loader/offload_module.py:98-123).  Here the camera track is extrapolated: the window is
+centred on the block the camera will be over ``prefetch_frames`` frames from now (velocity = smoothed displacement
+per frame), so the copy is issued before the boundary is reached and the swap has happened by the time the camera
+arrives.  ``stats()`` reports how many frames found the camera's block missing from the resident window (a stall:
+the frame then waits for the copy) and how many swaps had to wait for an unfinished copy."""
 from __future__ import annotations
 
 from typing import Any, Mapping
@@ -78,6 +86,10 @@ class OffloadModule(nn.Module):
         self.model.load_from_state_dict(rest, False)
         self._shrink_streamed_params()
         self.init = True
+        self.prefetch_frames = int(config.get("prefetch_frames", 8))
+        self._last_xy = None
+        self._velocity = None
+        self.frames = self.stalled_frames = self.late_swaps = 0
 
     # -- layout glue --------------------------------------------------------------------------------------
     def _to_internal(self, key: str, piece: torch.Tensor) -> torch.Tensor:
@@ -138,20 +150,62 @@ class OffloadModule(nn.Module):
         return self.model.load_from_state_dict(rest, False)
 
     # -- per-frame hook ---------------------------------------------------------------------------------------
+    def _block_at(self, xy) -> int:
+        sm = self.scene_mgr
+        nx, ny = sm._partition
+        lo = sm.aabb[0, :2].tolist()
+        width = sm.block_width.tolist()
+        bx = min(max(int((xy[0] - lo[0]) // width[0]), 0), nx - 1)
+        by = min(max(int((xy[1] - lo[1]) // width[1]), 0), ny - 1)
+        return bx * ny + by
+
+    def _window_of(self, block: int):
+        return calculate_block_neighbours(block, self.scene_mgr.block_partition.tolist(), self.scene_mgr.local_block_partition)
+
+    def _predicted_block(self, xy):
+        """Block under the camera ``prefetch_frames`` frames ahead, from an exponentially smoothed per-frame velocity."""
+        if self._last_xy is not None:
+            step = (xy[0] - self._last_xy[0], xy[1] - self._last_xy[1])
+            self._velocity = step if self._velocity is None else tuple(0.5 * v + 0.5 * s for v, s in zip(self._velocity, step))
+        self._last_xy = xy
+        if self._velocity is None or self.prefetch_frames <= 0:
+            return self._block_at(xy)
+        return self._block_at((xy[0] + self._velocity[0] * self.prefetch_frames, xy[1] + self._velocity[1] * self.prefetch_frames))
+
+    def stats(self) -> dict:
+        mgr = self.buffer_manager
+        return {"frames": self.frames, "stalled_frames": self.stalled_frames, "late_swaps": self.late_swaps,
+                "bytes_h2d": mgr.bytes_h2d, "bytes_d2d": mgr.bytes_d2d, "bytes_pushed": mgr.bytes_pushed}
+
     def _pre_forward(self, *args):
         rays = args[0]
-        block = int(self.scene_mgr.select_block_idx(rays.to(self.scene_mgr.aabb.device) if torch.is_tensor(rays) else rays))
-        window = calculate_block_neighbours(block, self.scene_mgr.block_partition.tolist(),
-                                            self.scene_mgr.local_block_partition)
+        xy = [float(v) for v in (rays[0, :2] if torch.is_tensor(rays) else rays.data[0, :2]).tolist()]
+        block_now = self._block_at(xy)
         mgr = self.buffer_manager
+        self.frames += 1
         if self.init:
-            mgr.update_buffer(window, init=True)
+            self._predicted_block(xy)
+            mgr.update_buffer(self._window_of(block_now), init=True)
             mgr.wait_update_done()
             self.load_buffer()
             self.init = False
             return
-        mgr.update_buffer(window)
+        target = self._window_of(self._predicted_block(xy))
+        if block_now not in target:              # never trade the block under the camera for a predicted one
+            target = self._window_of(block_now)
+        mgr.update_buffer(target)
         if mgr.update_done():
+            if not mgr.copy_finished():
+                self.late_swaps += 1             # the swap frame arrived before the copy: this frame waits for it
+            mgr.change_buffer()
+            self.load_buffer()
+        if block_now not in mgr.get_buffer().local_block_idxes:
+            # the camera outran the stream (a jump, or a speed the window cannot follow): wait for data that covers it
+            self.stalled_frames += 1
+            if mgr.pending is None or block_now not in mgr.pending:
+                if mgr.pending is not None:
+                    mgr.change_buffer()
+                mgr.update_buffer(self._window_of(block_now))
             mgr.change_buffer()
             self.load_buffer()
 

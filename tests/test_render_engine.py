@@ -148,3 +148,33 @@ def test_dynamic_loading_gpu_bf16_stream(tmp_path):
         b, _ = off(_pose(x, y), 4096, 16, 16, 120.0)
     torch.cuda.synchronize()
     assert (a.float() - b.float()).abs().mean() < 3.0
+
+
+def test_dynamic_loading_prefetches_ahead_of_a_scripted_camera_track(tmp_path):
+    """A camera flies along +x over a 6x6-block scene with a 3x3 window.  With ``prefetch_frames`` the window is
+    re-centred on the block the camera is about to enter BEFORE it crosses the boundary; without it (the reference's
+    policy) the window only follows after the crossing.  No frame stalls in either case at this speed."""
+    _save_random_model(tmp_path, [6, 6])
+    width = 4.0 / 6.0                                  # block width of the [-2, 2] scene
+
+    def fly(prefetch):
+        off = _engine(tmp_path, [6, 6], "cpu", offload_config={"local_plane_split": [3, 3], "plane_split": [6, 6],
+                                                             "prefetch_frames": prefetch, "swap_delay": 0})
+        module = off.model.model
+        centre_ahead = 0
+        for k in range(60):
+            x = -2.0 + width * 1.5 + 0.04 * k          # starts in the middle of block column 1, 0.06 blocks per frame
+            off(_pose(x, 0.1), 4096, 4, 4, 60.0)
+            col_now = int((x + 2.0) // width)
+            window = module.buffer_manager.get_buffer().local_block_idxes
+            cols = sorted({b // 6 for b in window})
+            assert col_now in cols
+            if len(cols) == 3 and cols[1] == col_now + 1:
+                centre_ahead += 1                      # window already centred on the next column
+        return module.stats(), centre_ahead
+
+    stats, ahead = fly(8)
+    assert stats["stalled_frames"] == 0 and stats["late_swaps"] == 0 and stats["frames"] == 60
+    assert ahead > 0
+    stats0, ahead0 = fly(0)
+    assert stats0["stalled_frames"] == 0 and ahead0 == 0
