@@ -87,8 +87,11 @@ class InferenceEngine(Module):
                     value.to(device)
             if "device" in vars(mod):
                 mod.device = device
-        if device.type == "cuda" and RuntimeType(self._config.get("runtime", "Torch")) is RuntimeType.Kernel:
-            for mod in self.model.modules():       # kernel runtime reads bf16 shadows of the feature grids
+        if device.type == "cuda" and RuntimeType(self._config.get("runtime", "Torch")) is RuntimeType.Kernel \
+                and self._config.get(_OFFLOAD_CONFIG_STR) is None:
+            # kernel runtime reads bf16 shadows of the feature grids (with dynamic loading the streamed window is the
+            # storage the kernels read, in the dtype the offload configuration asks for: no second copy)
+            for mod in self.model.modules():
                 if hasattr(mod, "enable_shadow") and hasattr(mod, "plane_coef"):
                     mod.enable_shadow(False)
 
