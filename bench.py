@@ -385,7 +385,7 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
             "loss_finite": bool(torch.isfinite(loss))}
 
 
-def stream_fps_gridnerf(frames: int = 200, blocks: int = 8, plane: int = 1024):
+def stream_fps_gridnerf(frames: int = int(os.environ.get("LMB_STREAM_FRAMES", "200")), blocks: int = 8, plane: int = 1024):
     """Dynamic loading figure (fifth benchmark shape at reduced block size): a scene of ``blocks x blocks`` spatial blocks
     with ``plane``^2 texels x (16 + 48) channels each, bf16 on pinned host memory, rendered through ``init_inference``
     with an ``offload_config`` (3x3-block resident window, prefetch ahead of the camera) along a fly-through at
@@ -450,6 +450,14 @@ def stream_fps_gridnerf(frames: int = 200, blocks: int = 8, plane: int = 1024):
         if k >= 2:
             times.append(start.elapsed_time(end))
     wall = time.time() - t_start
+    if os.environ.get("LMB_RENDER_PROFILE"):        # kernel table of one more frame, on stderr
+        from torch.profiler import ProfilerActivity
+        from torch.profiler import profile as torch_profile
+
+        with torch_profile(activities=[ProfilerActivity.CUDA]) as prof:
+            engine(torch.from_numpy(pose), RENDER_CHUNK, H, W, RENDER_FOCAL)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70), file=sys.stderr)
     st = engine.model.model.stats()
     ms = statistics.median(times)
     return {"metric": "GridNeRF 1080p render FPS with dynamic loading (host-resident blocks)", "value": 1000.0 / ms,

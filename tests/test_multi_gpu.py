@@ -63,3 +63,8 @@ def test_engine_block_model_parallel_render(world):
 @pytest.mark.parametrize("world", _worlds())
 def test_dynamic_loading_nvlink_fanout(world):
     _run_worker("worker_offload_fanout.py", world, "OFFLOAD_FANOUT_RESULTS", 2000)
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs at least 2 GPUs")
+def test_partitioned_optimizer_resumes_from_per_rank_shards():
+    _run_worker("worker_zero_resume.py", 2, "ZERO_RESUME_RESULTS", 2000)
