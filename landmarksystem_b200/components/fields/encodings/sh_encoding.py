@@ -1,11 +1,11 @@
 """Spherical-harmonics direction encoding, degree <= 4 -> 16 outputs (reference:
 landmark/nerf_components/model_components/fields/encodings/sh_encoding.py:6-59, which wraps
 ``tcnn.Encoding("SphericalHarmonics")``).  Directions are given in ``[0, 1]`` (tiny-cuda-nn's
-convention) when ``unit_range`` is set, else as unit vectors."""
+convention) when ``unit_range`` is set, else as unit vectors.  CUDA tensors go through ``sh_encode_kernel``
+(``ops/csrc/ngp_field.cu``), CPU tensors through the PyTorch statement of the basis."""
 import torch
 
 from ...model.base_module import BaseModule
-from ...utils.sh_utils import sh_basis
 
 
 class SHEncoding(BaseModule):
@@ -19,5 +19,6 @@ class SHEncoding(BaseModule):
         return self.levels ** 2
 
     def forward(self, dirs: torch.Tensor) -> torch.Tensor:
-        d = dirs * 2.0 - 1.0 if self.unit_range else dirs
-        return sh_basis(d.float(), self.levels - 1)
+        from ....ops.ngp_field import sh_encode
+
+        return sh_encode(dirs, self.levels, self.unit_range)

@@ -176,7 +176,7 @@ class TensorVMEncoding(VolumeEncoding):
 
     # -- forward ------------------------------------------------------------------------
     def _lookup(self, coords: torch.Tensor, ks: Sequence[int], count=None, out_dtype=torch.float32,
-                out_width: int = 0, zero_fill: bool = True) -> torch.Tensor:
+                out_width: int = 0, zero_fill: bool = True, tail=None) -> torch.Tensor:
         planes = [self.plane_coef[k] for k in ks]
         lines = [self.line_coef[k] for k in ks]
         if getattr(self, "lazy", False) and coords.is_cuda:
@@ -188,8 +188,9 @@ class TensorVMEncoding(VolumeEncoding):
                 self.flush_lazy()
         if self.use_shadow and coords.is_cuda:
             return vm_encode(coords, planes, lines, [p._lmb_shadow for p in planes], [l._lmb_shadow for l in lines],
-                             count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill)
-        return vm_encode(coords, planes, lines, count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill)
+                             count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill, tail=tail)
+        return vm_encode(coords, planes, lines, count=count, out_dtype=out_dtype, out_width=out_width, zero_fill=zero_fill,
+                         tail=tail)
 
     def fused_density_ok(self, xyzb: torch.Tensor) -> bool:
         from ....ops.vm import vm_density_supported
@@ -218,12 +219,13 @@ class TensorVMEncoding(VolumeEncoding):
         return vm_density(coords, planes, lines, None, None, weight, inner_relu, act, shift, count, route)
 
     def forward(self, xyzb: torch.Tensor, count=None, out_dtype=torch.float32, out_width: int = 0,
-                zero_fill: bool = True) -> torch.Tensor:
+                zero_fill: bool = True, tail=None) -> torch.Tensor:
         """``xyzb [N, 4]`` = block-local xyz in ``[-1, 1]`` + block index -> ``[N, sum(C) * n_levels]``
-        (``out_width`` asks for wider zero-padded rows, see :func:`landmarksystem_b200.ops.vm_encode`)."""
+        (``out_width`` asks for wider zero-padded rows and ``tail`` for the rays' directions behind the features, see
+        :func:`landmarksystem_b200.ops.vm_encode`)."""
         n_levels = len(self.reso_mode)
         if self.ndims == 1:
-            return self._lookup(xyzb, range(n_levels), count, out_dtype, out_width, zero_fill)
+            return self._lookup(xyzb, range(n_levels), count, out_dtype, out_width, zero_fill, tail)
         outs = []
         for i, (vec_id, (m0, m1)) in enumerate(zip(self.vector_mode, self.matrix_mode)):
             coords = torch.stack((xyzb[..., m0], xyzb[..., m1], xyzb[..., vec_id], xyzb[..., 3]), dim=-1)

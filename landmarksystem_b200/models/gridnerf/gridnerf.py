@@ -361,10 +361,10 @@ class GridNeRF(BaseNeRF):
             m.app_batch = m_dev
             if m._fused_app_stage_ok(coords):
                 from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_forward
-                from ...ops.select import put_dirs
 
-                feat = m.rgb_encoding(coords, count=m_dev, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False)
-                put_dirs(feat, 144, extra, None, m_dev)
+                # the lookup kernel writes the directions behind the features: rows leave it complete
+                feat = m.rgb_encoding(coords, count=m_dev, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False,
+                                      tail=(extra.contiguous().float(), None, 1, 144))
                 return rgb_decoder_forward(m.rgb_decoder, None, feat, m_dev)
             k = int(m_dev.item())
             return F.pad(m._rgb(coords[:k], extra[:k].contiguous(), None), (0, 0, 0, coords.shape[0] - k))
@@ -413,13 +413,13 @@ class GridNeRF(BaseNeRF):
         ``nonzero`` + gathers + ``index_put`` (benchmarks/nerf/gridnerf/gridnerf.py:846-871) without the
         host round trip, with static shapes."""
         from ...ops.fused_mlp import RGB_IN_WIDTH, rgb_decoder_forward
-        from ...ops.select import ScatterRows3, compact_rows, put_dirs
+        from ...ops.select import ScatterRows3, compact_rows
 
         idx, coords, count = compact_rows(app_mask, xyzb)
         self.app_batch = count
         # the colour head reads only the feature and direction columns of the first `count` rows
-        feat = self.rgb_encoding(coords, count=count, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False)
-        put_dirs(feat, 144, dirs, idx, count, samples_per_ray)
+        feat = self.rgb_encoding(coords, count=count, out_dtype=torch.bfloat16, out_width=RGB_IN_WIDTH, zero_fill=False,
+                                 tail=(dirs.contiguous().float(), idx, samples_per_ray, 144))
         vals = rgb_decoder_forward(self.rgb_decoder, None, feat, count)
         return ScatterRows3.apply(vals, idx, coords, count, xyzb.shape[0])
 

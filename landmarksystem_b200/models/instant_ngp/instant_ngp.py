@@ -91,6 +91,7 @@ class InstantNGP(BaseNeRF):
         if config.render_step_size is None:
             config.render_step_size = float(((self.aabb[1] - self.aabb[0]) ** 2).sum().sqrt()) / 1000
         self.step = 0
+        self._aabb_host = [float(v) for v in self.aabb.reshape(-1).tolist()]
         self.init_field_components()
         self.init_sampler()
         self.init_renderer()
@@ -141,6 +142,18 @@ class InstantNGP(BaseNeRF):
             local = local * mine[:, None]
         return torch.cat((local, block[:, None]), -1), inside
 
+    def _kernel_glue(self, rays) -> bool:
+        """The per-sample glue runs as kernels when both heads are on the fused MLP path and no cross-rank sum sits
+        between the density head and the colour head (spatial-block training sums the two across ranks there)."""
+        c = self.config
+        if not rays.is_cuda or (c.get("branch_parallel", False) and c.get("is_train", False)):
+            return False
+        if not (getattr(self.mlp_base_mlp, "use_fused", False) and getattr(self.mlp_head, "use_fused", False)):
+            return False
+        from ...ops import native
+
+        return native.available() and self.geo_feat_dim + c.appearance_embedding_dim <= 48
+
     def _mp_sum(self, t):
         c = self.config
         if c.get("branch_parallel", False) and c.get("is_train", False):
@@ -184,7 +197,30 @@ class InstantNGP(BaseNeRF):
         z_vals = 0.5 * (ts + te)
         sigma = torch.zeros(R * S, device=rays.device)
         rgb = torch.zeros(R * S, 3, device=rays.device)
-        if idx.numel() > 0:
+        if idx.numel() > 0 and self._kernel_glue(rays):
+            # kernel path: positions -> hash-grid coordinates in one launch; sigma and the colour head's bf16 input rows
+            # (SH | geometry | appearance) in one launch from the density head's output; one backward launch for both
+            from ...ops import ngp_field
+
+            full = idx.numel() == R * S
+            kidx = None if full else idx
+            o32, d32 = o.contiguous().float(), dvec.contiguous().float()
+            xyzb, inside = ngp_field.sample_positions(kidx, S, o32, d32, z_vals.reshape(-1).contiguous().float(), self.aabb,
+                                                      self._aabb_host, int(self.plane_division[0]), int(self.plane_division[1]))
+            h = self.mlp_base_mlp(self.mlp_base_grid(xyzb)).float()
+            per_ray = None
+            if self.training:
+                cam = rays[:, 6] if rays.shape[1] > 6 else torch.zeros(R, device=rays.device)
+                per_ray = self.embedding_appearance(cam.long().clamp(0, c.appearance_embedding_size - 1))
+            width = (16 + self.geo_feat_dim + c.appearance_embedding_dim + 15) // 16 * 16
+            rows, sig = ngp_field.head_rows(kidx, S, d32, h, inside, per_ray, c.appearance_embedding_dim, width)
+            color = self.mlp_head(rows).float()
+            if full:
+                sigma, rgb = sig, color
+            else:
+                sigma = sigma.index_put((idx,), sig)
+                rgb = rgb.index_put((idx,), color)
+        elif idx.numel() > 0:
             # positions and directions of the valid samples only (no packed [R, S, 13] sample block)
             ray = idx // S
             dirs = dvec[ray]

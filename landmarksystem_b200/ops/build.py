@@ -104,6 +104,44 @@ def build_all(verbose: bool = False, force: bool = False) -> Path:
     return lib
 
 
+def resource_digest() -> str:
+    """Markdown table of what ptxas reported for every kernel of the last build: registers, shared memory, stack frame
+    and spill bytes (the compiler's own ``-Xptxas -v`` lines, nothing is disassembled)."""
+    import re
+
+    rows = []
+    for log in sorted(OUT.glob("*.ptxas.log")):
+        name = None
+        stack = spill_st = spill_ld = 0
+        for line in log.read_text().splitlines():
+            m = re.search(r"Compiling entry function '([^']+)'", line)
+            if m:
+                name = m.group(1)
+                continue
+            m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if m:
+                stack, spill_st, spill_ld = (int(v) for v in m.groups())
+                continue
+            m = re.search(r"Used (\d+) registers(.*)", line)
+            if m and name:
+                smem = re.search(r"(\d+) bytes smem", m.group(2))
+                rows.append((log.name.replace(".ptxas.log", ".cu"), name, int(m.group(1)), int(smem.group(1)) if smem else 0,
+                             stack, spill_st, spill_ld))
+                name = None
+    try:
+        res = subprocess.run(["c++filt"], input="\n".join(r[1] for r in rows), capture_output=True, text=True)
+        pretty = res.stdout.splitlines() if res.returncode == 0 else [r[1] for r in rows]
+    except OSError:
+        pretty = [r[1] for r in rows]
+    out = ["| file | kernel | registers | static smem (B) | stack (B) | spill st / ld (B) |", "|---|---|---|---|---|---|"]
+    for (src, _, regs, smem, stack, st, ld), nice in zip(rows, pretty):
+        nice = re.sub(r"\(.*", "", nice).replace("lmb::", "").replace("void ", "")
+        out.append(f"| {src} | `{nice}` | {regs} | {smem} | {stack} | {st} / {ld} |")
+    return "\n".join(out)
+
+
 if __name__ == "__main__":
     build_all(verbose=True, force="--force" in sys.argv)
     print(library_path())
+    if "--digest" in sys.argv:
+        print(resource_digest())

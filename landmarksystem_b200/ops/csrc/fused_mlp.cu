@@ -116,8 +116,13 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
       if (spec.pe_stage && l == 0) {
         // f = first 27 accumulator columns; expand to the 150-wide decoder input, in place
         float f[32];
-        tc05::tmem_ld16(tmem_lane, f);
-        tc05::tmem_ld16(tmem_lane + 16, f + 16);
+        {
+          uint32_t r[32];
+          tc05::tmem_ld32_nowait(tmem_lane, r);
+          tc05::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+        }
         float x[160];
 #pragma unroll
         for (int i = 0; i < 27; ++i) {
@@ -142,9 +147,9 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
 #pragma unroll
         for (int c = 0; c < 20; ++c) store_chunk(act, c, row, x + 8 * c);
       } else {
-        for (int n0 = 0; n0 < N; n0 += 16) {
-          float v[16];
-          tc05::tmem_ld16(tmem_lane + n0, v);
+        // Accumulator columns come out of tensor memory 64 at a time (two 32-column loads in flight, one wait): the
+        // loads' latencies overlap, which is what bounds this kernel (one thread walks a whole row of the tile).
+        auto finish16 = [&](float* v, int n0) {
           if (bias) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] += bias[n0 + i];
@@ -179,6 +184,25 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
             for (int i = 0; i < 16; ++i)
               if (n0 + i < spec.out_dim) o[n0 + i] = v[i];
           }
+        };
+        int n0 = 0;
+        for (; n0 + 64 <= N; n0 += 64) {
+          uint32_t r[64];
+          tc05::tmem_ld32_nowait(tmem_lane + n0, r);
+          tc05::tmem_ld32_nowait(tmem_lane + n0 + 32, r + 32);
+          tc05::tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[16 * q + i]);
+            finish16(v, n0 + 16 * q);
+          }
+        }
+        for (; n0 < N; n0 += 16) {
+          float v[16];
+          tc05::tmem_ld16(tmem_lane + n0, v);
+          finish16(v, n0);
         }
       }
       // TMEM reads and shared-memory writes of this slot are complete before the next MMA / TMA

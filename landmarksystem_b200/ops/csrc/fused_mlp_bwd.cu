@@ -260,13 +260,13 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
 
     if (row == 0) issue_fwd(tmem + kColWork, aA, aW1, 160, 128);
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 16) {
-      float v[16];
-      tc05::tmem_ld16(tlane + kColWork + n0, v);
+    for (int n0 = 0; n0 < 128; n0 += 64) {                       // 64 accumulator columns per wait: load latencies overlap
+      float v[64];
+      tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i] + b1[n0 + i], 0.f);
-      store_chunk(bufH1, n0 >> 3, row, v);
-      store_chunk(bufH1, (n0 >> 3) + 1, row, v + 8);
+      for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i] + b1[n0 + i], 0.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) store_chunk(bufH1, (n0 >> 3) + c, row, v + 8 * c);
     }
     {
       float ones[8];
@@ -279,13 +279,13 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
 
     if (row == 0) issue_fwd(tmem + kColWork, aH1, aW2, 128, 128);
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 16) {
-      float v[16];
-      tc05::tmem_ld16(tlane + kColWork + n0, v);
+    for (int n0 = 0; n0 < 128; n0 += 64) {
+      float v[64];
+      tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i] + b2[n0 + i], 0.f);
-      store_chunk(bufHZ, n0 >> 3, row, v);
-      store_chunk(bufHZ, (n0 >> 3) + 1, row, v + 8);
+      for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i] + b2[n0 + i], 0.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) store_chunk(bufHZ, (n0 >> 3) + c, row, v + 8 * c);
     }
     LMB_EPILOGUE_DONE();
 
@@ -318,14 +318,18 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       issue_dgrad(tmem + kColWork, aS, aW3, 16, 0, 128);          // dh2 = dz3 W3
     }
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 16) {                         // dz2 = dh2 * [h2 > 0], in place of h2
-      float v[16], h[16];
-      tc05::tmem_ld16(tlane + kColWork + n0, v);
-      load_chunk2(bufHZ, n0 >> 3, row, h);
+    for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz2 = dh2 * [h2 > 0], in place of h2
+      float v[64];
+      tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = h[i] > 0.f ? v[i] : 0.f;
-      store_chunk(bufHZ, n0 >> 3, row, v);
-      store_chunk(bufHZ, (n0 >> 3) + 1, row, v + 8);
+      for (int q = 0; q < 4; ++q) {
+        float h[16];
+        load_chunk2(bufHZ, (n0 >> 3) + 2 * q, row, h);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[16 * q + i] = h[i] > 0.f ? v[16 * q + i] : 0.f;
+        store_chunk(bufHZ, (n0 >> 3) + 2 * q, row, v + 16 * q);
+        store_chunk(bufHZ, (n0 >> 3) + 2 * q + 1, row, v + 16 * q + 8);
+      }
     }
     LMB_EPILOGUE_DONE();
 
@@ -335,14 +339,18 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       issue_dgrad(tmem + kColWork, aHZ, aW2, 128, 0, 128);        // dh1 = dz2 W2
     }
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 16) {                         // dz1 = dh1 * [h1 > 0] -> HZ
-      float v[16], h[16];
-      tc05::tmem_ld16(tlane + kColWork + n0, v);
-      load_chunk2(bufH1, n0 >> 3, row, h);
+    for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz1 = dh1 * [h1 > 0] -> HZ
+      float v[64];
+      tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = h[i] > 0.f ? v[i] : 0.f;
-      store_chunk(bufHZ, n0 >> 3, row, v);
-      store_chunk(bufHZ, (n0 >> 3) + 1, row, v + 8);
+      for (int q = 0; q < 4; ++q) {
+        float h[16];
+        load_chunk2(bufH1, (n0 >> 3) + 2 * q, row, h);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[16 * q + i] = h[i] > 0.f ? v[16 * q + i] : 0.f;
+        store_chunk(bufHZ, (n0 >> 3) + 2 * q, row, v + 16 * q);
+        store_chunk(bufHZ, (n0 >> 3) + 2 * q + 1, row, v + 16 * q + 8);
+      }
     }
     LMB_EPILOGUE_DONE();
 
@@ -363,15 +371,13 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
   #pragma unroll
       for (int i = 0; i < 27; ++i) df[i] = 0.f;
       {
-        float v[16];
-        tc05::tmem_ld16(tlane + kColWork + 0, v);   pe_backward_cols<0>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 16, v);  pe_backward_cols<16>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 32, v);  pe_backward_cols<32>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 48, v);  pe_backward_cols<48>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 64, v);  pe_backward_cols<64>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 80, v);  pe_backward_cols<80>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 96, v);  pe_backward_cols<96>(v, f, df);
-        tc05::tmem_ld16(tlane + kColWork + 112, v); pe_backward_cols<112>(v, f, df);
+        float v[64];
+        tc05::tmem_ld64(tlane + kColWork + 0, v);
+        pe_backward_cols<0>(v, f, df);   pe_backward_cols<16>(v + 16, f, df);
+        pe_backward_cols<32>(v + 32, f, df);  pe_backward_cols<48>(v + 48, f, df);
+        tc05::tmem_ld64(tlane + kColWork + 64, v);
+        pe_backward_cols<64>(v, f, df);  pe_backward_cols<80>(v + 16, f, df);
+        pe_backward_cols<96>(v + 32, f, df);  pe_backward_cols<112>(v + 48, f, df);
       }
       LMB_EPILOGUE_DONE();
       if (row == 0) issue_dgrad(tmem + kColWork, aHZ, aW1, 128, 16, 16);   // d(x1)[:, 128:144]

@@ -9,24 +9,56 @@
 namespace lmb {
 
 // idx[pos] = i and coords_out[pos] = xyzb[i] for every i with mask[i] != 0; *count ends as the number of
-// selected rows.  Positions are handed out per warp (one atomic per warp), so rows of one warp stay
-// adjacent and in order.
+// selected rows.  A block of 256 threads takes 1024 consecutive elements (four per thread, one 32-bit mask load),
+// ranks its selected rows with a block-wide scan and reserves its output range with ONE atomic: a launch over 2^25
+// samples issues 2^15 atomics on the counter instead of one per warp (2^20), which is what bounded the kernel.
+// Rows of one block stay adjacent and in order.
+constexpr int kCompactPerThread = 4;
+
 __global__ void __launch_bounds__(256)
 compact_kernel(const unsigned char* __restrict__ mask, long long n, const float4* __restrict__ xyzb, int* __restrict__ idx,
-               float4* __restrict__ coords_out, int* __restrict__ count) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int lane = threadIdx.x & 31;
-  const bool sel = i < n && mask[i] != 0;
-  const unsigned won = __ballot_sync(0xffffffffu, sel);
-  if (won == 0) return;
-  const int leader = __ffs(won) - 1;
-  int base = 0;
-  if (lane == leader) base = atomicAdd(count, __popc(won));
-  base = __shfl_sync(0xffffffffu, base, leader);
-  if (sel) {
-    const int pos = base + __popc(won & ((1u << lane) - 1u));
-    idx[pos] = (int)i;
-    coords_out[pos] = xyzb[i];
+               float4* __restrict__ coords_out, int* __restrict__ count, int mask_aligned) {
+  __shared__ int warp_sum[8];
+  __shared__ int block_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * kCompactPerThread;
+  unsigned sel = 0;
+  if (mask_aligned && i0 + kCompactPerThread <= n) {
+    const uchar4 m = *reinterpret_cast<const uchar4*>(mask + i0);
+    sel = (m.x != 0 ? 1u : 0u) | (m.y != 0 ? 2u : 0u) | (m.z != 0 ? 4u : 0u) | (m.w != 0 ? 8u : 0u);
+  } else {
+#pragma unroll
+    for (int k = 0; k < kCompactPerThread; ++k)
+      if (i0 + k < n && mask[i0 + k] != 0) sel |= 1u << k;
+  }
+  const int mine = __popc(sel);
+  int incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += v;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int t = warp_sum[w];
+      warp_sum[w] = total;
+      total += t;
+    }
+    block_base = total > 0 ? atomicAdd(count, total) : 0;
+  }
+  __syncthreads();
+  int pos = block_base + warp_sum[warp] + incl - mine;
+#pragma unroll
+  for (int k = 0; k < kCompactPerThread; ++k) {
+    if (sel & (1u << k)) {
+      idx[pos] = (int)(i0 + k);
+      coords_out[pos] = xyzb[i0 + k];
+      ++pos;
+    }
   }
 }
 
@@ -86,7 +118,9 @@ LMB_API int lmb_compact_rows(const unsigned char* mask, long long n, const float
                              cudaStream_t stream) {
   LMB_CUDA_TRY(cudaMemsetAsync(count, 0, sizeof(int), stream));
   if (n <= 0) return 0;
-  compact_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(mask, n, (const float4*)xyzb, idx, (float4*)coords_out, count);
+  const int aligned = (reinterpret_cast<uintptr_t>(mask) & 3u) == 0 ? 1 : 0;
+  compact_kernel<<<ceil_div(n, 256 * kCompactPerThread), 256, 0, stream>>>(mask, n, (const float4*)xyzb, idx, (float4*)coords_out,
+                                                                           count, aligned);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -43,10 +43,20 @@ __device__ __forceinline__ Corner2 taps(float u, int size) {
   return c;
 }
 
+// Optional 16-column tail of every output row: the viewing direction of the row's ray (3 values) followed by 13 zeros,
+// written by the row's first thread as two 16-byte stores.  The colour head reads the direction from there, so the
+// row leaves this kernel complete and no separate pass has to patch three 2-byte values into every 320-byte row.
+struct DirTail {
+  const float* dirs;   // [rays, 3]; null: no tail
+  const int* idx;      // row -> flat sample index (ray = idx / samples_per_ray); null: row n reads dirs[n]
+  int samples_per_ray;
+  int col;             // first tail column, a multiple of 8
+};
+
 template <typename T, typename OutT>
 __global__ void __launch_bounds__(256)
 vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ count_ptr, long long max_n,
-                     VMLevels lv, OutT* __restrict__ out, int out_stride) {
+                     VMLevels lv, OutT* __restrict__ out, int out_stride, DirTail tail) {
   const int CH = lv.C >> 3;
   const long long n_valid = resolve_count(count_ptr, max_n);
   // grid-stride: the grid is capped, so a launch sized for a worst-case row capacity costs nothing when
@@ -57,6 +67,15 @@ vm_encode_fwd_kernel(const float4* __restrict__ coords, const int* __restrict__ 
   int ch = (int)(tid - n * CH);
   float4 q = __ldg(coords + n);
   int b = (int)q.w;
+  if (tail.dirs != nullptr && ch == 0) {
+    const float* d = tail.dirs + (tail.idx != nullptr ? (long long)(tail.idx[n] / tail.samples_per_ray) : n) * 3;
+    F8 a, z;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a.v[i] = 0.f; z.v[i] = 0.f; }
+    a.v[0] = d[0]; a.v[1] = d[1]; a.v[2] = d[2];
+    store8(out + n * out_stride + tail.col, a);
+    store8(out + n * out_stride + tail.col + 8, z);
+  }
   if (b < 0 || b >= lv.B) {
     F8 z;
 #pragma unroll
@@ -450,15 +469,21 @@ static int capped_grid(long long work_items, int threads) {
 }
 
 // param_dtype / io_dtype: 0 = fp32, 1 = bf16.
+// tail_dirs (may be null): see DirTail; tail_col must be a multiple of 8 with tail_col + 16 <= the row stride.
 LMB_API int lmb_vm_encode_fwd(const float* coords, const int* count_ptr, long long max_n, const VMLevels* levels,
-                              int param_dtype, void* out, int out_dtype, int out_stride, cudaStream_t stream) {
+                              int param_dtype, void* out, int out_dtype, int out_stride, const float* tail_dirs,
+                              const int* tail_idx, int tail_samples_per_ray, int tail_col, cudaStream_t stream) {
   if (max_n <= 0) return 0;
   if (levels->C % 8 != 0 || levels->L < 1 || levels->L > kMaxLevels) return (int)cudaErrorInvalidValue;
   const int CH = levels->C / 8;
   const int threads = 256;
   const int blocks = capped_grid(max_n * CH, threads);
   const float4* c4 = reinterpret_cast<const float4*>(coords);
-#define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out, out_stride > 0 ? out_stride : levels->L * levels->C)
+  const int stride = out_stride > 0 ? out_stride : levels->L * levels->C;
+  const DirTail tail{tail_dirs, tail_idx, tail_samples_per_ray > 0 ? tail_samples_per_ray : 1, tail_col};
+  if (tail_dirs != nullptr && (tail_col % 8 != 0 || tail_col < levels->L * levels->C || tail_col + 16 > stride))
+    return (int)cudaErrorInvalidValue;
+#define LAUNCH(T, O) vm_encode_fwd_kernel<T, O><<<blocks, threads, 0, stream>>>(c4, count_ptr, max_n, *levels, (O*)out, stride, tail)
   if (param_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
   else if (param_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
   else if (param_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);

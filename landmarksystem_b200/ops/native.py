@@ -62,7 +62,7 @@ def _declare(L: ctypes.CDLL) -> None:
 
 P = c_void_p
 _SIGNATURES = {
-    "lmb_vm_encode_fwd": [P, P, c_longlong, POINTER(VMLevels), c_int, P, c_int, c_int, P],
+    "lmb_vm_encode_fwd": [P, P, c_longlong, POINTER(VMLevels), c_int, P, c_int, c_int, P, P, c_int, c_int, P],
     "lmb_vm_encode_bwd": [P, P, c_longlong, POINTER(VMLevels), c_int, P, c_int, c_int, P],
     "lmb_weights_fwd": [P, P, c_int, c_int, P, P, P],
     "lmb_weights_bwd": [P, P, P, P, c_int, c_int, P, P],

@@ -148,9 +148,14 @@ class OccGridEstimator(torch.nn.Module):
             return
         res3 = self.resolution ** 3
         dev = self.occs.device
+        on_gpu = self.occs.is_cuda and native.available()
+        if on_gpu:
+            from . import ngp_field
+
+            self._refresh_count = getattr(self, "_refresh_count", 0) + 1
         for level in range(self.levels):
             if step < warmup_steps:
-                idx = torch.arange(res3, device=dev)
+                idx = None if on_gpu else torch.arange(res3, device=dev)
             else:
                 m = res3 // 4
                 uniform = torch.randint(res3, (m,), device=dev)
@@ -158,8 +163,23 @@ class OccGridEstimator(torch.nn.Module):
                 if occupied.numel() > m:
                     occupied = occupied[torch.randint(occupied.numel(), (m,), device=dev)]
                 idx = torch.cat((uniform, occupied))
-            occ = occ_eval_fn(self._cell_centers(level, idx)).reshape(-1).float()
             view = self.occs[level * res3:(level + 1) * res3]
+            if on_gpu:
+                # cell centres + decayed old value, the density query, then the two-pass maximum: three launches around
+                # the field evaluation instead of the index arithmetic, gather and scatter as tensor ops
+                seed = (step * 131 + level * 7919 + self._refresh_count * 104729) & 0x7FFFFFFF
+                xyz, decayed = ngp_field.occ_cells(idx, res3, self.resolution, self._roi_host, level, seed, True, view,
+                                                   ema_decay)
+                ngp_field.occ_update(idx, decayed, occ_eval_fn(xyz).reshape(-1), view)
+                continue
+            occ = occ_eval_fn(self._cell_centers(level, idx)).reshape(-1).float()
             view[idx] = torch.maximum(view[idx] * ema_decay, occ)
+        if on_gpu:
+            if getattr(self, "_sum_scratch", None) is None or self._sum_scratch.device != dev:
+                self._sum_scratch = torch.zeros(1, device=dev, dtype=torch.float64)
+            if not self.binaries.is_contiguous():
+                self.binaries = self.binaries.contiguous()
+            ngp_field.occ_binarise(self.occs, occ_thre, self.binaries.view(torch.uint8), self._sum_scratch)
+            return
         thre = min(float(self.occs.mean()), occ_thre)
         self.binaries = (self.occs > thre).view(self.binaries.shape)

@@ -96,7 +96,7 @@ class _VMEncode(torch.autograd.Function):
     (planes..., lines...) and optionally 2*L bf16 shadow tensors that the kernels read instead."""
 
     @staticmethod
-    def forward(ctx, coords, count, out_dtype, n_levels, out_width, zero_fill, *grids):
+    def forward(ctx, coords, count, out_dtype, n_levels, out_width, zero_fill, tail, *grids):
         masters = grids[: 2 * n_levels]
         shadows = grids[2 * n_levels:]
         read = shadows if shadows else masters
@@ -108,10 +108,12 @@ class _VMEncode(torch.autograd.Function):
         if zero_fill and (count is not None or width > n_levels * C):
             out.zero_()
         lv = _levels_struct(planes, lines)
+        t_dirs, t_idx, t_spr, t_col = tail if tail is not None else (None, None, 1, 0)
         native.check(
             native.lib().lmb_vm_encode_fwd(coords.data_ptr(), native.ptr(count), N, byref(lv),
                                            native.DTYPE_CODE[planes[0].dtype], out.data_ptr(),
-                                           native.DTYPE_CODE[out_dtype], width, native.stream_ptr()),
+                                           native.DTYPE_CODE[out_dtype], width, native.ptr(t_dirs), native.ptr(t_idx),
+                                           int(t_spr), int(t_col), native.stream_ptr()),
             "vm_encode_fwd")
         ctx.save_for_backward(coords, count, *read)
         ctx.n_levels = n_levels
@@ -145,28 +147,34 @@ class _VMEncode(torch.autograd.Function):
                                                native.DTYPE_CODE[dout.dtype], dout.shape[1], native.stream_ptr()),
                 "vm_encode_bwd")
         out_grads = [None if s else g for s, g in zip(sunk, grads)]
-        return (None, None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
+        return (None, None, None, None, None, None, None, *out_grads, *([None] * ctx.n_shadow))
 
 
 def vm_encode(coords: torch.Tensor, planes: List[torch.Tensor], lines: List[torch.Tensor],
               shadow_planes: Optional[List[torch.Tensor]] = None, shadow_lines: Optional[List[torch.Tensor]] = None,
               count: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32,
-              out_width: int = 0, zero_fill: bool = True) -> torch.Tensor:
+              out_width: int = 0, zero_fill: bool = True, tail=None) -> torch.Tensor:
     """Look up ``[N, L*C]`` features.  ``shadow_*`` (bf16 copies of the fp32 masters) are what the
     CUDA kernels read when given; gradients always flow to the fp32 masters.  ``out_width`` > L*C
     returns a wider, zero-padded row (room for columns a consumer kernel wants appended).  With
     ``zero_fill=False`` padding columns and rows past ``count`` are left uninitialised (for consumers
-    that never read them)."""
+    that never read them).  ``tail = (dirs [R, 3] fp32, idx int32 [N] or None, samples_per_ray, col)``: the kernel also
+    writes ``dirs[idx // samples_per_ray]`` (``dirs[row]`` without ``idx``) and 13 zeros into columns ``col .. col+15``."""
     if not coords.is_cuda:
         feat = vm_encode_reference(coords, planes, lines).to(out_dtype)
         if out_width > feat.shape[1]:
             feat = torch.nn.functional.pad(feat, (0, out_width - feat.shape[1]))
+        if tail is not None:
+            t_dirs, t_idx, t_spr, t_col = tail
+            rows = t_dirs if t_idx is None else t_dirs[(t_idx.long() // t_spr)]
+            feat[:, t_col:t_col + 16] = 0
+            feat[: rows.shape[0], t_col:t_col + 3] = rows[: feat.shape[0]].to(out_dtype)
         return feat
     coords = coords.contiguous().float()
     grids = list(planes) + list(lines)
     if shadow_planes is not None:
         grids += list(shadow_planes) + list(shadow_lines)
-    return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, zero_fill, *grids)
+    return _VMEncode.apply(coords, count, out_dtype, len(planes), out_width, zero_fill, tail, *grids)
 
 
 # -- fused density head: lookup + 1-wide linear (or channel sum) + activation -> sigma [N] ---------------------

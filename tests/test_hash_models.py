@@ -136,3 +136,32 @@ def test_volumetric_sampler_lean_output_matches_packed_samples():
     xyz = o2[:, None] + d2[:, None] * z[..., None]
     assert torch.allclose(samples.data[..., 9:12][valid], xyz[valid]) and torch.allclose(samples.data[..., 6:9][valid], d2[:, None].expand_as(xyz)[valid])
     assert torch.equal(samples.data[:, 0, 4], rays[:, 6])
+
+
+@pytest.mark.gpu
+def test_ngp_kernel_glue_equals_tensor_op_glue(tmp_path):
+    """One forward + backward of the Instant-NGP field with the per-sample glue as kernels and as tensor ops: same image,
+    same gradients (both run the same fused heads, so only summation order differs)."""
+    from landmarksystem_b200.models.instant_ngp.instant_ngp_trainer import NGPTrainer
+
+    cfg = BaseConfig.from_file(os.path.join(ROOT, "instant_ngp", "confs", "synthetic_tiny.py"),
+                               {"basedir": str(tmp_path), "device": "cuda", "n_iters": "1", "progress_refresh_rate": "1000",
+                                "runtime": "Kernel"})
+    trainer = NGPTrainer(cfg)
+    model = trainer.model.train()
+    rays, _ = trainer.data_mgr.get_rays(0)[:2]
+    results = []
+    for use_kernels in (True, False):
+        model._kernel_glue = (lambda r, keep=model.__class__._kernel_glue: keep(model, r)) if use_kernels else (lambda r: False)
+        torch.manual_seed(7)                                   # same stratified jitter in both passes
+        for p in model.parameters():
+            p.grad = None
+        out = model(rays)["rgb_map"]
+        out.square().sum().backward()
+        table = next(model.mlp_base_grid.parameters())
+        results.append((out.detach().clone(), table.grad.detach().clone().float(),
+                        model.embedding_appearance.weight.grad.detach().clone()))
+    (img_k, g_k, e_k), (img_t, g_t, e_t) = results
+    assert torch.allclose(img_k, img_t, atol=2e-3)
+    assert torch.allclose(g_k, g_t, atol=2e-3 * float(g_t.abs().max()) + 1e-7)
+    assert torch.allclose(e_k, e_t, atol=2e-2 * float(e_t.abs().max()) + 1e-7)

@@ -587,3 +587,45 @@ def test_adam_fused_with_plane_regularisers_matches_autograd_plus_adam(C, tv_dev
     torch.testing.assert_close(p.data, ref.data, rtol=1e-4, atol=2e-6)
     torch.testing.assert_close(p._lmb_shadow.float(), p.data, rtol=1e-2, atol=1e-3)
     assert p._lmb_pong.data_ptr() != p.data.data_ptr()
+
+
+@pytest.mark.parametrize("n", [1, 1023, 1024, 100003])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_compact_rows_selects_every_masked_row_once(n, offset):
+    """Mask compaction: the selected set, its count and the coordinates; rows of one 1024-element block stay in order.
+    ``offset`` makes the mask start at an address that is not a multiple of four (the scalar mask-load path)."""
+    from landmarksystem_b200.ops.select import compact_rows
+
+    g = torch.Generator().manual_seed(n + offset)
+    base = (torch.rand(n + offset, generator=g) < 0.3).to(DEV)
+    mask = base[offset:]
+    xyzb = torch.randn(n, 4, generator=g).to(DEV)
+    idx, coords, count = compact_rows(mask, xyzb)
+    k = int(count)
+    want = mask.nonzero(as_tuple=True)[0]
+    assert k == want.numel()
+    got = idx[:k].long()
+    assert torch.equal(got.sort().values, want)
+    assert torch.equal(coords[:k], xyzb[got])
+    same_block = (got[1:] // 1024) == (got[:-1] // 1024)
+    assert bool((got[1:][same_block] > got[:-1][same_block]).all())
+
+
+def test_vm_encode_writes_direction_tail():
+    """The lookup kernel appends the ray direction of every row (and zeros) behind the features: bf16 rows of the colour
+    head's width, with and without a row -> sample index, rows past the device-side count untouched."""
+    planes, lines, coords = _vm_case(C=16, L=1, N=1000)
+    cp, cl = [p.to(DEV) for p in planes], [l.to(DEV) for l in lines]
+    S, R = 8, 125
+    dirs = torch.randn(R, 3, device=DEV)
+    idx = torch.randperm(R * S, device=DEV)[:1000].to(torch.int32)
+    count = torch.tensor([700], device=DEV, dtype=torch.int32)
+    width, col = 80, 48
+    plain = vm_encode(coords.to(DEV), cp, cl, count=count, out_dtype=torch.bfloat16, out_width=width)
+    for use_idx in (True, False):
+        tail = (dirs if use_idx else dirs[idx.long() // S].contiguous(), idx if use_idx else None, S if use_idx else 1, col)
+        out = vm_encode(coords.to(DEV), cp, cl, count=count, out_dtype=torch.bfloat16, out_width=width, tail=tail)
+        assert torch.equal(out[:700, :col], plain[:700, :col])
+        assert torch.equal(out[:700, col:col + 3], dirs[idx[:700].long() // S].to(torch.bfloat16))
+        assert out[:700, col + 3:col + 16].abs().sum() == 0
+        assert out[700:].abs().sum() == 0                  # zero_fill default: rows past the count stay zero
