@@ -426,6 +426,14 @@ def _run(args, ref_root, bench):
             except Exception as exc:
                 also.append({"metric": "3DGS 1080p render FPS", "impl": "restatement",
                              "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]})
+            # Instant-NGP likewise: tiny-cuda-nn and nerfacc are not installed, the arm times the PyTorch restatement
+            try:
+                gc.collect()
+                torch.cuda.empty_cache()
+                also.append(bench.train_rate_ngp_restatement())
+            except Exception as exc:
+                also.append({"metric": "InstantNGP training rays/s", "impl": "restatement",
+                             "error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]})
         watchdog.cancel()
     emit()
     if dist.is_initialized():

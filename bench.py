@@ -385,6 +385,42 @@ def train_rate_ngp(rays_per_step: int = 1 << 18, steps: int = 8, warmup: int = 4
             "loss_finite": bool(torch.isfinite(loss))}
 
 
+def train_rate_ngp_restatement(rays_per_step: int = 1 << 18, steps: int = 3, warmup: int = 1):
+    """The Instant-NGP figure for the PyTorch restatement of the training step (``baseline/ngp_restatement.py``; the
+    reference's own Instant-NGP needs tiny-cuda-nn and nerfacc, which are not in the image): same field shape, same ray
+    distribution, same step size and sample cap as ``train_rate_ngp``."""
+    import torch
+
+    from baseline.ngp_restatement import Trainer
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    trainer = Trainer([[-1.0, -1.0, -1.0], [1.0, 1.0, 1.0]], step=0.02, max_samples=160, device=dev, grid_res=128,
+                      levels=16, features=2, log2_size=22, base_res=16, max_res=8192, n_cameras=8, app_dim=32)
+    g = torch.Generator(device=dev).manual_seed(0)
+    ang = torch.rand(rays_per_step, device=dev, generator=g) * 2 * math.pi
+    origin = torch.stack((3.0 * torch.cos(ang), 3.0 * torch.sin(ang), torch.rand(rays_per_step, device=dev, generator=g) - 0.5), -1)
+    aim = torch.rand(rays_per_step, 3, device=dev, generator=g) * 1.6 - 0.8
+    rays = torch.cat((origin, torch.nn.functional.normalize(aim - origin, dim=-1)), -1)
+    rgbs = torch.rand(rays_per_step, 3, device=dev, generator=g)
+    cams = torch.zeros(rays_per_step, device=dev)
+    times, loss = [], float("nan")
+    for k in range(warmup + steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        loss = trainer.train_step(rays, rgbs, cams)
+        end.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(start.elapsed_time(end))
+    ms = statistics.median(times)
+    return {"metric": "InstantNGP training rays/s (1 GPU, 2^18 rays per GPU and step, 16 x 2^22 hash grid)",
+            "impl": "restatement (PyTorch operators; tiny-cuda-nn and nerfacc are not in the image)",
+            "value": rays_per_step / (ms / 1e3), "ms_per_step": ms, "steps": steps, "n_gpus": 1,
+            "ray_chunk": trainer.chunk, "loss_finite": bool(math.isfinite(loss))}
+
+
 def stream_fps_gridnerf(frames: int = int(os.environ.get("LMB_STREAM_FRAMES", "200")), blocks: int = 8, plane: int = 1024):
     """Dynamic loading figure (fifth benchmark shape at reduced block size): a scene of ``blocks x blocks`` spatial blocks
     with ``plane``^2 texels x (16 + 48) channels each, bf16 on pinned host memory, rendered through ``init_inference``
@@ -784,7 +820,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp", "3dgs-restatement", "stream"],
+    ap.add_argument("--only", type=str, default=None, choices=["3dgs", "ngp", "3dgs-restatement", "ngp-restatement", "stream"],
                     help="run one secondary single-GPU benchmark alone and print its JSON (--profile adds the PyTorch "
                          "profiler's kernel table of two more steps on stderr)")
     ap.add_argument("--profile", action="store_true")
@@ -797,7 +833,7 @@ def main():
 
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         fn = {"3dgs": render_fps_3dgs, "ngp": train_rate_ngp, "3dgs-restatement": render_fps_3dgs_restatement,
-              "stream": stream_fps_gridnerf}[args.only]
+              "ngp-restatement": train_rate_ngp_restatement, "stream": stream_fps_gridnerf}[args.only]
         out = train_rate_ngp(profile=True) if (args.profile and args.only == "ngp") else fn()
         if int(os.environ.get("RANK", 0)) == 0:
             print(json.dumps(out))

@@ -60,8 +60,26 @@ class HashEncoding(VolumeEncoding):
     def get_out_dim(self) -> int:
         return self.meta.out_dim
 
+    def enable_table_shadow(self) -> None:
+        """Give every table a persistent fp32 gradient accumulator and a bf16 copy for the lookup kernel to read (both
+        maintained by the fused Adam kernel)."""
+        from ....ops import FusedAdam
+
+        for table in self.tables():
+            if table.params.is_cuda and getattr(table.params, "_lmb_shadow", None) is None:
+                FusedAdam.attach_sink(table.params, shadow=True)
+                table.params._lmb_shadow_version = table.params._version
+
     def _encode(self, xyz: torch.Tensor, table: _Table) -> torch.Tensor:
-        return hashgrid_encode(xyz, table.params.view(-1, self.features_per_level), self.meta)
+        p, F = table.params, self.features_per_level
+        shadow, sink = getattr(p, "_lmb_shadow", None), getattr(p, "_lmb_grad_sink", None)
+        if shadow is not None and xyz.is_cuda:
+            if p._version != getattr(p, "_lmb_shadow_version", None):      # the master was written outside the optimiser
+                shadow.copy_(p.detach())                                    # kernel (a checkpoint load): refresh the copy
+                p._lmb_shadow_version = p._version
+            return hashgrid_encode(xyz, p.view(-1, F), self.meta, shadow=shadow.view(-1, F),
+                                   sink=None if sink is None else sink.view(-1, F))
+        return hashgrid_encode(xyz, p.view(-1, F), self.meta)
 
     def forward(self, xyz: torch.Tensor) -> torch.Tensor:
         """``xyz [N, 3]`` in ``[0, 1]`` or ``[N, 4]`` with the block index in the last column."""

@@ -16,6 +16,7 @@
 // (features -> 27), whose output f together with the view direction d is expanded in registers to
 // [f, d, sin(f 2^k), cos(f 2^k), sin(d 2^k), cos(d 2^k)] (k = 0, 1) = 150 inputs of the 3-layer decoder.
 #include "fused_mlp.cuh"
+#include <cstdlib>
 
 namespace lmb {
 
@@ -34,6 +35,13 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
   unsigned char* act_base = smem + ((spec.blob_bytes + 1023) & ~1023);
   __shared__ __align__(8) uint64_t bar_w, bar_in[kSlots], bar_mma[kSlots];
   __shared__ uint32_t tmem_base_sh;
+  // per-layer tables: indexed with the run-time layer number, so a copy in shared memory (a kernel parameter indexed
+  // dynamically is spilled to local memory, and with the L1 carved down to shared memory every such read goes to L2)
+  __shared__ int sK[kMaxLayers], sN[kMaxLayers], sAct[kMaxLayers], sWoff[kMaxLayers], sBoff[kMaxLayers];
+  if (threadIdx.x < kMaxLayers) {
+    sK[threadIdx.x] = spec.K[threadIdx.x]; sN[threadIdx.x] = spec.N[threadIdx.x]; sAct[threadIdx.x] = spec.act[threadIdx.x];
+    sWoff[threadIdx.x] = spec.w_off[threadIdx.x]; sBoff[threadIdx.x] = spec.b_off[threadIdx.x];
+  }
 
   const int tid = threadIdx.x;
   const int slot = tid / kSlotThreads;
@@ -64,14 +72,22 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
   const long long n_rows = resolve_count(count_ptr, max_rows);
   const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
   const int in_chunks = spec.in_width >> 3;
-  const uint32_t in_bytes = (uint32_t)(in_chunks * kTileRows * 16);
+  const bool whole_rows = inputs.n128 + inputs.n64 > 0;
+  const uint32_t in_bytes = whole_rows ? (uint32_t)(inputs.n128 * kTileRows * 128 + inputs.n64 * kTileRows * 64)
+                                       : (uint32_t)(in_chunks * kTileRows * 16);
   const int bar_id = 1 + slot;
   uint32_t ph_in = 0, ph_mma = 0;
 
   for (long long tile = (long long)blockIdx.x * kSlots + slot; ok && tile < n_tiles; tile += (long long)gridDim.x * kSlots) {
     const long long row0 = tile * kTileRows;
     // ---- input tile: one TMA box [8 elems, 1 chunk, 128 rows] per 16-byte column chunk -------------
-    if (row == 0) {
+    if (row == 0 && whole_rows) {
+      tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
+      for (int a = 0; a < inputs.n128; ++a)
+        tc05::tma_load_2d(act + (size_t)a * kTileRows * 128, &inputs.map[0], a * 64, (int)row0, &bar_in[slot]);
+      if (inputs.n64)
+        tc05::tma_load_2d(act + (size_t)inputs.n128 * kTileRows * 128, &inputs.map[1], inputs.n128 * 64, (int)row0, &bar_in[slot]);
+    } else if (row == 0) {
       tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
       int src = 0;
       for (int c = 0; c < in_chunks; ++c) {
@@ -85,21 +101,35 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
     if (!tc05::bar_and(bar_id, kSlotThreads, got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
 
     float dir[3] = {0.f, 0.f, 0.f};
-    if (spec.pe_stage) {
+    if (spec.pe_stage && whole_rows) {
+      // the tile sits in the swizzled layout: take the three direction values from the row in global memory instead
+      if (row0 + row < n_rows) {
+        const __nv_bfloat16* dp = inputs.x0 + (row0 + row) * (long long)spec.in_width + spec.dir_col;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) dir[i] = __bfloat162float(dp[i]);
+      }
+    } else if (spec.pe_stage) {
 #pragma unroll
       for (int i = 0; i < 3; ++i) dir[i] = load_elem(act, spec.dir_col + i, row);
     }
 
     for (int l = 0; l < spec.n_layers; ++l) {
-      const int K = spec.K[l], N = spec.N[l];
+      const int K = sK[l], N = sN[l];
       // ---- MMA: D[128 x N] = A[128 x K] * W_l^T ----------------------------------------------------
       if (row == 0) {
         tc05::fence_after_sync();
         const uint32_t a_addr = tc05::smem_u32(act);
-        const uint32_t b_addr = tc05::smem_u32(wsm + spec.w_off[l]);
+        const uint32_t b_addr = tc05::smem_u32(wsm + sWoff[l]);
         const uint32_t idesc = tc05::idesc_bf16(N, false, false);
         for (int k = 0; k < K; k += 16) {
-          const uint64_t da = tc05::smem_desc(a_addr + (uint32_t)(k >> 3) * (kTileRows * 16), kTileRows * 16, 128);
+          uint64_t da;
+          if (l == 0 && whole_rows) {
+            const int k128 = inputs.n128 * 64;
+            da = k < k128 ? tc05::smem_desc_swizzled(a_addr + (uint32_t)(k >> 6) * (kTileRows * 128) + (uint32_t)(k & 63) * 2, 1024, 2)
+                          : tc05::smem_desc_swizzled(a_addr + (uint32_t)inputs.n128 * (kTileRows * 128) + (uint32_t)(k - k128) * 2, 512, 4);
+          } else {
+            da = tc05::smem_desc(a_addr + (uint32_t)(k >> 3) * (kTileRows * 16), kTileRows * 16, 128);
+          }
           const uint64_t db = tc05::smem_desc(b_addr + (uint32_t)(k >> 3) * (uint32_t)(N * 16), (uint32_t)(N * 16), 128);
           tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
         }
@@ -111,7 +141,8 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
       tc05::fence_after_sync();
 
       // ---- epilogue -------------------------------------------------------------------------------
-      const float* bias = spec.b_off[l] >= 0 ? reinterpret_cast<const float*>(wsm + spec.b_off[l]) : nullptr;
+      const float* bias = sBoff[l] >= 0 ? reinterpret_cast<const float*>(wsm + sBoff[l]) : nullptr;
+      const int act_l = sAct[l];
       const bool last = (l == spec.n_layers - 1);
       if (spec.pe_stage && l == 0) {
         // f = first 27 accumulator columns; expand to the 150-wide decoder input, in place
@@ -150,13 +181,22 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
         // Accumulator columns come out of tensor memory 64 at a time (two 32-column loads in flight, one wait): the
         // loads' latencies overlap, which is what bounds this kernel (one thread walks a whole row of the tile).
         auto finish16 = [&](float* v, int n0) {
-          if (bias) {
+          if (bias) {                              // biases sit 16-byte aligned in the blob: four per shared-memory load
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] += bias[n0 + i];
+            for (int i = 0; i < 16; i += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bias + n0 + i);
+              v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+            }
+          }
+          if (!last && act_l == ACT_RELU) {
+            // hidden layer: relu and the bf16 packing are one conversion instruction per pair of columns
+            store_chunk_relu(act, (n0 >> 3), row, v);
+            store_chunk_relu(act, (n0 >> 3) + 1, row, v + 8);
+            return;
           }
           // the activation is uniform per layer: branch once per 16 columns instead of letting the
           // compiler evaluate every transcendental for every element and select
-          switch (spec.act[l]) {
+          switch (act_l) {
             case ACT_RELU:
 #pragma unroll
               for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
@@ -237,6 +277,8 @@ LMB_API int lmb_fused_mlp_fwd_multi(const void* const* xs, const int* widths, in
       return (int)cudaErrorInvalidValue;
   MLPInputs inputs;
   inputs.n_src = n_src;
+  inputs.n128 = inputs.n64 = 0;
+  inputs.x0 = (const __nv_bfloat16*)xs[0];
   int chunk = 0;
   for (int s = 0; s < n_src; ++s) {
     if (widths[s] % 8 || widths[s] <= 0) return (int)cudaErrorInvalidValue;
@@ -247,6 +289,18 @@ LMB_API int lmb_fused_mlp_fwd_multi(const void* const* xs, const int* widths, in
   }
   for (int s = n_src; s <= kMaxSources; ++s) inputs.chunk_begin[s] = chunk;
   if (chunk * 8 != spec->in_width) return (int)cudaErrorInvalidValue;
+  // A single source is copied as whole rows into the swizzled layouts (LMB_MLP_WHOLE_ROWS=0 keeps the 8-column chunk
+  // copies, which several sources always use): 3 copy instructions and 384 requests per 160-column tile instead of 20
+  // and 2560, measured 0.236 ms against 0.298 ms per Mi rows of the colour head.
+  static const int whole_rows = getenv("LMB_MLP_WHOLE_ROWS") ? atoi(getenv("LMB_MLP_WHOLE_ROWS")) : 1;
+  if (whole_rows && n_src == 1) {
+    const int w = spec->in_width, rem = w % 64;
+    inputs.n128 = w / 64 + (rem > 32 ? 1 : 0);
+    inputs.n64 = (rem > 0 && rem <= 32) ? 1 : 0;
+    if (inputs.n128 * 64 + inputs.n64 * 32 < spec->K[0]) return (int)cudaErrorInvalidValue;
+    if (inputs.n128) { int rc = encode_swizzled_map(&inputs.map[0], xs[0], w, max_rows, 64); if (rc) return rc; }
+    if (inputs.n64) { int rc = encode_swizzled_map(&inputs.map[1], xs[0], w, max_rows, 32); if (rc) return rc; }
+  }
   const size_t smem = ((spec->blob_bytes + 1023) & ~1023) + (size_t)kSlots * kActBytes + 1024;
   if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
   static size_t configured = 0;

@@ -38,6 +38,11 @@ struct alignas(64) MLPInputs {
   CUtensorMap map[kMaxSources];
   int chunk_begin[kMaxSources + 1];
   int n_src;
+  // Single local source, whole-row copies: map[0] moves 64-column pieces (128-byte rows, SWIZZLE_128B), map[1] a last
+  // piece of at most 32 columns (64-byte rows, SWIZZLE_64B); 128 copy requests of 128 bytes per piece instead of 128
+  // requests of 16 bytes per 8-column chunk.  n128 / n64: number of pieces of either kind (0: chunked copies above).
+  int n128, n64;
+  const __nv_bfloat16* x0;      // source 0 (the kernel reads the view direction of the colour stage from it)
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -55,6 +60,16 @@ __device__ __forceinline__ void store_chunk(unsigned char* buf, int chunk, int r
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(buf + ((size_t)chunk * kTileRows + row) * 16) = u;
+}
+
+// relu(v) rounded to bf16, eight values -> one 16-byte chunk: `cvt.rn.relu.bf16x2.f32` clamps and packs a pair at once
+__device__ __forceinline__ void store_chunk_relu(unsigned char* buf, int chunk, int row, const float* v) {
+  uint4 u;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(v[2 * i + 1]), "f"(v[2 * i]));
   *reinterpret_cast<uint4*>(buf + ((size_t)chunk * kTileRows + row) * 16) = u;
 }
 
@@ -84,6 +99,22 @@ inline TensorMapEncodeTiledFn tensor_map_encoder() {
 
 // 3-D tensor map over a row-major bf16 [rows, width] matrix: (8 elements, width/8 chunks, rows), box
 // = one 16-byte chunk of 128 rows, so a tile lands in shared memory in the chunked operand layout.
+// Row-major [rows, width] bf16 as a 2-D tensor with a [box_cols x 128 rows] box written in a swizzled layout
+// (box_cols * 2 bytes = the swizzle span: 64 columns for SWIZZLE_128B, 32 for SWIZZLE_64B).  Columns past `width`
+// and rows past `rows` read as zeros.
+inline int encode_swizzled_map(CUtensorMap* map, const void* x, int width, long long rows, int box_cols) {
+  const cuuint64_t gdim[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)width * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)kTileRows};
+  const cuuint32_t estride[2] = {1, 1};
+  TensorMapEncodeTiledFn encode = tensor_map_encoder();
+  if (encode == nullptr) return 19999;
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), gdim, gstride, box, estride,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 10000 + (int)r;
+}
+
 inline int encode_input_map(CUtensorMap* map, const void* x, int width, long long rows) {
   const cuuint64_t gdim[3] = {8, (cuuint64_t)(width / 8), (cuuint64_t)rows};
   const cuuint64_t gstride[2] = {16, (cuuint64_t)width * 2};

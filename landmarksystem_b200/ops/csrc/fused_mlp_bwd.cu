@@ -203,6 +203,14 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     if (row == 0) tc05::fence_after_sync(); \
   }
 
+  if constexpr (!kPE) {
+    // An input narrower than the 160-column operand: the copies fill chunks [0, in_chunks) of every tile, the rest is
+    // written once here - zeros, and ones in column 159 (the bias column of dW1) - and never touched again.
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int c = in_chunks; c < 20; ++c)
+      *reinterpret_cast<uint4*>(bufA + ((size_t)c * kTileRows + row) * 16) = (c == 19) ? make_uint4(0, 0, 0, 0x3F800000u) : z;
+  }
+
   for (; ok && tile < n_tiles; tile += gridDim.x) {
     const long long row0 = tile * kTileRows;
     const bool valid = row0 + row < n_rows;
@@ -264,9 +272,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i] + b1[n0 + i], 0.f);
+      for (int i = 0; i < 64; i += 4) {               // four biases per shared-memory load
+        const float4 b4 = *reinterpret_cast<const float4*>(b1 + n0 + i);
+        v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+      }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) store_chunk(bufH1, (n0 >> 3) + c, row, v + 8 * c);
+      for (int c = 0; c < 8; ++c) store_chunk_relu(bufH1, (n0 >> 3) + c, row, v + 8 * c);   // relu inside the bf16 packing
     }
     {
       float ones[8];
@@ -283,9 +294,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = fmaxf(v[i] + b2[n0 + i], 0.f);
+      for (int i = 0; i < 64; i += 4) {
+        const float4 b4 = *reinterpret_cast<const float4*>(b2 + n0 + i);
+        v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+      }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) store_chunk(bufHZ, (n0 >> 3) + c, row, v + 8 * c);
+      for (int c = 0; c < 8; ++c) store_chunk_relu(bufHZ, (n0 >> 3) + c, row, v + 8 * c);
     }
     LMB_EPILOGUE_DONE();
 
@@ -472,8 +486,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
           __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(u);
 #pragma unroll
           for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-          *reinterpret_cast<uint4*>(dxr + n0) = u[0];
-          *reinterpret_cast<uint4*>(dxr + n0 + 8) = u[1];
+          if (n0 < spec.in_width) *reinterpret_cast<uint4*>(dxr + n0) = u[0];
+          if (n0 + 8 < spec.in_width) *reinterpret_cast<uint4*>(dxr + n0 + 8) = u[1];
         }
       }
       LMB_EPILOGUE_DONE();
@@ -494,8 +508,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
           __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(u);
 #pragma unroll
           for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-          *reinterpret_cast<uint4*>(dxr + 128 + n0) = u[0];
-          *reinterpret_cast<uint4*>(dxr + 128 + n0 + 8) = u[1];
+          if (128 + n0 < spec.in_width) *reinterpret_cast<uint4*>(dxr + 128 + n0) = u[0];
+          if (128 + n0 + 8 < spec.in_width) *reinterpret_cast<uint4*>(dxr + 128 + n0 + 8) = u[1];
         }
       }
       LMB_EPILOGUE_DONE();
@@ -603,20 +617,24 @@ LMB_API int lmb_rgb_mlp_bwd(const void* x, const int* count_ptr, long long max_r
 }
 
 // Plain three-layer perceptron 160 -> 128 -> 128 -> 16 (padded widths, see the kernel's header).  x: bf16
-// [max_rows, 160] with ones in column 159; dout: fp32 [max_rows, dout_stride] (spec.out_dim used); dx: bf16
-// [max_rows, 160]; gbuf as for lmb_rgb_mlp_bwd (dW1 [128][160] with db1 in column 159, dW2 [128][144] with db2 in
-// column 128, dW3^T [128][16], db3 [16]; the dW0^T block stays zero).
-LMB_API int lmb_mlp3_bwd(const void* x, const int* count_ptr, long long max_rows, const void* blob, const MLPSpec* spec,
-                         const float* dout, int dout_stride, void* dx, float* gbuf, int* status, cudaStream_t stream) {
+// [max_rows, x_width], x_width a multiple of 8: either 160 with ones in column 159, or at most 152 - the kernel then
+// supplies the zero columns and the ones column itself, so the caller pads nothing; dout: fp32 [max_rows, dout_stride]
+// (spec.out_dim used); dx: bf16 [max_rows, x_width]; gbuf as for lmb_rgb_mlp_bwd (dW1 [128][160] with db1 in column
+// 159, dW2 [128][144] with db2 in column 128, dW3^T [128][16], db3 [16]; the dW0^T block stays zero).
+LMB_API int lmb_mlp3_bwd(const void* x, int x_width, const int* count_ptr, long long max_rows, const void* blob,
+                         const MLPSpec* spec, const float* dout, int dout_stride, void* dx, float* gbuf, int* status,
+                         cudaStream_t stream) {
   if (max_rows <= 0) return 0;
-  const MLPSpec& s = *spec;
+  if (x_width % 8 != 0 || x_width < 8 || (x_width > 152 && x_width != 160)) return (int)cudaErrorInvalidValue;
+  MLPSpec s = *spec;
   if (s.n_layers != 3 || s.pe_stage || s.in_width != 160 || s.K[0] != 160 || s.N[0] != 128 || s.K[1] != 128 || s.N[1] != 128 ||
       s.K[2] != 128 || s.N[2] != 16 || s.out_dim < 1 || s.out_dim > 16 || s.b_off[0] < 0 || s.b_off[1] < 0 || s.b_off[2] < 0 ||
       s.blob_bytes % 16 || s.act[0] != ACT_RELU || s.act[1] != ACT_RELU || (s.act[2] != ACT_SIGMOID && s.act[2] != ACT_NONE) ||
       dout_stride < s.out_dim)
     return (int)cudaErrorInvalidValue;
+  s.in_width = x_width;                      // the kernel's copy width and dx row pitch; the operand stays 160 wide
   CUtensorMap xmap;
-  int rc = encode_input_map(&xmap, x, 160, max_rows);
+  int rc = encode_input_map(&xmap, x, x_width, max_rows);
   if (rc) return rc;
   const size_t smem = ((s.blob_bytes + 1023) & ~1023) + (size_t)(kBufA + kBufH1 + kBufHZ + kBufS) + 1024;
   if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;

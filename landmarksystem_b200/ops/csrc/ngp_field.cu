@@ -216,6 +216,61 @@ ngp_head_rows_bwd_kernel(long long m_total, const long long* __restrict__ idx, i
   }
 }
 
+// The same backward for the shape the shipped configurations use - 15 geometry features, rows of 64 columns (up to
+// 33 appearance channels): the row's gradient arrives as six 16-byte loads and d_h leaves as four, all register
+// indices are compile-time constants.
+__global__ void __launch_bounds__(256)
+ngp_head_rows_bwd_g15w64_kernel(long long m_total, const long long* __restrict__ idx, int samples_per_ray,
+                                const __nv_bfloat16* __restrict__ d_rows, const float* __restrict__ d_sigma,
+                                const float* __restrict__ h, const unsigned char* __restrict__ inside, int app,
+                                float* __restrict__ d_h, float* __restrict__ d_app) {
+  constexpr int kGeo = 15, kWidth = 64;
+  const long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = m < m_total;
+  const int lane = threadIdx.x & 31;
+  long long ray = -1;
+  float v[48];                                     // columns 16 .. 63 of the row
+#pragma unroll
+  for (int i = 0; i < 48; ++i) v[i] = 0.f;
+  if (live) {
+    ray = (idx ? idx[m] : m) / samples_per_ray;
+    const __nv_bfloat16* src = d_rows + m * kWidth + 16;
+#pragma unroll
+    for (int c = 0; c < 6; ++c) {
+      const F8 f = load8(src + 8 * c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[8 * c + j] = f.v[j];
+    }
+    const float keep = inside[m] ? 1.f : 0.f;
+    float4* dh = reinterpret_cast<float4*>(d_h + m * 16);
+    dh[0] = make_float4(d_sigma[m] * trunc_exp_grad(h[m * 16]) * keep, v[0] * keep, v[1] * keep, v[2] * keep);
+    dh[1] = make_float4(v[3] * keep, v[4] * keep, v[5] * keep, v[6] * keep);
+    dh[2] = make_float4(v[7] * keep, v[8] * keep, v[9] * keep, v[10] * keep);
+    dh[3] = make_float4(v[11] * keep, v[12] * keep, v[13] * keep, v[14] * keep);
+  }
+  if (d_app == nullptr) return;
+  const long long prev_ray = __shfl_up_sync(0xffffffffu, ray, 1);
+  const bool head = live && (lane == 0 || prev_ray != ray);
+  bool take[5];
+#pragma unroll
+  for (int s = 0; s < 5; ++s) {
+    const long long other_ray = __shfl_down_sync(0xffffffffu, ray, 1 << s);
+    take[s] = (lane + (1 << s) < 32) && (other_ray == ray);
+  }
+#pragma unroll
+  for (int k = 0; k < 33; ++k) {
+    if (k < app) {                                 // uniform across the grid
+      float g = v[kGeo + k];
+#pragma unroll
+      for (int s = 0; s < 5; ++s) {
+        const float o = __shfl_down_sync(0xffffffffu, g, 1 << s);
+        if (take[s]) g += o;
+      }
+      if (head) atomicAdd(d_app + ray * app + k, g);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Occupancy grid refresh.
 struct OccRoi { float centre[3], half[3]; };
@@ -341,8 +396,12 @@ LMB_API int lmb_ngp_head_rows_bwd(long long m, const long long* idx, int samples
                                   float* d_h, float* d_app, cudaStream_t stream) {
   if (m <= 0) return 0;
   if (16 + geo + app > width) return (int)cudaErrorInvalidValue;
-  ngp_head_rows_bwd_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(m, idx, samples_per_ray, d_rows, d_sigma, h, geo, inside, app,
-                                                                width, d_h, d_app);
+  if (geo == 15 && width == 64)
+    ngp_head_rows_bwd_g15w64_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(m, idx, samples_per_ray, d_rows, d_sigma, h, inside, app,
+                                                                         d_h, d_app);
+  else
+    ngp_head_rows_bwd_kernel<<<ceil_div(m, 256), 256, 0, stream>>>(m, idx, samples_per_ray, d_rows, d_sigma, h, geo, inside, app,
+                                                                  width, d_h, d_app);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -59,6 +59,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst_smem, const void* tmap, in
       ::"r"(smem_u32(dst_smem)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
 }
 
+// Tiled 2-D tensor load; c0 is the innermost coordinate (c0 * elemsize must stay 16-byte aligned).
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const void* tmap, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst_smem)), "l"(tmap), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---- TMEM ----------------------------------------------------------------------------------------
 // One full warp allocates `ncols` (power of two >= 32) TMEM columns; the base address lands in *dst.
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
@@ -115,6 +122,20 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
+  return d;
+}
+// K-major operand in a swizzled layout as the tensor-map swizzle modes write it: rows of 128 bytes (layout 2,
+// SWIZZLE_128B: groups of 8 rows are 1024 bytes apart) or of 64 bytes (layout 4, SWIZZLE_64B: 512 bytes apart).  The
+// 16-byte pieces of a row are XOR-permuted with the row number by both the copy engine and the tensor core (on absolute
+// shared-memory address bits), so the tile must start on a 1024- / 512-byte boundary; stepping 16 elements along K adds
+// 32 bytes to the start address.  The leading-dimension offset is unused for these layouts (encoded as 1).
+__device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t saddr, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)(layout_type & 7u) << 61;
   return d;
 }
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation, M = 128.

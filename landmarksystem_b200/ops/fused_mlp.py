@@ -36,7 +36,7 @@ native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, 
 native.register_signature("lmb_rgb_mlp_bwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
                                                native.P, native.P, native.P, native.P])
 native.register_signature("lmb_rgb_mlp_bwd_gbuf_floats", [])
-native.register_signature("lmb_mlp3_bwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
+native.register_signature("lmb_mlp3_bwd", [native.P, c_int, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P, c_int,
                                             native.P, native.P, native.P, native.P])
 
 
@@ -233,14 +233,21 @@ def mlp3_backward(packed: "PackedMLP", x: torch.Tensor, dout: torch.Tensor):
         p3.status = packed.status          # one status word per network: ``PackedMLP.check_status`` covers both kernels
     lib = native.lib()
     n, k0 = x.shape[0], packed.layers[0][0].shape[1]
-    x160 = torch.zeros(n, MLP3_IN, device=x.device, dtype=torch.bfloat16)
-    x160[:, :k0] = x[:, :k0]
-    x160[:, MLP3_ONES] = 1.0
     gbuf = torch.zeros(int(lib.lmb_rgb_mlp_bwd_gbuf_floats()), device=x.device, dtype=torch.float32)
-    dx = torch.empty_like(x160)
     dout = dout.contiguous().float()
-    native.check(lib.lmb_mlp3_bwd(x160.data_ptr(), None, n, p3.blob.data_ptr(), byref(p3.spec), dout.data_ptr(), dout.shape[1],
-                                  dx.data_ptr(), gbuf.data_ptr(), p3.status.data_ptr(), native.stream_ptr()), "mlp3_bwd")
+    direct = x.shape[1] <= MLP3_IN - 8 and x.is_contiguous()
+    if direct:
+        # the kernel reads the rows as they are and supplies the zero and ones columns of its 160-wide operand itself:
+        # no padded copy of the input, no padded gradient to slice
+        xin, dx = x, torch.empty_like(x)
+    else:
+        xin = torch.zeros(n, MLP3_IN, device=x.device, dtype=torch.bfloat16)
+        xin[:, :k0] = x[:, :k0]
+        xin[:, MLP3_ONES] = 1.0
+        dx = torch.empty_like(xin)
+    native.check(lib.lmb_mlp3_bwd(xin.data_ptr(), xin.shape[1], None, n, p3.blob.data_ptr(), byref(p3.spec), dout.data_ptr(),
+                                  dout.shape[1], dx.data_ptr(), gbuf.data_ptr(), p3.status.data_ptr(), native.stream_ptr()),
+                 "mlp3_bwd")
     g1 = gbuf[: 128 * 160].view(128, 160)
     g2 = gbuf[128 * 160: 128 * 160 + 128 * 144].view(128, 144)
     o = 128 * 160 + 128 * 144
@@ -261,6 +268,8 @@ def mlp3_backward(packed: "PackedMLP", x: torch.Tensor, dout: torch.Tensor):
     grads.append(g3t[:n2, :n_out].t().contiguous())
     if layers[-1][1] is not None:
         grads.append(db3[:n_out].contiguous())
+    if direct:
+        return dx, grads
     dx_out = torch.zeros_like(x)
     dx_out[:, :k0] = dx[:, :k0]
     return dx_out, grads

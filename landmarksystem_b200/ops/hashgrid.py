@@ -114,7 +114,7 @@ native.register_signature("lmb_hashgrid_bwd", [native.P, native.c_longlong, nati
 
 class _HashGrid(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, table, meta, out_dtype, shadow):
+    def forward(ctx, x, table, meta, out_dtype, shadow, sink):
         read = shadow if shadow is not None else table
         out = torch.empty((x.shape[0], meta.out_dim), device=x.device, dtype=out_dtype)
         ms = _meta_struct(meta)
@@ -122,21 +122,21 @@ class _HashGrid(torch.autograd.Function):
                                                    native.DTYPE_CODE[read.dtype], ctx_ref(ms), out.data_ptr(),
                                                    native.DTYPE_CODE[out_dtype], native.stream_ptr()), "hashgrid_fwd")
         ctx.save_for_backward(x)
-        ctx.meta, ctx.table = meta, table
+        ctx.meta, ctx.table, ctx.sink = meta, table, sink
         return out
 
     @staticmethod
     def backward(ctx, dout):
         (x,) = ctx.saved_tensors
         table, meta = ctx.table, ctx.meta
-        sink = getattr(table, "_lmb_grad_sink", None)
+        sink = ctx.sink if ctx.sink is not None else getattr(table, "_lmb_grad_sink", None)
         grad = sink if sink is not None else torch.zeros(table.shape, device=table.device, dtype=torch.float32)
         dout = dout.contiguous()
         ms = _meta_struct(meta)
         native.check(native.lib().lmb_hashgrid_bwd(x.data_ptr(), x.shape[0], ctx_ref(ms), dout.data_ptr(),
                                                    native.DTYPE_CODE[dout.dtype], grad.data_ptr(),
                                                    native.stream_ptr()), "hashgrid_bwd")
-        return None, (None if sink is not None else grad), None, None, None
+        return None, (None if sink is not None else grad), None, None, None, None
 
 
 def ctx_ref(struct):
@@ -145,9 +145,12 @@ def ctx_ref(struct):
     return byref(struct)
 
 
-def hashgrid_encode(x: torch.Tensor, table: torch.Tensor, meta: HashGridMeta,
-                    out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+def hashgrid_encode(x: torch.Tensor, table: torch.Tensor, meta: HashGridMeta, out_dtype: torch.dtype = torch.float32,
+                    shadow: torch.Tensor = None, sink: torch.Tensor = None) -> torch.Tensor:
+    """``shadow``: bf16 copy of ``table`` for the kernel to read; ``sink``: persistent fp32 accumulator that receives the
+    table gradient instead of a fresh tensor (both default to the attributes a fused optimiser attached to ``table``)."""
     if not x.is_cuda:
         return hashgrid_reference(x, table, meta).to(out_dtype)
-    shadow = getattr(table, "_lmb_shadow", None)
-    return _HashGrid.apply(x.contiguous().float(), table, meta, out_dtype, shadow)
+    if shadow is None:
+        shadow = getattr(table, "_lmb_shadow", None)
+    return _HashGrid.apply(x.contiguous().float(), table, meta, out_dtype, shadow, sink)

@@ -70,6 +70,14 @@ class RayModelTrainer(NeRFTrainer):
         if torch.device(self.config.device).type == "cuda" and bool(self.config.get("fused_optimizer", True)):
             from ..ops import FusedAdam
 
+            if not cfg.DDP and bool(cfg.get("hash_table_shadow", True)) and cfg.get("runtime", "Torch") == "Kernel":
+                # hash tables: the backward adds into a persistent accumulator that the Adam kernel clears, and the
+                # same kernel refreshes a bf16 copy that the lookup reads (half the bytes per gather; the reference's
+                # tiny-cuda-nn tables are fp16 with fp32 masters).  Not under NCCL data parallelism, which averages
+                # ``p.grad`` tensors.
+                for mod in self.module.modules():
+                    if hasattr(mod, "enable_table_shadow"):
+                        mod.enable_table_shadow()
             return FusedAdam(groups, eps=self.config.eps)     # one device pass per tensor, gradients cleared in it
         return torch.optim.Adam(groups, eps=self.config.eps)
 

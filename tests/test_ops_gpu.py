@@ -117,6 +117,32 @@ def test_hashgrid_fwd_bwd(log2):
     assert torch.allclose(t_gpu.grad.cpu(), t_ref.grad, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("levels,features", [(8, 2), (6, 2), (5, 4), (16, 2)])
+def test_hashgrid_on_ray_ordered_samples(levels, features):
+    """Samples ordered along rays (neighbouring rows share cells on the coarse levels): the backward's in-warp sums over
+    runs of equal cells, rows without a gradient in the middle of a run, a row count that is no multiple of the warp, and
+    level counts that do and do not fill the 4-level groups."""
+    g = torch.Generator().manual_seed(levels * 10 + features)
+    meta = make_meta(levels, features, 14, 4, 1.7 if levels < 16 else 1.4)     # finest resolution stays below ~700 cells:
+    # fp32 positions resolve the interpolation weights there whatever the rounding of x * scale + 0.5 (fused or not)
+    table = torch.randn(meta.offsets[-1], features, generator=g) * 0.1
+    R, S = 37, 53
+    o = torch.rand(R, 1, 3, generator=g) * 0.3
+    d = torch.nn.functional.normalize(torch.rand(R, 1, 3, generator=g), dim=-1)
+    t = torch.linspace(0.0, 0.9, S)[None, :, None]
+    x = (o + d * t).clamp(0.0, 1.0).reshape(-1, 3)
+    gout = torch.randn(x.shape[0], levels * features, generator=g)
+    gout[torch.rand(x.shape[0], generator=g) < 0.2] = 0.0
+    t_ref = table.clone().requires_grad_()
+    ref = hashgrid_reference(x, t_ref, meta)
+    ref.backward(gout)
+    t_gpu = table.to(DEV).requires_grad_()
+    out = hashgrid_encode(x.to(DEV), t_gpu, meta)
+    assert torch.allclose(out.cpu(), ref.detach(), atol=1e-5)
+    out.backward(gout.to(DEV))
+    assert torch.allclose(t_gpu.grad.cpu(), t_ref.grad, atol=2e-4, rtol=1e-4)
+
+
 def test_lazy_adam_matches_dense_adam():
     """Deferred Adam on planes: fed the same gradients, the touched texels' shadows are current before every
     step and after a flush every parameter equals the dense fused Adam result."""
