@@ -26,14 +26,17 @@ def batches(rank, n=8, rays=512):
     return out
 
 
-def make(root, **extra):
+def make(root, ckpt=None, **extra):
     conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "landmarksystem_b200", "models", "gridnerf",
                         "confs", "synthetic_tiny.py")
     over = {"basedir": root, "device": "cuda", "n_iters": "100", "batch_size": "1024", "DDP": "true", "nSamples": "32",
             "datadir": "ring:3:16x16:20:3", "progress_refresh_rate": "1000", "N_voxel_init": str(32 ** 3),
             "N_voxel_final": str(32 ** 3), "grid_dtype": "bf16"}
     over.update(extra)
-    tr = GridNeRFTrainer(BaseConfig.from_file(conf, over))
+    cfg = BaseConfig.from_file(conf, over)
+    if ckpt is not None:
+        cfg.ckpt = ckpt              # no console form: the field's default is None, so the parser cannot infer its type
+    tr = GridNeRFTrainer(cfg)
     tr.model.train()
     return tr
 
