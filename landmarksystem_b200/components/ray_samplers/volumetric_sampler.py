@@ -31,6 +31,11 @@ class VolumetricSampler(BaseSampler):
             mid = 0.5 * (t_starts + t_ends)[:, None]
             return self.density_fn(origins[ray_indices] + directions[ray_indices] * mid).reshape(-1)
 
+        # a field may evaluate the marched samples straight from the padded [R, S] interval block (sample index ->
+        # position -> density with its own kernels) instead of receiving gathered positions
+        from_samples = getattr(self.density_fn, "from_samples", None)
+        if from_samples is not None:
+            sigma_fn.from_samples = lambda idx, S, ts, te: from_samples(idx, S, origins, directions, ts, te)
         return sigma_fn
 
     @torch.no_grad()

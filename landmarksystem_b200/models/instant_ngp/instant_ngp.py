@@ -81,6 +81,34 @@ def get_normalized_directions(dirs: torch.Tensor) -> torch.Tensor:
     return (dirs / dirs.norm(dim=-1, keepdim=True) + 1.0) / 2.0
 
 
+class _FieldDensity:
+    """The density callback handed to the occupancy sampler: positions -> sigma, and - for the sampler's opacity culling on
+    the kernel path - marched intervals -> sigma without materialising gathered positions (sample index -> hash-grid
+    coordinate by ``ngp_positions_kernel``, then the density head)."""
+
+    def __init__(self, model):
+        self.model = model
+
+    def __call__(self, positions):
+        return self.model.density_fn(positions)
+
+    @torch.no_grad()
+    def from_samples(self, idx, samples_per_ray, origins, directions, t_starts, t_ends):
+        m = self.model
+        z = (0.5 * (t_starts + t_ends)).reshape(-1).contiguous().float()
+        if not m._kernel_glue(origins):
+            flat = idx if idx is not None else torch.arange(z.numel(), device=z.device)
+            ray = flat // samples_per_ray
+            return m.density_fn(origins[ray] + directions[ray] * z[flat][:, None]).reshape(-1)
+        from ...ops import ngp_field
+
+        xyzb, inside = ngp_field.sample_positions(idx, samples_per_ray, origins.contiguous().float(),
+                                                  directions.contiguous().float(), z, m.aabb, m._aabb_host,
+                                                  int(m.plane_division[0]), int(m.plane_division[1]))
+        h = m.mlp_base_mlp(m.mlp_base_grid(xyzb))
+        return torch.exp(h[:, 0].float()) * inside
+
+
 class InstantNGP(BaseNeRF):
     def __init__(self, aabb, device, near_far, scene_manager=None, config=None, group=None):
         super().__init__(config=config, scene_manager=scene_manager, aabb=aabb, device=device, near_far=list(near_far))
@@ -116,7 +144,7 @@ class InstantNGP(BaseNeRF):
         c = self.config
         self.occupancy_grid = OccGridEstimator(torch.cat((self.aabb[0], self.aabb[1])).cpu(), c.grid_resolution,
                                                c.grid_levels).to(self.device)
-        self.sampler = VolumetricSampler(self.occupancy_grid, self.density_fn, self.near_far, c.render_step_size,
+        self.sampler = VolumetricSampler(self.occupancy_grid, _FieldDensity(self), self.near_far, c.render_step_size,
                                          c.alpha_thre, c.cone_angle, c.max_samples_per_ray)
 
     def init_renderer(self):

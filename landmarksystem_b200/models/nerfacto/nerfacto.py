@@ -149,6 +149,20 @@ class Nerfacto(BaseNeRF):
             return all_reduce_sum_local_grad(t, c.mp_group)
         return t
 
+    def _kernel_glue(self, rays) -> bool:
+        """Kernel path for the per-sample glue: both field heads on the fused MLP kernels and no cross-rank sum between
+        the density head and the colour head (spatial-block training sums the two across ranks there)."""
+        c = self.config
+        if not rays.is_cuda or (c.get("branch_parallel", False) and c.get("is_train", False)):
+            return False
+        if not (getattr(self.mlp_base_mlp, "use_fused", False) and getattr(self.mlp_head, "use_fused", False)):
+            return False
+        from ...ops import native
+        from ...ops.fused_mlp import fused_mlp_supported
+
+        return (native.available() and self.geo_feat_dim + c.appearance_embedding_dim <= 48
+                and fused_mlp_supported(self.mlp_base_mlp) and fused_mlp_supported(self.mlp_head))
+
     def get_density(self, pos: torch.Tensor):
         xyzb, inside = self._positions(pos)
         h = self.mlp_base_mlp(self.mlp_base_grid(xyzb)).float()
@@ -165,14 +179,26 @@ class Nerfacto(BaseNeRF):
         samples, weights_list, samples_list = self.sampler(o, d, near, far, self.proposal_networks.density_fns, cam)
         R, S = samples.starts.shape[:2]
         pos = samples.positions.reshape(-1, 3)
-        density, geo = self.get_density(pos)
-        dirs = get_normalized_directions(d)[:, None, :].expand(-1, S, -1).reshape(-1, 3)
         if self.training:
-            app = self.embedding_appearance(cam.long().clamp(0, c.appearance_embedding_size - 1))[:, None, :]
+            app_ray = self.embedding_appearance(cam.long().clamp(0, c.appearance_embedding_size - 1))
         else:
-            app = self.embedding_appearance.weight.mean(0)[None, None, :].expand(R, 1, -1)   # mean embedding at eval
-        app = app.expand(-1, S, -1).reshape(-1, c.appearance_embedding_dim)
-        rgb = self.mlp_head(torch.cat((self.direction_encoding(dirs), geo, app), dim=-1)).float().view(R, S, 3)
+            app_ray = self.embedding_appearance.weight.mean(0)[None, :].expand(R, -1)           # mean embedding at eval
+        if self._kernel_glue(rays):
+            # sigma (truncated exp) and the colour head's bf16 rows [SH(dir) | geometry | appearance] in one launch from the
+            # density head's output, one launch for the backward of both (ops/csrc/ngp_field.cu)
+            from ...ops import ngp_field
+
+            xyzb, inside = self._positions(pos)
+            h = self.mlp_base_mlp(self.mlp_base_grid(xyzb)).float()
+            width = (16 + self.geo_feat_dim + c.appearance_embedding_dim + 15) // 16 * 16
+            rows, sigma = ngp_field.head_rows(None, S, d, h, inside, app_ray.contiguous(), c.appearance_embedding_dim, width)
+            density = sigma[:, None]
+            rgb = self.mlp_head(rows).float().view(R, S, 3)
+        else:
+            density, geo = self.get_density(pos)
+            dirs = get_normalized_directions(d)[:, None, :].expand(-1, S, -1).reshape(-1, 3)
+            app = app_ray[:, None, :].expand(-1, S, -1).reshape(-1, c.appearance_embedding_dim)
+            rgb = self.mlp_head(torch.cat((self.direction_encoding(dirs), geo, app), dim=-1)).float().view(R, S, 3)
         weights = samples.get_weights(density.view(R, S, 1))
         weights_list.append(weights)
         samples_list.append(samples)

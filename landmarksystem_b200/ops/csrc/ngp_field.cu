@@ -346,6 +346,53 @@ occ_threshold_kernel(long long n, const float* __restrict__ occs, const double* 
     binaries[i] = occs[i] > thre ? 1 : 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Opacity culling of marched samples (nerfacc's sampling with a density callback and alpha_thre > 0, as the reference
+// calls it in landmark/nerf_components/ray_samplers/volumetric_sampler.py:92-104): a sample survives if its opacity is
+// at least `alpha_thre` and the transmittance in front of it at least `early_stop_eps`; survivors move to the front of
+// the ray's row in order.  One warp per ray: opacity per lane, transmittance by a multiplicative warp scan with a
+// carry, positions by ballot.  In place: a row is read 32 samples at a time and written at or before where it is read.
+__global__ void __launch_bounds__(256)
+occ_cull_kernel(int R, int S, const float* __restrict__ sigma, float* __restrict__ ts, float* __restrict__ te,
+                int* __restrict__ counts, float alpha_thre, float early_stop_eps) {
+  const int ray = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (ray >= R) return;
+  const int n = counts[ray];
+  const long long base = (long long)ray * S;
+  float carry = 1.f;       // transmittance in front of this group of 32 samples
+  int kept = 0;
+  for (int s0 = 0; s0 < n; s0 += 32) {
+    const int s = s0 + lane;
+    const bool valid = s < n;
+    float a = 0.f, t0 = 0.f, t1 = 0.f;
+    if (valid) {
+      t0 = ts[base + s]; t1 = te[base + s];
+      a = 1.f - expf(-sigma[base + s] * (t1 - t0));
+    }
+    float incl = 1.f - a;                                      // inclusive product of (1 - alpha) over the lanes so far
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl *= v;
+    }
+    float before = __shfl_up_sync(0xffffffffu, incl, 1);
+    before = carry * (lane == 0 ? 1.f : before);
+    const bool keep = valid && a >= alpha_thre && before >= early_stop_eps;
+    const unsigned won = __ballot_sync(0xffffffffu, keep);
+    __syncwarp();                                              // every lane has read its sample before any lane writes
+    if (keep) {
+      const int pos = kept + __popc(won & ((1u << lane) - 1u));
+      ts[base + pos] = t0; te[base + pos] = t1;
+    }
+    kept += __popc(won);
+    carry *= __shfl_sync(0xffffffffu, incl, 31);
+  }
+  __syncwarp();
+  for (int s = kept + lane; s < n; s += 32) { ts[base + s] = 0.f; te[base + s] = 0.f; }
+  if (lane == 0) counts[ray] = kept;
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -438,6 +485,15 @@ LMB_API int lmb_occ_binarise(long long n, const float* occs, float threshold, do
   occ_sum_kernel<<<grid, 256, 0, stream>>>(n, occs, sum_scratch);
   LMB_LAUNCH_CHECK();
   occ_threshold_kernel<<<grid, 256, 0, stream>>>(n, occs, sum_scratch, threshold, binaries);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// sigma: fp32 [R, S] (values past counts[r] ignored); ts / te: fp32 [R, S], compacted in place; counts: int32 [R], updated
+LMB_API int lmb_occ_cull(int R, int S, const float* sigma, float* ts, float* te, int* counts, float alpha_thre,
+                         float early_stop_eps, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  occ_cull_kernel<<<ceil_div((long long)R * 32, 256), 256, 0, stream>>>(R, S, sigma, ts, te, counts, alpha_thre, early_stop_eps);
   LMB_LAUNCH_CHECK();
   return 0;
 }

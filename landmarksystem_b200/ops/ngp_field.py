@@ -26,6 +26,7 @@ native.register_signature("lmb_ngp_head_rows_bwd", [c_longlong, P, c_int, P, P, 
 native.register_signature("lmb_occ_cells", [c_longlong, P, c_int, P, c_int, c_uint, c_int, P, c_float, P, P, P])
 native.register_signature("lmb_occ_update", [c_longlong, P, P, P, P, P])
 native.register_signature("lmb_occ_binarise", [c_longlong, P, c_float, P, P, P])
+native.register_signature("lmb_occ_cull", [c_int, c_int, P, P, P, P, c_float, c_float, P])
 
 SH_WIDTH = 16
 
@@ -180,3 +181,14 @@ def occ_binarise(occs: torch.Tensor, threshold: float, binaries_u8: torch.Tensor
     """``binaries = occs > min(mean(occs), threshold)`` without a host read; ``scratch``: one float64 on the device."""
     native.check(native.lib().lmb_occ_binarise(occs.numel(), occs.data_ptr(), float(threshold), scratch.data_ptr(),
                                                binaries_u8.data_ptr(), native.stream_ptr()), "occ_binarise")
+
+
+@torch.no_grad()
+def occ_cull(sigma: torch.Tensor, ts: torch.Tensor, te: torch.Tensor, counts: torch.Tensor, alpha_thre: float,
+             early_stop_eps: float) -> None:
+    """In place: per ray keep the samples with opacity ``1 - exp(-sigma * (te - ts)) >= alpha_thre`` and transmittance in
+    front of them ``>= early_stop_eps``, moved to the front of the row in order; ``counts`` becomes the survivors' count.
+    ``sigma``, ``ts``, ``te``: fp32 ``[R, S]`` contiguous; ``counts``: int32 ``[R]``."""
+    R, S = ts.shape
+    native.check(native.lib().lmb_occ_cull(R, S, sigma.data_ptr(), ts.data_ptr(), te.data_ptr(), counts.data_ptr(),
+                                           float(alpha_thre), float(early_stop_eps), native.stream_ptr()), "occ_cull")

@@ -116,7 +116,22 @@ class OccGridEstimator(torch.nn.Module):
         else:
             counts, ts, te = march_reference(rays_o.float(), rays_d.float(), jitter, self.binaries, self.roi_aabb,
                                              near_plane, far_plane, render_step_size, cone_angle, max_samples)
-        if sigma_fn is not None and alpha_thre > 0.0:
+        if sigma_fn is not None and alpha_thre > 0.0 and rays_o.is_cuda:
+            # kernel path: densities of the marched samples (the callback may take the padded block directly and build the
+            # positions with its own kernel), then one warp per ray culls and compacts in place
+            from . import ngp_field
+
+            valid = torch.arange(max_samples, device=dev)[None] < counts[:, None]
+            idx = valid.reshape(-1).nonzero(as_tuple=True)[0]
+            if idx.numel():
+                full = idx.numel() == R * max_samples
+                if hasattr(sigma_fn, "from_samples"):
+                    dens = sigma_fn.from_samples(None if full else idx, max_samples, ts, te).reshape(-1).float()
+                else:
+                    dens = sigma_fn(ts.reshape(-1)[idx], te.reshape(-1)[idx], idx // max_samples).reshape(-1).float()
+                sig = dens if full else torch.zeros(R * max_samples, device=dev).index_put_((idx,), dens)
+                ngp_field.occ_cull(sig.contiguous(), ts, te, counts, alpha_thre, early_stop_eps)
+        elif sigma_fn is not None and alpha_thre > 0.0:
             valid = torch.arange(max_samples, device=dev)[None] < counts[:, None]
             idx = valid.reshape(-1).nonzero(as_tuple=True)[0]
             if idx.numel():

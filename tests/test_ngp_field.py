@@ -134,3 +134,33 @@ def test_occupancy_refresh_kernels():
     for thre in (0.01, 10.0):
         ngp_field.occ_binarise(occs, thre, binaries.view(torch.uint8), scratch)
         assert torch.equal(binaries, occs > min(float(occs.double().mean()), thre))
+
+
+@cuda
+def test_occ_cull_kernel_matches_the_tensor_statement():
+    dev = "cuda"
+    R, S = 333, 70
+    g = torch.Generator().manual_seed(3)
+    counts = torch.randint(0, S + 1, (R,), generator=g).to(torch.int32).to(dev)
+    counts[:3] = torch.tensor([0, S, 1], dtype=torch.int32)
+    valid = torch.arange(S, device=dev)[None] < counts[:, None]
+    ts = (torch.rand(R, S, generator=g).to(dev).cumsum(1) * 0.05) * valid
+    te = (ts + 0.04) * valid
+    sigma = (torch.rand(R, S, generator=g).to(dev) ** 3 * 40.0) * valid
+    thre, eps = 0.05, 1e-3
+    alpha = 1.0 - torch.exp(-sigma * (te - ts))
+    trans = torch.cumprod(torch.cat((torch.ones_like(alpha[:, :1]), 1.0 - alpha), -1), -1)[:, :-1]
+    keep = valid & (alpha >= thre) & (trans >= eps)
+    near = ((alpha - thre).abs() < 1e-5) | ((trans - eps).abs() < 1e-6)        # decisions within rounding of a threshold
+    order = torch.argsort((~keep).to(torch.int8), dim=1, stable=True)
+    want_ts, want_te = torch.gather(ts, 1, order), torch.gather(te, 1, order)
+    want_counts = keep.sum(1).to(torch.int32)
+    got_ts, got_te, got_counts = ts.clone(), te.clone(), counts.clone()
+    ngp_field.occ_cull(sigma.contiguous(), got_ts, got_te, got_counts, thre, eps)
+    clean = ~(near & valid).any(1)
+    assert clean.float().mean() > 0.9
+    assert torch.equal(got_counts[clean], want_counts[clean])
+    front = torch.arange(S, device=dev)[None] < want_counts[:, None]
+    sel = front & clean[:, None]
+    assert torch.equal(got_ts[sel], want_ts[sel]) and torch.equal(got_te[sel], want_te[sel])
+    assert float(got_ts[~front & clean[:, None]].abs().sum()) == 0.0
