@@ -1,6 +1,8 @@
 """Parallel wrappers of the inference model (reference:
 landmark/render/parallel_module/parallel_module.py:20-157): tensor (channel) parallel conversion and the
-data-parallel scatter / gather of the leading (ray) dimension with zero padding."""
+data-parallel scatter / gather of the leading (ray) dimension with zero padding.  Unlike the reference, which hands every
+rank one contiguous band of rows, the rows are dealt round-robin (``parallel_config["dp_interleave"]``, default on) so that
+the ranks' loads match."""
 from __future__ import annotations
 
 from typing import Any, Mapping
@@ -98,8 +100,17 @@ class ParallelModule(Module):
             first = torch.cat((first, pad), dim=0)
         size = first.shape[0] // dp
         args = list(stage_input.Args)
-        args[0] = first[part * size:(part + 1) * size]
+        if self._dp_interleaved():
+            # rows dealt round-robin: every rank gets a regular subsample of the image instead of one horizontal band, so
+            # the ranks' loads match (rays near the horizon cross far more of the scene than rays looking down)
+            args[0] = first[part::dp].contiguous()
+        else:
+            args[0] = first[part * size:(part + 1) * size]
         return tuple(args), stage_input.Kwargs
+
+    def _dp_interleaved(self) -> bool:
+        cfg = self._parallel_config
+        return True if cfg is None else bool(cfg.get("dp_interleave", True))
 
     def dp_gather(self, stage_input):
         ctx, _, dp, stride = self._dp_layout()
@@ -114,6 +125,8 @@ class ParallelModule(Module):
             gathered = torch.empty((single.shape[0] * dp, *single.shape[1:]), dtype=single.dtype, device=single.device)
             if ctx.get_global_rank() % stride == 0:
                 all_gather(gathered, single, comm_mode=ParallelMode.DATA_PARALLEL)
+            if self._dp_interleaved():             # rank-major blocks back to the original row order
+                gathered = gathered.view(dp, single.shape[0], *single.shape[1:]).transpose(0, 1).reshape(gathered.shape)
             if self._dp_gap_size > 0:
                 gathered = gathered[: -self._dp_gap_size]
             outs.append(gathered)

@@ -305,3 +305,40 @@ def test_hybrid_model_and_data_parallel_groups_train_consistently(tmp_path):
     assert not torch.allclose(by[(0, 0)][0], by[(1, 0)][0], atol=1e-3)
     for key in by:
         assert torch.allclose(by[key][1], by[(0, 0)][1], atol=1e-6)
+
+
+# -- data-parallel render: rows dealt round-robin (or in bands), results back in the original order --------------------
+def _dp_scatter_gather(rank, world):
+    from landmarksystem_b200.comm import CommContext
+    from landmarksystem_b200.render.parallel_module import ParallelModule, StageArgs
+    from landmarksystem_b200.utils import Config
+
+    ctx = CommContext()
+    ctx.init_distributed_env(world_size=world, rank=rank, backend="gloo")
+    ctx.init_groups(Config(tp_size=1))
+
+    class Plain(ParallelModule):
+        def _parallize(self, model):
+            return model
+
+    rows = torch.arange(11.0)[:, None].repeat(1, 2)                 # 11 rows: padded to 12 for 2 and for 4 ranks
+    parts = {}
+    for interleave in (True, False):
+        pm = Plain(torch.nn.Identity(), Config(parallel_config=Config(tp_size=1, dp_interleave=interleave)))
+        args, _ = pm.dp_scatter(StageArgs((rows,), {}))
+        assert args[0].shape[0] == 12 // world
+        res, _ = pm.dp_gather(StageArgs((args[0] * 2.0, "kept"), {}))
+        assert torch.equal(res[0], rows * 2.0) and res[1] == "kept"
+        parts[interleave] = args[0][:, 0].tolist()
+    ctx.destroy()
+    return parts
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_data_parallel_render_scatter_gather(world):
+    out = _run(_dp_scatter_gather, world)
+    size = 12 // world
+    for rank in range(world):
+        padded = list(range(11)) + [0]
+        assert [int(v) for v in out[rank][True]] == padded[rank::world]
+        assert [int(v) for v in out[rank][False]] == padded[rank * size:(rank + 1) * size]
