@@ -70,21 +70,22 @@ class HashEncoding(VolumeEncoding):
                 FusedAdam.attach_sink(table.params, shadow=True)
                 table.params._lmb_shadow_version = table.params._version
 
-    def _encode(self, xyz: torch.Tensor, table: _Table) -> torch.Tensor:
+    def _encode(self, xyz: torch.Tensor, table: _Table, out_dtype=torch.float32, precomputed=None) -> torch.Tensor:
         p, F = table.params, self.features_per_level
         shadow, sink = getattr(p, "_lmb_shadow", None), getattr(p, "_lmb_grad_sink", None)
         if shadow is not None and xyz.is_cuda:
             if p._version != getattr(p, "_lmb_shadow_version", None):      # the master was written outside the optimiser
                 shadow.copy_(p.detach())                                    # kernel (a checkpoint load): refresh the copy
                 p._lmb_shadow_version = p._version
-            return hashgrid_encode(xyz, p.view(-1, F), self.meta, shadow=shadow.view(-1, F),
-                                   sink=None if sink is None else sink.view(-1, F))
-        return hashgrid_encode(xyz, p.view(-1, F), self.meta)
+            return hashgrid_encode(xyz, p.view(-1, F), self.meta, out_dtype, shadow=shadow.view(-1, F),
+                                   sink=None if sink is None else sink.view(-1, F), precomputed=precomputed)
+        return hashgrid_encode(xyz, p.view(-1, F), self.meta, out_dtype, precomputed=precomputed)
 
-    def forward(self, xyz: torch.Tensor) -> torch.Tensor:
-        """``xyz [N, 3]`` in ``[0, 1]`` or ``[N, 4]`` with the block index in the last column."""
+    def forward(self, xyz: torch.Tensor, out_dtype=torch.float32, precomputed=None) -> torch.Tensor:
+        """``xyz [N, 3]`` in ``[0, 1]`` or ``[N, 4]`` with the block index in the last column.  ``out_dtype`` /
+        ``precomputed`` (single table only): see :func:`landmarksystem_b200.ops.hashgrid.hashgrid_encode`."""
         if xyz.shape[-1] == 3 or self.num_hash_table == 1:
-            return self._encode(xyz[:, :3], self.tables()[0])
+            return self._encode(xyz[:, :3], self.tables()[0], out_dtype, precomputed)
         block = xyz[:, 3].long()
         out = torch.zeros(xyz.shape[0], self.meta.out_dim, device=xyz.device, dtype=torch.float32)
         for b, table in enumerate(self.tables()):

@@ -45,7 +45,7 @@ class MLPDecoder(BaseModule):
     def linears(self):
         return [m for m in self.mlp if isinstance(m, torch.nn.Linear)]
 
-    def forward(self, features) -> torch.Tensor:
+    def forward(self, features, precomputed: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``features``: ``[N, K]`` or a sequence of ``[N, k_i]`` parts (concatenated along the last dimension; the
         fused path writes them straight into the kernel's bf16 input instead of materialising the concatenation)."""
         first = features[0] if isinstance(features, (tuple, list)) else features
@@ -53,7 +53,7 @@ class MLPDecoder(BaseModule):
             from ...ops.fused_mlp import fused_mlp_supported, mlp_forward
 
             if fused_mlp_supported(self):
-                return mlp_forward(self, features)
+                return mlp_forward(self, features, precomputed)
         if isinstance(features, (tuple, list)):
             features = torch.cat([f.to(first.dtype) for f in features], dim=-1)
         return self.mlp(features)

@@ -105,7 +105,12 @@ class _FieldDensity:
         xyzb, inside = ngp_field.sample_positions(idx, samples_per_ray, origins.contiguous().float(),
                                                   directions.contiguous().float(), z, m.aabb, m._aabb_host,
                                                   int(m.plane_division[0]), int(m.plane_division[1]))
-        h = m.mlp_base_mlp(m.mlp_base_grid(xyzb))
+        single = m.mlp_base_grid.num_hash_table == 1
+        feat = m.mlp_base_grid(xyzb, out_dtype=torch.bfloat16) if single else m.mlp_base_grid(xyzb)
+        h = m.mlp_base_mlp(feat)
+        # the step's own forward evaluates the survivors of the culling at the same positions with the same weights:
+        # it takes the features and the head's output from here instead of looking them up again
+        m._cull_cache = {"feat": feat, "h": h} if (single and m.training) else None
         return torch.exp(h[:, 0].float()) * inside
 
 
@@ -169,6 +174,26 @@ class InstantNGP(BaseNeRF):
             block = torch.zeros_like(block)
             local = local * mine[:, None]
         return torch.cat((local, block[:, None]), -1), inside
+
+    def _cached_field_rows(self, idx, samples_per_ray: int):
+        """Rows of the sampler's density query (this step, same weights) that belong to the samples ``idx`` that
+        survived the culling: ``(hash features bf16 [M, L*F], density-head output fp32 [M, 1+G])`` or ``(None, None)``."""
+        cache, self._cull_cache = getattr(self, "_cull_cache", None), None
+        cull = getattr(self.occupancy_grid, "last_cull", None)
+        if cache is None or cull is None or not torch.is_grad_enabled():
+            return None, None
+        feat, h = cache["feat"], cache["h"]
+        if feat.shape[0] != cull["n_queried"]:
+            return None, None
+        if idx.numel() == cull["n_queried"]:
+            return feat, h                          # nothing was culled; the compaction keeps the order
+        ray = idx // samples_per_ray
+        before = ray * samples_per_ray + cull["source"].reshape(-1)[idx].long()       # flat index before the compaction
+        if cull["queried"] is not None:
+            where = torch.full((cull["source"].numel(),), -1, dtype=torch.long, device=idx.device)
+            where[cull["queried"]] = torch.arange(cull["n_queried"], device=idx.device)
+            before = where[before]
+        return feat[before], h[before]
 
     def _kernel_glue(self, rays) -> bool:
         """The per-sample glue runs as kernels when both heads are on the fused MLP path and no cross-rank sum sits
@@ -235,7 +260,13 @@ class InstantNGP(BaseNeRF):
             o32, d32 = o.contiguous().float(), dvec.contiguous().float()
             xyzb, inside = ngp_field.sample_positions(kidx, S, o32, d32, z_vals.reshape(-1).contiguous().float(), self.aabb,
                                                       self._aabb_host, int(self.plane_division[0]), int(self.plane_division[1]))
-            h = self.mlp_base_mlp(self.mlp_base_grid(xyzb)).float()
+            feat_pre, h_pre = self._cached_field_rows(idx, S)
+            if self.mlp_base_grid.num_hash_table == 1:
+                # bf16 rows straight from the lookup kernel: what the head kernel reads and its backward returns
+                feat = self.mlp_base_grid(xyzb, out_dtype=torch.bfloat16, precomputed=feat_pre)
+            else:
+                feat = self.mlp_base_grid(xyzb)
+            h = self.mlp_base_mlp(feat, precomputed=h_pre).float()
             per_ray = None
             if self.training:
                 cam = rays[:, 6] if rays.shape[1] > 6 else torch.zeros(R, device=rays.device)

@@ -78,37 +78,47 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
   const int bar_id = 1 + slot;
   uint32_t ph_in = 0, ph_mma = 0;
 
-  for (long long tile = (long long)blockIdx.x * kSlots + slot; ok && tile < n_tiles; tile += (long long)gridDim.x * kSlots) {
-    const long long row0 = tile * kTileRows;
-    // ---- input tile: one TMA box [8 elems, 1 chunk, 128 rows] per 16-byte column chunk -------------
-    if (row == 0 && whole_rows) {
-      tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
+  // Input tile of a slot: whole rows in the swizzled layouts (single local source) or one box [8 columns x 128 rows] per
+  // 16-byte column chunk (several sources).  Issued by the slot's first thread.
+  auto issue_input = [&](long long t) {
+    const long long r0 = t * kTileRows;
+    tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
+    if (whole_rows) {
       for (int a = 0; a < inputs.n128; ++a)
-        tc05::tma_load_2d(act + (size_t)a * kTileRows * 128, &inputs.map[0], a * 64, (int)row0, &bar_in[slot]);
+        tc05::tma_load_2d(act + (size_t)a * kTileRows * 128, &inputs.map[0], a * 64, (int)r0, &bar_in[slot]);
       if (inputs.n64)
-        tc05::tma_load_2d(act + (size_t)inputs.n128 * kTileRows * 128, &inputs.map[1], inputs.n128 * 64, (int)row0, &bar_in[slot]);
-    } else if (row == 0) {
-      tc05::mbar_expect_tx(&bar_in[slot], in_bytes);
+        tc05::tma_load_2d(act + (size_t)inputs.n128 * kTileRows * 128, &inputs.map[1], inputs.n128 * 64, (int)r0, &bar_in[slot]);
+    } else {
       int src = 0;
       for (int c = 0; c < in_chunks; ++c) {
         while (src + 1 < inputs.n_src && c >= inputs.chunk_begin[src + 1]) ++src;
-        tc05::tma_load_3d(act + (size_t)c * kTileRows * 16, &inputs.map[src], 0, c - inputs.chunk_begin[src], (int)row0,
+        tc05::tma_load_3d(act + (size_t)c * kTileRows * 16, &inputs.map[src], 0, c - inputs.chunk_begin[src], (int)r0,
                           &bar_in[slot]);
       }
     }
+  };
+  const long long tile_stride = (long long)gridDim.x * kSlots;
+  const long long first_tile = (long long)blockIdx.x * kSlots + slot;
+  // The copy of a slot's NEXT tile is issued as soon as the last layer's MMA of the current tile has read the buffer, so
+  // it runs under the last epilogue instead of in front of the next tile (measured: 2 500 cycles of exposed wait per tile).
+  bool in_flight = ok && first_tile < n_tiles;
+  if (in_flight && row == 0) issue_input(first_tile);
+
+  for (long long tile = first_tile; ok && tile < n_tiles; tile += tile_stride) {
+    const long long row0 = tile * kTileRows;
+    float dir[3] = {0.f, 0.f, 0.f};
+    if (spec.pe_stage && whole_rows && row0 + row < n_rows) {
+      // the tile arrives in the swizzled layout: the three direction values come from the row in global memory, and
+      // the loads are in flight while the thread waits for the tile
+      const __nv_bfloat16* dp = inputs.x0 + (row0 + row) * (long long)spec.in_width + spec.dir_col;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) dir[i] = __bfloat162float(dp[i]);
+    }
     bool got = tc05::mbar_wait(&bar_in[slot], ph_in);
     ph_in ^= 1;
+    in_flight = false;
     if (!tc05::bar_and(bar_id, kSlotThreads, got)) { if (row == 0) atomicExch(status, 2); ok = false; break; }
-
-    float dir[3] = {0.f, 0.f, 0.f};
-    if (spec.pe_stage && whole_rows) {
-      // the tile sits in the swizzled layout: take the three direction values from the row in global memory instead
-      if (row0 + row < n_rows) {
-        const __nv_bfloat16* dp = inputs.x0 + (row0 + row) * (long long)spec.in_width + spec.dir_col;
-#pragma unroll
-        for (int i = 0; i < 3; ++i) dir[i] = __bfloat162float(dp[i]);
-      }
-    } else if (spec.pe_stage) {
+    if (spec.pe_stage && !whole_rows) {
 #pragma unroll
       for (int i = 0; i < 3; ++i) dir[i] = load_elem(act, spec.dir_col + i, row);
     }
@@ -121,17 +131,34 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
         const uint32_t a_addr = tc05::smem_u32(act);
         const uint32_t b_addr = tc05::smem_u32(wsm + sWoff[l]);
         const uint32_t idesc = tc05::idesc_bf16(N, false, false);
-        for (int k = 0; k < K; k += 16) {
-          uint64_t da;
-          if (l == 0 && whole_rows) {
-            const int k128 = inputs.n128 * 64;
-            da = k < k128 ? tc05::smem_desc_swizzled(a_addr + (uint32_t)(k >> 6) * (kTileRows * 128) + (uint32_t)(k & 63) * 2, 1024, 2)
-                          : tc05::smem_desc_swizzled(a_addr + (uint32_t)inputs.n128 * (kTileRows * 128) + (uint32_t)(k - k128) * 2, 512, 4);
-          } else {
-            da = tc05::smem_desc(a_addr + (uint32_t)(k >> 3) * (kTileRows * 16), kTileRows * 16, 128);
+        // One thread issues K/16 MMAs; their shared-memory descriptors differ only in the start-address field (bits
+        // 0-13, in 16-byte units), so each step is an add instead of a rebuilt descriptor - this thread's issue loop
+        // is in front of every layer of the slot.
+        uint64_t db = tc05::smem_desc(b_addr, (uint32_t)(N * 16), 128);
+        const uint64_t db_step = (uint64_t)((2 * N * 16) >> 4);             // two 8-column weight chunks per step
+        if (l == 0 && whole_rows) {
+          int k = 0;
+          for (int a = 0; a < inputs.n128 && k < K; ++a) {                   // 64-column pieces, 128-byte swizzle
+            uint64_t da = tc05::smem_desc_swizzled(a_addr + (uint32_t)a * (kTileRows * 128), 1024, 2);
+            for (int j = 0; j < 4 && k < K; ++j, k += 16) {
+              tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
+              da += 2; db += db_step;                                        // 16 columns = 32 bytes inside the row
+            }
           }
-          const uint64_t db = tc05::smem_desc(b_addr + (uint32_t)(k >> 3) * (uint32_t)(N * 16), (uint32_t)(N * 16), 128);
-          tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
+          if (k < K) {                                                       // last piece, 64-byte swizzle
+            uint64_t da = tc05::smem_desc_swizzled(a_addr + (uint32_t)inputs.n128 * (kTileRows * 128), 512, 4);
+            for (; k < K; k += 16) {
+              tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
+              da += 2; db += db_step;
+            }
+          }
+        } else {
+          uint64_t da = tc05::smem_desc(a_addr, kTileRows * 16, 128);
+          const uint64_t da_step = (uint64_t)((2 * kTileRows * 16) >> 4);   // two 8-column activation chunks per step
+          for (int k = 0; k < K; k += 16) {
+            tc05::mma_ss(tmem_slot, da, db, idesc, k > 0);
+            da += da_step; db += db_step;
+          }
         }
         tc05::mma_commit(&bar_mma[slot]);
       }
@@ -139,11 +166,15 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
       ph_mma ^= 1;
       if (!tc05::bar_and(bar_id, kSlotThreads, done)) { if (row == 0) atomicExch(status, 3); ok = false; break; }
       tc05::fence_after_sync();
+      const bool last = (l == spec.n_layers - 1);
+      if (last && tile + tile_stride < n_tiles) {        // the activation buffer is dead: fetch the slot's next tile
+        if (row == 0) issue_input(tile + tile_stride);
+        in_flight = true;
+      }
 
       // ---- epilogue -------------------------------------------------------------------------------
-      const float* bias = sBoff[l] >= 0 ? reinterpret_cast<const float*>(wsm + sBoff[l]) : nullptr;
+      const float* bias = (sBoff[l] >= 0 && !((spec.bias_in_gemm >> l) & 1)) ? reinterpret_cast<const float*>(wsm + sBoff[l]) : nullptr;
       const int act_l = sAct[l];
-      const bool last = (l == spec.n_layers - 1);
       if (spec.pe_stage && l == 0) {
         // f = first 27 accumulator columns; expand to the 150-wide decoder input, in place
         float f[32];
@@ -173,8 +204,9 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
           x[138 + 2 * i] = s1; x[139 + 2 * i] = s2;
           x[144 + 2 * i] = c1; x[145 + 2 * i] = c2;
         }
+        x[150] = 1.f;                               // ones column: multiplies the bias column of the next layer's weights
 #pragma unroll
-        for (int i = 150; i < 160; ++i) x[i] = 0.f;
+        for (int i = 151; i < 160; ++i) x[i] = 0.f;
 #pragma unroll
         for (int c = 0; c < 20; ++c) store_chunk(act, c, row, x + 8 * c);
       } else {
@@ -201,10 +233,13 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
 #pragma unroll
               for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
               break;
-            case ACT_SIGMOID:
+            case ACT_SIGMOID: {
+              const int need = last ? spec.out_dim - n0 : 16;       // the output layer is padded to 16 columns
 #pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = __fdividef(1.f, 1.f + __expf(-v[i]));
+              for (int i = 0; i < 16; ++i)
+                if (i < need) v[i] = __fdividef(1.f, 1.f + __expf(-v[i]));
               break;
+            }
             case ACT_TANH:
 #pragma unroll
               for (int i = 0; i < 16; ++i) v[i] = tanhf(v[i]);
@@ -244,6 +279,14 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
           tc05::tmem_ld16(tmem_lane + n0, v);
           finish16(v, n0);
         }
+        if (!last && sK[l + 1] > N) {
+          // the next layer reads more columns than this one produced: a ones column (its weights carry the bias there)
+          // followed by zeros
+          float fill[8] = {1.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          store_chunk(act, N >> 3, row, fill);
+          fill[0] = 0.f;
+          for (int c = (N >> 3) + 1; c < (sK[l + 1] >> 3); ++c) store_chunk(act, c, row, fill);
+        }
       }
       // TMEM reads and shared-memory writes of this slot are complete before the next MMA / TMA
       tc05::fence_before_sync();
@@ -252,6 +295,8 @@ fused_mlp_kernel(const __grid_constant__ MLPInputs inputs, const unsigned char* 
     }
   }
 
+  // a bounded wait gave up with the next tile's copy still in flight: let it land before shared memory is released
+  if (in_flight) tc05::mbar_wait(&bar_in[slot], ph_in);
   tc05::fence_before_sync();
   __syncthreads();
   if (tid < 32) tc05::tmem_dealloc(tmem_base_sh, 512);

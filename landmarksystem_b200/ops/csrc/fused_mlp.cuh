@@ -27,6 +27,8 @@ struct MLPSpec {
   int out_dim;              // number of valid output columns of the last layer
   int pe_stage;             // 1: GridNeRF colour expansion between layer 0 and layer 1
   int dir_col;              // column of the input row that holds the view direction (pe_stage)
+  int bias_in_gemm;         // bit l: layer l's bias is a column of its weights, multiplied by a ones column that the
+                            // kernels write into the layer's input (or it is zero): the epilogue adds nothing
 };
 
 // Input rows may be assembled from several tensors ("sources"), each contributing a contiguous range of

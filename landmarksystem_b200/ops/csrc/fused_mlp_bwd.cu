@@ -161,6 +161,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
   const float* b2 = reinterpret_cast<const float*>(wsm + spec.b_off[L1 + 1]);
   const float* b3 = reinterpret_cast<const float*>(wsm + spec.b_off[L1 + 2]);
   const bool out_sigmoid = spec.act[L1 + 2] == ACT_SIGMOID;
+  // biases that ride in the GEMM (a column of the weights against the ones column of the layer's input) or are zero
+  const bool skip_b1 = (spec.bias_in_gemm >> L1) & 1, skip_b2 = (spec.bias_in_gemm >> (L1 + 1)) & 1;
+  const int k_fwd2 = (skip_b2 && spec.K[L1 + 1] == 144) ? 144 : 128;
   const int n_out = kPE ? 3 : spec.out_dim;
   (void)aW0;
 
@@ -271,10 +274,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     for (int n0 = 0; n0 < 128; n0 += 64) {                       // 64 accumulator columns per wait: load latencies overlap
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
+      if (!skip_b1) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {               // four biases per shared-memory load
-        const float4 b4 = *reinterpret_cast<const float4*>(b1 + n0 + i);
-        v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        for (int i = 0; i < 64; i += 4) {             // four biases per shared-memory load
+          const float4 b4 = *reinterpret_cast<const float4*>(b1 + n0 + i);
+          v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        }
       }
 #pragma unroll
       for (int c = 0; c < 8; ++c) store_chunk_relu(bufH1, (n0 >> 3) + c, row, v + 8 * c);   // relu inside the bf16 packing
@@ -288,15 +293,17 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     }
     LMB_EPILOGUE_DONE();
 
-    if (row == 0) issue_fwd(tmem + kColWork, aH1, aW2, 128, 128);
+    if (row == 0) issue_fwd(tmem + kColWork, aH1, aW2, k_fwd2, 128);      // 144: the ones chunk of h1 times the bias column
     LMB_MMA_WAIT();
     for (int n0 = 0; n0 < 128; n0 += 64) {
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
+      if (!skip_b2) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        const float4 b4 = *reinterpret_cast<const float4*>(b2 + n0 + i);
-        v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        for (int i = 0; i < 64; i += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(b2 + n0 + i);
+          v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        }
       }
 #pragma unroll
       for (int c = 0; c < 8; ++c) store_chunk_relu(bufHZ, (n0 >> 3) + c, row, v + 8 * c);
@@ -591,7 +598,7 @@ LMB_API int lmb_rgb_mlp_bwd(const void* x, const int* count_ptr, long long max_r
   const MLPSpec& s = *spec;
   // the kernel is specialised to the colour-head shape; anything else is refused
   if (s.n_layers != 4 || !s.pe_stage || s.in_width != 160 || s.K[0] % 16 || s.K[0] < 16 || s.K[0] > 144 || s.N[0] != 32 ||
-      s.K[1] != 160 || s.N[1] != 128 || s.K[2] != 128 || s.N[2] != 128 || s.K[3] != 128 || s.N[3] != 16 || s.out_dim != 3 ||
+      s.K[1] != 160 || s.N[1] != 128 || (s.K[2] != 128 && s.K[2] != 144) || s.N[2] != 128 || s.K[3] != 128 || s.N[3] != 16 || s.out_dim != 3 ||
       s.b_off[0] >= 0 || s.b_off[1] < 0 || s.b_off[2] < 0 || s.b_off[3] < 0 || s.blob_bytes % 16 ||
       s.act[1] != ACT_RELU || s.act[2] != ACT_RELU || s.act[3] != ACT_SIGMOID || s.dir_col + 3 > 160)
     return (int)cudaErrorInvalidValue;

@@ -354,7 +354,7 @@ occ_threshold_kernel(long long n, const float* __restrict__ occs, const double* 
 // carry, positions by ballot.  In place: a row is read 32 samples at a time and written at or before where it is read.
 __global__ void __launch_bounds__(256)
 occ_cull_kernel(int R, int S, const float* __restrict__ sigma, float* __restrict__ ts, float* __restrict__ te,
-                int* __restrict__ counts, float alpha_thre, float early_stop_eps) {
+                int* __restrict__ counts, float alpha_thre, float early_stop_eps, int* __restrict__ src) {
   const int ray = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
   const int lane = threadIdx.x & 31;
   if (ray >= R) return;
@@ -384,6 +384,7 @@ occ_cull_kernel(int R, int S, const float* __restrict__ sigma, float* __restrict
     if (keep) {
       const int pos = kept + __popc(won & ((1u << lane) - 1u));
       ts[base + pos] = t0; te[base + pos] = t1;
+      if (src) src[base + pos] = s;              // where the survivor sat before: lets a caller reuse per-sample results
     }
     kept += __popc(won);
     carry *= __shfl_sync(0xffffffffu, incl, 31);
@@ -490,10 +491,11 @@ LMB_API int lmb_occ_binarise(long long n, const float* occs, float threshold, do
 }
 
 // sigma: fp32 [R, S] (values past counts[r] ignored); ts / te: fp32 [R, S], compacted in place; counts: int32 [R], updated
+// src (may be null): int32 [R, S], slot of every survivor before the compaction
 LMB_API int lmb_occ_cull(int R, int S, const float* sigma, float* ts, float* te, int* counts, float alpha_thre,
-                         float early_stop_eps, cudaStream_t stream) {
+                         float early_stop_eps, int* src, cudaStream_t stream) {
   if (R <= 0) return 0;
-  occ_cull_kernel<<<ceil_div((long long)R * 32, 256), 256, 0, stream>>>(R, S, sigma, ts, te, counts, alpha_thre, early_stop_eps);
+  occ_cull_kernel<<<ceil_div((long long)R * 32, 256), 256, 0, stream>>>(R, S, sigma, ts, te, counts, alpha_thre, early_stop_eps, src);
   LMB_LAUNCH_CHECK();
   return 0;
 }

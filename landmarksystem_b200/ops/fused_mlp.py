@@ -28,7 +28,7 @@ ACT = {"none": 0, "relu": 1, "sigmoid": 2, "tanh": 3, "exp": 4}
 class MLPSpec(Structure):
     _fields_ = [("n_layers", c_int), ("K", c_int * MAX_LAYERS), ("N", c_int * MAX_LAYERS), ("act", c_int * MAX_LAYERS),
                 ("w_off", c_int * MAX_LAYERS), ("b_off", c_int * MAX_LAYERS), ("blob_bytes", c_int),
-                ("in_width", c_int), ("out_dim", c_int), ("pe_stage", c_int), ("dir_col", c_int)]
+                ("in_width", c_int), ("out_dim", c_int), ("pe_stage", c_int), ("dir_col", c_int), ("bias_in_gemm", c_int)]
 
 
 native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P,
@@ -51,10 +51,13 @@ def _act_name(module) -> str:
     return {"relu": "relu", "sigmoid": "sigmoid", "tanh": "tanh"}.get(name, "unsupported")
 
 
-def pack_weight(w: torch.Tensor, n_pad: int, k_pad: int) -> torch.Tensor:
-    """``[N, K]`` -> bf16 ``[k_pad/8, n_pad, 8]`` flattened (zero padded)."""
+def pack_weight(w: torch.Tensor, n_pad: int, k_pad: int, bias: Optional[torch.Tensor] = None,
+                bias_col: Optional[int] = None) -> torch.Tensor:
+    """``[N, K]`` -> bf16 ``[k_pad/8, n_pad, 8]`` flattened (zero padded); ``bias`` goes into column ``bias_col``."""
     full = torch.zeros(n_pad, k_pad, device=w.device, dtype=torch.float32)
     full[: w.shape[0], : w.shape[1]] = w.detach().float()
+    if bias is not None:
+        full[: bias.shape[0], bias_col] = bias.detach().float()
     return full.view(n_pad, k_pad // 8, 8).permute(1, 0, 2).contiguous().to(torch.bfloat16).view(-1)
 
 
@@ -62,7 +65,11 @@ class PackedMLP:
     """Device blob + spec for a list of ``(weight [N,K], bias or None, activation)`` layers."""
 
     def __init__(self, layers: Sequence[Tuple[torch.Tensor, Optional[torch.Tensor], str]], in_width: int,
-                 out_dim: int, pe_stage: bool = False, dir_col: int = 0, k_override: Optional[List[int]] = None):
+                 out_dim: int, pe_stage: bool = False, dir_col: int = 0, k_override: Optional[List[int]] = None,
+                 bias_cols: Optional[dict] = None):
+        """``bias_cols``: ``{layer: column}`` - the layer's bias is written into that (otherwise zero) column of its padded
+        weights, which the kernels multiply with a ones column of the layer's input, so the epilogue adds nothing."""
+        self.bias_cols = bias_cols or {}
         self.layers = layers
         self.in_width, self.out_dim, self.pe_stage, self.dir_col, self.k_override = in_width, out_dim, pe_stage, dir_col, k_override
         self.versions = None
@@ -87,7 +94,11 @@ class PackedMLP:
             n_pad = _pad16(w.shape[0])
             assert k_pad <= MAX_K and n_pad <= MAX_N, "layer too wide for the fused kernel"
             spec.K[l], spec.N[l], spec.act[l] = k_pad, n_pad, ACT[act]
-            packed = pack_weight(w, n_pad, k_pad).view(torch.uint8)
+            col = self.bias_cols.get(l) if b is not None else None
+            if col is not None:
+                assert w.shape[1] <= col < k_pad, "bias column must lie in the zero padding of the weights"
+                spec.bias_in_gemm |= 1 << l
+            packed = pack_weight(w, n_pad, k_pad, b if col is not None else None, col).view(torch.uint8)
             spec.w_off[l] = off
             parts.append(packed)
             off += packed.numel()
@@ -217,6 +228,8 @@ class _PackedMLP3:
             parts.append(bias.view(torch.uint8))
             off += n_pad * 4
         spec.blob_bytes, spec.in_width, spec.out_dim, spec.pe_stage, spec.dir_col = off, MLP3_IN, w3.shape[0], 0, 0
+        # layers without a bias (the hash-grid heads): the kernel skips the bias adds of its recompute epilogues
+        spec.bias_in_gemm = (1 if b1 is None else 0) | (2 if b2 is None else 0)
         self.blob, self.spec, self.key = torch.cat(parts).contiguous(), spec, key
         if self.status is None:
             self.status = torch.zeros(1, device=dev, dtype=torch.int32)
@@ -277,9 +290,11 @@ def mlp3_backward(packed: "PackedMLP", x: torch.Tensor, dout: torch.Tensor):
 
 class _FusedMLPFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, packed, n_params, *params):
+    def forward(ctx, x, packed, n_params, precomputed, *params):
         ctx.packed, ctx.n_params = packed, n_params
         ctx.save_for_backward(x, *params)
+        if precomputed is not None:           # the same rows went through the same weights earlier in this step
+            return precomputed.view_as(precomputed)
         return packed.run(x)
 
     @staticmethod
@@ -288,7 +303,7 @@ class _FusedMLPFn(torch.autograd.Function):
         packed = ctx.packed
         if MLP3_BACKWARD_KERNEL and mlp3_backward_supported(packed):
             dx, grads = mlp3_backward(packed, x, dout)
-            return (dx if ctx.needs_input_grad[0] else None, None, None, *grads)
+            return (dx if ctx.needs_input_grad[0] else None, None, None, None, *grads)
         with torch.enable_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             xin = x.detach().requires_grad_(x.is_floating_point())
             leaves = [p.detach().requires_grad_() for p in params]
@@ -298,7 +313,7 @@ class _FusedMLPFn(torch.autograd.Function):
             k0 = packed.layers[0][0].shape[1]
             out = _torch_mlp(xin[:, :k0], pairs, [a for _, _, a in packed.layers]).float()
             grads = torch.autograd.grad(out[:, : packed.out_dim], [xin] + leaves, dout, allow_unused=True)
-        return (grads[0], None, None, *grads[1:])
+        return (grads[0], None, None, None, *grads[1:])
 
 
 class _CatPadBf16(torch.autograd.Function):
@@ -327,9 +342,10 @@ class _CatPadBf16(torch.autograd.Function):
         return (None, *grads)
 
 
-def mlp_forward(decoder, features) -> torch.Tensor:
+def mlp_forward(decoder, features, precomputed: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``features``: ``[N, K]`` tensor or a sequence of ``[N, k_i]`` tensors that are concatenated along the last
-    dimension while the kernel's bf16 input is written."""
+    dimension while the kernel's bf16 input is written.  ``precomputed``: the network's fp32 output for exactly these
+    rows, evaluated earlier with the same weights - no forward launch, the backward is recorded as usual."""
     packed = getattr(decoder, "_lmb_packed", None)
     layers = _decoder_layers(decoder)
     in_width = (layers[0][0].shape[1] + 7) // 8 * 8
@@ -344,8 +360,8 @@ def mlp_forward(decoder, features) -> torch.Tensor:
         x = features.contiguous()
     params = [t for w, b, _ in layers for t in ((w, b) if b is not None else (w,))]
     if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
-        return _FusedMLPFn.apply(x, packed, len(params), *params)
-    return packed.run(x)
+        return _FusedMLPFn.apply(x, packed, len(params), precomputed, *params)
+    return precomputed if precomputed is not None else packed.run(x)
 
 
 # -- GridNeRF colour head ---------------------------------------------------------------------------
@@ -367,9 +383,14 @@ def _rgb_packed(decoder) -> PackedMLP:
         lin = decoder.decoder.linears()
         layers = [(decoder.basis_mat.weight, None, "none"), (lin[0].weight, lin[0].bias, "relu"),
                   (lin[1].weight, lin[1].bias, "relu"), (lin[2].weight, lin[2].bias, "sigmoid")]
+        # the two hidden layers' biases ride in the GEMMs: column 150 of the first (the expansion stage writes a one
+        # there), column 128 of the second (its input gets a ones chunk behind the 128 activations: K = 144)
+        hidden = lin[1].weight.shape[1]
+        fold2 = lin[1].bias is not None and _pad16(hidden) + 16 <= MAX_K
         packed = PackedMLP(layers, in_width=RGB_IN_WIDTH, out_dim=3, pe_stage=True, dir_col=144,
-                           k_override=[_pad16(decoder.basis_mat.weight.shape[1]), 160, _pad16(lin[1].weight.shape[1]),
-                                       _pad16(lin[2].weight.shape[1])])
+                           k_override=[_pad16(decoder.basis_mat.weight.shape[1]), 160, _pad16(hidden) + (16 if fold2 else 0),
+                                       _pad16(lin[2].weight.shape[1])],
+                           bias_cols={1: 150, **({2: _pad16(hidden)} if fold2 else {})})
         decoder._lmb_packed = packed
     return packed
 

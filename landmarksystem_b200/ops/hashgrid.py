@@ -114,13 +114,19 @@ native.register_signature("lmb_hashgrid_bwd", [native.P, native.c_longlong, nati
 
 class _HashGrid(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, table, meta, out_dtype, shadow, sink):
+    def forward(ctx, x, table, meta, out_dtype, shadow, sink, precomputed):
         read = shadow if shadow is not None else table
-        out = torch.empty((x.shape[0], meta.out_dim), device=x.device, dtype=out_dtype)
-        ms = _meta_struct(meta)
-        native.check(native.lib().lmb_hashgrid_fwd(x.data_ptr(), x.shape[0], read.data_ptr(),
-                                                   native.DTYPE_CODE[read.dtype], ctx_ref(ms), out.data_ptr(),
-                                                   native.DTYPE_CODE[out_dtype], native.stream_ptr()), "hashgrid_fwd")
+        if precomputed is not None:
+            # the caller already looked these samples up with the same table (the sampler's density query of this
+            # step): only the backward runs here
+            assert precomputed.shape == (x.shape[0], meta.out_dim)
+            out = precomputed.view_as(precomputed)
+        else:
+            out = torch.empty((x.shape[0], meta.out_dim), device=x.device, dtype=out_dtype)
+            ms = _meta_struct(meta)
+            native.check(native.lib().lmb_hashgrid_fwd(x.data_ptr(), x.shape[0], read.data_ptr(),
+                                                       native.DTYPE_CODE[read.dtype], ctx_ref(ms), out.data_ptr(),
+                                                       native.DTYPE_CODE[out_dtype], native.stream_ptr()), "hashgrid_fwd")
         ctx.save_for_backward(x)
         ctx.meta, ctx.table, ctx.sink = meta, table, sink
         return out
@@ -136,7 +142,7 @@ class _HashGrid(torch.autograd.Function):
         native.check(native.lib().lmb_hashgrid_bwd(x.data_ptr(), x.shape[0], ctx_ref(ms), dout.data_ptr(),
                                                    native.DTYPE_CODE[dout.dtype], grad.data_ptr(),
                                                    native.stream_ptr()), "hashgrid_bwd")
-        return None, (None if sink is not None else grad), None, None, None, None
+        return None, (None if sink is not None else grad), None, None, None, None, None
 
 
 def ctx_ref(struct):
@@ -146,11 +152,13 @@ def ctx_ref(struct):
 
 
 def hashgrid_encode(x: torch.Tensor, table: torch.Tensor, meta: HashGridMeta, out_dtype: torch.dtype = torch.float32,
-                    shadow: torch.Tensor = None, sink: torch.Tensor = None) -> torch.Tensor:
+                    shadow: torch.Tensor = None, sink: torch.Tensor = None, precomputed: torch.Tensor = None) -> torch.Tensor:
     """``shadow``: bf16 copy of ``table`` for the kernel to read; ``sink``: persistent fp32 accumulator that receives the
-    table gradient instead of a fresh tensor (both default to the attributes a fused optimiser attached to ``table``)."""
+    table gradient instead of a fresh tensor (both default to the attributes a fused optimiser attached to ``table``);
+    ``precomputed``: the result of an earlier lookup of the same samples with the same table - returned as is, so that only
+    the backward is computed."""
     if not x.is_cuda:
         return hashgrid_reference(x, table, meta).to(out_dtype)
     if shadow is None:
         shadow = getattr(table, "_lmb_shadow", None)
-    return _HashGrid.apply(x.contiguous().float(), table, meta, out_dtype, shadow, sink)
+    return _HashGrid.apply(x.contiguous().float(), table, meta, out_dtype, shadow, sink, precomputed)

@@ -26,7 +26,7 @@ native.register_signature("lmb_ngp_head_rows_bwd", [c_longlong, P, c_int, P, P, 
 native.register_signature("lmb_occ_cells", [c_longlong, P, c_int, P, c_int, c_uint, c_int, P, c_float, P, P, P])
 native.register_signature("lmb_occ_update", [c_longlong, P, P, P, P, P])
 native.register_signature("lmb_occ_binarise", [c_longlong, P, c_float, P, P, P])
-native.register_signature("lmb_occ_cull", [c_int, c_int, P, P, P, P, c_float, c_float, P])
+native.register_signature("lmb_occ_cull", [c_int, c_int, P, P, P, P, c_float, c_float, P, P])
 
 SH_WIDTH = 16
 
@@ -185,10 +185,14 @@ def occ_binarise(occs: torch.Tensor, threshold: float, binaries_u8: torch.Tensor
 
 @torch.no_grad()
 def occ_cull(sigma: torch.Tensor, ts: torch.Tensor, te: torch.Tensor, counts: torch.Tensor, alpha_thre: float,
-             early_stop_eps: float) -> None:
+             early_stop_eps: float, want_source: bool = False) -> Optional[torch.Tensor]:
     """In place: per ray keep the samples with opacity ``1 - exp(-sigma * (te - ts)) >= alpha_thre`` and transmittance in
     front of them ``>= early_stop_eps``, moved to the front of the row in order; ``counts`` becomes the survivors' count.
-    ``sigma``, ``ts``, ``te``: fp32 ``[R, S]`` contiguous; ``counts``: int32 ``[R]``."""
+    ``sigma``, ``ts``, ``te``: fp32 ``[R, S]`` contiguous; ``counts``: int32 ``[R]``.  ``want_source``: also return int32
+    ``[R, S]`` with the slot every survivor had before the compaction (entries past ``counts`` undefined)."""
     R, S = ts.shape
+    src = torch.empty(R, S, dtype=torch.int32, device=ts.device) if want_source else None
     native.check(native.lib().lmb_occ_cull(R, S, sigma.data_ptr(), ts.data_ptr(), te.data_ptr(), counts.data_ptr(),
-                                           float(alpha_thre), float(early_stop_eps), native.stream_ptr()), "occ_cull")
+                                           float(alpha_thre), float(early_stop_eps), native.ptr(src), native.stream_ptr()),
+                 "occ_cull")
+    return src

@@ -100,6 +100,7 @@ class OccGridEstimator(torch.nn.Module):
         lie behind an (almost) opaque prefix, are dropped and the survivors are compacted to the front."""
         R = rays_o.shape[0]
         dev = rays_o.device
+        self.last_cull = None
         jitter = torch.rand(R, device=dev) if stratified else None
         if rays_o.is_cuda:
             counts = torch.empty(R, dtype=torch.int32, device=dev)
@@ -130,7 +131,10 @@ class OccGridEstimator(torch.nn.Module):
                 else:
                     dens = sigma_fn(ts.reshape(-1)[idx], te.reshape(-1)[idx], idx // max_samples).reshape(-1).float()
                 sig = dens if full else torch.zeros(R * max_samples, device=dev).index_put_((idx,), dens)
-                ngp_field.occ_cull(sig.contiguous(), ts, te, counts, alpha_thre, early_stop_eps)
+                src = ngp_field.occ_cull(sig.contiguous(), ts, te, counts, alpha_thre, early_stop_eps, want_source=True)
+                # which marched sample every survivor was: a field that cached per-sample results of the density query
+                # can reuse them for the survivors (``queried``: flat indices the query covered, None = all R x S)
+                self.last_cull = {"queried": None if full else idx, "source": src, "n_queried": idx.numel()}
         elif sigma_fn is not None and alpha_thre > 0.0:
             valid = torch.arange(max_samples, device=dev)[None] < counts[:, None]
             idx = valid.reshape(-1).nonzero(as_tuple=True)[0]

@@ -57,12 +57,14 @@ def main():
     assert getattr(tr.optimizer, "partitioned", False), type(tr.optimizer).__name__
     for it in range(4):
         tr.iteration = it
+        torch.manual_seed(1000 + it)            # the stratified sampling jitter of a step depends on the step alone
         tr.train_step(*data[it])
     tr.save_ckpt()
     dist.barrier()
     assert os.path.exists(tr._optim_path()) and f"-sub{rank}" in tr._optim_path()
     for it in range(4, 7):
         tr.iteration = it
+        torch.manual_seed(1000 + it)
         tr.train_step(*data[it])
     want = flat(tr)
     # a shard of the other rank must be refused
@@ -80,6 +82,7 @@ def main():
     resumed = make(root, ckpt="auto", start_iters="4")
     for it in range(4, 7):
         resumed.iteration = it
+        torch.manual_seed(1000 + it)
         resumed.train_step(*data[it])
     got = flat(resumed)
     err = float((got - want).abs().max())

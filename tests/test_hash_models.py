@@ -185,3 +185,45 @@ def test_ngp_restatement_baseline_trains():
     target = torch.rand(R, 3) * 0.2 + 0.6
     losses = [tr.train_step(rays, target, torch.zeros(R)) for _ in range(25)]
     assert losses[-1] < 0.3 * losses[0]
+
+
+def test_ngp_reuses_the_culling_pass_rows_for_the_survivors(tmp_path):
+    """The step's forward takes hash features / head outputs of the sampler's density query for the samples that survived
+    the culling: the row bookkeeping (survivor slot -> slot before the compaction -> row of the query), with the query
+    covering all R x S slots and covering a subset."""
+    from landmarksystem_b200.models.instant_ngp.instant_ngp_trainer import NGPTrainer
+
+    cfg = BaseConfig.from_file(os.path.join(ROOT, "instant_ngp", "confs", "synthetic_tiny.py"),
+                               {"basedir": str(tmp_path), "device": "cpu", "n_iters": "1", "datadir": "ring:3:12x12:14:3",
+                                "batch_size": "64", "progress_refresh_rate": "100"})
+    model = NGPTrainer(cfg).model.train()
+    R, S = 5, 6
+    g = torch.Generator().manual_seed(0)
+    for subset in (False, True):
+        marched = (torch.rand(R, S, generator=g) < 0.8) if subset else torch.ones(R, S, dtype=torch.bool)
+        marched = marched.sort(dim=1, descending=True).values                 # marched samples fill a row's front
+        queried = marched.reshape(-1).nonzero(as_tuple=True)[0]
+        n = queried.numel()
+        feat, h = torch.arange(n)[:, None].float().repeat(1, 4), torch.arange(n)[:, None].float().repeat(1, 2) + 0.5
+        keep = marched & (torch.rand(R, S, generator=g) < 0.6)
+        source = torch.zeros(R, S, dtype=torch.int32)
+        for r in range(R):
+            kept = keep[r].nonzero(as_tuple=True)[0]
+            source[r, : kept.numel()] = kept.to(torch.int32)
+        counts = keep.sum(1)
+        survivors = (torch.arange(S)[None] < counts[:, None]).reshape(-1).nonzero(as_tuple=True)[0]
+        model._cull_cache = {"feat": feat, "h": h}
+        model.occupancy_grid.last_cull = {"queried": queried if subset else None, "source": source, "n_queried": n}
+        got_feat, got_h = model._cached_field_rows(survivors, S)
+        row_of_slot = torch.full((R * S,), -1, dtype=torch.long)
+        row_of_slot[queried] = torch.arange(n)
+        want = row_of_slot[keep.reshape(-1).nonzero(as_tuple=True)[0]]        # kept slots in row-major order = survivors' order
+        assert torch.equal(got_feat[:, 0].long(), want) and torch.equal(got_h[:, 0], want.float() + 0.5)
+        assert model._cull_cache is None                                       # consumed
+    # nothing culled: the cached tensors are handed over as they are
+    n = R * S
+    feat, h = torch.zeros(n, 4), torch.zeros(n, 2)
+    model._cull_cache = {"feat": feat, "h": h}
+    model.occupancy_grid.last_cull = {"queried": None, "source": torch.arange(S, dtype=torch.int32).repeat(R, 1), "n_queried": n}
+    got_feat, got_h = model._cached_field_rows(torch.arange(n), S)
+    assert got_feat is feat and got_h is h
