@@ -187,13 +187,13 @@ class InstantNGP(BaseNeRF):
             return None, None
         if idx.numel() == cull["n_queried"]:
             return feat, h                          # nothing was culled; the compaction keeps the order
-        ray = idx // samples_per_ray
-        before = ray * samples_per_ray + cull["source"].reshape(-1)[idx].long()       # flat index before the compaction
-        if cull["queried"] is not None:
+        from ...ops import ngp_field
+
+        where = None
+        if cull["queried"] is not None:           # the query covered a subset of the slots: flat slot -> row of the query
             where = torch.full((cull["source"].numel(),), -1, dtype=torch.long, device=idx.device)
             where[cull["queried"]] = torch.arange(cull["n_queried"], device=idx.device)
-            before = where[before]
-        return feat[before], h[before]
+        return ngp_field.gather_cached_rows(idx, samples_per_ray, cull["source"], where, feat, h)
 
     def _kernel_glue(self, rays) -> bool:
         """The per-sample glue runs as kernels when both heads are on the fused MLP path and no cross-rank sum sits

@@ -164,6 +164,10 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
   // biases that ride in the GEMM (a column of the weights against the ones column of the layer's input) or are zero
   const bool skip_b1 = (spec.bias_in_gemm >> L1) & 1, skip_b2 = (spec.bias_in_gemm >> (L1 + 1)) & 1;
   const int k_fwd2 = (skip_b2 && spec.K[L1 + 1] == 144) ? 144 : 128;
+  // plain network with two layers only (K of the middle layer given as 0): h1 feeds the output layer directly and the
+  // middle layer's recompute, mask, weight-gradient and data-gradient groups are skipped
+  const bool two_layers = !kPE && spec.K[1] == 0;
+  const uint32_t aH2 = two_layers ? aH1 : aHZ;
   const int n_out = kPE ? 3 : spec.out_dim;
   (void)aW0;
 
@@ -293,6 +297,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     }
     LMB_EPILOGUE_DONE();
 
+    if (!two_layers) {
     if (row == 0) issue_fwd(tmem + kColWork, aH1, aW2, k_fwd2, 128);      // 144: the ones chunk of h1 times the bias column
     LMB_MMA_WAIT();
     for (int n0 = 0; n0 < 128; n0 += 64) {
@@ -309,8 +314,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       for (int c = 0; c < 8; ++c) store_chunk_relu(bufHZ, (n0 >> 3) + c, row, v + 8 * c);
     }
     LMB_EPILOGUE_DONE();
+    }
 
-    if (row == 0) issue_fwd(tmem + kColWork, aHZ, aW3, 128, 16);
+    if (row == 0) issue_fwd(tmem + kColWork, aH2, aW3, 128, 16);
     LMB_MMA_WAIT();
     {
       float v[16], dz[16];
@@ -335,10 +341,11 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
 
     // ================= layer 3 =================
     if (row == 0) {
-      issue_wgrad(tmem + kColDW3T, aHZ, aS, 16, !first);          // dW3^T += h2^T dz3
+      issue_wgrad(tmem + kColDW3T, aH2, aS, 16, !first);          // dW3^T += h2^T dz3
       issue_dgrad(tmem + kColWork, aS, aW3, 16, 0, 128);          // dh2 = dz3 W3
     }
     LMB_MMA_WAIT();
+    if (!two_layers) {
     for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz2 = dh2 * [h2 > 0], in place of h2
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
@@ -360,6 +367,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
       issue_dgrad(tmem + kColWork, aHZ, aW2, 128, 0, 128);        // dh1 = dz2 W2
     }
     LMB_MMA_WAIT();
+    }
     for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz1 = dh1 * [h1 > 0] -> HZ
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
@@ -634,7 +642,7 @@ LMB_API int lmb_mlp3_bwd(const void* x, int x_width, const int* count_ptr, long 
   if (max_rows <= 0) return 0;
   if (x_width % 8 != 0 || x_width < 8 || (x_width > 152 && x_width != 160)) return (int)cudaErrorInvalidValue;
   MLPSpec s = *spec;
-  if (s.n_layers != 3 || s.pe_stage || s.in_width != 160 || s.K[0] != 160 || s.N[0] != 128 || s.K[1] != 128 || s.N[1] != 128 ||
+  if (s.n_layers != 3 || s.pe_stage || s.in_width != 160 || s.K[0] != 160 || s.N[0] != 128 || (s.K[1] != 128 && s.K[1] != 0) || s.N[1] != 128 ||
       s.K[2] != 128 || s.N[2] != 16 || s.out_dim < 1 || s.out_dim > 16 || s.b_off[0] < 0 || s.b_off[1] < 0 || s.b_off[2] < 0 ||
       s.blob_bytes % 16 || s.act[0] != ACT_RELU || s.act[1] != ACT_RELU || (s.act[2] != ACT_SIGMOID && s.act[2] != ACT_NONE) ||
       dout_stride < s.out_dim)

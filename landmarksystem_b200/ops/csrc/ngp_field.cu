@@ -394,6 +394,27 @@ occ_cull_kernel(int R, int S, const float* __restrict__ sigma, float* __restrict
   if (lane == 0) counts[ray] = kept;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Rows of the sampler's density query for the samples that survived the culling.  Survivor m sits at flat slot idx[m]
+// of the compacted [R, S] block; before the compaction it sat at slot source[idx[m]] of the same ray, and the query
+// wrote row where[that flat slot] (where == nullptr: the query covered every slot, the row is the flat slot).  Two row
+// sets are gathered at once (hash features and head outputs), 16 bytes per thread.
+__global__ void __launch_bounds__(256)
+ngp_gather_cached_kernel(long long n, const long long* __restrict__ idx, int samples_per_ray, const int* __restrict__ source,
+                         const long long* __restrict__ where, const uint4* __restrict__ a_src, int a_pieces,
+                         const uint4* __restrict__ b_src, int b_pieces, uint4* __restrict__ a_dst, uint4* __restrict__ b_dst) {
+  const int pieces = a_pieces + b_pieces;
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long m = t / pieces;
+  if (m >= n) return;
+  const int piece = (int)(t - m * pieces);
+  const long long flat = idx[m];
+  long long row = (flat / samples_per_ray) * samples_per_ray + source[flat];
+  if (where != nullptr) row = where[row];
+  if (piece < a_pieces) a_dst[m * a_pieces + piece] = __ldg(a_src + row * a_pieces + piece);
+  else b_dst[m * b_pieces + (piece - a_pieces)] = __ldg(b_src + row * b_pieces + (piece - a_pieces));
+}
+
 }  // namespace lmb
 
 using namespace lmb;
@@ -496,6 +517,21 @@ LMB_API int lmb_occ_cull(int R, int S, const float* sigma, float* ts, float* te,
                          float early_stop_eps, int* src, cudaStream_t stream) {
   if (R <= 0) return 0;
   occ_cull_kernel<<<ceil_div((long long)R * 32, 256), 256, 0, stream>>>(R, S, sigma, ts, te, counts, alpha_thre, early_stop_eps, src);
+  LMB_LAUNCH_CHECK();
+  return 0;
+}
+
+// a / b: two row-major arrays with rows of a_bytes / b_bytes (multiples of 16); idx: int64 [n]; source: int32 [R * S];
+// where: int64 [R * S] or null
+LMB_API int lmb_ngp_gather_cached(long long n, const long long* idx, int samples_per_ray, const int* source, const long long* where,
+                                  const void* a_src, int a_bytes, const void* b_src, int b_bytes, void* a_dst, void* b_dst,
+                                  cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (a_bytes % 16 || b_bytes % 16 || a_bytes <= 0 || b_bytes <= 0) return (int)cudaErrorInvalidValue;
+  const int pieces = (a_bytes + b_bytes) / 16;
+  ngp_gather_cached_kernel<<<ceil_div(n * pieces, 256), 256, 0, stream>>>(n, idx, samples_per_ray, source, where, (const uint4*)a_src,
+                                                                         a_bytes / 16, (const uint4*)b_src, b_bytes / 16,
+                                                                         (uint4*)a_dst, (uint4*)b_dst);
   LMB_LAUNCH_CHECK();
   return 0;
 }

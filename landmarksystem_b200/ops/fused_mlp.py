@@ -193,8 +193,8 @@ def mlp3_backward_supported(packed: "PackedMLP") -> bool:
 
 
 class _PackedMLP3:
-    """The network zero-padded to 160 -> 128 -> 128 -> 16 in the kernel's blob layout (a two-layer network gets an
-    identity middle layer: relu(h) = h for h >= 0).  Re-packed when the optimiser generation or a parameter version moves."""
+    """The network zero-padded to 160 -> 128 -> 128 -> 16 in the kernel's blob layout (a two-layer network keeps the
+    blob's middle slot - an identity - but marks it so that the kernel skips that layer).  Re-packed when the optimiser generation or a parameter version moves."""
 
     def __init__(self, layers):
         self.layers, self.key, self.blob, self.spec, self.status = layers, None, None, None, None
@@ -230,6 +230,8 @@ class _PackedMLP3:
         spec.blob_bytes, spec.in_width, spec.out_dim, spec.pe_stage, spec.dir_col = off, MLP3_IN, w3.shape[0], 0, 0
         # layers without a bias (the hash-grid heads): the kernel skips the bias adds of its recompute epilogues
         spec.bias_in_gemm = (1 if b1 is None else 0) | (2 if b2 is None else 0)
+        if len(self.layers) == 2:
+            spec.K[1] = 0        # two-layer network: the kernel feeds h1 to the output layer and skips the middle layer
         self.blob, self.spec, self.key = torch.cat(parts).contiguous(), spec, key
         if self.status is None:
             self.status = torch.zeros(1, device=dev, dtype=torch.int32)

@@ -26,6 +26,7 @@ native.register_signature("lmb_ngp_head_rows_bwd", [c_longlong, P, c_int, P, P, 
 native.register_signature("lmb_occ_cells", [c_longlong, P, c_int, P, c_int, c_uint, c_int, P, c_float, P, P, P])
 native.register_signature("lmb_occ_update", [c_longlong, P, P, P, P, P])
 native.register_signature("lmb_occ_binarise", [c_longlong, P, c_float, P, P, P])
+native.register_signature("lmb_ngp_gather_cached", [c_longlong, P, c_int, P, P, P, c_int, P, c_int, P, P, P])
 native.register_signature("lmb_occ_cull", [c_int, c_int, P, P, P, P, c_float, c_float, P, P])
 
 SH_WIDTH = 16
@@ -196,3 +197,24 @@ def occ_cull(sigma: torch.Tensor, ts: torch.Tensor, te: torch.Tensor, counts: to
                                            float(alpha_thre), float(early_stop_eps), native.ptr(src), native.stream_ptr()),
                  "occ_cull")
     return src
+
+
+@torch.no_grad()
+def gather_cached_rows(idx: torch.Tensor, samples_per_ray: int, source: torch.Tensor, where: Optional[torch.Tensor],
+                       a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rows of ``a`` and ``b`` (results of a query over marched samples) for the survivors ``idx`` of a culling whose
+    compaction recorded ``source`` (see :func:`occ_cull`); ``where``: flat slot -> row of the query, ``None`` if the
+    query covered every slot."""
+    n = idx.numel()
+    if not _use_kernel(a):
+        before = (idx // samples_per_ray) * samples_per_ray + source.reshape(-1)[idx].long()
+        rows = before if where is None else where[before]
+        return a[rows], b[rows]
+    a, b = a.contiguous(), b.contiguous()
+    out_a = torch.empty((n, *a.shape[1:]), device=a.device, dtype=a.dtype)
+    out_b = torch.empty((n, *b.shape[1:]), device=b.device, dtype=b.dtype)
+    native.check(native.lib().lmb_ngp_gather_cached(n, idx.data_ptr(), samples_per_ray, source.data_ptr(), native.ptr(where),
+                                                    a.data_ptr(), a[0].numel() * a.element_size(), b.data_ptr(),
+                                                    b[0].numel() * b.element_size(), out_a.data_ptr(), out_b.data_ptr(),
+                                                    native.stream_ptr()), "ngp_gather_cached")
+    return out_a, out_b

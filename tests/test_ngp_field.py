@@ -164,3 +164,23 @@ def test_occ_cull_kernel_matches_the_tensor_statement():
     sel = front & clean[:, None]
     assert torch.equal(got_ts[sel], want_ts[sel]) and torch.equal(got_te[sel], want_te[sel])
     assert float(got_ts[~front & clean[:, None]].abs().sum()) == 0.0
+
+
+@cuda
+@pytest.mark.parametrize("subset", [False, True])
+def test_gather_cached_rows_kernel(subset):
+    dev = "cuda"
+    R, S = 97, 40
+    g = torch.Generator().manual_seed(5)
+    source = torch.stack([torch.randperm(S, generator=g) for _ in range(R)]).to(torch.int32).to(dev)
+    n_rows = R * S
+    where = None
+    if subset:
+        where = torch.randint(0, n_rows, (R * S,), generator=g).to(dev)
+    a = torch.randn(n_rows, 32, generator=g).to(torch.bfloat16).to(dev)
+    b = torch.randn(n_rows, 16, generator=g).to(dev)
+    idx = (torch.rand(R * S, generator=g) < 0.5).nonzero(as_tuple=True)[0].to(dev)
+    got_a, got_b = ngp_field.gather_cached_rows(idx, S, source, where, a, b)
+    before = (idx // S) * S + source.reshape(-1)[idx].long()
+    rows = before if where is None else where[before]
+    assert torch.equal(got_a, a[rows]) and torch.equal(got_b, b[rows])
