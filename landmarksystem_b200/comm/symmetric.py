@@ -23,6 +23,25 @@ for _name, _sig in (("lmb_symm_alloc", [c_longlong, ctypes.POINTER(c_void_p)]), 
     native.register_signature(_name, _sig)
 
 
+def multicast_supported(device: int = 0) -> bool:
+    """Whether the device reports NVLink multicast objects (what NVLS / ``multimem`` instructions need), read from the
+    driver attribute only - nothing is allocated or bound.  The kernels of this package do not use multicast: their
+    reduce-shaped traffic is either tiny or fused with an optimiser over plain peer loads, and a rank that dies while
+    its memory is bound to a multicast object disturbs its peers' GPUs, which the rank-failure tests must avoid.  The
+    probe lets a deployment log what the fabric offers (``NCCL_DEBUG=INFO`` shows whether NCCL uses it)."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        from cuda.bindings import driver as drv
+    except ImportError:
+        return False
+    err, dev = drv.cuDeviceGet(int(device))
+    if int(err) != 0:
+        return False
+    err, value = drv.cuDeviceGetAttribute(drv.CUdevice_attribute.CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev)
+    return int(err) == 0 and bool(value)
+
+
 class _RawCuda:
     """Minimal ``__cuda_array_interface__`` carrier so torch can wrap a raw device pointer."""
 

@@ -362,7 +362,51 @@ def case_merge_emulated(args):
                    bytes_=rays * (world * 32 + world * 24.0), rays=rays)
 
 
-CASES = {"mlp3_bwd": case_mlp3_bwd, "ray_losses": case_ray_losses, "prop_resample": case_prop_resample, "alpha_pool": case_alpha_pool,
+def case_a2a_emulated(args):
+    """The spatial-block all-to-all on one GPU (the rank is its own and only peer: same kernels, flags and waits as the
+    multi-GPU runs, peer stores landing in local memory): one sigma-shaped query - 16-byte records out, 4 bytes back."""
+    from ..parallel.branch_dispatch import BlockDispatcher
+
+    n = args.rows
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    disp = BlockDispatcher(n, max_w=6, max_v=3)
+    payload = torch.rand(n, 4, device="cuda", generator=gen)
+    payload[:, 3] = 0.0
+    owner = torch.zeros(n, dtype=torch.int32, device="cuda")
+    w = torch.randn(3, 1, device="cuda", generator=gen)
+
+    class Owner:
+        def parameters_for_autograd(self):
+            return []
+
+        def __call__(self, coords, extra, m):
+            return torch.tanh(coords[:, :3] @ w)
+
+    fn = Owner()
+    with torch.no_grad():
+        ms, best = time_kernel(lambda: disp.query(payload, owner, fn, 1, channel="bench"), args.iters)
+    disp.check()
+    # dispatch: 16 B read + 16 B stored to the owner; collect: 16 B read + 16 B written; combine / result: 4 B each way twice
+    return _report("a2a dispatch + collect + owner map + combine + result (1 rank, peers emulated)", ms, best,
+                   bytes_=n * (32 + 32 + 16.0), rows=n)
+
+
+def case_mlp_fwd_sources(args):
+    """The colour head with its input assembled from two sources (feature block + direction block), the path the
+    channel-parallel gather uses for peer slices; both sources are local here."""
+    from ..parallel.channel_gather_mlp import ChannelGatherColourHead
+
+    dec = _rgb_decoder(args.channels)
+    head = ChannelGatherColourHead(dec, n_levels=3, channels_per_rank=args.channels, max_rows=args.rows)
+    feat = (torch.randn(args.rows, 3 * args.channels, device="cuda") * 0.3).to(torch.bfloat16)
+    dirs = torch.nn.functional.normalize(torch.randn(args.rows, 3, device="cuda"), dim=-1)
+    ms, best = time_kernel(lambda: head(feat, dirs), args.iters)
+    return _report("fused_mlp_kernel, two input sources (copy into the symmetric buffer and two barriers included)", ms, best,
+                   flops=_mlp_flops(args.channels, args.rows, False), bytes_=args.rows * (3 * args.channels * 2 * 3 + 32 + 12.0),
+                   rows=args.rows)
+
+
+CASES = {"a2a_emulated": case_a2a_emulated, "mlp_fwd_sources": case_mlp_fwd_sources, "mlp3_bwd": case_mlp3_bwd, "ray_losses": case_ray_losses, "prop_resample": case_prop_resample, "alpha_pool": case_alpha_pool,
          "zero_adam_emulated": case_zero_adam_emulated, "merge_emulated": case_merge_emulated, "adam": case_adam, "lazy_adam": case_lazy_adam, "vm_fwd": case_vm_fwd, "vm_bwd": case_vm_bwd, "vm_bwd_sorted": case_vm_bwd_sorted,
          "mlp_fwd": case_mlp_fwd, "mlp_bwd": case_mlp_bwd, "composite": case_composite, "hash_fwd": case_hash_fwd}
 

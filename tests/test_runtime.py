@@ -246,3 +246,13 @@ def test_peer_barrier_wait_gives_up_and_reports_the_missing_peer():
         assert int(flags[0]) == expect_epoch          # the rank's own signal to itself did arrive
         assert start.elapsed_time(end) < 1000.0       # gave up after milliseconds, not the one-second default
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0                 # the context still works
+
+
+def test_multicast_probe_is_false_without_a_gpu():
+    """The NVLink-multicast probe only reads a driver attribute; on a machine without a GPU it answers False."""
+    from landmarksystem_b200.comm.symmetric import multicast_supported
+
+    if not torch.cuda.is_available():
+        assert multicast_supported() is False
+    else:
+        assert multicast_supported() in (True, False)
