@@ -396,13 +396,14 @@ def case_mlp_fwd_sources(args):
     channel-parallel gather uses for peer slices; both sources are local here."""
     from ..parallel.channel_gather_mlp import ChannelGatherColourHead
 
-    dec = _rgb_decoder(args.channels)
-    head = ChannelGatherColourHead(dec, n_levels=3, channels_per_rank=args.channels, max_rows=args.rows)
-    feat = (torch.randn(args.rows, 3 * args.channels, device="cuda") * 0.3).to(torch.bfloat16)
+    dec = _rgb_decoder(args.channels)                  # one level of `channels` appearance features
+    assert dec.basis_mat.weight.shape[1] == args.channels
+    head = ChannelGatherColourHead(dec, n_levels=1, channels_per_rank=args.channels, max_rows=args.rows)
+    feat = (torch.randn(args.rows, args.channels, device="cuda") * 0.3).to(torch.bfloat16)
     dirs = torch.nn.functional.normalize(torch.randn(args.rows, 3, device="cuda"), dim=-1)
     ms, best = time_kernel(lambda: head(feat, dirs), args.iters)
     return _report("fused_mlp_kernel, two input sources (copy into the symmetric buffer and two barriers included)", ms, best,
-                   flops=_mlp_flops(args.channels, args.rows, False), bytes_=args.rows * (3 * args.channels * 2 * 3 + 32 + 12.0),
+                   flops=_mlp_flops(args.channels, args.rows, False), bytes_=args.rows * (args.channels * 2 * 3 + 32 + 12.0),
                    rows=args.rows)
 
 
