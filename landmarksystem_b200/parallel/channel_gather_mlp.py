@@ -58,13 +58,16 @@ class ChannelGatherColourHead:
             original_refresh = packed.refresh
 
             def refresh():
-                # pack with the permuted basis columns
+                # pack with the permuted basis columns - only when a weight changed since the last packing
                 w = dec.basis_mat.weight
+                if packed.blob is not None and packed.versions == packed._versions():
+                    return
                 permuted = w.detach()[:, perm]
                 packed.layers = [(permuted, None, "none")] + packed.layers[1:]
                 packed.versions = None
                 original_refresh()
                 packed.layers = [(w, None, "none")] + packed.layers[1:]
+                packed.versions = packed._versions()          # versions of the real parameters, not of the permuted copy
 
             packed.refresh_permuted = refresh
             self.packed = packed
