@@ -801,7 +801,8 @@ def run_ours(args):
         gc.collect()
         torch.cuda.empty_cache()
         if n == 1:
-            for name, fn in (("3DGS 1080p render FPS", render_fps_3dgs), ("InstantNGP training rays/s", train_rate_ngp)):
+            for name, fn in (("3DGS 1080p render FPS", render_fps_3dgs), ("InstantNGP training rays/s", train_rate_ngp),
+                             ("GridNeRF 1080p render FPS with dynamic loading", lambda: stream_fps_gridnerf(frames=60))):
                 try:
                     also.append(fn())
                 except Exception as exc:

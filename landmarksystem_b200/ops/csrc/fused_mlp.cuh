@@ -29,6 +29,8 @@ struct MLPSpec {
   int dir_col;              // column of the input row that holds the view direction (pe_stage)
   int bias_in_gemm;         // bit l: layer l's bias is a column of its weights, multiplied by a ones column that the
                             // kernels write into the layer's input (or it is zero): the epilogue adds nothing
+  int hidden_cols;          // plain backward kernel: widest real hidden width (0 = as padded); at most 64 lets its
+                            // 128-column epilogues stop after the first 64 columns (the rest is zero padding)
 };
 
 // Input rows may be assembled from several tensors ("sources"), each contributing a contiguous range of

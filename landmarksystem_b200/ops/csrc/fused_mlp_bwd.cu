@@ -166,6 +166,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
   const int k_fwd2 = (skip_b2 && spec.K[L1 + 1] == 144) ? 144 : 128;
   // plain network with two layers only (K of the middle layer given as 0): h1 feeds the output layer directly and the
   // middle layer's recompute, mask, weight-gradient and data-gradient groups are skipped
+  // hidden layers of at most 64 real units (the hash-grid heads): the padded upper halves of h1 / h2 / dz are zero and
+  // stay zero, so they are written once below and the epilogues walk 64 columns instead of 128
+  const int hid = (!kPE && spec.hidden_cols > 0 && spec.hidden_cols <= 64) ? 64 : 128;
   const bool two_layers = !kPE && spec.K[1] == 0;
   const uint32_t aH2 = two_layers ? aH1 : aHZ;
   const int n_out = kPE ? 3 : spec.out_dim;
@@ -216,6 +219,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     const uint4 z = make_uint4(0, 0, 0, 0);
     for (int c = in_chunks; c < 20; ++c)
       *reinterpret_cast<uint4*>(bufA + ((size_t)c * kTileRows + row) * 16) = (c == 19) ? make_uint4(0, 0, 0, 0x3F800000u) : z;
+    if (hid < 128) {
+      for (int c = hid >> 3; c < 16; ++c) {
+        *reinterpret_cast<uint4*>(bufH1 + ((size_t)c * kTileRows + row) * 16) = z;
+        *reinterpret_cast<uint4*>(bufHZ + ((size_t)c * kTileRows + row) * 16) = z;
+      }
+    }
   }
 
   for (; ok && tile < n_tiles; tile += gridDim.x) {
@@ -275,7 +284,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
 
     if (row == 0) issue_fwd(tmem + kColWork, aA, aW1, 160, 128);
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 64) {                       // 64 accumulator columns per wait: load latencies overlap
+    for (int n0 = 0; n0 < hid; n0 += 64) {                       // 64 accumulator columns per wait: load latencies overlap
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
       if (!skip_b1) {
@@ -300,7 +309,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     if (!two_layers) {
     if (row == 0) issue_fwd(tmem + kColWork, aH1, aW2, k_fwd2, 128);      // 144: the ones chunk of h1 times the bias column
     LMB_MMA_WAIT();
-    for (int n0 = 0; n0 < 128; n0 += 64) {
+    for (int n0 = 0; n0 < hid; n0 += 64) {
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
       if (!skip_b2) {
@@ -346,7 +355,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     }
     LMB_MMA_WAIT();
     if (!two_layers) {
-    for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz2 = dh2 * [h2 > 0], in place of h2
+    for (int n0 = 0; n0 < hid; n0 += 64) {                         // dz2 = dh2 * [h2 > 0], in place of h2
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll
@@ -368,7 +377,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap xmap, const unsigned char* __
     }
     LMB_MMA_WAIT();
     }
-    for (int n0 = 0; n0 < 128; n0 += 64) {                         // dz1 = dh1 * [h1 > 0] -> HZ
+    for (int n0 = 0; n0 < hid; n0 += 64) {                         // dz1 = dh1 * [h1 > 0] -> HZ
       float v[64];
       tc05::tmem_ld64(tlane + kColWork + n0, v);
 #pragma unroll

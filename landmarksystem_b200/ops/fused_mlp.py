@@ -28,7 +28,7 @@ ACT = {"none": 0, "relu": 1, "sigmoid": 2, "tanh": 3, "exp": 4}
 class MLPSpec(Structure):
     _fields_ = [("n_layers", c_int), ("K", c_int * MAX_LAYERS), ("N", c_int * MAX_LAYERS), ("act", c_int * MAX_LAYERS),
                 ("w_off", c_int * MAX_LAYERS), ("b_off", c_int * MAX_LAYERS), ("blob_bytes", c_int),
-                ("in_width", c_int), ("out_dim", c_int), ("pe_stage", c_int), ("dir_col", c_int), ("bias_in_gemm", c_int)]
+                ("in_width", c_int), ("out_dim", c_int), ("pe_stage", c_int), ("dir_col", c_int), ("bias_in_gemm", c_int), ("hidden_cols", c_int)]
 
 
 native.register_signature("lmb_fused_mlp_fwd", [native.P, native.P, c_longlong, native.P, POINTER(MLPSpec), native.P,
@@ -232,6 +232,7 @@ class _PackedMLP3:
         spec.bias_in_gemm = (1 if b1 is None else 0) | (2 if b2 is None else 0)
         if len(self.layers) == 2:
             spec.K[1] = 0        # two-layer network: the kernel feeds h1 to the output layer and skips the middle layer
+        spec.hidden_cols = max(w.shape[0] for w, _, _ in self.layers[:-1])      # <= 64: the kernel's epilogues walk 64 columns
         self.blob, self.spec, self.key = torch.cat(parts).contiguous(), spec, key
         if self.status is None:
             self.status = torch.zeros(1, device=dev, dtype=torch.int32)
