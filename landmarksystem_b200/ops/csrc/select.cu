@@ -62,18 +62,6 @@ compact_kernel(const unsigned char* __restrict__ mask, long long n, const float4
   }
 }
 
-// x[j, col .. col+2] = dirs[idx[j] / S] (idx null: dirs[j]) as bf16, rows of width x_stride, first *count rows
-__global__ void __launch_bounds__(256)
-put_dirs_kernel(__nv_bfloat16* __restrict__ x, int x_stride, int col, const float* __restrict__ dirs, const int* __restrict__ idx,
-                const int* __restrict__ count_ptr, long long max_n, int S) {
-  const long long n = resolve_count(count_ptr, max_n);
-  for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (long long)gridDim.x * blockDim.x) {
-    const float* d = dirs + (idx != nullptr ? (long long)(idx[j] / S) : j) * 3;
-    __nv_bfloat16* o = x + j * x_stride + col;
-    o[0] = __float2bfloat16_rn(d[0]); o[1] = __float2bfloat16_rn(d[1]); o[2] = __float2bfloat16_rn(d[2]);
-  }
-}
-
 // payload[j] = (coords[j].xyz, dirs[idx[j] / S]), owner[j] = (int)coords[j].w for the first *count rows: the rows a
 // rank sends to the owners of the blocks its colour samples fall into
 __global__ void __launch_bounds__(256)
@@ -121,15 +109,6 @@ LMB_API int lmb_compact_rows(const unsigned char* mask, long long n, const float
   const int aligned = (reinterpret_cast<uintptr_t>(mask) & 3u) == 0 ? 1 : 0;
   compact_kernel<<<ceil_div(n, 256 * kCompactPerThread), 256, 0, stream>>>(mask, n, (const float4*)xyzb, idx, (float4*)coords_out,
                                                                            count, aligned);
-  LMB_LAUNCH_CHECK();
-  return 0;
-}
-
-LMB_API int lmb_put_dirs(void* x, int x_stride, int col, const float* dirs, const int* idx, const int* count_ptr,
-                         long long max_n, int S, cudaStream_t stream) {
-  if (max_n <= 0) return 0;
-  const long long want = (max_n + 255) / 256;       // capped grid: max_n may be a worst-case capacity far above the count
-  put_dirs_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((__nv_bfloat16*)x, x_stride, col, dirs, idx, count_ptr, max_n, S);
   LMB_LAUNCH_CHECK();
   return 0;
 }

@@ -11,7 +11,6 @@ from . import native
 
 P = native.P
 native.register_signature("lmb_compact_rows", [P, c_longlong, P, P, P, P, P])
-native.register_signature("lmb_put_dirs", [P, c_int, c_int, P, P, P, c_longlong, c_int, P])
 native.register_signature("lmb_scatter_rows3", [P, P, P, P, c_longlong, P, P])
 native.register_signature("lmb_gather_rows3", [P, P, P, P, c_longlong, P, P])
 native.register_signature("lmb_build_payload6", [P, P, P, P, c_longlong, c_int, P, P, P])
@@ -29,15 +28,6 @@ def compact_rows(mask: torch.Tensor, xyzb: torch.Tensor) -> Tuple[torch.Tensor, 
     native.check(native.lib().lmb_compact_rows(mask.data_ptr(), n, xyzb.data_ptr(), idx.data_ptr(), coords.data_ptr(),
                                                count.data_ptr(), native.stream_ptr()), "compact_rows")
     return idx, coords, count
-
-
-def put_dirs(x: torch.Tensor, col: int, dirs: torch.Tensor, idx, count: torch.Tensor, samples_per_ray: int = 1) -> None:
-    """In place: ``x[j, col:col+3] = dirs[idx[j] // samples_per_ray]`` (``idx=None``: ``dirs[j]``) for ``j < count``
-    (``x`` bf16 rows)."""
-    assert x.dtype == torch.bfloat16 and x.is_contiguous()
-    dirs = dirs.contiguous().float()
-    native.check(native.lib().lmb_put_dirs(x.data_ptr(), x.shape[1], col, dirs.data_ptr(), native.ptr(idx), count.data_ptr(),
-                                           x.shape[0], samples_per_ray, native.stream_ptr()), "put_dirs")
 
 
 def build_payload6(coords: torch.Tensor, dirs: torch.Tensor, idx: torch.Tensor, count: torch.Tensor, samples_per_ray: int):
