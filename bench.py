@@ -582,6 +582,22 @@ def render_phase_ours(holder, cfg, args, n, rank, world, dev):
         frame_ms, e2e_ms, img = time_engine_frames(
             engine, poses, rank, world, dev, lambda e, pose: e(torch.from_numpy(pose), RENDER_CHUNK, H, W, RENDER_FOCAL))
         ms, ms2 = statistics.median(frame_ms), statistics.median(e2e_ms)
+        if os.environ.get("LMB_RENDER_PROFILE"):       # kernel + host table of one more frame (rank 0, stderr)
+            from torch.profiler import ProfilerActivity
+            from torch.profiler import profile as torch_profile
+
+            if world > 1:
+                dist.barrier()
+            with torch_profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+                if rank == 0:
+                    engine(torch.from_numpy(poses[-1]), RENDER_CHUNK, H, W, RENDER_FOCAL)
+                else:
+                    engine()
+                torch.cuda.synchronize()
+            if rank == 0:
+                print(f"--- render profile, mode {mode}, {n} GPUs ---", file=sys.stderr)
+                print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=22, max_name_column_width=70), file=sys.stderr)
+                print(prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=14, max_name_column_width=70), file=sys.stderr)
         entry = {"metric": "GridNeRF 1080p render FPS through init_inference", "mode": mode, "value": 1000.0 / ms,
                  "ms_per_frame": ms, "e2e_value": 1000.0 / ms2, "e2e_ms_per_frame": ms2,
                  "d2h_bytes_per_frame": H * W * 4 * 4, "frames": len(frame_ms), "n_gpus": n, "samples_per_ray": SAMPLES,
