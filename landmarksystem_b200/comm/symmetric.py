@@ -8,7 +8,7 @@ waits) that orders such kernels across GPUs without a host round trip or an NCCL
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_longlong, c_uint, c_void_p
+from ctypes import c_int, c_longlong, c_void_p
 from typing import List, Optional
 
 import torch

@@ -16,7 +16,6 @@ import math
 from dataclasses import dataclass
 from typing import List
 
-import numpy as np
 import torch
 
 from . import native

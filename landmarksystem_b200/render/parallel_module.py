@@ -14,7 +14,6 @@ from ..comm import CommContext, ParallelMode, all_gather
 from ..utils import Config
 from .inference_module import InferenceModule
 from .optimization_manager import OptimizationManager
-from .types import StageInput
 
 
 class StageArgs:
