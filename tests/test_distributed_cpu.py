@@ -342,3 +342,28 @@ def test_data_parallel_render_scatter_gather(world):
         padded = list(range(11)) + [0]
         assert [int(v) for v in out[rank][True]] == padded[rank::world]
         assert [int(v) for v in out[rank][False]] == padded[rank * size:(rank + 1) * size]
+
+
+# -- the engine's user-input message: one fixed-size broadcast, object broadcast for what does not fit ------------------
+def _user_inputs(rank, world):
+    from landmarksystem_b200.comm import CommContext
+    from landmarksystem_b200.comm.collective import _broadcast_user_inputs_message
+    from landmarksystem_b200.utils import Config
+
+    ctx = CommContext()
+    ctx.init_distributed_env(world_size=world, rank=rank, backend="gloo")
+    ctx.init_groups(Config(tp_size=1))
+    small = [(torch.arange(16.0).reshape(4, 4), 262144, 1080, 1920, 2317.6), {"app_code": 3}]
+    got = _broadcast_user_inputs_message(small if rank == 0 else None)
+    assert torch.equal(got[0][0], small[0][0]) and got[0][1:] == small[0][1:] and got[1] == small[1]
+    big = [(torch.arange(50000.0),), {}]                     # 200 KB: does not fit the fixed buffer
+    got_big = _broadcast_user_inputs_message(big if rank == 0 else None)
+    assert torch.equal(got_big[0][0], big[0][0])
+    got = _broadcast_user_inputs_message(small if rank == 0 else None)       # and the fast path again afterwards
+    assert got[0][2] == 1080
+    ctx.destroy()
+    return True
+
+
+def test_engine_user_inputs_broadcast():
+    _run(_user_inputs, 2)
