@@ -183,7 +183,7 @@ def gs_orbit_camera(k: int, dev):
     return Camera.from_c2w(look_at(eye, torch.zeros(3), up=(0.0, 0.0, 1.0)).numpy(), 1920, 1080, focal_x=1400.0, zfar=2000.0).to(dev)
 
 
-def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = 20):
+def render_fps_3dgs(n_gauss: int = 6_000_000, frames: int = int(os.environ.get("LMB_3DGS_FRAMES", "20"))):
     """Secondary figures on 6 M random Gaussians through the public classes: ``Gaussian3DTrainer`` (its model, its fused
     optimiser, its ``train_step``: render, L1 + SSIM, rasteriser backward, densification statistics, Adam) and the model's
     evaluation-mode render call that the evaluator loops over (visibility prefilter, visible subset, rasteriser).
