@@ -60,11 +60,11 @@ class _WireTensor:
 def _to_wire(obj):
     if torch.is_tensor(obj) and obj.device.type == "cpu" and not obj.requires_grad and obj.dtype != torch.bfloat16:
         return _WireTensor(obj.numpy())
-    if isinstance(obj, tuple):
+    if type(obj) is tuple:                 # plain containers only: subclasses (named tuples, ...) travel as they are
         return tuple(_to_wire(o) for o in obj)
-    if isinstance(obj, list):
+    if type(obj) is list:
         return [_to_wire(o) for o in obj]
-    if isinstance(obj, dict):
+    if type(obj) is dict:
         return {k: _to_wire(v) for k, v in obj.items()}
     return obj
 
@@ -72,11 +72,11 @@ def _to_wire(obj):
 def _from_wire(obj):
     if isinstance(obj, _WireTensor):
         return torch.from_numpy(obj.array)
-    if isinstance(obj, tuple):
+    if type(obj) is tuple:
         return tuple(_from_wire(o) for o in obj)
-    if isinstance(obj, list):
+    if type(obj) is list:
         return [_from_wire(o) for o in obj]
-    if isinstance(obj, dict):
+    if type(obj) is dict:
         return {k: _from_wire(v) for k, v in obj.items()}
     return obj
 
