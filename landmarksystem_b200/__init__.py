@@ -69,4 +69,27 @@ def init_training(trainer_cls, config):
     return trainer_cls(config)
 
 
-__all__ = ["init_inference", "init_training", "Config"]
+# Names the reference exports from its package root (landmark/__init__.py:4-19).  They are resolved on first access so
+# that importing the package stays light for the configuration and data layers.
+_LAZY = {
+    "InferenceEngine": (".render.inference_engine", "InferenceEngine"),
+    "InferenceInterface": (".render.inference_module", "InferenceInterface"),
+    "InferenceModule": (".render.inference_module", "InferenceModule"),
+    "InferenceModuleInitializer": (".render.initializer", "InferenceModuleInitializer"),
+    "Model": (".components.model.base_model", "Model"),
+    "init_communication_context": (".comm", "init_communication_context"),
+}
+
+
+def __getattr__(name):
+    if name in _LAZY:
+        import importlib
+
+        module, attr = _LAZY[name]
+        value = getattr(importlib.import_module(module, __name__), attr)
+        globals()[name] = value
+        return value
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+__all__ = ["init_inference", "init_training", "Config", "EnvSetting", *_LAZY]

@@ -18,6 +18,32 @@ from ..cameras import Camera
 from .ray_utils import get_ray_directions_blender, get_rays, pose_spherical
 
 
+def _arg(args, name, default):
+    """``args.name`` of a namespace / mapping-like configuration, ``default`` when absent or ``None``-less."""
+    if args is None:
+        return default
+    value = args.get(name, default) if hasattr(args, "get") else getattr(args, name, default)
+    return default if value is None else value
+
+
+class _Overlay:
+    """A configuration seen through a dictionary of overrides."""
+
+    def __init__(self, base, over):
+        self._base, self._over = base, over
+
+    def get(self, name, default=None):
+        if name in self._over:
+            return self._over[name]
+        return _arg(self._base, name, default)
+
+    def __getattr__(self, name):
+        value = self.get(name, None)
+        if value is None:
+            raise AttributeError(name)
+        return value
+
+
 class BaseDataset(Dataset):
     def __init__(self, split: str = "train", downsample: float = 1.0, is_stack: bool = False, args=None):
         self.split, self.downsample, self.is_stack, self.args = split, downsample, is_stack, args
@@ -56,12 +82,74 @@ class VolumeRenderDataset(BaseDataset):
             self.all_idxs = torch.cat(idxs)
             self.all_rgbs = torch.cat(images) if images is not None else None
 
-    def read_meta_path(self, n_frames: int = 100, radius: float = 4.0, downward: float = -45.0):
-        """Spherical render path (``render_spherical``): poses only, no images."""
-        poses = torch.stack([pose_spherical(a, downward, radius) for a in np.linspace(-180, 180, n_frames + 1)[:-1]])
-        W, H = self.img_wh
+    def render_path_poses(self) -> torch.Tensor:
+        """Camera-to-world matrices ``[n, 4, 4]`` of the ``"path"`` split.
+
+        ``render_spherical``: ``render_nframes // render_skip`` cameras on ``render_ncircle`` turns of a circle of
+        radius ``render_spherical_radius`` looking ``render_downward`` degrees down, moved to ``self.cxyz`` when the
+        dataset has a scene centre, descending by ``render_spherical_zdiff`` over the first half of the frames and
+        climbing back over the second.  Otherwise the frames of ``datadir/trajectories/path{render_pathid}.json``
+        (``{"frames": [{"transform_matrix": ...}]}``), every ``render_skip``-th.
+        """
+        a = self.args
+        skip = max(int(_arg(a, "render_skip", 1)), 1)
+        if bool(_arg(a, "render_spherical", False)):
+            n = max(int(_arg(a, "render_nframes", 100)) // skip, 1)
+            radius = float(_arg(a, "render_spherical_radius", 4.0))
+            downward = float(_arg(a, "render_downward", -45.0))
+            zdiff = float(_arg(a, "render_spherical_zdiff", 1.0))
+            angles = np.linspace(0.0, 360.0 * float(_arg(a, "render_ncircle", 1)), n + 1)[:-1]
+            poses = torch.stack([pose_spherical(float(t), downward, radius) for t in angles])
+            centre = getattr(self, "cxyz", None)
+            if centre is not None:
+                poses[:, :3, 3] += torch.as_tensor(centre, dtype=torch.float32)[:3]
+            if zdiff > 0:
+                half, zstep = n // 2, zdiff / n * 2
+                k = torch.arange(n, dtype=torch.float32)
+                poses[:, 2, 3] -= torch.where(k < half, zstep * k, zdiff - zstep * (k - half))
+            return poses
+        import json
+
+        name = os.path.join(self.datadir, "trajectories", f"path{int(_arg(a, 'render_pathid', 0))}.json")
+        with open(name, "r", encoding="utf-8") as fh:
+            frames = json.load(fh)["frames"][::skip]
+        return torch.tensor([f["transform_matrix"] for f in frames], dtype=torch.float32)
+
+    def read_meta_path(self, n_frames: Optional[int] = None, radius: Optional[float] = None,
+                       downward: Optional[float] = None):
+        """Rays of the ``"path"`` split: poses only, no images (reference: base_dataset.py:151-214).
+
+        The image is ``render_px`` rows of 16:9 with the focal length of ``render_fov`` degrees (over the rows); near /
+        far planes and the bounding box come from ``render_near_far`` / ``render_lb`` / ``render_ub`` when set.  The
+        keyword arguments override the configured spherical path (frame count, radius, downward angle).
+        """
+        a = self.args
+        if n_frames is not None or radius is not None or downward is not None:
+            over = {"render_spherical": True, "render_skip": 1, "render_spherical_zdiff": 0.0}
+            if n_frames is not None:
+                over["render_nframes"] = n_frames
+            if radius is not None:
+                over["render_spherical_radius"] = radius
+            if downward is not None:
+                over["render_downward"] = downward
+            self.args = _Overlay(a, over)
+        try:
+            poses = self.render_path_poses()
+        finally:
+            self.args = a
+        if a is not None and _arg(a, "render_px", None) and self.split == "path":
+            H = int(_arg(a, "render_px", 720))
+            W = int(1920 / 1080 * H)
+            focal = 0.5 * H / np.tan(0.5 * np.deg2rad(float(_arg(a, "render_fov", 65.0))))
+        else:
+            (W, H), focal = self.img_wh, self.focal
+        if a is not None and _arg(a, "render_near_far", None):
+            self.near_far = list(a.render_near_far)
+        if a is not None and _arg(a, "render_lb", None) and _arg(a, "render_ub", None):
+            self.render_scene_bbox = torch.tensor([list(a.render_lb), list(a.render_ub)], dtype=torch.float32)
         self.is_stack = True
-        self.build_rays(poses, None, H, W, self.focal)
+        self.build_rays(poses, None, H, W, focal, _arg(a, "camera", "normal"))
+        self.render_poses, self.render_rays = poses, self.all_rays
 
     def __len__(self):
         return 0 if self.all_rays is None else self.all_rays.shape[0]

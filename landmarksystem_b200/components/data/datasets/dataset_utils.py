@@ -56,6 +56,12 @@ def prep_testdataset(config):
                                                      is_stack=True, args=config)
 
 
+def prep_pathdataset(config):
+    """The ``"path"`` split: a fly-around (``render_spherical``) or the frames of ``trajectories/path{id}.json``."""
+    return _dataset_cls(config.dataset_name, "nerf")(split="path", downsample=config.downsample_train,
+                                                     is_stack=True, args=config)
+
+
 def prep_dataset(enable_lpips, config):
     return prep_traindataset(enable_lpips, config), prep_testdataset(config)
 

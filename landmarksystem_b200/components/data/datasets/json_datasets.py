@@ -55,6 +55,9 @@ class _JsonNeRFDataset(VolumeRenderDataset):
         self.near_far = list(getattr(args, "train_near_far", None) or [0.1, 10.0])
         self.white_bg = bool(getattr(args, "white_bkgd", False))
         self.enable_lpips = enable_lpips
+        if split == "path":                          # fly-around or trajectory file: poses only, no images
+            self.read_meta_path()
+            return
         meta = load_transforms(self.datadir, split)
         W, H, focal = self.intrinsics(meta)
         paths, poses = frames_to_poses(meta)

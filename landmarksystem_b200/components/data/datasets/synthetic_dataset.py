@@ -48,9 +48,16 @@ def _rig(args, split):
 class SyntheticNeRFDataset(VolumeRenderDataset):
     def __init__(self, split="train", downsample=1.0, is_stack=False, args=None, enable_lpips=False):
         super().__init__(split, downsample, is_stack, args)
-        field, poses, H, W, focal, near, far = _rig(args, split)
+        field, poses, H, W, focal, near, far = _rig(args, "test" if split == "path" else split)
         H, W, focal = int(H / downsample), int(W / downsample), focal / downsample
         self.white_bg = bool(getattr(args, "white_bkgd", False))
+        if split == "path":                     # fly-around of the box centre (or a trajectory file): poses only
+            self.near_far, self.img_wh, self.focal = [near, far], (W, H), focal
+            self.datadir = str(getattr(args, "datadir", ""))
+            self.cxyz = ((np.array(list(args.lb)) + np.array(list(args.ub))) / 2).tolist()
+            self.read_meta_path()
+            self.all_rays[..., 3:6] = torch.nn.functional.normalize(self.all_rays[..., 3:6], dim=-1)
+            return
         data = make_blob_dataset(field, poses, H, W, focal, near, far, white_bg=self.white_bg,
                                  n_quad=int(getattr(args, "synthetic_quadrature", 128)), normalize_dirs=True)
         self.near_far = [near, far]

@@ -179,6 +179,27 @@ class OctreeGSEncoding(ScaffoldGSEncoding):
         pred = torch.log2(self.standard_dist / dist) / math.log2(self.fork) + self._extra_level
         self._anchor_mask = self._level.squeeze(1) <= self.map_to_int_level(pred, coarse_index - 1, self._level)
 
+    def plot_levels(self):
+        """Print and return ``[(level, anchors, share of all anchors)]`` (reference: octreegs_encoding.py:1086-1101)."""
+        level = self._level.detach().squeeze(1)
+        total = max(int(level.shape[0]), 1)
+        rows = []
+        for lv in range(int(self.levels)):
+            n = int((level == lv).sum())
+            rows.append((lv, n, n / total))
+            print(f"Level {lv}: {n}, Ratio: {n / total}")
+        return rows
+
+    def get_remove_duplicates(self, grid_coords: torch.Tensor, selected_grid_coords_unique: torch.Tensor,
+                              use_chunk: bool = True) -> torch.Tensor:
+        """``[N]`` mask of the rows of ``grid_coords`` that also appear in ``selected_grid_coords_unique`` (integer
+        voxel coordinates): one packed 64-bit key per voxel and a sorted membership test instead of the reference's
+        chunked all-pairs comparison (octreegs_encoding.py:628-660); ``use_chunk`` is accepted for compatibility."""
+        return torch.isin(voxel_keys(torch.round(grid_coords)), voxel_keys(torch.round(selected_grid_coords_unique)))
+
+    def construct_list_of_attributes(self):
+        return super().construct_list_of_attributes() + ["level", "extra_level", "info"]
+
     # -- PLY ---------------------------------------------------------------------------------------------------
     def save_ply(self, path: str):
         cols = self._ply_columns()

@@ -89,6 +89,30 @@ class ScaffoldGSEncoding(BaseGaussianEncoding):
     def get_opacity(self):
         return torch.sigmoid(self._opacity)
 
+    @property
+    def get_anchor_feat(self):
+        return self._anchor_feat
+
+    @property
+    def get_offset(self):
+        return self._offset
+
+    def set_anchor(self, new_anchor: torch.Tensor):
+        assert new_anchor.shape == self._anchor.shape, "the new anchors must keep the shape of the old ones"
+        self._anchor = nn.Parameter(new_anchor.to(self.device).float().contiguous(),
+                                    requires_grad=self._anchor.requires_grad)
+
+    def get_covariance(self, scaling_modifier: float = 1.0) -> torch.Tensor:
+        """Upper triangle ``[N, 6]`` of the anchors' world-space covariance ``R S S^T R^T`` (first three scales)."""
+        from ....components.utils.general_utils import build_scaling_rotation, strip_symmetric
+
+        L = build_scaling_rotation(scaling_modifier * self.get_scaling[:, :3], self._rotation)
+        return strip_symmetric(L @ L.transpose(1, 2))
+
+    def construct_list_of_attributes(self):
+        """Column names of the PLY file, in file order."""
+        return list(self._ply_columns().keys())
+
     def __len__(self):
         return self._anchor.shape[0]
 

@@ -143,13 +143,21 @@ class BaseGaussian(Model):
         assert found, "model has no Gaussian encoding"
         return found[-1]
 
-    def save_model(self, dir_path, rank: Optional[int] = None) -> None:
+    def save_ply(self, dir_path, rank: Optional[int] = None) -> None:
+        """``point_cloud[-sub{rank}].ply`` of the Gaussian encoding (reference: base_model.py:266-281)."""
         os.makedirs(dir_path, exist_ok=True)
         suffix = "" if rank is None else f"-sub{rank}"
-        name, encoding = self._find_gaussian_encoding()
-        encoding.save_ply(os.path.join(dir_path, f"point_cloud{suffix}.ply"))
-        rest = {k: v for k, v in self.state_dict().items() if not k.startswith(name + ".")}
-        torch.save(rest, os.path.join(dir_path, f"state_dict{suffix}.th"))
+        self._find_gaussian_encoding()[1].save_ply(os.path.join(dir_path, f"point_cloud{suffix}.ply"))
+
+    def save_state_dict(self, file_path) -> None:
+        """Everything but the Gaussian encoding, which travels as PLY (reference: base_model.py:283-304)."""
+        name, _ = self._find_gaussian_encoding()
+        torch.save({k: v for k, v in self.state_dict().items() if not k.startswith(name + ".")}, file_path)
+
+    def save_model(self, dir_path, rank: Optional[int] = None) -> None:
+        suffix = "" if rank is None else f"-sub{rank}"
+        self.save_ply(dir_path, rank)
+        self.save_state_dict(os.path.join(dir_path, f"state_dict{suffix}.th"))
         if self._kwargs_keys:
             self.save_kwargs(os.path.join(dir_path, f"kwargs{suffix}.th"))
 

@@ -214,10 +214,13 @@ class ProposalNetworkSampler(BaseSampler):
             b = self.anneal_slope
             self._anneal = b * frac / ((b - 1) * frac + 1)
 
-    def forward(self, origins, directions, near, far, density_fns: List[Callable], camera_indices=None):
-        """Returns ``(ray_samples, weights_list, ray_samples_list)``."""
-        self.initial_sampler.train(self.training)
-        self.pdf_sampler.train(self.training)
+    def forward(self, origins, directions, near, far, density_fns: List[Callable], camera_indices=None,
+                render_stratified_sampling: bool = False):
+        """Returns ``(ray_samples, weights_list, ray_samples_list)``.  ``render_stratified_sampling`` keeps the
+        jitter of the bins outside training as well (reference: proposal_network_sampler.py:184-199)."""
+        stratified = bool(self.training or render_stratified_sampling)
+        self.initial_sampler.train(stratified)
+        self.pdf_sampler.train(stratified)
         weights_list, samples_list = [], []
         n = self.num_proposal_network_iterations
         weights = ray_samples = None

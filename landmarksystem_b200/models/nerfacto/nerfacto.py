@@ -7,6 +7,7 @@ from typing import List, Optional, Tuple, Union
 import numpy as np
 import torch
 from torch import nn
+from pydantic import model_validator
 from typing_extensions import Literal
 
 from ...components.data.rays import Rays
@@ -31,6 +32,7 @@ class NerfactoConfig(ConfigClass):
     hidden_dim: int = 64
     hidden_dim_color: int = 64
     appearance_embedding_dim: int = 32
+    appearance_embed_dim: Optional[int] = None      # the reference's spelling (nerfacto.py:47); wins when given
     appearance_embedding_size: int = 1
     geo_feat_dim: int = 15
     num_layers: int = 2
@@ -62,11 +64,40 @@ class NerfactoConfig(ConfigClass):
     add_lpips: int = -1
     runtime: Literal["Torch", "Kernel"] = "Kernel"
     lr_init: float = 1e-2
+    lr: Optional[float] = None                      # the reference's spelling (nerfacto.py:95); wins when given
     lr_final: float = 0.0001
     lr_decay_max_steps: int = 50000
     eps: float = 1e-15
-    render_batch_size: int = 8192
+    # the "path" split of the datasets (fly-around or trajectory file)
+    render_px: int = 720
+    render_fov: float = 65.0
+    render_nframes: int = 100
+    render_skip: int = 1
+    render_fps: int = 30
+    render_spherical: bool = False
+    render_spherical_zdiff: float = 1.0
+    render_spherical_radius: float = 4.0
+    render_downward: float = -45.0
+    render_ncircle: float = 1
+    render_path: bool = False
+    render_pathid: int = 0
     render_near_far: Optional[List[float]] = None
+    render_lb: Optional[List[float]] = None
+    render_ub: Optional[List[float]] = None
+    render_batch_size: int = 8192
+    distance_scale: float = 25
+    render_stratified_sampling: bool = False        # the reference jitters evaluation renders too (True there)
+
+    @model_validator(mode="after")
+    def _one_spelling(self):
+        """Both spellings of the two renamed fields read the same value afterwards."""
+        if self.appearance_embed_dim is not None:
+            self.appearance_embedding_dim = int(self.appearance_embed_dim)
+        self.appearance_embed_dim = self.appearance_embedding_dim
+        if self.lr is not None:
+            self.lr_init = float(self.lr)
+        self.lr = self.lr_init
+        return self
 
 
 def scene_contraction(x: torch.Tensor) -> torch.Tensor:
@@ -176,7 +207,9 @@ class Nerfacto(BaseNeRF):
         cam = rays[:, 6] if rays.shape[1] > 6 else torch.zeros(rays.shape[0], device=rays.device)
         self.sampler.train(self.training)
         near, far = self.near_far
-        samples, weights_list, samples_list = self.sampler(o, d, near, far, self.proposal_networks.density_fns, cam)
+        samples, weights_list, samples_list = self.sampler(
+            o, d, near, far, self.proposal_networks.density_fns, cam,
+            render_stratified_sampling=bool(c.get("render_stratified_sampling", False)))
         R, S = samples.starts.shape[:2]
         pos = samples.positions.reshape(-1, 3)
         if self.training:

@@ -52,15 +52,37 @@ class OctreeGS(ScaffoldGS):
         self._init_decoder(dist2level=c.dist2level)
         self.iteration = 0
 
+    # -- the reference's model-level helpers (octree_gs/gs_model.py:203-221) ------------------------------------
+    def set_level(self, points, train_cameras):
+        c = self.config
+        self.gaussian_encoding.set_level(points, train_cameras, c.resolution_scales, c.dist_ratio, c.init_level, c.levels)
+
+    def set_coarse_interval(self):
+        self.gaussian_encoding.set_coarse_interval(self.config.coarse_iter, self.config.coarse_factor)
+
+    def set_anchor_mask(self, cam_center, iteration, resolution_scale):
+        self.gaussian_encoding.set_anchor_mask(cam_center, iteration, resolution_scale, self.anchor_decoder.training)
+
+    def plot_levels(self):
+        return self.gaussian_encoding.plot_levels()
+
     def create_from_pcd(self, pcd, spatial_lr_scale: float, cameras=None):
+        """With ``cameras`` the level structure is fitted first, on every ``ratio``-th distinct input point
+        (reference: octree_gs/gs_trainer.py:67-76), and the anchors are then built from those points."""
+        from types import SimpleNamespace
+
         import numpy as np
 
         c, enc = self.config, self.gaussian_encoding
         self.spatial_lr_scale = spatial_lr_scale
         if cameras:
             pts = torch.as_tensor(np.asarray(pcd.points), dtype=torch.float32, device=self.device)
-            enc.set_level(pts, cameras, c.resolution_scales, c.dist_ratio, c.init_level, c.levels)
-            enc.set_coarse_interval(c.coarse_iter, c.coarse_factor)
+            ratio = max(int(c.get("ratio", 1) or 1), 1)
+            if ratio > 1:
+                pts = torch.unique(pts[::ratio], dim=0)
+                pcd = SimpleNamespace(points=pts.cpu().numpy())
+            self.set_level(pts, cameras)
+            self.set_coarse_interval()
         enc.create_from_pcd(pcd)
 
     def _view_mask(self, cam):

@@ -2,6 +2,7 @@
 benchmarks/nerf/scaffold_gs/gs_model.py:18-444)."""
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -85,6 +86,16 @@ class ScaffoldGSConfig(ConfigClass):
     init_points_volume: bool = False
     runtime: str = "Torch"
     kernel_fusion: bool = False
+    # accepted from the reference's configuration files (scaffold_gs/gs_model.py:86-87, octree_gs/gs_model.py:33-41)
+    convert_SHs_python: bool = False            # no effect: colours come from the anchor decoder
+    compute_cov3D_python: bool = False          # pre-filter anchors with covariances built in PyTorch
+    white_background: bool = False
+    random_background: bool = False
+    data_device: str = "cuda"
+    eval: bool = False
+    ds: int = 1
+    ratio: int = 1                              # keep every ``ratio``-th input point (Octree-GS initialisation)
+    undistorted: bool = False
 
 
 class ScaffoldGS(BaseGaussian):
@@ -122,6 +133,23 @@ class ScaffoldGS(BaseGaussian):
         if self.config.appearance_dim > 0:
             self.embedding_appearance = torch.nn.Embedding(num_cameras, self.config.appearance_dim).to(self.device)
 
+    def get_appearance_code(self, appearance_code_idx):
+        return self.embedding_appearance(appearance_code_idx)
+
+    def save_mlp_checkpoints(self, path: str):
+        """The decoder heads (and feature bank / appearance embedding when present) in one file with the reference's
+        keys (scaffold_gs/gs_model.py, ``save_mlp_checkpoints``)."""
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        dec = self.anchor_decoder
+        out = {"anchor_decoder.opacity_mlp": dec.mlp_opacity.state_dict(),
+               "anchor_decoder.cov_mlp": dec.mlp_cov.state_dict(),
+               "anchor_decoder.color_mlp": dec.mlp_color.state_dict()}
+        if self.config.use_feat_bank and getattr(dec, "mlp_feature_bank", None) is not None:
+            out["anchor_decoder.mlp_feature_bank"] = dec.mlp_feature_bank.state_dict()
+        if self.embedding_appearance is not None:
+            out["anchor_decoder.embedding_appearance"] = self.embedding_appearance.state_dict()
+        torch.save(out, path)
+
     def init_renderer(self):
         self.renderer = GaussianRasterizer(None)
 
@@ -133,6 +161,15 @@ class ScaffoldGS(BaseGaussian):
     def prefilter_voxel(self, camera, anchor_mask=None, scaling_modifier: float = 1.0) -> torch.Tensor:
         enc = self.gaussian_encoding
         rast = GaussianRasterizer(raster_settings_for(camera, self.background, 1, scaling_modifier, self.config.debug))
+        if self.config.get("compute_cov3D_python", False):
+            cov = enc.get_covariance(1.0)       # the rasteriser settings already carry ``scaling_modifier``
+            if anchor_mask is None:
+                return rast.visible_filter(enc.get_anchor, cov3D_precomp=cov) > 0
+            idx = anchor_mask.nonzero().squeeze(-1)
+            radii = rast.visible_filter(enc.get_anchor[idx], cov3D_precomp=cov[idx])
+            out = torch.zeros_like(anchor_mask)
+            out[idx] = radii > 0
+            return out
         if anchor_mask is None:
             radii = rast.visible_filter(enc.get_anchor, scales=enc.get_scaling[:, :3], rotations=enc.get_rotation)
             return radii > 0

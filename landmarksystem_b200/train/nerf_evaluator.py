@@ -79,6 +79,8 @@ class NeRFEvaluator:
         mean = float(np.mean(psnrs)) if len(psnrs) else float("nan")
         if is_main_rank():
             print(f"======> {self.config.expname} test all psnr: {mean} <========================", flush=True)
+        if self.config.get("render_path", False) and hasattr(self, "render_path"):
+            self.render_path()
         return mean
 
 
@@ -115,6 +117,19 @@ class RayModelEvaluator(NeRFEvaluator):
         if cfg.get("runtime", "Torch") == "Kernel":
             model = ComponentConvertorFactory.get_convertor("runtime").convert(model, cfg)
         return model.eval()
+
+    @torch.no_grad()
+    def render_path(self, savePath=None):
+        """Render the ``"path"`` split (``render_path=True``: a fly-around or a trajectory file, no ground truth) into
+        ``<logfolder>/imgs_path_all/``; returns the number of frames."""
+        from ..components.data.datasets.dataset_utils import prep_pathdataset
+
+        dataset = prep_pathdataset(self.config)
+        savePath = savePath or f"{self.logfolder}/imgs_path_all/"
+        if is_main_rank():
+            os.makedirs(savePath, exist_ok=True)
+        self.evaluation(dataset, self.config, savePath, N_vis=-1, prtx="path_")
+        return int(dataset.all_rays.shape[0])
 
     def render_rays(self, rays):
         return self.model.render_all_rays(rays, chunk_size=self.config.get("render_batch_size", self.config.batch_size))

@@ -141,3 +141,31 @@ def test_metrics_logger_with_wandb_flag_but_no_package(tmp_path, capsys):
     log.log(1, {"Train/Loss": 0.5})
     log.close()
     assert (tmp_path / "metrics.jsonl").read_text().count("Train/Loss") == 1
+
+
+def test_nerfacto_config_accepts_both_spellings_and_render_fields():
+    """The reference spells two fields ``appearance_embed_dim`` / ``lr`` (nerfacto.py:47, 95); both spellings read the
+    same value, and the ``render_*`` fields of the path split are part of the block."""
+    from landmarksystem_b200.models.nerfacto.nerfacto import NerfactoConfig
+
+    a = NerfactoConfig(appearance_embed_dim=8, lr=3e-3, render_px=360, render_spherical=True)
+    assert a.appearance_embedding_dim == 8 and a.appearance_embed_dim == 8
+    assert a.lr_init == 3e-3 and a.lr == 3e-3 and a.render_px == 360 and a.render_spherical
+    b = NerfactoConfig(appearance_embedding_dim=16, lr_init=1e-3)
+    assert b.appearance_embed_dim == 16 and b.lr == 1e-3
+    flat = dict(iter(b))
+    assert {"render_nframes", "render_pathid", "render_lb", "distance_scale", "render_stratified_sampling"} <= set(flat)
+
+
+def test_package_root_exports_match_the_reference():
+    """``landmark/__init__.py:4-19`` exports these names from the package root."""
+    import landmarksystem_b200 as lm
+    from landmarksystem_b200.components.model.base_model import Model
+    from landmarksystem_b200.render.inference_module import InferenceModule
+
+    assert lm.InferenceModule is InferenceModule and lm.Model is Model
+    for name in ("InferenceEngine", "InferenceInterface", "InferenceModuleInitializer", "init_communication_context",
+                 "init_inference", "Config", "EnvSetting"):
+        assert getattr(lm, name) is not None
+    with pytest.raises(AttributeError):
+        lm.no_such_name

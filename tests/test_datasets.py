@@ -132,3 +132,47 @@ def test_drone_metadata_loader(tmp_path):
         json.dump({"fl_x": 55.0, "frames": frames}, fh)
     meta = load_drone_meta(str(tmp_path), "test", 4, stride=2)
     assert float(meta["focals"]) == 55.0 and len(meta["fnames"]) == 2
+
+
+def _path_args(tmp_path, **over):
+    base = dict(datadir=str(tmp_path), lb=[-1, -1, -1], ub=[1, 1, 1], train_near_far=[0.1, 5.0], white_bkgd=False,
+                camera="normal", render_px=18, render_fov=60.0, render_nframes=12, render_skip=2, render_spherical=True,
+                render_spherical_zdiff=0.5, render_spherical_radius=3.0, render_downward=-30.0, render_ncircle=1,
+                render_pathid=3, render_near_far=[0.2, 9.0], render_lb=[-2, -2, -2], render_ub=[2, 2, 2])
+    base.update(over)
+    return SimpleNamespace(**base)
+
+
+def test_path_split_spherical_and_trajectory(tmp_path):
+    """The ``"path"`` split of the ray datasets: a fly-around built from the ``render_*`` fields, or the frames of
+    ``trajectories/path{id}.json`` (reference: base_dataset.py:151-214)."""
+    import json
+
+    from landmarksystem_b200.components.data.datasets import dataset_dict
+    from landmarksystem_b200.components.data.datasets.ray_utils import pose_spherical
+
+    cls = dataset_dict["matrixcity"] if "matrixcity" in dataset_dict else next(iter(dataset_dict.values()))
+    ds = cls(split="path", downsample=1.0, is_stack=True, args=_path_args(tmp_path))
+    n, H = 12 // 2, 18
+    W = int(1920 / 1080 * H)
+    assert ds.all_rgbs is None and tuple(ds.img_wh) == (W, H)
+    assert ds.all_rays.shape == (n, H * W, 6) and ds.render_poses.shape == (n, 4, 4)
+    assert ds.near_far == [0.2, 9.0] and torch.equal(ds.render_scene_bbox, torch.tensor([[-2.0] * 3, [2.0] * 3]))
+    assert math.isclose(ds.focal if not isinstance(ds.focal, tuple) else ds.focal[0],
+                        0.5 * H / math.tan(math.radians(30.0)), rel_tol=1e-6)
+    # frame k: angle 360 k / n, 30 degrees down, radius 3; height drops by zstep * k in the first half, climbs after
+    zstep = 0.5 / n * 2
+    for k in range(n):
+        want = pose_spherical(360.0 * k / n, -30.0, 3.0)
+        want[2, 3] -= zstep * k if k < n // 2 else 0.5 - zstep * (k - n // 2)
+        assert torch.allclose(ds.render_poses[k], want, atol=1e-6)
+    # ray origins are the camera centres; the centre pixel looks at the (height-shifted) origin side of the sphere
+    assert torch.allclose(ds.all_rays[0, :, :3], ds.render_poses[0, :3, 3].expand(H * W, 3), atol=1e-6)
+
+    frames = [{"transform_matrix": (torch.eye(4) + 0.01 * k).tolist()} for k in range(7)]
+    os.makedirs(tmp_path / "trajectories")
+    with open(tmp_path / "trajectories" / "path3.json", "w", encoding="utf-8") as fh:
+        json.dump({"frames": frames}, fh)
+    ds2 = cls(split="path", downsample=1.0, is_stack=True, args=_path_args(tmp_path, render_spherical=False, render_skip=3))
+    assert ds2.render_poses.shape[0] == 3                                  # frames 0, 3, 6
+    assert torch.allclose(ds2.render_poses[1], torch.eye(4) + 0.03)

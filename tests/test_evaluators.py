@@ -33,3 +33,9 @@ def test_train_then_evaluate_cpu(family, tmod, tcls, emod, ecls, conf, extra, tm
     ev = getattr(importlib.import_module(f"landmarksystem_b200.models.{family}.{emod}"), ecls)(cfg)
     assert np.isfinite(ev.eval())
     assert any(f.endswith(".png") for f in os.listdir(ev.save_folder))
+    if family == "gridnerf":                     # the "path" split: a fly-around without ground truth
+        cfg.render_spherical, cfg.render_nframes, cfg.render_px = True, 3, 9
+        cfg.render_spherical_radius, cfg.render_near_far = 3.0, None
+        assert ev.render_path() == 3
+        frames = sorted(f for f in os.listdir(os.path.join(ev.logfolder, "imgs_path_all")) if f.startswith("path_"))
+        assert len(frames) == 3

@@ -159,6 +159,75 @@ def test_octree_lod_kernel_matches_torch():
         assert (cpu._anchor_mask != gpu._anchor_mask.cpu()).float().mean() < 1e-3
 
 
+def test_anchor_encoding_accessors_and_octree_helpers(tmp_path):
+    """Accessors the reference's encodings offer (scaffoldgs_encoding.py:307-760, octreegs_encoding.py:445-1101)."""
+    from landmarksystem_b200.components.utils.general_utils import build_rotation
+
+    torch.manual_seed(1)
+    enc = OctreeGSEncoding(feat_dim=8, n_offsets=4, base_layer=3, device="cpu", visible_threshold=0.0)
+    enc.levels, enc.init_level = 3, 0
+    enc.create_from_pcd(_pcd(300))
+    n = len(enc)
+    enc._rotation.data = torch.nn.functional.normalize(torch.randn(n, 4), dim=-1)
+    assert enc.get_anchor_feat is enc._anchor_feat and enc.get_offset is enc._offset
+    cov = enc.get_covariance(2.0)                                   # upper triangle of R S S^T R^T, S = 2 * scales
+    R, S = build_rotation(enc._rotation), 2.0 * enc.get_scaling[:, :3]
+    full = R @ torch.diag_embed(S * S) @ R.transpose(1, 2)
+    assert torch.allclose(cov, torch.stack((full[:, 0, 0], full[:, 0, 1], full[:, 0, 2], full[:, 1, 1], full[:, 1, 2],
+                                            full[:, 2, 2]), -1), atol=1e-6)
+    path = str(tmp_path / "pc.ply")
+    enc.save_ply(path)
+    assert list(read_ply(path).dtype.names) == enc.construct_list_of_attributes()
+    rows = enc.plot_levels()
+    assert sum(r[1] for r in rows) == n and abs(sum(r[2] for r in rows) - 1.0) < 1e-6
+    grid = torch.tensor([[0, 0, 0], [1, 2, 3], [-4, 5, 6], [7, 7, 7]], dtype=torch.float32)
+    sel = torch.tensor([[1, 2, 3], [7, 7, 7], [9, 9, 9]], dtype=torch.float32)
+    assert enc.get_remove_duplicates(grid, sel).tolist() == [False, True, False, True]
+    moved = enc.get_anchor + 1.0
+    enc.set_anchor(moved)
+    assert torch.equal(enc.get_anchor, moved)
+    with pytest.raises(AssertionError):
+        enc.set_anchor(moved[:-1])
+
+
+def test_scaffold_model_helpers_cov_prefilter_and_mlp_file(tmp_path):
+    """Model-level helpers of the reference (scaffold_gs/gs_model.py, octree_gs/gs_model.py:200-221, 428-443,
+    base_model.py:266-304): the covariance route of the anchor pre-filter agrees with the scale / rotation route."""
+    import importlib
+
+    from landmarksystem_b200.components.data.cameras import Camera
+    from landmarksystem_b200.synthetic import ring_cameras
+
+    mod = importlib.import_module("landmarksystem_b200.models.octree_gs.gs_trainer")
+    conf = os.path.join(ROOT, "octree_gs", "confs", "synthetic_train.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": str(tmp_path), "device": "cpu", "n_iters": "1",
+                                      "datadir": "ring:3:16x16:18:3", "init_points_num": "80",
+                                      "progress_refresh_rate": "100"})
+    assert cfg.ratio == 1 and cfg.compute_cov3D_python is False
+    model = mod.OctreeGSTrainer(cfg).model
+    cam = [Camera.from_c2w(p.numpy(), 32, 32, 40.0, uid=i) for i, p in enumerate(ring_cameras(3, 3.0))][0]
+    model.set_anchor_mask(cam.camera_center, 10 ** 6, 1.0)
+    mask = model.gaussian_encoding._anchor_mask.clone()
+    by_scales = model.prefilter_voxel(cam, anchor_mask=mask)
+    cfg.compute_cov3D_python = True
+    by_cov = model.prefilter_voxel(cam, anchor_mask=mask)
+    cfg.compute_cov3D_python = False
+    assert by_scales.any() and torch.equal(by_scales, by_cov)
+    assert len(model.plot_levels()) == model.gaussian_encoding.levels
+    code = model.get_appearance_code(torch.tensor(0)) if model.embedding_appearance is not None else None
+    assert code is None or code.shape == (cfg.appearance_dim,)
+
+    model.save_mlp_checkpoints(str(tmp_path / "mlp" / "checkpoint.pth"))
+    saved = torch.load(str(tmp_path / "mlp" / "checkpoint.pth"), weights_only=False)
+    assert {"anchor_decoder.opacity_mlp", "anchor_decoder.cov_mlp", "anchor_decoder.color_mlp"} <= set(saved)
+    assert ("anchor_decoder.embedding_appearance" in saved) == (model.embedding_appearance is not None)
+    model.save_ply(str(tmp_path / "out"), rank=1)
+    model.save_state_dict(str(tmp_path / "out" / "state_dict-sub1.th"))
+    assert os.path.exists(tmp_path / "out" / "point_cloud-sub1.ply")
+    rest = torch.load(str(tmp_path / "out" / "state_dict-sub1.th"), weights_only=False)
+    assert rest and not any(k.startswith("gaussian_encoding.") for k in rest)
+
+
 @pytest.mark.parametrize("family,trainer_name", [("origin_gs", "Gaussian3DTrainer"), ("scaffold_gs", "ScaffoldGSTrainer"),
                                                   ("octree_gs", "OctreeGSTrainer")])
 def test_cpu_smoke_training_and_checkpoint(family, trainer_name, tmp_path):
