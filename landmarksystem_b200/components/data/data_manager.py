@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 from torch.utils.data import ConcatDataset, DataLoader
 
-from .datasets.dataset_utils import (DatasetInfo, DistributedSampler, get_preprocessed_loader, prep_dataset,
+from .datasets.dataset_utils import (CameraDistributedSampler, DatasetInfo, get_preprocessed_loader, prep_dataset,
                                      prep_sampler, prep_testdataset, prep_testdataset_gs, prep_traindataset,
                                      prep_traindataset_gs)
 
@@ -124,7 +124,7 @@ class DatasetManager:
     def _build_train_loader(self):
         cfg = self.config
         ddp = bool(cfg.get("DDP", False)) and torch.distributed.is_initialized()
-        self.distributed_sampler = DistributedSampler(self.train_dataset) if ddp else None
+        self.distributed_sampler = CameraDistributedSampler(self.train_dataset) if ddp else None
         collate = getattr(self.train_dataset, "collate_fn", None) or self.full_train_dataset.collate_fn
         self.train_loader = DataLoader(self.train_dataset, batch_size=1, collate_fn=collate, shuffle=not ddp,
                                        num_workers=0, sampler=self.distributed_sampler)

@@ -27,8 +27,29 @@ class SimpleSampler:
         return self.ids[self.curr:self.curr + self.batch]
 
 
-class DistributedSampler(torch.utils.data.distributed.DistributedSampler):
-    """Alias kept for API parity."""
+class DistributedSampler:
+    """Ray sampler of data-parallel training (reference: dataset_utils.py:41-62): every rank draws the same
+    permutation of an epoch (seeded with ``seed + epoch``) and takes its own ``batch`` out of each stride of
+    ``batch * world_size`` ids, so the ranks' batches of a step are disjoint."""
+
+    def __init__(self, total: int, batch: int, rank: int, world_size: int, seed: int = 0):
+        self.total, self.batch, self.rank, self.world_size, self.seed = total, batch, rank, world_size, seed
+        self.curr, self.epoch, self.ids = total, 0, None
+
+    def nextids(self) -> torch.Tensor:
+        stride = self.batch * self.world_size
+        self.curr += stride
+        if self.ids is None or self.curr + stride > self.total:
+            gen = torch.Generator()
+            gen.manual_seed(self.seed + self.epoch)
+            self.ids = torch.randperm(self.total, generator=gen)
+            self.curr, self.epoch = 0, self.epoch + 1
+        lo = self.curr + self.rank * self.batch
+        return self.ids[lo:lo + self.batch]
+
+
+class CameraDistributedSampler(torch.utils.data.distributed.DistributedSampler):
+    """Per-rank camera order of data-parallel Gaussian training (``torch``'s sampler under a local name)."""
 
 
 @dataclass
@@ -92,8 +113,21 @@ def prep_testdataset_gs(config):
 
 
 def get_preprocessed_loader(config):
+    """Loader over pre-computed ray shards.  Under data parallelism every replica (a model-parallel group when
+    ``model_parallel_and_DDP``, else a rank) reads its own share of the shards and ``batch_size`` is divided among the
+    replicas (reference: dataset_utils.py:147-176)."""
     from .processed_dataset import PreprocessedDataset
 
     ds = PreprocessedDataset(config.preprocessed_dir, config.processed_data_type)
-    return torch.utils.data.DataLoader(ds, batch_size=max(config.batch_size // ds.shard_rays, 1), shuffle=True,
-                                       num_workers=0, pin_memory=torch.cuda.is_available())
+    shards = max(config.batch_size // ds.shard_rays, 1)
+    pin = torch.cuda.is_available()
+    if config.get("DDP", False):
+        if config.get("model_parallel_and_DDP", False):
+            replicas, rank = int(config.get("num_mp_groups", 1) or 1), int(config.get("dp_rank", 0) or 0)
+        else:
+            replicas, rank = int(config.get("world_size", 1) or 1), int(config.get("rank", 0) or 0)
+        if replicas > 1:
+            sampler = CameraDistributedSampler(ds, num_replicas=replicas, rank=rank, shuffle=True, seed=0, drop_last=False)
+            return torch.utils.data.DataLoader(ds, batch_size=max(shards // replicas, 1), sampler=sampler, num_workers=0,
+                                               pin_memory=pin)
+    return torch.utils.data.DataLoader(ds, batch_size=shards, shuffle=True, num_workers=0, pin_memory=pin)

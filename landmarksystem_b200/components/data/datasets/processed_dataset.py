@@ -16,6 +16,9 @@ class PreprocessedDataset(Dataset):
         assert data_type == "file", "only file-backed shards are supported (no object store offline)"
         self.root = root
         self.num = int(np.load(os.path.join(root, "num.npz"))["num"])
+        if self.num > 0:                          # shards written with another size than the default
+            with np.load(os.path.join(root, f"{0:010d}.npz")) as first:
+                self.shard_rays = int(first["idxs"].shape[0])
 
     def __len__(self):
         return self.num

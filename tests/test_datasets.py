@@ -105,6 +105,23 @@ def test_shard_preprocessing_single_and_distributed(tmp_path):
     assert total == 3
     rows = torch.cat([PreprocessedDataset(str(tmp_path / "dist"))[k][2] for k in range(3)])
     assert rows.unique().numel() == 3 * 512                  # no ray is duplicated across shards
+    # the loader under data parallelism: the replicas' shards of an epoch are disjoint, batch divided among them
+    from landmarksystem_b200.components.data.datasets.dataset_utils import get_preprocessed_loader
+    from landmarksystem_b200.utils import Config
+
+    assert preprocess(ds, str(tmp_path / "many"), shard_rays=128) == 12
+    seen = []
+    for rank in range(2):
+        cfg = Config(preprocessed_dir=str(tmp_path / "many"), processed_data_type="file", batch_size=512, DDP=True,
+                     model_parallel_and_DDP=False, world_size=2, rank=rank)
+        loader = get_preprocessed_loader(cfg)
+        assert loader.batch_size == 2                          # 512 rays = 4 shards of 128, two per replica
+        seen.append(torch.cat([b[2].reshape(-1) for b in loader]))
+    assert seen[0].numel() == seen[1].numel() == 6 * 128
+    assert torch.cat(seen).unique().numel() == 12 * 128
+    single = get_preprocessed_loader(Config(preprocessed_dir=str(tmp_path / "many"), processed_data_type="file",
+                                            batch_size=512, DDP=False))
+    assert single.batch_size == 4
 
 
 def test_drone_metadata_loader(tmp_path):
@@ -176,3 +193,21 @@ def test_path_split_spherical_and_trajectory(tmp_path):
     ds2 = cls(split="path", downsample=1.0, is_stack=True, args=_path_args(tmp_path, render_spherical=False, render_skip=3))
     assert ds2.render_poses.shape[0] == 3                                  # frames 0, 3, 6
     assert torch.allclose(ds2.render_poses[1], torch.eye(4) + 0.03)
+
+
+def test_distributed_ray_sampler_is_disjoint_and_reseeds_per_epoch():
+    from landmarksystem_b200.components.data.datasets.dataset_utils import DistributedSampler
+
+    world, batch, total = 3, 4, 40
+    samplers = [DistributedSampler(total, batch, r, world, seed=5) for r in range(world)]
+    seen, first_epoch = [], None
+    for step in range(6):                                   # 3 steps fit into 40 ids; the 4th starts a new epoch
+        ids = [s.nextids() for s in samplers]
+        flat = torch.cat(ids)
+        assert all(i.numel() == batch for i in ids) and flat.unique().numel() == world * batch
+        seen.append(flat)
+        if step == 0:
+            first_epoch = samplers[0].ids.clone()
+    assert torch.cat(seen[:3]).unique().numel() == 3 * world * batch          # no id twice within an epoch
+    assert samplers[0].epoch == 2 and not torch.equal(samplers[0].ids, first_epoch)
+    assert all(torch.equal(s.ids, samplers[0].ids) for s in samplers)
