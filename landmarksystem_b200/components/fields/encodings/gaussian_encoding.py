@@ -149,6 +149,43 @@ class GaussianEncoding(BaseGaussianEncoding):
         L = build_scaling_rotation(scaling_modifier * self.get_scaling, self._rotation)
         return strip_symmetric(L @ L.transpose(1, 2))
 
+    # -- setters (reference: gaussian_encoding.py:855-925).  With ``act_cache`` outside training the value is the
+    # ACTIVATED quantity and lands in the cache the getters read; otherwise it replaces the raw tensor. ---------
+    def _set(self, cache_name: str, attr: str, value: torch.Tensor):
+        if self.act_cache and not self.training:
+            self._cache[cache_name] = value
+        elif isinstance(getattr(self, attr), nn.Parameter):
+            getattr(self, attr).data = value
+        else:
+            setattr(self, attr, value)
+
+    def set_scaling(self, value: torch.Tensor):
+        self._set("scaling", "_scaling", value)
+
+    def set_rotation(self, value: torch.Tensor):
+        self._set("rotation", "_rotation", value)
+
+    def set_opacity(self, value: torch.Tensor):
+        self._set("opacity", "_opacity", value)
+
+    def set_features(self, value: torch.Tensor):
+        if not (self.act_cache and not self.training):
+            raise NotImplementedError("features are set as a whole only through the activation cache")
+        self._cache["features"] = value
+
+    def set_xyz(self, value: torch.Tensor):
+        if isinstance(self._xyz, nn.Parameter):
+            self._xyz.data = value
+        else:
+            self._xyz = value
+
+    # -- optimiser surgery under the reference's method names (gaussian_encoding.py:429-496) ---------------------
+    def cat_tensors_to_optimizer(self, tensors_dict: Dict[str, torch.Tensor], optimizer) -> Dict[str, nn.Parameter]:
+        return cat_tensors_to_optimizer(optimizer, tensors_dict)
+
+    def replace_tensor_to_optimizer(self, tensor: torch.Tensor, name: str, optimizer) -> Dict[str, nn.Parameter]:
+        return replace_tensor_to_optimizer(optimizer, tensor, name)
+
     def oneupSHdegree(self):
         if self.active_sh_degree < self.max_sh_degree:
             self.active_sh_degree += 1

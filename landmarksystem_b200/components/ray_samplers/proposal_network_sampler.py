@@ -184,6 +184,13 @@ class ProposalNetworks(nn.Module):
         self.density_fns = [self.networks[0 if use_same_proposal_network else i].density_fn
                             for i in range(num_proposal_iterations)]
 
+    def density_fn(self, positions: torch.Tensor, level: int = 0) -> torch.Tensor:
+        """Density of proposal level ``level`` at ``positions``."""
+        return self.density_fns[level](positions)
+
+    def get_density(self, positions: torch.Tensor, level: int = 0) -> torch.Tensor:
+        return self.density_fn(positions, level)
+
 
 class ProposalNetworkSampler(BaseSampler):
     def __init__(self, num_proposal_samples_per_ray: Tuple[int, ...] = (256, 96), num_nerf_samples_per_ray: int = 48,

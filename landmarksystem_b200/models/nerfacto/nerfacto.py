@@ -200,6 +200,21 @@ class Nerfacto(BaseNeRF):
         raw, geo = torch.split(h, [1, self.geo_feat_dim], dim=-1)
         return self._mp_sum(trunc_exp(raw) * inside[:, None]), self._mp_sum(geo * inside[:, None])
 
+    def density_fn(self, positions: torch.Tensor) -> torch.Tensor:
+        """Density only, at world positions ``[..., 3]`` (reference: nerfacto.py:228-236)."""
+        return self.get_density(positions.reshape(-1, 3))[0].reshape(*positions.shape[:-1], 1)
+
+    def set_anneal(self, step: int) -> float:
+        """Proposal-weight annealing of mip-NeRF 360 (eq. 18) at ``step``, handed to the sampler (reference:
+        nerfacto.py:339-353)."""
+        c = self.config
+        self.step = step
+        frac = float(np.clip(step / max(c.proposal_weights_anneal_max_num_iters, 1), 0, 1))
+        b = c.proposal_weights_anneal_slope
+        anneal = b * frac / ((b - 1) * frac + 1)
+        self.sampler.set_anneal(anneal)
+        return anneal
+
     def forward(self, rays_chunk):
         c = self.config
         rays = rays_chunk.data if isinstance(rays_chunk, Rays) else rays_chunk

@@ -114,6 +114,24 @@ class NeRFTrainer:
     def evaluation(self, *args, **kwargs):
         raise NotImplementedError
 
+    @torch.no_grad()
+    def eval(self) -> float:
+        """Evaluate the current model on the test split and return the mean PSNR (reference:
+        landmark/train/nerf_trainer.py:208-300).  Ray trainers write ``<logfolder>/imgs_vis/test_all_*``, camera
+        trainers ``<logfolder>/imgs_test_all/*``."""
+        import inspect
+
+        self.model.eval()
+        params = inspect.signature(self.evaluation).parameters
+        if "save_path" in params:
+            value = self.evaluation(os.path.join(self.logfolder, "imgs_test_all"))
+        else:
+            value = self.evaluation(prefix="test_all_", n_vis=int(self.config.get("N_vis", -1)))
+        if dist.is_initialized() and dist.get_rank() != 0:
+            return value
+        print(f"======> {self.config.expname} test all psnr: {value} <========================", flush=True)
+        return value
+
     def barrier(self):
         if dist.is_initialized():
             dist.barrier()

@@ -103,6 +103,19 @@ class RayModelTrainer(NeRFTrainer):
         t = min(step / max(cfg.lr_decay_max_steps, 1), 1.0)
         return float(np.exp(np.log(cfg.lr_init) * (1 - t) + np.log(cfg.lr_final) * t))
 
+    def update_learning_rate(self) -> float:
+        """Apply the schedule at the current iteration to every scheduled group (reference:
+        instant_ngp_trainer.py:169-178)."""
+        lr = self.lr_at(self.iteration)
+        for group in self.optimizer.param_groups:
+            if group.get("scheduled", True):
+                group["lr"] = lr
+        return lr
+
+    def save_optimizer(self, path: str) -> None:
+        """``{"optimizer": state_dict}`` at ``path`` (reference: instant_ngp_trainer.py:159-167)."""
+        torch.save({"optimizer": self.optimizer.state_dict()}, path)
+
     def before_forward(self, it: int):
         pass
 
@@ -121,10 +134,7 @@ class RayModelTrainer(NeRFTrainer):
             self.dp_sync.sync([p for g in self.optimizer.param_groups for p in g["params"]])
         self.optimizer.step()
         self.optimizer.zero_grad(set_to_none=True)
-        lr = self.lr_at(self.iteration)
-        for group in self.optimizer.param_groups:
-            if group.get("scheduled", True):
-                group["lr"] = lr
+        self.update_learning_rate()
         return torch.mean((ret["rgb_map"].detach() - rgb_train) ** 2)
 
     def train(self):
@@ -156,7 +166,7 @@ class RayModelTrainer(NeRFTrainer):
         if cfg.model_parallel:
             if cfg.dp_rank == 0:
                 self.module.save_model(self.logfolder, rank=cfg.mp_rank)
-            torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+            self.save_optimizer(self._optim_path())
             self.barrier()
             if final and cfg.rank == 0 and cfg.branch_parallel:
                 n = cfg.model_parallel_degree
@@ -169,7 +179,7 @@ class RayModelTrainer(NeRFTrainer):
             if is_main_rank():
                 self.module.save_model(self.logfolder)
             if is_main_rank() or bool(getattr(self.optimizer, "partitioned", False)):
-                torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+                self.save_optimizer(self._optim_path())
 
     @torch.no_grad()
     def evaluation(self, prefix: str = "", n_vis: int = 5, save: bool = True):

@@ -26,6 +26,7 @@ def test_train_then_evaluate_cpu(family, tmod, tcls, emod, ecls, conf, extra, tm
     path = os.path.join(ROOT, family, "confs", conf)
     trainer = getattr(importlib.import_module(f"landmarksystem_b200.models.{family}.{tmod}"), tcls)(BaseConfig.from_file(path, over))
     trainer.train()
+    assert np.isfinite(trainer.eval())
     cfg = BaseConfig.from_file(path, over)
     cfg.is_train = False
     cfg.ckpt = (os.path.join(trainer.logfolder, "point_cloud", "iteration_3", "point_cloud.ply") if gaussian

@@ -43,6 +43,36 @@ def test_gaussian_encoding_ply_roundtrip_and_properties(tmp_path):
     assert torch.allclose(third.get_scaling, enc.get_scaling, rtol=1e-4)
 
 
+def test_gaussian_encoding_setters_follow_the_activation_cache():
+    """Setters of the reference (gaussian_encoding.py:855-925): raw tensors in training, activated values through
+    the cache when ``act_cache`` is on and the module evaluates."""
+    enc = GaussianEncoding(1, act_cache=True, device="cpu")
+    enc.create_from_pcd(_pcd(20))
+    enc.train()
+    raw = torch.full_like(enc._scaling, -2.0)
+    enc.set_scaling(raw)
+    assert torch.allclose(enc.get_scaling, torch.exp(raw))
+    with pytest.raises(NotImplementedError):
+        enc.set_features(enc.get_features)
+    enc.eval()
+    act = torch.full_like(enc._opacity, 0.25)
+    enc.set_opacity(act)
+    assert torch.equal(enc.get_opacity, act)                        # taken as the activated value
+    feats = torch.zeros_like(enc.get_features)
+    enc.set_features(feats)
+    assert enc.get_features is feats
+    moved = enc.get_xyz.detach() + 1
+    enc.set_xyz(moved)
+    assert torch.equal(enc.get_xyz, moved) and isinstance(enc._xyz, torch.nn.Parameter)
+    opt = torch.optim.Adam([{"params": [enc._xyz], "name": "xyz"}], lr=1e-3)
+    enc._xyz.grad = torch.ones_like(enc._xyz)
+    opt.step()
+    new = enc.cat_tensors_to_optimizer({"xyz": torch.zeros(3, 3)}, opt)
+    assert new["xyz"].shape[0] == 23 and opt.state[new["xyz"]]["exp_avg"][-3:].abs().sum() == 0
+    swapped = enc.replace_tensor_to_optimizer(torch.ones(23, 3), "xyz", opt)
+    assert opt.param_groups[0]["params"][0] is swapped["xyz"] and opt.state[swapped["xyz"]]["exp_avg"].abs().sum() == 0
+
+
 def test_densify_and_prune_keeps_optimizer_in_sync():
     torch.manual_seed(0)
     enc = GaussianEncoding(1, device="cpu")

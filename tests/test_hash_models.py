@@ -101,6 +101,21 @@ def test_cpu_smoke(family, module, cls, tmp_path):
     assert os.path.exists(os.path.join(trainer.logfolder, "state_dict.th"))
     state = torch.load(os.path.join(trainer.logfolder, "state_dict.th"), weights_only=False)
     assert "mlp_base_grid.tcnn_encoding.params" in state      # reference checkpoint key of the hash table
+    # helper methods of the reference's trainers / models
+    trainer.iteration = 10
+    lr = trainer.update_learning_rate()
+    assert lr == trainer.lr_at(10) and all(g["lr"] == lr for g in trainer.optimizer.param_groups if g.get("scheduled", True))
+    trainer.save_optimizer(str(tmp_path / "opt.th"))
+    assert "optimizer" in torch.load(str(tmp_path / "opt.th"), weights_only=False)
+    if family == "nerfacto":
+        m = trainer.module
+        pts = torch.rand(5, 7, 3) * 2 - 1
+        with torch.no_grad():
+            assert m.density_fn(pts).shape == (5, 7, 1)
+            assert m.proposal_networks.get_density(pts.reshape(-1, 3), 1).shape[0] == 35
+        half = m.set_anneal(cfg.proposal_weights_anneal_max_num_iters // 2)
+        b = cfg.proposal_weights_anneal_slope
+        assert abs(half - b * 0.5 / ((b - 1) * 0.5 + 1)) < 1e-9 and m.sampler._anneal == half and m.set_anneal(10 ** 9) == 1.0
 
 
 @pytest.mark.gpu
