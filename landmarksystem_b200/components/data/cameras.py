@@ -44,6 +44,34 @@ class Camera:
             self.full_proj_transform = w2v @ proj
             self.camera_center = w2v.inverse()[3, :3]
 
+    # -- the reference's field names (landmark/nerf_components/data/cameras.py:33-66) as read-only views --------
+    @property
+    def width(self) -> int:
+        return self.image_width
+
+    @property
+    def height(self) -> int:
+        return self.image_height
+
+    @property
+    def FovX(self) -> float:
+        return self.FoVx
+
+    @property
+    def FovY(self) -> float:
+        return self.FoVy
+
+    @property
+    def device(self):
+        return self.world_view_transform.device if self.world_view_transform is not None else torch.device("cpu")
+
+    @property
+    def c2w(self) -> Optional[torch.Tensor]:
+        """Camera-to-world matrix ``[4, 4]`` in COLMAP axes (x right, y down, z forward)."""
+        if self.world_view_transform is None:
+            return None
+        return torch.linalg.inv(self.world_view_transform.transpose(0, 1))
+
     @property
     def tanfovx(self) -> float:
         return math.tan(self.FoVx * 0.5)

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import os
 
+import torch
 import torch.distributed as dist
 
 
@@ -92,3 +93,79 @@ def init_distributed_mode(env: str = "single_node", backend: str = None, timeout
                                 timeout=datetime.timedelta(seconds=timeout_s))
         dist.barrier()
     return {"rank": rank, "world_size": world, "local_rank": local}
+
+
+# -- process-wide group registry under the reference's function names (landmark/train/utils/distributed_utils.py:
+# 14-70, 171-227).  The trainers keep their groups on the run configuration (``comm/train_groups.py``); these helpers
+# serve scripts written against the module-level interface. ------------------------------------------------------
+_GROUPS = {"dp": None, "mp": None, "mp_ranks": [0], "mp_part": 0}
+
+
+def is_dist_avail_and_initialized() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+def is_main_process() -> bool:
+    return get_rank() == 0
+
+
+def get_local_size() -> int:
+    """Ranks on this node (``LOCAL_SIZE`` / ``LOCAL_WORLD_SIZE`` of the launcher); 1 outside a distributed run."""
+    if not is_dist_avail_and_initialized():
+        return 1
+    return int(os.environ.get("LOCAL_SIZE", os.environ.get("LOCAL_WORLD_SIZE", 1)))
+
+
+def save_on_master(*args, **kwargs) -> None:
+    if is_main_rank():
+        torch.save(*args, **kwargs)
+
+
+def setup_for_distributed(is_master: bool):
+    """Silence ``print`` on every rank but the master's (``print(..., force=True)`` still prints everywhere).
+    Returns the original ``print`` so that a caller can restore it."""
+    import builtins
+
+    original = builtins.print
+
+    def rank_print(*args, **kwargs):
+        if kwargs.pop("force", False) or is_master:
+            original(*args, **kwargs)
+
+    builtins.print = rank_print
+    return original
+
+
+def init_comm_groups(model_parallel_degree: int = 8) -> None:
+    """Contiguous model-parallel groups of ``model_parallel_degree`` ranks and the data-parallel groups strided
+    across them; every rank creates every group (collective) and keeps its own two."""
+    from ..comm.train_groups import group_layout
+
+    assert dist.is_initialized(), "initialise torch.distributed first"
+    rank = dist.get_rank()
+    mp_groups, dp_groups = group_layout(dist.get_world_size(), model_parallel_degree)
+    for ranks in mp_groups:
+        group = dist.new_group(ranks)
+        if rank in ranks:
+            _GROUPS["mp"], _GROUPS["mp_ranks"] = group, list(ranks)
+    for ranks in dp_groups:
+        group = dist.new_group(ranks)
+        if rank in ranks:
+            _GROUPS["dp"] = group
+    _GROUPS["mp_part"] = rank % model_parallel_degree
+
+
+def get_dp_group():
+    return _GROUPS["dp"]
+
+
+def get_mp_group():
+    return _GROUPS["mp"]
+
+
+def get_mp_rank0() -> int:
+    return _GROUPS["mp_ranks"][0]
+
+
+def get_mp_part() -> int:
+    return _GROUPS["mp_part"]

@@ -211,3 +211,17 @@ def test_distributed_ray_sampler_is_disjoint_and_reseeds_per_epoch():
     assert torch.cat(seen[:3]).unique().numel() == 3 * world * batch          # no id twice within an epoch
     assert samplers[0].epoch == 2 and not torch.equal(samplers[0].ids, first_epoch)
     assert all(torch.equal(s.ids, samplers[0].ids) for s in samplers)
+
+
+def test_camera_reference_field_names():
+    """``width / height / FovX / FovY / c2w / device`` as the reference's camera record names them."""
+    from landmarksystem_b200.components.data.cameras import Camera
+    from landmarksystem_b200.synthetic import ring_cameras
+
+    pose = ring_cameras(4, 3.0)[1].numpy()
+    cam = Camera.from_c2w(pose, 32, 24, 30.0)
+    want = pose.copy()
+    want[:3, 1:3] *= -1                                       # OpenGL -> COLMAP axes
+    assert np.allclose(cam.c2w.numpy(), want, atol=1e-6)
+    assert (cam.width, cam.height) == (32, 24) and cam.FovX == cam.FoVx and cam.FovY == cam.FoVy
+    assert cam.device == torch.device("cpu") and cam.to("cpu").width == 32

@@ -367,3 +367,39 @@ def _user_inputs(rank, world):
 
 def test_engine_user_inputs_broadcast():
     _run(_user_inputs, 2)
+
+
+def _module_level_groups(rank, world):
+    from landmarksystem_b200.train import utils as tu
+
+    assert tu.is_dist_avail_and_initialized() and tu.is_main_process() == (rank == 0)
+    tu.init_comm_groups(model_parallel_degree=2)
+    mp = torch.tensor([float(rank)])
+    dist.all_reduce(mp, group=tu.get_mp_group())            # ranks {0,1} and {2,3}
+    dp = torch.tensor([float(rank)])
+    dist.all_reduce(dp, group=tu.get_dp_group())            # ranks {0,2} and {1,3}
+    return float(mp), float(dp), tu.get_mp_rank0(), tu.get_mp_part()
+
+
+def test_module_level_group_helpers():
+    """``init_comm_groups / get_dp_group / get_mp_group / get_mp_rank0 / get_mp_part`` of the reference's
+    ``distributed_utils`` (world 4, model-parallel degree 2)."""
+    out = _run(_module_level_groups, 4)
+    assert out[0] == (1.0, 2.0, 0, 0) and out[1] == (1.0, 4.0, 0, 1)
+    assert out[2] == (5.0, 2.0, 2, 0) and out[3] == (5.0, 4.0, 2, 1)
+
+
+def test_print_silencer_and_save_on_master(tmp_path, capsys):
+    import builtins
+
+    from landmarksystem_b200.train import utils as tu
+
+    original = tu.setup_for_distributed(False)
+    try:
+        print("hidden")
+        print("shown", force=True)
+    finally:
+        builtins.print = original
+    assert capsys.readouterr().out == "shown\n"
+    tu.save_on_master({"a": 1}, str(tmp_path / "x.th"))     # single process: rank 0
+    assert torch.load(str(tmp_path / "x.th"), weights_only=False) == {"a": 1} and tu.get_local_size() == 1
