@@ -15,7 +15,7 @@ import torch
 from torch.utils.data import Dataset
 
 from ..cameras import Camera
-from .ray_utils import get_ray_directions_blender, get_rays, pose_spherical
+from .ray_utils import get_ray_directions_blender, get_rays, load_json_render_path, pose_spherical
 
 
 def _arg(args, name, default):
@@ -108,12 +108,9 @@ class VolumeRenderDataset(BaseDataset):
                 k = torch.arange(n, dtype=torch.float32)
                 poses[:, 2, 3] -= torch.where(k < half, zstep * k, zdiff - zstep * (k - half))
             return poses
-        import json
-
-        name = os.path.join(self.datadir, "trajectories", f"path{int(_arg(a, 'render_pathid', 0))}.json")
-        with open(name, "r", encoding="utf-8") as fh:
-            frames = json.load(fh)["frames"][::skip]
-        return torch.tensor([f["transform_matrix"] for f in frames], dtype=torch.float32)
+        poses = load_json_render_path(os.path.join(self.datadir, "trajectories"),
+                                      f"path{int(_arg(a, 'render_pathid', 0))}.json", skip)
+        return torch.as_tensor(poses, dtype=torch.float32)
 
     def read_meta_path(self, n_frames: Optional[int] = None, radius: Optional[float] = None,
                        downward: Optional[float] = None):

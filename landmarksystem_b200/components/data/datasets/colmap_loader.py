@@ -227,3 +227,39 @@ def write_model_text(sparse_dir: str, cameras, images, points) -> None:
         for k in range(len(xyz)):
             fh.write(f"{k + 1} " + " ".join(repr(float(v)) for v in xyz[k]) + " " + " ".join(str(int(v)) for v in rgb[k])
                      + f" {float(err[k])!r}\n")
+
+
+# -- dense-reconstruction arrays and the names the 3DGS code base uses for the readers -----------------------------
+def read_colmap_bin_array(path: str) -> np.ndarray:
+    """A COLMAP dense array (depth / normal map): text header ``width&height&channels&`` followed by float32 values in
+    column-major order; returns ``[height, width]`` or ``[height, width, channels]``."""
+    with open(path, "rb") as fh:
+        header = b""
+        while header.count(b"&") < 3:
+            byte = fh.read(1)
+            assert byte, f"{path}: truncated header"
+            header += byte
+        width, height, channels = (int(v) for v in header.split(b"&")[:3])
+        data = np.frombuffer(fh.read(), dtype=np.float32, count=width * height * channels)
+    return np.transpose(data.reshape((width, height, channels), order="F"), (1, 0, 2)).squeeze()
+
+
+def write_colmap_bin_array(path: str, array: np.ndarray) -> None:
+    """Inverse of :func:`read_colmap_bin_array`."""
+    a = np.asarray(array, dtype=np.float32)
+    a = a[..., None] if a.ndim == 2 else a
+    height, width, channels = a.shape
+    with open(path, "wb") as fh:
+        fh.write(f"{width}&{height}&{channels}&".encode("ascii"))
+        fh.write(np.transpose(a, (1, 0, 2)).reshape(-1, order="F").tobytes())
+
+
+def read_next_bytes(fid: BinaryIO, num_bytes: int, format_char_sequence: str, endian_character: str = "<"):
+    """Read and unpack the next ``num_bytes`` of a binary model file."""
+    return struct.unpack(endian_character + format_char_sequence, fid.read(num_bytes))
+
+
+Camera = ColmapCamera                                   # record names of the reference's loader
+Image = ColmapImage
+read_extrinsics_binary, read_extrinsics_text = read_images_binary, read_images_text
+read_intrinsics_binary, read_intrinsics_text = read_cameras_binary, read_cameras_text

@@ -38,22 +38,115 @@ def get_rays(directions, c2w, camera_mode: str = "normal"):
     return get_rays_with_directions(dirs, c2w)
 
 
+def trans_t(t: float) -> torch.Tensor:
+    """Translation by ``t`` along z, homogeneous ``[4, 4]``."""
+    m = torch.eye(4)
+    m[2, 3] = float(t)
+    return m
+
+
+def rot_phi(phi: float) -> torch.Tensor:
+    """Rotation by ``phi`` radians about x, homogeneous ``[4, 4]``."""
+    c, s = math.cos(phi), math.sin(phi)
+    return torch.tensor([[1, 0, 0, 0], [0, c, -s, 0], [0, s, c, 0], [0, 0, 0, 1]], dtype=torch.float32)
+
+
+def rot_theta(theta: float) -> torch.Tensor:
+    """Rotation by ``theta`` radians about y (NeRF-synthetic sign), homogeneous ``[4, 4]``."""
+    c, s = math.cos(theta), math.sin(theta)
+    return torch.tensor([[c, 0, -s, 0], [0, 1, 0, 0], [s, 0, c, 0], [0, 0, 0, 1]], dtype=torch.float32)
+
+
 def pose_spherical(theta_deg: float, phi_deg: float, radius: float) -> torch.Tensor:
     """Camera on a sphere looking at the origin (NeRF-synthetic convention)."""
-    def trans_t(t):
-        return torch.tensor([[1, 0, 0, 0], [0, 1, 0, 0], [0, 0, 1, t], [0, 0, 0, 1]], dtype=torch.float32)
-
-    def rot_phi(p):
-        c, s = math.cos(p), math.sin(p)
-        return torch.tensor([[1, 0, 0, 0], [0, c, -s, 0], [0, s, c, 0], [0, 0, 0, 1]], dtype=torch.float32)
-
-    def rot_theta(t):
-        c, s = math.cos(t), math.sin(t)
-        return torch.tensor([[c, 0, -s, 0], [0, 1, 0, 0], [s, 0, c, 0], [0, 0, 0, 1]], dtype=torch.float32)
-
     c2w = rot_theta(math.radians(theta_deg)) @ rot_phi(math.radians(phi_deg)) @ trans_t(radius)
     flip = torch.tensor([[-1, 0, 0, 0], [0, 0, 1, 0], [0, 1, 0, 0], [0, 0, 0, 1]], dtype=torch.float32)
     return flip @ c2w
+
+
+def get_ray_directions(H: int, W: int, focal, center=None) -> torch.Tensor:
+    """Per-pixel directions ``[H, W, 3]`` of a camera that looks along +z with y down (OpenCV axes), pixel ``(i, j)``
+    at integer coordinates, not normalised (reference: ray_utils.py:473-491)."""
+    fx, fy = (focal, focal) if not isinstance(focal, (list, tuple)) else focal
+    cx, cy = (W / 2, H / 2) if center is None else center
+    j, i = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+    return torch.stack(((i - cx) / fx, (j - cy) / fy, torch.ones_like(i)), -1)
+
+
+def depth2dist(z_vals: torch.Tensor, cos_angle: torch.Tensor) -> torch.Tensor:
+    """Sample spacings along the ray from depths along the optical axis: differences of ``z_vals [..., S]`` (the last
+    one open-ended, 1e10) scaled by ``cos_angle [...]``, the per-ray ratio of ray length to depth."""
+    gaps = torch.diff(z_vals, dim=-1)
+    last = torch.full_like(z_vals[..., :1], 1e10)
+    return torch.cat((gaps, last), dim=-1) * cos_angle[..., None]
+
+
+def patchify(img: torch.Tensor, rays_o: torch.Tensor, rays_d: torch.Tensor, H: int, W: int, ps: int):
+    """Cut an image and its rays into non-overlapping ``ps x ps`` patches (incomplete border patches are dropped):
+    returns ``(rgb [n, ps*ps, 3], rays [n, ps*ps, 6])`` with patches in row-major order."""
+    def cut(t):
+        t = t.reshape(H, W, 3)[:H // ps * ps, :W // ps * ps]
+        return t.reshape(H // ps, ps, W // ps, ps, 3).permute(0, 2, 1, 3, 4).reshape(-1, ps * ps, 3)
+
+    return cut(img), torch.cat((cut(rays_o), cut(rays_d)), dim=-1)
+
+
+def listify_matrix(matrix) -> List[list]:
+    """Rows of a matrix as plain lists (for JSON)."""
+    return [list(row) for row in matrix]
+
+
+def read_Image(f_path: str, transform=None) -> torch.Tensor:
+    """RGB image as ``[H*W, 3]`` floats in [0, 1]; ``transform`` (a PIL -> ``[3, H, W]`` tensor callable) is optional."""
+    from PIL import Image
+
+    with Image.open(f_path) as im:
+        im = im.convert("RGB")
+        chw = transform(im) if transform is not None else torch.from_numpy(
+            np.asarray(im, dtype=np.float32) / 255.0).permute(2, 0, 1)
+    return chw.reshape(3, -1).permute(1, 0).contiguous()
+
+
+def load_json_render_path(pathfolder: str, posefile: str, render_skip: int = 1) -> np.ndarray:
+    """Camera-to-world matrices of every ``render_skip``-th frame of a trajectory file."""
+    assert posefile.endswith("json"), "trajectory files are JSON"
+    with open(os.path.join(pathfolder, posefile), "r", encoding="utf-8") as fh:
+        frames = json.load(fh)["frames"][::max(int(render_skip), 1)]
+    return np.array([f["transform_matrix"] for f in frames])
+
+
+def pad_poses(p: np.ndarray) -> np.ndarray:
+    """``[..., 3, 4]`` -> ``[..., 4, 4]`` with the homogeneous bottom row."""
+    bottom = np.broadcast_to(np.array([0.0, 0.0, 0.0, 1.0]), p[..., :1, :4].shape)
+    return np.concatenate((p[..., :3, :4], bottom), axis=-2)
+
+
+def unpad_poses(p: np.ndarray) -> np.ndarray:
+    return p[..., :3, :4]
+
+
+def transform_poses_pca(poses: np.ndarray):
+    """Re-express camera-to-world poses ``[N, 3|4, 4]`` in the principal axes of the camera positions (largest spread
+    along x, smallest along z), centred on their mean, flipped so that the cameras' y axes point up on average, and
+    scaled so that the positions fit in [-1, 1]^3.  Returns ``(poses [N, 3, 4], transform [4, 4])`` where
+    ``transform`` maps old world coordinates to new ones."""
+    centres = poses[:, :3, 3]
+    mean = centres.mean(axis=0)
+    spread = centres - mean
+    eigval, eigvec = np.linalg.eigh(spread.T @ spread)           # ascending eigenvalues of a symmetric matrix
+    rot = eigvec[:, ::-1].T
+    if np.linalg.det(rot) < 0:
+        rot = np.diag([1.0, 1.0, -1.0]) @ rot
+    transform = np.eye(4)
+    transform[:3, :3], transform[:3, 3] = rot, rot @ -mean
+    out = unpad_poses(transform @ pad_poses(poses))
+    if out.mean(axis=0)[2, 1] < 0:                                # cameras upside down on average
+        flip = np.diag([1.0, -1.0, -1.0, 1.0])
+        out, transform = flip[:3, :3] @ out, flip @ transform
+    scale = 1.0 / np.max(np.abs(out[:, :3, 3]))
+    out[:, :3, 3] *= scale
+    transform = np.diag([scale, scale, scale, 1.0]) @ transform
+    return out, transform
 
 
 def load_transforms(datadir: str, split: str) -> Dict:

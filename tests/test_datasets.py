@@ -225,3 +225,36 @@ def test_camera_reference_field_names():
     assert np.allclose(cam.c2w.numpy(), want, atol=1e-6)
     assert (cam.width, cam.height) == (32, 24) and cam.FovX == cam.FoVx and cam.FovY == cam.FoVy
     assert cam.device == torch.device("cpu") and cam.to("cpu").width == 32
+
+
+def test_ray_and_pose_helpers(tmp_path):
+    """Helper functions under the reference's names (dataloader/utils/ray_utils.py, colmap_loader.py)."""
+    from landmarksystem_b200.components.data.datasets import ray_utils as ru
+
+    d = ru.get_ray_directions(4, 6, (10.0, 20.0))
+    assert d.shape == (4, 6, 3) and torch.allclose(d[1, 2], torch.tensor([(2 - 3) / 10.0, (1 - 2) / 20.0, 1.0]))
+    z = torch.tensor([[1.0, 2.0, 4.0]])
+    assert torch.allclose(ru.depth2dist(z, torch.tensor([2.0])), torch.tensor([[2.0, 4.0, 2e10]]))
+    H, W, ps = 4, 6, 2
+    img = torch.arange(H * W * 3, dtype=torch.float32).view(H * W, 3)
+    rgb, rays = ru.patchify(img, img + 1000, img + 2000, H, W, ps)
+    assert rgb.shape == (6, 4, 3) and rays.shape == (6, 4, 6)
+    full = img.view(H, W, 3)
+    assert torch.equal(rgb[4].view(ps, ps, 3), full[2:4, 2:4])            # patch (row 1, column 1)
+    assert torch.equal(rays[4, :, :3], rgb[4] + 1000) and torch.equal(rays[4, :, 3:], rgb[4] + 2000)
+    assert ru.listify_matrix(np.eye(2)) == [[1.0, 0.0], [0.0, 1.0]]
+
+    rng = np.random.default_rng(0)
+    poses = np.tile(np.eye(4)[:3], (30, 1, 1))
+    poses[:, :3, 3] = rng.normal(size=(30, 3)) * np.array([0.5, 5.0, 2.0]) + np.array([10.0, -3.0, 2.0])
+    out, T = ru.transform_poses_pca(poses)
+    c = out[:, :3, 3]
+    assert np.isclose(np.abs(c).max(), 1.0) and np.allclose(c.mean(0), 0, atol=1e-9)
+    assert c.std(0)[0] > c.std(0)[1] > c.std(0)[2]                          # principal axes, largest spread first
+    assert np.allclose(ru.unpad_poses(T @ ru.pad_poses(poses))[:, :3, 3], c)
+    assert out.mean(axis=0)[2, 1] >= 0 and ru.pad_poses(out).shape == (30, 4, 4)
+
+    depth = rng.random((5, 7)).astype(np.float32)
+    cl.write_colmap_bin_array(str(tmp_path / "depth.bin"), depth)
+    assert np.array_equal(cl.read_colmap_bin_array(str(tmp_path / "depth.bin")), depth)
+    assert cl.read_extrinsics_binary is cl.read_images_binary and cl.read_intrinsics_text is cl.read_cameras_text
