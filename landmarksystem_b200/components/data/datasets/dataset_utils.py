@@ -112,6 +112,28 @@ def prep_testdataset_gs(config):
                                                          args=config, preload=config.preload)
 
 
+def prep_dataset_gs(config):
+    """``(train, test)`` camera datasets."""
+    return prep_traindataset_gs(config), prep_testdataset_gs(config)
+
+
+def PILtoTorch(pil_img) -> torch.Tensor:
+    """A PIL image as a ``[C, H, W]`` tensor in [0, 1] (grey images get one channel)."""
+    import numpy as np
+
+    t = torch.from_numpy(np.array(pil_img)) / 255.0
+    return t.permute(2, 0, 1) if t.dim() == 3 else t[None]
+
+
+def getNeRFppNorm(cams) -> dict:
+    """Centre and extent of a camera rig: ``translate`` = minus the mean camera centre, ``radius`` = 1.1 x the largest
+    distance of a camera from that mean (the scene-extent convention of 3D Gaussian splatting)."""
+    centres = torch.stack([torch.as_tensor(c.camera_center, dtype=torch.float32).cpu() for c in cams])
+    mean = centres.mean(dim=0)
+    radius = float((centres - mean).norm(dim=-1).max()) * 1.1
+    return {"translate": (-mean).numpy(), "radius": radius}
+
+
 def get_preprocessed_loader(config):
     """Loader over pre-computed ray shards.  Under data parallelism every replica (a model-parallel group when
     ``model_parallel_and_DDP``, else a rank) reads its own share of the shards and ``batch_size`` is divided among the

@@ -156,3 +156,97 @@ def auto_orient_and_center_poses(poses: np.ndarray, method: str = "up", center_m
 
 def poses_to_tensor(poses: np.ndarray, device="cpu") -> torch.Tensor:
     return torch.as_tensor(np.asarray(poses), dtype=torch.float32, device=device)
+
+
+# -- small vector / ordering / lens helpers (reference: landmark/nerf_components/data/cameras.py:111-127, 287-321,
+# 364-376, 398-553) ------------------------------------------------------------------------------------------------
+def unit_vector(data, axis: Optional[int] = None) -> np.ndarray:
+    """``data`` scaled to unit Euclidean length along ``axis`` (the whole array when it is one-dimensional)."""
+    v = np.array(data, dtype=np.float64)
+    if v.ndim == 1 or axis is None:
+        return v / np.sqrt(np.sum(v * v))
+    return v / np.sqrt(np.sum(v * v, axis=axis, keepdims=True))
+
+
+def normalize_with_norm(x: torch.Tensor, dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(x / |x|, |x|)`` along ``dim`` with the norm clamped away from zero."""
+    norm = torch.linalg.vector_norm(x, dim=dim, keepdim=True).clamp_min(float(np.finfo(float).eps) * 4.0)
+    return x / norm, norm
+
+
+def get_ordered_poses_and_k(poses: torch.Tensor, Ks: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Greedy tour through the cameras: start at the first pose and always move to the nearest camera centre not yet
+    visited.  ``poses [N, 3|4, 4]``, ``Ks [N, 3, 3]``; returns both in tour order."""
+    n = poses.shape[0]
+    centres = poses[:, :3, 3]
+    left = torch.ones(n, dtype=torch.bool)
+    order = [0]
+    left[0] = False
+    for _ in range(n - 1):
+        d = torch.linalg.vector_norm(centres - centres[order[-1]], dim=1)
+        d = torch.where(left, d, torch.full_like(d, float("inf")))
+        nxt = int(torch.argmin(d))
+        order.append(nxt)
+        left[nxt] = False
+    idx = torch.tensor(order, dtype=torch.long)
+    return poses[idx], Ks[idx]
+
+
+def get_distortion_params(k1: float = 0.0, k2: float = 0.0, k3: float = 0.0, k4: float = 0.0, p1: float = 0.0,
+                          p2: float = 0.0) -> torch.Tensor:
+    """OpenCV-style lens parameters as one vector ``[k1, k2, k3, k4, p1, p2]``."""
+    return torch.tensor([k1, k2, k3, k4, p1, p2], dtype=torch.float32)
+
+
+def radial_and_tangential_distort(coords: torch.Tensor, distortion_params: torch.Tensor) -> torch.Tensor:
+    """Forward lens model on normalised image coordinates ``[..., 2]``: radial polynomial ``1 + k1 r^2 + k2 r^4 +
+    k3 r^6 + k4 r^8`` and the two tangential terms."""
+    k1, k2, k3, k4, p1, p2 = (distortion_params[..., i] for i in range(6))
+    x, y = coords[..., 0], coords[..., 1]
+    r2 = x * x + y * y
+    radial = 1.0 + r2 * (k1 + r2 * (k2 + r2 * (k3 + r2 * k4)))
+    xd = x * radial + 2.0 * p1 * x * y + p2 * (r2 + 2.0 * x * x)
+    yd = y * radial + 2.0 * p2 * x * y + p1 * (r2 + 2.0 * y * y)
+    return torch.stack((xd, yd), dim=-1)
+
+
+def radial_and_tangential_undistort(coords: torch.Tensor, distortion_params: torch.Tensor, eps: float = 1e-3,
+                                    max_iterations: int = 10) -> torch.Tensor:
+    """Invert :func:`radial_and_tangential_distort` by Newton's method started at the distorted point; a point whose
+    Jacobian determinant falls under ``eps`` stops moving."""
+    k1, k2, k3, k4, p1, p2 = (distortion_params[..., i] for i in range(6))
+    xd, yd = coords[..., 0], coords[..., 1]
+    x, y = xd.clone(), yd.clone()
+    for _ in range(max_iterations):
+        r2 = x * x + y * y
+        radial = 1.0 + r2 * (k1 + r2 * (k2 + r2 * (k3 + r2 * k4)))
+        d_radial = k1 + r2 * (2.0 * k2 + r2 * (3.0 * k3 + r2 * 4.0 * k4))        # d radial / d r^2
+        fx = x * radial + 2.0 * p1 * x * y + p2 * (r2 + 2.0 * x * x) - xd
+        fy = y * radial + 2.0 * p2 * x * y + p1 * (r2 + 2.0 * y * y) - yd
+        fx_x = radial + 2.0 * x * x * d_radial + 2.0 * p1 * y + 6.0 * p2 * x
+        fx_y = 2.0 * x * y * d_radial + 2.0 * p1 * x + 2.0 * p2 * y
+        fy_x = 2.0 * x * y * d_radial + 2.0 * p2 * y + 2.0 * p1 * x
+        fy_y = radial + 2.0 * y * y * d_radial + 2.0 * p2 * x + 6.0 * p1 * y
+        det = fx_x * fy_y - fx_y * fy_x
+        ok = det.abs() > eps
+        safe = torch.where(ok, det, torch.ones_like(det))
+        x = x - torch.where(ok, (fx * fy_y - fy * fx_y) / safe, torch.zeros_like(det))
+        y = y - torch.where(ok, (fy * fx_x - fx * fy_x) / safe, torch.zeros_like(det))
+    return torch.stack((x, y), dim=-1)
+
+
+def rotation_matrix(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """The rotation ``[3, 3]`` about ``a x b`` that turns the direction of ``a`` into the direction of ``b``
+    (Rodrigues' formula); opposite vectors turn by pi about an axis perpendicular to ``a``."""
+    a = a / torch.linalg.vector_norm(a)
+    b = b / torch.linalg.vector_norm(b)
+    v = torch.linalg.cross(a, b)
+    c = torch.dot(a, b)
+    if float(c) < -1.0 + 1e-8:
+        helper = torch.eye(3, dtype=a.dtype)[int(torch.argmin(a.abs()))]
+        axis = torch.linalg.cross(a, helper)
+        axis = axis / torch.linalg.vector_norm(axis)
+        return 2.0 * torch.outer(axis, axis) - torch.eye(3, dtype=a.dtype)
+    K = torch.zeros(3, 3, dtype=a.dtype)
+    K[0, 1], K[0, 2], K[1, 0], K[1, 2], K[2, 0], K[2, 1] = -v[2], v[1], v[2], -v[0], -v[1], v[0]
+    return torch.eye(3, dtype=a.dtype) + K + K @ K / (1.0 + c)

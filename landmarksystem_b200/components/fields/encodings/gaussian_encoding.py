@@ -87,6 +87,13 @@ def cat_tensors_to_optimizer(optimizer, tensors: Dict[str, torch.Tensor]) -> Dic
     return out
 
 
+def build_covariance_from_scaling_rotation(scaling: torch.Tensor, scaling_modifier: float, rotation: torch.Tensor):
+    """Upper triangle ``[N, 6]`` of ``R S S^T R^T`` with ``S = diag(scaling_modifier * scaling)`` and ``R`` from the
+    quaternions ``rotation`` (reference: gaussian_encoding.py:22-38)."""
+    L = build_scaling_rotation(scaling_modifier * scaling, rotation)
+    return strip_symmetric(L @ L.transpose(1, 2))
+
+
 class GaussianEncoding(BaseGaussianEncoding):
     def __init__(self, sh_degree: int = 3, percent_dense: float = 0.01, act_cache: bool = False, device="cuda"):
         super().__init__()
@@ -145,9 +152,10 @@ class GaussianEncoding(BaseGaussianEncoding):
     def get_opacity(self):
         return self._cached("opacity", lambda: self.opacity_activation(self._opacity))
 
+    covariance_activation = staticmethod(build_covariance_from_scaling_rotation)
+
     def get_covariance(self, scaling_modifier: float = 1.0):
-        L = build_scaling_rotation(scaling_modifier * self.get_scaling, self._rotation)
-        return strip_symmetric(L @ L.transpose(1, 2))
+        return build_covariance_from_scaling_rotation(self.get_scaling, scaling_modifier, self._rotation)
 
     # -- setters (reference: gaussian_encoding.py:855-925).  With ``act_cache`` outside training the value is the
     # ACTIVATED quantity and lands in the cache the getters read; otherwise it replaces the raw tensor. ---------

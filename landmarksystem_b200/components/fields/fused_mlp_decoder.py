@@ -7,6 +7,20 @@ same parameters as ``MLPDecoder`` (biases included), so a checkpoint loads into 
 from .mlp_decoder import MLPDecoder
 
 
+def activation_to_tcnn_string(activation) -> str:
+    """Name of a ``torch.nn`` activation in tiny-cuda-nn's vocabulary (``"ReLU"``, ``"Leaky ReLU"``, ``"Sigmoid"``,
+    ``"Softplus"``, ``"Tanh"``, ``"None"``), the vocabulary the reference's network descriptions use
+    (fused_mlp_decoder.py:9-34)."""
+    import torch
+
+    names = ((torch.nn.ReLU, "ReLU"), (torch.nn.LeakyReLU, "Leaky ReLU"), (torch.nn.Sigmoid, "Sigmoid"),
+             (torch.nn.Softplus, "Softplus"), (torch.nn.Tanh, "Tanh"), (type(None), "None"))
+    for cls, name in names:
+        if isinstance(activation, cls):
+            return name
+    raise ValueError(f"activation {activation} has no fused counterpart (supported: {[n for _, n in names]})")
+
+
 class FusedMLPDecoder(MLPDecoder):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)

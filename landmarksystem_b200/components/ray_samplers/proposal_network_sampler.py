@@ -171,6 +171,12 @@ class HashMLPDensityField(BaseModule):
     forward = density_fn
 
 
+def contract(x: torch.Tensor) -> torch.Tensor:
+    """L-infinity scene contraction: identity inside the unit cube, ``(2 - 1/|x|) x / |x|`` outside."""
+    mag = x.abs().amax(dim=-1, keepdim=True).clamp_min(1e-9)
+    return torch.where(mag < 1, x, (2 - 1 / mag) * (x / mag))
+
+
 class ProposalNetworks(nn.Module):
     def __init__(self, aabb, num_proposal_iterations: int = 2, proposal_net_args_list: Sequence[dict] = (),
                  use_same_proposal_network: bool = False, spatial_distortion=None, device="cpu"):

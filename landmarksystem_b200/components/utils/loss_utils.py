@@ -30,6 +30,18 @@ def _gaussian_window(size: int, sigma: float, channels: int, like: torch.Tensor)
     return w2d.expand(channels, 1, size, size).contiguous().to(device=like.device, dtype=like.dtype)
 
 
+def gaussian(window_size: int, sigma: float) -> torch.Tensor:
+    """Normalised 1-D Gaussian of ``window_size`` taps centred on the middle tap."""
+    x = torch.arange(window_size, dtype=torch.float32) - window_size // 2
+    g = torch.exp(-(x ** 2) / (2 * sigma ** 2))
+    return g / g.sum()
+
+
+def create_window(window_size: int, channel: int) -> torch.Tensor:
+    """Depth-wise SSIM filter ``[channel, 1, window_size, window_size]`` (sigma 1.5)."""
+    return _gaussian_window(window_size, 1.5, channel, torch.zeros(()))
+
+
 def ssim(img1: torch.Tensor, img2: torch.Tensor, window_size: int = 11, size_average: bool = True) -> torch.Tensor:
     """SSIM with an 11x11 Gaussian window (sigma 1.5); images are ``[C, H, W]`` or ``[N, C, H, W]``."""
     if img1.dim() == 3:
@@ -139,14 +151,23 @@ def interlevel_loss(weights_list, spacing_starts_list, spacing_ends_list) -> tor
 _LPIPS = {}
 
 
-def rgb_lpips(np_gt, np_im, net_name: str, device):
-    """LPIPS needs the external ``lpips`` package and its pretrained weights; unavailable offline."""
+def init_lpips(net_name: str, device):
+    """The LPIPS network ``"alex"`` / ``"vgg"`` on ``device``, or ``None`` when the external ``lpips`` package (and
+    its pretrained weights) is not installed."""
+    assert net_name in ("alex", "vgg")
     try:
-        import lpips  # noqa: F401
+        import lpips
     except ImportError:
-        return float("nan")
+        return None
+    return lpips.LPIPS(net=net_name, version="0.1").eval().to(device)
+
+
+def rgb_lpips(np_gt, np_im, net_name: str, device):
+    """LPIPS needs the external ``lpips`` package and its pretrained weights; ``nan`` without them."""
     if net_name not in _LPIPS:
-        _LPIPS[net_name] = lpips.LPIPS(net=net_name, version="0.1").eval().to(device)
+        _LPIPS[net_name] = init_lpips(net_name, device)
+    if _LPIPS[net_name] is None:
+        return float("nan")
     gt = torch.from_numpy(np_gt).permute(2, 0, 1).contiguous().to(device)
     im = torch.from_numpy(np_im).permute(2, 0, 1).contiguous().to(device)
     return _LPIPS[net_name](gt, im, normalize=True).item()

@@ -258,3 +258,28 @@ def test_ray_and_pose_helpers(tmp_path):
     cl.write_colmap_bin_array(str(tmp_path / "depth.bin"), depth)
     assert np.array_equal(cl.read_colmap_bin_array(str(tmp_path / "depth.bin")), depth)
     assert cl.read_extrinsics_binary is cl.read_images_binary and cl.read_intrinsics_text is cl.read_cameras_text
+
+
+def test_lens_ordering_and_rotation_helpers():
+    torch.manual_seed(0)
+    assert np.allclose(pu.unit_vector([3.0, 4.0]), [0.6, 0.8])
+    assert np.allclose(np.linalg.norm(pu.unit_vector(np.ones((4, 3)), axis=1), axis=1), 1.0)
+    v, n = pu.normalize_with_norm(torch.tensor([[3.0, 4.0], [0.0, 0.0]]), dim=-1)
+    assert torch.allclose(v[0], torch.tensor([0.6, 0.8])) and float(n[0]) == 5.0 and torch.isfinite(v).all()
+    # greedy nearest-neighbour tour along a line visited out of order
+    xs = [0.0, 5.0, 1.0, 4.0, 2.0]
+    poses = torch.eye(4).repeat(5, 1, 1)
+    poses[:, 0, 3] = torch.tensor(xs)
+    Ks = torch.arange(5, dtype=torch.float32)[:, None, None] * torch.ones(5, 3, 3)
+    op, ok = pu.get_ordered_poses_and_k(poses, Ks)
+    assert op[:, 0, 3].tolist() == [0.0, 1.0, 2.0, 4.0, 5.0] and ok[:, 0, 0].tolist() == [0.0, 2.0, 4.0, 3.0, 1.0]
+    # undistort inverts the lens model
+    params = pu.get_distortion_params(k1=0.1, k2=-0.02, k3=0.003, p1=0.004, p2=-0.003)
+    pts = torch.rand(200, 2) * 1.2 - 0.6
+    back = pu.radial_and_tangential_undistort(pu.radial_and_tangential_distort(pts, params), params)
+    assert torch.allclose(back, pts, atol=1e-5)
+    for a, b in ((torch.tensor([1.0, 2.0, 3.0]), torch.tensor([-2.0, 0.5, 1.0])),
+                 (torch.tensor([0.0, 0.0, 2.0]), torch.tensor([0.0, 0.0, -1.0]))):
+        R = pu.rotation_matrix(a, b)
+        assert torch.allclose(R @ (a / a.norm()), b / b.norm(), atol=1e-6)
+        assert torch.allclose(R @ R.T, torch.eye(3), atol=1e-6) and abs(float(torch.linalg.det(R)) - 1.0) < 1e-5

@@ -73,6 +73,37 @@ def test_gaussian_encoding_setters_follow_the_activation_cache():
     assert opt.param_groups[0]["params"][0] is swapped["xyz"] and opt.state[swapped["xyz"]]["exp_avg"].abs().sum() == 0
 
 
+def test_rasterizer_component_renders_several_models_in_one_sort():
+    """``GaussianSplattingRasterizer``: a list of models renders like one model that holds all their Gaussians."""
+    from landmarksystem_b200.components.data.cameras import Camera
+    from landmarksystem_b200.components.renderers import GassianSplattingRasterizer, GaussianSplattingRasterizer
+    from landmarksystem_b200.synthetic import ring_cameras
+
+    assert GassianSplattingRasterizer is GaussianSplattingRasterizer
+    torch.manual_seed(0)
+    parts = []
+    for seed in (0, 1):
+        enc = GaussianEncoding(1, device="cpu")
+        enc.create_from_pcd(_pcd(40, seed=seed))
+        enc._opacity.data.fill_(1.5)
+        enc._scaling.data.fill_(-2.0)
+        parts.append(enc)
+    whole = GaussianEncoding(1, device="cpu")
+    whole._set_params(*(torch.cat([getattr(p, n).detach() for p in parts]) for n in
+                        ("_xyz", "_features_dc", "_features_rest", "_scaling", "_rotation", "_opacity")))
+    cam = Camera.from_c2w(ring_cameras(4, 3.0)[0].numpy(), 24, 20, 30.0)
+    renderer = GaussianSplattingRasterizer(white_background=True)
+    both = renderer(parts, camera=cam)
+    one = renderer(whole, camera=cam)
+    assert both["counts"] == [len(parts[0]), len(parts[1])] and both["render"].shape == (3, 20, 24)
+    assert torch.allclose(both["render"], one["render"], atol=1e-6) and torch.equal(both["radii"], one["radii"])
+    assert both["visibility_filter"].any() and float(one["render"].detach().min()) < 0.99        # something was drawn
+    first_only = renderer(parts[0], camera=cam)["render"]
+    assert not torch.allclose(first_only, both["render"], atol=1e-3)
+    both["render"].sum().backward()
+    assert parts[1]._xyz.grad is not None and parts[1]._xyz.grad.abs().sum() > 0
+
+
 def test_densify_and_prune_keeps_optimizer_in_sync():
     torch.manual_seed(0)
     enc = GaussianEncoding(1, device="cpu")

@@ -99,3 +99,33 @@ def test_cat_pad_bf16_concatenates_pads_and_routes_gradients():
     g = torch.randn(7, 16).to(torch.bfloat16)
     out.backward(g)
     assert torch.equal(a.grad, g[:, :3].float()) and torch.equal(c.grad, g[:, 8:10].float()) and b.grad is None
+
+
+def test_small_helpers_under_reference_names():
+    """``gaussian / create_window`` (SSIM filter), ``build_covariance_from_scaling_rotation``, ``getNeRFppNorm``,
+    ``PILtoTorch``, ``activation_to_tcnn_string`` and ``contract``."""
+    from types import SimpleNamespace
+
+    import numpy as np
+    import pytest
+
+    from landmarksystem_b200.components.data.datasets.dataset_utils import PILtoTorch, getNeRFppNorm
+    from landmarksystem_b200.components.fields.encodings.gaussian_encoding import build_covariance_from_scaling_rotation
+    from landmarksystem_b200.components.fields.fused_mlp_decoder import activation_to_tcnn_string
+    from landmarksystem_b200.components.ray_samplers.proposal_network_sampler import contract
+    from landmarksystem_b200.components.utils.loss_utils import create_window, gaussian
+
+    g = gaussian(11, 1.5)
+    w = create_window(11, 3)
+    assert abs(float(g.sum()) - 1) < 1e-6 and int(g.argmax()) == 5 and torch.allclose(w[1, 0], torch.outer(g, g))
+    cov = build_covariance_from_scaling_rotation(torch.tensor([[1.0, 2.0, 3.0]]), 2.0, torch.tensor([[1.0, 0, 0, 0]]))
+    assert torch.allclose(cov, torch.tensor([[4.0, 0, 0, 16.0, 0, 36.0]]))
+    cams = [SimpleNamespace(camera_center=torch.tensor(c)) for c in ([0.0, 0, 0], [2.0, 0, 0], [1.0, 3.0, 0])]
+    norm = getNeRFppNorm(cams)
+    assert np.allclose(norm["translate"], [-1.0, -1.0, 0.0]) and abs(norm["radius"] - 1.1 * 2.0) < 1e-6
+    assert PILtoTorch(np.full((4, 5), 255, np.uint8)).shape == (1, 4, 5)
+    assert float(PILtoTorch(np.full((4, 5, 3), 51, np.uint8)).max()) == pytest.approx(0.2)
+    assert activation_to_tcnn_string(torch.nn.LeakyReLU()) == "Leaky ReLU" and activation_to_tcnn_string(None) == "None"
+    with pytest.raises(ValueError):
+        activation_to_tcnn_string(torch.nn.GELU())
+    assert torch.allclose(contract(torch.tensor([[0.5, 0, 0], [4.0, 0, 0]])), torch.tensor([[0.5, 0, 0], [1.75, 0, 0]]))
