@@ -90,3 +90,6 @@ class DynamicLoadGroupInitializer(GroupInitializer):
                 if ranks:
                     groups.append(ranks)
         return groups
+
+
+ProcessGroupInitializer = GroupInitializer      # base-class name of the reference (communicator/group_initializer.py)

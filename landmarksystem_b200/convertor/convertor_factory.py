@@ -90,3 +90,6 @@ class ComponentConvertorFactory:
     def get_convertor(convertor_type: str) -> BaseConvertor:
         assert convertor_type in ComponentConvertorFactory._TABLE, f"unknown convertor '{convertor_type}'"
         return ComponentConvertorFactory._TABLE[convertor_type]()
+
+
+ComponentsConvertorBase = BaseConvertor         # base-class name of the reference (components_convertor/convertor_factory.py)

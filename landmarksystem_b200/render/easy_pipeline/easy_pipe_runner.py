@@ -11,10 +11,14 @@ from .task import StopTask, Task
 
 class EasyPipeRunner:
     def __init__(self, items: List[PipelineItem]):
+        self.items = items
         self.job_queue, self.result_queue = SimpleQueue(), SimpleQueue()
-        self.pipeline = SimplePipeline(items, self.job_queue, self.result_queue)
+        self.pipeline = self.create_pipe()
         self.pipeline.start()
         self.pending = 0
+
+    def create_pipe(self) -> SimplePipeline:
+        return SimplePipeline(self.items, self.job_queue, self.result_queue)
 
     def run_batch(self, payloads) -> None:
         for p in payloads:
@@ -31,5 +35,20 @@ class EasyPipeRunner:
             raise task.payload
         return task.payload
 
+    def get_from_result_queue(self):
+        """The next raw task of the result queue (blocking)."""
+        return self.result_queue.get()
+
+    def get_result_task(self, block: bool = False):
+        """The next finished task, or ``None`` when ``block`` is false and none is ready."""
+        if not block and self.result_queue.empty():
+            return None
+        task = self.get_from_result_queue()
+        self.pending = max(self.pending - 1, 0)
+        return task
+
     def stop(self) -> None:
         self.pipeline.stop()
+
+    def wait_stop(self) -> None:
+        self.pipeline.wait_stop()

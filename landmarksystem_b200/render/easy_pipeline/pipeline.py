@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 from queue import SimpleQueue
-from typing import Callable, List
+from typing import Callable, List, Optional
 
 from .task import StopTask
 from .worker import ProfileWorkerThread, SimpleWorker, WorkerThread
@@ -15,6 +15,7 @@ class PipelineItem:
     n_workers: int = 1
     use_cuda_stream: bool = False
     profile: bool = False
+    init_fn: Optional[Callable] = None          # builds a per-worker resource; ``fn(resource, payload)`` then
 
 
 class SimplePipeline:
@@ -22,11 +23,11 @@ class SimplePipeline:
         self.items, self.threads = items, []
         queues = [job_queue] + [SimpleQueue() for _ in items[:-1]] + [result_queue]
         for i, item in enumerate(items):
-            assert item.n_workers == 1 or i == len(items) - 1 or True
             for _ in range(item.n_workers):
                 cls = ProfileWorkerThread if item.profile else WorkerThread
-                self.threads.append(cls(SimpleWorker(item.fn), queues[i], queues[i + 1], use_cuda_stream=item.use_cuda_stream))
-        self.job_queue = job_queue
+                self.threads.append(cls(SimpleWorker(item.fn, item.init_fn), queues[i], queues[i + 1],
+                                        use_cuda_stream=item.use_cuda_stream))
+        self.job_queue, self.result_queue = job_queue, result_queue
 
     def start(self):
         for t in self.threads:
@@ -35,5 +36,11 @@ class SimplePipeline:
     def stop(self):
         for _ in range(max(self.items[0].n_workers, 1)):
             self.job_queue.put(StopTask())
+        self.wait_stop()
+
+    def wait_stop(self, timeout: float = 10.0):
         for t in self.threads:
-            t.join(timeout=10)
+            t.join(timeout=timeout)
+
+    def get_result_queue(self) -> SimpleQueue:
+        return self.result_queue

@@ -4,19 +4,31 @@ from __future__ import annotations
 
 import threading
 from queue import SimpleQueue
-from typing import Callable
+from typing import Callable, Optional
 
 import torch
 
 from .task import EmptyTask, StopTask, Task
 
 
-class SimpleWorker:
-    def __init__(self, fn: Callable):
-        self.fn = fn
+class Worker:
+    """Stage interface: ``process(payload)`` returns the stage's output."""
 
     def process(self, payload):
-        return self.fn(payload)
+        raise NotImplementedError
+
+
+class SimpleWorker(Worker):
+    """A callable as a stage.  With ``init_fn`` the worker builds a private resource once (a model replica, a buffer
+    pool) and the callable receives it first: ``fn(resource, payload)``."""
+
+    def __init__(self, fn: Callable, init_fn: Optional[Callable] = None):
+        self.fn = fn
+        self.has_resource = init_fn is not None
+        self.resource = init_fn() if init_fn is not None else None
+
+    def process(self, payload):
+        return self.fn(self.resource, payload) if self.has_resource else self.fn(payload)
 
 
 class WorkerThread(threading.Thread):
@@ -52,6 +64,19 @@ class WorkerThread(threading.Thread):
         if self.device is not None:
             torch.cuda.set_device(self.device)
         self.loop()
+
+    # -- queue access under the reference's method names (worker.py:101-124) ---------------------------------
+    def get_from_job_queue(self):
+        return self.in_queue.get()
+
+    def put_to_result_queue(self, result):
+        self.out_queue.put(result)
+
+    def put_stop_task(self):
+        self.in_queue.put(StopTask())
+
+    def wait_stop(self, timeout: float = 10.0):
+        self.join(timeout=timeout)
 
 
 class ProfileWorkerThread(WorkerThread):

@@ -127,6 +127,30 @@ def test_easy_pipeline_orders_results_and_reports_errors():
     runner.stop()
 
 
+def test_easy_pipeline_worker_resources_and_queue_access():
+    """A stage with ``init_fn`` owns a resource built once per worker; the reference's queue-level calls
+    (``get_result_task``, ``get_result_queue``, ``wait_stop``) work on the same runner."""
+    from landmarksystem_b200.render.easy_pipeline import SimpleWorker, Worker
+
+    built = []
+
+    def make_resource():
+        built.append(1)
+        return {"offset": 100}
+
+    assert issubclass(SimpleWorker, Worker)
+    runner = EasyPipeRunner([PipelineItem(lambda res, x: x + res["offset"], init_fn=make_resource),
+                             PipelineItem(lambda x: -x)])
+    assert runner.get_result_task(block=False) is None
+    runner.run_batch([1, 2])
+    first = runner.get_result_task(block=True)
+    assert first.payload == -101 and runner.get_result() == -102 and built == [1]
+    assert runner.pipeline.get_result_queue() is runner.result_queue
+    runner.stop()
+    runner.wait_stop()
+    assert not any(t.is_alive() for t in runner.pipeline.threads)
+
+
 @pytest.mark.gpu
 def test_init_inference_kernel_runtime_gpu(tmp_path):
     _save_random_model(tmp_path, [2, 2])
