@@ -148,6 +148,33 @@ class VolumeRenderDataset(BaseDataset):
         self.build_rays(poses, None, H, W, focal, _arg(a, "camera", "normal"))
         self.render_poses, self.render_rays = poses, self.all_rays
 
+    def preprocess(self, args=None, batch_size: int = 8192, root: Optional[str] = None) -> int:
+        """Shuffle this dataset's rays and write them as shards of ``batch_size`` rays under ``root`` (default
+        ``args.preprocessed_dir``); returns the number of shards (reference: matrixcity_dataset.py:113-302)."""
+        from .processed_dataset import preprocess
+
+        flat = self._flat_view()
+        return preprocess(flat, root or (args or self.args).preprocessed_dir, shard_rays=batch_size)
+
+    def distpreprocess(self, args=None, batch_size: int = 8192, root: Optional[str] = None, group=None) -> int:
+        """The same collectively: every rank of the default group writes its share of the shards (reference:
+        matrixcity_dataset.py:304-515)."""
+        import torch.distributed as dist
+
+        from .processed_dataset import dist_preprocess
+
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        return dist_preprocess(self._flat_view(), root or (args or self.args).preprocessed_dir, rank, world,
+                               shard_rays=batch_size, group=group)
+
+    def _flat_view(self):
+        from types import SimpleNamespace
+
+        assert self.all_rgbs is not None, "this split has no colours to store"
+        return SimpleNamespace(all_rays=self.all_rays.reshape(-1, self.all_rays.shape[-1]),
+                               all_rgbs=self.all_rgbs.reshape(-1, 3), all_idxs=self.all_idxs.reshape(-1))
+
     def __len__(self):
         return 0 if self.all_rays is None else self.all_rays.shape[0]
 

@@ -13,6 +13,15 @@ class MergeType(str, Enum):
     Unevenly = "Unevenly"  # explicit split sizes along a dimension
     List = "List"          # one state-dict key per block
 
+    @classmethod
+    def check(cls, item) -> bool:
+        """Whether ``item`` names a merge type (reference: landmark/render/util/types.py:20-26)."""
+        try:
+            cls(item)
+        except ValueError:
+            return False
+        return True
+
 
 class StageInput(str, Enum):
     Args = "Args"

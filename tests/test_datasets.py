@@ -283,3 +283,16 @@ def test_lens_ordering_and_rotation_helpers():
         R = pu.rotation_matrix(a, b)
         assert torch.allclose(R @ (a / a.norm()), b / b.norm(), atol=1e-6)
         assert torch.allclose(R @ R.T, torch.eye(3), atol=1e-6) and abs(float(torch.linalg.det(R)) - 1.0) < 1e-5
+
+
+def test_dataset_shard_methods_and_merge_type_check(tmp_path):
+    from landmarksystem_b200.components.data.datasets import dataset_dict
+    from landmarksystem_b200.render.types import MergeType
+
+    assert MergeType.check("Unevenly") and not MergeType.check("Sometimes")
+    args = SimpleNamespace(datadir="ring:4:16x16:18:3", lb=[-1, -1, -1], ub=[1, 1, 1], white_bkgd=False,
+                           preprocessed_dir=str(tmp_path / "shards"))
+    ds = dataset_dict["synthetic"](split="train", downsample=1.0, is_stack=True, args=args)
+    assert ds.preprocess(args, batch_size=256) == 4                       # 4 images x 256 rays
+    assert PreprocessedDataset(args.preprocessed_dir)[3][1].shape == (256, 3)
+    assert ds.distpreprocess(root=str(tmp_path / "dist"), batch_size=512) == 2
