@@ -278,10 +278,26 @@ def test_scaffold_model_helpers_cov_prefilter_and_mlp_file(tmp_path):
     code = model.get_appearance_code(torch.tensor(0)) if model.embedding_appearance is not None else None
     assert code is None or code.shape == (cfg.appearance_dim,)
 
+    with torch.no_grad():                                       # make the saved heads differ from a fresh initialisation
+        for prm in model.anchor_decoder.mlp_color.parameters():
+            prm.add_(0.37)
     model.save_mlp_checkpoints(str(tmp_path / "mlp" / "checkpoint.pth"))
     saved = torch.load(str(tmp_path / "mlp" / "checkpoint.pth"), weights_only=False)
     assert {"anchor_decoder.opacity_mlp", "anchor_decoder.cov_mlp", "anchor_decoder.color_mlp"} <= set(saved)
     assert ("anchor_decoder.embedding_appearance" in saved) == (model.embedding_appearance is not None)
+    # the decoder file converts into the flat state dict a fresh model loads beside the point cloud
+    from landmarksystem_b200.render.utils import transform_gs_mlp_checkpoint
+
+    model.save_ply(str(tmp_path / "mlp"))
+    flat = transform_gs_mlp_checkpoint(str(tmp_path / "mlp" / "checkpoint.pth"), out_dir=str(tmp_path / "converted"))
+    assert os.path.exists(tmp_path / "converted" / "point_cloud.ply")
+    fresh = mod.OctreeGSTrainer(cfg).build_model()
+    if model.embedding_appearance is not None:
+        fresh.set_appearance(model.embedding_appearance.num_embeddings)
+    fresh.load_from_state_dict(fresh.get_state_dict_from_ckpt(str(tmp_path / "converted" / "point_cloud.ply"), "cpu"))
+    assert flat.endswith("state_dict.th") and fresh.get_primitives_num == model.get_primitives_num
+    for a, b in zip(fresh.anchor_decoder.mlp_color.parameters(), model.anchor_decoder.mlp_color.parameters()):
+        assert torch.equal(a, b)
     model.save_ply(str(tmp_path / "out"), rank=1)
     model.save_state_dict(str(tmp_path / "out" / "state_dict-sub1.th"))
     assert os.path.exists(tmp_path / "out" / "point_cloud-sub1.ply")
