@@ -435,3 +435,29 @@ class FusedChannelParallelTensorVMEncoding(ChannelParallelTensorVMEncoding):
         super().__init__(*args, **kwargs)
         if torch.device(self.device).type == "cuda":
             self.enable_shadow(fused_optimizer=False)
+
+
+class CoefParam(torch.nn.Module):
+    """A list of plane / line coefficient tensors as one module, so that a wrapper which only accepts modules
+    (``DistributedDataParallel``) can hold them; ``forward`` samples one of them in the reference layout
+    (reference: tensor_vm_encoding.py:639-677, unused there as well).
+
+    ``coefs[k]``: ``[1, C, B, H, W]`` planes or ``[1, C, Z, B]`` lines; ``coordinates[idx_dim]``: a ``grid_sample``
+    coordinate tensor for that layout."""
+
+    def __init__(self, coefs: Sequence[torch.Tensor]) -> None:
+        super().__init__()
+        self.params = torch.nn.ParameterList([c if isinstance(c, torch.nn.Parameter) else torch.nn.Parameter(c)
+                                              for c in coefs])
+
+    def forward(self, coordinates: torch.Tensor, idx_plane: int, idx_dim: int, align_corners: bool = True):
+        return F.grid_sample(self.params[idx_plane], coordinates[[idx_dim]], align_corners=align_corners)
+
+    def __setitem__(self, idx: int, value):
+        self.params[idx] = value
+
+    def __getitem__(self, idx: int):
+        return self.params[idx]
+
+    def __len__(self) -> int:
+        return len(self.params)

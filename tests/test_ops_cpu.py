@@ -129,3 +129,45 @@ def test_small_helpers_under_reference_names():
     with pytest.raises(ValueError):
         activation_to_tcnn_string(torch.nn.GELU())
     assert torch.allclose(contract(torch.tensor([[0.5, 0, 0], [4.0, 0, 0]])), torch.tensor([[0.5, 0, 0], [1.75, 0, 0]]))
+
+
+def test_tcnn_shaped_front_end():
+    """``tcnn.Encoding`` / ``tcnn.Network`` descriptions of the reference's call sites (hash_encoding.py:97-107,
+    sh_encoding.py:35-38, fused_mlp_decoder.py:86-90) served by this package's own components."""
+    import pytest
+
+    from landmarksystem_b200.components.utils.tcnn_utils import TCNN_EXISTS, tcnn
+    from landmarksystem_b200.ops.ngp_field import sh_encode
+
+    assert TCNN_EXISTS
+    torch.manual_seed(0)
+    enc = tcnn.Encoding(3, {"otype": "HashGrid", "n_levels": 4, "n_features_per_level": 2, "log2_hashmap_size": 10,
+                            "base_resolution": 4, "per_level_scale": 1.5}, device="cpu")
+    with torch.no_grad():
+        enc.params.normal_()
+    x = torch.rand(7, 5, 3)
+    ref = hashgrid_reference(x.reshape(-1, 3), enc.params.view(-1, 2), make_meta(4, 2, 10, 4, 1.5)).reshape(7, 5, 8)
+    assert enc.n_output_dims == 8 and torch.allclose(enc(x), ref, atol=1e-6)
+    enc(x).sum().backward()
+    assert enc.params.grad is not None and enc.params.grad.abs().sum() > 0
+
+    sh = tcnn.Encoding(3, {"otype": "SphericalHarmonics", "degree": 4}, device="cpu")
+    d = F.normalize(torch.randn(6, 3), dim=-1)
+    assert sh.n_output_dims == 16 and torch.allclose(sh((d + 1) / 2), sh_encode(d, 4, False), atol=1e-5)
+
+    net = tcnn.Network(32, 16, {"otype": "FullyFusedMLP", "activation": "ReLU", "output_activation": "None",
+                                "n_neurons": 64, "n_hidden_layers": 1}, device="cpu")
+    w0, w1 = [p for p in net.inner.parameters()]
+    h = torch.randn(3, 4, 32)
+    assert net.params.numel() == 32 * 64 + 64 * 16
+    assert torch.allclose(net(h), torch.relu(h @ w0.T) @ w1.T, atol=1e-5)
+    both = tcnn.NetworkWithInputEncoding(3, 4, {"otype": "HashGrid", "n_levels": 2, "base_resolution": 4,
+                                                "per_level_scale": 2.0, "log2_hashmap_size": 8},
+                                         {"otype": "CutlassMLP", "n_neurons": 16, "n_hidden_layers": 2,
+                                          "output_activation": "Sigmoid"}, device="cpu")
+    out = both(torch.rand(9, 3))
+    assert out.shape == (9, 4) and float(out.detach().min()) > 0 and float(out.detach().max()) < 1
+    with pytest.raises(ValueError):
+        tcnn.Encoding(3, {"otype": "Frequency"})
+    with pytest.raises(ValueError):
+        tcnn.Network(3, 3, {"otype": "FullyFusedMLP", "activation": "Tanh"})
