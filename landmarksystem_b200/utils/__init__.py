@@ -1,6 +1,6 @@
 """Framework-wide utilities and string constants (reference: landmark/utils/__init__.py:6-11)."""
 from .config import Config
-from .env import EnvSetting
+from .env import EnvSetting, parse_env
 from .singleton import SingletonMeta
 
 _RANK_STR = "rank"
@@ -12,6 +12,7 @@ MERGE_TYPE_STR = "merge_type"
 __all__ = [
     "Config",
     "EnvSetting",
+    "parse_env",
     "SingletonMeta",
     "_RANK_STR",
     "_WORLD_SIZE_STR",

@@ -6,6 +6,17 @@ import os
 import subprocess
 
 
+def parse_env(env_name: str) -> bool:
+    """A boolean switch from the environment: ``True`` / ``ON`` / ``1`` are true, unset / ``False`` / ``OFF`` / ``0``
+    false, anything else is an error (reference: landmark/utils/env.py:6-19)."""
+    value = os.getenv(env_name)
+    if value in ("True", "ON", "1"):
+        return True
+    if value in (None, "False", "OFF", "0"):
+        return False
+    raise NotImplementedError(f"{env_name}={value!r}: expected True/ON/1 or False/OFF/0")
+
+
 def _slurm_master_addr() -> str:
     nodelist = os.environ.get("SLURM_NODELIST", "")
     try:

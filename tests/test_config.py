@@ -1,4 +1,5 @@
 """L0: attribute dict, typed config blocks, conf-file loading and console overrides."""
+import os
 import textwrap
 
 import pytest
@@ -169,3 +170,37 @@ def test_package_root_exports_match_the_reference():
         assert getattr(lm, name) is not None
     with pytest.raises(AttributeError):
         lm.no_such_name
+
+
+def test_env_switch_parsing_and_slurm_discovery(monkeypatch):
+    """``parse_env`` and the SLURM branch of ``EnvSetting`` (reference: landmark/utils/env.py:6-46)."""
+    from landmarksystem_b200.utils import EnvSetting, parse_env
+
+    monkeypatch.delenv("LMB_TEST_SWITCH", raising=False)
+    assert parse_env("LMB_TEST_SWITCH") is False
+    for text, want in (("ON", True), ("1", True), ("True", True), ("OFF", False), ("0", False), ("False", False)):
+        monkeypatch.setenv("LMB_TEST_SWITCH", text)
+        assert parse_env("LMB_TEST_SWITCH") is want
+    monkeypatch.setenv("LMB_TEST_SWITCH", "maybe")
+    with pytest.raises(NotImplementedError):
+        parse_env("LMB_TEST_SWITCH")
+
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(name, raising=False)
+    monkeypatch.setenv("SLURM_PROCID", "5")
+    monkeypatch.setenv("SLURM_NTASKS", "16")
+    monkeypatch.setenv("SLURM_LOCALID", "1")
+    monkeypatch.setenv("SLURM_JOB_ID", "4321")
+    monkeypatch.setenv("SLURM_NODELIST", "node[01-02]")
+    monkeypatch.setenv("COMM_TIMEOUT", "77")
+    try:
+        EnvSetting.refresh()
+        assert EnvSetting.SLURM and (EnvSetting.RANK, EnvSetting.WORLD_SIZE, EnvSetting.LOCAL_RANK) == (5, 16, 1)
+        assert EnvSetting.COMM_TIMEOUT == 77 and os.environ["MASTER_PORT"] == str(29500 + 321)
+        assert os.environ["MASTER_ADDR"]                      # first host of the node list, or loopback without scontrol
+    finally:
+        for name in ("SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID", "SLURM_JOB_ID", "SLURM_NODELIST", "COMM_TIMEOUT",
+                     "RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+            monkeypatch.delenv(name, raising=False)
+        EnvSetting.refresh()
+    assert not EnvSetting.SLURM and EnvSetting.WORLD_SIZE == 1
