@@ -117,6 +117,50 @@ def test_dynamic_loading_window_reuses_resident_blocks(tmp_path):
     assert mgr.get_buffer().local_block_idxes == [1, 3] and mgr.bytes_h2d == 2 * first
 
 
+def test_user_defined_model_and_adapter_through_init_inference():
+    """A model and an inference module written by a user of the framework: no configuration, no checkpoint - the
+    reference's engine smoke test (tests/test_inference_framework/test_inference.py:389-393, tests/utils.py:15-31)."""
+    from landmarksystem_b200 import InferenceEngine, InferenceModule
+    from landmarksystem_b200.components.model.base_model import BaseNeRF
+
+    class SimpleModel(BaseNeRF):
+        def __init__(self, N=10):
+            super().__init__()
+            self.layer1 = torch.nn.Linear(N, N)
+            self.layer2 = torch.nn.ReLU()
+
+        @staticmethod
+        def get_kwargs():
+            return {"N": 10}
+
+        def forward(self, x):
+            return self.layer2(self.layer1(x))
+
+    class Doubling(InferenceModule):
+        def __init__(self, **kwargs):
+            super().__init__(SimpleModel(**kwargs))
+
+        def preprocess(self, x, scale=1.0):
+            return (x * scale,), {}
+
+        def forward(self, x):
+            return self.model(x)
+
+        def postprocess(self, y):
+            return {"doubled": 2.0 * y}
+
+    torch.manual_seed(0)
+    cfg = dict(runtime="Torch", kernel_fusion=False, ckpt_path=None)
+    bare = lm.init_inference(SimpleModel, None, None, dict(cfg))
+    assert isinstance(bare, InferenceEngine)
+    x = torch.ones(10, 10)
+    assert bare(x).shape == (10, 10) and float(bare(x).min()) >= 0
+    engine = lm.init_inference(SimpleModel, Doubling, None, dict(cfg))
+    inner = [m for m in engine.modules() if isinstance(m, SimpleModel)][0]
+    out = engine(x, scale=3.0)
+    assert set(out) == {"doubled"} and torch.allclose(out["doubled"], 2.0 * inner(3.0 * x))
+
+
 def test_easy_pipeline_orders_results_and_reports_errors():
     runner = EasyPipeRunner([PipelineItem(lambda x: x + 1), PipelineItem(lambda x: x * 2)])
     runner.run_batch([1, 2, 3])
