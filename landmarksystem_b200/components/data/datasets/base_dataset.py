@@ -65,10 +65,16 @@ class VolumeRenderDataset(BaseDataset):
 
     def build_rays(self, poses: torch.Tensor, images: Optional[List[torch.Tensor]], H: int, W: int, focal,
                    camera_mode: str = "normal"):
-        """Fill ``all_rays/all_rgbs/all_idxs`` from per-image poses (OpenGL c2w) and ``[H*W, 3]`` images."""
-        dirs = get_ray_directions_blender(H, W, focal)
+        """Fill ``all_rays/all_rgbs/all_idxs`` from per-image poses (OpenGL c2w) and ``[H*W, 3]`` images.  ``focal``:
+        one number (or an ``(fx, fy)`` tuple) for every image, or a one-dimensional numpy array with one focal length
+        per image."""
+        per_image = isinstance(focal, np.ndarray) and focal.ndim == 1
+        assert not per_image or len(focal) == len(poses), "one focal length per image"
+        dirs = None if per_image else get_ray_directions_blender(H, W, focal)
         rays, idxs = [], []
         for k, c2w in enumerate(poses):
+            if per_image:
+                dirs = get_ray_directions_blender(H, W, float(focal[k]))
             o, d = get_rays(dirs, torch.as_tensor(c2w, dtype=torch.float32), camera_mode)
             rays.append(torch.cat((o, d), -1))
             idxs.append(torch.full((H * W,), float(k)))

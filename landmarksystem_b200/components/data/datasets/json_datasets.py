@@ -67,9 +67,19 @@ class _JsonNeRFDataset(VolumeRenderDataset):
         self.build_rays(torch.from_numpy(poses), images, H, W, focal, getattr(args, "camera", "normal"))
 
     def intrinsics(self, meta):
+        """``(W, H, focal)``; ``focal`` is one number, or an array with one focal length per frame when the file gives
+        ``fl_x`` inside the frames (the reference's drone layout, ray_utils.py:122-170; one image size for all)."""
         ds = float(self.downsample)
-        W, H = int(meta.get("w", 1920) / ds), int(meta.get("h", 1080) / ds)
-        return W, H, float(meta["fl_x"]) / ds
+        frames = meta.get("frames", [])
+        first = frames[0] if frames else {}
+        W = int(meta.get("w", first.get("w", 1920)) / ds)
+        H = int(meta.get("h", first.get("h", 1080)) / ds)
+        if "fl_x" in meta:
+            return W, H, float(meta["fl_x"]) / ds
+        if "fl_x" in first:
+            return W, H, np.asarray([float(f["fl_x"]) for f in frames], dtype=np.float64) / ds
+        assert "camera_angle_x" in meta, "transforms file gives neither a focal length nor camera_angle_x"
+        return W, H, 0.5 * W / math.tan(0.5 * float(meta["camera_angle_x"]))
 
     def transform_poses(self, poses: np.ndarray) -> np.ndarray:
         return poses
@@ -116,18 +126,53 @@ class CityGaussianDataset(GaussianSplattingDataset):
 
         meta = load_transforms(args.datadir, split)
         ds = float(downsample)
-        W, H = int(meta.get("w", 1920) / ds), int(meta.get("h", 1080) / ds)
-        fx = float(meta["fl_x"]) / ds
-        fy = float(meta.get("fl_y", meta["fl_x"])) / ds
         paths, poses = frames_to_poses(meta)
         rot, trans = getattr(args, "pose_rotation", [0, 0, 0]), getattr(args, "pose_translation", [0, 0, 0])
-        for k, (p, c2w) in enumerate(zip(paths, poses)):
+        for k, (p, c2w, frame) in enumerate(zip(paths, poses, meta["frames"])):
             if any(float(v) != 0 for v in list(rot) + list(trans)):
                 c2w = pose_rotate_translate(c2w, rot, trans)
+            path = _resolve(args.datadir, p, f"images_{int(ds)}")
+            W, H, fx, fy = self._intrinsics(meta, frame, path, ds)
             cam = Camera.from_c2w(c2w, W, H, fx, fy, uid=k, image_name=os.path.basename(p))
-            cam.image_path = _resolve(args.datadir, p, f"images_{int(ds)}")
+            cam.image_path = path
             if preload:
                 cam.image = self.load_image(cam)
             self.cameras.append(cam)
         self.white_bg = bool(getattr(args, "white_bkgd", False))
         self.compute_extent()
+
+    _size_cache = None
+
+    def _intrinsics(self, meta, frame, image_path: str, ds: float):
+        """``(W, H, fx, fy)`` of one frame.  Three layouts of ``transforms_*.json`` are read (reference:
+        city_dataset.py:568-612 and the data-preparation page of its documentation): one focal length for the whole
+        file (``fl_x`` [, ``fl_y``, ``w``, ``h``]), one field of view (``camera_angle_x``), or focal length and size per
+        frame.  A size that the file does not give is taken from the image itself (read once when it is global)."""
+        def size_of(scope):
+            if "w" in scope and "h" in scope:
+                return int(scope["w"]), int(scope["h"])
+            return None
+
+        size = size_of(frame) or size_of(meta)
+        if size is None:
+            if "fl_x" in frame or self._size_cache is None:
+                if os.path.isfile(image_path):
+                    from PIL import Image
+
+                    with Image.open(image_path) as im:
+                        size = im.size
+                else:
+                    size = (1920, 1080)                  # the MatrixCity frame size
+                if "fl_x" not in frame:
+                    self._size_cache = size
+            else:
+                size = self._size_cache
+        W0, H0 = size
+        if "fl_x" in frame:
+            fx0, fy0 = float(frame["fl_x"]), float(frame.get("fl_y", frame["fl_x"]))
+        elif "fl_x" in meta:
+            fx0, fy0 = float(meta["fl_x"]), float(meta.get("fl_y", meta["fl_x"]))
+        else:
+            assert "camera_angle_x" in meta, "transforms file gives neither a focal length nor camera_angle_x"
+            fx0 = fy0 = 0.5 * W0 / math.tan(0.5 * float(meta["camera_angle_x"]))
+        return int(W0 / ds), int(H0 / ds), fx0 / ds, fy0 / ds

@@ -296,3 +296,94 @@ def test_dataset_shard_methods_and_merge_type_check(tmp_path):
     assert ds.preprocess(args, batch_size=256) == 4                       # 4 images x 256 rays
     assert PreprocessedDataset(args.preprocessed_dir)[3][1].shape == (256, 3)
     assert ds.distpreprocess(root=str(tmp_path / "dist"), batch_size=512) == 2
+
+
+def test_camera_dataset_reads_three_intrinsics_layouts(tmp_path):
+    """``transforms_*.json`` with one focal length, one field of view, or focal length and size per frame."""
+    import json
+
+    from PIL import Image
+
+    pose = np.eye(4).tolist()
+    os.makedirs(tmp_path / "images")
+    for k, (w, h) in enumerate(((40, 30), (20, 10))):
+        Image.fromarray(np.zeros((h, w, 3), np.uint8)).save(tmp_path / "images" / f"image_{k}.png")
+    frames = [{"file_path": f"./images/image_{k}.png", "transform_matrix": pose} for k in range(2)]
+    args = SimpleNamespace(datadir=str(tmp_path), white_bkgd=False)
+
+    def load(meta):
+        with open(tmp_path / "transforms_train.json", "w", encoding="utf-8") as fh:
+            json.dump(meta, fh)
+        return gaussian_dataset_dict["city"]("train", 1.0, args).cameras
+
+    cams = load({"fl_x": 50.0, "fl_y": 60.0, "w": 40, "h": 30, "frames": frames})
+    assert all((c.image_width, c.image_height) == (40, 30) for c in cams)
+    assert math.isclose(cams[0].FoVx, 2 * math.atan(40 / 100.0)) and math.isclose(cams[0].FoVy, 2 * math.atan(30 / 120.0))
+    cams = load({"camera_angle_x": 0.8, "frames": frames})              # size from the first image
+    assert (cams[1].image_width, cams[1].image_height) == (40, 30) and math.isclose(cams[0].FoVx, 0.8, rel_tol=1e-6)
+    multi = [dict(f, fl_x=25.0 * (k + 1), fl_y=25.0 * (k + 1), w=w, h=h) for k, (f, (w, h)) in
+             enumerate(zip(frames, ((40, 30), (20, 10))))]
+    cams = load({"camera_model": "SIMPLE_PINHOLE", "frames": multi})
+    assert (cams[1].image_width, cams[1].image_height) == (20, 10)
+    assert math.isclose(cams[0].FoVx, 2 * math.atan(40 / 50.0)) and math.isclose(cams[1].FoVx, 2 * math.atan(20 / 100.0))
+
+
+def test_ray_dataset_with_one_focal_length_per_frame(tmp_path):
+    import json
+
+    from PIL import Image
+
+    from landmarksystem_b200.components.data.datasets import dataset_dict
+    from landmarksystem_b200.components.data.datasets.ray_utils import get_ray_directions_blender
+
+    os.makedirs(tmp_path / "images")
+    frames = []
+    for k, fl in enumerate((30.0, 45.0, 60.0)):
+        Image.fromarray(np.full((6, 8, 3), 40 * k, np.uint8)).save(tmp_path / "images" / f"image_{k}.png")
+        frames.append({"fl_x": fl, "fl_y": fl, "w": 8, "h": 6, "file_path": f"./images/image_{k}.png",
+                       "transform_matrix": np.eye(4).tolist()})
+    with open(tmp_path / "transforms_train.json", "w", encoding="utf-8") as fh:
+        json.dump({"camera_model": "SIMPLE_PINHOLE", "frames": frames}, fh)
+    args = SimpleNamespace(datadir=str(tmp_path), lb=[-1, -1, -1], ub=[1, 1, 1], white_bkgd=False, camera="normal")
+    ds = dataset_dict["matrixcity"](split="train", downsample=1.0, is_stack=True, args=args)
+    assert ds.all_rays.shape == (3, 48, 6) and tuple(ds.img_wh) == (8, 6)
+    for k, fl in enumerate((30.0, 45.0, 60.0)):                         # identity pose: ray directions = camera directions
+        assert torch.allclose(ds.all_rays[k, :, 3:], get_ray_directions_blender(6, 8, fl).reshape(-1, 3))
+    assert torch.allclose(ds.all_rgbs[2], torch.full((48, 3), 80 / 255.0))
+
+
+def test_colmap_to_transforms_conversion(tmp_path):
+    """A sparse model converted to the transforms layout gives the cameras the COLMAP dataset itself gives."""
+    import json
+
+    from PIL import Image
+
+    from landmarksystem_b200.components.data.datasets.colmap2nerf import convert, main
+
+    cameras, images, points = _toy_model()
+    cl.write_model_binary(str(tmp_path / "sparse" / "0"), cameras, images, points)
+    os.makedirs(tmp_path / "images")
+    for im in images.values():
+        cam = cameras[im.camera_id]
+        Image.fromarray(np.zeros((cam.height, cam.width, 3), np.uint8)).save(tmp_path / "images" / im.name)
+    n_train, n_test = convert(str(tmp_path / "sparse" / "0"), str(tmp_path), holdout=8)
+    assert (n_train, n_test) == (14, 3)
+    with open(tmp_path / "transforms_train.json", encoding="utf-8") as fh:
+        meta = json.load(fh)
+    assert "fl_x" not in meta and meta["frames"][0]["file_path"] == "./images/img_001.png"      # two cameras: per frame
+    args = SimpleNamespace(datadir=str(tmp_path), eval=True, white_bkgd=False)
+    direct = gaussian_dataset_dict["colmap"]("train", 1.0, args).cameras
+    via_json = gaussian_dataset_dict["city"]("train", 1.0, args).cameras
+    assert len(direct) == len(via_json) == 14
+    for a, b in zip(direct, via_json):
+        assert a.image_name == b.image_name and (a.image_width, a.image_height) == (b.image_width, b.image_height)
+        assert torch.allclose(a.camera_center, b.camera_center, atol=1e-4)
+        assert torch.allclose(a.world_view_transform, b.world_view_transform, atol=1e-4)
+        assert abs(a.FoVx - b.FoVx) < 1e-6 and abs(a.FoVy - b.FoVy) < 1e-6
+    # one shared camera -> one focal length for the file; the command-line entry point writes the same files
+    single = {k: cl.ColmapImage(v.id, v.qvec, v.tvec, 1, v.name, v.xys, v.point3D_ids) for k, v in images.items()}
+    cl.write_model_text(str(tmp_path / "one"), {1: cameras[1]}, single, points)
+    main(["--recon_dir", str(tmp_path / "one"), "--output_dir", str(tmp_path / "one_out"), "--holdout", "0"])
+    with open(tmp_path / "one_out" / "transforms_train.json", encoding="utf-8") as fh:
+        meta = json.load(fh)
+    assert meta["fl_x"] == 80.0 and meta["fl_y"] == 82.0 and (meta["w"], meta["h"]) == (64, 48) and len(meta["frames"]) == 17
