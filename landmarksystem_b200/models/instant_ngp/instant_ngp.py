@@ -106,12 +106,40 @@ class _FieldDensity:
                                                   directions.contiguous().float(), z, m.aabb, m._aabb_host,
                                                   int(m.plane_division[0]), int(m.plane_division[1]))
         single = m.mlp_base_grid.num_hash_table == 1
+        if not single:
+            xyzb, inside = window_remap(m.scene_manager, xyzb, inside, int(m.plane_division[0]), int(m.plane_division[1]))
         feat = m.mlp_base_grid(xyzb, out_dtype=torch.bfloat16) if single else m.mlp_base_grid(xyzb)
         h = m.mlp_base_mlp(feat)
         # the step's own forward evaluates the survivors of the culling at the same positions with the same weights:
         # it takes the features and the head's output from here instead of looking them up again
         m._cull_cache = {"feat": feat, "h": h} if (single and m.training) else None
         return torch.exp(h[:, 0].float()) * inside
+
+
+def window_block_ids(scene_manager, bx: torch.Tensor, by: torch.Tensor, nx: int, ny: int, inside: torch.Tensor):
+    """Table index of every sample from its block coordinates ``(bx, by)``.  With the whole scene resident that is the
+    row-major block id; under dynamic loading only a window of ``local_block_partition`` blocks is resident, its tables
+    sit in window order, and samples outside the window are masked (the reference indexes tables by the window-relative
+    ``block_idx`` of ``SceneManager.assign_blockIdx``, benchmarks/nerf/instant_ngp/instant_ngp.py:239-255)."""
+    local = getattr(scene_manager, "local_block_partition", None)
+    if scene_manager is None or local is None or [int(local[0]), int(local[1])] == [int(nx), int(ny)]:
+        return bx * ny + by, inside
+    lx, ly = int(local[0]), int(local[1])
+    rx, ry = bx - scene_manager.relative_block_idx_x, by - scene_manager.relative_block_idx_y
+    within = (rx >= 0) & (rx < lx) & (ry >= 0) & (ry < ly)
+    return torch.where(within, rx * ly + ry, torch.zeros_like(rx)), inside & within
+
+
+def window_remap(scene_manager, xyzb: torch.Tensor, inside: torch.Tensor, nx: int, ny: int):
+    """:func:`window_block_ids` applied to ``[M, 4]`` rows that carry the row-major block id in their last column (the
+    output of the position kernel); rows outside the resident window are zeroed and masked."""
+    local = getattr(scene_manager, "local_block_partition", None)
+    if scene_manager is None or local is None or [int(local[0]), int(local[1])] == [int(nx), int(ny)]:
+        return xyzb, inside
+    block = xyzb[:, 3]
+    bx, by = torch.div(block, ny, rounding_mode="floor"), torch.remainder(block, ny)
+    rel, keep = window_block_ids(scene_manager, bx, by, nx, ny, inside)
+    return torch.cat((xyzb[:, :3] * keep[:, None], rel[:, None]), -1), keep
 
 
 class InstantNGP(BaseNeRF):
@@ -165,8 +193,8 @@ class InstantNGP(BaseNeRF):
         nx, ny = self.plane_division
         u, v = norm[:, 0] * nx, norm[:, 1] * ny
         bx, by = u.floor().clamp(0, nx - 1), v.floor().clamp(0, ny - 1)
+        block, inside = window_block_ids(self.scene_manager, bx, by, nx, ny, inside)
         local = torch.stack((u - bx, v - by, norm[:, 2]), -1) * inside[:, None]
-        block = bx * ny + by
         c = self.config
         if c.get("branch_parallel", False) and c.get("is_train", False):
             mine = block == float(c.mp_rank)
@@ -261,6 +289,9 @@ class InstantNGP(BaseNeRF):
             xyzb, inside = ngp_field.sample_positions(kidx, S, o32, d32, z_vals.reshape(-1).contiguous().float(), self.aabb,
                                                       self._aabb_host, int(self.plane_division[0]), int(self.plane_division[1]))
             feat_pre, h_pre = self._cached_field_rows(idx, S)
+            if self.mlp_base_grid.num_hash_table > 1:
+                xyzb, inside = window_remap(self.scene_manager, xyzb, inside, int(self.plane_division[0]),
+                                            int(self.plane_division[1]))
             if self.mlp_base_grid.num_hash_table == 1:
                 # bf16 rows straight from the lookup kernel: what the head kernel reads and its backward returns
                 feat = self.mlp_base_grid(xyzb, out_dtype=torch.bfloat16, precomputed=feat_pre)

@@ -20,7 +20,7 @@ from ...components.renderers import VolumeRenderer
 from ...components.utils.activation_utils import trunc_exp
 from ...configs import ConfigClass
 from ...ops import composite_render
-from ..instant_ngp.instant_ngp import get_normalized_directions
+from ..instant_ngp.instant_ngp import get_normalized_directions, window_block_ids
 
 
 class NerfactoConfig(ConfigClass):
@@ -164,8 +164,8 @@ class Nerfacto(BaseNeRF):
         nx, ny = self.plane_division
         u, v = norm[:, 0] * nx, norm[:, 1] * ny
         bx, by = u.floor().clamp(0, nx - 1), v.floor().clamp(0, ny - 1)
+        block, inside = window_block_ids(self.scene_manager, bx, by, nx, ny, inside)
         local = torch.stack((u - bx, v - by, norm[:, 2]), -1) * inside[:, None]
-        block = bx * ny + by
         c = self.config
         if c.get("branch_parallel", False) and c.get("is_train", False):
             mine = block == float(c.mp_rank)

@@ -117,6 +117,62 @@ def test_dynamic_loading_window_reuses_resident_blocks(tmp_path):
     assert mgr.get_buffer().local_block_idxes == [1, 3] and mgr.bytes_h2d == 2 * first
 
 
+def _ngp_config(tmp_path, division, **extra):
+    from landmarksystem_b200.models.instant_ngp.instant_ngp import InstantNGPConfig
+
+    mc = InstantNGPConfig(num_levels=4, base_res=8, max_res=64, log2_hashmap_size=12, grid_resolution=16, grid_levels=1,
+                          train_near_far=[0.5, 6.0], appearance_embedding_size=4, render_step_size=0.05, cone_angle=0.0,
+                          max_samples_per_ray=96, background_color="black", runtime="Torch",
+                          render_stratified_sampling=False)
+    cfg = Config(dict(mc))
+    cfg.update(is_train=False, device="cpu", lb=[-2.0, -2.0, -0.5], ub=[2.0, 2.0, 0.5], plane_division=division,
+               branch_parallel=False, ckpt=str(tmp_path / "state_dict.th"), kwargs=str(tmp_path / "kwargs.th"),
+               aabb_norm_range=[0, 1], **extra)
+    return cfg
+
+
+def test_dynamic_loading_of_a_hash_table_model_matches_the_full_model(tmp_path):
+    """InstantNGP with one hash table per block (the reference tests this combination with a [1, 2] window,
+    tests/test_inference_framework/test_single_device/test_torch_inference.py:210-319): a 1x1 window follows the camera
+    over all four blocks; the tables of the window sit in window order, so samples are routed by window-relative ids."""
+    from landmarksystem_b200.models.instant_ngp.instant_ngp import InstantNGP, window_remap
+    from landmarksystem_b200.ops.ngp_field import sample_positions
+
+    torch.manual_seed(0)
+    cfg = _ngp_config(tmp_path, [2, 2])
+    sm = SceneManager(cfg)
+    model = InstantNGP(sm.aabb, "cpu", [0.5, 6.0], scene_manager=sm, config=cfg)
+    for p in model.mlp_base_grid.parameters():
+        p.data.normal_(0, 1.0)                      # a visibly structured random field, different in every block
+    for head in (model.mlp_base_mlp, model.mlp_head):
+        for p in head.parameters():
+            p.data.mul_(4.0)
+    model.save_model(str(tmp_path))
+    full = lm.init_inference(InstantNGP, make_adapter(InstantNGP), _ngp_config(tmp_path, [2, 2]), Config(runtime="Torch"))
+    off = lm.init_inference(InstantNGP, make_adapter(InstantNGP), _ngp_config(tmp_path, [2, 2]),
+                            Config(runtime="Torch", offload_config={"local_plane_split": [1, 1], "plane_split": [2, 2]}))
+    images = []
+    for x, y in ((-1.0, -1.0), (-1.0, 1.0), (1.0, 1.0), (1.0, -1.0)):
+        a, _ = full(_pose(x, y), 4096, 16, 16, 120.0)
+        b, _ = off(_pose(x, y), 4096, 16, 16, 120.0)
+        assert torch.equal(a, b) and a[..., :3].float().std() > 1.0
+        images.append(a)
+    assert not torch.equal(images[0], images[2])    # the blocks really hold different content
+    stats = off.model.model.stats()
+    assert stats["frames"] == 4 and stats["bytes_h2d"] > 0
+
+    # rows of the position kernel's layout (row-major block id in the last column) remapped to the window
+    inner = off.model.model.inner
+    o = torch.tensor([[1.0, -1.0, 3.0]]).repeat(8, 1)
+    d = torch.nn.functional.normalize(torch.tensor([[0.02 * k - 0.07, 0.3 * (k % 3) - 0.3, -1.0] for k in range(8)]), dim=-1)
+    z = torch.linspace(2.6, 3.4, 8 * 4)
+    xyzb, inside = sample_positions(None, 4, o, d, z, inner.aabb, None, 2, 2)
+    got, keep = window_remap(inner.scene_manager, xyzb, inside, 2, 2)
+    pos = (o[:, None] + d[:, None] * z.view(8, 4)[..., None]).reshape(-1, 3)
+    want, want_keep = inner._positions(pos)
+    assert torch.equal(keep, want_keep) and torch.allclose(got, want, atol=1e-6) and keep.any() and not keep.all()
+
+
 def test_user_defined_model_and_adapter_through_init_inference():
     """A model and an inference module written by a user of the framework: no configuration, no checkpoint - the
     reference's engine smoke test (tests/test_inference_framework/test_inference.py:389-393, tests/utils.py:15-31)."""
