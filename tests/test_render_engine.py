@@ -173,6 +173,40 @@ def test_dynamic_loading_of_a_hash_table_model_matches_the_full_model(tmp_path):
     assert torch.equal(keep, want_keep) and torch.allclose(got, want, atol=1e-6) and keep.any() and not keep.all()
 
 
+def test_dynamic_loading_of_nerfacto_matches_the_full_model(tmp_path):
+    """Nerfacto (contracted scene, proposal networks that stay resident, one field table per block) under a 1x1 window."""
+    from landmarksystem_b200.models.nerfacto.nerfacto import Nerfacto, NerfactoConfig
+
+    def config(**extra):
+        mc = NerfactoConfig(num_levels=4, base_res=8, max_res=64, log2_hashmap_size=12, hidden_dim=32, hidden_dim_color=32,
+                            appearance_embedding_size=4, num_proposal_samples_per_ray=(32, 16), num_nerf_samples_per_ray=12,
+                            proposal_net_args_list=[{"hidden_dim": 16, "log2_hashmap_size": 10, "num_levels": 3, "max_res": 32},
+                                                    {"hidden_dim": 16, "log2_hashmap_size": 10, "num_levels": 3, "max_res": 64}],
+                            train_near_far=[0.5, 6.0], background_color="black", runtime="Torch")
+        cfg = Config(dict(mc))
+        cfg.update(is_train=False, device="cpu", lb=[-2.0, -2.0, -0.5], ub=[2.0, 2.0, 0.5], plane_division=[2, 2],
+                   branch_parallel=False, ckpt=str(tmp_path / "state_dict.th"), kwargs=str(tmp_path / "kwargs.th"),
+                   aabb_norm_range=[0, 1], **extra)
+        return cfg
+
+    torch.manual_seed(0)
+    cfg = config()
+    sm = SceneManager(cfg)
+    model = Nerfacto(sm.aabb, "cpu", [0.5, 6.0], scene_manager=sm, config=cfg)
+    for p in model.mlp_base_grid.parameters():
+        p.data.normal_(0, 1.0)
+    model.save_model(str(tmp_path))
+    full = lm.init_inference(Nerfacto, make_adapter(Nerfacto), config(), Config(runtime="Torch"))
+    off = lm.init_inference(Nerfacto, make_adapter(Nerfacto), config(),
+                            Config(runtime="Torch", offload_config={"local_plane_split": [1, 1], "plane_split": [2, 2]}))
+    for x, y in ((-1.0, -1.0), (1.0, 1.0), (-1.0, 1.0)):
+        a, _ = full(_pose(x, y), 4096, 12, 12, 120.0)
+        b, _ = off(_pose(x, y), 4096, 12, 12, 120.0)
+        assert torch.equal(a, b)
+    mgr = off.model.model.buffer_manager
+    assert len(mgr.get_buffer().local_block_idxes) == 1 and off.model.model.stats()["bytes_h2d"] > 0
+
+
 def test_user_defined_model_and_adapter_through_init_inference():
     """A model and an inference module written by a user of the framework: no configuration, no checkpoint - the
     reference's engine smoke test (tests/test_inference_framework/test_inference.py:389-393, tests/utils.py:15-31)."""
