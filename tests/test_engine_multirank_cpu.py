@@ -1,0 +1,159 @@
+"""The rendering engine on several CPU ranks (gloo): data parallel, channel ("tensor") parallel and both together give
+rank 0 the image one process renders - the reference's multi-device render tests
+(tests/test_inference_framework/test_multi_device/test_torch_parallel_inference.py:22-313) without GPUs."""
+import multiprocessing as mp
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gridnerf_config(folder, **extra):
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRFConfig
+    from landmarksystem_b200.utils import Config
+
+    mc = GridNeRFConfig(resMode=[1, 2], n_lamb_sigma=[16], n_lamb_sh=[48], nonlinear_density=True, view_pe=2, fea_pe=2,
+                        train_near_far=[0.5, 6.0], step_ratio=2.0, n_importance=48, sampling_opt=True)
+    cfg = Config(dict(mc))
+    cfg.update(is_train=False, device="cpu", lb=[-2.0, -2.0, -0.5], ub=[2.0, 2.0, 0.5], plane_division=[1, 1],
+               branch_parallel=False, ckpt=os.path.join(folder, "state_dict.th"), kwargs=os.path.join(folder, "kwargs.th"))
+    cfg.update(extra)
+    return cfg
+
+
+def _ngp_config(folder, **extra):
+    from landmarksystem_b200.models.instant_ngp.instant_ngp import InstantNGPConfig
+    from landmarksystem_b200.utils import Config
+
+    mc = InstantNGPConfig(num_levels=4, base_res=8, max_res=64, log2_hashmap_size=12, grid_resolution=16, grid_levels=1,
+                          train_near_far=[0.5, 6.0], appearance_embedding_size=4, render_step_size=0.05, cone_angle=0.0,
+                          max_samples_per_ray=96, background_color="black", runtime="Torch",
+                          render_stratified_sampling=False)
+    cfg = Config(dict(mc))
+    cfg.update(is_train=False, device="cpu", lb=[-2.0, -2.0, -0.5], ub=[2.0, 2.0, 0.5], plane_division=[1, 1],
+               branch_parallel=False, ckpt=os.path.join(folder, "state_dict.th"), kwargs=os.path.join(folder, "kwargs.th"),
+               aabb_norm_range=[0, 1], **extra)
+    return cfg
+
+
+def _pose():
+    from landmarksystem_b200.synthetic import look_at
+
+    return look_at(torch.tensor([-0.9, 0.8, 3.0]), torch.tensor([-0.85, 0.8, 0.0]), up=(0.0, 1.0, 0.0))
+
+
+def _save_models(folder):
+    from landmarksystem_b200.components.scene import SceneManager
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF
+    from landmarksystem_b200.models.instant_ngp.instant_ngp import InstantNGP
+
+    torch.manual_seed(0)
+    os.makedirs(os.path.join(folder, "grid"))
+    os.makedirs(os.path.join(folder, "ngp"))
+    cfg = _gridnerf_config(os.path.join(folder, "grid"))
+    sm = SceneManager(cfg)
+    grid = GridNeRF(sm.aabb, [32, 32, 16], "cpu", near_far=[0.5, 6.0], scene_manager=sm, config=cfg)
+    for p in grid.density_encoding.parameters():
+        p.data.abs_().mul_(3.0)
+    grid.save_model(os.path.join(folder, "grid"))
+    os.makedirs(os.path.join(folder, "grid22"))
+    cfg = _gridnerf_config(os.path.join(folder, "grid22"), plane_division=[2, 2])
+    sm = SceneManager(cfg)
+    blocks = GridNeRF(sm.aabb, [64, 64, 16], "cpu", near_far=[0.5, 6.0], scene_manager=sm, config=cfg)
+    for p in blocks.density_encoding.parameters():
+        p.data.abs_().mul_(3.0)
+    blocks.save_model(os.path.join(folder, "grid22"))
+    cfg = _ngp_config(os.path.join(folder, "ngp"))
+    sm = SceneManager(cfg)
+    ngp = InstantNGP(sm.aabb, "cpu", [0.5, 6.0], scene_manager=sm, config=cfg)
+    for p in ngp.mlp_base_grid.parameters():
+        p.data.normal_(0, 1.0)
+    ngp.save_model(os.path.join(folder, "ngp"))
+
+
+def _render(kind, folder, parallel):
+    import landmarksystem_b200 as lm
+    from landmarksystem_b200.models.gridnerf.gridnerf import GridNeRF
+    from landmarksystem_b200.models.instant_ngp.instant_ngp import InstantNGP
+    from landmarksystem_b200.render.adapters import make_adapter
+    from landmarksystem_b200.utils import Config
+
+    if kind == "grid":
+        cls, cfg = GridNeRF, _gridnerf_config(os.path.join(folder, "grid"))
+    elif kind == "grid22":
+        cls, cfg = GridNeRF, _gridnerf_config(os.path.join(folder, "grid22"), plane_division=[2, 2])
+    else:
+        cls, cfg = InstantNGP, _ngp_config(os.path.join(folder, "ngp"))
+    inference = Config(runtime="Torch", kernel_fusion=False)
+    parallel = dict(parallel) if parallel is not None else None
+    offload = parallel.pop("offload", None) if parallel else None
+    if parallel:
+        inference.parallel_config = Config(parallel)
+    if offload is not None:
+        inference.offload_config = Config(offload)
+    engine = lm.init_inference(cls, make_adapter(cls), cfg, inference)
+    rank = int(os.environ.get("RANK", 0))
+    out = engine(_pose(), 4096, 18, 24, 30.0) if rank == 0 else engine()
+    return out[0].clone() if rank == 0 else None
+
+
+def _worker(rank, world, port, folder, kind, parallel, queue):
+    import traceback
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    try:
+        image = _render(kind, folder, parallel)
+        queue.put((rank, None, None if image is None else image.numpy()))
+    except Exception:
+        queue.put((rank, traceback.format_exc(), None))
+
+
+def _run(world, folder, kind, parallel):
+    ctx = mp.get_context("spawn")
+    queue = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, folder, kind, parallel, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get() for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    for r in results:
+        assert r[1] is None, r[1]
+    return torch.from_numpy([r for r in results if r[0] == 0][0][2])
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    folder = str(tmp_path_factory.mktemp("engine_models"))
+    _save_models(folder)
+    return folder
+
+
+@pytest.mark.parametrize("kind,world,parallel", [
+    ("grid", 2, {"tp_size": 1}),                     # data parallel: the rays of the frame dealt over two ranks
+    ("grid", 2, {"tp_size": 2}),                     # channel parallel: every rank holds half of the feature channels
+    ("grid", 4, {"tp_size": 2}),                     # two channel-parallel groups, data parallel across them
+    ("ngp", 2, {"tp_size": 1}),
+    # dynamic loading together with data parallelism: the ranks share the host reads of a new window (`use_nccl`)
+    ("grid22", 2, {"tp_size": 1, "offload": {"local_plane_split": [2, 1], "plane_split": [2, 2], "use_nccl": True}}),
+])
+def test_engine_on_cpu_ranks_equals_one_process(models, kind, world, parallel):
+    # a window shows only its own blocks, so the one-process image of that case is rendered through the same window
+    alone = {"offload": dict(parallel["offload"], use_nccl=False)} if "offload" in parallel else None
+    single = _render(kind, models, alone)
+    assert single.shape == (18, 24, 4) and single[..., :3].float().std() > 1.0
+    multi = _run(world, models, kind, parallel)
+    assert (multi.float() - single.float()).abs().max() <= 1.0          # 8-bit rounding of sums taken in another order
