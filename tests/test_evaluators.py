@@ -9,7 +9,9 @@ from landmarksystem_b200.configs import BaseConfig
 ROOT = os.path.join(os.path.dirname(__file__), "..", "landmarksystem_b200", "models")
 CASES = [("gridnerf", "gridnerf_trainer", "GridNeRFTrainer", "gridnerf_evaluator", "GridNeRFEvaluator", "synthetic_tiny.py", {"nSamples": "24"}),
          ("instant_ngp", "instant_ngp_trainer", "NGPTrainer", "instant_ngp_evaluator", "NGPEvaluator", "synthetic_tiny.py", {}),
+         ("nerfacto", "nerfacto_trainer", "NerfactoTrainer", "nerfacto_evaluator", "NerfactoEvaluator", "synthetic_tiny.py", {}),
          ("origin_gs", "gs_trainer", "Gaussian3DTrainer", "gs_evaluator", "Gaussian3DEvaluator", "synthetic_train.py", {"init_points_num": "60"}),
+         ("scaffold_gs", "gs_trainer", "ScaffoldGSTrainer", "gs_evaluator", "ScaffoldGSEvaluator", "synthetic_train.py", {"init_points_num": "60"}),
          ("octree_gs", "gs_trainer", "OctreeGSTrainer", "gs_evaluator", "OctreeGSEvaluator", "synthetic_train.py", {"init_points_num": "60"})]
 
 
