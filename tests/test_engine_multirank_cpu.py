@@ -157,3 +157,54 @@ def test_engine_on_cpu_ranks_equals_one_process(models, kind, world, parallel):
     assert single.shape == (18, 24, 4) and single[..., :3].float().std() > 1.0
     multi = _run(world, models, kind, parallel)
     assert (multi.float() - single.float()).abs().max() <= 1.0          # 8-bit rounding of sums taken in another order
+
+
+def _evaluate(conf, over, ckpt):
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.instant_ngp.instant_ngp_evaluator import NGPEvaluator
+
+    cfg = BaseConfig.from_file(conf, dict(over))
+    cfg.is_train = False
+    cfg.ckpt = ckpt
+    cfg.render_stratified_sampling = False          # jitter-free renders: the split and the whole frame see the same samples
+    return NGPEvaluator(cfg).eval()
+
+
+def _eval_worker(rank, world, port, conf, over, ckpt, queue):
+    import traceback
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    try:
+        queue.put((rank, None, _evaluate(conf, over, ckpt)))
+    except Exception:
+        queue.put((rank, traceback.format_exc(), None))
+
+
+def test_evaluator_splits_the_pixels_over_cpu_ranks(tmp_path):
+    """The evaluator under two ranks (every rank renders half of each test image, reference:
+    benchmarks/nerf/instant_ngp/instant_ngp_evaluator.py with a `*_ddp_render` configuration) reports the PSNR of one."""
+    from landmarksystem_b200.configs import BaseConfig
+    from landmarksystem_b200.models.instant_ngp.instant_ngp_trainer import NGPTrainer
+
+    conf = os.path.join(ROOT, "landmarksystem_b200", "models", "instant_ngp", "confs", "synthetic_tiny.py")
+    over = {"basedir": str(tmp_path), "device": "cpu", "n_iters": "3", "datadir": "ring:3:12x12:14:3", "batch_size": "64",
+            "progress_refresh_rate": "100", "N_vis": "-1"}
+    trainer = NGPTrainer(BaseConfig.from_file(conf, dict(over)))
+    trainer.train()
+    ckpt = os.path.join(trainer.logfolder, "state_dict.th")
+    alone = _evaluate(conf, over, ckpt)
+    ctx = mp.get_context("spawn")
+    queue = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_eval_worker, args=(r, 2, port, conf, over, ckpt, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [queue.get() for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+    for r in results:
+        assert r[1] is None, r[1]
+    for r in results:
+        assert abs(r[2] - alone) < 1e-3, (r[2], alone)
