@@ -187,3 +187,26 @@ def test_gpu_kernel_path_trains_as_well_as_the_plain_path(tmp_path):
     assert fast._graph_state["graph"] is not None
     assert psnr["plain"] > 15.0, psnr
     assert psnr["kernel"] > psnr["plain"] - 1.0, psnr
+
+
+def test_cpu_training_with_every_optional_branch(tmp_path):
+    """Appearance embedding, NeRF branch (residual), distortion loss, grid upsampling, alpha-mask rebuild, L1 / TV / ortho
+    regularisers, white background and the sampling optimisation in one short run (reference switches:
+    benchmarks/nerf/gridnerf/gridnerf.py:33-134, gridnerf_trainer.py:220-330)."""
+    import numpy as np
+
+    cfg = BaseConfig.from_file(CONF, {"basedir": str(tmp_path), "device": "cpu", "n_iters": "12", "batch_size": "128",
+                                      "datadir": "ring:4:16x16:20:3", "progress_refresh_rate": "4", "N_vis": "1",
+                                      "vis_every": "6", "nSamples": "24"})
+    cfg.update(encode_app=True, appearance_embedding_size=4, add_nerf=4, nerf_D=3, nerf_W=32, nerf_n_importance=8,
+               residnerf=True, add_distort=2, upsamp_list=[6], update_AlphaMask_list=[8], L1_weight_inital=8e-5,
+               L1_weight_rest=4e-5, TV_weight_density=0.1, TV_weight_app=0.01, Ortho_weight=0.01, white_bkgd=True,
+               sampling_opt=True)
+    trainer = GridNeRFTrainer(cfg)
+    start = [int(v) for v in trainer.module.gridSize]
+    psnrs = trainer.train()
+    assert len(psnrs) == 3 and all(np.isfinite(psnrs))
+    assert [int(v) for v in trainer.module.gridSize] != start              # the grid was upsampled at iteration 6
+    assert trainer.module.alphaMask is not None                            # rebuilt at iteration 8
+    assert np.isfinite(trainer.eval())
+    assert any(f.endswith(".png") for f in os.listdir(os.path.join(trainer.logfolder, "imgs_vis")))
