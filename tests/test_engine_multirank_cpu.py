@@ -208,3 +208,85 @@ def test_evaluator_splits_the_pixels_over_cpu_ranks(tmp_path):
         assert r[1] is None, r[1]
     for r in results:
         assert abs(r[2] - alone) < 1e-3, (r[2], alone)
+
+
+def _train_worker(rank, world, port, family, over, mode, queue):
+    import importlib
+    import traceback
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    try:
+        from landmarksystem_b200.configs import BaseConfig
+
+        name = "instant_ngp_trainer" if family == "instant_ngp" else "nerfacto_trainer"
+        mod = importlib.import_module(f"landmarksystem_b200.models.{family}.{name}")
+        trainer_cls = mod.NGPTrainer if family == "instant_ngp" else mod.NerfactoTrainer
+        conf = os.path.join(ROOT, "landmarksystem_b200", "models", family, "confs", "synthetic_tiny.py")
+        cfg = BaseConfig.from_file(conf, dict(over))
+        if mode == "branch":
+            cfg.branch_parallel, cfg.plane_division = True, [2, 1]
+        else:
+            cfg.DDP = True
+        trainer = trainer_cls(cfg)
+        trainer.train()
+        first = next(iter(trainer.module.mlp_head.parameters())).detach().clone()
+        queue.put((rank, None, (trainer.eval(), trainer.logfolder, first.numpy())))
+    except Exception:
+        queue.put((rank, traceback.format_exc(), None))
+
+
+def _spawn_training(family, over, mode):
+    ctx = mp.get_context("spawn")
+    queue = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_train_worker, args=(r, 2, port, family, over, mode, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [queue.get() for _ in range(2)]
+    for p in procs:
+        p.join(timeout=180)
+    for r in results:
+        assert r[1] is None, r[1]
+    return {r[0]: r[2] for r in results}
+
+
+@pytest.mark.parametrize("family", ["instant_ngp", "nerfacto"])
+def test_hash_models_train_in_parallel_on_cpu_ranks(family, tmp_path):
+    """Spatial-block ("branch") parallel and data parallel training of the hash-grid models on two ranks (reference:
+    instant_ngp_trainer.py:95-125, confs `*_BranchParallel.py` / `*_ddp*.py`).  Branch parallel: one table per rank, the
+    merged checkpoint evaluates in ONE process to the PSNR the two ranks measured together.  Data parallel: the
+    replicas hold identical weights after training."""
+    import importlib
+
+    import numpy as np
+
+    from landmarksystem_b200.configs import BaseConfig
+
+    over = {"basedir": str(tmp_path), "device": "cpu", "n_iters": "4", "datadir": "ring:4:12x12:14:3", "batch_size": "64",
+            "progress_refresh_rate": "2", "N_vis": "-1"}
+    if family == "instant_ngp":
+        over["render_stratified_sampling"] = "False"
+    else:
+        over["use_proposal_weight_anneal"] = "False"      # the annealing exponent is trainer state, not checkpoint content
+    out = _spawn_training(family, over, "branch")
+    psnr, folder, _ = out[0]
+    assert abs(out[1][0] - psnr) < 1e-6
+    files = set(os.listdir(folder))
+    assert {"state_dict-sub0.th", "state_dict-sub1.th", "state_dict-merged.th", "kwargs-merged.th"} <= files
+    merged = torch.load(os.path.join(folder, "state_dict-merged.th"), weights_only=False)
+    assert {"mlp_base_grid.tcnn_encoding.0.params", "mlp_base_grid.tcnn_encoding.1.params"} <= set(merged)
+
+    name = "instant_ngp_evaluator" if family == "instant_ngp" else "nerfacto_evaluator"
+    ev_mod = importlib.import_module(f"landmarksystem_b200.models.{family}.{name}")
+    ev_cls = ev_mod.NGPEvaluator if family == "instant_ngp" else ev_mod.NerfactoEvaluator
+    conf = os.path.join(ROOT, "landmarksystem_b200", "models", family, "confs", "synthetic_tiny.py")
+    cfg = BaseConfig.from_file(conf, dict(over))
+    cfg.update(is_train=False, plane_division=[2, 1], ckpt=os.path.join(folder, "state_dict-merged.th"),
+               kwargs=os.path.join(folder, "kwargs-merged.th"), expname="merged_eval")
+    alone = ev_cls(cfg).eval()
+    assert abs(alone - psnr) < 1e-3, (alone, psnr)
+
+    out = _spawn_training(family, dict(over, expname="ddp_run"), "ddp")
+    assert np.allclose(out[0][2], out[1][2], atol=1e-7) and abs(out[0][0] - out[1][0]) < 1e-6
