@@ -437,7 +437,7 @@ class GridNeRFTrainer(NeRFTrainer):
             if with_optimizer:
                 self.save_optimizer()
             self.barrier()
-            if final and cfg.rank == 0 and cfg.branch_parallel:
+            if final and cfg.rank == 0:         # spatial blocks are stacked, channel slices concatenated
                 n = cfg.model_parallel_degree
                 merged, kwargs = self.module.merge_ckpts(
                     [f"{self.logfolder}/state_dict-sub{r}.th" for r in range(n)],
