@@ -101,11 +101,36 @@ class RayModelEvaluator(NeRFEvaluator):
     def build_from_kwargs(self, kwargs):
         return self.model_cls(**kwargs)
 
+    def resolve_auto_ckpt(self):
+        """``ckpt="auto"``: the files of the run with this ``expname`` (reference: gridnerf_evaluator.py:53-75).  A run
+        without model parallelism wrote ``state_dict.th``; a model-parallel run wrote one file per rank and a merged
+        one - ``ckpt_type="full"`` takes the merged file (every rank then slices what it needs), ``"sub"`` the
+        file of this rank's part, which only a process that renders that part alone can use."""
+        cfg = self.config
+        if cfg.get("ckpt") != "auto":
+            return
+        if cfg.get("branch_parallel", False) or cfg.get("channel_parallel", False):
+            kind = cfg.get("ckpt_type", "full")
+            if kind == "full":
+                suffix = "-merged"
+            elif kind == "sub":
+                assert int(cfg.world_size) == 1 or not cfg.get("channel_parallel", False), \
+                    "ckpt_type='sub' names one rank's slice; channel-parallel rendering slices the merged file itself"
+                cfg.part = int(cfg.get("part", cfg.rank) or 0)
+                suffix = f"-sub{cfg.part}"
+            else:
+                raise ValueError(f"ckpt_type '{kind}' is not known (full, sub)")
+        else:
+            suffix = ""
+        cfg.ckpt = f"{self.logfolder}/state_dict{suffix}.th"
+        cfg.kwargs = f"{self.logfolder}/kwargs{suffix}.th"
+
     def create_model(self):
         from ..convertor import ComponentConvertorFactory
 
         cfg = self.config
         self.scene_mgr.to(cfg.device)
+        self.resolve_auto_ckpt()
         kwargs_fp = cfg.get("kwargs") or cfg.ckpt.replace("state_dict", "kwargs")
         kwargs = self.model_cls.get_kwargs_from_ckpt(kwargs_fp, cfg.device)
         kwargs.update(device=cfg.device, scene_manager=self.scene_mgr, config=cfg)

@@ -287,6 +287,13 @@ def test_hash_models_train_in_parallel_on_cpu_ranks(family, tmp_path):
                kwargs=os.path.join(folder, "kwargs-merged.th"), expname="merged_eval")
     alone = ev_cls(cfg).eval()
     assert abs(alone - psnr) < 1e-3, (alone, psnr)
+    # ``ckpt="auto"`` finds the merged files of the run by its experiment name
+    auto = BaseConfig.from_file(conf, dict(over))
+    auto.update(is_train=False, plane_division=[2, 1], branch_parallel=True, ckpt="auto", ckpt_type="full")
+    evaluator = ev_cls.__new__(ev_cls)
+    evaluator.config, evaluator.logfolder = auto, folder
+    evaluator.resolve_auto_ckpt()
+    assert auto.ckpt == os.path.join(folder, "state_dict-merged.th") and auto.kwargs == os.path.join(folder, "kwargs-merged.th")
 
     out = _spawn_training(family, dict(over, expname="ddp_run"), "ddp")
     assert np.allclose(out[0][2], out[1][2], atol=1e-7) and abs(out[0][0] - out[1][0]) < 1e-6

@@ -33,8 +33,12 @@ def test_train_then_evaluate_cpu(family, tmod, tcls, emod, ecls, conf, extra, tm
     cfg.is_train = False
     cfg.ckpt = (os.path.join(trainer.logfolder, "point_cloud", "iteration_3", "point_cloud.ply") if gaussian
                 else os.path.join(trainer.logfolder, "state_dict.th"))
+    if family == "instant_ngp":                  # "auto": the files of the run with this experiment name
+        cfg.ckpt = "auto"
     ev = getattr(importlib.import_module(f"landmarksystem_b200.models.{family}.{emod}"), ecls)(cfg)
     assert np.isfinite(ev.eval())
+    if family == "instant_ngp":
+        assert ev.config.ckpt == os.path.join(trainer.logfolder, "state_dict.th")
     assert any(f.endswith(".png") for f in os.listdir(ev.save_folder))
     if family == "gridnerf":                     # the "path" split: a fly-around without ground truth
         cfg.render_spherical, cfg.render_nframes, cfg.render_px = True, 3, 9
