@@ -121,6 +121,16 @@ class TensorVMEncoding(VolumeEncoding):
                 if name in state and tuple(state[name].shape) != tuple(param.shape):
                     param.data = torch.empty_like(state[name], device=param.device)  # adopt checkpoint shape
 
+    def to_reference_layout(self, name: str, tensor: torch.Tensor) -> torch.Tensor:
+        """A checkpoint tensor in the layout the block splitter expects: planes exported channels-last
+        (``[1, B, H, W, C]``, the ``*_channel_last.th`` files) come back as ``[1, C, B, H, W]`` (a view)."""
+        if name.startswith("plane_coef.") and tensor.dim() == 5:
+            k = int(name.split(".")[1])
+            C = self.plane_coef[k].shape[-1] if k < len(self.plane_coef) and self.plane_coef[k].dim() == 4 else None
+            if C is not None and tensor.shape[-1] == C and tensor.shape[1] != C:
+                return tensor.permute(0, 4, 1, 2, 3)
+        return tensor
+
     @staticmethod
     def block_to_internal(name: str, piece: torch.Tensor) -> torch.Tensor:
         """One-block slice in checkpoint layout -> the in-memory (channels-last) layout, for dynamic loading."""

@@ -74,7 +74,7 @@ class OffloadModule(nn.Module):
         if config.get("channel_last", False) and hasattr(self.inner, "channel_last"):
             self.inner.channel_last()
         dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, None: None, "fp32": None}[config.get("dtype")]
-        merged = _find_state_dict(merged_state_dict)
+        merged = {k: self._to_reference(k, v) for k, v in _find_state_dict(merged_state_dict).items()}
         self.merge_config = self.inner.get_merge_config()
         self.streamed = mergeable_keys(self.merge_config, merged)
         blocks = create_blocks(self.merge_config, merged, plane_split, to_internal=self._to_internal, dtype=dtype,
@@ -96,6 +96,15 @@ class OffloadModule(nn.Module):
         mod, tail = _owner(self.inner, key)
         fn = getattr(mod, "block_to_internal", None)
         return fn(".".join(tail), piece) if fn is not None else piece
+
+    def _to_reference(self, key: str, tensor: torch.Tensor) -> torch.Tensor:
+        """Checkpoint variants (channels-last planes) brought to the layout the merge configuration describes."""
+        try:
+            mod, tail = _owner(self.inner, key)
+        except (AttributeError, IndexError, KeyError):
+            return tensor
+        fn = getattr(mod, "to_reference_layout", None)
+        return fn(".".join(tail), tensor) if fn is not None and torch.is_tensor(tensor) else tensor
 
     def _targets(self):
         """``{buffer key: [(module, attribute name or list index, slot or None)]}`` the buffer tensors feed."""

@@ -106,6 +106,35 @@ def test_dynamic_loading_matches_full_model_cpu(tmp_path):
     assert mgr.bytes_h2d > 0 and len(mgr.get_buffer().local_block_idxes) == 1
 
 
+def test_channel_last_checkpoint_renders_like_the_original(tmp_path):
+    """``transform_gridnerf_model_to_channel_last`` writes ``*_channel_last.th`` with planes stored ``[1, B, H, W, C]``
+    (reference: landmark/render/util/utils.py:6-19, tests/test_module/test_util/test_channel_last_transform.py); the
+    engine renders the same image from either file, resident or under dynamic loading with ``channel_last=True``."""
+    from landmarksystem_b200.render.utils import transform_gridnerf_model_to_channel_last
+
+    _save_random_model(tmp_path, [2, 2])
+    original = torch.load(str(tmp_path / "state_dict.th"), weights_only=False)
+    out = transform_gridnerf_model_to_channel_last(str(tmp_path / "state_dict.th"))
+    assert out.endswith("state_dict_channel_last.th")
+    moved = torch.load(out, weights_only=False)
+    key = "density_encoding.plane_coef.0"
+    assert moved[key].shape == tuple(original[key].shape[i] for i in (0, 2, 3, 4, 1))
+    assert torch.equal(moved[key].permute(0, 4, 1, 2, 3), original[key])
+    assert torch.equal(moved["density_encoding.line_coef.0"], original["density_encoding.line_coef.0"])
+
+    def engine(ckpt, **inference):
+        cfg = _model_config(tmp_path, [2, 2], "cpu")
+        cfg.ckpt = ckpt
+        return lm.init_inference(GridNeRF, make_adapter(GridNeRF), cfg, Config(runtime="Torch", kernel_fusion=False, **inference))
+
+    want, _ = engine(str(tmp_path / "state_dict.th"))(_pose(-0.9, 0.8), 4096, 16, 16, 60.0)
+    got, _ = engine(out)(_pose(-0.9, 0.8), 4096, 16, 16, 60.0)
+    assert torch.equal(got, want) and want[..., :3].float().std() > 1.0
+    window = {"local_plane_split": [2, 2], "plane_split": [2, 2], "channel_last": True}
+    streamed, _ = engine(out, offload_config=window)(_pose(-0.9, 0.8), 4096, 16, 16, 60.0)
+    assert (streamed.float() - want.float()).abs().max() <= 1.0
+
+
 def test_dynamic_loading_window_reuses_resident_blocks(tmp_path):
     _save_random_model(tmp_path, [2, 2])
     off = _engine(tmp_path, [2, 2], "cpu", offload_config={"local_plane_split": [2, 1], "plane_split": [2, 2]})
