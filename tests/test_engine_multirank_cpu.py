@@ -147,6 +147,7 @@ def models(tmp_path_factory):
     ("grid", 2, {"tp_size": 2}),                     # channel parallel: every rank holds half of the feature channels
     ("grid", 4, {"tp_size": 2}),                     # two channel-parallel groups, data parallel across them
     ("ngp", 2, {"tp_size": 1}),
+    ("grid22", 2, {"tp_size": 2}),                   # a block-stacked (branch-parallel) checkpoint rendered channel parallel
     # dynamic loading together with data parallelism: the ranks share the host reads of a new window (`use_nccl`)
     ("grid22", 2, {"tp_size": 1, "offload": {"local_plane_split": [2, 1], "plane_split": [2, 2], "use_nccl": True}}),
 ])
