@@ -67,10 +67,17 @@ class Camera:
 
     @property
     def c2w(self) -> Optional[torch.Tensor]:
-        """Camera-to-world matrix ``[4, 4]`` in COLMAP axes (x right, y down, z forward)."""
+        """Camera-to-world matrix ``[4, 4]`` in COLMAP axes (x right, y down, z forward).  Assignable: adapters of the
+        reference clear it (``cam.c2w = None``) before a camera travels to other ranks."""
+        if "_c2w" in self.__dict__:
+            return self.__dict__["_c2w"]
         if self.world_view_transform is None:
             return None
         return torch.linalg.inv(self.world_view_transform.transpose(0, 1))
+
+    @c2w.setter
+    def c2w(self, value) -> None:
+        self.__dict__["_c2w"] = value
 
     @property
     def tanfovx(self) -> float:

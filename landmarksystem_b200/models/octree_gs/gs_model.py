@@ -94,7 +94,7 @@ class OctreeGS(ScaffoldGS):
         enc = self.gaussian_encoding
         app = None
         if self.embedding_appearance is not None:
-            app = self.embedding_appearance(torch.tensor(int(cam.uid), device=self.device))
+            app = self.embedding_appearance(torch.tensor(self._appearance_index(cam), device=self.device))
         prog = enc._prog_ratio if enc.dist2level == "progressive" else None
         return self.anchor_decoder(cam.camera_center, enc.get_anchor, enc._anchor_feat, enc._offset, enc.get_scaling,
                                    visible, level=enc.get_level, prog_ratio=prog, transition_mask=enc.transition_mask,

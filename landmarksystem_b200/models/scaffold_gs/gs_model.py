@@ -186,13 +186,25 @@ class ScaffoldGS(BaseGaussian):
         enc = self.gaussian_encoding
         app = None
         if self.embedding_appearance is not None:
-            app = self.embedding_appearance(torch.tensor(int(cam.uid), device=self.device))
+            app = self.embedding_appearance(torch.tensor(self._appearance_index(cam), device=self.device))
         return self.anchor_decoder(cam.camera_center, enc.get_anchor, enc._anchor_feat, enc._offset, enc.get_scaling,
                                    visible, appearance_code=app)
 
-    def forward(self, viewpoint_camera, scaling_modifier: float = 1.0, retain_grad: bool = False):
+    def _appearance_index(self, cam) -> int:
+        """Row of the appearance embedding for this view: the camera's own while training or when no code was asked
+        for, else the requested ``ape_code`` (reference: octree_gs/gs_model.py:254-260)."""
+        code = int(getattr(self, "_ape_code", -1))
+        return int(cam.uid) if (self.training or code < 0) else code
+
+    def forward(self, viewpoint_camera, scaling_modifier: float = 1.0, retain_grad: bool = False,
+                render_exclude_filter=None, ape_code: int = -1):
+        """``render_exclude_filter``: optional ``[n_anchors]`` mask ANDed with the visibility of the anchors;
+        ``ape_code``: appearance-embedding row to render with outside training (``-1``: the camera's own)."""
         cam = viewpoint_camera.to(self.device)
+        self._ape_code = ape_code
         visible = self._view_mask(cam)
+        if render_exclude_filter is not None:
+            visible = visible & render_exclude_filter.to(visible.device)
         xyz, color, opacity, scaling, rot, neural_opacity, mask = self._decode(cam, visible)
         screenspace = torch.zeros_like(xyz, requires_grad=True) + 0
         if self.training:

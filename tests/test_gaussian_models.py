@@ -274,6 +274,19 @@ def test_scaffold_model_helpers_cov_prefilter_and_mlp_file(tmp_path):
     by_cov = model.prefilter_voxel(cam, anchor_mask=mask)
     cfg.compute_cov3D_python = False
     assert by_scales.any() and torch.equal(by_scales, by_cov)
+    # the reference's extra forward arguments: an anchor filter and an explicit appearance code (eval only)
+    model.eval()
+    with torch.no_grad():
+        base = model(cam)
+        nothing = model(cam, 1.0, False, torch.zeros_like(mask), -1)
+        assert torch.allclose(nothing, model.background[:, None, None].expand_as(nothing)) and not torch.allclose(base, nothing)
+        if model.embedding_appearance is not None and model.embedding_appearance.num_embeddings > 1:
+            model.embedding_appearance.weight.data.normal_(0, 2.0)
+            own, other = model(cam, ape_code=-1), model(cam, ape_code=(int(cam.uid) + 1) % model.embedding_appearance.num_embeddings)
+            assert not torch.allclose(own, other) and torch.allclose(own, model(cam, ape_code=int(cam.uid)))
+    model.train()
+    cam.c2w = None                                                  # adapters of the reference clear it before pickling
+    assert cam.c2w is None
     assert len(model.plot_levels()) == model.gaussian_encoding.levels
     code = model.get_appearance_code(torch.tensor(0)) if model.embedding_appearance is not None else None
     assert code is None or code.shape == (cfg.appearance_dim,)
