@@ -55,8 +55,21 @@ def focal2fov(focal, pixels):
     return 2 * math.atan(pixels / (2 * focal))
 
 
-def pose_rotate_translate(c2w, rotation_deg, translation):
-    """Apply a global Euler XYZ rotation (degrees) and translation to a camera-to-world matrix."""
+def pose_rotate_translate(c2w, rotation_deg=None, translation=None, *reference_tail, **reference_kw):
+    """Apply a global Euler XYZ rotation (degrees) and translation to a camera-to-world matrix:
+    ``pose_rotate_translate(c2w, [rx, ry, rz], [tx, ty, tz]) -> c2w'`` with ``c2w' = [R | t] c2w``.
+
+    The reference's calling convention is accepted as well (graphics_utils.py:88-123):
+    ``pose_rotate_translate(world_to_view, rot_x, rot_y, rot_z, trans) -> world_to_view'`` - the same motion applied to
+    the inverse of the given matrix, result inverted back."""
+    if reference_tail or reference_kw or not hasattr(rotation_deg, "__len__"):
+        names = ("rot_x", "rot_y", "rot_z", "trans")
+        positional = [v for v in (rotation_deg, translation) + tuple(reference_tail) if v is not None]
+        given = dict(zip(names, positional))
+        given.update(reference_kw)
+        moved = pose_rotate_translate(np.linalg.inv(np.asarray(c2w, dtype=np.float64)),
+                                      [given["rot_x"], given["rot_y"], given["rot_z"]], given["trans"])
+        return np.linalg.inv(moved.astype(np.float64)).astype(np.float32)
     rx, ry, rz = [math.radians(float(a)) for a in rotation_deg]
     Rx = np.array([[1, 0, 0], [0, math.cos(rx), -math.sin(rx)], [0, math.sin(rx), math.cos(rx)]])
     Ry = np.array([[math.cos(ry), 0, math.sin(ry)], [0, 1, 0], [-math.sin(ry), 0, math.cos(ry)]])

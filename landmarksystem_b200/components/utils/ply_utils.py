@@ -105,9 +105,29 @@ def storePly(path: str, xyz: np.ndarray, rgb: np.ndarray) -> None:
                      "blue": rgb[:, 2].astype(np.uint8)})
 
 
-def init_ply(datadir: str, aabb: Sequence[Sequence[float]], n_points: int = 100_000, seed: int = 0) -> str:
+def init_ply(datadir: str, aabb: Sequence[Sequence[float]], n_points=100_000, seed: int = 0, init_points_num=None):
     """Random cloud on the ground plane (``z = lb_z``) of the AABB, written to
-    ``datadir/points3d_init.ply`` and returned as a path (the reference's fallback when no SfM cloud exists)."""
+    ``datadir/points3d_init.ply`` and returned as a path (the reference's fallback when no SfM cloud exists).
+
+    The reference's form ``init_ply(folder, aabb, init_type, init_points_num)`` (ply_utils.py:17-50) is accepted as
+    well and returns the cloud itself: ``init_type="ply"`` draws the random cloud, ``"colmap"`` reads
+    ``folder/sparse/0/points3D.{ply,bin,txt}`` (converting to ``.ply`` on first use)."""
+    if isinstance(n_points, str):
+        kind, count = n_points, int(init_points_num if init_points_num is not None else (seed or 100_000))
+        if kind == "colmap":
+            from ..data.datasets.colmap_loader import read_points3D_binary, read_points3D_text
+
+            base = os.path.join(datadir, "sparse", "0")
+            ply = os.path.join(base, "points3D.ply")
+            if not os.path.exists(ply):
+                try:
+                    xyz, rgb, _ = read_points3D_binary(os.path.join(base, "points3D.bin"))
+                except FileNotFoundError:
+                    xyz, rgb, _ = read_points3D_text(os.path.join(base, "points3D.txt"))
+                storePly(ply, xyz, rgb)
+            return fetchPly(ply)
+        assert kind == "ply", f"init_type '{kind}' is not known (ply, colmap)"
+        return fetchPly(init_ply(datadir, aabb, count))
     path = os.path.join(datadir, "points3d_init.ply")
     rng = np.random.default_rng(seed)
     lb, ub = np.asarray(aabb[0], dtype=np.float32), np.asarray(aabb[1], dtype=np.float32)
@@ -118,9 +138,29 @@ def init_ply(datadir: str, aabb: Sequence[Sequence[float]], n_points: int = 100_
     return path
 
 
-def get_pcd(config, aabb=None) -> BasicPointCloud:
-    """Initial cloud: ``config.point_path`` (.ply / .las) if given, else a random ground-plane cloud."""
+def get_pcd(config, aabb=None, *reference_tail, dataset=None) -> BasicPointCloud:
+    """Initial cloud: ``config.point_path`` (.ply / .las) if given, else the sparse reconstruction of ``dataset`` when it
+    carries one (COLMAP datasets, in the dataset's own world frame), else a random ground-plane cloud.
+
+    The reference's form ``get_pcd(loaded_iter, config, aabb, logfolder, model)`` (ply_utils.py:116-144) is accepted:
+    with ``loaded_iter`` set the model loads ``config.ckpt`` and nothing is returned, otherwise the cloud is built as
+    above (COLMAP points for ``dataset_name="Colmap"``)."""
+    if reference_tail or not (hasattr(config, "get") or hasattr(config, "point_path") or hasattr(config, "init_points_num")):
+        loaded_iter, config, aabb = config, aabb, (reference_tail[0] if reference_tail else None)
+        model = reference_tail[2] if len(reference_tail) > 2 else None
+        if loaded_iter:
+            model.load_from_state_dict(model.get_state_dict_from_ckpt(config.ckpt, config.device))
+            return None
+        if not getattr(config, "point_path", None) and str(getattr(config, "dataset_name", "")).lower() == "colmap":
+            return init_ply(config.datadir, aabb, "colmap", int(getattr(config, "init_points_num", 100_000)))
+        return get_pcd(config, aabb)
     path = getattr(config, "point_path", None)
+    if not path and dataset is not None and hasattr(dataset, "initial_point_cloud"):
+        xyz, rgb = dataset.initial_point_cloud()
+        if xyz is not None and len(xyz) > 0:
+            pcd = BasicPointCloud(points=np.asarray(xyz, dtype=np.float32), colors=np.asarray(rgb, dtype=np.float32),
+                                  normals=np.zeros((len(xyz), 3), dtype=np.float32))
+            return _cap_points(pcd, int(getattr(config, "max_init_points", -1)))
     if path:
         pcd = fetchLas(path) if path.endswith(".las") else fetchPly(path)
     else:
@@ -132,7 +172,10 @@ def get_pcd(config, aabb=None) -> BasicPointCloud:
         if not getattr(config, "init_points_volume", False):
             xyz[:, 2] = lb[2]
         pcd = BasicPointCloud(points=xyz, colors=rng.random((n, 3), dtype=np.float32), normals=np.zeros_like(xyz))
-    limit = int(getattr(config, "max_init_points", -1))
+    return _cap_points(pcd, int(getattr(config, "max_init_points", -1)))
+
+
+def _cap_points(pcd: BasicPointCloud, limit: int) -> BasicPointCloud:
     if limit > 0 and len(pcd.points) > limit:
         keep = np.random.default_rng(0).choice(len(pcd.points), limit, replace=False)
         pcd = BasicPointCloud(pcd.points[keep], pcd.colors[keep], pcd.normals[keep])

@@ -17,7 +17,7 @@ class OctreeGSTrainer(ScaffoldGSTrainer):
         if cfg.start_checkpoint:
             model.load_from_state_dict(model.get_state_dict_from_ckpt(cfg.start_checkpoint, cfg.device))
         else:
-            model.create_from_pcd(get_pcd(cfg, self.aabb), self.spatial_lr_scale,
+            model.create_from_pcd(get_pcd(cfg, self.aabb, dataset=self.data_mgr.full_train_dataset), self.spatial_lr_scale,
                                   cameras=self.data_mgr.full_train_dataset.cameras)
         return model
 

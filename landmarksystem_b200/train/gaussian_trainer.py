@@ -65,7 +65,7 @@ class GaussianTrainerBase(NeRFTrainer):
             state = model.get_state_dict_from_ckpt(cfg.start_checkpoint, cfg.device)
             model.load_from_state_dict(state)
         else:
-            pcd = get_pcd(cfg, self.aabb)
+            pcd = get_pcd(cfg, self.aabb, dataset=self.data_mgr.full_train_dataset)   # SfM points when the dataset has them
             model.create_from_pcd(pcd, self.spatial_lr_scale)
         return model.to(cfg.device) if hasattr(model, "to") else model
 

@@ -387,3 +387,30 @@ def test_colmap_to_transforms_conversion(tmp_path):
     with open(tmp_path / "one_out" / "transforms_train.json", encoding="utf-8") as fh:
         meta = json.load(fh)
     assert meta["fl_x"] == 80.0 and meta["fl_y"] == 82.0 and (meta["w"], meta["h"]) == (64, 48) and len(meta["frames"]) == 17
+
+
+def test_initial_cloud_from_the_sparse_reconstruction(tmp_path):
+    """COLMAP datasets seed the Gaussians with their SfM points (reference: ply_utils.py:116-144 picks
+    ``init_type="colmap"`` for ``dataset_name="Colmap"``); both calling conventions of the helpers."""
+    from landmarksystem_b200.components.utils.ply_utils import get_pcd, init_ply
+
+    cameras, images, points = _toy_model()
+    cl.write_model_binary(str(tmp_path / "sparse" / "0"), cameras, images, points)
+    args = SimpleNamespace(datadir=str(tmp_path), eval=True, white_bkgd=False, dataset_name="Colmap", point_path=None,
+                           init_points_num=77, max_init_points=-1, random_seed=0)
+    train = gaussian_dataset_dict["Colmap"]("train", 1.0, args)
+    aabb = [[-1.0, -1.0, 0.0], [1.0, 1.0, 1.0]]
+    pcd = get_pcd(args, aabb, dataset=train)
+    assert pcd.points.shape == (50, 3) and np.allclose(pcd.points, train.initial_point_cloud()[0])
+    assert get_pcd(args, aabb).points.shape == (77, 3)                      # no dataset: the random ground-plane cloud
+    capped = get_pcd(SimpleNamespace(**dict(vars(args), max_init_points=20)), aabb, dataset=train)
+    assert capped.points.shape == (20, 3)
+
+    cloud = init_ply(str(tmp_path), aabb, "colmap", 10)                      # the reference's positional form
+    assert cloud.points.shape == (50, 3) and np.allclose(np.sort(cloud.points, 0), np.sort(points[0].astype(np.float32), 0))
+    assert os.path.exists(tmp_path / "sparse" / "0" / "points3D.ply")
+    flat = init_ply(str(tmp_path), aabb, "ply", 31)
+    assert flat.points.shape == (31, 3) and np.allclose(flat.points[:, 2], 0.0)
+    assert init_ply(str(tmp_path), aabb, 12).endswith("points3d_init.ply")  # this package's form returns the path
+    via_reference = get_pcd(None, args, aabb, str(tmp_path), None)           # (loaded_iter, config, aabb, logfolder, model)
+    assert via_reference.points.shape == (50, 3)

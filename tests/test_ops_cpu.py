@@ -171,3 +171,20 @@ def test_tcnn_shaped_front_end():
         tcnn.Encoding(3, {"otype": "Frequency"})
     with pytest.raises(ValueError):
         tcnn.Network(3, 3, {"otype": "FullyFusedMLP", "activation": "Tanh"})
+
+
+def test_pose_rotate_translate_both_calling_conventions():
+    """Camera-to-world in / out with vectors, or the reference's world-to-view in / out with three angles (positional
+    or by keyword, graphics_utils.py:88-123): the same rigid motion."""
+    import numpy as np
+
+    from landmarksystem_b200.components.data import pose_utils as pu
+    from landmarksystem_b200.components.utils.graphics_utils import pose_rotate_translate
+
+    c2w = np.concatenate((pu.viewmatrix([0.2, 1, 0.1], [0, 0, 1], [1, -3, 0.5]), [[0, 0, 0, 1]]))
+    moved = pose_rotate_translate(c2w, [10, 20, 30], [1, 2, 3])
+    assert np.allclose(moved[:3, 3], (moved[:3, :3] @ np.linalg.inv(c2w[:3, :3])) @ c2w[:3, 3] + [1, 2, 3], atol=1e-5)
+    w2v = np.linalg.inv(c2w)
+    for out in (pose_rotate_translate(w2v, 10, 20, 30, [1, 2, 3]),
+                pose_rotate_translate(w2v, rot_x=10, rot_y=20, rot_z=30, trans=[1, 2, 3])):
+        assert np.allclose(np.linalg.inv(out.astype(np.float64)), moved, atol=1e-5)
