@@ -26,7 +26,26 @@ def get_rays_with_directions(directions: torch.Tensor, c2w: torch.Tensor) -> Tup
     return rays_o.reshape(-1, 3), rays_d.reshape(-1, 3)
 
 
-def get_rays(directions, c2w, camera_mode: str = "normal"):
+def get_rays(directions, c2w, camera_mode="normal", *reference_tail, **reference_kw):
+    """``get_rays(directions [H, W, 3], c2w, camera_mode)`` -> ``(origins [H*W, 3], directions [H*W, 3])``; in
+    ``"panorama"`` mode the directions cover the full sphere (equirectangular) and only their shape is used.
+
+    The reference's form ``get_rays(H, W, K, c2w, camera_mode="normal", offset=0.5)`` (ray_utils.py:424-469) is
+    accepted as well: pixels at integer coordinates against the intrinsics ``K``, unit-length directions."""
+    if isinstance(directions, int):
+        H, W, K = directions, int(c2w), camera_mode
+        pose = reference_tail[0] if reference_tail else reference_kw["c2w"]
+        mode = reference_tail[1] if len(reference_tail) > 1 else reference_kw.get("camera_mode", "normal")
+        offset = reference_tail[2] if len(reference_tail) > 2 else reference_kw.get("offset", 0.5)
+        pose = torch.as_tensor(pose, dtype=torch.float32)
+        j, i = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+        if mode == "normal":
+            cam = torch.stack(((i - K[0][2]) / K[0][0], -(j - K[1][2]) / K[1][1], -torch.ones_like(i)), -1)
+        else:
+            theta, phi = 2 * math.pi * (i + offset) / W, math.pi * (j + offset) / H
+            cam = torch.stack((-torch.sin(phi) * torch.sin(theta), torch.cos(phi), torch.sin(phi) * torch.cos(theta)), -1)
+        o, d = get_rays_with_directions(cam, pose)
+        return o, d / d.norm(dim=-1, keepdim=True)
     if camera_mode == "normal":
         return get_rays_with_directions(directions, c2w)
     # panorama: equirectangular directions over the full sphere
@@ -57,11 +76,14 @@ def rot_theta(theta: float) -> torch.Tensor:
     return torch.tensor([[c, 0, -s, 0], [0, 1, 0, 0], [s, 0, c, 0], [0, 0, 0, 1]], dtype=torch.float32)
 
 
-def pose_spherical(theta_deg: float, phi_deg: float, radius: float) -> torch.Tensor:
-    """Camera on a sphere looking at the origin (NeRF-synthetic convention)."""
+def pose_spherical(theta_deg: float, phi_deg: float, radius: float, zval=None) -> torch.Tensor:
+    """Camera on a sphere looking at the origin (NeRF-synthetic convention); ``zval`` overrides the camera height."""
     c2w = rot_theta(math.radians(theta_deg)) @ rot_phi(math.radians(phi_deg)) @ trans_t(radius)
     flip = torch.tensor([[-1, 0, 0, 0], [0, 0, 1, 0], [0, 1, 0, 0], [0, 0, 0, 1]], dtype=torch.float32)
-    return flip @ c2w
+    c2w = flip @ c2w
+    if zval is not None:
+        c2w[2, 3] = float(zval)
+    return c2w
 
 
 def get_ray_directions(H: int, W: int, focal, center=None) -> torch.Tensor:

@@ -66,8 +66,16 @@ def get_interpolated_k(k_a: np.ndarray, k_b: np.ndarray, steps: int = 10) -> Lis
 
 
 def get_interpolated_poses_many(poses: Sequence[np.ndarray], Ks: Optional[Sequence[np.ndarray]] = None,
-                                steps_per_transition: int = 10) -> Tuple[np.ndarray, Optional[np.ndarray]]:
-    """Piecewise interpolation through all key poses (and intrinsics); returns stacked ``[N, 3, 4]`` (and ``[N, 3, 3]``)."""
+                                steps_per_transition: int = 10, order_poses: bool = False
+                                ) -> Tuple[np.ndarray, Optional[np.ndarray]]:
+    """Piecewise interpolation through all key poses (and intrinsics); returns stacked ``[N, 3, 4]`` (and ``[N, 3, 3]``).
+    ``order_poses`` first arranges the key poses as a greedy nearest-neighbour tour (:func:`get_ordered_poses_and_k`)."""
+    if order_poses:
+        stacked = torch.as_tensor(np.stack([np.asarray(p) for p in poses]), dtype=torch.float64)
+        ks = torch.as_tensor(np.stack([np.asarray(k) for k in Ks]), dtype=torch.float64) if Ks is not None else \
+            torch.zeros(len(poses), 3, 3, dtype=torch.float64)
+        stacked, ks = get_ordered_poses_and_k(stacked, ks)
+        poses, Ks = list(stacked.numpy()), (list(ks.numpy()) if Ks is not None else None)
     traj, traj_k = [], []
     for i in range(len(poses) - 1):
         traj += get_interpolated_poses(np.asarray(poses[i]), np.asarray(poses[i + 1]), steps_per_transition)

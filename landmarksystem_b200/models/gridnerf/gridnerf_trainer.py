@@ -9,6 +9,7 @@ from __future__ import annotations
 import os
 import sys
 import time
+from typing import Optional
 
 import numpy as np
 import torch
@@ -139,9 +140,10 @@ class GridNeRFTrainer(NeRFTrainer):
         suffix = f"-sub{cfg.rank}" if per_rank else ""
         return os.path.join(self.optim_dir, f"{cfg.expname}_opt{suffix}.th")
 
-    def save_optimizer(self):
+    def save_optimizer(self, path: Optional[str] = None):
+        """``{"optimizer": state_dict}`` at ``path`` (default: this run's ``optim/{expname}_opt[-sub{r}].th``)."""
         os.makedirs(self.optim_dir, exist_ok=True)
-        torch.save({"optimizer": self.optimizer.state_dict()}, self._optim_path())
+        torch.save({"optimizer": self.optimizer.state_dict()}, path or self._optim_path())
 
     def _replace_optimizer(self, groups):
         """New optimiser over ``groups`` (parameters were replaced or added); the old one's peer-mapped buffers are

@@ -194,7 +194,15 @@ class Nerfacto(BaseNeRF):
         return (native.available() and self.geo_feat_dim + c.appearance_embedding_dim <= 48
                 and fused_mlp_supported(self.mlp_base_mlp) and fused_mlp_supported(self.mlp_head))
 
-    def get_density(self, pos: torch.Tensor):
+    def get_density(self, pos: torch.Tensor, directions: Optional[torch.Tensor] = None,
+                    z_vals: Optional[torch.Tensor] = None):
+        """``(density [N, 1], geometry features [N, G])`` at world positions ``pos [N, 3]``; with the reference's
+        arguments ``(origins, directions, z_vals)`` the positions are ``origins + directions * z_vals[..., None]``."""
+        if directions is not None and z_vals is not None:
+            lead = pos.shape[:-1]
+            pos = (pos + directions * z_vals[..., None]).reshape(-1, 3)
+            sigma, geo = self.get_density(pos)
+            return sigma.reshape(*lead, 1), geo.reshape(*lead, -1)
         xyzb, inside = self._positions(pos)
         h = self.mlp_base_mlp(self.mlp_base_grid(xyzb)).float()
         raw, geo = torch.split(h, [1, self.geo_feat_dim], dim=-1)
@@ -260,8 +268,8 @@ class Nerfacto(BaseNeRF):
             out["weights_list"], out["ray_samples_list"] = weights_list, samples_list
         return out
 
-    def get_optparam_groups(self):
-        lr = self.config.lr_init
+    def get_optparam_groups(self, lr: Optional[float] = None):
+        lr = self.config.lr_init if lr is None else lr
         return [{"params": list(self.mlp_base_grid.parameters()) + list(self.mlp_base_mlp.parameters())
                  + list(self.mlp_head.parameters()) + list(self.embedding_appearance.parameters()), "lr": lr, "name": "fields"},
                 {"params": list(self.proposal_networks.parameters()), "lr": lr, "name": "proposal_networks"}]

@@ -59,10 +59,19 @@ def init_distributed_mode(env: str = "single_node", backend: str = None, timeout
     (reference: landmark/train/utils/distributed_utils.py:73-140).  ``env``: ``"single_node"`` / ``"torchrun"`` read
     ``RANK / WORLD_SIZE / LOCAL_RANK``; ``"slurm"`` derives them from ``SLURM_PROCID / SLURM_NTASKS / SLURM_LOCALID`` and
     takes the first host of ``SLURM_NODELIST`` as master; ``"aliyun"`` reads the DLC launcher's ``RANK`` (node rank),
-    ``WORLD_SIZE`` (node count) and ``LOCAL_RANK`` with ``NPROC_PER_NODE`` processes per node.  Idempotent."""
+    ``WORLD_SIZE`` (node count) and ``LOCAL_RANK`` with ``NPROC_PER_NODE`` processes per node.  Idempotent.
+
+    The reference passes its configuration object: ``init_distributed_mode(args)`` reads ``args.env`` and writes
+    ``args.rank / args.world_size / args.local_rank / args.distributed`` back."""
     import datetime
 
-    import torch
+    if not isinstance(env, str):
+        args = env
+        info = init_distributed_mode(str(getattr(args, "env", None) or "single_node"), backend, timeout_s)
+        for key, value in info.items():
+            setattr(args, key, value)
+        args.distributed = info["world_size"] > 1
+        return info
 
     if env == "slurm":
         rank, world = int(os.environ["SLURM_PROCID"]), int(os.environ["SLURM_NTASKS"])

@@ -414,3 +414,40 @@ def test_initial_cloud_from_the_sparse_reconstruction(tmp_path):
     assert init_ply(str(tmp_path), aabb, 12).endswith("points3d_init.ply")  # this package's form returns the path
     via_reference = get_pcd(None, args, aabb, str(tmp_path), None)           # (loaded_iter, config, aabb, logfolder, model)
     assert via_reference.points.shape == (50, 3)
+
+
+def test_get_rays_in_the_reference_form():
+    from landmarksystem_b200.components.data.datasets import ray_utils as ru
+
+    H, W, f = 6, 8, 12.0
+    K = torch.tensor([[f, 0, W / 2], [0, f, H / 2], [0, 0, 1.0]])
+    pose = ru.pose_spherical(40.0, -30.0, 3.0, zval=1.25)
+    assert float(pose[2, 3]) == 1.25
+    o, d = ru.get_rays(H, W, K, pose)                                 # reference: (H, W, K, c2w)
+    assert o.shape == (H * W, 3) and torch.allclose(d.norm(dim=-1), torch.ones(H * W), atol=1e-6)
+    dirs = ru.get_ray_directions_blender(H, W, f) - torch.tensor([0.5 / f, -0.5 / f, 0.0])      # integer pixel coordinates
+    o2, d2 = ru.get_rays(dirs, pose)                                  # this package: (directions, c2w)
+    assert torch.allclose(o, o2) and torch.allclose(d, d2 / d2.norm(dim=-1, keepdim=True), atol=1e-6)
+    po, pd = ru.get_rays(H, W, K, pose, "panorama")
+    qo, qd = ru.get_rays(dirs, pose, "panorama")
+    assert torch.allclose(pd, qd / qd.norm(dim=-1, keepdim=True), atol=1e-5)
+
+
+def test_interpolation_through_ordered_key_poses_and_args_style_distributed_init(monkeypatch):
+    poses = [np.eye(4)[:3] for _ in range(4)]
+    for k, x in enumerate((0.0, 3.0, 1.0, 2.0)):
+        poses[k] = poses[k].copy()
+        poses[k][0, 3] = x
+    plain, _ = pu.get_interpolated_poses_many(poses, None, steps_per_transition=2)
+    tour, _ = pu.get_interpolated_poses_many(poses, None, steps_per_transition=2, order_poses=True)
+    assert plain.shape == tour.shape == (6, 3, 4)
+    assert np.all(np.diff(tour[:, 0, 3]) >= -1e-9) and not np.all(np.diff(plain[:, 0, 3]) >= 0)   # the tour never turns back
+
+    from landmarksystem_b200.train.utils import init_distributed_mode
+
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(name, raising=False)
+    args = SimpleNamespace(env="single_node")
+    info = init_distributed_mode(args)                       # the reference passes its configuration object
+    assert info == {"rank": 0, "world_size": 1, "local_rank": 0}
+    assert (args.rank, args.world_size, args.local_rank, args.distributed) == (0, 1, 0, False)
