@@ -23,13 +23,24 @@ def _reinstantiate(module: BaseModule, new_cls, **extra):
 
 
 class BaseConvertor:
-    def convert(self, model: nn.Module, config) -> nn.Module:
+    def convert(self, model: nn.Module, config, state_dict=None, verbose: bool = False) -> nn.Module:
+        """``state_dict``: a full checkpoint to load into the model before the conversion (the reference passes the
+        state it wants the converted components to start from, convertor_factory.py:77-127); ``verbose`` prints the
+        class swaps."""
         raise NotImplementedError
+
+    @staticmethod
+    def _preload(model, state_dict):
+        if state_dict is not None:
+            loader = getattr(model, "load_from_state_dict", None)
+            loader(state_dict, False) if loader is not None else model.load_state_dict(state_dict, strict=False)
 
 
 class ParallelConvertor(BaseConvertor):
-    def convert(self, model, config):
+    def convert(self, model, config, state_dict=None, verbose: bool = False):
         from .convert_maps import PARALLEL_MAPS
+
+        self._preload(model, state_dict)
 
         if getattr(config, "channel_parallel", False):
             table, degree = PARALLEL_MAPS["ChannelParallel"], int(config.channel_parallel_size)
@@ -51,6 +62,8 @@ class ParallelConvertor(BaseConvertor):
                                  init_state_dict=init_state)
             if getattr(child, "use_shadow", False):
                 new.enable_shadow(getattr(config, "fused_optimizer", True), getattr(child, "lazy", False))
+            if verbose:
+                print(f"{name}: {type(child).__name__} -> {new_cls.__name__} (part {part} of {degree})", flush=True)
             setattr(model, name, new)
         return model
 
@@ -58,8 +71,10 @@ class ParallelConvertor(BaseConvertor):
 class RuntimeConvertor(BaseConvertor):
     """``runtime == "Kernel"``: swap components for their fused counterparts, keeping the weights."""
 
-    def convert(self, model, config=None):
+    def convert(self, model, config=None, state_dict=None, verbose: bool = False):
         from .convert_maps import KERNEL_FUSION_MAP
+
+        self._preload(model, state_dict)
 
         def walk(parent):
             for name, child in list(parent.named_children()):
@@ -68,6 +83,8 @@ class RuntimeConvertor(BaseConvertor):
                     new = _reinstantiate(child, new_cls)
                     new.load_state_dict(child.state_dict(), strict=False)
                     new.to(next(child.parameters()).device if any(True for _ in child.parameters()) else "cpu")
+                    if verbose:
+                        print(f"{name}: {type(child).__name__} -> {new_cls.__name__}", flush=True)
                     setattr(parent, name, new)
                 else:
                     walk(child)
@@ -87,7 +104,8 @@ class ComponentConvertorFactory:
     _TABLE = {"parallelize": ParallelConvertor, "runtime": RuntimeConvertor}
 
     @staticmethod
-    def get_convertor(convertor_type: str) -> BaseConvertor:
+    def get_convertor(convertor_type: str = None, convert_type: str = None) -> BaseConvertor:
+        convertor_type = convertor_type if convertor_type is not None else convert_type    # the reference's keyword
         assert convertor_type in ComponentConvertorFactory._TABLE, f"unknown convertor '{convertor_type}'"
         return ComponentConvertorFactory._TABLE[convertor_type]()
 

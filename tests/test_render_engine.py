@@ -365,3 +365,21 @@ def test_dynamic_loading_prefetches_ahead_of_a_scripted_camera_track(tmp_path):
     assert ahead > 0
     stats0, ahead0 = fly(0)
     assert stats0["stalled_frames"] == 0 and ahead0 == 0
+
+
+def test_runtime_convertor_takes_a_state_dict_and_reports_swaps(tmp_path, capsys):
+    """``convert(model, config, state_dict, verbose)`` as the reference calls it (convertor_factory.py:77-127)."""
+    from landmarksystem_b200.components.fields.fused_mlp_decoder import FusedMLPDecoder
+    from landmarksystem_b200.convertor import ComponentConvertorFactory
+
+    source = _save_random_model(tmp_path, [1, 1])
+    cfg = _model_config(tmp_path, [1, 1])
+    sm = SceneManager(cfg)
+    torch.manual_seed(5)
+    fresh = GridNeRF(sm.aabb, [32, 32, 16], "cpu", near_far=[0.5, 6.0], scene_manager=sm, config=cfg)
+    state = torch.load(str(tmp_path / "state_dict.th"), weights_only=False)
+    converted = ComponentConvertorFactory.get_convertor(convert_type="runtime").convert(fresh, cfg, state, True)
+    printed = capsys.readouterr().out
+    assert "->" in printed and any(isinstance(m, FusedMLPDecoder) for m in converted.modules())
+    for (name, a), (_, b) in zip(source.state_dict().items(), converted.state_dict().items()):
+        assert torch.allclose(a, b), name
