@@ -12,7 +12,10 @@ from .tensor_dataclass import TensorDataClass
 class Rays(TensorDataClass):
     def __init__(self, origin: Optional[torch.Tensor] = None, dirs: Optional[torch.Tensor] = None,
                  camera_idx: Optional[torch.Tensor] = None, near=None, far=None, data: Optional[torch.Tensor] = None,
-                 rank=None, group=None):
+                 rank=None, group=None, device=None, _data: Optional[torch.Tensor] = None):
+        """``device`` (move the packed tensor there) and ``_data`` (alias of ``data``) are the reference's keywords
+        (rays.py:8-40)."""
+        data = data if data is not None else _data
         if data is None:
             assert origin is not None and dirs is not None, "Rays needs origin and dirs (or packed data)"
             if camera_idx is None:
@@ -23,7 +26,7 @@ class Rays(TensorDataClass):
         elif data.shape[-1] == 6:
             data = torch.cat((data, torch.zeros_like(data[..., :1])), dim=-1)
         assert data.shape[-1] == 7, "packed rays are [..., 7]"
-        super().__init__(data, rank, group)
+        super().__init__(data if device is None else data.to(device), rank, group)
         self.near, self.far = near, far
 
     @property

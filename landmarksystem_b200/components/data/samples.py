@@ -25,7 +25,9 @@ class Samples(TensorDataClass):
     def __init__(self, xyz: Optional[torch.Tensor] = None, dirs: Optional[torch.Tensor] = None,
                  z_vals: Optional[torch.Tensor] = None, camera_idx: Optional[torch.Tensor] = None,
                  block_idx: Optional[torch.Tensor] = None, sigma: Optional[torch.Tensor] = None,
-                 rgb: Optional[torch.Tensor] = None, data: Optional[torch.Tensor] = None, rank=None, group=None):
+                 rgb: Optional[torch.Tensor] = None, data: Optional[torch.Tensor] = None, rank=None, group=None,
+                 device=None, _data: Optional[torch.Tensor] = None):
+        data = data if data is not None else _data          # ``_data`` / ``device``: the reference's keywords
         self._has_z_vals = z_vals is not None
         self._has_camera_idx = camera_idx is not None
         self._has_block_idx = block_idx is not None
@@ -49,7 +51,7 @@ class Samples(TensorDataClass):
                 data[..., _RGB] = rgb
         else:
             self._has_z_vals = self._has_camera_idx = self._has_block_idx = True
-        super().__init__(data, rank, group)
+        super().__init__(data if device is None else data.to(device), rank, group)
 
     # -- field views ------------------------------------------------------------
     @property
