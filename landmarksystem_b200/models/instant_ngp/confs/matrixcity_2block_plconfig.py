@@ -2,3 +2,4 @@
 from landmarksystem_b200.models.instant_ngp.confs._matrixcity import train
 
 config = train("plconfig")
+train_config, dataset_config, model_config = config        # the blocks by name, for files that import this one with *

@@ -2,3 +2,4 @@
 from landmarksystem_b200.models.scaffold_gs.confs._matrixcity import train
 
 config = train()
+train_config, dataset_config, model_config = config        # the blocks by name, for files that import this one with *
