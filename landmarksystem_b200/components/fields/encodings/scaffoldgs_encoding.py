@@ -56,8 +56,11 @@ def segment_amax(values: torch.Tensor, index: torch.Tensor, n_segments: int) -> 
 class ScaffoldGSEncoding(BaseGaussianEncoding):
     def __init__(self, feat_dim: int = 32, n_offsets: int = 10, voxel_size: float = 0.01, update_depth: int = 3,
                  update_init_factor: int = 16, update_hierachy_factor: int = 4, percent_dense: float = 0.01,
-                 device="cuda"):
+                 device="cuda", use_feat_bank: bool = False):
+        # ``use_feat_bank`` is accepted as in the reference (scaffoldgs_encoding.py, constructor); the feature bank
+        # itself lives in the anchor decoder
         super().__init__()
+        self.use_feat_bank = bool(use_feat_bank)
         dev = device if (torch.cuda.is_available() or str(device) == "cpu") else "cpu"
         self.device = torch.device(dev)
         self.feat_dim, self.n_offsets, self.voxel_size = feat_dim, n_offsets, voxel_size
