@@ -148,6 +148,7 @@ class DatasetManager:
     def divide_dataset(self, plane_division, aabb_xy):
         """Assign each training camera to the XY cell under its centre; returns cells' camera counts."""
         nx, ny = plane_division
+        self._cells_ny = int(ny)
         (x0, y0), (x1, y1) = aabb_xy
         self.cells = [[] for _ in range(nx * ny)]
         for i, cam in enumerate(self.full_train_dataset.cameras):
@@ -157,7 +158,11 @@ class DatasetManager:
             self.cells[bx * ny + by].append(i)
         return [len(c) for c in self.cells]
 
-    def switch_cell(self, cell_idx: int):
+    def switch_cell(self, cell_idx):
+        """``cell_idx``: row-major cell index, or the reference's ``(bx, by)`` block coordinate."""
+        if not isinstance(cell_idx, int):
+            bx, by = (int(v) for v in cell_idx)
+            cell_idx = bx * int(self._cells_ny) + by
         self.iter_cnt = 0
         self.train_dataset = torch.utils.data.Subset(self.full_train_dataset, self.cells[cell_idx])
         self._build_train_loader()

@@ -314,7 +314,16 @@ class GaussianEncoding(BaseGaussianEncoding):
         self.xyz_gradient_accum, self.denom = self.xyz_gradient_accum[keep], self.denom[keep]
         self.max_radii2D = self.max_radii2D[keep]
 
-    def densification_postfix(self, new: Dict[str, torch.Tensor], optimizer):
+    def densification_postfix(self, new, *rest, optimizer=None):
+        """Append new Gaussians: ``densification_postfix({"xyz": ..., "f_dc": ..., "f_rest": ..., "opacity": ...,
+        "scaling": ..., "rotation": ...}, optimizer)``, or the reference's positional form ``(new_xyz, new_features_dc,
+        new_features_rest, new_opacities, new_scaling, new_rotation, optimizer)`` (gaussian_encoding.py:498-542)."""
+        if torch.is_tensor(new):
+            tensors = (new,) + tuple(rest[:5])
+            optimizer = rest[5] if len(rest) > 5 else optimizer
+            new = dict(zip(("xyz", "f_dc", "f_rest", "opacity", "scaling", "rotation"), tensors))
+        else:
+            optimizer = rest[0] if rest else optimizer
         self._adopt(cat_tensors_to_optimizer(optimizer, new))
         n = self._xyz.shape[0]
         self.xyz_gradient_accum = torch.zeros(n, 1, device=self._xyz.device)

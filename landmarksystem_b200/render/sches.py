@@ -13,29 +13,29 @@ from .instructions import (BroadcastInputsInstruction, CallInstruction, DefModIn
 
 
 class AbstractSche:
-    def steps(self) -> List[type]:
+    def steps(self, rank=None) -> List[type]:
         raise NotImplementedError
 
 
 class InferenceSche(AbstractSche):
-    def steps(self):
+    def steps(self, rank=None):       # ``rank``: accepted as in the reference; the list is the same on every rank
         return [DefModInstruction, PreprocessInstruction, CallInstruction, PostprocessInstruction]
 
 
 class MultiDeviceSche(InferenceSche):
-    def steps(self):
+    def steps(self, rank=None):       # ``rank``: accepted as in the reference; the list is the same on every rank
         return [DefModInstruction, BroadcastInputsInstruction, PreprocessInstruction, CallInstruction,
                 PostprocessInstruction]
 
 
 class DDPSche(MultiDeviceSche):
-    def steps(self):
+    def steps(self, rank=None):       # ``rank``: accepted as in the reference; the list is the same on every rank
         return [DefModInstruction, BroadcastInputsInstruction, PreprocessInstruction, DPScatterInstruction,
                 CallInstruction, DPGatherInstruction, PostprocessInstruction]
 
 
 class DDPPipeSche(DDPSche):
-    def steps(self):
+    def steps(self, rank=None):       # ``rank``: accepted as in the reference; the list is the same on every rank
         return [DefModInstruction, BroadcastInputsInstruction, PreprocessInstruction, DPScatterInstruction,
                 PipeSubmitInstruction, PipeGetResultInstruction, DPGatherInstruction, PostprocessInstruction]
 

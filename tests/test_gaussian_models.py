@@ -355,3 +355,35 @@ def test_gpu_training_improves_psnr(family, trainer_name, gain, tmp_path):
     before = trainer.evaluation(str(tmp_path / "before"), stride=1)
     after = trainer.train()
     assert after > before + gain, (before, after)
+
+
+def test_camera_cells_and_positional_densification(tmp_path):
+    """Per-block camera subsets of the data manager (``divide_dataset / switch_cell / use_all_data``, reference:
+    data_manager.py:196-329) and the reference's positional form of ``densification_postfix``."""
+    from landmarksystem_b200.components.data.data_manager import DatasetManager
+
+    conf = os.path.join(ROOT, "origin_gs", "confs", "synthetic_train.py")
+    cfg = BaseConfig.from_file(conf, {"basedir": str(tmp_path), "device": "cpu", "datadir": "ring:8:8x8:10:3"})
+    mgr = DatasetManager(cfg)
+    total = mgr.train_data_size
+    counts = mgr.divide_dataset([2, 2], ((-4.0, -4.0), (4.0, 4.0)))
+    assert sum(counts) == total == 8 and len(counts) == 4 and max(counts) < total
+    mgr.switch_cell((1, 0))                                       # block coordinate -> cell 2
+    assert mgr.train_data_size == counts[2]
+    cam, image = mgr.get_camera("train")
+    assert float(cam.camera_center[0]) >= 0.0 and float(cam.camera_center[1]) < 0.0
+    mgr.switch_cell(3)
+    assert mgr.train_data_size == counts[3]
+    mgr.use_all_data()
+    assert mgr.train_data_size == total
+
+    enc = GaussianEncoding(1, device="cpu")
+    enc.create_from_pcd(_pcd(10))
+    groups = [{"params": [getattr(enc, a)], "lr": 1e-3, "name": n} for n, a in
+              (("xyz", "_xyz"), ("f_dc", "_features_dc"), ("f_rest", "_features_rest"), ("opacity", "_opacity"),
+               ("scaling", "_scaling"), ("rotation", "_rotation"))]
+    opt = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
+    enc.densification_postfix(torch.ones(3, 3), torch.zeros(3, 1, 3), torch.zeros(3, 3, 3), torch.zeros(3, 1),
+                              torch.zeros(3, 3), torch.tensor([[1.0, 0, 0, 0]]).repeat(3, 1), opt)
+    assert len(enc) == 13 and torch.equal(enc.get_xyz[-3:], torch.ones(3, 3)) and enc.denom.shape[0] == 13
+    assert all(g["params"][0].shape[0] == 13 for g in opt.param_groups)
