@@ -34,7 +34,7 @@ import numpy as np
 import torch
 
 
-def _rng_state() -> Dict[str, Any]:
+def capture_rng_state() -> Dict[str, Any]:
     state = {"torch": torch.get_rng_state(), "numpy": np.random.get_state(), "python": random.getstate()}
     if torch.cuda.is_available():
         state["cuda"] = torch.cuda.get_rng_state()
@@ -203,7 +203,7 @@ class AsyncCheckpointer:
                 cur.wait_event(event)        # no staging copy: later work of the training stream waits for the reads
         else:
             host_state = _to_host(state)
-        rng = _rng_state()
+        rng = capture_rng_state()
         payload_meta = dict(meta or {}, world=world, time=time.time(), format="lmb200-sharded-v1")
 
         def rendezvous(phase: str):
