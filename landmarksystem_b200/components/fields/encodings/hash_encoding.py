@@ -89,6 +89,8 @@ class HashEncoding(VolumeEncoding):
         block = xyz[:, 3].long()
         out = torch.zeros(xyz.shape[0], self.meta.out_dim, device=xyz.device, dtype=torch.float32)
         for b, table in enumerate(self.tables()):
+            if table.params.numel() == 0:        # not resident (dynamic loading): its samples are masked by the caller
+                continue
             idx = (block == b).nonzero(as_tuple=True)[0]
             if idx.numel():
                 out = out.index_put((idx,), self._encode(xyz[idx, :3], table))

@@ -156,6 +156,8 @@ def hashgrid_encode(x: torch.Tensor, table: torch.Tensor, meta: HashGridMeta, ou
     table gradient instead of a fresh tensor (both default to the attributes a fused optimiser attached to ``table``);
     ``precomputed``: the result of an earlier lookup of the same samples with the same table - returned as is, so that only
     the backward is computed."""
+    if table.numel() < meta.n_params:           # a table smaller than the level layout would be read out of bounds
+        raise ValueError(f"hash table holds {table.numel()} values, the level layout needs {meta.n_params}")
     if not x.is_cuda:
         return hashgrid_reference(x, table, meta).to(out_dtype)
     if shadow is None:
