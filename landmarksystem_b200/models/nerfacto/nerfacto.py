@@ -208,6 +208,15 @@ class Nerfacto(BaseNeRF):
         raw, geo = torch.split(h, [1, self.geo_feat_dim], dim=-1)
         return self._mp_sum(trunc_exp(raw) * inside[:, None]), self._mp_sum(geo * inside[:, None])
 
+    @property
+    def proposal_sampler(self):
+        """The proposal sampler under the reference's attribute name (nerfacto.py:168)."""
+        return self.sampler
+
+    def step_cb(self, step: int) -> None:
+        """Per-iteration callback of the sampler's update schedule and annealing."""
+        self.sampler.step_cb(step)
+
     def density_fn(self, positions: torch.Tensor) -> torch.Tensor:
         """Density only, at world positions ``[..., 3]`` (reference: nerfacto.py:228-236)."""
         return self.get_density(positions.reshape(-1, 3))[0].reshape(*positions.shape[:-1], 1)

@@ -113,6 +113,9 @@ def test_cpu_smoke(family, module, cls, tmp_path):
         with torch.no_grad():
             assert m.density_fn(pts).shape == (5, 7, 1)
             assert m.proposal_networks.get_density(pts.reshape(-1, 3), 1).shape[0] == 35
+        assert m.proposal_sampler is m.sampler
+        m.step_cb(7)
+        assert m.sampler._step == 7
         half = m.set_anneal(cfg.proposal_weights_anneal_max_num_iters // 2)
         b = cfg.proposal_weights_anneal_slope
         assert abs(half - b * 0.5 / ((b - 1) * 0.5 + 1)) < 1e-9 and m.sampler._anneal == half and m.set_anneal(10 ** 9) == 1.0
