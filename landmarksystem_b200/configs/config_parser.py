@@ -61,6 +61,22 @@ def _coerce(name: str, raw, target_type):
         raise ValueError(f"Invalid value {raw} for argument {name}.") from exc
 
 
+def _from_text(raw):
+    if not isinstance(raw, str):
+        return raw
+    low = raw.lower()
+    if low in ("none", "null"):
+        return None
+    if low in ("true", "false"):
+        return low == "true"
+    for kind in (int, float):
+        try:
+            return kind(raw)
+        except ValueError:
+            pass
+    return raw
+
+
 class BaseConfig(Config):
     """Flattened run configuration."""
 
@@ -98,6 +114,11 @@ class BaseConfig(Config):
                 import torch
 
                 cfg[key] = torch.device(str(raw))
+                continue
+            if cfg[key] is None:
+                # a field that is unset in the file (``ckpt``, ``kwargs``, ``point_path``, ...) carries no type to coerce
+                # to: take the text as it stands, with the usual spellings of none / numbers / booleans recognised
+                cfg[key] = _from_text(raw)
                 continue
             assert target in _SCALARS, \
                 f"Unsupported type {target} for argument {key}, please set this argument in config file."

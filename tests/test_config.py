@@ -204,3 +204,16 @@ def test_env_switch_parsing_and_slurm_discovery(monkeypatch):
             monkeypatch.delenv(name, raising=False)
         EnvSetting.refresh()
     assert not EnvSetting.SLURM and EnvSetting.WORLD_SIZE == 1
+
+
+def test_console_override_of_a_field_the_file_leaves_unset(tmp_path):
+    conf = tmp_path / "conf.py"
+    conf.write_text(textwrap.dedent("""
+        from landmarksystem_b200.configs import DatasetConfig, TrainConfig
+        config = [TrainConfig(model_name="m", expname="x", n_iters=1), DatasetConfig(datadir="d", lb=[0, 0, 0], ub=[1, 1, 1])]
+    """))
+    assert BaseConfig.from_file(str(conf)).ckpt is None
+    cfg = BaseConfig.from_file(str(conf), parse_console_args(["--ckpt", "log/x/state_dict.th"]))
+    assert cfg.ckpt == "log/x/state_dict.th"
+    assert BaseConfig.from_file(str(conf), {"ckpt": "none"}).ckpt is None
+    assert BaseConfig.from_file(str(conf), {"ckpt": "12"}).ckpt == 12

@@ -46,3 +46,22 @@ def test_train_then_evaluate_cpu(family, tmod, tcls, emod, ecls, conf, extra, tm
         assert ev.render_path() == 3
         frames = sorted(f for f in os.listdir(os.path.join(ev.logfolder, "imgs_path_all")) if f.startswith("path_"))
         assert len(frames) == 3
+
+
+def test_command_line_entry_points_train_evaluate_and_render_a_path(tmp_path):
+    """``python -m ...gridnerf_trainer --config ... --key value`` then ``...gridnerf_evaluator --ckpt auto --render_path
+    True``: console overrides (also of fields the file leaves unset), checkpoint discovery by experiment name, test
+    views and a fly-around written by one evaluator call."""
+    import glob
+
+    from landmarksystem_b200.models.gridnerf import gridnerf_evaluator, gridnerf_trainer
+
+    conf = os.path.join(ROOT, "gridnerf", "confs", "synthetic_tiny.py")
+    common = ["--config", conf, "--basedir", str(tmp_path), "--device", "cpu", "--datadir", "ring:3:12x12:14:3",
+              "--batch_size", "64", "--nSamples", "24", "--N_vis", "-1"]
+    gridnerf_trainer.main(common + ["--n_iters", "3", "--progress_refresh_rate", "100"])
+    run = glob.glob(str(tmp_path / "*"))[0]
+    gridnerf_evaluator.main(common + ["--ckpt", "auto", "--render_path", "True", "--render_spherical", "True",
+                                      "--render_nframes", "2", "--render_px", "9", "--render_spherical_radius", "3.0"])
+    assert sorted(os.listdir(os.path.join(run, "imgs_path_all"))) == ["path_000.png", "path_001.png"]
+    assert any(f.endswith(".png") for f in os.listdir(os.path.join(run, "imgs_test_all")))
