@@ -198,6 +198,19 @@ class GaussianSplattingDataset(BaseDataset):
         self.preload = preload
         self.cameras_extent = 1.0
 
+    def resolution_factor(self, original_width: int, resolution_scale: float = 1.0) -> float:
+        """Extra size divisor from the ``resolution`` field of the configuration (reference:
+        base_dataset.py:344-358): ``-1`` keeps the size, ``1 / 2 / 4 / 8`` divide it, any other number is the target
+        width in pixels; ``resolution_scale`` multiplies the divisor (multi-scale training).  Camera size, focal length
+        and the loaded image all follow the same divisor, so renders and ground truth keep matching."""
+        resolution = getattr(self.args, "resolution", -1) if self.args is not None else -1
+        resolution = -1 if resolution is None else resolution
+        if resolution == -1:
+            return float(resolution_scale)
+        if resolution in (1, 2, 4, 8):
+            return float(resolution) * float(resolution_scale)
+        return float(original_width) / float(resolution) * float(resolution_scale)
+
     def load_image(self, cam: Camera) -> torch.Tensor:
         if cam.image is not None:
             return cam.image

@@ -64,10 +64,11 @@ class ColmapGaussianDataset(GaussianSplattingDataset):
                 continue
             cc = cams[im.camera_id]
             fx, fy = cc.focal()
-            W, H = int(round(cc.width / ds)), int(round(cc.height / ds))
+            ds_cam = ds * self.resolution_factor(cc.width)
+            W, H = int(round(cc.width / ds_cam)), int(round(cc.height / ds_cam))
             R = im.rotation().T                                   # camera-to-world rotation, as Camera.R expects
             T = im.tvec - im.rotation() @ shift                   # world moved by `shift`
-            cam = Camera(uid=len(cameras), image_width=W, image_height=H, FoVx=_fov(fx / ds, W), FoVy=_fov(fy / ds, H),
+            cam = Camera(uid=len(cameras), image_width=W, image_height=H, FoVx=_fov(fx / ds_cam, W), FoVy=_fov(fy / ds_cam, H),
                          R=R.astype(np.float32), T=T.astype(np.float32), image_name=os.path.basename(im.name))
             cam.image_path = os.path.join(args.datadir, image_dir, im.name)
             if preload:

@@ -175,4 +175,5 @@ class CityGaussianDataset(GaussianSplattingDataset):
         else:
             assert "camera_angle_x" in meta, "transforms file gives neither a focal length nor camera_angle_x"
             fx0 = fy0 = 0.5 * W0 / math.tan(0.5 * float(meta["camera_angle_x"]))
+        ds = ds * self.resolution_factor(W0)
         return int(W0 / ds), int(H0 / ds), fx0 / ds, fy0 / ds

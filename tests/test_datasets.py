@@ -451,3 +451,27 @@ def test_interpolation_through_ordered_key_poses_and_args_style_distributed_init
     info = init_distributed_mode(args)                       # the reference passes its configuration object
     assert info == {"rank": 0, "world_size": 1, "local_rank": 0}
     assert (args.rank, args.world_size, args.local_rank, args.distributed) == (0, 1, 0, False)
+
+
+def test_resolution_field_scales_the_cameras(tmp_path):
+    """``resolution``: ``-1`` keeps the size, ``1 / 2 / 4 / 8`` divide it, another number is the target width
+    (reference: base_dataset.py:344-358); the field of view does not change, the loaded image follows the camera."""
+    from PIL import Image
+
+    cameras, images, points = _toy_model()
+    cl.write_model_binary(str(tmp_path / "sparse" / "0"), cameras, images, points)
+    os.makedirs(tmp_path / "images")
+    for im in images.values():
+        cam = cameras[im.camera_id]
+        Image.fromarray(np.zeros((cam.height, cam.width, 3), np.uint8)).save(tmp_path / "images" / im.name)
+
+    def first(resolution):
+        args = SimpleNamespace(datadir=str(tmp_path), eval=True, white_bkgd=False, resolution=resolution)
+        return gaussian_dataset_dict["colmap"]("train", 1.0, args)
+
+    full, half, width16 = first(-1), first(2), first(16)
+    a, b, c = full.cameras[0], half.cameras[0], width16.cameras[0]                 # camera 2 of the toy model: 32 x 24
+    assert (a.image_width, a.image_height) == (32, 24) and (b.image_width, b.image_height) == (16, 12)
+    assert (c.image_width, c.image_height) == (16, 12)
+    assert abs(a.FoVx - b.FoVx) < 1e-6 and abs(a.FoVy - c.FoVy) < 1e-6
+    assert half.load_image(b).shape == (3, 12, 16)
