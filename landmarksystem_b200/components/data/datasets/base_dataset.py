@@ -221,11 +221,31 @@ class GaussianSplattingDataset(BaseDataset):
             img = img.resize((cam.image_width, cam.image_height), Image.LANCZOS)
         return torch.from_numpy(np.asarray(img, dtype=np.float32) / 255.0).permute(2, 0, 1).contiguous()
 
+    @property
+    def resolution_scales(self) -> List[float]:
+        scales = getattr(self.args, "resolution_scales", None) if self.args is not None else None
+        return [float(s) for s in scales] if scales else [1.0]
+
     def __len__(self):
-        return len(self.cameras)
+        return len(self.cameras) * len(self.resolution_scales)
 
     def __getitem__(self, i):
-        cam = self.cameras[i]
+        """Item ``i`` is camera ``i // n_scales`` at scale ``i % n_scales`` of ``resolution_scales`` (reference:
+        base_dataset.py:314-331): the same view with width and height divided by the scale (field of view unchanged),
+        ``resolution_scale`` set on the camera - Octree-GS picks coarser levels for it - and the image loaded at that size."""
+        scales = self.resolution_scales
+        cam = self.cameras[i // len(scales)]
+        scale = scales[i % len(scales)]
+        if scale != 1.0:
+            import dataclasses
+
+            full = cam.image
+            cam = dataclasses.replace(cam, image_width=max(int(round(cam.image_width / scale)), 1),
+                                      image_height=max(int(round(cam.image_height / scale)), 1),
+                                      resolution_scale=scale, image=None)
+            if full is not None:                 # images held in memory (preloaded / synthetic): resample them
+                cam.image = torch.nn.functional.interpolate(full[None].float(), size=(cam.image_height, cam.image_width),
+                                                            mode="bilinear", align_corners=False, antialias=True)[0]
         return cam, self.load_image(cam)
 
     @staticmethod

@@ -475,3 +475,21 @@ def test_resolution_field_scales_the_cameras(tmp_path):
     assert (c.image_width, c.image_height) == (16, 12)
     assert abs(a.FoVx - b.FoVx) < 1e-6 and abs(a.FoVy - c.FoVy) < 1e-6
     assert half.load_image(b).shape == (3, 12, 16)
+
+
+def test_multi_scale_items_of_the_camera_dataset(tmp_path):
+    """``resolution_scales=[1, 2]``: twice as many items; odd items are the same views at half size with
+    ``resolution_scale`` set and an image of that size (reference: base_dataset.py:314-331)."""
+    from landmarksystem_b200.components.data.datasets import gaussian_dataset_dict as table
+
+    args = SimpleNamespace(datadir="ring:3:16x12:14:3", lb=[-1, -1, -1], ub=[1, 1, 1], white_bkgd=False,
+                           resolution_scales=[1.0, 2.0])
+    ds = table["synthetic"]("train", 1.0, args)
+    assert len(ds) == 2 * len(ds.cameras) == 6
+    cam0, img0 = ds[2]
+    cam1, img1 = ds[3]
+    assert cam0.uid == cam1.uid and cam0.resolution_scale == 1.0 and cam1.resolution_scale == 2.0
+    assert (cam1.image_width, cam1.image_height) == (cam0.image_width // 2, cam0.image_height // 2)
+    assert img1.shape[-2:] == (cam1.image_height, cam1.image_width) and img0.shape[-2:] == (cam0.image_height, cam0.image_width)
+    assert abs(cam0.FoVx - cam1.FoVx) < 1e-9 and torch.equal(cam0.full_proj_transform, cam1.full_proj_transform)
+    assert abs(float(img0.mean()) - float(img1.mean())) < 0.05
