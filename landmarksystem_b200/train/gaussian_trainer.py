@@ -133,8 +133,11 @@ class GaussianTrainerBase(NeRFTrainer):
                 if is_main_rank():
                     print(f"[{cfg.expname}] iter {self.iteration:06d} loss {ema:.5f} psnr {ps:.2f} primitives {n} "
                           f"({(time.time() - t0) / (self.iteration - cfg.start_iters) * 1e3:.1f} ms/it)", flush=True)
-                    self.logger.log(self.iteration, {"train_loss/l1_loss": float(Ll1), "train_loss/total_loss": lv,
-                                                     "train_psnr": ps, "primitives_num": n})
+                    scalars = {"train_loss/l1_loss": float(Ll1), "train_loss/total_loss": lv, "train_psnr": ps,
+                               "primitives_num": n}
+                    if torch.device(cfg.device).type == "cuda":       # tag of the reference (origin_gs/gs_trainer.py:168-178)
+                        scalars["gpu/cur_memory_allocated"] = torch.cuda.memory_allocated() / 2 ** 20
+                    self.logger.log(self.iteration, scalars)
             if self.iteration in cfg.save_iterations:
                 self.save()
             if self.iteration in cfg.test_iterations:
