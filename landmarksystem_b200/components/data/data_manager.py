@@ -164,7 +164,9 @@ class DatasetManager:
             bx, by = (int(v) for v in cell_idx)
             cell_idx = bx * int(self._cells_ny) + by
         self.iter_cnt = 0
-        self.train_dataset = torch.utils.data.Subset(self.full_train_dataset, self.cells[cell_idx])
+        n_scales = len(getattr(self.full_train_dataset, "resolution_scales", [1.0]))
+        items = [c * n_scales + k for c in self.cells[cell_idx] for k in range(n_scales)]    # every scale of the cell's cameras
+        self.train_dataset = torch.utils.data.Subset(self.full_train_dataset, items)
         self._build_train_loader()
 
     def use_all_data(self):
